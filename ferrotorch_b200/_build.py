@@ -1,0 +1,123 @@
+"""In-tree build of the native libraries.
+
+Two shared objects are produced under ``ferrotorch_b200/_C``:
+
+* ``libft_kernels.so``  - every ``csrc/kernels/*.cu`` compiled by nvcc for
+  ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a``), CUDA runtime
+  linked statically, no link-time dependency on the driver library, so the
+  library imports on a machine without a GPU.
+* ``libft_runtime.so``  - the host runtime in ``csrc/runtime/*.cpp`` (TCP
+  backend, collectives, CPU tensor/autograd core, data loader, serializers,
+  JIT IR ...), plain C++20.
+
+Objects are rebuilt only when the source (or a header) is newer than the object.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+OUT = ROOT / "_C"
+OBJ = OUT / "obj"
+
+NVCC = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+CXX = os.environ.get("CXX") or shutil.which("g++") or "g++"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
+    "-I", str(CSRC / "kernels"), "-I", str(CSRC / "include"),
+]
+CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread", "-I", str(CSRC / "include"), "-I", str(CSRC / "runtime")]
+
+
+def _newest_header_mtime(dirs) -> float:
+    m = 0.0
+    for d in dirs:
+        for ext in ("*.h", "*.hpp", "*.cuh"):
+            for p in Path(d).rglob(ext):
+                m = max(m, p.stat().st_mtime)
+    return m
+
+
+def _compile(cmd, src, obj, verbose):
+    if verbose:
+        print(" ".join(map(str, cmd)), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compile failed: {src}\n{r.stdout}\n{r.stderr}")
+    if verbose and r.stderr.strip():
+        print(r.stderr, flush=True)
+    return obj
+
+
+def _build_lib(name, sources, compiler, flags, link_cmd, hdr_dirs, verbose, extra_flags=()):
+    OBJ.mkdir(parents=True, exist_ok=True)
+    lib = OUT / name
+    hdr_m = _newest_header_mtime(hdr_dirs)
+    jobs, objs = [], []
+    for src in sources:
+        obj = OBJ / (src.stem + ("_cu.o" if src.suffix == ".cu" else "_cpp.o"))
+        objs.append(obj)
+        if (not obj.exists()) or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m):
+            jobs.append(([compiler, *flags, *extra_flags, "-c", str(src), "-o", str(obj)], src, obj))
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+            futs = [ex.submit(_compile, c, s, o, verbose) for c, s, o in jobs]
+            for f in futs:
+                f.result()
+    if jobs or not lib.exists():
+        cmd = [*link_cmd, "-o", str(lib), *map(str, objs)]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {name}\n{r.stdout}\n{r.stderr}")
+    return lib
+
+
+def kernel_sources():
+    return sorted((CSRC / "kernels").glob("*.cu"))
+
+
+def runtime_sources():
+    return sorted((CSRC / "runtime").glob("*.cpp"))
+
+
+def build_kernels(verbose=False, ptxas_info=False):
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    link = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-Xcompiler", "-fPIC"]
+    return _build_lib("libft_kernels.so", kernel_sources(), NVCC, NVCC_FLAGS, link, [CSRC / "kernels", CSRC / "include"],
+                      verbose or ptxas_info, extra)
+
+
+def build_runtime(verbose=False):
+    srcs = runtime_sources()
+    if not srcs:
+        return None
+    link = [CXX, "-shared", "-pthread"]
+    lib = _build_lib("libft_runtime.so", srcs, CXX, CXX_FLAGS, link, [CSRC / "runtime", CSRC / "include"], verbose)
+    return lib
+
+
+def build_all(verbose=False):
+    OUT.mkdir(parents=True, exist_ok=True)
+    k = build_kernels(verbose)
+    r = build_runtime(verbose)
+    return k, r
+
+
+if __name__ == "__main__":
+    v = "-v" in sys.argv
+    if "--ptxas" in sys.argv:
+        for o in OBJ.glob("*_cu.o"):
+            o.unlink()
+        build_kernels(ptxas_info=True)
+    else:
+        print(build_all(verbose=v))

@@ -1,0 +1,276 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a.
+//
+//   D[M,N] = A (x) B  (+ bias[N]),  bf16 operands, f32 accumulation in TMEM,
+//   bf16 or f32 output.
+//
+// Operand layouts (row-major memory, leading dimension in elements):
+//   a_mn = 0 : A memory is [M,K]  (K contiguous)      a_mn = 1 : A memory is [K,M]  (M contiguous)
+//   b_mn = 0 : B memory is [N,K]  (K contiguous)      b_mn = 1 : B memory is [K,N]  (N contiguous)
+// so (0,0) is Linear forward x.W^T, (0,1) is dgrad dY.W, (1,1) is wgrad dY^T.X.
+//
+// Structure per CTA (one CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles into a 4-stage smem ring (128B swizzle)
+//   warp 1      allocates TMEM (2 x 256 columns), one lane issues tcgen05.mma (128x256x16)
+//   warps 2..5  epilogue: tcgen05.ld -> registers -> (+bias) -> bf16/f32 -> swizzled smem -> TMA store
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// Every mbarrier wait is bounded; on expiry the role records its site in the status word and
+// the CTA falls through to teardown (TMEM is freed, in-flight stores are drained).
+//
+// Capability parity: replaces the cuBLAS GemmEx wrappers of ferrotorch-gpu/src/blas.rs:1964-2922
+// and the three-launch linear_fused CUDA path of ferrotorch-core/src/grad_fns/linalg.rs:1223-1262.
+#include "common.cuh"
+#include "host_common.h"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 128;      // 32 rows x 128 B per warp per buffer
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * 2 * EPI_BUF_BYTES + 256 + 1024;
+
+FT_DEVICE bool mbar_wait_deadline(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0xff) == 0 && globaltimer_ns() - t0 > 2000000000ull) return false;
+  }
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmD, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+               uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + STAGES * A_STAGE_BYTES;
+  uint8_t* sEpi = sB + STAGES * B_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sEpi + EPI_WARPS * 2 * EPI_BUF_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tfull_bar[a], 1); mbar_init(&tempty_bar[a], EPI_WARPS); }
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmD); }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t s = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait_deadline(&empty_bar[s], phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 1, s); ok = false; break; }
+          mbar_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; j++) tma_load_2d(a_dst + j * (BK * 128), &tmA, &full_bar[s], m0 + j * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full_bar[s], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++) tma_load_2d(b_dst + j * (BK * 128), &tmB, &full_bar[s], n0 + j * 64, kb * BK);
+          }
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // let copies that are already in flight land before the CTA's shared memory goes away
+        for (int i = 0; i < 64; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(BM, BN, /*bf16*/ 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t s = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait_deadline(&tempty_bar[acc], acc_phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 2, acc); ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait_deadline(&full_bar[s], phase)) { ft_set_status(status, FT_K_GEMM, 3, s); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_base = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++) {
+            // K-major: 8-row groups 1024 B apart, the K slice moves 32 B inside the 128 B swizzle row.
+            // MN-major: 64-element atoms BK*128 B apart (leading offset), 8 k-rows = 1024 B (stride offset),
+            //           a K slice of 16 rows moves 2048 B.
+            const uint64_t adesc = A_MN ? make_smem_desc(a_base + k * (UMMA_K * 128), BK * 128, 1024, FT_SWZ_128B)
+                                        : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024, FT_SWZ_128B);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * (UMMA_K * 128), BK * 128, 1024, FT_SWZ_128B)
+                                        : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024, FT_SWZ_128B);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;                      // TMEM lane quarter this warp may access
+    const int ew = warp - 2;                     // staging slot
+    uint8_t* my_buf = sEpi + ew * 2 * EPI_BUF_BYTES;
+    constexpr int EPI_COLS = OUT_F32 ? 32 : 64;
+    constexpr int CHUNKS = BN / EPI_COLS;
+    uint32_t acc = 0, acc_phase = 0;
+    uint32_t nstore = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait_deadline(&tfull_bar[acc], acc_phase)) { if (lane == 0) ft_set_status(status, FT_K_GEMM, 4, acc); ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < CHUNKS; c++) {
+        uint8_t* buf = my_buf + (nstore & 1) * EPI_BUF_BYTES;
+        uint32_t v[OUT_F32 ? 32 : 64];
+        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
+        if constexpr (!OUT_F32) tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+        // the buffer used two stores ago must have been read out by the TMA engine
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        tmem_ld_wait();
+        const int col0 = n0 + c * EPI_COLS;
+        if (bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < EPI_COLS; i++) {
+            float b = (col0 + i < N) ? __bfloat162float(__ldg(bias + col0 + i)) : 0.f;
+            v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
+          }
+        }
+        uint8_t* row = buf + lane * 128;
+        if constexpr (OUT_F32) {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            uint4 pk = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            uint32_t p[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+              p[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col0 < N && (m0 + q * 32) < M) {
+          tma_store_2d(&tmD, buf, col0, m0 + q * 32);
+        }
+        if (lane == 0) tma_store_commit();
+        nstore++;
+      }
+      // all TMEM reads of this accumulator are complete (tmem_ld_wait above)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, bool OUT_F32>
+int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, const void* bias, int M, int N, int K,
+           int num_sms, cudaStream_t stream) {
+  auto kern = ft_gemm_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    FT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
+                                                  ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+int g_num_sms[64] = {0};
+
+}  // namespace
+
+// D[M,N] = A (x) B (+bias). All pointers are device pointers; lda/ldb/ldd in elements.
+// out_f32 = 0: D is bf16; 1: D is f32. Requirements: base pointers 16-byte aligned,
+// lda/ldb multiples of 8, ldd*elem_size a multiple of 16, M,N,K >= 1.
+FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda,
+                           int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_f32, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return FT_ERR_ARG;
+  if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
+  int dev = 0;
+  FT_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FT_ERR_ARG;
+  if (!g_num_sms[dev]) FT_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+
+  CUtensorMap tA, tB, tD;
+  int r;
+  if (!a_mn) r = ft_make_tmap_2d(&tA, A, 2, true, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tA, A, 2, true, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+  if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+  if (out_f32) r = ft_make_tmap_2d(&tD, D, 4, false, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  else         r = ft_make_tmap_2d(&tD, D, 2, true, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (r) return r;
+
+  const int sms = g_num_sms[dev];
+#define FT_GEMM_CASE(AM, BMN, OF) \
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, sms, stream);
+  FT_GEMM_CASE(0, 0, 0) FT_GEMM_CASE(0, 1, 0) FT_GEMM_CASE(1, 0, 0) FT_GEMM_CASE(1, 1, 0)
+  FT_GEMM_CASE(0, 0, 1) FT_GEMM_CASE(0, 1, 1) FT_GEMM_CASE(1, 0, 1) FT_GEMM_CASE(1, 1, 1)
+#undef FT_GEMM_CASE
+  return FT_ERR_ARG;
+}

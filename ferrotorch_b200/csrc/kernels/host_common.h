@@ -1,0 +1,48 @@
+// Host-side helpers shared by the kernel launchers: error codes, the driver
+// entry point for tensor-map encoding (looked up at run time so the library
+// has no link-time dependency on libcuda and imports on a machine with no
+// driver), and a per-device status word that kernels write instead of trapping.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define FT_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Return codes of every exported launcher. 0 = launched; negative = refused
+// before any launch (bad argument); positive = a CUDA runtime error code.
+enum FtError : int {
+  FT_OK = 0,
+  FT_ERR_ARG = -1,         // unsupported shape / alignment
+  FT_ERR_DRIVER = -2,      // driver entry point unavailable
+  FT_ERR_TMAP = -3,        // cuTensorMapEncodeTiled refused the descriptor
+  FT_ERR_TOO_LARGE = -4,   // request exceeds a compiled-in maximum
+};
+
+#define FT_CUDA_TRY(expr)                                  \
+  do {                                                     \
+    cudaError_t _e = (expr);                               \
+    if (_e != cudaSuccess) return (int)_e;                 \
+  } while (0)
+
+typedef CUresult (*PFN_ftTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                               CUtensorMapFloatOOBfill);
+
+PFN_ftTensorMapEncodeTiled ft_get_tmap_encoder();
+
+// Encode a 2-D row-major tensor map (dims given innermost first).
+//   elem_bytes 2 (bf16) or 4 (f32). ld_bytes = row pitch in bytes (multiple of 16).
+int ft_make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, bool is_bf16, uint64_t inner, uint64_t outer,
+                    uint64_t ld_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz);
+// 3-D variant: dims (inner, mid, outer) with pitches for mid and outer.
+int ft_make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_bf16, uint64_t d0, uint64_t d1,
+                    uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
+                    CUtensorMapSwizzle swz);
+int ft_make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, bool is_bf16, const uint64_t dims[4],
+                    const uint64_t pitches_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz);
+
+// Per-device status word in device memory (lazily allocated, zeroed).
+uint32_t* ft_status_ptr();

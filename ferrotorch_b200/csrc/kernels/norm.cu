@@ -1,0 +1,311 @@
+// RMSNorm / LayerNorm forward and backward, bf16 storage with f32 math.
+// One CTA per row (grid-stride over rows), 128-bit loads, row kept in registers
+// between the reduction and the normalisation so x is read from HBM once.
+//
+// Capability parity: RMSNORM_PTX / RMSNORM_BACKWARD_PTX (ferrotorch-gpu/src/kernels.rs:7910,8057),
+// RMSNORM_BF16_PTX (ferrotorch-gpu/src/bf16.rs:926), LAYERNORM* (kernels.rs:7394,7593).
+#include "common.cuh"
+#include "host_common.h"
+
+#define FT_VPT_DISPATCH(d, ...)                              \
+  do {                                                      \
+    if ((d) <= 512 * 8) { constexpr int V = 1; __VA_ARGS__; } \
+    else if ((d) <= 512 * 16) { constexpr int V = 2; __VA_ARGS__; } \
+    else { constexpr int V = 4; __VA_ARGS__; }              \
+  } while (0)
+
+namespace {
+
+constexpr int NT = 512;          // threads per CTA
+constexpr int MAXV_LIMIT = 4;    // 16-byte vectors per thread  => d <= 512*4*8 = 16384
+
+// y = (x [+ res]) * rstd * w ;  optionally writes the summed residual stream back to `xout`.
+template <int MAXV, bool HAS_RES>
+__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                                         const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                         __nv_bfloat16* __restrict__ xout, float* __restrict__ rstd_out,
+                                                         int rows, int d, float eps) {
+  __shared__ float red[32];
+  const int nvec = d >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
+    const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * d) : nullptr;
+    float v[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        bf16x8_to_float(xr[c], v[i]);
+        if (HAS_RES) {
+          float r[8];
+          bf16x8_to_float(rr[c], r);
+#pragma unroll
+          for (int e = 0; e < 8; e++) v[i][e] += r[e];
+          bf16x8 o = float_to_bf16x8(v[i]);
+          reinterpret_cast<bf16x8*>(xout + (size_t)row * d)[c] = o;
+          bf16x8_to_float(o, v[i]);  // normalise exactly what the residual stream stores
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) ss += v[i][e] * v[i][e];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float wv[8], o[8];
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = v[i][e] * rstd * wv[e];
+        reinterpret_cast<bf16x8*>(y + (size_t)row * d)[c] = float_to_bf16x8(o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ dres]; dw partial per CTA in f32.
+template <int MAXV, bool HAS_DRES>
+__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                                                         const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                                                         float* __restrict__ dw_partial, int rows, int d) {
+  __shared__ float red[32];
+  const int nvec = d >> 3;
+  float dwacc[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; i++)
+#pragma unroll
+    for (int e = 0; e < 8; e++) dwacc[i][e] = 0.f;
+  float wv[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; i++) {
+    int c = threadIdx.x + i * NT;
+    if (c < nvec) bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float xh[MAXV][8], g[MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float xv[8], dyv[8];
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], xv);
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(dy + (size_t)row * d)[c], dyv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          xh[i][e] = xv[e] * rstd;
+          g[i][e] = dyv[e] * wv[i][e];
+          dot += g[i][e] * xh[i][e];
+          dwacc[i][e] += dyv[e] * xh[i][e];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / (float)d;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = rstd * (g[i][e] - xh[i][e] * dot);
+        if (HAS_DRES) {
+          float r[8];
+          bf16x8_to_float(reinterpret_cast<const bf16x8*>(dres + (size_t)row * d)[c], r);
+#pragma unroll
+          for (int e = 0; e < 8; e++) o[e] += r[e];
+        }
+        reinterpret_cast<bf16x8*>(dx + (size_t)row * d)[c] = float_to_bf16x8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; i++) {
+    int c = threadIdx.x + i * NT;
+    if (c < nvec) {
+      float4* p = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * d + (size_t)c * 8);
+      p[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      p[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// dw[c] (+)= sum_p partial[p][c]; fixed summation order => bit-stable run to run.
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw_bf16,
+                                       float* __restrict__ dw_f32, int nparts, int d, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * d + c];
+  if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
+  if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
+}
+
+// LayerNorm forward: y = (x-mean)*rstd*w + b
+template <int MAXV>
+__global__ void __launch_bounds__(NT) layernorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                           const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                                                           float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                                           int d, float eps) {
+  __shared__ float red[32];
+  const int nvec = d >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[MAXV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], v[i]);
+#pragma unroll
+        for (int e = 0; e < 8; e++) s += v[i][e];
+      }
+    }
+    const float mean = block_sum(s, red) / (float)d;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec)
+#pragma unroll
+        for (int e = 0; e < 8; e++) { float t = v[i][e] - mean; ss += t * t; }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / (float)d + eps);
+    if (threadIdx.x == 0) { if (mean_out) mean_out[row] = mean; if (rstd_out) rstd_out[row] = rstd; }
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float wv[8], bv[8], o[8];
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv);
+        if (b) bf16x8_to_float(reinterpret_cast<const bf16x8*>(b)[c], bv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = (v[i][e] - mean) * rstd * wv[e] + (b ? bv[e] : 0.f);
+        reinterpret_cast<bf16x8*>(y + (size_t)row * d)[c] = float_to_bf16x8(o);
+      }
+    }
+  }
+}
+
+// LayerNorm backward: dx, and per-CTA partials of dw and db.
+template <int MAXV>
+__global__ void __launch_bounds__(NT) layernorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                           const __nv_bfloat16* __restrict__ dy, const float* __restrict__ mean_in,
+                                                           const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                                           float* __restrict__ dw_partial, float* __restrict__ db_partial,
+                                                           int rows, int d) {
+  __shared__ float red[32];
+  const int nvec = d >> 3;
+  float dwacc[MAXV][8], dbacc[MAXV][8], wv[MAXV][8];
+#pragma unroll
+  for (int i = 0; i < MAXV; i++) {
+    int c = threadIdx.x + i * NT;
+#pragma unroll
+    for (int e = 0; e < 8; e++) { dwacc[i][e] = 0.f; dbacc[i][e] = 0.f; }
+    if (c < nvec) bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[MAXV][8], g[MAXV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float xv[8], dyv[8];
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], xv);
+        bf16x8_to_float(reinterpret_cast<const bf16x8*>(dy + (size_t)row * d)[c], dyv);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+          xh[i][e] = (xv[e] - mean) * rstd;
+          g[i][e] = dyv[e] * wv[i][e];
+          s1 += g[i][e];
+          s2 += g[i][e] * xh[i][e];
+          dwacc[i][e] += dyv[e] * xh[i][e];
+          dbacc[i][e] += dyv[e];
+        }
+      }
+    }
+    s1 = block_sum(s1, red) / (float)d;
+    s2 = block_sum(s2, red) / (float)d;
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+      int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[e] = rstd * (g[i][e] - s1 - xh[i][e] * s2);
+        reinterpret_cast<bf16x8*>(dx + (size_t)row * d)[c] = float_to_bf16x8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; i++) {
+    int c = threadIdx.x + i * NT;
+    if (c < nvec)
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        dw_partial[(size_t)blockIdx.x * d + (size_t)c * 8 + e] = dwacc[i][e];
+        db_partial[(size_t)blockIdx.x * d + (size_t)c * 8 + e] = dbacc[i][e];
+      }
+  }
+}
+
+}  // namespace
+
+// Number of per-CTA partial rows the backward kernels write for `rows` rows.
+FT_EXPORT int ft_norm_bwd_parts(int rows) { return rows < 296 ? rows : 296; }
+
+FT_EXPORT int ft_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xout, float* rstd, int rows, int d,
+                             float eps, cudaStream_t st) {
+  if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
+  int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (res)
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                                                  (__nv_bfloat16*)y, (__nv_bfloat16*)xout, rstd, rows, d, eps));
+  else
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+                                                   nullptr, rstd, rows, d, eps));
+  return (int)cudaGetLastError();
+}
+
+// dw_partial: f32 scratch of ft_norm_bwd_parts(rows) * d elements. dw_bf16 / dw_f32: either may be null.
+FT_EXPORT int ft_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
+                             float* dw_partial, void* dw_bf16, float* dw_f32, int accumulate, int rows, int d, cudaStream_t st) {
+  if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
+  int grid = ft_norm_bwd_parts(rows);
+  if (dres)
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
+                                                  (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, d));
+  else
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
+                                                   nullptr, (__nv_bfloat16*)dx, dw_partial, rows, d));
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
+  return (int)cudaGetLastError();
+}
+
+FT_EXPORT int ft_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, int rows, int d,
+                               float eps, cudaStream_t st) {
+  if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
+  int grid = rows < 148 * 8 ? rows : 148 * 8;
+  FT_VPT_DISPATCH(d, layernorm_fwd_kernel<V><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)b,
+                                            (__nv_bfloat16*)y, mean, rstd, rows, d, eps));
+  return (int)cudaGetLastError();
+}
+
+FT_EXPORT int ft_layernorm_bwd(const void* x, const void* w, const void* dy, const float* mean, const float* rstd, void* dx,
+                               float* dw_partial, float* db_partial, void* dw_bf16, void* db_bf16, int rows, int d,
+                               cudaStream_t st) {
+  if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
+  int grid = ft_norm_bwd_parts(rows);
+  FT_VPT_DISPATCH(d, layernorm_bwd_kernel<V><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, mean, rstd,
+                                            (__nv_bfloat16*)dx, dw_partial, db_partial, rows, d));
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, nullptr, grid, d, 0);
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(db_partial, (__nv_bfloat16*)db_bf16, nullptr, grid, d, 0);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,120 @@
+"""bf16 GEMM on the tcgen05 kernel, and the differentiable ``linear`` built on it.
+
+``gemm(a, b, a_mn=, b_mn=)`` computes ``D[M,N] = A (x) B`` where the flags say
+which dimension of each operand is contiguous in memory:
+
+* ``a_mn=False``: ``a`` is ``[M,K]``;  ``a_mn=True``: ``a`` is ``[K,M]`` (used transposed)
+* ``b_mn=False``: ``b`` is ``[N,K]``;  ``b_mn=True``: ``b`` is ``[K,N]``
+
+so ``(False, False)`` is ``x @ w.T`` (Linear forward), ``(False, True)`` is
+``dy @ w`` (dgrad) and ``(True, True)`` is ``dy.T @ x`` (wgrad). No operand is
+ever transposed in memory: the layout goes into the TMA/UMMA descriptors.
+
+On CPU tensors the same function evaluates the product with ``torch.matmul``
+in f32 (the oracle the GPU tests compare against).
+
+Reference parity: cuBLAS wrappers ferrotorch-gpu/src/blas.rs:1964-2922 and
+``linear_fused`` ferrotorch-core/src/grad_fns/linalg.rs:1214-1262.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .. import _lib
+from ..errors import InvalidArgument
+
+_FORCE_LIBRARY = os.environ.get("FT_GEMM_BACKEND", "") == "cublas"  # A/B switch for the library baseline
+
+
+def _as_2d_rowmajor(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 2:
+        raise InvalidArgument(f"gemm operands must be 2-D, got {tuple(t.shape)}")
+    if t.stride(1) != 1 or (t.stride(0) % 8) or (t.data_ptr() % 16):
+        t = t.contiguous()
+    return t
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias: torch.Tensor | None = None,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise InvalidArgument(f"gemm inner dimensions differ: {K} vs {Kb}")
+    if not a.is_cuda or _FORCE_LIBRARY:
+        A = a.t() if a_mn else a
+        B = b if b_mn else b.t()
+        if a.is_cuda:
+            r = torch.matmul(A, B)
+            if bias is not None:
+                r = r + bias
+            r = r.to(out_dtype)
+        else:
+            r = torch.matmul(A.float(), B.float())
+            if bias is not None:
+                r = r + bias.float()
+            r = r.to(out_dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise InvalidArgument("gemm expects bf16 operands on CUDA")
+    a = _as_2d_rowmajor(a)
+    b = _as_2d_rowmajor(b)
+    if out is None:
+        ldd_align = 8 if out_dtype == torch.bfloat16 else 4
+        if N % ldd_align == 0:
+            out = torch.empty((M, N), device=a.device, dtype=out_dtype)
+        else:  # pad the leading dimension so each output row starts on a 16-byte boundary
+            Np = (N + ldd_align - 1) // ldd_align * ldd_align
+            out = torch.empty((M, Np), device=a.device, dtype=out_dtype)[:, :N]
+    else:
+        out_dtype = out.dtype
+        if out.stride(1) != 1:
+            raise InvalidArgument("gemm out must be row-major")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise InvalidArgument("gemm output must be bf16 or f32")
+    if bias is not None:
+        bias = bias.to(torch.bfloat16).contiguous()
+    with torch.cuda.device(a.device):
+        _lib.call("ft_gemm_bf16", _lib.P(a), _lib.P(b), _lib.P(out), _lib.P(bias), M, N, K, ctypes.c_int64(a.stride(0)),
+                  ctypes.c_int64(b.stride(0)), ctypes.c_int64(out.stride(0)), int(a_mn), int(b_mn),
+                  int(out_dtype == torch.float32), _lib.S())
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = gemm(x2, w, bias=bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.shp = shp
+        return y.reshape(*shp[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(ctx.shp)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T + bias`` for ``w`` of shape ``[out, in]`` with autograd; bf16 CUDA tensors run on the tcgen05 GEMM."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        return _LinearFn.apply(x, w, bias)
+    return torch.nn.functional.linear(x, w, bias)

@@ -1,0 +1,172 @@
+"""RoPE, SwiGLU, embedding and residual-add on the hand-written kernels, with autograd.
+
+Reference parity: half-rotation RoPE (ferrotorch-gpu/src/bf16.rs:1438, ferrotorch-nn/src/transformer.rs:49,503),
+SwiGLU (ferrotorch-nn/src/transformer.rs:677), Embedding (ferrotorch-nn/src/embedding.rs:66,195).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _lib
+
+
+def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None):
+    """cos/sin tables ``[max_pos, head_dim/2]`` in f32. ``scaling``: {"type": "linear"|"ntk"|"yarn", "factor": f, ...}."""
+    half = head_dim // 2
+    base = float(theta)
+    if scaling and scaling.get("type") == "ntk":
+        base = base * scaling["factor"] ** (head_dim / (head_dim - 2))
+    inv = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
+    pos = torch.arange(max_pos, dtype=torch.float64)
+    if scaling and scaling.get("type") == "linear":
+        pos = pos / scaling["factor"]
+    if scaling and scaling.get("type") == "yarn":
+        f = scaling["factor"]
+        orig = scaling.get("original_max_position", max_pos)
+        beta_fast, beta_slow = scaling.get("beta_fast", 32.0), scaling.get("beta_slow", 1.0)
+
+        def corr(n):
+            return head_dim * math.log(orig / (n * 2 * math.pi)) / (2 * math.log(base))
+        lo, hi = max(math.floor(corr(beta_fast)), 0), min(math.ceil(corr(beta_slow)), half - 1)
+        ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+        inv = inv / f * ramp + inv * (1 - ramp)
+    ang = torch.outer(pos, inv)
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def rope_inplace(x2: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, head0: int, nheads: int, head_dim: int,
+                 inverse: bool = False, positions: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate heads ``[head0, head0+nheads)`` of the packed ``[tokens, row]`` buffer in place."""
+    tokens = x2.shape[0]
+    if x2.is_cuda:
+        _lib.call("ft_rope_inplace", x2, cos, sin, positions, tokens, seq_len, x2.stride(0), head0, nheads, head_dim, int(inverse),
+                  _lib.S())
+        return x2
+    pos = positions.long() if positions is not None else (torch.arange(tokens, device=x2.device) % seq_len)
+    c, s = cos[pos].unsqueeze(1), sin[pos].unsqueeze(1)
+    if inverse:
+        s = -s
+    v = x2[:, head0 * head_dim:(head0 + nheads) * head_dim].reshape(tokens, nheads, head_dim).float()
+    a, b = v[..., : head_dim // 2], v[..., head_dim // 2:]
+    out = torch.cat([a * c - b * s, b * c + a * s], -1).to(x2.dtype)
+    x2[:, head0 * head_dim:(head0 + nheads) * head_dim] = out.reshape(tokens, nheads * head_dim)
+    return x2
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, positions):
+        # x: [B, S, H, D]
+        B, S, H, D = x.shape
+        y = x.contiguous().clone().reshape(B * S, H * D)
+        rope_inplace(y, cos, sin, S, 0, H, D, False, positions)
+        ctx.save_for_backward(cos, sin, positions if positions is not None else torch.empty(0))
+        ctx.meta = (B, S, H, D, positions is not None)
+        return y.reshape(B, S, H, D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin, pos = ctx.saved_tensors
+        B, S, H, D, has_pos = ctx.meta
+        g = dy.contiguous().clone().reshape(B * S, H * D)
+        rope_inplace(g, cos, sin, S, 0, H, D, True, pos if has_pos else None)
+        return g.reshape(B, S, H, D), None, None, None
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
+    """Half-rotation RoPE on ``x`` of shape ``[B, S, H, D]`` (differentiable)."""
+    return _RopeFn.apply(x, cos, sin, positions)
+
+
+def swiglu_fwd(gu2: torch.Tensor) -> torch.Tensor:
+    rows, F2 = gu2.shape
+    F = F2 // 2
+    if gu2.is_cuda:
+        out = torch.empty((rows, F), device=gu2.device, dtype=gu2.dtype)
+        _lib.call("ft_swiglu_fwd", gu2, out, rows, F, _lib.S())
+        return out
+    g, u = gu2[:, :F].float(), gu2[:, F:].float()
+    return (torch.nn.functional.silu(g) * u).to(gu2.dtype)
+
+
+def swiglu_bwd(gu2: torch.Tensor, dout2: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+    rows, F2 = gu2.shape
+    F = F2 // 2
+    if gu2.is_cuda:
+        dgu = gu2 if inplace else torch.empty_like(gu2)
+        _lib.call("ft_swiglu_bwd", gu2, dout2, dgu, rows, F, _lib.S())
+        return dgu
+    g, u, d = gu2[:, :F].float(), gu2[:, F:].float(), dout2.float()
+    sg = torch.sigmoid(g)
+    silu = g * sg
+    return torch.cat([d * u * (sg + silu * (1 - sg)), d * silu], 1).to(gu2.dtype)
+
+
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        shp = gu.shape
+        gu2 = gu.reshape(-1, shp[-1]).contiguous()
+        ctx.save_for_backward(gu2)
+        ctx.shp = shp
+        return swiglu_fwd(gu2).reshape(*shp[:-1], shp[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu2,) = ctx.saved_tensors
+        return swiglu_bwd(gu2, dout.reshape(gu2.shape[0], -1).contiguous()).reshape(ctx.shp)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gate_up = [..., gate | up]`` (differentiable, one fused kernel each way)."""
+    return _SwiGLUFn.apply(gate_up)
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    flat = ids.reshape(-1).contiguous()
+    if table.is_cuda and table.dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
+        out = torch.empty((flat.numel(), table.shape[1]), device=table.device, dtype=table.dtype)
+        _lib.call("ft_embedding_fwd", flat, table, out, flat.numel(), table.shape[1], table.shape[0], None, _lib.S())
+        return out.reshape(*ids.shape, table.shape[1])
+    return table[flat].reshape(*ids.shape, table.shape[1])
+
+
+def embedding_bwd(ids: torch.Tensor, dout2: torch.Tensor, dtable: torch.Tensor) -> torch.Tensor:
+    """``dtable[ids] += dout`` (dtable bf16 or f32, already zeroed or holding a running sum)."""
+    flat = ids.reshape(-1).contiguous()
+    if dtable.is_cuda and dout2.dtype == torch.bfloat16:
+        _lib.call("ft_embedding_bwd", flat, dout2, dtable, flat.numel(), dtable.shape[1], dtable.shape[0],
+                  int(dtable.dtype == torch.float32), _lib.S())
+        return dtable
+    dtable.index_add_(0, flat, dout2.to(dtable.dtype))
+    return dtable
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        ctx.save_for_backward(ids)
+        ctx.tshape = table.shape
+        return embedding_fwd(ids, table)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        dt = torch.zeros(ctx.tshape, device=dout.device, dtype=dout.dtype)
+        embedding_bwd(ids, dout.reshape(-1, ctx.tshape[1]).contiguous(), dt)
+        return None, dt
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return _EmbeddingFn.apply(ids, table)
+
+
+def add_(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = a + b`` for contiguous bf16 tensors (``out`` may alias ``a``)."""
+    out = a if out is None else out
+    if a.is_cuda and a.dtype == torch.bfloat16 and a.numel() % 8 == 0 and a.is_contiguous() and b.is_contiguous():
+        _lib.call("ft_add_bf16", a, b, out, a.numel(), _lib.S())
+        return out
+    return torch.add(a, b, out=out)

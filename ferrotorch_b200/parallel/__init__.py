@@ -1,0 +1,5 @@
+"""Parallelism: flat parameter units, FSDP / DDP / tensor / pipeline parallel engines, collectives, symmetric memory."""
+from .flat import FlatUnit, TensorSpec
+from .fsdp import FSDP, ShardingStrategy, AdamWConfig
+
+__all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig"]
