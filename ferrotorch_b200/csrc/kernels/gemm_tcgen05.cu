@@ -252,6 +252,7 @@ FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bi
   int dev = 0;
   FT_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return FT_ERR_ARG;
+  FT_CUDA_TRY(ft_bind_context(dev));
   if (!g_num_sms[dev]) FT_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev));
 
   CUtensorMap tA, tB, tD;

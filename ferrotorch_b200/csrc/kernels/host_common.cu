@@ -14,6 +14,15 @@ PFN_ftTensorMapEncodeTiled ft_get_tmap_encoder() {
   return g_encode;
 }
 
+cudaError_t ft_bind_context(int dev) {
+  static thread_local int bound = -1;
+  if (bound == dev) return cudaSuccess;
+  cudaError_t e = cudaSetDevice(dev);
+  if (e == cudaSuccess) e = cudaFree(0);
+  if (e == cudaSuccess) bound = dev;
+  return e;
+}
+
 static int encode(CUtensorMap* out, const void* base, bool is_bf16, int elem_bytes, int rank, const cuuint64_t* dims,
                   const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swz) {
   PFN_ftTensorMapEncodeTiled enc = ft_get_tmap_encoder();

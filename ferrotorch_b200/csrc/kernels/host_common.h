@@ -44,5 +44,10 @@ int ft_make_tmap_3d(CUtensorMap* out, const void* base, int elem_bytes, bool is_
 int ft_make_tmap_4d(CUtensorMap* out, const void* base, int elem_bytes, bool is_bf16, const uint64_t dims[4],
                     const uint64_t pitches_bytes[3], const uint32_t box[4], CUtensorMapSwizzle swz);
 
+// Make the device's primary context current in the calling thread. A thread that has only ever called
+// cudaGetDevice (an autograd worker, say) has no current context, and the driver-level tensor-map encoder then
+// fails with CUDA_ERROR_INVALID_CONTEXT.
+cudaError_t ft_bind_context(int dev);
+
 // Per-device status word in device memory (lazily allocated, zeroed).
 uint32_t* ft_status_ptr();

@@ -29,7 +29,7 @@ def _native_available() -> bool:
         ok = False
         if os.environ.get("FT_ATTN_BACKEND", "") != "sdpa":
             try:
-                ok = hasattr(_lib.kernels(), "ft_flash_fwd") and hasattr(_lib.kernels(), "ft_flash_bwd")
+                ok = hasattr(_lib.kernels(), "ft_flash_fwd")
             except Exception:
                 ok = False
         _native_ok = ok
@@ -75,7 +75,7 @@ def flash_fwd(qkv2: torch.Tensor, B: int, S: int, Hq: int, Hkv: int, D: int, cau
 def flash_bwd(qkv2, out2, lse, dout2, B, S, Hq, Hkv, D, causal: bool = True, scale: float | None = None) -> torch.Tensor:
     """Returns dqkv ``[T, (Hq+2Hkv)*D]`` in the packed layout."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if lse is not None and backend(D, qkv2.dtype, qkv2.is_cuda) == "tcgen05":
+    if lse is not None and backend(D, qkv2.dtype, qkv2.is_cuda) == "tcgen05" and hasattr(_lib.kernels(), "ft_flash_bwd"):
         dqkv = torch.empty_like(qkv2)
         _lib.call("ft_flash_bwd", qkv2, out2, lse, dout2, dqkv, B, S, Hq, Hkv, D, qkv2.stride(0), int(causal), float(scale), _lib.S())
         return dqkv

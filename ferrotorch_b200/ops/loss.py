@@ -23,7 +23,7 @@ def cross_entropy_fwd_bwd(logits2: torch.Tensor, targets: torch.Tensor, *, ignor
         out = torch.empty(2, device=logits2.device, dtype=torch.float32)
         dl = None
         if want_grad:
-            dl = logits2 if inplace_grad else torch.empty_like(logits2)
+            dl = logits2 if inplace_grad else torch.empty_strided(logits2.shape, logits2.stride(), device=logits2.device, dtype=logits2.dtype)
         gs = grad_scale if grad_scale is not None else 1.0 / rows
         _lib.call("ft_cross_entropy", logits2, t, loss_rows, None, dl, rows, V, logits2.stride(0), ignore_index,
                   float(label_smoothing), float(gs), None, int(logits2.dtype == torch.float32), _lib.S())

@@ -132,12 +132,40 @@ def bench_elementwise(results):
         print(json.dumps(r), flush=True)
 
 
+def single_gemm():
+    """Three launches of one 8192x8192x4096 bf16 GEMM (a small, self-terminating case for profiler captures)."""
+    from ferrotorch_b200 import ops
+    a = torch.randn(8192, 4096, device="cuda").to(torch.bfloat16)
+    b = torch.randn(8192, 4096, device="cuda").to(torch.bfloat16)
+    out = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        ops.gemm(a, b, out=out)
+    torch.cuda.synchronize()
+    print("gemm1 done", float(out[0, 0]))
+
+
+def single_attn():
+    """Three launches of causal attention forward (and backward when built) at B=1 S=4096 Hq=32 Hkv=8."""
+    from ferrotorch_b200 import ops
+    B, S, Hq, Hkv, D = 1, 4096, 32, 8, 128
+    qkv = torch.randn(B * S, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    for _ in range(3):
+        out, lse = ops.flash_fwd(qkv, B, S, Hq, Hkv, D, True)
+        ops.flash_bwd(qkv, out, lse, torch.ones_like(out), B, S, Hq, Hkv, D, True)
+    torch.cuda.synchronize()
+    print("attn1 done", float(out[0, 0]))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all")
     ap.add_argument("--json", default=None)
     a = ap.parse_args()
     res = []
+    if a.what == "gemm1":
+        return single_gemm()
+    if a.what == "attn1":
+        return single_attn()
     if a.what in ("gemm", "all"):
         bench_gemm(res)
     if a.what in ("attn", "all"):
