@@ -19,6 +19,7 @@ import os
 import torch
 
 from .. import _lib
+from ._workspace import workspace
 
 _native_ok: bool | None = None
 
@@ -34,6 +35,10 @@ def _native_available() -> bool:
                 ok = False
         _native_ok = ok
     return _native_ok
+
+
+def _bwd_native() -> bool:
+    return os.environ.get("FT_ATTN_BWD", "") != "sdpa" and hasattr(_lib.kernels(), "ft_flash_bwd_ws")
 
 
 def backend(D: int = 128, dtype=torch.bfloat16, device_is_cuda: bool = True) -> str:
@@ -75,9 +80,13 @@ def flash_fwd(qkv2: torch.Tensor, B: int, S: int, Hq: int, Hkv: int, D: int, cau
 def flash_bwd(qkv2, out2, lse, dout2, B, S, Hq, Hkv, D, causal: bool = True, scale: float | None = None) -> torch.Tensor:
     """Returns dqkv ``[T, (Hq+2Hkv)*D]`` in the packed layout."""
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if lse is not None and backend(D, qkv2.dtype, qkv2.is_cuda) == "tcgen05" and hasattr(_lib.kernels(), "ft_flash_bwd"):
+    if lse is not None and backend(D, qkv2.dtype, qkv2.is_cuda) == "tcgen05" and _bwd_native():
         dqkv = torch.empty_like(qkv2)
-        _lib.call("ft_flash_bwd", qkv2, out2, lse, dout2, dqkv, B, S, Hq, Hkv, D, qkv2.stride(0), int(causal), float(scale), _lib.S())
+        delta = workspace(qkv2.device, "flash_delta", B * Hq * S * 4)
+        if not dout2.is_contiguous():
+            dout2 = dout2.contiguous()
+        _lib.call("ft_flash_bwd_ws", qkv2, out2, lse, dout2, dqkv, delta, B, S, Hq, Hkv, D, qkv2.stride(0), int(causal), float(scale),
+                  _lib.S())
         return dqkv
     with torch.enable_grad():
         leaf = qkv2.detach().requires_grad_(True)
