@@ -33,6 +33,18 @@ constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * 2 * EPI_BUF_BYTES + 256 + 1024;
 
+// Tile order: groups of RASTER_GM tile-rows, walked row-fastest inside a group, so the ~148 tiles in flight
+// cover a near-square patch of the output (16 x ~9 tiles) and both operands are re-used out of L2.
+constexpr int RASTER_GM = 16;
+FT_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int group_size = RASTER_GM * tiles_n;
+  const int first_m = (tile / group_size) * RASTER_GM;
+  const int gm = min(RASTER_GM, tiles_m - first_m);
+  const int local = tile % group_size;
+  m0 = (first_m + local % gm) * BM;
+  n0 = (local / gm) * BN;
+}
+
 FT_DEVICE bool mbar_wait_deadline(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
@@ -83,7 +95,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t s = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        int m0, n0;
+        tile_coords(tile, tiles_m, tiles_n, m0, n0);
         for (int kb = 0; kb < num_kb; kb++) {
           if (!mbar_wait_deadline(&empty_bar[s], phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 1, s); ok = false; break; }
           mbar_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
@@ -155,7 +168,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t nstore = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      int m0, n0;
+      tile_coords(tile, tiles_m, tiles_n, m0, n0);
       if (!mbar_wait_deadline(&tfull_bar[acc], acc_phase)) { if (lane == 0) ft_set_status(status, FT_K_GEMM, 4, acc); ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
