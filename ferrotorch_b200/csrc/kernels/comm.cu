@@ -1,0 +1,409 @@
+// Collectives and fused compute+collective kernels over NVLink peer memory (sm_100a).
+//
+// Every rank runs one process on its own GPU and maps every peer's symmetric buffers into its address space
+// (torch.distributed._symmetric_memory provides the mapping). The kernels below address peers with plain
+// ld/st (or multimem.* through the NVSwitch multicast address when one is bound) - no TMA multicast is used anywhere.
+//
+// Synchronisation: a per-rank flag block in symmetric memory, flags[phase][src_rank] (u32). A rank announces phase
+// completion by storing the launch's sequence number into its slot on every peer (st.release.sys) and waits until all
+// of its own slots reach that number (ld.acquire.sys). Every wait has a deadline (default 2 s): when it expires the
+// kernel records {kernel, site, peer} in the status word and returns without touching peer data, so a missing peer
+// turns into an error the host can read instead of a hung GPU.
+//
+//   ft_comm_allreduce      in-place two-shot all-reduce (each rank reduces its 1/N slice from all peers in fixed rank
+//                          order, scales, and pushes the result to every peer), bf16 or f32, optional NVLS path
+//   ft_comm_allreduce_1shot small messages: every rank reduces the whole buffer locally from all peers
+//   ft_comm_reduce_scatter / ft_comm_allgather
+//   ft_fsdp_rs_adamw_ag    reduce-scatter of a flat bf16 gradient unit fused with the sharded AdamW update of the f32
+//                          master/moments and the all-gather (push) of the updated bf16 slice to every peer
+//
+// Capability parity: star all-reduce / all-gather / reduce-scatter on host vectors (ferrotorch-distributed/src/
+// collective.rs:64-410), NCCL wrappers (nccl_collective.rs:75-260), FSDP sync_gradients + broadcast_updated_params
+// (fsdp.rs:627-845).
+#include "common.cuh"
+#include "host_common.h"
+
+namespace {
+
+constexpr int MAX_RANKS = 8;
+constexpr uint64_t COMM_TIMEOUT_NS = 2000000000ull;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+// flags block per rank: u32 [4 phases][MAX_RANKS] followed by a u32 grid counter per phase pair
+struct CommSync {
+  uint32_t* flags[MAX_RANKS];   // flags[r] = base of rank r's flag block (peer mapped)
+  uint32_t* counter;            // local device memory, u32[2], zero between launches
+  int rank, world;
+  uint32_t seq;                 // sequence number of this launch (same on every rank)
+};
+
+// One thread per peer: tell every peer that this rank reached `phase` of launch `seq`.
+FT_DEVICE void signal_peers(const CommSync& s, int phase) {
+  if (threadIdx.x < s.world) st_release_sys(s.flags[threadIdx.x] + phase * MAX_RANKS + s.rank, s.seq);
+}
+// Every thread < world polls one local slot. Returns false on timeout (warp-uniform result for warp 0).
+FT_DEVICE bool wait_peers(const CommSync& s, int phase, uint32_t* status, int site) {
+  bool ok = true;
+  if (threadIdx.x < s.world) {
+    ok = wait_flag_ge(s.flags[s.rank] + phase * MAX_RANKS + threadIdx.x, s.seq, COMM_TIMEOUT_NS);
+    if (!ok) ft_set_status(status, FT_K_COMM, site, threadIdx.x);
+  }
+  return ok;
+}
+
+// Start-of-kernel rendezvous: CTA 0 signals; every CTA waits on the local flags. Returns false if any peer is missing.
+FT_DEVICE bool comm_begin(const CommSync& s, uint32_t* status) {
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) ok_sh = 1;
+  __syncthreads();
+  if (blockIdx.x == 0) signal_peers(s, 0);
+  if (!wait_peers(s, 0, status, 1)) ok_sh = 0;
+  __syncthreads();
+  return ok_sh != 0;
+}
+
+// End-of-kernel rendezvous: the last CTA to finish announces completion to the peers and waits for theirs, so that when
+// the kernel retires (a) every peer has finished reading this rank's buffers and (b) every peer's pushes into this
+// rank's buffers have landed.
+FT_DEVICE void comm_end(const CommSync& s, uint32_t* status) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int last;
+  if (threadIdx.x == 0) {
+    uint32_t prev = atomicAdd(s.counter, 1u);
+    last = (prev == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!last) return;
+  if (threadIdx.x == 0) *s.counter = 0;    // ready for the next launch on this stream
+  __threadfence_system();
+  signal_peers(s, 1);
+  wait_peers(s, 1, status, 2);
+}
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static FT_DEVICE void load(const __nv_bfloat16* p, float* f) { bf16x8 v = *reinterpret_cast<const bf16x8*>(p); bf16x8_to_float(v, f); }
+  static FT_DEVICE void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<bf16x8*>(p) = float_to_bf16x8(f); }
+};
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static FT_DEVICE void load(const float* p, float* f) { float4 v = *reinterpret_cast<const float4*>(p); f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
+  static FT_DEVICE void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// two-shot all-reduce, in place: buf_p[i] <- scale * sum_q buf_q[i]
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_2shot_kernel(PeerPtrs bufs, CommSync s, size_t n, float scale, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = n / V;
+  const size_t per = (nvec + s.world - 1) / s.world;
+  const size_t lo = per * s.rank, hi = min(nvec, lo + per);
+  for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] = 0.f;
+    float f[MAX_RANKS][V];
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) Vec16<T>::load(reinterpret_cast<const T*>(bufs.p[q]) + i * V, f[q]);
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world)
+#pragma unroll
+        for (int e = 0; e < V; e++) acc[e] += f[q][e];
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] *= scale;
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) Vec16<T>::store(reinterpret_cast<T*>(bufs.p[q]) + i * V, acc);
+  }
+  // scalar tail (n % V) handled by rank 0
+  if (s.rank == 0 && blockIdx.x == 0) {
+    for (size_t i = nvec * V + threadIdx.x; i < n; i += blockDim.x) {
+      float a = 0.f;
+      for (int q = 0; q < s.world; q++) a += (float)reinterpret_cast<const T*>(bufs.p[q])[i];
+      a *= scale;
+      for (int q = 0; q < s.world; q++) reinterpret_cast<T*>(bufs.p[q])[i] = (T)a;
+    }
+  }
+  comm_end(s, status);
+}
+
+// NVLS variant (bf16): the switch reduces (multimem.ld_reduce) and broadcasts (multimem.st). `mc` is this rank's
+// mapping of the multicast address of the same symmetric buffer. Accumulation is f32 inside the switch.
+__global__ void __launch_bounds__(512) allreduce_nvls_bf16_kernel(__nv_bfloat16* mc, __nv_bfloat16* local, CommSync s, size_t n,
+                                                                  float scale, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  const size_t nvec = n / 8;
+  const size_t per = (nvec + s.world - 1) / s.world;
+  const size_t lo = per * s.rank, hi = min(nvec, lo + per);
+  for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
+    uint32_t r0, r1, r2, r3;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "l"(mc + i * 8)
+                 : "memory");
+    if (scale != 1.f) {
+      uint32_t r[4] = {r0, r1, r2, r3};
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&r[e]));
+        __nv_bfloat162 h = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+        r[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      r0 = r[0]; r1 = r[1]; r2 = r[2]; r3 = r[3];
+    }
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc + i * 8), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+                 : "memory");
+  }
+  comm_end(s, status);
+}
+
+// one-shot: out_local[i] = scale * sum_q buf_q[i]; for messages small enough that latency dominates
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_1shot_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t n, float scale,
+                                                              uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = n / V;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] = 0.f;
+    for (int q = 0; q < s.world; q++) {
+      float f[V];
+      Vec16<T>::load(reinterpret_cast<const T*>(bufs.p[q]) + i * V, f);
+#pragma unroll
+      for (int e = 0; e < V; e++) acc[e] += f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] *= scale;
+    Vec16<T>::store(out + i * V, acc);
+  }
+  if (blockIdx.x == 0)
+    for (size_t i = nvec * V + threadIdx.x; i < n; i += blockDim.x) {
+      float a = 0.f;
+      for (int q = 0; q < s.world; q++) a += (float)reinterpret_cast<const T*>(bufs.p[q])[i];
+      out[i] = (T)(a * scale);
+    }
+  comm_end(s, status);
+}
+
+// reduce-scatter: out_local[i] = scale * sum_q buf_q[rank*chunk + i], i < chunk
+template <typename T>
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t chunk, float scale,
+                                                             uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = chunk / V, base = chunk * s.rank;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] = 0.f;
+    for (int q = 0; q < s.world; q++) {
+      float f[V];
+      Vec16<T>::load(reinterpret_cast<const T*>(bufs.p[q]) + base + i * V, f);
+#pragma unroll
+      for (int e = 0; e < V; e++) acc[e] += f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; e++) acc[e] *= scale;
+    Vec16<T>::store(out + i * V, acc);
+  }
+  comm_end(s, status);
+}
+
+// all-gather (push): buf_q[rank*chunk + i] = src_local[i] for every q
+template <typename T>
+__global__ void __launch_bounds__(512) allgather_kernel(PeerPtrs bufs, const T* __restrict__ src, CommSync s, size_t chunk, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = chunk / V, base = chunk * s.rank;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + i * V);
+    for (int q = 0; q < s.world; q++) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(bufs.p[q]) + base + i * V) = v;
+  }
+  comm_end(s, status);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// FSDP: reduce-scatter(mean) of the bf16 gradient unit + AdamW on the owned f32 slice + push all-gather
+// ---------------------------------------------------------------------------------------------------------
+struct AdamWArgsC { float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2; };
+
+__global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, CommSync s, float* __restrict__ master,
+                                                               float* __restrict__ m, float* __restrict__ v, size_t chunk, AdamWArgsC a,
+                                                               const float* __restrict__ grad_scale_ptr, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  const float inv_world = (grad_scale_ptr ? *grad_scale_ptr : 1.f) / (float)s.world;
+  const float decay = 1.f - a.lr * a.weight_decay, step = a.lr / a.bias_c1, inv_c2 = rsqrtf(a.bias_c2);
+  const size_t nvec = chunk / 8, base = chunk * s.rank;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float f[MAX_RANKS][8];
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) Vec16<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(grads.p[q]) + base + i * 8, f[q]);
+    float g[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) g[e] = 0.f;
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world)
+#pragma unroll
+        for (int e = 0; e < 8; e++) g[e] += f[q][e];          // fixed rank order: identical bits on every rank
+    float4* pm = reinterpret_cast<float4*>(master + i * 8);
+    float4* mm = reinterpret_cast<float4*>(m + i * 8);
+    float4* vv = reinterpret_cast<float4*>(v + i * 8);
+    float p[8], m1[8], v1[8];
+    { float4 t0 = pm[0], t1 = pm[1]; p[0] = t0.x; p[1] = t0.y; p[2] = t0.z; p[3] = t0.w; p[4] = t1.x; p[5] = t1.y; p[6] = t1.z; p[7] = t1.w; }
+    { float4 t0 = mm[0], t1 = mm[1]; m1[0] = t0.x; m1[1] = t0.y; m1[2] = t0.z; m1[3] = t0.w; m1[4] = t1.x; m1[5] = t1.y; m1[6] = t1.z; m1[7] = t1.w; }
+    { float4 t0 = vv[0], t1 = vv[1]; v1[0] = t0.x; v1[1] = t0.y; v1[2] = t0.z; v1[3] = t0.w; v1[4] = t1.x; v1[5] = t1.y; v1[6] = t1.z; v1[7] = t1.w; }
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const float gg = g[e] * inv_world;
+      p[e] *= decay;
+      m1[e] = a.beta1 * m1[e] + (1.f - a.beta1) * gg;
+      v1[e] = a.beta2 * v1[e] + (1.f - a.beta2) * gg * gg;
+      p[e] -= step * m1[e] / (sqrtf(v1[e]) * inv_c2 + a.eps);
+    }
+    pm[0] = make_float4(p[0], p[1], p[2], p[3]); pm[1] = make_float4(p[4], p[5], p[6], p[7]);
+    mm[0] = make_float4(m1[0], m1[1], m1[2], m1[3]); mm[1] = make_float4(m1[4], m1[5], m1[6], m1[7]);
+    vv[0] = make_float4(v1[0], v1[1], v1[2], v1[3]); vv[1] = make_float4(v1[4], v1[5], v1[6], v1[7]);
+    const bf16x8 out = float_to_bf16x8(p);
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(params.p[q]) + base + i * 8) = out;
+  }
+  comm_end(s, status);
+}
+
+// stand-alone device barrier (phase 0 + phase 1 rendezvous, no data)
+__global__ void comm_barrier_kernel(CommSync s, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  comm_end(s, status);
+}
+
+inline int comm_grid(size_t work, int max_ctas) {
+  size_t g = (work + 511) / 512;
+  if (g < 1) g = 1;
+  return (int)(g < (size_t)max_ctas ? g : (size_t)max_ctas);
+}
+
+int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return FT_ERR_ARG;
+  for (int i = 0; i < MAX_RANKS; i++) s.flags[i] = i < world ? reinterpret_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
+  s.counter = counter;
+  s.rank = rank;
+  s.world = world;
+  s.seq = seq;
+  return FT_OK;
+}
+
+}  // namespace
+
+// Size in bytes of the per-rank flag block the kernels expect (zero-initialised symmetric memory).
+FT_EXPORT int ft_comm_flag_bytes() { return 4 * MAX_RANKS * 4; }
+
+// buf_ptrs / flag_ptrs: host arrays of `world` device pointers (this rank's mappings of every rank's buffer / flag block).
+// counter: local device u32[2], zeroed once. seq: launch sequence number, identical on all ranks, increasing by one per launch.
+// dtype: 0 bf16, 1 f32. mc_ptr: multicast mapping of the same buffer or null (NVLS used only when non-null, bf16, n % (8*world) == 0).
+FT_EXPORT int ft_comm_allreduce(void* const* buf_ptrs, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                                int64_t n, int dtype, float scale, void* mc_ptr, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  if (n <= 0) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  uint32_t* status = ft_status_ptr();
+  const int V = dtype == 0 ? 8 : 4;
+  const int grid = comm_grid((size_t)n / V / world + 1, max_ctas > 0 ? max_ctas : 64);
+  if (mc_ptr && dtype == 0 && (n % (8 * (int64_t)world)) == 0)
+    allreduce_nvls_bf16_kernel<<<grid, 512, 0, st>>>((__nv_bfloat16*)mc_ptr, (__nv_bfloat16*)buf_ptrs[rank], s, (size_t)n, scale, status);
+  else if (dtype == 0)
+    allreduce_2shot_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, s, (size_t)n, scale, status);
+  else
+    allreduce_2shot_kernel<float><<<grid, 512, 0, st>>>(b, s, (size_t)n, scale, status);
+  return (int)cudaGetLastError();
+}
+
+FT_EXPORT int ft_comm_allreduce_1shot(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
+                                      uint32_t seq, int64_t n, int dtype, float scale, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  if (n <= 0) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  const int V = dtype == 0 ? 8 : 4;
+  const int grid = comm_grid((size_t)n / V + 1, max_ctas > 0 ? max_ctas : 32);
+  if (dtype == 0) allreduce_1shot_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, (size_t)n, scale, ft_status_ptr());
+  else allreduce_1shot_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, (size_t)n, scale, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// out[chunk] = scale * sum over ranks of buf_q[rank*chunk : (rank+1)*chunk]; chunk % (16/elem) == 0
+FT_EXPORT int ft_comm_reduce_scatter(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
+                                     uint32_t seq, int64_t chunk, int dtype, float scale, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  const int V = dtype == 0 ? 8 : 4;
+  if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
+  if (dtype == 0) reduce_scatter_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, (size_t)chunk, scale, ft_status_ptr());
+  else reduce_scatter_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, (size_t)chunk, scale, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// every rank's buf[rank*chunk : (rank+1)*chunk] on every peer = src[chunk]
+FT_EXPORT int ft_comm_allgather(void* const* buf_ptrs, const void* src, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
+                                uint32_t seq, int64_t chunk, int dtype, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  const int V = dtype == 0 ? 8 : 4;
+  if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
+  if (dtype == 0) allgather_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (const __nv_bfloat16*)src, s, (size_t)chunk, ft_status_ptr());
+  else allgather_kernel<float><<<grid, 512, 0, st>>>(b, (const float*)src, s, (size_t)chunk, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+FT_EXPORT int ft_comm_barrier(void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  comm_barrier_kernel<<<1, 32, 0, st>>>(s, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// grad_ptrs / param_ptrs: `world` mappings of every rank's full bf16 gradient / parameter unit (padded = world*chunk elements).
+// master, m, v: this rank's f32 slices [chunk]. chunk % 8 == 0. step >= 1 (bias correction).
+FT_EXPORT int ft_fsdp_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptrs, void* const* flag_ptrs, uint32_t* counter, int rank,
+                                  int world, uint32_t seq, float* master, float* m, float* v, int64_t chunk, float lr, float beta1,
+                                  float beta2, float eps, float weight_decay, int step, const float* grad_scale_ptr, int max_ctas,
+                                  cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  if (chunk <= 0 || chunk % 8 || step < 1) return FT_ERR_ARG;
+  PeerPtrs g, p;
+  for (int i = 0; i < MAX_RANKS; i++) { g.p[i] = i < world ? grad_ptrs[i] : nullptr; p.p[i] = i < world ? param_ptrs[i] : nullptr; }
+  AdamWArgsC a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step)};
+  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 96);
+  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, ft_status_ptr());
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,160 @@
+"""Symmetric (peer-mapped) device memory and the NVLink collectives built on it.
+
+``SymmetricBuffer`` allocates a buffer that every rank of the group maps into its own address space
+(torch.distributed._symmetric_memory does the cuMem export/import and, where the fabric supports it, binds an
+NVSwitch multicast address). ``SymmComm`` launches the hand-written collective kernels of ``csrc/kernels/comm.cu``
+on such buffers: peers are addressed by plain loads/stores from inside the kernel, completion is signalled through
+a flag block in symmetric memory, and every device-side wait has a deadline - a missing peer surfaces as
+:class:`~ferrotorch_b200.errors.Timeout` from :meth:`SymmComm.check`, not as a hung GPU.
+
+Reference parity: the TCP/NCCL transports under ferrotorch-distributed/src/{backend,nccl_backend,gpu_collective}.rs;
+the reference has no peer-memory path at all.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import List, Optional
+
+import torch
+
+from .. import _lib
+from ..errors import DistributedError, Timeout
+
+
+def _symm_mod():
+    import torch.distributed._symmetric_memory as sm
+    return sm
+
+
+class SymmetricBuffer:
+    """A 1-D buffer of ``numel`` elements of ``dtype`` mapped on every rank of ``group``."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device, group=None, zero: bool = False):
+        import torch.distributed as dist
+        sm = _symm_mod()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        name = self.group.group_name
+        try:
+            sm.enable_symm_mem_for_group(name)
+        except Exception:
+            pass
+        self.tensor = sm.empty(numel, dtype=dtype, device=device)
+        if zero:
+            self.tensor.zero_()
+        self.handle = sm.rendezvous(self.tensor, name)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        mc = getattr(self.handle, "multicast_ptr", 0) or 0
+        self.multicast_ptr = int(mc) if os.environ.get("FT_DISABLE_NVLS", "0") != "1" else 0
+        self.itemsize = self.tensor.element_size()
+
+    def ptr_array(self, elem_offset: int = 0):
+        off = elem_offset * self.itemsize
+        return (ctypes.c_void_p * self.world)(*[p + off for p in self.ptrs])
+
+    def mc(self, elem_offset: int = 0) -> int:
+        return self.multicast_ptr + elem_offset * self.itemsize if self.multicast_ptr else 0
+
+
+class SymmComm:
+    """Launcher of the peer-memory collectives for one process group (at most 8 ranks on one NVSwitch domain)."""
+
+    def __init__(self, device, group=None):
+        import torch.distributed as dist
+        self.device = torch.device(device)
+        self.flags = SymmetricBuffer(_lib.kernels().ft_comm_flag_bytes() // 4, torch.int32, device, group, zero=True)
+        self.group, self.world, self.rank = self.flags.group, self.flags.world, self.flags.rank
+        self.flag_ptrs = self.flags.ptr_array()
+        self.counter = torch.zeros(2, device=device, dtype=torch.int32)
+        self.seq = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)        # every rank's flag block is zeroed before anybody signals into it
+
+    def _next(self) -> int:
+        self.seq += 1
+        return self.seq
+
+    def all_reduce_(self, buf: SymmetricBuffer, numel: int, elem_offset: int = 0, scale: float = 1.0, use_nvls: bool = True,
+                    max_ctas: int = 0) -> None:
+        """In-place sum (times ``scale``) across ranks of ``buf[elem_offset : elem_offset+numel]``."""
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        mc = buf.mc(elem_offset) if use_nvls else 0
+        _lib.call("ft_comm_allreduce", buf.ptr_array(elem_offset), self.flag_ptrs, self.counter, self.rank, self.world, self._next(),
+                  numel, dt, float(scale), mc, max_ctas, _lib.S())
+
+    def all_reduce_small(self, buf: SymmetricBuffer, out: torch.Tensor, numel: int, elem_offset: int = 0, scale: float = 1.0) -> torch.Tensor:
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        _lib.call("ft_comm_allreduce_1shot", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world,
+                  self._next(), numel, dt, float(scale), 0, _lib.S())
+        return out
+
+    def reduce_scatter(self, buf: SymmetricBuffer, out: torch.Tensor, chunk: int, elem_offset: int = 0, scale: float = 1.0) -> torch.Tensor:
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        _lib.call("ft_comm_reduce_scatter", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world,
+                  self._next(), chunk, dt, float(scale), 0, _lib.S())
+        return out
+
+    def all_gather(self, buf: SymmetricBuffer, src: torch.Tensor, chunk: int, elem_offset: int = 0) -> None:
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        _lib.call("ft_comm_allgather", buf.ptr_array(elem_offset), src, self.flag_ptrs, self.counter, self.rank, self.world, self._next(),
+                  chunk, dt, 0, _lib.S())
+
+    def barrier(self) -> None:
+        _lib.call("ft_comm_barrier", self.flag_ptrs, self.counter, self.rank, self.world, self._next(), _lib.S())
+
+    def check(self) -> None:
+        """Synchronise and raise :class:`Timeout` if a device-side wait on a peer ran out since the last check."""
+        st = _lib.read_status()
+        if st:
+            kernel, site, peer = st >> 24, (st >> 16) & 0xFF, st & 0xFFFF
+            raise Timeout(message=f"device-side wait timed out: kernel {kernel}, site {site}, peer {peer}")
+
+
+class FusedShardedAdamW:
+    """Reduce-scatter + sharded AdamW + all-gather of one flat unit in a single kernel over peer memory.
+
+    Owns the symmetric arenas: every unit's bf16 parameter buffer is moved into one symmetric allocation and the
+    engine's rotating gradient buffers into another, so a peer can read any rank's gradients and write any
+    rank's parameters.
+    """
+
+    def __init__(self, engine):
+        self.e = engine
+        dev, group = engine.device, engine.pg
+        self.comm = SymmComm(dev, group)
+        units = engine.units
+        total = sum(u.padded for u in units)
+        self.params = SymmetricBuffer(total, torch.bfloat16, dev, group)
+        off = 0
+        self.offset = {}
+        name_to_param = {}
+        for mod in engine.model.modules():
+            for attr, unit_attr in (("flat", "unit"), ("embed_flat", "embed_unit"), ("norm_flat", "norm_unit"), ("head_flat", "head_unit")):
+                if hasattr(mod, attr) and hasattr(mod, unit_attr):
+                    name_to_param[getattr(mod, unit_attr).name] = getattr(mod, attr)
+        with torch.no_grad():
+            for u in units:
+                view = self.params.tensor[off: off + u.padded]
+                view.copy_(u.full)
+                u.full = view
+                p = name_to_param.get(u.name)
+                if p is not None:
+                    p.data = view
+                self.offset[u.name] = off
+                off += u.padded
+        nbuf = len(engine._grad_pool)
+        self.maxn = max(u.padded for u in units)
+        self.grads = SymmetricBuffer(nbuf * self.maxn, torch.bfloat16, dev, group)
+        engine._grad_pool = [self.grads.tensor[i * self.maxn: (i + 1) * self.maxn] for i in range(nbuf)]
+        torch.cuda.synchronize(dev)
+        import torch.distributed as dist
+        dist.barrier(group)
+
+    def step(self, unit, slot: int) -> None:
+        o = self.e.optim
+        c = self.comm
+        _lib.call("ft_fsdp_rs_adamw_ag", self.grads.ptr_array(slot * self.maxn), self.params.ptr_array(self.offset[unit.name]),
+                  c.flag_ptrs, c.counter, c.rank, c.world, c._next(), unit.master, unit.exp_avg, unit.exp_avg_sq, unit.chunk, o.lr,
+                  o.betas[0], o.betas[1], o.eps, o.weight_decay, unit.step, None, 0, _lib.S())
