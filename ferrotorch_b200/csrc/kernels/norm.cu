@@ -6,6 +6,7 @@
 // RMSNORM_BF16_PTX (ferrotorch-gpu/src/bf16.rs:926), LAYERNORM* (kernels.rs:7394,7593).
 #include "common.cuh"
 #include "host_common.h"
+#include <mutex>
 
 #define FT_VPT_DISPATCH(d, ...)                              \
   do {                                                      \
@@ -307,5 +308,66 @@ FT_EXPORT int ft_layernorm_bwd(const void* x, const void* w, const void* dy, con
                                             (__nv_bfloat16*)dx, dw_partial, db_partial, rows, d));
   colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, nullptr, grid, d, 0);
   colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(db_partial, (__nv_bfloat16*)db_bf16, nullptr, grid, d, 0);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared in include/ferrotorch/noalloc.h).
+//
+// Some callers cannot allocate device memory at the point where they need this kernel: code running inside a
+// region where cudaMalloc is forbidden or would synchronise the device (a latency-critical serving loop, a
+// plug-in that was handed fixed buffers by its host application, a process whose memory pool is owned by
+// another runtime). ft_rmsnorm_bwd needs a scratch buffer for the per-CTA partial sums of dw; this variant keeps
+// that scratch in a fixed array that lives inside the loaded library image on every GPU, so the call itself
+// performs no cudaMalloc / cudaFree and calls no allocating library routine.
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+constexpr int NOALLOC_PARTS = 148;        // one partial row per SM
+constexpr int NOALLOC_MAX_D = 8192;       // largest hidden size accepted
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[NOALLOC_PARTS * NOALLOC_MAX_D];   // 4.6 MiB per GPU
+
+float* g_noalloc_scratch_ptr[64] = {nullptr};
+std::mutex g_noalloc_mu;
+
+// The array's name is only a host-side handle; the device address has to be asked for, once per device,
+// with that device current.
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  FT_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FT_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_scratch_ptr[dev]) {
+    float* p = nullptr;
+    FT_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_bwd_scratch));
+    if (!p) return FT_ERR_DRIVER;
+    g_noalloc_scratch_ptr[dev] = p;
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return FT_OK;
+}
+}  // namespace
+
+FT_EXPORT int ft_rmsnorm_bwd_noalloc_max_d() { return NOALLOC_MAX_D; }
+
+FT_EXPORT int ft_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
+                                     void* dw_bf16, float* dw_f32, int accumulate, int rows, int d, cudaStream_t st) {
+  if (d % 8 || rows <= 0 || d <= 0) return FT_ERR_ARG;
+  if (d > NOALLOC_MAX_D) {
+    fprintf(stderr, "[ferrotorch_b200] ft_rmsnorm_bwd_noalloc: hidden size %d exceeds the built-in scratch (max %d); "
+                    "use ft_rmsnorm_bwd with caller-provided scratch\n", d, NOALLOC_MAX_D);
+    return FT_ERR_TOO_LARGE;
+  }
+  float* scratch = nullptr;
+  int r = noalloc_scratch(&scratch);
+  if (r) return r;
+  const int grid = rows < NOALLOC_PARTS ? rows : NOALLOC_PARTS;
+  // every partial row in [0, grid) is fully overwritten by its CTA, so nothing has to be cleared between calls
+  if (dres)
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
+                                                                      rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, d));
+  else
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
+                                                                       rstd, nullptr, (__nv_bfloat16*)dx, scratch, rows, d));
+  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();
 }
