@@ -8,8 +8,8 @@
 //             blocks (64 queries): S^T = K.Q^T, dP^T = V.dO^T -> P^T, dS^T -> dV += P^T.dO, dK += dS^T.Q
 // Every product is a tcgen05.mma with the accumulator in TMEM; the "transposed" operands (K in dS.K, dO in P^T.dO,
 // Q in dS^T.Q) are the same shared-memory tiles read through MN-major descriptors, so nothing is transposed or
-// loaded twice. Roles per CTA as in the forward kernel: warp 0 TMA, warp 1 MMA issue, warps 2..5 one thread per
-// accumulator row for the exp2 / dS arithmetic and the final TMEM -> bf16 -> smem -> TMA store.
+// loaded twice. Roles per CTA (320 threads): warp 0 TMA, warp 1 MMA issue, warps 2..9 two threads per
+// accumulator row (32 columns each) for the exp2 / dS arithmetic and the final TMEM -> bf16 -> smem -> TMA store.
 //
 // The reference has no attention backward on the GPU (ferrotorch-gpu/src/flash_attention.rs is forward only;
 // ferrotorch-nn/src/flash_attention.rs:373-384 recomputes untiled on the CPU).
@@ -19,7 +19,7 @@
 namespace {
 
 constexpr int BD = 128;                 // head dim
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;             // warp 0 TMA, warp 1 MMA, warps 2..9 arithmetic (two warps per TMEM lane quarter, 32 columns each)
 constexpr float LOG2E = 1.4426950408889634f;
 
 FT_DEVICE bool bw_wait(uint64_t* bar, uint32_t parity) {
@@ -97,7 +97,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&sp_full[i], 1); }
-    mbar_init(ds_ready, 128);
+    mbar_init(ds_ready, 256);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
@@ -173,6 +173,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;          // which 32 of the 64 key columns this warp handles
     const int r = q * 32 + lane;
     const int qidx = m0 + r;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
@@ -184,9 +185,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       if (!bw_wait(&sp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_BWD, 5, j); ok = false; break; }
       tc_fence_after();
       const int kv0 = j * DQ_BN;
-      uint32_t pk[32];
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
+      uint32_t pk[16];
+      {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tS + lane_off + (j & 1) * 64 + half * 32, sv);
         tmem_ld_32x32b_x32(tdP + lane_off + (j & 1) * 64 + half * 32, dv);
@@ -202,7 +202,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
             ds[e] = p * (__uint_as_float(dv[col]) - dlt) * scale;
           }
           __nv_bfloat162 hh = __floats2bfloat162_rn(ds[0], ds[1]);
-          pk[half * 16 + c] = *reinterpret_cast<uint32_t*>(&hh);
+          pk[c] = *reinterpret_cast<uint32_t*>(&hh);
         }
       }
       if (j > 0) {
@@ -210,8 +210,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       }
       uint8_t* row = sdS + r * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; c8++)
-        *reinterpret_cast<uint4*>(row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
+      for (int c4 = 0; c4 < 4; c4++)
+        *reinterpret_cast<uint4*>(row + (((half * 4 + c4) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -220,7 +220,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
     if (ok) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; c++) {
+      for (int c = half * 2; c < half * 2 + 2; c++) {
         uint32_t ov[32];
         tmem_ld_32x32b_x32(tdQ + lane_off + c * 32, ov);
         tmem_ld_wait();
@@ -238,7 +238,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (threadIdx.x == 64) {
         tma_store_3d(&tmdQ, sQ, h * BD, m0, b);
         tma_store_3d(&tmdQ, sQ + 16384, h * BD + 64, m0, b);
@@ -298,7 +298,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); mbar_init(&st_full[i], 1); }
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(dkv_done, 1);
     mbar_fence_init();
   }
@@ -379,30 +379,30 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
     }
   } else {
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;            // which 32 of the 64 query columns this warp handles
     const int r = q * 32 + lane;                 // key row inside the block
     const int kvidx = kv0 + r;
-    const int tid = threadIdx.x - 64;            // 0..127 among the row threads
+    const int tid = threadIdx.x - 64;            // 0..255 among the arithmetic threads
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const bool kvalid = kvidx < S;
     bool ok = true;
     for (int it = 0; it < n_it && ok; it++) {
       const int hq = g * group + it / nqi, q0 = (i_start + it % nqi) * DKV_BM;
       // stage this step's row statistics: threads 0..63 fetch lse (log2 domain), 64..127 fetch delta
-      {
+      if (tid < 128) {
         const int qi = q0 + (tid & 63);
         float v;
         if (tid < 64) v = (qi < S) ? lse[((size_t)b * Hq + hq) * S + qi] * LOG2E : INFINITY;
         else v = (qi < S) ? delta[((size_t)b * Hq + hq) * S + qi] : 0.f;
         sStat[(it & 1) * 128 + tid] = v;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       const float* st_lse = sStat + (it & 1) * 128;
       const float* st_dlt = st_lse + 64;
       if (!bw_wait(&st_full[it & 1], (it >> 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_BWD, 15, it); ok = false; break; }
       tc_fence_after();
-      uint32_t ppk[32], dpk[32];
-#pragma unroll
-      for (int half = 0; half < 2; half++) {
+      uint32_t ppk[16], dpk[16];
+      {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tSt + lane_off + (it & 1) * 64 + half * 32, sv);
         tmem_ld_32x32b_x32(tdPt + lane_off + (it & 1) * 64 + half * 32, dv);
@@ -419,8 +419,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
             ds[e] = p * (__uint_as_float(dv[2 * c + e]) - st_dlt[col]) * scale;
           }
           __nv_bfloat162 hp = __floats2bfloat162_rn(pp[0], pp[1]), hd = __floats2bfloat162_rn(ds[0], ds[1]);
-          ppk[half * 16 + c] = *reinterpret_cast<uint32_t*>(&hp);
-          dpk[half * 16 + c] = *reinterpret_cast<uint32_t*>(&hd);
+          ppk[c] = *reinterpret_cast<uint32_t*>(&hp);
+          dpk[c] = *reinterpret_cast<uint32_t*>(&hd);
         }
       }
       if (it > 0) {
@@ -429,9 +429,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
       uint8_t* prow = sPt + r * 128;
       uint8_t* drow = sdSt + r * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; c8++) {
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(ppk[4 * c8], ppk[4 * c8 + 1], ppk[4 * c8 + 2], ppk[4 * c8 + 3]);
-        *reinterpret_cast<uint4*>(drow + ((c8 ^ (r & 7)) << 4)) = make_uint4(dpk[4 * c8], dpk[4 * c8 + 1], dpk[4 * c8 + 2], dpk[4 * c8 + 3]);
+      for (int c4 = 0; c4 < 4; c4++) {
+        const int sw = ((half * 4 + c4) ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(prow + sw) = make_uint4(ppk[4 * c4], ppk[4 * c4 + 1], ppk[4 * c4 + 2], ppk[4 * c4 + 3]);
+        *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dpk[4 * c4], dpk[4 * c4 + 1], dpk[4 * c4 + 2], dpk[4 * c4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -446,7 +447,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         const uint32_t tsrc = which == 0 ? tdV : tdK;
         uint8_t* sdst = which == 0 ? sV : sK;
 #pragma unroll 1
-        for (int c = 0; c < 4; c++) {
+        for (int c = half * 2; c < half * 2 + 2; c++) {
           uint32_t ov[32];
           tmem_ld_32x32b_x32(tsrc + lane_off + c * 32, ov);
           tmem_ld_wait();
@@ -465,7 +466,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (threadIdx.x == 64) {
         tma_store_3d(&tmdKV, sV, vcol, kv0, b);
         tma_store_3d(&tmdKV, sV + 16384, vcol + 64, kv0, b);

@@ -93,7 +93,7 @@ class FSDP:
             if u.world != self.world or u.rank != self.rank:
                 raise InvalidArgument(f"unit {u.name} was built for world {u.world}/rank {u.rank}, engine has {self.world}/{self.rank}")
         self.device = self.units[0].device
-        self.comm = comm or os.environ.get("FT_FSDP_COMM", "nccl")
+        self.comm = comm or os.environ.get("FT_FSDP_COMM", "fused")
         self.step_count = 0
         cuda = self.device.type == "cuda"
         self.side = torch.cuda.Stream(device=self.device, priority=0) if (cuda and overlap_optimizer) else None
@@ -114,7 +114,14 @@ class FSDP:
         self._fused = None
         if self.world > 1 and self.comm == "fused":
             from .symm import FusedShardedAdamW
-            self._fused = FusedShardedAdamW(self)
+            try:
+                self._fused = FusedShardedAdamW(self)
+            except (RuntimeError, ImportError, AttributeError) as e:   # no symmetric memory on this fabric: library collectives
+                import warnings
+                warnings.warn(f"symmetric memory unavailable ({e}); FSDP falls back to NCCL collectives")
+                self.comm = "nccl"
+        if self.world == 1:
+            self.comm = "none"
 
     # -- owner plumbing ---------------------------------------------------------------
     @staticmethod

@@ -1,0 +1,149 @@
+"""Worker entry points for the multi-process tests (launched by torch.distributed.run from test_multigpu.py).
+
+    python -m torch.distributed.run --nproc-per-node N tests/mp_workers.py <case>
+"""
+import os
+import sys
+import time
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+import torch
+import torch.distributed as dist
+
+
+def _init():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    return rank, world, dev
+
+
+def case_collectives():
+    from ferrotorch_b200.parallel.symm import SymmComm, SymmetricBuffer
+    rank, world, dev = _init()
+    comm = SymmComm(dev)
+    for dtype, tol in ((torch.bfloat16, 2e-2), (torch.float32, 1e-5)):
+        for n in (8 * world, 1 << 12, (1 << 20) + 8 * world * 3, 3 * (1 << 22)):
+            buf = SymmetricBuffer(n, dtype, dev)
+            torch.manual_seed(100 + rank)
+            x = (torch.rand(n, device=dev) * 2 - 1).to(dtype)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            for nvls in (False, True):
+                buf.tensor.copy_(x)
+                torch.cuda.synchronize(); dist.barrier()
+                comm.all_reduce_(buf, n, scale=1.0, use_nvls=nvls)
+                comm.check()
+                err = (buf.tensor.float() - ref).abs().max().item()
+                assert err <= tol * world, (str(dtype), n, nvls, err)
+            # mean via scale, one-shot
+            buf.tensor.copy_(x)
+            torch.cuda.synchronize(); dist.barrier()
+            out = torch.empty(n, device=dev, dtype=dtype)
+            comm.all_reduce_small(buf, out, n, scale=1.0 / world)
+            comm.check()
+            assert (out.float() - ref / world).abs().max().item() <= tol
+            # reduce-scatter / all-gather round trip
+            chunk = n // world
+            if chunk % 8 == 0 and chunk * world == n:
+                buf.tensor.copy_(x)
+                torch.cuda.synchronize(); dist.barrier()
+                rs = torch.empty(chunk, device=dev, dtype=dtype)
+                comm.reduce_scatter(buf, rs, chunk)
+                comm.check()
+                assert (rs.float() - ref[rank * chunk:(rank + 1) * chunk]).abs().max().item() <= tol * world
+                comm.all_gather(buf, rs, chunk)
+                comm.check()
+                assert (buf.tensor.float() - ref).abs().max().item() <= tol * world
+            del buf
+    comm.barrier()
+    comm.check()
+    # bit-identical across ranks (fixed reduction order)
+    n = 1 << 16
+    buf = SymmetricBuffer(n, torch.float32, dev)
+    torch.manual_seed(7 + rank)
+    buf.tensor.copy_(torch.randn(n, device=dev))
+    torch.cuda.synchronize(); dist.barrier()
+    comm.all_reduce_(buf, n, scale=1.0 / world, use_nvls=False)
+    comm.check()
+    gathered = [torch.empty(n, device=dev) for _ in range(world)]
+    dist.all_gather(gathered, buf.tensor)
+    for g in gathered[1:]:
+        assert torch.equal(g, gathered[0])
+    if rank == 0:
+        print("COLLECTIVES_OK")
+
+
+def case_fsdp():
+    from ferrotorch_b200.models import LlamaConfig, LlamaForCausalLM
+    from ferrotorch_b200.parallel import FSDP, AdamWConfig
+    rank, world, dev = _init()
+    cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=512)
+    results = {}
+    for comm in ("nccl", "fused"):
+        model = LlamaForCausalLM(cfg, device=dev, world=world, rank=rank, seed=0)
+        eng = FSDP(model, AdamWConfig(lr=3e-3, betas=(0.9, 0.95), weight_decay=0.01), comm=comm)
+        torch.manual_seed(11 + rank)
+        ids = torch.randint(0, cfg.vocab_size, (2, 129), device=dev)
+        losses = []
+        for _ in range(6):
+            losses.append(eng.train_step(ids[:, :-1], ids[:, 1:]).item())
+        eng.synchronize()
+        torch.cuda.synchronize()
+        from ferrotorch_b200 import _lib
+        assert _lib.read_status() == 0
+        w = model.model.layers[0].unit.full.float().clone()
+        results[comm] = (losses, w)
+        # parameters identical on every rank after the updates
+        ws = [torch.empty_like(w) for _ in range(world)]
+        dist.all_gather(ws, w)
+        for o in ws[1:]:
+            assert torch.equal(o, ws[0]), comm
+        assert losses[-1] < losses[0], (comm, losses)
+    la, lb = results["nccl"][0], results["fused"][0]
+    assert all(abs(a - b) < 5e-2 for a, b in zip(la, lb)), (la, lb)
+    rel = (results["nccl"][1] - results["fused"][1]).norm() / results["nccl"][1].norm()
+    assert rel.item() < 2e-2, rel.item()
+    if rank == 0:
+        print("FSDP_OK", la, lb)
+
+
+def case_timeout():
+    """A peer that does not show up: the waiting rank's kernel gives up after its deadline and reports it."""
+    from ferrotorch_b200.parallel.symm import SymmComm
+    from ferrotorch_b200.errors import Timeout
+    rank, world, dev = _init()
+    comm = SymmComm(dev)
+    comm.barrier()
+    comm.check()
+    if rank == 0:
+        comm.barrier()                 # nobody else joins this one
+        try:
+            comm.check()
+            raise AssertionError("expected a timeout")
+        except Timeout:
+            pass
+    else:
+        comm.seq += 1                  # stay in step with rank 0's sequence numbers without launching anything
+        time.sleep(3.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    # the context is still usable and the fabric still works after the timeout
+    comm.barrier()
+    comm.check()
+    x = torch.ones(4, device=dev)
+    dist.all_reduce(x)
+    assert x[0].item() == world
+    if rank == 0:
+        print("TIMEOUT_OK")
+
+
+if __name__ == "__main__":
+    try:
+        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout}[sys.argv[1]]()
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()

@@ -1,0 +1,40 @@
+"""Multi-GPU tests: peer-memory collectives, fused FSDP kernel vs the NCCL path, bounded-wait timeout.
+
+Each case runs as child processes (one per GPU) under torch.distributed.run on 127.0.0.1."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _run(case: str, nproc: int, port: int, extra_env=None, timeout=600):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "mp_workers.py"), case]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stdout[-3000:] + "\n" + r.stderr[-3000:]
+    return r.stdout
+
+
+def _n():
+    return min(torch.cuda.device_count(), 4)
+
+
+def test_symm_collectives():
+    assert "COLLECTIVES_OK" in _run("collectives", _n(), 29611)
+
+
+def test_fsdp_fused_matches_nccl():
+    assert "FSDP_OK" in _run("fsdp", _n(), 29612)
+
+
+def test_peer_timeout_is_reported_not_hung():
+    out = _run("timeout", 2, 29613, {"NCCL_NVLS_ENABLE": "0", "FT_DISABLE_NVLS": "1"})
+    assert "TIMEOUT_OK" in out
