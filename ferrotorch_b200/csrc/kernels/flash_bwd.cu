@@ -59,7 +59,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
 // dQ
 // ------------------------------------------------------------------------------------------------------------
 constexpr int DQ_BM = 128, DQ_BN = 64;
-constexpr int DQ_SMEM_DATA = 32768 /*Q*/ + 32768 /*dO*/ + 2 * 16384 /*K*/ + 2 * 16384 /*V*/ + 16384 /*dS*/;
+constexpr int DQ_ST = 3;              // K/V ring depth: a slot is released only after dQ += dS.K of its block, so two blocks must be in flight
+constexpr int DQ_SMEM_DATA = 32768 /*Q*/ + 32768 /*dO*/ + DQ_ST * 16384 /*K*/ + DQ_ST * 16384 /*V*/ + 16384 /*dS*/;
 constexpr int DQ_SMEM = DQ_SMEM_DATA + 256 + 1024;
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -73,17 +74,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sdO = sQ + 32768;
-  uint8_t* sK = sdO + 32768;      // 2 stages x 16 KiB
-  uint8_t* sV = sK + 32768;       // 2 stages x 16 KiB
-  uint8_t* sdS = sV + 32768;      // 16 KiB
+  uint8_t* sK = sdO + 32768;              // DQ_ST stages x 16 KiB
+  uint8_t* sV = sK + DQ_ST * 16384;       // DQ_ST stages x 16 KiB
+  uint8_t* sdS = sV + DQ_ST * 16384;      // 16 KiB
   uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + 16384);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;   // [2]
-  uint64_t* ds_ready = bars + 7;
-  uint64_t* dq_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* kv_full = bars + 1;   // [DQ_ST]
+  uint64_t* kv_empty = bars + 5;  // [DQ_ST]
+  uint64_t* sp_full = bars + 9;   // [2]
+  uint64_t* ds_ready = bars + 11;
+  uint64_t* dq_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mblk = gridDim.x - 1 - blockIdx.x;
@@ -96,7 +97,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&sp_full[i], 1); }
+    for (int i = 0; i < DQ_ST; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < 2; i++) mbar_init(&sp_full[i], 1);
     mbar_init(ds_ready, 256);
     mbar_init(dq_done, 1);
     mbar_fence_init();
@@ -118,8 +120,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       tma_load_3d(sdO + 16384, &tmdO, qdo_full, h * BD + 64, m0, b);
       const int kcol = (Hq + g) * BD, vcol = (Hq + Hkv + g) * BD;
       for (int j = 0; j < nblk; j++) {
-        const int s = j & 1;
-        if (!bw_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_BWD, 1, j); break; }
+        const int s = j % DQ_ST;
+        if (!bw_wait(&kv_empty[s], ((j / DQ_ST) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_BWD, 1, j); break; }
         mbar_expect_tx(&kv_full[s], 32768);
         tma_load_3d(sK + s * 16384, &tmKV, &kv_full[s], kcol, j * DQ_BN, b);
         tma_load_3d(sK + s * 16384 + 8192, &tmKV, &kv_full[s], kcol + 64, j * DQ_BN, b);
@@ -133,7 +135,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       constexpr uint32_t idesc_dq = make_idesc_f16(128, 128, 1, 0, 1);
       const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sdO), ds_base = smem_u32(sdS);
       auto issue_s_dp = [&](int j) {
-        const uint32_t k_base = smem_u32(sK + (j & 1) * 16384), v_base = smem_u32(sV + (j & 1) * 16384);
+        const uint32_t k_base = smem_u32(sK + (j % DQ_ST) * 16384), v_base = smem_u32(sV + (j % DQ_ST) * 16384);
 #pragma unroll
         for (int kk = 0; kk < 8; kk++) {
           const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
@@ -155,19 +157,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
         issue_s_dp(0);
         for (int j = 0; j < nblk; j++) {
           if (j + 1 < nblk) {
-            if (!bw_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1)) { ft_set_status(status, FT_K_FA_BWD, 3, j); break; }
+            if (!bw_wait(&kv_full[(j + 1) % DQ_ST], ((j + 1) / DQ_ST) & 1)) { ft_set_status(status, FT_K_FA_BWD, 3, j); break; }
             tc_fence_after();
             issue_s_dp(j + 1);
           }
           if (!bw_wait(ds_ready, j & 1)) { ft_set_status(status, FT_K_FA_BWD, 4, j); break; }
           tc_fence_after();
-          const uint32_t k_base = smem_u32(sK + (j & 1) * 16384);
+          const uint32_t k_base = smem_u32(sK + (j % DQ_ST) * 16384);
 #pragma unroll
           for (int kk = 0; kk < 4; kk++)
             umma_f16_ss(tdQ, make_smem_desc(ds_base + kk * 32, 16, 1024, FT_SWZ_128B),
                         make_smem_desc(k_base + kk * 2048, 8192, 1024, FT_SWZ_128B), idesc_dq, (j | kk) != 0);
           umma_commit(dq_done);
-          umma_commit(&kv_empty[j & 1]);
+          umma_commit(&kv_empty[j % DQ_ST]);
         }
       }
     }
@@ -256,7 +258,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
 // dK / dV
 // ------------------------------------------------------------------------------------------------------------
 constexpr int DKV_BN = 128 /*keys per CTA*/, DKV_BM = 64 /*queries per step*/;
-constexpr int DKV_SMEM_DATA = 32768 /*K*/ + 32768 /*V*/ + 2 * 16384 /*Q*/ + 2 * 16384 /*dO*/ + 16384 /*P^T*/ + 16384 /*dS^T*/ + 1024 /*stats*/;
+constexpr int DKV_ST = 3;             // Q/dO ring depth (a slot is released only after dV/dK of its step)
+constexpr int DKV_SMEM_DATA = 32768 /*K*/ + 32768 /*V*/ + DKV_ST * 16384 /*Q*/ + DKV_ST * 16384 /*dO*/ + 16384 /*P^T*/ + 16384 /*dS^T*/ + 1024 /*stats*/;
 constexpr int DKV_SMEM = DKV_SMEM_DATA + 256 + 1024;
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -270,19 +273,19 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + 32768;
-  uint8_t* sQ = sV + 32768;        // 2 stages x 16 KiB
-  uint8_t* sdO = sQ + 32768;       // 2 stages x 16 KiB
-  uint8_t* sPt = sdO + 32768;      // 16 KiB
+  uint8_t* sQ = sV + 32768;                // DKV_ST stages x 16 KiB
+  uint8_t* sdO = sQ + DKV_ST * 16384;      // DKV_ST stages x 16 KiB
+  uint8_t* sPt = sdO + DKV_ST * 16384;     // 16 KiB
   uint8_t* sdSt = sPt + 16384;     // 16 KiB
   float* sStat = reinterpret_cast<float*>(sdSt + 16384);   // [2][128]: lse2 (64) | delta (64)
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStat) + 1024);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;   // [2]
-  uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* st_full = bars + 5;    // [2]
-  uint64_t* pds_ready = bars + 7;
-  uint64_t* dkv_done = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* qdo_full = bars + 1;   // [DKV_ST]
+  uint64_t* qdo_empty = bars + 5;  // [DKV_ST]
+  uint64_t* st_full = bars + 9;    // [2]
+  uint64_t* pds_ready = bars + 11;
+  uint64_t* dkv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = blockIdx.x;                      // key block 0 has the most query blocks and is scheduled first
@@ -297,7 +300,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); mbar_init(&st_full[i], 1); }
+    for (int i = 0; i < DKV_ST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    for (int i = 0; i < 2; i++) mbar_init(&st_full[i], 1);
     mbar_init(pds_ready, 256);
     mbar_init(dkv_done, 1);
     mbar_fence_init();
@@ -319,9 +323,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
       tma_load_3d(sV, &tmKV128, kv_full, vcol, kv0, b);
       tma_load_3d(sV + 16384, &tmKV128, kv_full, vcol + 64, kv0, b);
       for (int it = 0; it < n_it; it++) {
-        const int s = it & 1;
+        const int s = it % DKV_ST;
         const int hq = g * group + it / nqi, q0 = (i_start + it % nqi) * DKV_BM;
-        if (!bw_wait(&qdo_empty[s], ((it >> 1) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_BWD, 11, it); break; }
+        if (!bw_wait(&qdo_empty[s], ((it / DKV_ST) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_BWD, 11, it); break; }
         mbar_expect_tx(&qdo_full[s], 32768);
         tma_load_3d(sQ + s * 16384, &tmQ64, &qdo_full[s], hq * BD, q0, b);
         tma_load_3d(sQ + s * 16384 + 8192, &tmQ64, &qdo_full[s], hq * BD + 64, q0, b);
@@ -335,7 +339,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
       constexpr uint32_t idesc_acc = make_idesc_f16(128, 128, 1, 0, 1);
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), pt_base = smem_u32(sPt), dst_base = smem_u32(sdSt);
       auto issue_st = [&](int it) {
-        const uint32_t q_base = smem_u32(sQ + (it & 1) * 16384), do_base = smem_u32(sdO + (it & 1) * 16384);
+        const uint32_t q_base = smem_u32(sQ + (it % DKV_ST) * 16384), do_base = smem_u32(sdO + (it % DKV_ST) * 16384);
 #pragma unroll
         for (int kk = 0; kk < 8; kk++) {
           const uint32_t ao = (kk >> 2) * 16384 + (kk & 3) * 32, bo = (kk >> 2) * 8192 + (kk & 3) * 32;
@@ -357,13 +361,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         issue_st(0);
         for (int it = 0; it < n_it; it++) {
           if (it + 1 < n_it) {
-            if (!bw_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1)) { ft_set_status(status, FT_K_FA_BWD, 13, it); break; }
+            if (!bw_wait(&qdo_full[(it + 1) % DKV_ST], ((it + 1) / DKV_ST) & 1)) { ft_set_status(status, FT_K_FA_BWD, 13, it); break; }
             tc_fence_after();
             issue_st(it + 1);
           }
           if (!bw_wait(pds_ready, it & 1)) { ft_set_status(status, FT_K_FA_BWD, 14, it); break; }
           tc_fence_after();
-          const uint32_t q_base = smem_u32(sQ + (it & 1) * 16384), do_base = smem_u32(sdO + (it & 1) * 16384);
+          const uint32_t q_base = smem_u32(sQ + (it % DKV_ST) * 16384), do_base = smem_u32(sdO + (it % DKV_ST) * 16384);
 #pragma unroll
           for (int kk = 0; kk < 4; kk++)
             umma_f16_ss(tdV, make_smem_desc(pt_base + kk * 32, 16, 1024, FT_SWZ_128B),
@@ -373,7 +377,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
             umma_f16_ss(tdK, make_smem_desc(dst_base + kk * 32, 16, 1024, FT_SWZ_128B),
                         make_smem_desc(q_base + kk * 2048, 8192, 1024, FT_SWZ_128B), idesc_acc, (it | kk) != 0);
           umma_commit(dkv_done);
-          umma_commit(&qdo_empty[it & 1]);
+          umma_commit(&qdo_empty[it % DKV_ST]);
         }
       }
     }
@@ -386,17 +390,19 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const bool kvalid = kvidx < S;
     bool ok = true;
+    // row statistics of a step (threads 0..63 fetch lse in the log2 domain, 64..127 fetch delta) are fetched one step
+    // ahead, so the global-memory latency is hidden behind the previous step's arithmetic
+    auto fetch_stat = [&](int it2) -> float {
+      const int hq2 = g * group + it2 / nqi, qi = (i_start + it2 % nqi) * DKV_BM + (tid & 63);
+      if (tid < 64) return (qi < S) ? lse[((size_t)b * Hq + hq2) * S + qi] * LOG2E : INFINITY;
+      return (qi < S) ? delta[((size_t)b * Hq + hq2) * S + qi] : 0.f;
+    };
+    if (tid < 128 && n_it > 0) sStat[tid] = fetch_stat(0);
     for (int it = 0; it < n_it && ok; it++) {
-      const int hq = g * group + it / nqi, q0 = (i_start + it % nqi) * DKV_BM;
-      // stage this step's row statistics: threads 0..63 fetch lse (log2 domain), 64..127 fetch delta
-      if (tid < 128) {
-        const int qi = q0 + (tid & 63);
-        float v;
-        if (tid < 64) v = (qi < S) ? lse[((size_t)b * Hq + hq) * S + qi] * LOG2E : INFINITY;
-        else v = (qi < S) ? delta[((size_t)b * Hq + hq) * S + qi] : 0.f;
-        sStat[(it & 1) * 128 + tid] = v;
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const int q0 = (i_start + it % nqi) * DKV_BM;
+      asm volatile("bar.sync 1, 256;" ::: "memory");    // publishes sStat[it&1]; everyone has finished reading sStat[(it+1)&1]
+      float next_stat = 0.f;
+      if (tid < 128 && it + 1 < n_it) next_stat = fetch_stat(it + 1);
       const float* st_lse = sStat + (it & 1) * 128;
       const float* st_dlt = st_lse + 64;
       if (!bw_wait(&st_full[it & 1], (it >> 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_BWD, 15, it); ok = false; break; }
@@ -434,6 +440,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         *reinterpret_cast<uint4*>(prow + sw) = make_uint4(ppk[4 * c4], ppk[4 * c4 + 1], ppk[4 * c4 + 2], ppk[4 * c4 + 3]);
         *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dpk[4 * c4], dpk[4 * c4 + 1], dpk[4 * c4 + 2], dpk[4 * c4 + 3]);
       }
+      if (tid < 128 && it + 1 < n_it) sStat[((it + 1) & 1) * 128 + tid] = next_stat;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_ready);

@@ -61,7 +61,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_full = bars + 7;    // [2]
   uint64_t* p_ready = bars + 9;
   uint64_t* pv_done = bars + 10;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_empty = bars + 11;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int mblk = gridDim.x - 1 - blockIdx.x;   // heaviest (latest) query blocks first
@@ -73,7 +74,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; i++) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); }
+    for (int i = 0; i < 2; i++) { mbar_init(&k_full[i], 1); mbar_init(&v_full[i], 1); mbar_init(&kv_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&k_empty[i], 1); }
     mbar_init(p_ready, 128);
     mbar_init(pv_done, 1);
     mbar_fence_init();
@@ -92,12 +93,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_load_3d(sQ, &tmQ, q_full, h * FA_D, m0, b);
       tma_load_3d(sQ + 16384, &tmQ, q_full, h * FA_D + 64, m0, b);
       const int kcol = (Hq + g) * FA_D, vcol = (Hq + Hkv + g) * FA_D;
-      for (int j = 0; j < nblk; j++) {
+      // load order K(0), K(1), V(0), K(2), V(1), ...: K's slot is free as soon as S of two blocks ago has retired, V's only
+      // after O += P.V of two blocks ago, so issuing K one block ahead of V keeps the single producer thread from stalling
+      // the next S behind a V slot
+      auto load_k = [&](int j) -> bool {
         const int s = j & 1;
-        if (!fa_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_FWD, 1, j); break; }
+        if (!fa_wait(&k_empty[s], ((j >> 1) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_FWD, 1, j); return false; }
         mbar_expect_tx(&k_full[s], FA_KV_BYTES);
         tma_load_3d(sK + s * FA_KV_BYTES, &tmKV, &k_full[s], kcol, j * FA_BN, b);
         tma_load_3d(sK + s * FA_KV_BYTES + 8192, &tmKV, &k_full[s], kcol + 64, j * FA_BN, b);
+        return true;
+      };
+      bool ok = load_k(0);
+      for (int j = 0; j < nblk && ok; j++) {
+        if (j + 1 < nblk) ok = load_k(j + 1);
+        if (!ok) break;
+        const int s = j & 1;
+        if (!fa_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) { ft_set_status(status, FT_K_FA_FWD, 9, j); break; }
         mbar_expect_tx(&v_full[s], FA_KV_BYTES);
         tma_load_3d(sV + s * FA_KV_BYTES, &tmKV, &v_full[s], vcol, j * FA_BN, b);
         tma_load_3d(sV + s * FA_KV_BYTES + 8192, &tmKV, &v_full[s], vcol + 64, j * FA_BN, b);
@@ -117,6 +129,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_f16_ss(tS + (j & 1) * FA_BN, ad, bd, idesc_s, kk != 0);
         }
         umma_commit(&s_full[j & 1]);
+        umma_commit(&k_empty[j & 1]);
       };
       bool ok = fa_wait(q_full, 0);
       if (ok) ok = fa_wait(&k_full[0], 0);

@@ -1,0 +1,10 @@
+"""Distributed runtime: backends, collectives, DDP (CPU control plane); the GPU engines live in ``ferrotorch_b200.parallel``."""
+from .backend import (Backend, TcpBackend, SimulatedBackend, SubBackend, FAULT_NONE, FAULT_DROP_NEXT_SEND, FAULT_DELAY_SEND_MS,
+                      FAULT_CORRUPT_LENGTH, FAULT_CLOSE)
+from .collective import (ReduceOp, DEFAULT_COLLECTIVE_TIMEOUT, allreduce, allreduce_with_timeout, broadcast, all_gather,
+                         all_gather_with_timeout, reduce_scatter, reduce_scatter_tensor, reduce_scatter_with_timeout, all_to_all,
+                         all_to_all_with_timeout, all_to_all_single_uneven, barrier, send, recv, sendrecv, PendingCollective,
+                         async_all_gather, async_reduce_scatter, async_allreduce)
+from .ddp import DDP, compute_buckets, DEFAULT_BUCKET_SIZE_BYTES
+from ..errors import (DistributedError, InvalidWorldSize, InvalidRank, SelfSend, SizeMismatch, IoError, ChannelClosed, UnsupportedOp,
+                      Timeout, NoConnection, BackendUnavailable)

@@ -1,0 +1,197 @@
+"""CPU control plane: backends, collectives, DDP (world size 2 over TCP, MLP 784-256-10), failure detection on the host."""
+import multiprocessing as mp
+import os
+import threading
+import time
+
+import pytest
+import torch
+
+import ferrotorch_b200.distributed as fd
+from ferrotorch_b200 import errors
+
+
+def _threads(world, fn):
+    backs = fd.SimulatedBackend.create_group(world)
+    out, errs = [None] * world, []
+
+    def run(r):
+        try:
+            out[r] = fn(backs[r], r)
+        except BaseException as e:  # noqa
+            errs.append(e)
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    [t.start() for t in ts]
+    [t.join(30) for t in ts]
+    if errs:
+        raise errs[0]
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("algo", ["star", "ring"])
+def test_allreduce_sum_mean(world, algo):
+    def fn(b, r):
+        x = torch.arange(10, dtype=torch.float32) + r
+        return fd.allreduce(x, b, fd.ReduceOp.Sum, algorithm=algo), fd.allreduce(x, b, fd.ReduceOp.Mean, algorithm=algo)
+    res = _threads(world, fn)
+    exp = sum(torch.arange(10, dtype=torch.float32) + r for r in range(world))
+    for s, m in res:
+        assert torch.equal(s, exp)
+        assert torch.allclose(m, exp / world)
+    for s, m in res[1:]:
+        assert torch.equal(m, res[0][1])       # bit-identical on every rank
+
+
+def test_all_gather_reduce_scatter_all_to_all_broadcast():
+    world = 4
+
+    def fn(b, r):
+        x = torch.full((2, 3), float(r))
+        g = fd.all_gather(x, b)
+        s = fd.all_gather(torch.tensor(float(r)), b)
+        rs = fd.reduce_scatter(torch.arange(8, dtype=torch.float32).reshape(8, 1) * (r + 1), b, fd.ReduceOp.Sum)
+        a2a = fd.all_to_all(torch.arange(4, dtype=torch.float32) + 10 * r, b)
+        bc = fd.broadcast(torch.full((3,), float(r)), b, root=2)
+        bt = fd.broadcast(torch.full((3,), float(r)), b, root=1, algorithm="tree")
+        return g, s, rs, a2a, bc, bt
+    res = _threads(world, fn)
+    for r, (g, s, rs, a2a, bc, bt) in enumerate(res):
+        assert g.shape == (8, 3) and torch.equal(g[::2, 0], torch.arange(4.0))
+        assert torch.equal(s, torch.arange(4.0))
+        assert torch.equal(rs.flatten(), torch.arange(8.0)[2 * r: 2 * r + 2] * 10)
+        assert torch.equal(a2a, torch.tensor([r + 10.0 * p for p in range(4)]))
+        assert torch.equal(bc, torch.full((3,), 2.0)) and torch.equal(bt, torch.full((3,), 1.0))
+
+
+def test_world1_identity_and_empty_and_errors():
+    (b,) = fd.SimulatedBackend.create_group(1)
+    x = torch.randn(4, 2)
+    assert torch.equal(fd.allreduce(x, b, fd.ReduceOp.Mean), x)
+    assert torch.equal(fd.all_gather(x, b), x)
+    assert fd.all_gather(torch.empty(0, 3), b).shape == (0, 3)
+    b2 = fd.SimulatedBackend.create_group(2)
+    with pytest.raises(errors.ShapeMismatch):
+        fd.reduce_scatter(torch.zeros(3, 2), b2[0])
+    with pytest.raises(errors.SelfSend):
+        b2[0].send(b"x", 0)
+    with pytest.raises(errors.InvalidRank):
+        b2[0].send(b"x", 5)
+
+
+def test_recv_timeout_and_fault_injection():
+    a, b = fd.SimulatedBackend.create_group(2)
+    t0 = time.time()
+    with pytest.raises(errors.Timeout):
+        a.recv_timeout(4, 1, 0.2)
+    assert 0.15 < time.time() - t0 < 2.0
+    # a dropped message: the receiver's collective times out instead of hanging
+    b.inject_fault(fd.FAULT_DROP_NEXT_SEND)
+    b.send(b"abcd", 0)
+    with pytest.raises(errors.Timeout):
+        a.recv_timeout(4, 1, 0.2)
+    # a corrupted frame length is reported as a size mismatch
+    b.inject_fault(fd.FAULT_CORRUPT_LENGTH)
+    b.send(b"abcd", 0)
+    with pytest.raises(errors.SizeMismatch):
+        a.recv_timeout(4, 1, 1.0)
+    # a closed channel is reported as such
+    b.inject_fault(fd.FAULT_CLOSE)
+    with pytest.raises(errors.ChannelClosed):
+        b.send(b"abcd", 0)
+    with pytest.raises(errors.ChannelClosed):
+        a.recv_timeout(4, 1, 1.0)
+
+
+def test_rank_that_never_joins_times_out_collective():
+    backs = fd.SimulatedBackend.create_group(2)
+    with pytest.raises(errors.Timeout):
+        fd.allreduce(torch.ones(4), backs[1], fd.ReduceOp.Sum, timeout=0.3)   # rank 0 never shows up
+
+
+def test_sub_backend_and_async():
+    def fn(b, r):
+        if r in (1, 3):
+            sub = fd.SubBackend(b, [1, 3])
+            return fd.allreduce(torch.tensor([float(r)]), sub, fd.ReduceOp.Sum)
+        return None
+    res = _threads(4, fn)
+    assert res[1].item() == 4.0 and res[3].item() == 4.0
+
+    def fn2(b, r):
+        h = fd.async_all_gather(torch.tensor([float(r)]), b)
+        return h.wait(10)
+    res = _threads(2, fn2)
+    assert torch.equal(res[0], torch.tensor([0.0, 1.0]))
+
+
+def test_bucket_plan_reverse_order():
+    ps = [torch.zeros(10), torch.zeros(20), torch.zeros(30), torch.zeros(5)]
+    assert fd.compute_buckets(ps, bucket_size_bytes=4 * 35) == [[3, 2], [1, 0]]
+    assert fd.compute_buckets(ps, bucket_size_bytes=1) == [[3], [2], [1], [0]]
+
+
+def _mlp(seed=0):
+    torch.manual_seed(seed)
+    m = torch.nn.Sequential(torch.nn.Linear(784, 256), torch.nn.ReLU(), torch.nn.Linear(256, 10))
+    for l in (m[0], m[2]):
+        torch.nn.init.kaiming_uniform_(l.weight, nonlinearity="relu")   # the reference's Linear init: Kaiming-uniform, ReLU gain, zero bias
+        torch.nn.init.zeros_(l.bias)
+    return m
+
+
+def _ddp_worker(rank, world, port, q):
+    torch.set_num_threads(1)
+    backend = fd.TcpBackend(rank, world, f"127.0.0.1:{port}")
+    model = _mlp(0)
+    ddp = fd.DDP(model, backend)
+    ddp.broadcast_parameters(0)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    g = torch.Generator().manual_seed(1234)
+    X = torch.randn(100, 128, 784, generator=g)
+    Y = torch.randint(0, 10, (100, 128), generator=g)
+    grads = None
+    for step in range(100):
+        x, y = X[step, rank * 64:(rank + 1) * 64], Y[step, rank * 64:(rank + 1) * 64]
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(ddp(x), y)
+        loss.backward()
+        ddp.sync_gradients()
+        if step == 99:
+            grads = [p.grad.numpy().copy() for p in model.parameters()]
+        opt.step()
+    q.put((rank, [p.detach().numpy().copy() for p in model.parameters()], grads))
+    backend.barrier()
+
+
+def test_config1_ddp_world2_tcp_matches_single_process():
+    """World size 2 over TCP, MLP 784->256->10, batch 64 per rank, SGD lr 0.01 momentum 0.9, 100 steps: gradients and
+    parameters bit-identical across ranks and within 1e-5 of single-process batch-128 training."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 100
+    ps = [ctx.Process(target=_ddp_worker, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in ps]
+    got = {}
+    for _ in range(2):
+        r, params, grads = q.get(timeout=180)
+        got[r] = (params, grads)
+    [p.join(30) for p in ps]
+    import numpy as np
+    for a, b in zip(got[0][0], got[1][0]):
+        assert np.array_equal(a, b)
+    for a, b in zip(got[0][1], got[1][1]):
+        assert np.array_equal(a, b)
+    # single process, batch 128
+    torch.set_num_threads(1)
+    model = _mlp(0)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    g = torch.Generator().manual_seed(1234)
+    X = torch.randn(100, 128, 784, generator=g)
+    Y = torch.randint(0, 10, (100, 128), generator=g)
+    for step in range(100):
+        opt.zero_grad()
+        torch.nn.functional.cross_entropy(model(X[step]), Y[step]).backward()
+        opt.step()
+    for a, b in zip(got[0][0], model.parameters()):
+        assert np.abs(a - b.detach().numpy()).max() < 1e-5
