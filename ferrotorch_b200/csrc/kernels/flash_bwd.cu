@@ -8,8 +8,8 @@
 //             blocks (64 queries): S^T = K.Q^T, dP^T = V.dO^T -> P^T, dS^T -> dV += P^T.dO, dK += dS^T.Q
 // Every product is a tcgen05.mma with the accumulator in TMEM; the "transposed" operands (K in dS.K, dO in P^T.dO,
 // Q in dS^T.Q) are the same shared-memory tiles read through MN-major descriptors, so nothing is transposed or
-// loaded twice. Roles per CTA (320 threads): warp 0 TMA, warp 1 MMA issue, warps 2..9 two threads per
-// accumulator row (32 columns each) for the exp2 / dS arithmetic and the final TMEM -> bf16 -> smem -> TMA store.
+// loaded twice. Roles per CTA: warp 0 TMA, warp 1 MMA issue, then BWD_PARTS arithmetic warps per TMEM lane quarter, i.e. BWD_PARTS threads per
+// accumulator row (64/BWD_PARTS columns each) for the exp2 / dS arithmetic and the final TMEM -> bf16 -> smem -> TMA store.
 //
 // The reference has no attention backward on the GPU (ferrotorch-gpu/src/flash_attention.rs is forward only;
 // ferrotorch-nn/src/flash_attention.rs:373-384 recomputes untiled on the CPU).
@@ -19,8 +19,17 @@
 namespace {
 
 constexpr int BD = 128;                 // head dim
-constexpr int BWD_THREADS = 320;             // warp 0 TMA, warp 1 MMA, warps 2..9 arithmetic (two warps per TMEM lane quarter, 32 columns each)
+constexpr int BWD_PARTS = 2;                 // arithmetic warps per TMEM lane quarter; each handles 64/BWD_PARTS = 16 score columns
+constexpr int BWD_COLS = 64 / BWD_PARTS;
+constexpr int BWD_ARITH = 128 * BWD_PARTS;    // arithmetic threads
+constexpr int BWD_THREADS = 64 + BWD_ARITH;   // warp 0 TMA, warp 1 MMA, then the arithmetic warps (latency is hidden by warp count: 4 per scheduler)
 constexpr float LOG2E = 1.4426950408889634f;
+
+template <int COLS>
+FT_DEVICE void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  if constexpr (COLS == 32) tmem_ld_32x32b_x32(taddr, r);
+  else tmem_ld_32x32b_x16(taddr, r);
+}
 
 FT_DEVICE bool bw_wait(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -99,7 +108,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
     mbar_init(qdo_full, 1);
     for (int i = 0; i < DQ_ST; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     for (int i = 0; i < 2; i++) mbar_init(&sp_full[i], 1);
-    mbar_init(ds_ready, 256);
+    mbar_init(ds_ready, BWD_ARITH);
     mbar_init(dq_done, 1);
     mbar_fence_init();
   }
@@ -175,7 +184,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
     }
   } else {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;          // which 32 of the 64 key columns this warp handles
+    const int part = (warp - 2) >> 2;          // which BWD_COLS of the 64 key columns this warp handles
     const int r = q * 32 + lane;
     const int qidx = m0 + r;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
@@ -187,18 +196,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       if (!bw_wait(&sp_full[j & 1], (j >> 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_BWD, 5, j); ok = false; break; }
       tc_fence_after();
       const int kv0 = j * DQ_BN;
-      uint32_t pk[16];
+      uint32_t pk[BWD_COLS / 2];
       {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tS + lane_off + (j & 1) * 64 + half * 32, sv);
-        tmem_ld_32x32b_x32(tdP + lane_off + (j & 1) * 64 + half * 32, dv);
+        uint32_t sv[BWD_COLS], dv[BWD_COLS];
+        tmem_ld_cols<BWD_COLS>(tS + lane_off + (j & 1) * 64 + part * BWD_COLS, sv);
+        tmem_ld_cols<BWD_COLS>(tdP + lane_off + (j & 1) * 64 + part * BWD_COLS, dv);
         tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
+        for (int c = 0; c < BWD_COLS / 2; c++) {
           float ds[2];
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const int col = 2 * c + e, kv = kv0 + half * 32 + col;
+            const int col = 2 * c + e, kv = kv0 + part * BWD_COLS + col;
             float p = exp2f(__uint_as_float(sv[col]) * scale_log2 - lse2);
             if ((causal && kv > qidx) || kv >= S) p = 0.f;
             ds[e] = p * (__uint_as_float(dv[col]) - dlt) * scale;
@@ -212,8 +221,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
       }
       uint8_t* row = sdS + r * 128;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; c4++)
-        *reinterpret_cast<uint4*>(row + (((half * 4 + c4) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+      for (int c4 = 0; c4 < BWD_COLS / 8; c4++)
+        *reinterpret_cast<uint4*>(row + (((part * (BWD_COLS / 8) + c4) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -222,7 +231,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
     if (ok) {
       tc_fence_after();
 #pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; c++) {
+      for (int c = part * (4 / BWD_PARTS); c < (part + 1) * (4 / BWD_PARTS); c++) {   // 128 output columns = 4 chunks of 32
         uint32_t ov[32];
         tmem_ld_32x32b_x32(tdQ + lane_off + c * 32, ov);
         tmem_ld_wait();
@@ -240,7 +249,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ,    // qkv, box {64,
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(BWD_ARITH) : "memory");
       if (threadIdx.x == 64) {
         tma_store_3d(&tmdQ, sQ, h * BD, m0, b);
         tma_store_3d(&tmdQ, sQ + 16384, h * BD + 64, m0, b);
@@ -302,7 +311,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
     mbar_init(kv_full, 1);
     for (int i = 0; i < DKV_ST; i++) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     for (int i = 0; i < 2; i++) mbar_init(&st_full[i], 1);
-    mbar_init(pds_ready, 256);
+    mbar_init(pds_ready, BWD_ARITH);
     mbar_init(dkv_done, 1);
     mbar_fence_init();
   }
@@ -383,10 +392,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
     }
   } else {
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;            // which 32 of the 64 query columns this warp handles
+    const int part = (warp - 2) >> 2;            // which BWD_COLS of the 64 query columns this warp handles
     const int r = q * 32 + lane;                 // key row inside the block
     const int kvidx = kv0 + r;
-    const int tid = threadIdx.x - 64;            // 0..255 among the arithmetic threads
+    const int tid = threadIdx.x - 64;            // index among the arithmetic threads
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const bool kvalid = kvidx < S;
     bool ok = true;
@@ -400,29 +409,37 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
     if (tid < 128 && n_it > 0) sStat[tid] = fetch_stat(0);
     for (int it = 0; it < n_it && ok; it++) {
       const int q0 = (i_start + it % nqi) * DKV_BM;
-      asm volatile("bar.sync 1, 256;" ::: "memory");    // publishes sStat[it&1]; everyone has finished reading sStat[(it+1)&1]
+      asm volatile("bar.sync 1, %0;" ::"n"(BWD_ARITH) : "memory");    // publishes sStat[it&1]; everyone has finished reading sStat[(it+1)&1]
       float next_stat = 0.f;
       if (tid < 128 && it + 1 < n_it) next_stat = fetch_stat(it + 1);
       const float* st_lse = sStat + (it & 1) * 128;
       const float* st_dlt = st_lse + 64;
       if (!bw_wait(&st_full[it & 1], (it >> 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_BWD, 15, it); ok = false; break; }
       tc_fence_after();
-      uint32_t ppk[16], dpk[16];
+      uint32_t ppk[BWD_COLS / 2], dpk[BWD_COLS / 2];
       {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tSt + lane_off + (it & 1) * 64 + half * 32, sv);
-        tmem_ld_32x32b_x32(tdPt + lane_off + (it & 1) * 64 + half * 32, dv);
+        uint32_t sv[BWD_COLS], dv[BWD_COLS];
+        tmem_ld_cols<BWD_COLS>(tSt + lane_off + (it & 1) * 64 + part * BWD_COLS, sv);
+        tmem_ld_cols<BWD_COLS>(tdPt + lane_off + (it & 1) * 64 + part * BWD_COLS, dv);
+        float sl[BWD_COLS], sd[BWD_COLS];
+#pragma unroll
+        for (int c4 = 0; c4 < BWD_COLS / 4; c4++) {
+          const float4 a = reinterpret_cast<const float4*>(st_lse + part * BWD_COLS)[c4];
+          const float4 d = reinterpret_cast<const float4*>(st_dlt + part * BWD_COLS)[c4];
+          sl[4 * c4] = a.x; sl[4 * c4 + 1] = a.y; sl[4 * c4 + 2] = a.z; sl[4 * c4 + 3] = a.w;
+          sd[4 * c4] = d.x; sd[4 * c4 + 1] = d.y; sd[4 * c4 + 2] = d.z; sd[4 * c4 + 3] = d.w;
+        }
         tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
+        for (int c = 0; c < BWD_COLS / 2; c++) {
           float pp[2], ds[2];
 #pragma unroll
           for (int e = 0; e < 2; e++) {
-            const int col = half * 32 + 2 * c + e, qi = q0 + col;
-            float p = exp2f(__uint_as_float(sv[2 * c + e]) * scale_log2 - st_lse[col]);
+            const int cc = 2 * c + e, qi = q0 + part * BWD_COLS + cc;
+            float p = exp2f(__uint_as_float(sv[cc]) * scale_log2 - sl[cc]);
             if ((causal && kvidx > qi) || !kvalid) p = 0.f;
             pp[e] = p;
-            ds[e] = p * (__uint_as_float(dv[2 * c + e]) - st_dlt[col]) * scale;
+            ds[e] = p * (__uint_as_float(dv[cc]) - sd[cc]) * scale;
           }
           __nv_bfloat162 hp = __floats2bfloat162_rn(pp[0], pp[1]), hd = __floats2bfloat162_rn(ds[0], ds[1]);
           ppk[c] = *reinterpret_cast<uint32_t*>(&hp);
@@ -435,8 +452,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
       uint8_t* prow = sPt + r * 128;
       uint8_t* drow = sdSt + r * 128;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; c4++) {
-        const int sw = ((half * 4 + c4) ^ (r & 7)) << 4;
+      for (int c4 = 0; c4 < BWD_COLS / 8; c4++) {
+        const int sw = ((part * (BWD_COLS / 8) + c4) ^ (r & 7)) << 4;
         *reinterpret_cast<uint4*>(prow + sw) = make_uint4(ppk[4 * c4], ppk[4 * c4 + 1], ppk[4 * c4 + 2], ppk[4 * c4 + 3]);
         *reinterpret_cast<uint4*>(drow + sw) = make_uint4(dpk[4 * c4], dpk[4 * c4 + 1], dpk[4 * c4 + 2], dpk[4 * c4 + 3]);
       }
@@ -454,7 +471,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         const uint32_t tsrc = which == 0 ? tdV : tdK;
         uint8_t* sdst = which == 0 ? sV : sK;
 #pragma unroll 1
-        for (int c = half * 2; c < half * 2 + 2; c++) {
+        for (int c = part * (4 / BWD_PARTS); c < (part + 1) * (4 / BWD_PARTS); c++) {   // 128 output columns = 4 chunks of 32
           uint32_t ov[32];
           tmem_ld_32x32b_x32(tsrc + lane_off + c * 32, ov);
           tmem_ld_wait();
@@ -473,7 +490,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmKV128,  // qkv, box {
         }
       }
       fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(BWD_ARITH) : "memory");
       if (threadIdx.x == 64) {
         tma_store_3d(&tmdKV, sV, vcol, kv0, b);
         tma_store_3d(&tmdKV, sV + 16384, vcol + 64, kv0, b);

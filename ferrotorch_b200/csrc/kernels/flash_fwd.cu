@@ -174,20 +174,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_wait();
       const int kv0 = j * FA_BN;
       const bool need_mask = (causal && kv0 + FA_BN - 1 > m0) || (kv0 + FA_BN > S);
-      float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < 64; c++) {
           const int kv = kv0 + c;
-          float v = __uint_as_float(sv[c]);
-          if ((causal && kv > qidx) || kv >= S) v = -INFINITY;
-          sv[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          if ((causal && kv > qidx) || kv >= S) sv[c] = __float_as_uint(-INFINITY);
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains instead of one of length 64
+#pragma unroll
+      for (int c = 0; c < 64; c++) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float m_new = fmaxf(m_used, mx);
       if (m_new == -INFINITY) m_new = 0.f;
       const bool grow = (m_new - m_used) * scale_log2 > 8.f;     // also true on the first block (m_used = -inf)
@@ -198,17 +195,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float moff = m_used * scale_log2;
-      float rowsum = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 32; c++) {
         const float p0 = exp2f(__uint_as_float(sv[2 * c]) * scale_log2 - moff);
         const float p1 = exp2f(__uint_as_float(sv[2 * c + 1]) * scale_log2 - moff);
-        rowsum += p0 + p1;
+        rs4[c & 3] += p0 + p1;
         __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
         pk[c] = *reinterpret_cast<uint32_t*>(&hh);
       }
-      l = l * alpha + rowsum;
+      l = l * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
       if (j > 0) {
         if (!fa_wait(pv_done, (j - 1) & 1)) { if (lane == 0) ft_set_status(status, FT_K_FA_FWD, 7, j); ok = false; break; }
         tc_fence_after();

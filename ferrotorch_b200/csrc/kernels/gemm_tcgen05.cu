@@ -31,7 +31,11 @@ constexpr int EPI_WARPS = 4;
 constexpr int EPI_BUF_BYTES = 32 * 128;      // 32 rows x 128 B per warp per buffer
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * 2 * EPI_BUF_BYTES + 256 + 1024;
+// One staging buffer per epilogue warp (not two): the CTA then leaves ~18 KiB of the SM's shared memory unclaimed, which is what lets
+// CTAs of bandwidth-bound kernels from other streams (the optimizer, the collectives) become resident beside the GEMM instead of
+// queueing behind it.
+constexpr int EPI_BUFS = 1;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES + 256 + 1024;
 
 // Tile order: groups of RASTER_GM tile-rows, walked row-fastest inside a group, so the ~148 tiles in flight
 // cover a near-square patch of the output (16 x ~9 tiles) and both operands are re-used out of L2.
@@ -64,7 +68,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* sA = smem;
   uint8_t* sB = sA + STAGES * A_STAGE_BYTES;
   uint8_t* sEpi = sB + STAGES * B_STAGE_BYTES;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sEpi + EPI_WARPS * 2 * EPI_BUF_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sEpi + EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -161,7 +165,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;                      // TMEM lane quarter this warp may access
     const int ew = warp - 2;                     // staging slot
-    uint8_t* my_buf = sEpi + ew * 2 * EPI_BUF_BYTES;
+    uint8_t* my_buf = sEpi + ew * EPI_BUFS * EPI_BUF_BYTES;
     constexpr int EPI_COLS = OUT_F32 ? 32 : 64;
     constexpr int CHUNKS = BN / EPI_COLS;
     uint32_t acc = 0, acc_phase = 0;
@@ -175,12 +179,12 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < CHUNKS; c++) {
-        uint8_t* buf = my_buf + (nstore & 1) * EPI_BUF_BYTES;
+        uint8_t* buf = my_buf + (nstore % EPI_BUFS) * EPI_BUF_BYTES;
         uint32_t v[OUT_F32 ? 32 : 64];
         tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
         if constexpr (!OUT_F32) tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
-        // the buffer used two stores ago must have been read out by the TMA engine
-        if (lane == 0) tma_store_wait_read<1>();
+        // the previous store from this buffer must have been read out by the TMA engine
+        if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
         __syncwarp();
         tmem_ld_wait();
         const int col0 = n0 + c * EPI_COLS;

@@ -270,12 +270,16 @@ FT_EXPORT int ft_loss_mean(const float* loss_rows, const int64_t* targets, int r
 }
 
 // grad_dtype: 0 = bf16, 1 = f32. p_bf16 may be null. step >= 1.
+// max_ctas > 0 caps the grid: a small grid (two CTAs per SM) keeps the kernel's register/thread footprint low enough that a
+// persistent GEMM launched on another stream can always become resident beside it, which is what lets the optimizer run
+// concurrently with backward instead of delaying it.
 FT_EXPORT int ft_adamw_flat(float* master, void* p_bf16, float* m, float* v, const void* grad, int64_t n, int grad_dtype, float lr,
                             float beta1, float beta2, float eps, float weight_decay, int step, int maximize,
-                            const float* grad_scale_ptr, const int* skip_ptr, cudaStream_t st) {
+                            const float* grad_scale_ptr, const int* skip_ptr, int max_ctas, cudaStream_t st) {
   if (n <= 0 || step < 1) return FT_ERR_ARG;
   AdamWArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), maximize};
   int grid = flat_grid(((size_t)n + 3) / 4, 256);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grad_dtype == 0)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, (__nv_bfloat16*)p_bf16, m, v, (const __nv_bfloat16*)grad, (size_t)n, a,
                                                       grad_scale_ptr, skip_ptr);

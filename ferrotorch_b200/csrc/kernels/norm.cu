@@ -136,15 +136,24 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// dw[c] (+)= sum_p partial[p][c]; fixed summation order => bit-stable run to run.
+// dw[c] (+)= sum_p partial[p][c]. A CTA of 32x8 threads owns 32 columns; the 8 thread rows each add every 8th partial row and
+// are then combined in a fixed order, so the result is bit-stable run to run.
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw_bf16,
                                        float* __restrict__ dw_f32, int nparts, int d, int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x, ry = threadIdx.y;
   float s = 0.f;
-  for (int p = 0; p < nparts; p++) s += partial[(size_t)p * d + c];
-  if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
-  if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
+  if (c < d)
+    for (int p = ry; p < nparts; p += 8) s += partial[(size_t)p * d + c];
+  sm[ry][threadIdx.x] = s;
+  __syncthreads();
+  if (ry == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) t += sm[i][threadIdx.x];
+    if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + t : t;
+    if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + t : t);
+  }
 }
 
 // LayerNorm forward: y = (x-mean)*rstd*w + b
@@ -286,7 +295,7 @@ FT_EXPORT int ft_rmsnorm_bwd(const void* x, const void* w, const void* dy, const
   else
     FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
                                                    nullptr, (__nv_bfloat16*)dx, dw_partial, rows, d));
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
+  colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();
 }
 
@@ -306,8 +315,8 @@ FT_EXPORT int ft_layernorm_bwd(const void* x, const void* w, const void* dy, con
   int grid = ft_norm_bwd_parts(rows);
   FT_VPT_DISPATCH(d, layernorm_bwd_kernel<V><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, mean, rstd,
                                             (__nv_bfloat16*)dx, dw_partial, db_partial, rows, d));
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, nullptr, grid, d, 0);
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(db_partial, (__nv_bfloat16*)db_bf16, nullptr, grid, d, 0);
+  colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, nullptr, grid, d, 0);
+  colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(db_partial, (__nv_bfloat16*)db_bf16, nullptr, grid, d, 0);
   return (int)cudaGetLastError();
 }
 
@@ -368,6 +377,6 @@ FT_EXPORT int ft_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* d
   else
     FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
                                                                        rstd, nullptr, (__nv_bfloat16*)dx, scratch, rows, d));
-  colsum_partials_kernel<<<(d + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
+  colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(scratch, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();
 }

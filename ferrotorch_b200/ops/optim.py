@@ -14,11 +14,11 @@ from ._workspace import workspace
 
 def adamw_flat_(master: torch.Tensor, p_bf16: torch.Tensor | None, m: torch.Tensor, v: torch.Tensor, grad: torch.Tensor, *, lr: float,
                 beta1: float, beta2: float, eps: float, weight_decay: float, step: int, maximize: bool = False,
-                grad_scale: torch.Tensor | None = None, skip: torch.Tensor | None = None) -> None:
+                grad_scale: torch.Tensor | None = None, skip: torch.Tensor | None = None, max_ctas: int = 0) -> None:
     n = master.numel()
     if master.is_cuda:
         _lib.call("ft_adamw_flat", master, p_bf16, m, v, grad, n, int(grad.dtype == torch.float32), lr, beta1, beta2, eps,
-                  weight_decay, step, int(maximize), grad_scale, skip, _lib.S())
+                  weight_decay, step, int(maximize), grad_scale, skip, max_ctas, _lib.S())
         return
     g = grad.float()
     if grad_scale is not None:

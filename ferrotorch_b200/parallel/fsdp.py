@@ -96,7 +96,11 @@ class FSDP:
         self.comm = comm or os.environ.get("FT_FSDP_COMM", "fused")
         self.step_count = 0
         cuda = self.device.type == "cuda"
-        self.side = torch.cuda.Stream(device=self.device, priority=0) if (cuda and overlap_optimizer) else None
+        if os.environ.get("FT_NO_SIDE_STREAM") == "1":
+            overlap_optimizer = False
+        self._opt_ctas = int(os.environ.get("FT_OPT_CTAS", "296")) if (cuda and overlap_optimizer) else 0   # two CTAs per SM beside the GEMM
+        self._debug_skip_opt = os.environ.get("FT_DEBUG_SKIP_OPT") == "1"      # diagnosis only: measures the step without any update
+        self.side = torch.cuda.Stream(device=self.device, priority=-1) if (cuda and overlap_optimizer) else None
         # gradient buffers: a small rotating pool of full-size bf16 buffers, sized for the largest unit
         maxn = max(u.padded for u in self.units)
         self._grad_pool = [torch.empty(maxn, device=self.device, dtype=torch.bfloat16) for _ in range(max(grad_buffers, 1))]
@@ -167,9 +171,12 @@ class FSDP:
             import contextlib
             ctx = contextlib.nullcontext()
         with ctx:
-            if self.world == 1:
+            if self._debug_skip_opt:
+                pass
+            elif self.world == 1:
                 ops.adamw_flat_(unit.master, unit.full, unit.exp_avg, unit.exp_avg_sq, unit.grad, lr=o.lr, beta1=o.betas[0],
-                                beta2=o.betas[1], eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize)
+                                beta2=o.betas[1], eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize,
+                                max_ctas=self._opt_ctas)
             elif self._fused is not None:
                 self._fused.step(unit, slot)
             else:
@@ -177,7 +184,7 @@ class FSDP:
                 self.dist.reduce_scatter_tensor(gs, unit.grad, op=self.dist.ReduceOp.AVG, group=self.pg)
                 mine = unit.shard_slice(unit.full)
                 ops.adamw_flat_(unit.master, mine, unit.exp_avg, unit.exp_avg_sq, gs, lr=o.lr, beta1=o.betas[0], beta2=o.betas[1],
-                                eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize)
+                                eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize, max_ctas=self._opt_ctas)
                 self.dist.all_gather_into_tensor(unit.full, mine, group=self.pg)
             if self.side is not None:
                 ev = torch.cuda.Event()
