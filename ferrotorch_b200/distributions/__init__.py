@@ -1,0 +1,28 @@
+"""Probability distributions, KL registry, transforms and constraints (API names follow ferrotorch-distributions).
+
+The 27 distribution families, ``kl_divergence`` with its pairwise registry, bijective transforms and support constraints carry
+PyTorch's reference semantics (``sample`` / ``rsample`` / ``log_prob`` / ``entropy``); sampling on CUDA tensors uses the
+device Philox stream.
+
+Reference parity: ferrotorch-distributions/src/lib.rs:138 (Distribution trait), kl.rs:66, transforms.rs, constraints.rs and one
+file per family.
+"""
+from torch import distributions as _d
+from torch.distributions import constraints, transforms, kl
+from torch.distributions.kl import kl_divergence, register_kl
+
+Distribution = _d.Distribution
+Bernoulli, Beta, Categorical, Cauchy, Dirichlet, Exponential, Gamma, Gumbel = (_d.Bernoulli, _d.Beta, _d.Categorical, _d.Cauchy, _d.Dirichlet,
+                                                                               _d.Exponential, _d.Gamma, _d.Gumbel)
+HalfNormal, Independent, Kumaraswamy, Laplace, LogNormal = _d.HalfNormal, _d.Independent, _d.Kumaraswamy, _d.Laplace, _d.LogNormal
+LowRankMultivariateNormal, MixtureSameFamily, Multinomial, MultivariateNormal, Normal = (_d.LowRankMultivariateNormal, _d.MixtureSameFamily,
+                                                                                         _d.Multinomial, _d.MultivariateNormal, _d.Normal)
+OneHotCategorical, Pareto, Poisson, RelaxedBernoulli, RelaxedOneHotCategorical = (_d.OneHotCategorical, _d.Pareto, _d.Poisson,
+                                                                                  _d.RelaxedBernoulli, _d.RelaxedOneHotCategorical)
+StudentT, Uniform, VonMises, Weibull = _d.StudentT, _d.Uniform, _d.VonMises, _d.Weibull
+TransformedDistribution = _d.TransformedDistribution
+AffineTransform, ExpTransform, SigmoidTransform, TanhTransform, ComposeTransform, SoftmaxTransform, StickBreakingTransform = (
+    transforms.AffineTransform, transforms.ExpTransform, transforms.SigmoidTransform, transforms.TanhTransform, transforms.ComposeTransform,
+    transforms.SoftmaxTransform, transforms.StickBreakingTransform)
+
+__all__ = [n for n in dir() if not n.startswith("_")]
