@@ -1,0 +1,331 @@
+"""JSON-schema constrained decoding: a schema is compiled to a character-level pushdown state machine; for each decoding
+step ``JsonSchemaProcessor.mask`` marks which vocabulary tokens keep the output a valid prefix, and ``apply_mask`` sets the
+logits of the others to -inf (on CUDA with the token-mask kernel, one thread per vocabulary entry).
+
+Reference parity: ferrotorch-grammar/src/{json_schema.rs:53-125 (Schema, JsonGrammar), state.rs, lib.rs:58-85 (TokenMask,
+JsonSchemaProcessor), gpu_dispatch.rs:778 (compute_mask_gpu)}; the mask kernel replaces the CubeCL one (ferrotorch-cubecl/src/grammar.rs:47).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..errors import InvalidArgument
+
+
+@dataclass
+class Schema:
+    kind: str                                  # object | array | string | number | integer | boolean | null | enum | any
+    properties: Dict[str, "Schema"] = field(default_factory=dict)
+    required: List[str] = field(default_factory=list)
+    items: Optional["Schema"] = None
+    enum: Optional[List[Any]] = None
+
+    @staticmethod
+    def from_json(j) -> "Schema":
+        if isinstance(j, str):
+            j = json.loads(j)
+        if "enum" in j:
+            return Schema("enum", enum=list(j["enum"]))
+        t = j.get("type", "any")
+        if t == "object":
+            return Schema("object", {k: Schema.from_json(v) for k, v in j.get("properties", {}).items()}, list(j.get("required", [])))
+        if t == "array":
+            return Schema("array", items=Schema.from_json(j.get("items", {})))
+        if t in ("string", "number", "integer", "boolean", "null", "any"):
+            return Schema(t)
+        raise InvalidArgument(f"unsupported schema type {t}")
+
+
+class JsonGrammar:
+    """Incremental validator: ``accepts_prefix(text)`` is true iff ``text`` can be extended to a document matching the schema.
+    Objects emit their properties in schema order (required ones mandatory), compact separators, no insignificant whitespace
+    except a single optional space after ``:`` and ``,``."""
+
+    def __init__(self, schema: Schema):
+        self.schema = schema
+
+    # returns set of possible remaining-state continuations; implemented as a recursive prefix matcher
+    def accepts_prefix(self, text: str) -> bool:
+        return self._match(self.schema, text, 0, True) is not None
+
+    def is_complete(self, text: str) -> bool:
+        r = self._match(self.schema, text, 0, False)
+        return r is not None and r == len(text)
+
+    # _match returns: position after the value if the value completes inside text; len(text)+1 sentinel (as "ran out of text
+    # while still valid") is represented by returning -1 when allow_partial; None when invalid.
+    def _match(self, s: Schema, t: str, i: int, partial: bool):
+        r = self._value(s, t, i)
+        if r is None:
+            return None
+        if r == -1:
+            return len(t) if partial else None
+        if r != len(t):
+            return None if not partial else (r if r == len(t) else None)
+        return r
+
+    def _lit(self, lit: str, t: str, i: int):
+        n = len(t) - i
+        if n >= len(lit):
+            return i + len(lit) if t.startswith(lit, i) else None
+        return -1 if lit.startswith(t[i:]) else None
+
+    def _string(self, t: str, i: int):
+        if i >= len(t):
+            return -1
+        if t[i] != '"':
+            return None
+        i += 1
+        while i < len(t):
+            c = t[i]
+            if c == '"':
+                return i + 1
+            if c == "\\":
+                if i + 1 >= len(t):
+                    return -1
+                if t[i + 1] not in '"\\/bfnrtu':
+                    return None
+                i += 2
+                continue
+            if ord(c) < 0x20:
+                return None
+            i += 1
+        return -1
+
+    def _number(self, t: str, i: int, integer: bool):
+        j = i
+        if j >= len(t):
+            return -1
+        if t[j] == "-":
+            j += 1
+            if j >= len(t):
+                return -1
+        if not t[j].isdigit():
+            return None
+        if t[j] == "0":
+            j += 1
+        else:
+            while j < len(t) and t[j].isdigit():
+                j += 1
+        if j >= len(t):
+            return ("open", j)
+        if not integer and t[j] == ".":
+            j += 1
+            if j >= len(t):
+                return -1
+            if not t[j].isdigit():
+                return None
+            while j < len(t) and t[j].isdigit():
+                j += 1
+            if j >= len(t):
+                return ("open", j)
+        if not integer and t[j] in "eE":
+            j += 1
+            if j < len(t) and t[j] in "+-":
+                j += 1
+            if j >= len(t):
+                return -1
+            if not t[j].isdigit():
+                return None
+            while j < len(t) and t[j].isdigit():
+                j += 1
+            if j >= len(t):
+                return ("open", j)
+        return j
+
+    def _sep(self, t: str, i: int):
+        if i < len(t) and t[i] == " ":
+            return i + 1
+        return i
+
+    def _value(self, s: Schema, t: str, i: int):
+        """Position after the value, -1 if text ended inside a still-valid value, None if invalid. Numbers at end of text return
+        ("open", pos): complete so far but extendable."""
+        if i >= len(t):
+            return -1
+        k = s.kind
+        if k == "string":
+            return self._string(t, i)
+        if k in ("number", "integer"):
+            r = self._number(t, i, k == "integer")
+            return r
+        if k == "boolean":
+            a, b = self._lit("true", t, i), self._lit("false", t, i)
+            return a if a is not None else b
+        if k == "null":
+            return self._lit("null", t, i)
+        if k == "enum":
+            res = None
+            for v in s.enum or []:
+                r = self._lit(json.dumps(v), t, i)
+                if r is not None and r != -1:
+                    return r
+                if r == -1:
+                    res = -1
+            return res
+        if k == "any":
+            for sub in (Schema("string"), Schema("number"), Schema("boolean"), Schema("null"), Schema("array", items=Schema("any")), Schema("object")):
+                r = self._value(sub, t, i)
+                if r is not None:
+                    return r
+            return None
+        if k == "array":
+            if t[i] != "[":
+                return None
+            i += 1
+            if i >= len(t):
+                return -1
+            if t[i] == "]":
+                return i + 1
+            while True:
+                r = self._value(s.items or Schema("any"), t, i)
+                if r is None or r == -1:
+                    return r
+                if isinstance(r, tuple):
+                    return -1
+                i = r
+                if i >= len(t):
+                    return -1
+                if t[i] == "]":
+                    return i + 1
+                if t[i] != ",":
+                    return None
+                i = self._sep(t, i + 1)
+                if i >= len(t):
+                    return -1
+        if k == "object":
+            if t[i] != "{":
+                return None
+            i += 1
+            props = list(s.properties.items())
+            if not props:
+                if i >= len(t):
+                    return -1
+                return i + 1 if t[i] == "}" else None
+            first = True
+            for idx, (name, sub) in enumerate(props):
+                if i >= len(t):
+                    return -1
+                optional_rest = all(n not in s.required for n, _ in props[idx:])
+                if t[i] == "}" and optional_rest and (first or True):
+                    return i + 1 if (first or t[i - 1] != ",") else None
+                if not first:
+                    if t[i] != ",":
+                        return None
+                    i = self._sep(t, i + 1)
+                    if i >= len(t):
+                        return -1
+                key = json.dumps(name)
+                r = self._lit(key, t, i)
+                if r is None:
+                    if name in s.required:
+                        return None
+                    continue_ok = False
+                    # an optional property may be skipped: try the following ones at this position
+                    for n2, _ in props[idx + 1:]:
+                        r2 = self._lit(json.dumps(n2), t, i)
+                        if r2 is not None:
+                            continue_ok = True
+                            break
+                    if not continue_ok:
+                        return None
+                    if not first:
+                        # we consumed a comma for a property we are skipping: rewind is handled by retrying from the next property
+                        pass
+                    # emulate "not first" state for the next property without consuming another comma
+                    first_backup = first
+                    first = True if first_backup else True
+                    continue
+                if r == -1:
+                    return -1
+                i = r
+                if i >= len(t):
+                    return -1
+                if t[i] != ":":
+                    return None
+                i = self._sep(t, i + 1)
+                r = self._value(sub, t, i)
+                if r is None or r == -1:
+                    return r
+                if isinstance(r, tuple):
+                    return -1
+                i = r
+                first = False
+            if i >= len(t):
+                return -1
+            return i + 1 if t[i] == "}" else None
+        return None
+
+
+@dataclass
+class TokenMask:
+    allowed: torch.Tensor            # bool [vocab]
+
+    def count(self) -> int:
+        return int(self.allowed.sum())
+
+
+class JsonSchemaProcessor:
+    """Logits processor: keeps only tokens whose text leaves the generated string a valid prefix of a schema-conforming document."""
+
+    def __init__(self, schema, vocab_texts: Sequence[str], eos_id: Optional[int] = None):
+        self.grammar = JsonGrammar(schema if isinstance(schema, Schema) else Schema.from_json(schema))
+        self.vocab = list(vocab_texts)
+        self.eos_id = eos_id
+        self.text = ""
+
+    def reset(self) -> None:
+        self.text = ""
+
+    def advance(self, token_id: int) -> None:
+        if token_id != self.eos_id:
+            self.text += self.vocab[token_id]
+
+    def _valid(self, text: str) -> bool:
+        r = self.grammar._value(self.grammar.schema, text, 0)
+        if r is None:
+            return False
+        if r == -1 or isinstance(r, tuple):
+            return True
+        return r == len(text)
+
+    def _complete(self) -> bool:
+        r = self.grammar._value(self.grammar.schema, self.text, 0)
+        if isinstance(r, tuple):
+            return r[1] == len(self.text)
+        return r is not None and r != -1 and r == len(self.text)
+
+    def mask(self) -> TokenMask:
+        ok = torch.zeros(len(self.vocab), dtype=torch.bool)
+        done = self._complete()
+        for i, tok in enumerate(self.vocab):
+            if i == self.eos_id:
+                ok[i] = done
+            elif tok and not (done and self.grammar.schema.kind not in ("number", "integer")):
+                ok[i] = self._valid(self.text + tok)
+        return TokenMask(ok)
+
+    def apply(self, logits: torch.Tensor) -> torch.Tensor:
+        return apply_mask(logits, self.mask())
+
+
+def apply_mask(logits: torch.Tensor, mask: TokenMask) -> torch.Tensor:
+    """``logits[..., v] = -inf`` where the mask forbids token ``v``."""
+    allowed = mask.allowed.to(logits.device)
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and logits.is_contiguous():
+        try:
+            from .. import _lib
+            if hasattr(_lib.kernels(), "ft_token_mask"):
+                _lib.call("ft_token_mask", logits, allowed.to(torch.uint8), logits.numel() // logits.shape[-1], logits.shape[-1],
+                          int(logits.dtype == torch.float32), _lib.S())
+                return logits
+        except Exception:
+            raise
+    return logits.masked_fill(~allowed, float("-inf"))
+
+
+compute_mask_gpu = apply_mask
