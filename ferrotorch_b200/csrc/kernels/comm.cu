@@ -38,6 +38,8 @@ struct CommSync {
   uint32_t* counter;            // local device memory, u32[2], zero between launches
   int rank, world;
   uint32_t seq;                 // sequence number of this launch (same on every rank)
+  uint32_t* seq_dev;            // optional: the sequence lives in device memory (seq = *seq_dev + 1, written back by the last CTA), so a
+                                // launch captured in a CUDA graph advances it on every replay
 };
 
 // One thread per peer: tell every peer that this rank reached `phase` of launch `seq`.
@@ -55,7 +57,8 @@ FT_DEVICE bool wait_peers(const CommSync& s, int phase, uint32_t* status, int si
 }
 
 // Start-of-kernel rendezvous: CTA 0 signals; every CTA waits on the local flags. Returns false if any peer is missing.
-FT_DEVICE bool comm_begin(const CommSync& s, uint32_t* status) {
+FT_DEVICE bool comm_begin(CommSync& s, uint32_t* status) {
+  if (s.seq_dev) s.seq = *reinterpret_cast<volatile uint32_t*>(s.seq_dev) + 1;   // read before any CTA can reach comm_end's write-back
   __shared__ int ok_sh;
   if (threadIdx.x == 0) ok_sh = 1;
   __syncthreads();
@@ -82,6 +85,7 @@ FT_DEVICE void comm_end(const CommSync& s, uint32_t* status) {
   __threadfence_system();
   signal_peers(s, 1);
   wait_peers(s, 1, status, 2);
+  if (s.seq_dev && threadIdx.x == 0) *s.seq_dev = s.seq;
 }
 
 template <typename T> struct Vec16;
@@ -304,6 +308,7 @@ int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, 
   s.rank = rank;
   s.world = world;
   s.seq = seq;
+  s.seq_dev = nullptr;
   return FT_OK;
 }
 
@@ -335,11 +340,14 @@ FT_EXPORT int ft_comm_allreduce(void* const* buf_ptrs, void* const* flag_ptrs, u
   return (int)cudaGetLastError();
 }
 
+// seq_dev (optional, device u32): when non-null the launch takes its sequence number from device memory and advances it, which makes
+// the launch replayable from a CUDA graph; `seq` is then ignored. All ranks must use the same mode for a given flag block.
 FT_EXPORT int ft_comm_allreduce_1shot(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
-                                      uint32_t seq, int64_t n, int dtype, float scale, int max_ctas, cudaStream_t st) {
+                                      uint32_t seq, int64_t n, int dtype, float scale, int max_ctas, uint32_t* seq_dev, cudaStream_t st) {
   CommSync s;
   int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
   if (r) return r;
+  s.seq_dev = seq_dev;
   if (n <= 0) return FT_ERR_ARG;
   PeerPtrs b;
   for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;

@@ -1,0 +1,366 @@
+// Decode-path kernels for tensor-parallel LLM serving (small token batch, paged KV cache, block size 16).
+//
+// The projections run as split-K GEMMs (ft_gemm_bf16_splitk) that leave f32 partial planes P[s][token][n]; each kernel
+// here consumes those planes directly, summing over s on the fly, so no stand-alone reduction pass exists:
+//   ft_decode_qkv_rope_kvwrite   sum -> RoPE at each sequence's position -> q [B,Hq,D] bf16 and K/V written into their cache pages
+//   ft_paged_attn_decode         one query token per sequence against the paged cache, GQA, split over the sequence; the last
+//                                CTA of each (sequence, kv head) merges the splits (self-resetting counters, no extra launch)
+//   ft_decode_swiglu             sum -> silu(gate)*up -> bf16
+//   ft_decode_ar_residual_norm   row-parallel output: sum of planes -> one-shot all-reduce over NVLink peer memory (fixed rank
+//                                order) -> + residual -> RMSNorm, in one kernel (the 128 KB-class all-reduce of TP decoding)
+//   ft_splitk_reduce             generic plane sum (+bias) to bf16 or f32 (LM head logits)
+//   ft_paged_kv_write            copy prefill K/V rows from the packed QKV buffer into cache pages
+// Launch sequence numbers for the cross-GPU flags are read from device memory and advanced by the kernel itself, so the
+// whole decode step can be captured once in a CUDA graph and replayed.
+//
+// Capability parity: KVPage/PagePool/PagedKVCache bookkeeping exists only on the CPU in the reference
+// (ferrotorch-nn/src/paged_attention.rs:59-518); its GPU inferencer has no KV cache and re-prefills every token
+// (ferrotorch-llama/examples/llama3_8b_gpu.rs:118-122, ferrotorch-llama/src/gpu.rs:518-700).
+#include "common.cuh"
+#include "host_common.h"
+
+namespace {
+
+constexpr int KV_BLOCK = 16;
+constexpr int MAXR = 8;
+constexpr uint64_t DEC_TIMEOUT_NS = 2000000000ull;
+
+FT_DEVICE float plane_sum(const float* __restrict__ p, int splits, size_t plane_stride, size_t idx) {
+  float a = 0.f;
+  for (int s = 0; s < splits; s++) a += p[s * plane_stride + idx];
+  return a;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// generic plane sum
+// ------------------------------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int rows, int N, int64_t ldp, size_t plane_stride,
+                                     const __nv_bfloat16* __restrict__ bias, OutT* __restrict__ out, int64_t ldo) {
+  const size_t total = (size_t)rows * N;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / N), n = (int)(i % N);
+    float a = plane_sum(partial, splits, plane_stride, (size_t)r * ldp + n);
+    if (bias) a += __bfloat162float(bias[n]);
+    out[(size_t)r * ldo + n] = (OutT)a;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// QKV epilogue: plane sum + RoPE + q store + KV cache write
+// grid (B, Hq + 2*Hkv), block D/2 threads: thread i owns the rotation pair (i, i + D/2)
+// ------------------------------------------------------------------------------------------------------------
+__global__ void qkv_rope_kvwrite_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride, int Hq, int Hkv,
+                                        int D, const int* __restrict__ positions, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
+                                        __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                        const int* __restrict__ block_table, int max_blocks) {
+  const int b = blockIdx.x, h = blockIdx.y, i = threadIdx.x, half = D >> 1;
+  const int pos = positions[b];
+  const size_t base = (size_t)b * ldp + (size_t)h * D;
+  float lo = plane_sum(partial, splits, plane_stride, base + i);
+  float hi = plane_sum(partial, splits, plane_stride, base + i + half);
+  if (h < Hq + Hkv) {   // q and k heads are rotated, v heads are not
+    const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+    const float a = lo * c - hi * s, bb = hi * c + lo * s;
+    lo = a;
+    hi = bb;
+  }
+  if (h < Hq) {
+    __nv_bfloat16* q = q_out + ((size_t)b * Hq + h) * D;
+    q[i] = __float2bfloat16(lo);
+    q[i + half] = __float2bfloat16(hi);
+  } else {
+    const int blk = block_table[(size_t)b * max_blocks + pos / KV_BLOCK];
+    if (blk < 0) return;
+    const bool is_k = h < Hq + Hkv;
+    const int kvh = is_k ? h - Hq : h - Hq - Hkv;
+    __nv_bfloat16* dst = (is_k ? k_cache : v_cache) + (((size_t)blk * KV_BLOCK + pos % KV_BLOCK) * Hkv + kvh) * D;
+    dst[i] = __float2bfloat16(lo);
+    dst[i + half] = __float2bfloat16(hi);
+  }
+}
+
+// prefill: rows of the packed qkv buffer [tokens, ld] (token t of sequence b at row b*S + t) -> cache pages
+__global__ void paged_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, int S, int Hq, int Hkv, int D,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                      const int* __restrict__ block_table, int max_blocks, int pos0) {
+  const int t = blockIdx.x, b = blockIdx.y;
+  const int vec = (Hkv * D) / 8;
+  const int pos = pos0 + t;
+  const int blk = block_table[(size_t)b * max_blocks + pos / KV_BLOCK];
+  if (blk < 0) return;
+  const __nv_bfloat16* row = qkv + ((size_t)b * S + t) * ld;
+  const size_t dst = ((size_t)blk * KV_BLOCK + pos % KV_BLOCK) * Hkv * D;
+  for (int i = threadIdx.x; i < vec; i += blockDim.x) {
+    reinterpret_cast<bf16x8*>(k_cache + dst)[i] = reinterpret_cast<const bf16x8*>(row + (size_t)Hq * D)[i];
+    reinterpret_cast<bf16x8*>(v_cache + dst)[i] = reinterpret_cast<const bf16x8*>(row + (size_t)(Hq + Hkv) * D)[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// paged decode attention (D = 128, group size G = Hq/Hkv <= 8)
+// grid (nsplit, Hkv, B), 128 threads. Workspace per (b, kvh, split): G * (2 + 128) floats. counters: int [B*Hkv], zero.
+// ------------------------------------------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                                                                const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
+                                                                int max_blocks, const int* __restrict__ seq_lens, int Hq, int Hkv, float scale,
+                                                                float* __restrict__ ws, int* __restrict__ counters,
+                                                                __nv_bfloat16* __restrict__ out) {
+  constexpr int D = 128;
+  const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int len = seq_lens[b];
+  const int per = (((len + nsplit - 1) / nsplit) + KV_BLOCK - 1) / KV_BLOCK * KV_BLOCK;   // whole pages per split
+  const int t0 = split * per, t1 = min(len, t0 + per);
+  float qv[G][4], acc[G][4], m[G], l[G];
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(q + ((size_t)b * Hq + kvh * G + g) * D + lane * 4);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    qv[g][0] = a.x * scale; qv[g][1] = a.y * scale; qv[g][2] = c.x * scale; qv[g][3] = c.y * scale;
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+  }
+  for (int t = t0 + warp; t < t1; t += 4) {
+    const int blk = block_table[(size_t)b * max_blocks + t / KV_BLOCK];
+    const size_t off = (((size_t)blk * KV_BLOCK + t % KV_BLOCK) * Hkv + kvh) * D + lane * 4;
+    const uint2 kr = *reinterpret_cast<const uint2*>(k_cache + off), vr = *reinterpret_cast<const uint2*>(v_cache + off);
+    const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
+    const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      float s = qv[g][0] * k0.x + qv[g][1] * k0.y + qv[g][2] * k1.x + qv[g][3] * k1.y;
+      s = warp_sum(s);
+      const float mn = fmaxf(m[g], s);
+      const float a = __expf(m[g] - mn), p = __expf(s - mn);
+      l[g] = l[g] * a + p;
+      acc[g][0] = acc[g][0] * a + p * v0.x; acc[g][1] = acc[g][1] * a + p * v0.y;
+      acc[g][2] = acc[g][2] * a + p * v1.x; acc[g][3] = acc[g][3] * a + p * v1.y;
+      m[g] = mn;
+    }
+  }
+  // merge the four warps of this CTA
+  __shared__ float sm_m[4][G], sm_l[4][G], sm_acc[4][G][D];
+  __shared__ int is_last;
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+#pragma unroll
+    for (int e = 0; e < 4; e++) sm_acc[warp][g][lane * 4 + e] = acc[g][e];
+  }
+  __syncthreads();
+  float* my_ws = ws + (((size_t)b * Hkv + kvh) * nsplit + split) * G * (2 + D);
+  for (int i = threadIdx.x; i < G * D; i += 128) {
+    const int g = i / D, d = i % D;
+    const float mm = fmaxf(fmaxf(sm_m[0][g], sm_m[1][g]), fmaxf(sm_m[2][g], sm_m[3][g]));
+    float a = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float f = (sm_m[w][g] == -INFINITY) ? 0.f : __expf(sm_m[w][g] - mm);
+      a += sm_acc[w][g][d] * f;
+      ll += sm_l[w][g] * f;
+    }
+    my_ws[g * (2 + D) + 2 + d] = a;
+    if (d == 0) { my_ws[g * (2 + D)] = mm; my_ws[g * (2 + D) + 1] = ll; }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(&counters[b * Hkv + kvh], 1);
+    is_last = (prev == nsplit - 1);
+    if (is_last) counters[b * Hkv + kvh] = 0;     // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* base = ws + ((size_t)b * Hkv + kvh) * nsplit * G * (2 + D);
+  for (int i = threadIdx.x; i < G * D; i += 128) {
+    const int g = i / D, d = i % D;
+    float mm = -INFINITY;
+    for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, base[(size_t)s * G * (2 + D) + g * (2 + D)]);
+    float a = 0.f, ll = 0.f;
+    for (int s = 0; s < nsplit; s++) {
+      const float* p = base + (size_t)s * G * (2 + D) + g * (2 + D);
+      const float f = (p[0] == -INFINITY) ? 0.f : __expf(p[0] - mm);
+      a += p[2 + d] * f;
+      ll += p[1] * f;
+    }
+    out[((size_t)b * Hq + kvh * G + g) * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// SwiGLU on split-K planes: P[s][b][0:F] = gate, P[s][b][F:2F] = up
+// ------------------------------------------------------------------------------------------------------------
+__global__ void decode_swiglu_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride, int rows, int F,
+                                     __nv_bfloat16* __restrict__ out) {
+  const size_t total = (size_t)rows * F;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / F), f = (int)(i % F);
+    const float g = plane_sum(partial, splits, plane_stride, (size_t)r * ldp + f);
+    const float u = plane_sum(partial, splits, plane_stride, (size_t)r * ldp + F + f);
+    out[i] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// plane sum -> all-reduce (one shot, peer loads) -> + residual -> RMSNorm
+//   grid = rows * chunks CTAs (all co-resident), 256 threads, each CTA owns `cols = d/chunks` columns of one token row.
+//   sync block (device ints): [0] launch sequence, [1] grid barrier A counter, [2] grid barrier B counter (monotonic).
+//   sym[r] = rank r's staging buffer: 2 slots x rows_pad x d floats (slot = sequence parity).
+//   flags[r] = rank r's flag block: u32[MAXR], flags[r][q] = last sequence number rank q announced.
+// ------------------------------------------------------------------------------------------------------------
+struct ArNormArgs {
+  float* sym[MAXR];
+  uint32_t* flags[MAXR];
+  int rank, world;
+};
+
+FT_DEVICE bool grid_barrier(int* ctr, int target, uint32_t* status, int site) {
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(ctr, 1);
+    uint64_t t0 = globaltimer_ns();
+    while (*reinterpret_cast<volatile int*>(ctr) < target) {
+      if (globaltimer_ns() - t0 > DEC_TIMEOUT_NS) { ft_set_status(status, FT_K_COMM, site, blockIdx.x); ok = false; break; }
+    }
+    __threadfence();
+  }
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) ok_sh = ok;
+  __syncthreads();
+  return ok_sh != 0;
+}
+
+__global__ void __launch_bounds__(256) decode_ar_residual_norm_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride,
+                                                                      ArNormArgs a, int* __restrict__ sync, __nv_bfloat16* __restrict__ x,
+                                                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h,
+                                                                      float* __restrict__ sumsq, int rows, int rows_pad, int d, int chunks, float eps,
+                                                                      uint32_t* status) {
+  __shared__ float red[32];
+  const int row = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+  const int cols = d / chunks, c0 = chunk * cols;
+  const int seq = sync[0] + 1;                       // every CTA reads it before any barrier; CTA 0 advances it at the very end
+  const int nctas = gridDim.x;
+  const size_t slot = (size_t)(seq & 1) * rows_pad * d;
+  // phase A: local plane sum into this rank's staging slot
+  float* mine = a.sym[a.rank] + slot + (size_t)row * d + c0;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) mine[i] = plane_sum(partial, splits, plane_stride, (size_t)row * ldp + c0 + i);
+  if (a.world > 1) {
+    __threadfence_system();
+    if (!grid_barrier(&sync[1], seq * nctas, status, 11)) return;
+    if (blockIdx.x == 0 && threadIdx.x < a.world) st_release_sys(a.flags[threadIdx.x] + a.rank, (uint32_t)seq);
+    bool ok = true;
+    if (threadIdx.x < a.world) {
+      ok = wait_flag_ge(a.flags[a.rank] + threadIdx.x, (uint32_t)seq, DEC_TIMEOUT_NS);
+      if (!ok) ft_set_status(status, FT_K_COMM, 12, threadIdx.x);
+    }
+    if (__syncthreads_or(!ok)) return;
+  }
+  // phase B: cross-rank sum in fixed rank order + residual; row-wide sum of squares
+  float ss = 0.f;
+  __nv_bfloat16* xr = x + (size_t)row * d + c0;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = 0.f;
+    for (int r = 0; r < a.world; r++) v += a.sym[r][slot + (size_t)row * d + c0 + i];
+    v += __bfloat162float(xr[i]);
+    const __nv_bfloat16 vb = __float2bfloat16(v);
+    xr[i] = vb;
+    const float vf = __bfloat162float(vb);
+    ss += vf * vf;
+  }
+  ss = block_sum(ss, red);
+  float* ssq = sumsq + (size_t)(seq & 1) * rows_pad * chunks;
+  if (threadIdx.x == 0) ssq[row * chunks + chunk] = ss;
+  if (!grid_barrier(&sync[2], seq * nctas, status, 13)) return;
+  float tot = 0.f;
+  for (int c = 0; c < chunks; c++) tot += ssq[row * chunks + c];
+  const float rstd = rsqrtf(tot / (float)d + eps);
+  __nv_bfloat16* hr = h + (size_t)row * d + c0;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x)
+    hr[i] = __float2bfloat16(__bfloat162float(xr[i]) * rstd * __bfloat162float(w[c0 + i]));
+  if (blockIdx.x == 0 && threadIdx.x == 0) sync[0] = seq;    // everybody is past barrier B, so nobody still needs the old value
+}
+
+inline int small_grid(size_t work, int block) {
+  size_t g = (work + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > 592 ? 592 : g));
+}
+
+}  // namespace
+
+// out[r][n] = sum_s partial[s][r][n] (+bias[n]); partial planes are rows x ldp floats, plane_stride = elements between planes.
+FT_EXPORT int ft_splitk_reduce(const float* partial, int splits, int rows, int N, int64_t ldp, int64_t plane_stride, const void* bias, void* out,
+                               int64_t ldo, int out_f32, cudaStream_t st) {
+  if (splits < 1 || rows < 1 || N < 1) return FT_ERR_ARG;
+  const int grid = small_grid((size_t)rows * N, 256);
+  if (out_f32) splitk_reduce_kernel<float><<<grid, 256, 0, st>>>(partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (float*)out, ldo);
+  else splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, ldo);
+  return (int)cudaGetLastError();
+}
+
+// positions[b] = index of the token being decoded in sequence b; caches are [num_blocks, 16, Hkv, D] bf16.
+FT_EXPORT int ft_decode_qkv_rope_kvwrite(const float* partial, int splits, int64_t ldp, int64_t plane_stride, int B, int Hq, int Hkv, int D,
+                                         const int* positions, const float* cos_t, const float* sin_t, void* q_out, void* k_cache,
+                                         void* v_cache, const int* block_table, int max_blocks, cudaStream_t st) {
+  if (B < 1 || D % 2 || D / 2 > 1024) return FT_ERR_ARG;
+  qkv_rope_kvwrite_kernel<<<dim3(B, Hq + 2 * Hkv), D / 2, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, Hq, Hkv, D, positions, cos_t, sin_t,
+                                                                  (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                                                  block_table, max_blocks);
+  return (int)cudaGetLastError();
+}
+
+FT_EXPORT int ft_paged_kv_write(const void* qkv, int64_t ld, int B, int S, int Hq, int Hkv, int D, void* k_cache, void* v_cache,
+                                const int* block_table, int max_blocks, int pos0, cudaStream_t st) {
+  if ((Hkv * D) % 8 || (ld % 8)) return FT_ERR_ARG;
+  paged_kv_write_kernel<<<dim3(S, B), 128, 0, st>>>((const __nv_bfloat16*)qkv, ld, S, Hq, Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                                    block_table, max_blocks, pos0);
+  return (int)cudaGetLastError();
+}
+
+// q, out: bf16 [B, Hq, 128]; seq_lens[b] counts the tokens already in the cache (including the one just written).
+// ws: f32 scratch of B * Hkv * nsplit * (Hq/Hkv) * 130 floats; counters: int [B*Hkv], zero before the first call (the kernel re-zeroes them).
+FT_EXPORT int ft_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
+                                   const int* seq_lens, int B, int Hq, int Hkv, int D, float scale, int nsplit, float* ws, int* counters, void* out,
+                                   cudaStream_t st) {
+  if (D != 128 || Hq % Hkv || nsplit < 1 || nsplit > 64) return FT_ERR_ARG;
+  const int G = Hq / Hkv;
+  dim3 grid(nsplit, Hkv, B);
+#define FT_PA(GG)                                                                                                                      \
+  if (G == GG) {                                                                                                                       \
+    paged_attn_decode_kernel<GG><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+                                                       block_table, max_blocks, seq_lens, Hq, Hkv, scale, ws, counters, (__nv_bfloat16*)out); \
+    return (int)cudaGetLastError();                                                                                                    \
+  }
+  FT_PA(1) FT_PA(2) FT_PA(4) FT_PA(8)
+#undef FT_PA
+  return FT_ERR_ARG;
+}
+
+FT_EXPORT int ft_decode_swiglu(const float* partial, int splits, int64_t ldp, int64_t plane_stride, int rows, int F, void* out, cudaStream_t st) {
+  if (rows < 1 || F < 1) return FT_ERR_ARG;
+  decode_swiglu_kernel<<<small_grid((size_t)rows * F, 256), 256, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, rows, F, (__nv_bfloat16*)out);
+  return (int)cudaGetLastError();
+}
+
+// sym_ptrs / flag_ptrs: `world` mappings of every rank's staging buffer (2 * rows_pad * d floats) and flag block (u32[8], zeroed once).
+// sync: int[4] device memory, zeroed once. sumsq: float[2 * rows_pad * chunks]. x: residual stream [rows, d] bf16, updated in place;
+// h: normalised output [rows, d] bf16. d % chunks == 0; rows * chunks CTAs must all be resident (<= number of SMs).
+FT_EXPORT int ft_decode_ar_residual_norm(const float* partial, int splits, int64_t ldp, int64_t plane_stride, void* const* sym_ptrs,
+                                         void* const* flag_ptrs, int rank, int world, int* sync, void* x, const void* w, void* h, float* sumsq,
+                                         int rows, int rows_pad, int d, int chunks, float eps, cudaStream_t st) {
+  if (world < 1 || world > MAXR || rows < 1 || chunks < 1 || d % chunks || rows * chunks > 148) return FT_ERR_ARG;
+  ArNormArgs a;
+  for (int i = 0; i < MAXR; i++) { a.sym[i] = i < world ? (float*)sym_ptrs[i] : nullptr; a.flags[i] = i < world ? (uint32_t*)flag_ptrs[i] : nullptr; }
+  a.rank = rank;
+  a.world = world;
+  decode_ar_residual_norm_kernel<<<rows * chunks, 256, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, a, sync, (__nv_bfloat16*)x,
+                                                              (const __nv_bfloat16*)w, (__nv_bfloat16*)h, sumsq, rows, rows_pad, d, chunks, eps,
+                                                              ft_status_ptr());
+  return (int)cudaGetLastError();
+}

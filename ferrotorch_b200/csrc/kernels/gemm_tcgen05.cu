@@ -62,7 +62,7 @@ template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmD, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-               uint32_t* status) {
+               int k_splits, uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -78,8 +78,12 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + BK - 1) / BK;
+  // A work item is (output tile, K split); split s of a tile accumulates k-blocks [s*kb_per, (s+1)*kb_per) and stores to plane s of D
+  // (D's tensor map is 3-D: [splits, M, N]), so short-and-wide problems (decode: a few token rows against a large weight) still
+  // spread the weight stream over every SM. k_splits == 1 is the ordinary GEMM.
+  const int num_kb_total = (K + BK - 1) / BK;
+  const int kb_per = (num_kb_total + k_splits - 1) / k_splits;
+  const int num_tiles = tiles_m * tiles_n * k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -100,8 +104,9 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m0, n0;
-        tile_coords(tile, tiles_m, tiles_n, m0, n0);
-        for (int kb = 0; kb < num_kb; kb++) {
+        tile_coords(tile / k_splits, tiles_m, tiles_n, m0, n0);
+        const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait_deadline(&empty_bar[s], phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 1, s); ok = false; break; }
           mbar_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
@@ -136,7 +141,14 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait_deadline(&tempty_bar[acc], acc_phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 2, acc); ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; kb++) {
+        const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
+        if (kb0 >= kb1) {   // an empty split (K not divisible): nothing to accumulate; the epilogue stores zeros for it
+          umma_commit(&tfull_bar[acc]);
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1;
+          continue;
+        }
+        for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait_deadline(&full_bar[s], phase)) { ft_set_status(status, FT_K_GEMM, 3, s); ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + s * A_STAGE_BYTES);
@@ -150,7 +162,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                         : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024, FT_SWZ_128B);
             const uint64_t bdesc = B_MN ? make_smem_desc(b_base + k * (UMMA_K * 128), BK * 128, 1024, FT_SWZ_128B)
                                         : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024, FT_SWZ_128B);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -173,7 +185,9 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m0, n0;
-      tile_coords(tile, tiles_m, tiles_n, m0, n0);
+      tile_coords(tile / k_splits, tiles_m, tiles_n, m0, n0);
+      const int split = tile % k_splits;
+      const bool empty_split = split * kb_per >= num_kb_total;
       if (!mbar_wait_deadline(&tfull_bar[acc], acc_phase)) { if (lane == 0) ft_set_status(status, FT_K_GEMM, 4, acc); ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
@@ -187,6 +201,10 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
         __syncwarp();
         tmem_ld_wait();
+        if (empty_split) {
+#pragma unroll
+          for (int i = 0; i < (OUT_F32 ? 32 : 64); i++) v[i] = 0u;
+        }
         const int col0 = n0 + c * EPI_COLS;
         if (bias != nullptr) {
 #pragma unroll
@@ -217,7 +235,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && col0 < N && (m0 + q * 32) < M) {
-          tma_store_2d(&tmD, buf, col0, m0 + q * 32);
+          tma_store_3d(&tmD, buf, col0, m0 + q * 32, split);
         }
         if (lane == 0) tma_store_commit();
         nstore++;
@@ -242,17 +260,17 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, const void* bias, int M, int N, int K,
-           int num_sms, cudaStream_t stream) {
+           int k_splits, int num_sms, cudaStream_t stream) {
   auto kern = ft_gemm_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
     FT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                  ft_status_ptr());
+                                                  k_splits, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -260,12 +278,9 @@ int g_num_sms[64] = {0};
 
 }  // namespace
 
-// D[M,N] = A (x) B (+bias). All pointers are device pointers; lda/ldb/ldd in elements.
-// out_f32 = 0: D is bf16; 1: D is f32. Requirements: base pointers 16-byte aligned,
-// lda/ldb multiples of 8, ldd*elem_size a multiple of 16, M,N,K >= 1.
-FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda,
-                           int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_f32, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return FT_ERR_ARG;
+static int gemm_impl(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb,
+                     int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 64) return FT_ERR_ARG;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
   int dev = 0;
   FT_CUDA_TRY(cudaGetDevice(&dev));
@@ -281,15 +296,32 @@ FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bi
   if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
   else       r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
-  if (out_f32) r = ft_make_tmap_2d(&tD, D, 4, false, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
-  else         r = ft_make_tmap_2d(&tD, D, 2, true, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+  const uint64_t eb = out_f32 ? 4 : 2;
+  r = ft_make_tmap_3d(&tD, D, (int)eb, !out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)k_splits, (uint64_t)ldd * eb, (uint64_t)M * ldd * eb,
+                      out_f32 ? 32 : 64, 32, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
 
   const int sms = g_num_sms[dev];
 #define FT_GEMM_CASE(AM, BMN, OF) \
-  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, sms, stream);
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream);
   FT_GEMM_CASE(0, 0, 0) FT_GEMM_CASE(0, 1, 0) FT_GEMM_CASE(1, 0, 0) FT_GEMM_CASE(1, 1, 0)
   FT_GEMM_CASE(0, 0, 1) FT_GEMM_CASE(0, 1, 1) FT_GEMM_CASE(1, 0, 1) FT_GEMM_CASE(1, 1, 1)
 #undef FT_GEMM_CASE
   return FT_ERR_ARG;
+}
+
+// D[M,N] = A (x) B (+bias). All pointers are device pointers; lda/ldb/ldd in elements.
+// out_f32 = 0: D is bf16; 1: D is f32. Requirements: base pointers 16-byte aligned,
+// lda/ldb multiples of 8, ldd*elem_size a multiple of 16, M,N,K >= 1.
+FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda,
+                           int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_f32, cudaStream_t stream) {
+  return gemm_impl(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream);
+}
+
+// Split-K form: partial[s][M][N] (f32, contiguous planes of M*ldd elements) = A (x) B restricted to the s-th slice of K.
+// The caller (or a fused consumer kernel) sums the planes. Used when M*N is small and K large, e.g. decoding, where the
+// operand stream has to be spread over all SMs.
+FT_EXPORT int ft_gemm_bf16_splitk(const void* A, const void* B, float* partial, int M, int N, int K, int64_t lda, int64_t ldb,
+                                  int64_t ldd, int a_mn, int b_mn, int k_splits, cudaStream_t stream) {
+  return gemm_impl(A, B, partial, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, 1, k_splits, stream);
 }

@@ -84,10 +84,14 @@ class SymmComm:
         _lib.call("ft_comm_allreduce", buf.ptr_array(elem_offset), self.flag_ptrs, self.counter, self.rank, self.world, self._next(),
                   numel, dt, float(scale), mc, max_ctas, _lib.S())
 
-    def all_reduce_small(self, buf: SymmetricBuffer, out: torch.Tensor, numel: int, elem_offset: int = 0, scale: float = 1.0) -> torch.Tensor:
+    def all_reduce_small(self, buf: SymmetricBuffer, out: torch.Tensor, numel: int, elem_offset: int = 0, scale: float = 1.0,
+                         seq_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One-shot all-reduce into ``out``. With ``seq_dev`` (a device int32 scalar, zero-initialised, used by every rank for this
+        communicator) the launch numbers itself on the device and can be captured in a CUDA graph and replayed."""
         dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        seq = 0 if seq_dev is not None else self._next()
         _lib.call("ft_comm_allreduce_1shot", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world,
-                  self._next(), numel, dt, float(scale), 0, _lib.S())
+                  seq, numel, dt, float(scale), 0, seq_dev, _lib.S())
         return out
 
     def reduce_scatter(self, buf: SymmetricBuffer, out: torch.Tensor, chunk: int, elem_offset: int = 0, scale: float = 1.0) -> torch.Tensor:

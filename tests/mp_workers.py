@@ -141,9 +141,38 @@ def case_timeout():
         print("TIMEOUT_OK")
 
 
+def case_tp_decode():
+    """Tensor-parallel engine (prefill + graph-replayed decode) against the dense f32 reference, identical tokens on every rank."""
+    from ferrotorch_b200.models import LlamaConfig
+    from ferrotorch_b200.models.llama_infer import LlamaTPEngine, TPContext, random_hf_weights, reference_last_logits
+    rank, world, dev = _init()
+    cfg = LlamaConfig(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=256)
+    W = random_hf_weights(cfg, dev, seed=1, std=0.05)
+    eng = LlamaTPEngine(cfg, TPContext(dev), max_batch=4, max_seq=128, device=dev, weights=W, use_graph=True)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (4, 40), device=dev)
+    seq = ids.clone()
+    tok = eng.prefill(ids)
+    for step in range(6):
+        ref = reference_last_logits(cfg, W, seq)
+        mine = ref[:, rank * eng.V:(rank + 1) * eng.V]
+        err = (eng.logits - mine).abs().max().item()
+        assert err < 0.06 * ref.abs().max().item() + 0.02, (step, err)
+        toks = [torch.empty_like(tok) for _ in range(world)]
+        dist.all_gather(toks, tok.contiguous())
+        for t in toks[1:]:
+            assert torch.equal(t, toks[0])
+        seq = torch.cat([seq, tok[:, None]], 1)
+        tok = eng.decode_step().clone()
+    eng.check()
+    if rank == 0:
+        print("TP_DECODE_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout}[sys.argv[1]]()
+        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode}[sys.argv[1]]()
     finally:
         if dist.is_initialized():
             dist.destroy_process_group()

@@ -35,6 +35,10 @@ def test_fsdp_fused_matches_nccl():
     assert "FSDP_OK" in _run("fsdp", _n(), 29612)
 
 
+def test_tp_decode_engine_matches_reference():
+    assert "TP_DECODE_OK" in _run("tp_decode", 2, 29614)
+
+
 def test_peer_timeout_is_reported_not_hung():
     out = _run("timeout", 2, 29613, {"NCCL_NVLS_ENABLE": "0", "FT_DISABLE_NVLS": "1"})
     assert "TIMEOUT_OK" in out
