@@ -39,10 +39,12 @@ class TPContext:
         self.group = group
         self.world = self.dist.get_world_size(group) if self.dist else 1
         self.rank = self.dist.get_rank(group) if self.dist else 0
-        self.comm = None
+        self.comm = None          # host-numbered launches (prefill all-reduces)
+        self.comm_graph = None    # device-numbered launches (replayed from CUDA graphs); its own flag block, the two numberings must not mix
         if self.world > 1:
             from ..parallel.symm import SymmComm
             self.comm = SymmComm(self.device, group)
+            self.comm_graph = SymmComm(self.device, group)
 
     def symmetric(self, numel: int, dtype: torch.dtype, zero: bool = True):
         """(local tensor, ctypes array of every rank's pointer) - a plain local buffer when the group has one rank."""
@@ -54,10 +56,22 @@ class TPContext:
         return b.tensor, b.ptr_array(), b
 
 
-def _splits_for(N: int, K: int) -> int:
+def _splits_for(N: int, K: int, sms: int = 148) -> int:
+    """Number of K slices for a decode GEMM. Cost model per work item (one 256-row weight tile x one K slice): weight bytes streamed,
+    32 KiB of partial-plane write + read, and ~90 KB-equivalent of pipeline fill/drain; the estimate is waves x item cost, minimised
+    over the slice counts that leave no empty slice."""
     tiles_n = (N + 255) // 256
     kb = (K + 63) // 64
-    return max(1, min(kb, 64, math.ceil(148 / tiles_n)))
+    best, best_t = 1, float("inf")
+    for sp in range(1, min(kb, 64) + 1):
+        kb_per = -(-kb // sp)
+        if -(-kb // kb_per) != sp:
+            continue
+        items = tiles_n * sp
+        t = math.ceil(items / sms) * (256 * kb_per * 64 * 2 + 32768 + 90000)
+        if t < best_t:
+            best, best_t = sp, t
+    return best
 
 
 class _SplitKGemm:
@@ -199,7 +213,7 @@ class LlamaTPEngine:
         slot.zero_()
         slot[r, : self.B, 0] = val
         slot[r, : self.B, 1] = (idx + r * self.V).float()
-        self.ctx.comm.all_reduce_small(self._pick_buf, self.pick_out, w * PAD_ROWS * 2, seq_dev=self.pick_seq)
+        self.ctx.comm_graph.all_reduce_small(self._pick_buf, self.pick_out, w * PAD_ROWS * 2, seq_dev=self.pick_seq)
         allv = self.pick_out.view(w, PAD_ROWS, 2)
         best = allv[:, : self.B, 0].argmax(dim=0)
         self.tokens.copy_(allv[best, torch.arange(self.B, device=self.dev), 1].long())

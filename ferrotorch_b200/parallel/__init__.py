@@ -1,5 +1,6 @@
 """Parallelism: flat parameter units, FSDP / DDP / tensor / pipeline parallel engines, collectives, symmetric memory."""
 from .flat import FlatUnit, TensorSpec
 from .fsdp import FSDP, ShardingStrategy, AdamWConfig
+from .ddp import DDP, SyncBatchNorm2d
 
-__all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig"]
+__all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig", "DDP", "SyncBatchNorm2d"]
