@@ -8,3 +8,5 @@ from .collective import (ReduceOp, DEFAULT_COLLECTIVE_TIMEOUT, allreduce, allred
 from .ddp import DDP, compute_buckets, DEFAULT_BUCKET_SIZE_BYTES
 from ..errors import (DistributedError, InvalidWorldSize, InvalidRank, SelfSend, SizeMismatch, IoError, ChannelClosed, UnsupportedOp,
                       Timeout, NoConnection, BackendUnavailable)
+from .extras import (DeviceMesh, Placement, Replicate, Shard, Partial, DTensor, PipelineSchedule, Pipeline, RpcAgent, MAX_RPC_BYTES,
+                     ShardingStrategy, FSDP, TensorShardSpec, ShardMetadata, save_distributed, load_distributed, reshard, AsyncCheckpointer)

@@ -29,13 +29,16 @@ class Conv1x1(nn.Conv2d):
         super().__init__(cin, cout, 1, stride, 0, bias=bias)
 
     def forward(self, x):
-        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and self.out_channels % 8 == 0 \
+        w = self.weight
+        if x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+            x, w = x.to(torch.bfloat16), w.to(torch.bfloat16)        # autocast policy: convolutions run in the reduced dtype
+        if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and self.out_channels % 8 == 0 \
                 and x.is_contiguous(memory_format=torch.channels_last):
             if self.stride[0] > 1:
                 x = x[:, :, :: self.stride[0], :: self.stride[1]].contiguous(memory_format=torch.channels_last)
             N, C, H, W = x.shape
             rows = x.permute(0, 2, 3, 1).reshape(N * H * W, C)
-            y = ops.linear(rows, self.weight.view(self.out_channels, C), self.bias)
+            y = ops.linear(rows, w.view(self.out_channels, C), None if self.bias is None else self.bias.to(torch.bfloat16))
             return y.view(N, H, W, self.out_channels).permute(0, 3, 1, 2)
         return super().forward(x)
 

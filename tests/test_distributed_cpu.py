@@ -195,3 +195,98 @@ def test_config1_ddp_world2_tcp_matches_single_process():
         opt.step()
     for a, b in zip(got[0][0], model.parameters()):
         assert np.abs(a - b.detach().numpy()).max() < 1e-5
+
+
+def test_device_mesh_and_dtensor_redistribute():
+    mesh = fd.DeviceMesh([2, 2], ["dp", "tp"])
+    assert mesh.coordinates(3) == (1, 1) and mesh.rank_of((1, 0)) == 2
+    assert mesh.group_ranks(1, "dp") == [1, 3] and mesh.group_ranks(2, "tp") == [2, 3]
+    full = torch.arange(24.).reshape(4, 6)
+
+    def fn(b, r):
+        dt = fd.DTensor.from_full(full, b, fd.Shard(1))
+        assert dt.local.shape == (4, 3) and dt.full_shape() == (4, 6)
+        rep = dt.redistribute(fd.Replicate())
+        part = fd.DTensor(torch.full((2, 2), float(r + 1)), b, fd.Partial())
+        rs = part.redistribute(fd.Shard(0))
+        return rep.local, dt.redistribute(fd.Shard(0)).local, part.redistribute(fd.Replicate()).local, rs.local
+    res = _threads(2, fn)
+    for r, (rep, s0, ar, rs) in enumerate(res):
+        assert torch.equal(rep, full) and torch.equal(s0, full[2 * r:2 * r + 2])
+        assert torch.equal(ar, torch.full((2, 2), 3.0)) and torch.equal(rs, torch.full((1, 2), 3.0))
+
+
+@pytest.mark.parametrize("sched", [fd.PipelineSchedule.GPipe, fd.PipelineSchedule.OneFOneB])
+def test_pipeline_matches_single_process(sched):
+    torch.manual_seed(0)
+    s0, s1 = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh()), torch.nn.Linear(8, 3)
+    x, y = torch.randn(8, 6), torch.randn(8, 3)
+    ref0, ref1 = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.Tanh()), torch.nn.Linear(8, 3)
+    ref0.load_state_dict(s0.state_dict()); ref1.load_state_dict(s1.state_dict())
+    torch.nn.functional.mse_loss(ref1(ref0(x)), y).backward()
+
+    def fn(b, r):
+        p = fd.Pipeline(s0 if r == 0 else s1, b, 4, sched, timeout=20)
+        return p.step(x if r == 0 else None, y if r == 1 else None, torch.nn.functional.mse_loss)
+    res = _threads(2, fn)
+    assert res[1] is not None
+    assert torch.allclose(s0[0].weight.grad, ref0[0].weight.grad, atol=1e-5)       # a real gradient reached the first stage
+    assert torch.allclose(s1.weight.grad, ref1.weight.grad, atol=1e-5)
+
+
+def test_rpc_roundtrip_and_remote_error():
+    def fn(b, r):
+        ag = fd.RpcAgent(b, timeout=10)
+        if r == 1:
+            ag.register("add", lambda a, c: a + c)
+            ag.register("boom", lambda: 1 / 0)
+            return ag.serve(0)
+        out = ag.rpc_sync(1, "add", torch.ones(3), 2)
+        fut = ag.rpc_async(1, "add", 1, 2)
+        v = fut.wait(10)
+        try:
+            ag.rpc_sync(1, "boom")
+            bad = False
+        except errors.WorkerPanic:
+            bad = True
+        ag.shutdown(1)
+        return out, v, bad
+    res = _threads(2, fn)
+    assert torch.equal(res[0][0], torch.full((3,), 3.0)) and res[0][1] == 3 and res[0][2] and res[1] == 3
+
+
+@pytest.mark.parametrize("strategy", [fd.ShardingStrategy.FullShard, fd.ShardingStrategy.ShardGradOp, fd.ShardingStrategy.NoShard])
+def test_cpu_fsdp_matches_averaged_gradients(strategy):
+    torch.manual_seed(1)
+    base = torch.nn.Linear(4, 2)
+    xs = [torch.randn(3, 4), torch.randn(3, 4)]
+    ref = torch.nn.Linear(4, 2)
+    ref.load_state_dict(base.state_dict())
+    (ref(xs[0]).sum() / 2 + ref(xs[1]).sum() / 2).backward()
+
+    def fn(b, r):
+        m = torch.nn.Linear(4, 2)
+        m.load_state_dict(base.state_dict())
+        f = fd.FSDP(m, b, strategy, timeout=20)
+        f(xs[r]).sum().backward()
+        f.sync_gradients()
+        return [s.grad.clone() for s in f.shard_parameters()]
+    res = _threads(2, fn)
+    full_w = ref.weight.grad.reshape(-1)
+    if strategy == fd.ShardingStrategy.NoShard:
+        assert torch.allclose(res[0][0], full_w, atol=1e-6)
+    else:
+        assert torch.allclose(torch.cat([res[0][0], res[1][0]]), full_w, atol=1e-6)
+
+
+def test_distributed_checkpoint_reshards_on_world_change(tmp_path):
+    full = {"w": torch.arange(24.).reshape(6, 4), "b": torch.arange(6.)}
+    for r in range(2):
+        fd.save_distributed(tmp_path, {k: v.chunk(2, 0)[r] for k, v in full.items()}, r, 2)
+    same = fd.load_distributed(tmp_path, 1, 2)
+    assert torch.equal(same["w"], full["w"][3:])
+    parts = [fd.load_distributed(tmp_path, r, 3) for r in range(3)]
+    assert torch.equal(torch.cat([p["w"] for p in parts]), full["w"]) and torch.equal(torch.cat([p["b"] for p in parts]), full["b"])
+    ck = fd.AsyncCheckpointer()
+    ck.save_async(tmp_path / "a", {"w": full["w"]}, 0, 1).wait(10)
+    assert torch.equal(fd.load_distributed(tmp_path / "a", 0, 1)["w"], full["w"])

@@ -35,6 +35,10 @@ def test_fsdp_fused_matches_nccl():
     assert "FSDP_OK" in _run("fsdp", _n(), 29612)
 
 
+def test_ddp_fused_allreduce_and_syncbn():
+    assert "DDP_OK" in _run("ddp", 2, 29615)
+
+
 def test_tp_decode_engine_matches_reference():
     assert "TP_DECODE_OK" in _run("tp_decode", 2, 29614)
 
