@@ -92,7 +92,7 @@ def runtime_sources():
 
 def build_kernels(verbose=False, ptxas_info=False):
     extra = ["-Xptxas", "-v"] if ptxas_info else []
-    link = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-Xcompiler", "-fPIC"]
+    link = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-Xcompiler", "-fPIC", "-Xlinker", "--exclude-libs,ALL"]
     return _build_lib("libft_kernels.so", kernel_sources(), NVCC, NVCC_FLAGS, link, [CSRC / "kernels", CSRC / "include"],
                       verbose or ptxas_info, extra)
 

@@ -38,7 +38,9 @@ def _load(name: str):
             _build.build_all()
     if not path.exists():
         raise NativeLibraryMissing(f"{path} is missing; run `python -m ferrotorch_b200._build`")
-    return ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+    # local binding: the kernels library carries its own static CUDA runtime, whose symbols must not interpose on the ones other
+    # libraries in the process (cuDNN, NCCL) resolve lazily
+    return ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
 
 
 def kernels():

@@ -100,71 +100,183 @@ __global__ void paged_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv, int
 
 // ------------------------------------------------------------------------------------------------------------
 // paged decode attention (D = 128, group size G = Hq/Hkv <= 8)
-// grid (nsplit, Hkv, B), 128 threads. Workspace per (b, kvh, split): G * (2 + 128) floats. counters: int [B*Hkv], zero.
+// grid (nsplit, Hkv, B), 128 threads. Workspace per (b, kvh, split, g): PA_WS_ROW floats = 128 accumulators, running max, running sum, 2 pad.
+// counters: int [B*Hkv], zero before the first launch (the kernel re-zeroes them).
+// A CTA streams its token range through a three-stage shared-memory ring of 64-token K/V chunks filled by 16-byte cp.async copies
+// (XOR-swizzled 16-byte columns), so the whole range is in flight after one page-table lookup. Each warp owns 16 tokens of a chunk:
+// S = Q K^T and O += P V run on mma.sync m16n8k16 with the G query heads as the (zero-padded) M rows -- the decode shape has M = G <= 8,
+// far below a tcgen05 tile, and the kernel is bound by the K/V stream, not by the tensor pipe.
 // ------------------------------------------------------------------------------------------------------------
-template <int G>
+constexpr int PA_CHUNK = 64, PA_STAGES = 3;
+constexpr int PA_STAGE_BYTES = PA_CHUNK * 128 * 2 * 2;       // K and V rows of one chunk
+constexpr int PA_SMEM = PA_STAGES * PA_STAGE_BYTES;
+constexpr int PA_WS_ROW = 132;
+constexpr int PA_MAX_SPLIT = 64;
+
+FT_DEVICE void cp_async16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory"); }
+FT_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+FT_DEVICE void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+FT_DEVICE void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+FT_DEVICE void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+FT_DEVICE void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+FT_DEVICE uint32_t pa_sw(int row, int chunk) { return (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)); }
+
 __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                                                 const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                                                                 int max_blocks, const int* __restrict__ seq_lens, int Hq, int Hkv, float scale,
                                                                 float* __restrict__ ws, int* __restrict__ counters,
                                                                 __nv_bfloat16* __restrict__ out) {
   constexpr int D = 128;
+  extern __shared__ __align__(128) uint8_t pa_smem[];
+  const int G = Hq / Hkv;
   const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int len = seq_lens[b];
   const int per = (((len + nsplit - 1) / nsplit) + KV_BLOCK - 1) / KV_BLOCK * KV_BLOCK;   // whole pages per split
   const int t0 = split * per, t1 = min(len, t0 + per);
-  float qv[G][4], acc[G][4], m[G], l[G];
+  const int nchunks = t1 > t0 ? (t1 - t0 + PA_CHUNK - 1) / PA_CHUNK : 0;
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(pa_smem);
+  const int* bt = block_table + (size_t)b * max_blocks;
+
+  auto load_chunk = [&](int c, int stage) {
+    const int c0 = t0 + c * PA_CHUNK, cnt = min(PA_CHUNK, t1 - c0);
+    const uint32_t kdst = smem_base + stage * PA_STAGE_BYTES, vdst = kdst + PA_CHUNK * D * 2;
+    for (int i = threadIdx.x; i < cnt * 16; i += 128) {            // 16 copies of 16 bytes per 256-byte row
+      const int r = i >> 4, part = i & 15, t = c0 + r;
+      const int blk = __ldg(bt + t / KV_BLOCK);
+      const size_t off = (((size_t)blk * KV_BLOCK + t % KV_BLOCK) * Hkv + kvh) * D + part * 8;
+      cp_async16(kdst + pa_sw(r, part), k_cache + off);
+      cp_async16(vdst + pa_sw(r, part), v_cache + off);
+    }
+    // rows up to the next multiple of 16 feed the tensor cores with weight zero: they must hold finite values
+    uint8_t* kz = pa_smem + stage * PA_STAGE_BYTES;
+    for (int i = cnt * 16 + threadIdx.x; i < ((cnt + 15) & ~15) * 16; i += 128) {
+      const int r = i >> 4, part = i & 15;
+      *reinterpret_cast<uint4*>(kz + pa_sw(r, part)) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(kz + PA_CHUNK * D * 2 + pa_sw(r, part)) = make_uint4(0, 0, 0, 0);
+    }
+  };
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + ((size_t)b * Hq + kvh * G + g) * D + lane * 4);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    qv[g][0] = a.x * scale; qv[g][1] = a.y * scale; qv[g][2] = c.x * scale; qv[g][3] = c.y * scale;
-    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-    m[g] = -INFINITY;
-    l[g] = 0.f;
+  for (int s = 0; s < PA_STAGES; s++) {
+    if (s < nchunks) load_chunk(s, s);
+    cp_async_commit();
   }
-  for (int t = t0 + warp; t < t1; t += 4) {
-    const int blk = block_table[(size_t)b * max_blocks + t / KV_BLOCK];
-    const size_t off = (((size_t)blk * KV_BLOCK + t % KV_BLOCK) * Hkv + kvh) * D + lane * 4;
-    const uint2 kr = *reinterpret_cast<const uint2*>(k_cache + off), vr = *reinterpret_cast<const uint2*>(v_cache + off);
-    const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x)), k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
-    const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x)), v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+
+  // A fragments of Q (rows = query heads of this KV head, rows >= G are zero): registers 0 and 2 of every k-step
+  const int g_row = lane >> 2, qc = (lane & 3) * 2;
+  uint32_t qf[8][2];
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-      float s = qv[g][0] * k0.x + qv[g][1] * k0.y + qv[g][2] * k1.x + qv[g][3] * k1.y;
-      s = warp_sum(s);
-      const float mn = fmaxf(m[g], s);
-      const float a = __expf(m[g] - mn), p = __expf(s - mn);
-      l[g] = l[g] * a + p;
-      acc[g][0] = acc[g][0] * a + p * v0.x; acc[g][1] = acc[g][1] * a + p * v0.y;
-      acc[g][2] = acc[g][2] * a + p * v1.x; acc[g][3] = acc[g][3] * a + p * v1.y;
-      m[g] = mn;
+  for (int ks = 0; ks < 8; ks++) {
+    qf[ks][0] = qf[ks][1] = 0u;
+    if (g_row < G) {
+      const __nv_bfloat16* qp = q + ((size_t)b * Hq + kvh * G + g_row) * D + ks * 16 + qc;
+      qf[ks][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qf[ks][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
     }
   }
-  // merge the four warps of this CTA
-  __shared__ float sm_m[4][G], sm_l[4][G], sm_acc[4][G][D];
+  const float sl2 = scale * 1.4426950408889634f;
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;                             // of head g_row; l_run is this thread's share of the row sum
+
+  for (int c = 0; c < nchunks; c++) {
+    cp_async_wait<PA_STAGES - 1>();
+    __syncthreads();
+    const int stage = c % PA_STAGES, cnt = min(PA_CHUNK, t1 - (t0 + c * PA_CHUNK));
+    const uint32_t kbase = smem_base + stage * PA_STAGE_BYTES, vbase = kbase + PA_CHUNK * D * 2;
+    const int r0 = warp * 16;
+    if (r0 < cnt) {
+      float sacc[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; j++) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+      {
+        const int row = r0 + (lane & 7) + ((lane >> 4) << 3), cb = (lane >> 3) & 1;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+          uint32_t kb[4];
+          ldmatrix_x4(kb, kbase + pa_sw(row, ks * 2 + cb));
+          mma_16816(sacc[0], qf[ks][0], 0u, qf[ks][1], 0u, kb[0], kb[1]);
+          mma_16816(sacc[1], qf[ks][0], 0u, qf[ks][1], 0u, kb[2], kb[3]);
+        }
+      }
+      bool valid[2][2];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          valid[j][e] = r0 + j * 8 + qc + e < cnt;
+          if (valid[j][e]) mx = fmaxf(mx, sacc[j][e]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);                         // finite: the group holds at least one live token
+      const float alpha = exp2f((m_run - m_new) * sl2);
+      float p[2][2], psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; j++)
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+          p[j][e] = valid[j][e] ? exp2f((sacc[j][e] - m_new) * sl2) : 0.f;
+          psum += p[j][e];
+        }
+      l_run = l_run * alpha + psum;
+      m_run = m_new;
+#pragma unroll
+      for (int i = 0; i < 16; i++) { o[i][0] *= alpha; o[i][1] *= alpha; }
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(p[0][0], p[0][1]), p1 = __floats2bfloat162_rn(p[1][0], p[1][1]);
+      const uint32_t pa0 = *reinterpret_cast<uint32_t*>(&p0), pa2 = *reinterpret_cast<uint32_t*>(&p1);
+      {
+        const int row = r0 + (lane & 7) + (((lane >> 3) & 1) << 3), cb = lane >> 4;
+#pragma unroll
+        for (int dp = 0; dp < 8; dp++) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, vbase + pa_sw(row, dp * 2 + cb));
+          mma_16816(o[2 * dp], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+          mma_16816(o[2 * dp + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
+        }
+      }
+    }
+    __syncthreads();                                                // the stage is free again
+    if (c + PA_STAGES < nchunks) load_chunk(c + PA_STAGES, stage);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  __syncthreads();
+  // merge the four warps of this CTA (the ring is idle: its first bytes hold the per-warp accumulators)
+  __shared__ float sm_m[4][8], sm_l[4][8];
   __shared__ int is_last;
+  float (*sm_acc)[8][D] = reinterpret_cast<float (*)[8][D]>(pa_smem);
+  if (g_row < G) {
+    if ((lane & 3) == 0) { sm_m[warp][g_row] = m_run; sm_l[warp][g_row] = l_run; }
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
-#pragma unroll
-    for (int e = 0; e < 4; e++) sm_acc[warp][g][lane * 4 + e] = acc[g][e];
+    for (int i = 0; i < 16; i++) *reinterpret_cast<float2*>(&sm_acc[warp][g_row][i * 8 + qc]) = make_float2(o[i][0], o[i][1]);
   }
   __syncthreads();
-  float* my_ws = ws + (((size_t)b * Hkv + kvh) * nsplit + split) * G * (2 + D);
+  float* my_ws = ws + (((size_t)b * Hkv + kvh) * nsplit + split) * G * PA_WS_ROW;
   for (int i = threadIdx.x; i < G * D; i += 128) {
     const int g = i / D, d = i % D;
     const float mm = fmaxf(fmaxf(sm_m[0][g], sm_m[1][g]), fmaxf(sm_m[2][g], sm_m[3][g]));
     float a = 0.f, ll = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; w++) {
-      const float f = (sm_m[w][g] == -INFINITY) ? 0.f : __expf(sm_m[w][g] - mm);
+      const float f = (sm_m[w][g] == -INFINITY) ? 0.f : exp2f((sm_m[w][g] - mm) * sl2);
       a += sm_acc[w][g][d] * f;
       ll += sm_l[w][g] * f;
     }
-    my_ws[g * (2 + D) + 2 + d] = a;
-    if (d == 0) { my_ws[g * (2 + D)] = mm; my_ws[g * (2 + D) + 1] = ll; }
+    my_ws[g * PA_WS_ROW + d] = a;
+    if (d == 0) { my_ws[g * PA_WS_ROW + D] = mm * scale; my_ws[g * PA_WS_ROW + D + 1] = ll; }
   }
   __threadfence();
   __syncthreads();
@@ -176,19 +288,45 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloa
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  const float* base = ws + ((size_t)b * Hkv + kvh) * nsplit * G * (2 + D);
-  for (int i = threadIdx.x; i < G * D; i += 128) {
-    const int g = i / D, d = i % D;
-    float mm = -INFINITY;
-    for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, base[(size_t)s * G * (2 + D) + g * (2 + D)]);
-    float a = 0.f, ll = 0.f;
+  // the last CTA of this (sequence, KV head) combines the splits: first the weights f[s][g] and row sums, then one pass of float4 loads
+  const float* base = ws + ((size_t)b * Hkv + kvh) * nsplit * G * PA_WS_ROW;
+  float* sm_pm = reinterpret_cast<float*>(pa_smem + 32768);        // [nsplit * G] each, behind the warp accumulators
+  float* sm_pl = sm_pm + PA_MAX_SPLIT * 8;
+  float* sm_L = sm_pl + PA_MAX_SPLIT * 8;
+  for (int i = threadIdx.x; i < nsplit * G; i += 128) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(base + (size_t)i * PA_WS_ROW + D));
+    sm_pm[i] = ml.x;
+    sm_pl[i] = ml.y;
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    float mm = -INFINITY, ll = 0.f;
+    for (int s = 0; s < nsplit; s++) mm = fmaxf(mm, sm_pm[s * G + g]);
     for (int s = 0; s < nsplit; s++) {
-      const float* p = base + (size_t)s * G * (2 + D) + g * (2 + D);
-      const float f = (p[0] == -INFINITY) ? 0.f : __expf(p[0] - mm);
-      a += p[2 + d] * f;
-      ll += p[1] * f;
+      const float pm = sm_pm[s * G + g];
+      const float f = (pm == -INFINITY) ? 0.f : __expf(pm - mm);
+      ll += sm_pl[s * G + g] * f;
+      sm_pm[s * G + g] = f;
     }
-    out[((size_t)b * Hq + kvh * G + g) * D + d] = __float2bfloat16(ll > 0.f ? a / ll : 0.f);
+    sm_L[g] = ll;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * (D / 4); i += 128) {
+    const int g = i / (D / 4), d4 = (i % (D / 4)) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 16
+    for (int s = 0; s < nsplit; s++) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(base + ((size_t)s * G + g) * PA_WS_ROW + d4));
+      const float f = sm_pm[s * G + g];
+      a.x += v.x * f; a.y += v.y * f; a.z += v.z * f; a.w += v.w * f;
+    }
+    const float inv = sm_L[g] > 0.f ? 1.f / sm_L[g] : 0.f;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv), hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + ((size_t)b * Hq + kvh * G + g) * D + d4) = pk;
   }
 }
 
@@ -324,22 +462,24 @@ FT_EXPORT int ft_paged_kv_write(const void* qkv, int64_t ld, int B, int S, int H
 }
 
 // q, out: bf16 [B, Hq, 128]; seq_lens[b] counts the tokens already in the cache (including the one just written).
-// ws: f32 scratch of B * Hkv * nsplit * (Hq/Hkv) * 130 floats; counters: int [B*Hkv], zero before the first call (the kernel re-zeroes them).
+// ws: f32 scratch of B * Hkv * nsplit * (Hq/Hkv) * 132 floats (16-byte aligned); counters: int [B*Hkv], zero before the first call
+// (the kernel re-zeroes them). Hq/Hkv <= 8, nsplit <= 64.
 FT_EXPORT int ft_paged_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_blocks,
                                    const int* seq_lens, int B, int Hq, int Hkv, int D, float scale, int nsplit, float* ws, int* counters, void* out,
                                    cudaStream_t st) {
-  if (D != 128 || Hq % Hkv || nsplit < 1 || nsplit > 64) return FT_ERR_ARG;
-  const int G = Hq / Hkv;
-  dim3 grid(nsplit, Hkv, B);
-#define FT_PA(GG)                                                                                                                      \
-  if (G == GG) {                                                                                                                       \
-    paged_attn_decode_kernel<GG><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
-                                                       block_table, max_blocks, seq_lens, Hq, Hkv, scale, ws, counters, (__nv_bfloat16*)out); \
-    return (int)cudaGetLastError();                                                                                                    \
+  if (D != 128 || Hq % Hkv || Hq / Hkv > 8 || nsplit < 1 || nsplit > PA_MAX_SPLIT || (reinterpret_cast<uintptr_t>(ws) & 15)) return FT_ERR_ARG;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_set[64] = {};
+  if (dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(paged_attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PA_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev] = true;
   }
-  FT_PA(1) FT_PA(2) FT_PA(4) FT_PA(8)
-#undef FT_PA
-  return FT_ERR_ARG;
+  paged_attn_decode_kernel<<<dim3(nsplit, Hkv, B), 128, PA_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
+                                                                       block_table, max_blocks, seq_lens, Hq, Hkv, scale, ws, counters,
+                                                                       (__nv_bfloat16*)out);
+  return (int)cudaGetLastError();
 }
 
 FT_EXPORT int ft_decode_swiglu(const float* partial, int splits, int64_t ldp, int64_t plane_stride, int rows, int F, void* out, cudaStream_t st) {

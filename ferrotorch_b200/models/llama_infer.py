@@ -177,8 +177,9 @@ class LlamaTPEngine:
         self.attn = torch.zeros(PAD_ROWS, self.Hq * self.D, device=dev, dtype=torch.bfloat16)
         self.act = torch.zeros(PAD_ROWS, self.F, device=dev, dtype=torch.bfloat16)
         self.logits = torch.zeros(B, self.V, device=dev, dtype=torch.float32)
-        self.nsplit = 16
-        self.attn_ws = torch.zeros(B * self.Hkv * self.nsplit * (self.Hq // self.Hkv) * 130, device=dev, dtype=torch.float32)
+        # about two CTAs per SM across (batch, kv head, split); the kernel accepts at most 64 splits
+        self.nsplit = max(1, min(64, -(-296 // max(1, B * self.Hkv))))
+        self.attn_ws = torch.zeros(B * self.Hkv * self.nsplit * (self.Hq // self.Hkv) * 132, device=dev, dtype=torch.float32)
         self.attn_ctr = torch.zeros(B * self.Hkv, device=dev, dtype=torch.int32)
         # all-reduce staging: two slots of [PAD_ROWS, d] floats per rank + flag block + grid-barrier ints
         self.ar_sym, self.ar_sym_ptrs, self._ar_sym_buf = self.ctx.symmetric(2 * PAD_ROWS * d, torch.float32)

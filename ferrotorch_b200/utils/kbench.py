@@ -156,6 +156,30 @@ def single_attn():
     print("attn1 done", float(out[0, 0]))
 
 
+def bench_paged(results):
+    """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1."""
+    import math
+    from ferrotorch_b200 import _lib
+    pk = peaks()
+    for Hq, Hkv, B, L, nsplit in [(8, 1, 8, 2304, 16), (8, 1, 8, 2304, 37), (64, 8, 8, 2304, 5), (64, 8, 8, 2304, 16)]:
+        D, mb = 128, (L + 15) // 16
+        kc = torch.randn(B * mb, 16, Hkv, D, device="cuda").to(torch.bfloat16)
+        vc = torch.randn_like(kc)
+        bt = torch.arange(B * mb, device="cuda", dtype=torch.int32).view(B, mb)
+        lens = torch.full((B,), L, device="cuda", dtype=torch.int32)
+        q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+        out = torch.empty_like(q)
+        ws = torch.zeros(B * Hkv * nsplit * (Hq // Hkv) * 132, device="cuda")
+        ctr = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
+        fn = lambda: _lib.call("ft_paged_attn_decode", q, kc, vc, bt, mb, lens, B, Hq, Hkv, D, 1 / math.sqrt(D), nsplit, ws, ctr, out, _lib.S())
+        med, best = time_fn(fn, iters=20)
+        nbytes = B * L * Hkv * D * 2 * 2
+        r = {"case": f"paged_attn_decode B{B} L{L} Hq{Hq} Hkv{Hkv} nsplit{nsplit}", "us_median": med * 1e3, "gbs": nbytes / med / 1e6,
+             "frac_of_hbm": nbytes / best / 1e6 / pk["hbm_gbs"]}
+        results.append(r)
+        print(json.dumps(r), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", nargs="?", default="all")
@@ -170,6 +194,8 @@ def main():
         bench_gemm(res)
     if a.what in ("attn", "all"):
         bench_attn(res)
+    if a.what in ("paged", "all"):
+        bench_paged(res)
     if a.what in ("elementwise", "all"):
         bench_elementwise(res)
     if a.json:

@@ -40,7 +40,7 @@ def test_paged_attention_decode(Hq, Hkv):
     q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
     nsplit = 4
-    ws = torch.zeros(B * Hkv * nsplit * (Hq // Hkv) * 130, device="cuda")
+    ws = torch.zeros(B * Hkv * nsplit * (Hq // Hkv) * 132, device="cuda")
     ctr = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
     for _ in range(2):      # second call checks that the counters reset themselves
         _lib.call("ft_paged_attn_decode", q, kc, vc, perm, max_blocks, lens, B, Hq, Hkv, D, 1.0 / math.sqrt(D), nsplit, ws, ctr, out, _lib.S())
