@@ -280,7 +280,7 @@ int g_num_sms[64] = {0};
 
 static int gemm_impl(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb,
                      int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 64) return FT_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
   int dev = 0;
   FT_CUDA_TRY(cudaGetDevice(&dev));

@@ -316,15 +316,14 @@ class JsonSchemaProcessor:
 def apply_mask(logits: torch.Tensor, mask: TokenMask) -> torch.Tensor:
     """``logits[..., v] = -inf`` where the mask forbids token ``v``."""
     allowed = mask.allowed.to(logits.device)
-    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16) and logits.is_contiguous():
-        try:
-            from .. import _lib
-            if hasattr(_lib.kernels(), "ft_token_mask"):
-                _lib.call("ft_token_mask", logits, allowed.to(torch.uint8), logits.numel() // logits.shape[-1], logits.shape[-1],
-                          int(logits.dtype == torch.float32), _lib.S())
-                return logits
-        except Exception:
-            raise
+    if logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16, torch.float16) and logits.is_contiguous():
+        from ..ops import tensor_ops
+        V = logits.shape[-1]
+        pad = (-V) % 32
+        bits = torch.nn.functional.pad(allowed.to(torch.int64), (0, pad)).view(-1, 32)
+        words = (bits << torch.arange(32, device=bits.device)).sum(-1)                      # bit v%32 of word v//32 = token v allowed
+        words = torch.where(words >= 2 ** 31, words - 2 ** 32, words).to(torch.int32)
+        return tensor_ops.token_mask_(logits, words)
     return logits.masked_fill(~allowed, float("-inf"))
 
 

@@ -278,7 +278,7 @@ def compile_cuda(source: str, arch: str = "sm_100a") -> bytes:
     err, prog = nvrtc.nvrtcCreateProgram(source.encode(), b"fused.cu", 0, [], [])
     if err != nvrtc.nvrtcResult.NVRTC_SUCCESS:
         raise FerrotorchError(f"nvrtcCreateProgram failed: {err}")
-    opts = [f"--gpu-architecture={arch}".encode(), b"-std=c++17", b"--use_fast_math", b"-lineinfo"] + [f"-I{d}".encode() for d in _cuda_include_dirs()]
+    opts = [f"--gpu-architecture={arch}".encode(), b"-std=c++17", b"-lineinfo"] + [f"-I{d}".encode() for d in _cuda_include_dirs()]
     (err,) = nvrtc.nvrtcCompileProgram(prog, len(opts), opts)
     if err != nvrtc.nvrtcResult.NVRTC_SUCCESS:
         _, n = nvrtc.nvrtcGetProgramLogSize(prog)

@@ -10,3 +10,5 @@ from .attention import attention_packed, flash_fwd, flash_bwd
 from . import attention
 
 __all__ = [n for n in dir() if not n.startswith("_")]
+from . import tensor_ops  # noqa: E402
+from . import nn_ops  # noqa: E402

@@ -79,11 +79,44 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise InvalidArgument("gemm output must be bf16 or f32")
     if bias is not None:
         bias = bias.to(torch.bfloat16).contiguous()
+    splits = _auto_splits(M, N, K)
+    if splits > 1:
+        # few output tiles and a long K (weight gradients of 1x1 convolutions, decode): spread K over the SMs as f32 planes, then sum
+        planes = _plane_cache(a.device, splits * M * N)[: splits * M * N].view(splits, M, N)
+        with torch.cuda.device(a.device):
+            _lib.call("ft_gemm_bf16_splitk", _lib.P(a), _lib.P(b), _lib.P(planes), M, N, K, ctypes.c_int64(a.stride(0)), ctypes.c_int64(b.stride(0)),
+                      ctypes.c_int64(N), int(a_mn), int(b_mn), splits, _lib.S())
+            _lib.call("ft_splitk_reduce", _lib.P(planes), splits, M, N, ctypes.c_int64(N), ctypes.c_int64(M * N), _lib.P(bias), _lib.P(out),
+                      ctypes.c_int64(out.stride(0)), int(out_dtype == torch.float32), _lib.S())
+        return out
     with torch.cuda.device(a.device):
         _lib.call("ft_gemm_bf16", _lib.P(a), _lib.P(b), _lib.P(out), _lib.P(bias), M, N, K, ctypes.c_int64(a.stride(0)),
                   ctypes.c_int64(b.stride(0)), ctypes.c_int64(out.stride(0)), int(a_mn), int(b_mn),
                   int(out_dtype == torch.float32), _lib.S())
     return out
+
+
+_planes: dict = {}
+
+
+def _plane_cache(device: torch.device, numel: int) -> torch.Tensor:
+    buf = _planes.get(device)
+    if buf is None or buf.numel() < numel:
+        buf = _planes[device] = torch.empty(max(numel, 1 << 22), device=device, dtype=torch.float32)
+    return buf
+
+
+def _auto_splits(M: int, N: int, K: int) -> int:
+    """Number of K slices: 1 unless the 128x256 output tiles cover less than half of the 148 SMs and K is long enough that every
+    slice still runs at least eight 64-wide K steps. N must be a multiple of 4 (f32 plane rows start on 16-byte boundaries)."""
+    tiles = -(-M // 128) * -(-N // 256)
+    if tiles * 2 > 148 or N % 4 or K < 2048:
+        return 1
+    splits = min(148 // tiles, K // 512)
+    num_kb = -(-K // 64)
+    while splits > 1 and -(-num_kb // splits) * (splits - 1) >= num_kb:               # no empty trailing slice
+        splits -= 1
+    return max(splits, 1)
 
 
 class _LinearFn(torch.autograd.Function):

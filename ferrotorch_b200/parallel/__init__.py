@@ -2,5 +2,7 @@
 from .flat import FlatUnit, TensorSpec
 from .fsdp import FSDP, ShardingStrategy, AdamWConfig
 from .ddp import DDP, SyncBatchNorm2d
+from .tp import ColumnParallelLinear, RowParallelLinear, ParallelEmbedding, TpGemmContext
 
-__all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig", "DDP", "SyncBatchNorm2d"]
+__all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig", "DDP", "SyncBatchNorm2d", "ColumnParallelLinear", "RowParallelLinear",
+           "ParallelEmbedding", "TpGemmContext"]

@@ -43,6 +43,29 @@ class Conv1x1(nn.Conv2d):
         return super().forward(x)
 
 
+def bn_act(bn: torch.nn.BatchNorm2d, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = True) -> torch.Tensor:
+    """BatchNorm (+ residual add) (+ ReLU). Channels-last CUDA f32/bf16 activations take the fused two-stage-statistics kernels; everything else
+    (CPU, NCHW, SyncBatchNorm subclasses with their own forward) the module's own path."""
+    fused = (type(bn).forward is torch.nn.BatchNorm2d.forward and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float32, torch.bfloat16)
+             and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last) and bn.affine and bn.track_running_stats
+             and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous(memory_format=torch.channels_last))))
+    if not fused:
+        out = bn(x)
+        if residual is not None:
+            out = out + residual
+        return torch.relu(out) if relu else out
+    if bn.training and bn.num_batches_tracked is not None:
+        bn.num_batches_tracked.add_(1)
+    return ops.nn_ops.batch_norm_nhwc(x, bn.weight, bn.bias, bn.running_mean, bn.running_var, residual=residual, relu=relu, training=bn.training,
+                                      momentum=0.1 if bn.momentum is None else bn.momentum, eps=bn.eps)
+
+
+def max_pool(x: torch.Tensor, k: int, s: int, p: int) -> torch.Tensor:
+    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last):
+        return ops.nn_ops.max_pool2d_nhwc(x, k, s, p)
+    return F.max_pool2d(x, k, s, p)
+
+
 def conv3x3(cin, cout, stride=1, groups=1, dilation=1):
     return nn.Conv2d(cin, cout, 3, stride, dilation, dilation, groups, bias=False)
 
@@ -58,10 +81,9 @@ class BasicBlock(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.bn2(self.conv2(out))
-        return self.relu(out + idt)
+        idt = x if self.downsample is None else bn_act(self.downsample[1], self.downsample[0](x), relu=False)
+        out = bn_act(self.bn1, self.conv1(x))
+        return bn_act(self.bn2, self.conv2(out), residual=idt)
 
 
 class Bottleneck(nn.Module):
@@ -76,11 +98,10 @@ class Bottleneck(nn.Module):
         self.downsample = downsample
 
     def forward(self, x):
-        idt = x if self.downsample is None else self.downsample(x)
-        out = self.relu(self.bn1(self.conv1(x)))
-        out = self.relu(self.bn2(self.conv2(out)))
-        out = self.bn3(self.conv3(out))
-        return self.relu(out + idt)
+        idt = x if self.downsample is None else bn_act(self.downsample[1], self.downsample[0](x), relu=False)
+        out = bn_act(self.bn1, self.conv1(x))
+        out = bn_act(self.bn2, self.conv2(out))
+        return bn_act(self.bn3, self.conv3(out), residual=idt)
 
 
 class ResNet(nn.Module):
@@ -123,7 +144,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*layers)
 
     def features(self, x):
-        x = self.maxpool(self.relu(self.bn1(self.conv1(x))))
+        x = max_pool(bn_act(self.bn1, self.conv1(x)), 3, 2, 1)
         return self.layer4(self.layer3(self.layer2(self.layer1(x))))
 
     def forward(self, x):

@@ -224,9 +224,50 @@ def case_ddp():
         print("DDP_OK")
 
 
+def case_tp_gemm():
+    """Fused all-gather->GEMM and GEMM->reduce-scatter against the unfused library path, several launches in a row (flag / parity reuse)."""
+    from ferrotorch_b200 import _lib
+    from ferrotorch_b200.parallel import ColumnParallelLinear, RowParallelLinear, ParallelEmbedding
+    rank, world, dev = _init()
+    M, D, Fdim = 128 * world * 3, 512, 1024 + 256
+    torch.manual_seed(0)
+    w1, w2 = (torch.randn(Fdim, D, device=dev) * 0.05).bfloat16(), (torch.randn(D, Fdim, device=dev) * 0.05).bfloat16()
+    col_f, col_n = ColumnParallelLinear(D, Fdim, device=dev, comm="fused"), ColumnParallelLinear(D, Fdim, device=dev, comm="nccl")
+    row_f, row_n = RowParallelLinear(Fdim, D, device=dev, comm="fused"), RowParallelLinear(Fdim, D, device=dev, comm="nccl")
+    for m in (col_f, col_n):
+        m.load_full_weight(w1)
+    for m in (row_f, row_n):
+        m.load_full_weight(w2)
+    with torch.no_grad():
+        for it in range(5):
+            torch.manual_seed(10 + it)
+            x_full = torch.randn(M, D, device=dev).bfloat16()               # same on every rank
+            xs = x_full[rank * (M // world): (rank + 1) * (M // world)].contiguous()
+            h_f, h_n = col_f(xs), col_n(xs)
+            ref_h = (x_full.float() @ w1.float().t())[:, rank * (Fdim // world): (rank + 1) * (Fdim // world)]
+            assert h_f.shape == (M, Fdim // world)
+            assert (h_f.float() - ref_h).abs().max() < 0.05 and (h_f.float() - h_n.float()).abs().max() < 0.02, it
+            y_f, y_n = row_f(h_n), row_n(h_n)
+            hf_all = [torch.empty_like(h_n) for _ in range(world)]
+            dist.all_gather(hf_all, h_n)
+            ref_y = (torch.cat(hf_all, 1).float() @ w2.float().t())[rank * (M // world): (rank + 1) * (M // world)]
+            assert y_f.shape == (M // world, D)
+            assert (y_f.float() - ref_y).abs().max() < 0.06, (it, float((y_f.float() - ref_y).abs().max()))
+            assert (y_f.float() - y_n.float()).abs().max() < 0.05
+    emb = ParallelEmbedding(64 * world, 32, device=dev)
+    full = torch.arange(64 * world * 32, device=dev, dtype=torch.float32).view(64 * world, 32).bfloat16()
+    emb.load_full_weight(full)
+    ids = torch.randint(0, 64 * world, (4, 9), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    assert torch.equal(emb(ids), full[ids])
+    assert _lib.read_status() == 0
+    dist.barrier()
+    if rank == 0:
+        print("TP_GEMM_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp}[sys.argv[1]]()
+        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp, "tp_gemm": case_tp_gemm}[sys.argv[1]]()
     finally:
         if dist.is_initialized():
             dist.destroy_process_group()

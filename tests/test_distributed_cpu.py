@@ -290,3 +290,44 @@ def test_distributed_checkpoint_reshards_on_world_change(tmp_path):
     ck = fd.AsyncCheckpointer()
     ck.save_async(tmp_path / "a", {"w": full["w"]}, 0, 1).wait(10)
     assert torch.equal(fd.load_distributed(tmp_path / "a", 0, 1)["w"], full["w"])
+
+
+def _tp_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from ferrotorch_b200.parallel import ColumnParallelLinear, ParallelEmbedding, RowParallelLinear
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        M, D, Fd = 8 * world, 16, 24
+        w1, w2, x = torch.randn(Fd, D), torch.randn(D, Fd), torch.randn(M, D)
+        col = ColumnParallelLinear(D, Fd, dtype=torch.float32)
+        row = RowParallelLinear(Fd, D, dtype=torch.float32)
+        col.load_full_weight(w1)
+        row.load_full_weight(w2)
+        xs = x[rank * (M // world): (rank + 1) * (M // world)]
+        y = row(col(xs))
+        ref = (x @ w1.t() @ w2.t())[rank * (M // world): (rank + 1) * (M // world)]
+        emb = ParallelEmbedding(10 * world, 4, dtype=torch.float32)
+        full = torch.arange(10 * world * 4, dtype=torch.float32).view(10 * world, 4)
+        emb.load_full_weight(full)
+        ids = torch.tensor([[0, 10 * world - 1, 7], [3, 11 % (10 * world), 5]])
+        q.put((rank, float((y - ref).abs().max()), bool(torch.equal(emb(ids), full[ids]))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_layers_world2_gloo():
+    """Column/row-parallel linears (sequence-parallel) and the vocabulary-parallel embedding over a CPU group equal the dense computation."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29741
+    ps = [ctx.Process(target=_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=120) for _ in ps]
+    for p in ps:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, err, emb_ok in res:
+        assert err < 1e-4 and emb_ok, (rank, err, emb_ok)

@@ -20,15 +20,16 @@ def test_fused_kernel_vectorised_and_strided(dtype, tol):
     cf = jit.compile(_f, backend="cuda")
     l0 = _lib.launch_calls
     out = cf(x, y, b)                                # b is broadcast -> strided kernel
-    ref = _f(x.float(), y.float(), b.float())
+    ref = _f(x, y, b)                                # eager in the same dtype: the generated code rounds through the storage type after every op, as eager does
     assert cf.stats.fused_kernels == 1 and _lib.launch_calls > l0
-    assert (out[1].float() - ref[1]).abs().max() < tol
-    assert (out[0].float() - ref[0]).abs().max() < tol * 1027 ** 0.5 * 4
+    rel = lambda a, r: ((a.float() - r.float()).abs() / (1 + r.float().abs())).max()   # noqa: E731
+    assert rel(out[1], ref[1]) < tol
+    assert rel(out[0], ref[0]) < tol * 4
     f2 = lambda p, q: torch.tanh(p) * q + F.silu(p)  # noqa: E731  all operands dense -> 16-byte vector kernel, ragged tail (512*1027 % 8 != 0 for bf16)
     c2 = jit.compile(f2, backend="cuda")
-    assert (c2(x, y).float() - f2(x.float(), y.float())).abs().max() < tol
+    assert rel(c2(x, y), f2(x, y)) < tol
     xs = x[:, ::2]                                   # strided view
-    assert (c2(xs, y[:, ::2]).float() - f2(xs.float(), y[:, ::2].float())).abs().max() < tol
+    assert rel(c2(xs, y[:, ::2]), f2(xs, y[:, ::2])) < tol
     assert _lib.read_status() == 0
 
 

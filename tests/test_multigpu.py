@@ -39,6 +39,10 @@ def test_ddp_fused_allreduce_and_syncbn():
     assert "DDP_OK" in _run("ddp", 2, 29615)
 
 
+def test_tp_fused_gemm_collectives():
+    assert "TP_GEMM_OK" in _run("tp_gemm", 2, 29616)
+
+
 def test_tp_decode_engine_matches_reference():
     assert "TP_DECODE_OK" in _run("tp_decode", 2, 29614)
 
