@@ -238,6 +238,36 @@ __global__ void __launch_bounds__(512) allgather_kernel(PeerPtrs bufs, const T* 
   comm_end(s, status);
 }
 
+// all-to-all (pull): out[q*chunk + i] = buf_q[rank*chunk + i]: every rank exposes W chunks (chunk q is addressed to rank q) and pulls the chunks
+// addressed to itself from every peer. The building block of Ulysses sequence parallelism and of expert dispatch / combine.
+template <typename T>
+__global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t chunk, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = chunk / V, total = nvec * s.world;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int q = (int)(i / nvec);
+    const size_t k = i % nvec;
+    const int src = (s.rank + q) % s.world;                 // start at the own chunk so the ranks do not all read the same peer first
+    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(bufs.p[src]) + chunk * s.rank + k * V);
+    *reinterpret_cast<uint4*>(out + chunk * src + k * V) = v;
+  }
+  comm_end(s, status);
+}
+
+// broadcast (pull): out[i] = buf_root[i] on every rank
+template <typename T>
+__global__ void __launch_bounds__(512) broadcast_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, int root, size_t n, uint32_t* status) {
+  if (!comm_begin(s, status)) return;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = n / V;
+  if (s.rank != root || out != bufs.p[root]) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x)
+      *reinterpret_cast<uint4*>(out + i * V) = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(bufs.p[root]) + i * V);
+  }
+  comm_end(s, status);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // FSDP: reduce-scatter(mean) of the bf16 gradient unit + AdamW on the owned f32 slice + push all-gather
 // ---------------------------------------------------------------------------------------------------------
@@ -387,6 +417,38 @@ FT_EXPORT int ft_comm_allgather(void* const* buf_ptrs, const void* src, void* co
   const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
   if (dtype == 0) allgather_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (const __nv_bfloat16*)src, s, (size_t)chunk, ft_status_ptr());
   else allgather_kernel<float><<<grid, 512, 0, st>>>(b, (const float*)src, s, (size_t)chunk, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// out[q*chunk : (q+1)*chunk] = rank q's buf[rank*chunk : (rank+1)*chunk]; buf holds world*chunk elements on every rank.
+FT_EXPORT int ft_comm_alltoall(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                               int64_t chunk, int dtype, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  const int V = dtype == 0 ? 8 : 4;
+  if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  const int grid = comm_grid((size_t)chunk * world / V, max_ctas > 0 ? max_ctas : 64);
+  if (dtype == 0) alltoall_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, (size_t)chunk, ft_status_ptr());
+  else alltoall_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, (size_t)chunk, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// out[0:n] on every rank = root's buf[0:n].
+FT_EXPORT int ft_comm_broadcast(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                                int root, int64_t n, int dtype, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  if (r) return r;
+  const int V = dtype == 0 ? 8 : 4;
+  if (n <= 0 || n % V || root < 0 || root >= world) return FT_ERR_ARG;
+  PeerPtrs b;
+  for (int i = 0; i < MAX_RANKS; i++) b.p[i] = i < world ? buf_ptrs[i] : nullptr;
+  const int grid = comm_grid((size_t)n / V, max_ctas > 0 ? max_ctas : 64);
+  if (dtype == 0) broadcast_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, root, (size_t)n, ft_status_ptr());
+  else broadcast_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, root, (size_t)n, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 

@@ -2,7 +2,8 @@
 from .flat import FlatUnit, TensorSpec
 from .fsdp import FSDP, ShardingStrategy, AdamWConfig
 from .ddp import DDP, SyncBatchNorm2d
+from .cp import UlyssesAttention, ring_attention
 from .tp import ColumnParallelLinear, RowParallelLinear, ParallelEmbedding, TpGemmContext
 
 __all__ = ["FlatUnit", "TensorSpec", "FSDP", "ShardingStrategy", "AdamWConfig", "DDP", "SyncBatchNorm2d", "ColumnParallelLinear", "RowParallelLinear",
-           "ParallelEmbedding", "TpGemmContext"]
+           "ParallelEmbedding", "TpGemmContext", "UlyssesAttention", "ring_attention"]

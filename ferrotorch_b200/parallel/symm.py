@@ -105,6 +105,18 @@ class SymmComm:
         _lib.call("ft_comm_allgather", buf.ptr_array(elem_offset), src, self.flag_ptrs, self.counter, self.rank, self.world, self._next(),
                   chunk, dt, 0, _lib.S())
 
+    def all_to_all(self, buf: SymmetricBuffer, out: torch.Tensor, chunk: int, elem_offset: int = 0) -> torch.Tensor:
+        """``out[q*chunk:(q+1)*chunk]`` = rank q's ``buf[rank*chunk:(rank+1)*chunk]`` (every rank exposes ``world`` chunks, chunk q addressed to rank q)."""
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        _lib.call("ft_comm_alltoall", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world, self._next(), chunk, dt, 0, _lib.S())
+        return out
+
+    def broadcast(self, buf: SymmetricBuffer, out: torch.Tensor, numel: int, root: int = 0, elem_offset: int = 0) -> torch.Tensor:
+        dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        _lib.call("ft_comm_broadcast", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world, self._next(), root, numel, dt, 0,
+                  _lib.S())
+        return out
+
     def barrier(self) -> None:
         _lib.call("ft_comm_barrier", self.flag_ptrs, self.counter, self.rank, self.world, self._next(), _lib.S())
 

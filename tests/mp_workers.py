@@ -265,9 +265,48 @@ def case_tp_gemm():
         print("TP_GEMM_OK")
 
 
+def case_cp():
+    """Peer-memory all-to-all / broadcast kernels, Ulysses attention over them and ring attention pulling K/V blocks from peers."""
+    from ferrotorch_b200 import _lib
+    from ferrotorch_b200.parallel import UlyssesAttention, ring_attention
+    from ferrotorch_b200.parallel.symm import SymmComm, SymmetricBuffer
+    rank, world, dev = _init()
+    comm = SymmComm(dev)
+    for dtype in (torch.bfloat16, torch.float32):
+        chunk = 4096 + 64
+        buf = SymmetricBuffer(world * chunk, dtype, dev)
+        buf.tensor.copy_((torch.arange(world * chunk, device=dev) % 251 + rank * 1000).to(dtype))
+        out = torch.empty(world * chunk, device=dev, dtype=dtype)
+        comm.all_to_all(buf, out, chunk)
+        for q in range(world):
+            exp = (torch.arange(rank * chunk, (rank + 1) * chunk, device=dev) % 251 + q * 1000).to(dtype)
+            assert torch.equal(out[q * chunk:(q + 1) * chunk], exp), (dtype, q)
+        b = torch.empty(chunk, device=dev, dtype=dtype)
+        comm.broadcast(buf, b, chunk, root=world - 1)
+        assert torch.equal(b, (torch.arange(chunk, device=dev) % 251 + (world - 1) * 1000).to(dtype))
+    torch.manual_seed(0)
+    S, Hq, Hkv, D = 256 * world, 8, 2 * world, 128
+    Q, K, V = (torch.randn(S, h, D, device=dev).bfloat16() for h in (Hq, Hkv, Hkv))
+    sl = slice(rank * (S // world), (rank + 1) * (S // world))
+    rep = Hq // Hkv
+    for causal in (True, False):
+        ref = torch.nn.functional.scaled_dot_product_attention(Q.float().transpose(0, 1)[None], K.float().repeat_interleave(rep, 1).transpose(0, 1)[None],
+                                                               V.float().repeat_interleave(rep, 1).transpose(0, 1)[None], is_causal=causal)[0].transpose(0, 1)[sl]
+        with torch.no_grad():
+            u = UlyssesAttention(causal=causal)(Q[sl].contiguous(), K[sl].contiguous(), V[sl].contiguous())
+        assert (u.float() - ref).abs().max() < 3e-2, ("ulysses", causal, float((u.float() - ref).abs().max()))
+        kvbuf = SymmetricBuffer(2 * K[sl].numel(), torch.bfloat16, dev)
+        r = ring_attention(Q[sl].contiguous(), K[sl].contiguous(), V[sl].contiguous(), causal=causal, fabric=(comm, kvbuf))
+        assert (r.float() - ref).abs().max() < 3e-2, ("ring", causal, float((r.float() - ref).abs().max()))
+    assert _lib.read_status() == 0
+    dist.barrier()
+    if rank == 0:
+        print("CP_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp, "tp_gemm": case_tp_gemm}[sys.argv[1]]()
+        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp, "tp_gemm": case_tp_gemm, "cp": case_cp}[sys.argv[1]]()
     finally:
         if dist.is_initialized():
             dist.destroy_process_group()

@@ -331,3 +331,44 @@ def test_tensor_parallel_layers_world2_gloo():
         assert p.exitcode == 0
     for rank, err, emb_ok in res:
         assert err < 1e-4 and emb_ok, (rank, err, emb_ok)
+
+
+def _cp_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from ferrotorch_b200.parallel import UlyssesAttention, ring_attention
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        S, Hq, Hkv, D = 16 * world, 4, 2, 8
+        Q, K, V = torch.randn(S, Hq, D), torch.randn(S, Hkv, D), torch.randn(S, Hkv, D)
+        sl = slice(rank * (S // world), (rank + 1) * (S // world))
+        errs = []
+        for causal in (True, False):
+            rep = Hq // Hkv
+            ref = torch.nn.functional.scaled_dot_product_attention(Q.transpose(0, 1)[None], K.repeat_interleave(rep, 1).transpose(0, 1)[None],
+                                                                   V.repeat_interleave(rep, 1).transpose(0, 1)[None], is_causal=causal)[0].transpose(0, 1)[sl]
+            ql = Q[sl].clone().requires_grad_()
+            u = UlyssesAttention(causal=causal)(ql, K[sl], V[sl])
+            u.sum().backward()
+            errs.append(float((u - ref).abs().max()))
+            errs.append(float((ring_attention(Q[sl], K[sl], V[sl], causal=causal) - ref).abs().max()))
+            assert ql.grad is not None and ql.grad.shape == ql.shape
+        q.put((rank, max(errs)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ulysses_and_ring_attention_world2_gloo():
+    """Sequence-parallel attention (head exchange and K/V ring) equals dense attention on the gathered sequence, causal and not."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_cp_worker, args=(r, 2, 29743, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=120) for _ in ps]
+    for p in ps:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, err in res:
+        assert err < 1e-5, (rank, err)

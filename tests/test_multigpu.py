@@ -43,6 +43,10 @@ def test_tp_fused_gemm_collectives():
     assert "TP_GEMM_OK" in _run("tp_gemm", 2, 29616)
 
 
+def test_context_parallel_attention_and_exchange_kernels():
+    assert "CP_OK" in _run("cp", 2, 29617)
+
+
 def test_tp_decode_engine_matches_reference():
     assert "TP_DECODE_OK" in _run("tp_decode", 2, 29614)
 
