@@ -34,6 +34,8 @@ NVCC_FLAGS = [
     "--use_fast_math", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
     "-I", str(CSRC / "kernels"), "-I", str(CSRC / "include"),
 ]
+# bandwidth-bound generic kernels keep IEEE-accurate transcendentals (they are compared against f32 / f64 references at tight tolerances)
+PRECISE_MATH = {"elementwise.cu", "reduce_index.cu", "nn_ops.cu"}
 CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread", "-I", str(CSRC / "include"), "-I", str(CSRC / "runtime")]
 
 
@@ -66,7 +68,8 @@ def _build_lib(name, sources, compiler, flags, link_cmd, hdr_dirs, verbose, extr
         obj = OBJ / (src.stem + ("_cu.o" if src.suffix == ".cu" else "_cpp.o"))
         objs.append(obj)
         if (not obj.exists()) or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m):
-            jobs.append(([compiler, *flags, *extra_flags, "-c", str(src), "-o", str(obj)], src, obj))
+            fl = [f for f in flags if not (f == "--use_fast_math" and src.name in PRECISE_MATH)]
+            jobs.append(([compiler, *fl, *extra_flags, "-c", str(src), "-o", str(obj)], src, obj))
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
             futs = [ex.submit(_compile, c, s, o, verbose) for c, s, o in jobs]

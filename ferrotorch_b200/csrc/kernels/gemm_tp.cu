@@ -296,7 +296,8 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
       if (MODE == 2) {
-        __threadfence_system();                                    // this lane's peer stores are visible before the count
+        // release pattern: the warp barrier orders every lane's peer stores before lane 0's release-add (cumulativity), so the owner that
+        // acquires the count sees the whole 32-row slab; no per-lane system fence is needed
         __syncwarp();
         if (lane == 0) red_release_sys_add(a.cnt[p] + (size_t)par * tpr * tiles_n + tin * tiles_n + ni, 1u);
       }
@@ -308,33 +309,56 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t want = ((a.seq + 1u) >> 1) * 4u * (uint32_t)W;
       const __nv_bfloat16* mine = a.stage[a.rank] + (size_t)par * W * m_loc * N;
       const int et = threadIdx.x - 64;                              // 0..127 over the four epilogue warps
-      for (int u = g_id; u < tpr * tiles_n; u += g_n) {
+      for (int ut = g_id; ut < tpr * tiles_n; ut += g_n) {
         bool fine = true;
-        if (lane == 0) fine = wait_flag_ge(a.cnt[a.rank] + (size_t)par * tpr * tiles_n + u, want, WAIT_NS);
+        if (lane == 0) fine = wait_flag_ge(a.cnt[a.rank] + (size_t)par * tpr * tiles_n + ut, want, WAIT_NS);
         fine = __shfl_sync(0xffffffffu, fine, 0);
         __syncwarp();                                               // lane 0's acquire orders the whole warp's reads of the partials
-        if (!fine) { if (lane == 0) ft_set_status(status, FT_K_TP, 9, u); break; }
-        const int tin = u / tiles_n, n0 = (u % tiles_n) * BN;
-        for (int vix = et; vix < BM * (BN / 8); vix += 128) {
-          const int r = vix / (BN / 8), cv = vix % (BN / 8);
-          if (n0 + cv * 8 >= N) continue;
-          const size_t off = ((size_t)tin * BM + r) * N + n0 + cv * 8;
-          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < W; s++) {
-            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(mine + (size_t)s * m_loc * N + off));
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        if (!fine) { if (lane == 0) ft_set_status(status, FT_K_TP, 9, ut); break; }
+        const int tin = ut / tiles_n, n0 = (ut % tiles_n) * BN;
+        // four 16-byte vectors per thread per pass and all W partials of each issued before use: the reduce is a pure stream of local
+        // memory and needs many loads in flight per thread to run at bandwidth
+        constexpr int UNR = 4;
+        for (int vb = et; vb < BM * (BN / 8); vb += 128 * UNR) {
+          float accv[UNR][8];
+          size_t off[UNR];
+          bool live[UNR];
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-              const float2 f = __bfloat1622float2(h[e]);
-              accv[2 * e] += f.x;
-              accv[2 * e + 1] += f.y;
+          for (int u = 0; u < UNR; u++) {
+            const int vix = vb + u * 128;
+            const int r = vix / (BN / 8), cv = vix % (BN / 8);
+            live[u] = vix < BM * (BN / 8) && n0 + cv * 8 < N;
+            off[u] = ((size_t)tin * BM + r) * N + n0 + cv * 8;
+#pragma unroll
+            for (int e = 0; e < 8; e++) accv[u][e] = 0.f;
+          }
+#pragma unroll
+          for (int s = 0; s < MAXR; s++) {
+            if (s < W) {
+              uint4 raw[UNR];
+#pragma unroll
+              for (int u = 0; u < UNR; u++) raw[u] = live[u] ? __ldcg(reinterpret_cast<const uint4*>(mine + (size_t)s * m_loc * N + off[u])) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+              for (int u = 0; u < UNR; u++) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  const float2 f = __bfloat1622float2(h[e]);
+                  accv[u][2 * e] += f.x;
+                  accv[u][2 * e + 1] += f.y;
+                }
+              }
             }
           }
-          uint4 o;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-          for (int e = 0; e < 4; e++) oh[e] = __floats2bfloat162_rn(accv[2 * e], accv[2 * e + 1]);
-          *reinterpret_cast<uint4*>(a.out + off) = o;
+          for (int u = 0; u < UNR; u++) {
+            if (!live[u]) continue;
+            uint4 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; e++) oh[e] = __floats2bfloat162_rn(accv[u][2 * e], accv[u][2 * e + 1]);
+            *reinterpret_cast<uint4*>(a.out + off[u]) = o;
+          }
         }
       }
     }

@@ -372,3 +372,66 @@ def test_ulysses_and_ring_attention_world2_gloo():
         assert p.exitcode == 0
     for rank, err in res:
         assert err < 1e-5, (rank, err)
+
+
+def test_heartbeat_failure_detection_and_elastic_restart(tmp_path):
+    """Three rank threads train; rank 2 stops between steps (no GPU involved). The survivors notice through the heartbeat store within the
+    timeout, re-rendezvous as a world of two with new ranks, and reload the distributed checkpoint re-sharded for the new world."""
+    import threading
+    from ferrotorch_b200.distributed import load_distributed, save_distributed
+    from ferrotorch_b200.distributed.elastic import DistributedMonitor, ElasticCoordinator, HeartbeatMonitor, MemoryStore, RankFailure, resume_from_checkpoint
+    store = MemoryStore()
+    full = torch.arange(24, dtype=torch.float32).view(6, 4)
+    for r in range(3):
+        save_distributed(str(tmp_path), {"w": full[r * 2:(r + 1) * 2].clone()}, r, 3, {"w": 0})
+    results, errors = {}, []
+
+    def rank_fn(rank):
+        try:
+            hb = HeartbeatMonitor(store, rank, 3, interval_s=0.01, timeout_s=0.15).start()
+            if rank == 2:
+                time.sleep(0.05)
+                hb.stop()                                  # "dies" between steps: stops heartbeating and never joins again
+                return
+            t0 = time.monotonic()
+            failed = None
+            while time.monotonic() - t0 < 5:
+                try:
+                    hb.check()
+                except RankFailure as e:
+                    failed = e.ranks
+                    break
+                time.sleep(0.01)
+            hb.stop()
+            assert failed == [2], failed
+            m = ElasticCoordinator(store, min_world=2, timeout_s=5).rendezvous(rank, 3, failed, generation=0)
+            state = resume_from_checkpoint(str(tmp_path), m)
+            results[rank] = (m, state["w"], time.monotonic() - t0)
+        except Exception as e:                             # noqa: BLE001
+            errors.append((rank, repr(e)))
+    import time
+    ts = [threading.Thread(target=rank_fn, args=(r,)) for r in range(3)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(20)
+    assert not errors, errors
+    assert set(results) == {0, 1}
+    for old in (0, 1):
+        m, w, dt = results[old]
+        assert (m.generation, m.rank, m.world, m.old_ranks) == (1, old, 2, [0, 1]) and dt < 2.0
+        assert torch.equal(w, full[old * 3:(old + 1) * 3])                 # 6 rows over 2 ranks now
+    with pytest.raises(Exception):
+        ElasticCoordinator(store, min_world=3).rendezvous(0, 3, [2], 0)
+    with pytest.raises(Exception):
+        ElasticCoordinator(MemoryStore(), timeout_s=0.1).rendezvous(0, 3, [2], 0)   # rank 1 never joins -> Timeout, not a hang
+    mon = DistributedMonitor("tokens", roofline_ms=1.0)
+    for _ in range(3):
+        with mon.span("step"):
+            with mon.span("compute"):
+                time.sleep(0.002)
+            with mon.span("comm"):
+                time.sleep(0.001)
+        mon.end_step(1000)
+    s = mon.summary(skip=1)
+    assert s["tokens_per_s"] > 0 and 0 < s["comm_to_compute"] < 2 and 0 < s["fraction_of_roofline"] < 1

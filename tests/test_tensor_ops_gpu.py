@@ -25,12 +25,12 @@ def test_unary_forward_and_backward(dtype, tol):
         got, ref = T.unary(name, x), fn(ref_in)
         err = ((got.to(ref.dtype) - ref).abs() / (1 + ref.abs())).max().item()
         assert err < tol * 4, (name, err)
-    assert torch.allclose(T.unary("elu", x, 0.7).float(), F.elu(x.float(), 0.7), atol=tol * 4, rtol=tol * 4)
-    assert torch.allclose(T.unary("clamp", x, -0.5, 0.25).float(), x.float().clamp(-0.5, 0.25), atol=tol, rtol=tol)
-    assert torch.allclose(T.unary("scale", x, 2.0, 1.0).float(), x.float() * 2 + 1, atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(T.unary("elu", x, 0.7).to(ref_in.dtype), F.elu(ref_in, 0.7), atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(T.unary("clamp", x, -0.5, 0.25).to(ref_in.dtype), ref_in.clamp(-0.5, 0.25), atol=tol, rtol=tol)
+    assert torch.allclose(T.unary("scale", x, 2.0, 1.0).to(ref_in.dtype), ref_in * 2 + 1, atol=tol * 4, rtol=tol * 4)
     pos = x.abs() + 0.5
-    assert torch.allclose(T.unary("log", pos).float(), pos.float().log(), atol=tol * 4, rtol=tol * 4)
-    assert torch.allclose(T.unary("rsqrt", pos).float(), pos.float().rsqrt(), atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(T.unary("log", pos).to(ref_in.dtype), pos.to(ref_in.dtype).log(), atol=tol * 4, rtol=tol * 4)
+    assert torch.allclose(T.unary("rsqrt", pos).to(ref_in.dtype), pos.to(ref_in.dtype).rsqrt(), atol=tol * 4, rtol=tol * 4)
     if dtype in (torch.float32, torch.float64):
         g = _t(333, 1001, dtype=dtype, seed=1)
         for name, fn, saved_is_out in [("relu", torch.relu, False), ("gelu", F.gelu, False), ("gelu_tanh", lambda t: F.gelu(t, approximate="tanh"), False),
