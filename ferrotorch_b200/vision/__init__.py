@@ -8,3 +8,16 @@ from .ops import (box_convert, box_area, box_iou, generalized_box_iou, distance_
 from .data import (read_image, write_image, Mnist, Cifar10, Cifar100, DatasetFolder, ImageFolder, Compose, ToTensor, VisionNormalize, Resize,
                    CenterCrop, RandomCrop, RandomHorizontalFlip, RandomVerticalFlip, RandomResizedCrop, RandomRotation, ColorJitter, GaussianNoise,
                    RandomGaussianBlur, RandomApply, ElasticTransform, TrivialAugmentWide)
+from . import models2, segmentation, detection  # noqa: E402
+from .models2 import MobileNetV3, MobileNetV3Small, MobileNetV3Large, mobilenet_v3_small, mobilenet_v3_large, InceptionV3, inception_v3, SwinTransformer, swin_tiny  # noqa: E402
+from .segmentation import Fcn, DeepLabV3, Lraspp, Aspp, fcn_resnet50, deeplabv3_resnet50, lraspp_mobilenet_v3_large  # noqa: E402
+from .detection import (FeaturePyramidNetwork, AnchorGenerator, Rpn, decode_boxes, encode_boxes, postprocess_detections, postprocess_masks, FasterRcnn,  # noqa: E402
+                        MaskRcnn, KeypointRcnn, RetinaNet, Fcos, Ssd300, fasterrcnn_resnet50_fpn, maskrcnn_resnet50_fpn, keypointrcnn_resnet50_fpn,
+                        retinanet_resnet50_fpn, fcos_resnet50_fpn, ssd300_vgg16)
+
+for _n, _c in (("mobilenet_v3_small", mobilenet_v3_small), ("mobilenet_v3_large", mobilenet_v3_large), ("inception_v3", inception_v3), ("swin_tiny", swin_tiny),
+               ("fcn_resnet50", fcn_resnet50), ("deeplabv3_resnet50", deeplabv3_resnet50), ("lraspp_mobilenet_v3_large", lraspp_mobilenet_v3_large),
+               ("fasterrcnn_resnet50_fpn", fasterrcnn_resnet50_fpn), ("maskrcnn_resnet50_fpn", maskrcnn_resnet50_fpn),
+               ("keypointrcnn_resnet50_fpn", keypointrcnn_resnet50_fpn), ("retinanet_resnet50_fpn", retinanet_resnet50_fpn), ("fcos_resnet50_fpn", fcos_resnet50_fpn),
+               ("ssd300_vgg16", ssd300_vgg16)):
+    models.register_model(_n, _c)

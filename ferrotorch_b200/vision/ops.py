@@ -93,28 +93,43 @@ def remove_small_boxes(boxes: torch.Tensor, min_size: float) -> torch.Tensor:
 
 
 def nms(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torch.Tensor:
-    """Greedy non-maximum suppression; returns kept indices in decreasing score order. The suppression matrix is computed in one
-    batched IoU and resolved with a short sequential scan over the sorted candidates."""
+    """Greedy non-maximum suppression; returns kept indices in decreasing score order. CPU boxes run the native sorted sweep (O(N) memory);
+    CUDA boxes the mask + on-device sweep kernels."""
     if boxes.numel() == 0:
         return torch.empty(0, dtype=torch.long, device=boxes.device)
     order = scores.argsort(descending=True)
-    b = boxes[order]
-    iou = box_iou(b, b).triu(1) > iou_threshold
-    keep = torch.ones(len(b), dtype=torch.bool, device=boxes.device)
-    iou_c = iou.cpu() if len(b) > 4096 else iou
-    keep_c = keep.cpu() if len(b) > 4096 else keep
-    for i in range(len(b)):
-        if keep_c[i]:
-            keep_c &= ~iou_c[i]
-            keep_c[i] = True
-    return order[keep_c.to(boxes.device)]
+    b = boxes[order].float().contiguous()
+    n = len(b)
+    if boxes.is_cuda:
+        from .. import _lib
+        words = (n + 63) // 64
+        mask = torch.empty(n * words, dtype=torch.int64, device=boxes.device)
+        keep = torch.empty(n, dtype=torch.uint8, device=boxes.device)
+        _lib.call("ft_nms_sorted", b, n, float(iou_threshold), mask, keep, None, _lib.S())
+        return order[keep.bool()]
+    import ctypes
+    from .. import _lib
+    fn = _lib.runtime().ft_nms_sorted_f32
+    fn.restype = ctypes.c_int64
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]
+    keep = torch.empty(n, dtype=torch.uint8)
+    fn(b.data_ptr(), n, float(iou_threshold), keep.data_ptr())
+    return order[keep.bool()]
 
 
 def batched_nms(boxes, scores, idxs, iou_threshold: float):
+    """Class-wise NMS: a coordinate offset per class for small inputs, a per-class loop above 4000 boxes (bounded suppression work)."""
     if boxes.numel() == 0:
         return torch.empty(0, dtype=torch.long, device=boxes.device)
-    off = idxs.to(boxes) * (boxes.max() + 1)
-    return nms(boxes + off[:, None], scores, iou_threshold)
+    if len(boxes) <= 4000:
+        off = idxs.to(boxes) * (boxes.max() + 1)
+        return nms(boxes + off[:, None], scores, iou_threshold)
+    keep = torch.zeros(len(boxes), dtype=torch.bool, device=boxes.device)
+    for c in torch.unique(idxs):
+        sel = torch.where(idxs == c)[0]
+        keep[sel[nms(boxes[sel], scores[sel], iou_threshold)]] = True
+    k = torch.where(keep)[0]
+    return k[scores[k].argsort(descending=True)]
 
 
 def sigmoid_focal_loss(inputs, targets, alpha: float = 0.25, gamma: float = 2.0, reduction: str = "none"):

@@ -154,3 +154,15 @@ def test_gguf_dequant_and_token_mask():
     ref = logits.masked_fill(~allow.cuda(), float("-inf"))
     assert torch.equal(T.token_mask_(logits.clone(), words), ref)
     assert torch.equal(T.token_mask_(logits.bfloat16(), words), ref.bfloat16())
+
+
+def test_nms_kernels_match_host_sweep():
+    from ferrotorch_b200.vision import ops as V
+    g = torch.Generator().manual_seed(0)
+    for n in (1, 63, 64, 65, 1000, 5000):
+        b = torch.rand(n, 4, generator=g) * 100
+        b[:, 2:] = b[:, :2] + torch.rand(n, 2, generator=g) * 30 + 1
+        s = torch.rand(n, generator=g)
+        assert torch.equal(V.nms(b.cuda(), s.cuda(), 0.5).cpu(), V.nms(b, s, 0.5)), n
+    idx = torch.randint(0, 7, (5000,), generator=g)
+    assert torch.equal(V.batched_nms(b.cuda(), s.cuda(), idx.cuda(), 0.4).cpu(), V.batched_nms(b, s, idx, 0.4))
