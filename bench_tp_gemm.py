@@ -21,7 +21,7 @@ def main():
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--ncopy", type=int, default=8)
+    ap.add_argument("--ncopy", type=int, default=0, help="copier CTAs of the all-gather GEMM (0 = kernel default)")
     a = ap.parse_args()
     import torch
     import torch.distributed as dist

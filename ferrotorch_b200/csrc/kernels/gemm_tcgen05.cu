@@ -58,11 +58,30 @@ FT_DEVICE bool mbar_wait_deadline(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// Epilogue extras: activation code applied after the bias, then an optional residual tile added (residual rows are ldr elements apart, same
+// dtype as the output); in_f16 selects fp16 operands (bias / residual / bf16-typed output are then fp16 as well).
+struct EpiArgs {
+  int act;                       // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh), 4 silu
+  const void* residual;
+  int64_t ldr;
+  int in_f16;
+};
+
+FT_DEVICE float epi_act(int act, float x) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.f);
+    case 2: return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+    case 3: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case 4: return x / (1.f + __expf(-x));
+    default: return x;
+  }
+}
+
 template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmD, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-               int k_splits, uint32_t* status) {
+               int k_splits, uint32_t* status, const EpiArgs epi) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -134,7 +153,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(BM, BN, /*bf16*/ 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      const uint32_t idesc = epi.in_f16 ? make_idesc_f16(BM, BN, /*f16*/ 0, A_MN ? 1 : 0, B_MN ? 1 : 0)
+                                        : make_idesc_f16(BM, BN, /*bf16*/ 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t s = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -209,8 +229,33 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (bias != nullptr) {
 #pragma unroll
           for (int i = 0; i < EPI_COLS; i++) {
-            float b = (col0 + i < N) ? __bfloat162float(__ldg(bias + col0 + i)) : 0.f;
+            float b = 0.f;
+            if (col0 + i < N) b = epi.in_f16 ? __half2float(__ldg(reinterpret_cast<const __half*>(bias) + col0 + i)) : __bfloat162float(__ldg(bias + col0 + i));
             v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
+          }
+        }
+        if (epi.act != 0) {
+#pragma unroll
+          for (int i = 0; i < EPI_COLS; i++) v[i] = __float_as_uint(epi_act(epi.act, __uint_as_float(v[i])));
+        }
+        if (epi.residual != nullptr && m0 + q * 32 + lane < M) {
+          // the lane owns one output row: its residual segment is EPI_COLS contiguous elements
+          const size_t roff = (size_t)(m0 + q * 32 + lane) * (size_t)epi.ldr + col0;
+          if constexpr (OUT_F32) {
+            const float* rp = reinterpret_cast<const float*>(epi.residual) + roff;
+#pragma unroll
+            for (int i = 0; i < EPI_COLS; i++)
+              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + rp[i]);
+          } else if (epi.in_f16) {
+            const __half* rp = reinterpret_cast<const __half*>(epi.residual) + roff;
+#pragma unroll
+            for (int i = 0; i < EPI_COLS; i++)
+              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __half2float(rp[i]));
+          } else {
+            const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(epi.residual) + roff;
+#pragma unroll
+            for (int i = 0; i < EPI_COLS; i++)
+              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(rp[i]));
           }
         }
         uint8_t* row = buf + lane * 128;
@@ -226,8 +271,13 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t p[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
-              p[e] = *reinterpret_cast<uint32_t*>(&h);
+              if (epi.in_f16) {
+                __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                p[e] = *reinterpret_cast<uint32_t*>(&h);
+              } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                p[e] = *reinterpret_cast<uint32_t*>(&h);
+              }
             }
             *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
           }
@@ -260,7 +310,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, const void* bias, int M, int N, int K,
-           int k_splits, int num_sms, cudaStream_t stream) {
+           int k_splits, int num_sms, cudaStream_t stream, const EpiArgs& epi) {
   auto kern = ft_gemm_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
@@ -270,7 +320,7 @@ int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                  k_splits, ft_status_ptr());
+                                                  k_splits, ft_status_ptr(), epi);
   return (int)cudaGetLastError();
 }
 
@@ -279,7 +329,9 @@ int g_num_sms[64] = {0};
 }  // namespace
 
 static int gemm_impl(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb,
-                     int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream) {
+                     int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream, EpiArgs epi = EpiArgs{0, nullptr, 0, 0}) {
+  if (epi.act < 0 || epi.act > 4) return FT_ERR_ARG;
+  const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
   int dev = 0;
@@ -290,20 +342,20 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
 
   CUtensorMap tA, tB, tD;
   int r;
-  if (!a_mn) r = ft_make_tmap_2d(&tA, A, 2, true, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-  else       r = ft_make_tmap_2d(&tA, A, 2, true, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!a_mn) r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
-  if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
-  else       r = ft_make_tmap_2d(&tB, B, 2, true, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   const uint64_t eb = out_f32 ? 4 : 2;
-  r = ft_make_tmap_3d(&tD, D, (int)eb, !out_f32, (uint64_t)N, (uint64_t)M, (uint64_t)k_splits, (uint64_t)ldd * eb, (uint64_t)M * ldd * eb,
+  r = ft_make_tmap_3d(&tD, D, (int)eb, !out_f32 && in_bf16, (uint64_t)N, (uint64_t)M, (uint64_t)k_splits, (uint64_t)ldd * eb, (uint64_t)M * ldd * eb,
                       out_f32 ? 32 : 64, 32, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
 
   const int sms = g_num_sms[dev];
 #define FT_GEMM_CASE(AM, BMN, OF) \
-  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream);
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream, epi);
   FT_GEMM_CASE(0, 0, 0) FT_GEMM_CASE(0, 1, 0) FT_GEMM_CASE(1, 0, 0) FT_GEMM_CASE(1, 1, 0)
   FT_GEMM_CASE(0, 0, 1) FT_GEMM_CASE(0, 1, 1) FT_GEMM_CASE(1, 0, 1) FT_GEMM_CASE(1, 1, 1)
 #undef FT_GEMM_CASE
@@ -316,6 +368,13 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
 FT_EXPORT int ft_gemm_bf16(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda,
                            int64_t ldb, int64_t ldd, int a_mn, int b_mn, int out_f32, cudaStream_t stream) {
   return gemm_impl(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream);
+}
+
+// Extended form: fp16 operands (in_f16 = 1; bias, residual and a 16-bit output are fp16 then), an activation after the bias
+// (act: 0 none, 1 relu, 2 gelu, 3 gelu-tanh, 4 silu) and a residual matrix [M, N] (rows ldr elements apart, dtype of D) added last.
+FT_EXPORT int ft_gemm_ex(const void* A, const void* B, void* D, const void* bias, const void* residual, int M, int N, int K, int64_t lda, int64_t ldb,
+                         int64_t ldd, int64_t ldr, int a_mn, int b_mn, int out_f32, int in_f16, int act, cudaStream_t stream) {
+  return gemm_impl(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream, EpiArgs{act, residual, ldr, in_f16});
 }
 
 // Split-K form: partial[s][M][N] (f32, contiguous planes of M*ldd elements) = A (x) B restricted to the s-th slice of K.

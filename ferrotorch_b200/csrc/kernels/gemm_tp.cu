@@ -1,14 +1,15 @@
 // Tensor-parallel GEMMs fused with their collective over peer-mapped (symmetric) memory, bf16, NT layout (x [rows, K] . w[N, K]^T).
 //
 //  MODE 1  all-gather -> GEMM (column-parallel Linear): every rank holds a row shard X_r [M/W, K] and a weight shard W_r [N/W, K] and wants
-//          Y_r = [X_0; ..; X_{W-1}] W_r^T. A few CTAs of the kernel are copiers: they pull the peers' shards, 32 KiB at a time, through a
-//          shared-memory ring with bulk async copies (peer global -> smem -> local gathered buffer; no multicast) and publish a per-row-tile
-//          flag. The other CTAs run the tcgen05 GEMM: tiles over the local shard first (no waiting), then over the peers' rows in ring order,
-//          each tile's TMA producer waiting (bounded) for the row tile's flag. The transfer of row tile i+1 overlaps the math of row tile i.
+//          Y_r = [X_0; ..; X_{W-1}] W_r^T. A few CTAs of the kernel are copiers: they PUSH this rank's shard, 32 KiB at a time, through a
+//          shared-memory ring with bulk async copies (local global -> smem -> every peer's gathered buffer; posted writes, no multicast)
+//          and bump a per-row-tile counter on each peer. The other CTAs run the tcgen05 GEMM: tiles over the local shard first (no
+//          waiting), then over the peers' rows in ring order, each tile's TMA producer waiting (bounded) for the row tile's counter. The
+//          gathered buffer is double-buffered by launch parity; a pusher checks the peer's `done` flag of two launches before.
 //
 //  MODE 2  GEMM -> reduce-scatter (row-parallel Linear): every rank holds X[:, K/W slice] and W[:, K/W slice]; the partial product of each
-//          128 x 256 tile goes from TMEM through a shared-memory transpose straight into the OWNER rank's staging buffer with 16-byte peer
-//          stores (bf16), followed by a release-add on the owner's per-tile counter. Tiles are visited owner (rank+1), (rank+2), ... with the
+//          128 x 256 tile goes from TMEM through swizzled shared memory straight into the OWNER rank's staging buffer with TMA stores
+//          (bf16, peer-mapped destination), followed -- once the stores have completed -- by a release-add on the owner's tile counter. Tiles are visited owner (rank+1), (rank+2), ... with the
 //          rank's own rows last. When a CTA runs out of GEMM tiles its epilogue warps reduce the tiles this rank owns: wait (bounded) for the
 //          counter to reach 4 W, sum the W partials in fixed rank order in f32, write bf16. The staging buffer is double-buffered by the parity
 //          of the launch number; a writer checks that the owner finished the launch two before (the `done` flag) before touching a slot.
@@ -37,13 +38,18 @@ constexpr uint64_t WAIT_NS = 2000000000ull;
 constexpr int COPY_CHUNK = 32768, COPY_STAGES = 6, COPY_AHEAD = 4;      // COPY_STAGES >= COPY_AHEAD + 2
 constexpr uint32_t FT_K_TP = 7;
 
+struct StageMaps {
+  CUtensorMap m[MAXR];                    // MODE 2: tensor map of this rank's slot in every owner's staging buffer (current parity)
+};
+
 struct TpArgs {
   int rank, world;
   uint32_t seq;
   int ncopy;                              // MODE 1: number of copier CTAs (blockIdx.x < ncopy)
-  const __nv_bfloat16* x_peers[MAXR];     // MODE 1: every rank's shard [M/W, K]
-  __nv_bfloat16* xg;                      // MODE 1: local gathered buffer [M, K]
-  uint32_t* tile_ready;                   // MODE 1: local u32[M / 128], holds the seq of the launch that filled the row tile
+  int split;                              // MODE 1: copier work items per local row tile (each pushes a contiguous range of chunks)
+  const __nv_bfloat16* x_local;           // MODE 1: this rank's shard [M/W, K]
+  __nv_bfloat16* xg[MAXR];                // MODE 1: every rank's gathered buffer [2][M][K] (symmetric)
+  uint32_t* tile_cnt[MAXR];               // MODE 1: every rank's counters u32[2][M / 128] (symmetric): pushes received per row tile and parity
   __nv_bfloat16* stage[MAXR];             // MODE 2: every rank's staging buffer [2][W][M/W][N]
   uint32_t* cnt[MAXR];                    // MODE 2: every rank's counters u32[2][tiles_m_local * tiles_n]
   __nv_bfloat16* out;                     // MODE 2: local result [M/W, N]
@@ -83,7 +89,8 @@ FT_DEVICE void publish_done(const TpArgs& a) {
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAg, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmD, const TpArgs a, int M, int N, int K, uint32_t* status) {
+                  const __grid_constant__ CUtensorMap tmD, const __grid_constant__ StageMaps stage_maps, const TpArgs a, int M, int N, int K,
+                  uint32_t* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,9 +98,8 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int tiles_m = M / BM, tiles_n = (N + BN - 1) / BN, tpr = tiles_m / W;     // tpr: row tiles per rank
   const int m_loc = M / W;
 
-  if (MODE == 1 && threadIdx.x == 0 && blockIdx.x == 0) {
-    for (int q = 0; q < W; q++) st_release_sys(a.flags[q] + a.rank, a.seq);        // my shard may be read
-  }
+  const uint32_t par = a.seq & 1u;
+  const uint32_t launches_this_parity = (a.seq + 1u) >> 1;
 
   // ------------------------------------------------------------------ copier CTAs (MODE 1) ---------------------------------------------
   if (MODE == 1 && (int)blockIdx.x < a.ncopy) {
@@ -105,34 +111,48 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int nchunks = (int)((tile_bytes + COPY_CHUNK - 1) / COPY_CHUNK);
       uint32_t issued = 0;                                                         // chunks loaded so far by this CTA (ring position / parity)
       bool ok = true;
-      for (int i = blockIdx.x; i < (W - 1) * tpr && ok; i += a.ncopy) {
-        const int p = (a.rank + 1 + i / tpr) % W, t = i % tpr;
-        if (!wait_flag_ge(a.flags[a.rank] + p, a.seq, WAIT_NS)) { ft_set_status(status, FT_K_TP, 1, p); ok = false; break; }
-        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x_peers[p]) + (size_t)t * tile_bytes;
-        uint8_t* dst = reinterpret_cast<uint8_t*>(a.xg) + (size_t)(p * tpr + t) * tile_bytes;
+      // nobody may still be reading the parity slot this launch overwrites: every peer finished launch seq - 2
+      if (a.seq > 2) {
+        for (int q = 0; q < W && ok; q++) {
+          if (q == a.rank) continue;
+          if (!wait_flag_ge(a.flags[a.rank] + MAXR + q, a.seq - 2, WAIT_NS)) { ft_set_status(status, FT_K_TP, 1, q); ok = false; }
+        }
+      }
+      for (int item = blockIdx.x; item < tpr * a.split && ok; item += a.ncopy) {
+        const int t = item / a.split, part = item % a.split;
+        const int c_begin = (int)((long long)nchunks * part / a.split), c_end = (int)((long long)nchunks * (part + 1) / a.split);
+        const int n_it = c_end - c_begin;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x_local) + (size_t)t * tile_bytes;
+        const size_t dst_off = ((size_t)par * tiles_m + (size_t)(a.rank * tpr + t)) * tile_bytes;
         const uint32_t base = issued;
-        for (int c = 0; c < nchunks + COPY_AHEAD && ok; c++) {
-          if (c < nchunks) {
+        for (int c = 0; c < n_it + COPY_AHEAD && ok; c++) {
+          if (c < n_it) {
             const uint32_t g = base + c, s = g % COPY_STAGES;
-            if (g >= (uint32_t)COPY_STAGES) tma_store_wait_read<COPY_STAGES - COPY_AHEAD - 1>();   // the store that last read this stage is done with it
-            const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - (size_t)c * COPY_CHUNK);
+            if (g >= (uint32_t)COPY_STAGES) tma_store_wait_read<COPY_STAGES - COPY_AHEAD - 1>();   // the stores that last read this stage are done with it
+            const size_t off = (size_t)(c_begin + c) * COPY_CHUNK;
+            const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - off);
             mbar_expect_tx(&full[s], bytes);
-            bulk_load(smem + s * COPY_CHUNK, src + (size_t)c * COPY_CHUNK, bytes, &full[s]);
+            bulk_load(smem + s * COPY_CHUNK, src + off, bytes, &full[s]);
             issued++;
           }
           if (c >= COPY_AHEAD) {
             const int cc = c - COPY_AHEAD;
             const uint32_t g = base + cc, s = g % COPY_STAGES;
             if (!mbar_wait_deadline(&full[s], (g / COPY_STAGES) & 1)) { ft_set_status(status, FT_K_TP, 2, s); ok = false; break; }
-            const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - (size_t)cc * COPY_CHUNK);
-            bulk_store(dst + (size_t)cc * COPY_CHUNK, smem + s * COPY_CHUNK, bytes);
+            const size_t off = (size_t)(c_begin + cc) * COPY_CHUNK;
+            const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - off);
+            for (int d = 1; d < W; d++) {                                          // one posted write per peer, starting at a different peer per chunk
+              const int q = (a.rank + 1 + (d - 1 + cc) % (W - 1)) % W;
+              bulk_store(reinterpret_cast<uint8_t*>(a.xg[q]) + dst_off + off, smem + s * COPY_CHUNK, bytes);
+            }
             tma_store_commit();
           }
         }
         if (!ok) break;
-        tma_store_wait<0>();                                                       // the row tile is in local memory
-        __threadfence();
-        st_release_sys(a.tile_ready + (p * tpr + t), a.seq);
+        tma_store_wait<0>();                                                       // every peer has this item's bytes
+        __threadfence_system();
+        for (int q = 0; q < W; q++)
+          if (q != a.rank) red_release_sys_add(a.tile_cnt[q] + (size_t)par * tiles_m + (a.rank * tpr + t), 1u);
       }
       if (!ok) {
         tma_store_wait<0>();
@@ -188,7 +208,11 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int n0 = ni * BN;
         const bool remote = MODE == 1 && p != a.rank;
         if (remote) {
-          if (!wait_flag_ge(a.tile_ready + (p * tpr + tin), a.seq, WAIT_NS)) { ft_set_status(status, FT_K_TP, 3, p); ok = false; break; }
+          if (!wait_flag_ge(a.tile_cnt[a.rank] + (size_t)par * tiles_m + (p * tpr + tin), launches_this_parity * (uint32_t)a.split, WAIT_NS)) {
+            ft_set_status(status, FT_K_TP, 3, p);
+            ok = false;
+            break;
+          }
           fence_proxy_async_global();
         }
         const int a_row = (MODE == 1 && !remote) ? tin * BM : (p * tpr + tin) * BM;
@@ -236,7 +260,7 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     constexpr int CHUNKS = BN / 64;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    const uint32_t par = a.seq & 1u;
+    int pend_p = -1, pend_idx = 0;                                 // MODE 2: tile whose stores are issued but not yet announced
     for (int tile = g_id; tile < num_tiles && ok; tile += g_n) {
       int p, tin, ni;
       tile_map(tile, p, tin, ni);
@@ -256,7 +280,7 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t v[64];
         tmem_ld_32x32b_x32(t_row + c * 64, v);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, v + 32);
-        if (MODE == 1) { if (lane == 0) tma_store_wait_read<0>(); }
+        if (lane == 0) tma_store_wait_read<0>();                   // the previous store from this buffer has been read out
         __syncwarp();
         tmem_ld_wait();
         uint8_t* row = buf + lane * 128;
@@ -271,42 +295,42 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
         const int col0 = n0 + c * 64;
-        if (MODE == 1) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0 && col0 < N) tma_store_2d(&tmD, buf, col0, (p * tpr + tin) * BM + q * 32);
-          if (lane == 0) tma_store_commit();
-        } else {
-          __syncwarp();
-          // 8 lanes cover one 128-byte row segment: 4 rows per instruction, 8 instructions for the 32 rows of this warp
-          __nv_bfloat16* dst_base = a.stage[p] + (((size_t)par * W + a.rank) * m_loc + (size_t)tin * BM + q * 32) * N + col0;
-          const int sub = lane & 7;
-#pragma unroll
-          for (int it = 0; it < 8; it++) {
-            const int r = it * 4 + (lane >> 3);
-            const uint4 val = *reinterpret_cast<const uint4*>(buf + r * 128 + ((sub ^ (r & 7)) << 4));
-            if (col0 + sub * 8 < N) st_peer_v4(dst_base + (size_t)r * N + sub * 8, val);
-          }
-          __syncwarp();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col0 < N) {
+          if (MODE == 1) tma_store_2d(&tmD, buf, col0, (p * tpr + tin) * BM + q * 32);
+          else tma_store_2d(&stage_maps.m[p], buf, col0, tin * BM + q * 32);      // this rank's slot in owner p's staging buffer
         }
+        if (lane == 0) tma_store_commit();
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
-      if (MODE == 2) {
-        // release pattern: the warp barrier orders every lane's peer stores before lane 0's release-add (cumulativity), so the owner that
-        // acquires the count sees the whole 32-row slab; no per-lane system fence is needed
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(a.cnt[p] + (size_t)par * tpr * tiles_n + tin * tiles_n + ni, 1u);
+      if (MODE == 2 && lane == 0) {
+        // announce the PREVIOUS tile: its four store groups are complete once at most the four newest (this tile's) are pending
+        if (pend_p >= 0) {
+          tma_store_wait<CHUNKS>();
+          __threadfence_system();
+          red_release_sys_add(a.cnt[pend_p] + (size_t)par * tpr * tiles_n + pend_idx, 1u);
+        }
+        pend_p = p;
+        pend_idx = tin * tiles_n + ni;
       }
     }
-    if (MODE == 1 && lane == 0) tma_store_wait<0>();
+    if (lane == 0) {
+      tma_store_wait<0>();
+      if (MODE == 2 && pend_p >= 0) {
+        __threadfence_system();
+        red_release_sys_add(a.cnt[pend_p] + (size_t)par * tpr * tiles_n + pend_idx, 1u);
+      }
+    }
+    __syncwarp();
 
     if (MODE == 2 && ok) {
       // ---- reduce the tiles this rank owns: partial from rank s is at stage[rank][par][s][rows][N] ----
-      const uint32_t want = ((a.seq + 1u) >> 1) * 4u * (uint32_t)W;
+      const uint32_t want = launches_this_parity * 4u * (uint32_t)W;
       const __nv_bfloat16* mine = a.stage[a.rank] + (size_t)par * W * m_loc * N;
       const int et = threadIdx.x - 64;                              // 0..127 over the four epilogue warps
       for (int ut = g_id; ut < tpr * tiles_n; ut += g_n) {
@@ -391,10 +415,11 @@ int fill_common(TpArgs& a, int rank, int world, int64_t seq, void* const* flag_p
 FT_EXPORT int ft_tp_flag_bytes() { return 2 * MAXR * 4; }
 
 // Column-parallel forward: out[M, n_loc] = gather(x shards)[M, K] . w_loc[n_loc, K]^T.
-//   x_peers[r]: rank r's shard [M/world, K] bf16 in symmetric memory; xg: local scratch [M, K] bf16; tile_ready: local u32[M/128] zeroed once;
-//   flag_ptrs[r]: rank r's flag block; cta_done: local u64 zeroed once. M/world must be a multiple of 128, K of 8 (and tile bytes of 16).
-FT_EXPORT int ft_tp_ag_gemm(void* const* x_peers, void* xg, const void* w_loc, void* out, int M, int n_loc, int K, int rank, int world, int64_t seq,
-                            void* tile_ready, void* const* flag_ptrs, void* cta_done, int ncopy, cudaStream_t st) {
+//   x_local: this rank's shard [M/world, K] bf16; xg_ptrs[r]: rank r's gathered buffer [2][M][K] bf16 (symmetric memory);
+//   cnt_ptrs[r]: rank r's tile counters u32[2][M/128] (symmetric, zeroed once); flag_ptrs[r]: rank r's flag block; cta_done: local u64 zeroed once.
+//   M/world must be a multiple of 128, K and n_loc of 8. ncopy: copier CTAs (0 = default).
+FT_EXPORT int ft_tp_ag_gemm(const void* x_local, void* const* xg_ptrs, void* const* cnt_ptrs, const void* w_loc, void* out, int M, int n_loc, int K, int rank,
+                            int world, int64_t seq, void* const* flag_ptrs, void* cta_done, int ncopy, cudaStream_t st) {
   TpArgs a = {};
   if (int e = fill_common(a, rank, world, seq, flag_ptrs, cta_done)) return e;
   if (M < 1 || n_loc < 1 || K < 1 || (M % (BM * world)) || (K & 7) || (n_loc & 7)) return FT_ERR_ARG;
@@ -402,15 +427,21 @@ FT_EXPORT int ft_tp_ag_gemm(void* const* x_peers, void* xg, const void* w_loc, v
   FT_CUDA_TRY(cudaGetDevice(&dev));
   FT_CUDA_TRY(ft_bind_context(dev));
   if (!g_sms[dev]) FT_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
-  for (int r = 0; r < world; r++) a.x_peers[r] = (const __nv_bfloat16*)x_peers[r];
-  a.xg = (__nv_bfloat16*)xg;
-  a.tile_ready = (uint32_t*)tile_ready;
-  a.ncopy = world > 1 ? (ncopy > 0 ? ncopy : 8) : 0;
+  const int tpr = M / BM / world;
+  for (int r = 0; r < world; r++) {
+    a.xg[r] = (__nv_bfloat16*)xg_ptrs[r];
+    a.tile_cnt[r] = (uint32_t*)cnt_ptrs[r];
+  }
+  a.x_local = (const __nv_bfloat16*)x_local;
+  a.ncopy = world > 1 ? (ncopy > 0 ? ncopy : 16) : 0;
+  a.split = a.ncopy > tpr ? a.ncopy / tpr : 1;
   if (a.ncopy >= g_sms[dev]) return FT_ERR_ARG;
+  const size_t par_off = (size_t)((uint32_t)seq & 1u) * (size_t)M * K;
   CUtensorMap tA, tAg, tB, tD;
+  StageMaps sm = {};
   int r;
-  if ((r = ft_make_tmap_2d(&tA, x_peers[rank], 2, true, (uint64_t)K, (uint64_t)(M / world), (uint64_t)K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
-  if ((r = ft_make_tmap_2d(&tAg, xg, 2, true, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
+  if ((r = ft_make_tmap_2d(&tA, x_local, 2, true, (uint64_t)K, (uint64_t)(M / world), (uint64_t)K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
+  if ((r = ft_make_tmap_2d(&tAg, (const __nv_bfloat16*)xg_ptrs[rank] + par_off, 2, true, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   if ((r = ft_make_tmap_2d(&tB, w_loc, 2, true, (uint64_t)K, (uint64_t)n_loc, (uint64_t)K * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   if ((r = ft_make_tmap_2d(&tD, out, 2, true, (uint64_t)n_loc, (uint64_t)M, (uint64_t)n_loc * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   static bool configured = false;
@@ -421,7 +452,8 @@ FT_EXPORT int ft_tp_ag_gemm(void* const* x_peers, void* xg, const void* w_loc, v
   const int tiles = (M / BM) * ((n_loc + BN - 1) / BN);
   int gemm_ctas = g_sms[dev] - a.ncopy;
   if (tiles < gemm_ctas) gemm_ctas = tiles;
-  ft_tp_gemm_kernel<1><<<a.ncopy + gemm_ctas, NUM_THREADS, SMEM_BYTES, st>>>(tA, tAg, tB, tD, a, M, n_loc, K, ft_status_ptr());
+  // the grid size enters the `done` accounting, so it must not change between launches of one context: shapes are fixed per context
+  ft_tp_gemm_kernel<1><<<a.ncopy + gemm_ctas, NUM_THREADS, SMEM_BYTES, st>>>(tA, tAg, tB, tD, sm, a, M, n_loc, K, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -437,13 +469,18 @@ FT_EXPORT int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptr
   FT_CUDA_TRY(cudaGetDevice(&dev));
   FT_CUDA_TRY(ft_bind_context(dev));
   if (!g_sms[dev]) FT_CUDA_TRY(cudaDeviceGetAttribute(&g_sms[dev], cudaDevAttrMultiProcessorCount, dev));
-  for (int r = 0; r < world; r++) {
-    a.stage[r] = (__nv_bfloat16*)stage_ptrs[r];
-    a.cnt[r] = (uint32_t*)cnt_ptrs[r];
+  const size_t m_loc = (size_t)M / world;
+  const uint32_t par = (uint32_t)seq & 1u;
+  StageMaps sm = {};
+  int r;
+  for (int q = 0; q < world; q++) {
+    a.stage[q] = (__nv_bfloat16*)stage_ptrs[q];
+    a.cnt[q] = (uint32_t*)cnt_ptrs[q];
+    const __nv_bfloat16* slot = (const __nv_bfloat16*)stage_ptrs[q] + ((size_t)par * world + rank) * m_loc * N;
+    if ((r = ft_make_tmap_2d(&sm.m[q], slot, 2, true, (uint64_t)N, (uint64_t)m_loc, (uint64_t)N * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   }
   a.out = (__nv_bfloat16*)out;
   CUtensorMap tA, tB;
-  int r;
   if ((r = ft_make_tmap_2d(&tA, x, 2, true, (uint64_t)k_loc, (uint64_t)M, (uint64_t)k_loc * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   if ((r = ft_make_tmap_2d(&tB, w, 2, true, (uint64_t)k_loc, (uint64_t)N, (uint64_t)k_loc * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))) return r;
   static bool configured = false;
@@ -453,6 +490,6 @@ FT_EXPORT int ft_tp_gemm_rs(const void* x, const void* w, void* const* stage_ptr
   }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_sms[dev] ? tiles : g_sms[dev];
-  ft_tp_gemm_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tA, tA, tB, tA, a, M, N, k_loc, ft_status_ptr());
+  ft_tp_gemm_kernel<2><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tA, tA, tB, tA, sm, a, M, N, k_loc, ft_status_ptr());
   return (int)cudaGetLastError();
 }

@@ -37,8 +37,23 @@ def _as_2d_rowmajor(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+_ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4}
+
+
+def _act_torch(r: torch.Tensor, act) -> torch.Tensor:
+    F = torch.nn.functional
+    return {0: lambda t: t, 1: F.relu, 2: F.gelu, 3: lambda t: F.gelu(t, approximate="tanh"), 4: F.silu}[_ACT[act]](r)
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias: torch.Tensor | None = None,
-         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+         out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, act: str | None = None,
+         residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``D = act(A (x) B + bias) + residual``. Operands bf16 or fp16 (both the same); output in the operand dtype or f32. The epilogue order is
+    bias, activation (``relu`` / ``gelu`` / ``gelu_tanh`` / ``silu``), residual add (``residual`` is ``[M, N]`` in the output dtype)."""
+    if act not in _ACT:
+        raise InvalidArgument(f"unknown epilogue activation {act!r}")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else (a.dtype if a.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16)
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
     if K != Kb:
@@ -46,26 +61,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if not a.is_cuda or _FORCE_LIBRARY:
         A = a.t() if a_mn else a
         B = b if b_mn else b.t()
-        if a.is_cuda:
-            r = torch.matmul(A, B)
-            if bias is not None:
-                r = r + bias
-            r = r.to(out_dtype)
-        else:
-            r = torch.matmul(A.float(), B.float())
-            if bias is not None:
-                r = r + bias.float()
-            r = r.to(out_dtype)
+        r = torch.matmul(A, B).float() if a.is_cuda else torch.matmul(A.float(), B.float())
+        if bias is not None:
+            r = r + bias.float()
+        r = _act_torch(r, act)
+        if residual is not None:
+            r = r + residual.float()
+        r = r.to(out_dtype)
         if out is not None:
             out.copy_(r)
             return out
         return r
-    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
-        raise InvalidArgument("gemm expects bf16 operands on CUDA")
+    if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
+        raise InvalidArgument("gemm expects bf16 or fp16 operands of one dtype on CUDA")
+    in_f16 = a.dtype == torch.float16
     a = _as_2d_rowmajor(a)
     b = _as_2d_rowmajor(b)
     if out is None:
-        ldd_align = 8 if out_dtype == torch.bfloat16 else 4
+        ldd_align = 4 if out_dtype == torch.float32 else 8
         if N % ldd_align == 0:
             out = torch.empty((M, N), device=a.device, dtype=out_dtype)
         else:  # pad the leading dimension so each output row starts on a 16-byte boundary
@@ -75,10 +88,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out_dtype = out.dtype
         if out.stride(1) != 1:
             raise InvalidArgument("gemm out must be row-major")
-    if out_dtype not in (torch.bfloat16, torch.float32):
-        raise InvalidArgument("gemm output must be bf16 or f32")
+    if out_dtype not in (a.dtype, torch.float32):
+        raise InvalidArgument("gemm output must have the operand dtype or be f32")
     if bias is not None:
-        bias = bias.to(torch.bfloat16).contiguous()
+        bias = bias.to(a.dtype).contiguous()
+    if residual is not None:
+        if residual.shape != (M, N) or residual.dtype != out_dtype or residual.stride(1) != 1:
+            raise InvalidArgument("residual must be a row-major [M, N] tensor in the output dtype")
+    if in_f16 or act is not None and _ACT[act] or residual is not None:
+        with torch.cuda.device(a.device):
+            _lib.call("ft_gemm_ex", _lib.P(a), _lib.P(b), _lib.P(out), _lib.P(bias), _lib.P(residual), M, N, K, ctypes.c_int64(a.stride(0)), ctypes.c_int64(b.stride(0)),
+                      ctypes.c_int64(out.stride(0)), ctypes.c_int64(residual.stride(0) if residual is not None else 0), int(a_mn), int(b_mn),
+                      int(out_dtype == torch.float32), int(in_f16), _ACT[act], _lib.S())
+        return out
     splits = _auto_splits(M, N, K)
     if splits > 1:
         # few output tiles and a long K (weight gradients of 1x1 convolutions, decode): spread K over the SMs as f32 planes, then sum
@@ -151,3 +173,61 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         return _LinearFn.apply(x, w, bias)
     return torch.nn.functional.linear(x, w, bias)
+
+
+def matmul_exact(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, beta: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """f32 / f64 matrix product without operand rounding, on the FMA pipes: ``[.., M, K] @ [.., K, N]`` with one shared batch shape (or an
+    unbatched operand broadcast over the batch), either operand possibly a transposed view. ``out = alpha * a @ b + beta * out``."""
+    if a.dtype != b.dtype or a.dtype not in (torch.float32, torch.float64):
+        raise InvalidArgument("matmul_exact takes two f32 or two f64 tensors")
+    if not a.is_cuda:
+        r = torch.matmul(a, b) * alpha
+        return r if out is None else out.mul_(beta).add_(r)
+    if a.dim() < 2 or b.dim() < 2 or a.shape[-1] != b.shape[-2]:
+        raise InvalidArgument(f"matmul_exact shapes {tuple(a.shape)} x {tuple(b.shape)}")
+    batch_shape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    nb = 1
+    for s in batch_shape:
+        nb *= s
+
+    def prep(t):
+        m = t.reshape(-1, *t.shape[-2:]) if t.dim() > 2 else t[None]
+        if m.shape[0] not in (1, nb):
+            m = t.expand(*batch_shape, *t.shape[-2:]).reshape(nb, *t.shape[-2:])
+        trans = m.stride(-1) != 1 and m.stride(-2) == 1
+        if not trans and m.stride(-1) != 1:
+            m = m.contiguous()
+        return m, int(trans), (m.stride(-1) if trans else m.stride(-2)), (0 if m.shape[0] == 1 else m.stride(0))
+    am, ta, lda, sa = prep(a)
+    bm, tb_, ldb, sb = prep(b)
+    M, K, N = a.shape[-2], a.shape[-1], b.shape[-1]
+    if out is None:
+        out = torch.empty(*batch_shape, M, N, device=a.device, dtype=a.dtype)
+        beta = 0.0
+    _lib.call("ft_gemm_simt", 0 if a.dtype == torch.float32 else 3, am, bm, out, nb, M, N, K, ctypes.c_int64(max(lda, 1)), ctypes.c_int64(max(ldb, 1)),
+              ctypes.c_int64(N), ctypes.c_int64(sa), ctypes.c_int64(sb), ctypes.c_int64(M * N), ta, tb_, float(alpha), float(beta), _lib.S())
+    return out
+
+
+def mv(a: torch.Tensor, x: torch.Tensor, trans: bool = False) -> torch.Tensor:
+    """``a @ x`` (or ``a.T @ x`` with ``trans``) for a row-major f32 / f64 matrix."""
+    if not a.is_cuda or a.dtype not in (torch.float32, torch.float64):
+        return (a.t() if trans else a) @ x
+    a = a if a.stride(1) == 1 else a.contiguous()
+    y = torch.empty(a.shape[1] if trans else a.shape[0], device=a.device, dtype=a.dtype)
+    _lib.call("ft_gemv", 0 if a.dtype == torch.float32 else 3, a, x.contiguous(), y, a.shape[0], a.shape[1], ctypes.c_int64(a.stride(0)), int(trans), 1.0, 0.0, _lib.S())
+    return y
+
+
+def dot(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    return mv(x.reshape(1, -1), y.reshape(-1))[0] if x.is_cuda and x.dtype in (torch.float32, torch.float64) else torch.dot(x, y)
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Batched product: bf16 / fp16 batches run the tcgen05 GEMM per batch entry; f32 / f64 the exact strided-batched kernel."""
+    if a.dtype in (torch.float32, torch.float64) or not a.is_cuda:
+        return matmul_exact(a, b) if a.is_cuda else torch.bmm(a, b)
+    out = torch.empty(a.shape[0], a.shape[1], b.shape[2], device=a.device, dtype=a.dtype)
+    for i in range(a.shape[0]):
+        gemm(a[i], b[i], b_mn=True, out=out[i])
+    return out

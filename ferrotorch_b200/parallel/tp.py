@@ -27,7 +27,7 @@ from .symm import SymmetricBuffer
 class TpGemmContext:
     """Buffers and launch numbering of the fused kernels for one (mode, M, N, K) problem on one process group."""
 
-    def __init__(self, mode: str, M: int, N: int, K: int, device, group=None, ncopy: int = 8):
+    def __init__(self, mode: str, M: int, N: int, K: int, device, group=None, ncopy: int = 0):
         if mode not in ("ag_gemm", "gemm_rs"):
             raise InvalidArgument("mode must be ag_gemm or gemm_rs")
         self.group = group if group is not None else dist.group.WORLD
@@ -40,9 +40,9 @@ class TpGemmContext:
         self.cta_done = torch.zeros(1, device=device, dtype=torch.int64)
         self.seq = 0
         if mode == "ag_gemm":                 # N = local output features, K = input features
-            self.x_shard = SymmetricBuffer(M // W * K, torch.bfloat16, device, self.group)
-            self.xg = torch.empty(M, K, device=device, dtype=torch.bfloat16)
-            self.tile_ready = torch.zeros(M // 128, device=device, dtype=torch.int32)
+            self.x_shard = torch.empty(M // W, K, device=device, dtype=torch.bfloat16)
+            self.xg = SymmetricBuffer(2 * M * K, torch.bfloat16, device, self.group)          # peers push into it, double-buffered by parity
+            self.tile_cnt = SymmetricBuffer(2 * (M // 128), torch.int32, device, self.group, zero=True)
         else:                                 # N = output features, K = local input features
             tiles = (M // W // 128) * ((N + 255) // 256)
             self.stage = SymmetricBuffer(2 * M * N, torch.bfloat16, device, self.group)
@@ -51,17 +51,18 @@ class TpGemmContext:
         dist.barrier(self.group)              # every rank's flags / counters are zero before anybody signals
 
     def shard_view(self) -> torch.Tensor:
-        """This rank's ``[M / W, K]`` input shard inside symmetric memory; producers write here (or use :meth:`ag_gemm` with a tensor to copy)."""
-        return self.x_shard.tensor.view(self.M // self.world, self.K)
+        """A persistent ``[M / W, K]`` buffer for this rank's input shard (any contiguous bf16 tensor can be passed to :meth:`ag_gemm` instead)."""
+        return self.x_shard
 
     def ag_gemm(self, x_shard: Optional[torch.Tensor], w_loc: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if x_shard is not None:
-            self.shard_view().copy_(x_shard)
+        x = self.x_shard if x_shard is None else x_shard.contiguous()
+        if x.shape != (self.M // self.world, self.K) or x.dtype != torch.bfloat16:
+            raise InvalidArgument("input shard must be bf16 [M / world, K]")
         if out is None:
             out = torch.empty(self.M, self.N, device=self.device, dtype=torch.bfloat16)
         self.seq += 1
-        _lib.call("ft_tp_ag_gemm", self.x_shard.ptr_array(), self.xg, w_loc, out, self.M, self.N, self.K, self.rank, self.world, self.seq,
-                  self.tile_ready, self.flags.ptr_array(), self.cta_done, self.ncopy, _lib.S())
+        _lib.call("ft_tp_ag_gemm", x, self.xg.ptr_array(), self.tile_cnt.ptr_array(), w_loc, out, self.M, self.N, self.K, self.rank, self.world, self.seq,
+                  self.flags.ptr_array(), self.cta_done, self.ncopy, _lib.S())
         return out
 
     def gemm_rs(self, x: torch.Tensor, w_loc: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -68,3 +68,43 @@ def test_linear_autograd_matches_reference():
     for got, ref in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad), (bias.grad, br.grad)):
         rel = (got.float() - ref).norm() / (ref.norm() + 1e-6)
         assert rel.item() < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("act", [None, "relu", "gelu", "gelu_tanh", "silu"])
+def test_gemm_epilogue_activation_residual_and_fp16(dtype, act):
+    from ferrotorch_b200 import ops
+    import torch.nn.functional as F
+    g = torch.Generator(device="cuda").manual_seed(0)
+    M, N, K = 300, 520, 264
+    a, b = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(dtype), (torch.randn(N, K, device="cuda", generator=g) * 0.5).to(dtype)
+    bias, res = torch.randn(N, device="cuda", generator=g).to(dtype), torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    out = ops.gemm(a, b, bias=bias, act=act, residual=res)
+    ref = a.float() @ b.float().t() + bias.float()
+    ref = {None: lambda t: t, "relu": F.relu, "gelu": F.gelu, "gelu_tanh": lambda t: F.gelu(t, approximate="tanh"), "silu": F.silu}[act](ref) + res.float()
+    assert out.dtype == dtype and (out.float() - ref).abs().max() < (0.08 if dtype == torch.bfloat16 else 0.02)
+    o32 = ops.gemm(a, b, act=act, out_dtype=torch.float32, residual=res.float())
+    ref32 = {None: lambda t: t, "relu": F.relu, "gelu": F.gelu, "gelu_tanh": lambda t: F.gelu(t, approximate="tanh"), "silu": F.silu}[act](a.float() @ b.float().t()) + res.float()
+    assert (o32 - ref32).abs().max() < 2e-3
+
+
+def test_exact_gemm_gemv_and_split_k_path():
+    from ferrotorch_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for dtype, tol in ((torch.float32, 2e-4), (torch.float64, 1e-11)):
+        a, b = torch.randn(3, 70, 45, device="cuda", generator=g).to(dtype), torch.randn(3, 45, 90, device="cuda", generator=g).to(dtype)
+        assert (ops.matmul_exact(a, b) - a @ b).abs().max() < tol
+        assert (ops.matmul_exact(a.transpose(1, 2).contiguous().transpose(1, 2), b.transpose(1, 2).contiguous().transpose(1, 2)) - a @ b).abs().max() < tol
+        assert (ops.matmul_exact(a[0], b) - a[0] @ b).abs().max() < tol                       # broadcast over the batch
+        m, x = torch.randn(77, 130, device="cuda", generator=g).to(dtype), torch.randn(130, device="cuda", generator=g).to(dtype)
+        assert (ops.mv(m, x) - m @ x).abs().max() < tol * 10 and (ops.mv(m, torch.ones(77, device="cuda", dtype=dtype), trans=True) - m.sum(0)).abs().max() < tol * 10
+        assert abs(float(ops.dot(x, x)) - float((x * x).sum())) < tol * 100
+    # weight-gradient shape: tiny output, very long K -> split over the SMs
+    dy, x = (torch.randn(200_000, 64, device="cuda", generator=g) * 0.1).bfloat16(), (torch.randn(200_000, 256, device="cuda", generator=g) * 0.1).bfloat16()
+    from ferrotorch_b200.ops.gemm import _auto_splits
+    assert _auto_splits(64, 256, 200_000) > 1
+    dw = ops.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    ref = dy.float().t() @ x.float()
+    assert (dw - ref).abs().max() < 0.05 * ref.abs().max().clamp_min(1)
+    bb = ops.bmm(torch.randn(4, 128, 64, device="cuda", generator=g).bfloat16(), torch.randn(4, 64, 96, device="cuda", generator=g).bfloat16())
+    assert bb.shape == (4, 128, 96)
