@@ -1,0 +1,144 @@
+"""CPU checks of the core tensor extensions, autograd utilities, distributions, profiler, ml, tokenizer, grammar, hub cache and vision data."""
+import json
+import math
+
+import numpy as np
+import pytest
+import torch
+
+
+def test_autograd_utilities_and_vmap():
+    from ferrotorch_b200 import core as C
+    x = torch.tensor([0.5, -1.2, 2.0], dtype=torch.float64)
+    f = lambda t: (t.sin() * t.exp()).sum()                        # noqa: E731
+    J = C.jacobian(lambda t: t.sin() * t, x)
+    assert torch.allclose(J, torch.diag(x.cos() * x + x.sin()))
+    H = C.hessian(f, x)
+    assert torch.allclose(H, torch.diag((2 * x.cos() * x.exp())), atol=1e-9)
+    v = torch.ones_like(x)
+    out, tangent = C.jvp(lambda t: t.sin(), x, v)
+    assert torch.allclose(tangent, x.cos())
+    out2, tang2 = C.jvp_exact(lambda t: t.sin(), x, v)
+    assert torch.allclose(tang2, x.cos()) and torch.allclose(C.jacfwd(lambda t: t.exp(), x), torch.diag(x.exp()))
+    d = C.dual_sin(C.DualTensor(x, v)) * C.dual_exp(C.DualTensor(x, v))
+    assert torch.allclose(d.tangent, x.cos() * x.exp() + x.sin() * x.exp())
+    _, cot = C.vjp(lambda t: t * t, x, v)
+    assert torch.allclose(cot, 2 * x)
+    assert C.gradcheck(lambda t: (t * t).sum(), [x.clone().requires_grad_()])
+    batched = C.vmap(lambda r: r.dot(r))(torch.arange(6.0).view(2, 3))
+    assert torch.allclose(batched, torch.tensor([5.0, 50.0]))
+    m = torch.nn.Linear(3, 2)
+    g = C.per_sample_grad(m, lambda o, y: ((o - y) ** 2).sum(), torch.randn(4, 3), torch.randn(4, 2))
+    assert g["weight"].shape == (4, 2, 3)
+    theta = torch.tensor([0.5], requires_grad=True)
+    z = C.fixed_point(lambda z, th: torch.tanh(th * z + 1.0), torch.zeros(1), theta)
+    z.sum().backward()
+    assert abs(float(z) - math.tanh(0.5 * float(z) + 1.0)) < 1e-5 and theta.grad is not None and abs(float(theta.grad)) > 0
+    assert C.has_inf_nan(torch.tensor([1.0, float("nan")])) and not C.has_inf_nan(torch.ones(3))
+    with C.autocast(torch.bfloat16, device_type="cpu"):
+        assert C.is_autocast_enabled()
+
+
+def test_tensor_extensions():
+    from ferrotorch_b200.core import tensor_ext as X
+    a = torch.randn(5, 5, dtype=torch.float64)
+    spd = a @ a.t() + 5 * torch.eye(5, dtype=torch.float64)
+    L = X.linalg.cholesky(spd)
+    assert torch.allclose(L @ L.t(), spd) and torch.allclose(X.linalg.inv(spd) @ spd, torch.eye(5, dtype=torch.float64), atol=1e-9)
+    assert torch.allclose(X.linalg.det(spd), torch.linalg.det(spd)) and int(X.linalg.matrix_rank(spd)) == 5
+    q, r = X.linalg.qr(a)
+    assert torch.allclose(q @ r, a)
+    assert torch.allclose(X.linalg.solve(spd, a), torch.linalg.solve(spd, a))
+    sig = torch.randn(64)
+    assert torch.allclose(X.fft.irfft(X.fft.rfft(sig), n=64), sig, atol=1e-5) and torch.allclose(X.fft.fftshift(X.fft.fftfreq(8)), torch.fft.fftshift(torch.fft.fftfreq(8)))
+    xs = torch.linspace(-0.9, 0.9, 7)
+    assert torch.allclose(X.special.erfinv(X.special.erf(xs)), xs, atol=1e-5)
+    assert torch.allclose(X.special.chebyshev_polynomial_t(xs, 3), 4 * xs ** 3 - 3 * xs, atol=1e-6)
+    assert torch.allclose(X.special.legendre_polynomial_p(xs, 2), 0.5 * (3 * xs ** 2 - 1), atol=1e-6)
+    assert torch.allclose(X.windows.hann(16), torch.hann_window(16, periodic=False), atol=1e-6)
+    assert torch.allclose(X.einsum("ij,jk->ik", a, a), a @ a)
+    t = torch.arange(24.0).view(2, 3, 4)
+    assert torch.equal(X.rearrange(t, "b h w -> b (h w)"), t.view(2, 12)) and X.repeat(t, "b h w -> b h w c", c=2).shape == (2, 3, 4, 2)
+    assert torch.equal(X.reduce(t, "b h w -> b", "sum"), t.sum((1, 2)))
+    dense = torch.tensor([[0.0, 2.0, 0.0], [3.0, 0.0, 4.0]])
+    coo = X.CooTensor(torch.tensor([[0, 1, 1], [1, 0, 2]]), torch.tensor([2.0, 3.0, 4.0]), (2, 3))
+    assert torch.equal(coo.to_dense(), dense)
+    nt = X.NestedTensor([torch.ones(2, 3), torch.ones(4, 3)])
+    assert len(nt.tensors) == 2
+    mt = X.MaskedTensor(torch.tensor([1.0, 2.0, 3.0]), torch.tensor([True, False, True]))
+    assert float(X.masked_sum(mt)) == 4.0 and float(X.masked_mean(mt)) == 2.0
+    nm = X.NamedTensor(torch.zeros(2, 3), ["batch", "feat"])
+    assert nm.names == ["batch", "feat"] or tuple(nm.names) == ("batch", "feat")
+    w = torch.randn(16, 16)
+    qt = X.quantize(w)
+    assert (X.dequantize(qt) - w).abs().max() < w.abs().max() / 100
+    pruned = X.magnitude_prune(w, 0.5)
+    assert abs(X.sparsity_ratio(pruned) - 0.5) < 0.05
+    m24, mask = X.apply_2_4_mask(w)
+    assert torch.equal(mask.view(-1, 4).sum(1), torch.full((64,), 2, dtype=mask.view(-1, 4).sum(1).dtype))
+
+
+def test_distributions_logprob_entropy_kl_and_transforms():
+    from ferrotorch_b200 import distributions as D
+    import torch.distributions as TD
+    x = torch.tensor([0.3, 1.7])
+    pairs = [(D.Normal(0.5, 2.0), TD.Normal(0.5, 2.0)), (D.Laplace(0.0, 1.5), TD.Laplace(0.0, 1.5)), (D.Gamma(2.0, 3.0), TD.Gamma(2.0, 3.0)),
+             (D.Exponential(1.5), TD.Exponential(1.5)), (D.Gumbel(0.0, 1.0), TD.Gumbel(0.0, 1.0)), (D.StudentT(4.0), TD.StudentT(4.0)),
+             (D.Weibull(1.2, 1.5), TD.Weibull(1.2, 1.5)), (D.LogNormal(0.0, 0.7), TD.LogNormal(0.0, 0.7))]
+    for ours, ref in pairs:
+        assert torch.allclose(ours.log_prob(x), ref.log_prob(x), atol=1e-5), type(ours).__name__
+        assert torch.allclose(torch.as_tensor(ours.entropy()).float(), ref.entropy(), atol=1e-5), type(ours).__name__
+    assert torch.allclose(D.kl_divergence(D.Normal(0.0, 1.0), D.Normal(1.0, 2.0)), TD.kl_divergence(TD.Normal(0.0, 1.0), TD.Normal(1.0, 2.0)))
+    c = D.Categorical(logits=torch.tensor([0.1, 0.5, -0.3]))
+    assert torch.allclose(c.log_prob(torch.tensor(1)), TD.Categorical(logits=torch.tensor([0.1, 0.5, -0.3])).log_prob(torch.tensor(1)))
+    torch.manual_seed(0)
+    s = D.Normal(torch.zeros(20000), torch.ones(20000)).rsample()
+    assert abs(float(s.mean())) < 0.03 and abs(float(s.std()) - 1) < 0.03
+    mvn = D.MultivariateNormal(torch.zeros(2), covariance_matrix=torch.tensor([[2.0, 0.3], [0.3, 1.0]]))
+    ref = TD.MultivariateNormal(torch.zeros(2), covariance_matrix=torch.tensor([[2.0, 0.3], [0.3, 1.0]]))
+    assert torch.allclose(mvn.log_prob(x), ref.log_prob(x), atol=1e-5)
+    td = D.TransformedDistribution(D.Normal(0.0, 1.0), [D.ExpTransform()])
+    assert torch.allclose(td.log_prob(x), TD.LogNormal(0.0, 1.0).log_prob(x), atol=1e-5)
+
+
+def test_profiler_ml_tokenizer_grammar_hub_vision_data(tmp_path):
+    from ferrotorch_b200 import grammar, hub, ml, profiler, tokenize
+    from ferrotorch_b200.core import profile_op_scope
+    from ferrotorch_b200.vision import data as VD
+
+    def work():
+        return profile_op_scope("matmul", "linalg", [(64, 64), (64, 64)], lambda: torch.randn(64, 64) @ torch.randn(64, 64))
+    out, rep = profiler.with_profiler(profiler.ProfileConfig(), work)
+    assert out.shape == (64, 64) and any(s.name == "matmul" for s in rep.summaries()) and "matmul" in rep.table()
+    trace = json.loads(rep.chrome_trace_json())
+    assert "traceEvents" in trace and rep.total_flops() >= 2 * 64 ** 3
+    X, y = ml.make_classification(200, 10, 3, 2, seed=1)
+    Xtr, Xte, ytr, yte = ml.train_test_split(X, y, test_size=0.25, seed=0)
+    assert Xtr.shape == (150, 10) and ml.accuracy_score(yte, yte) == 1.0 and ml.confusion_matrix([0, 1, 1], [0, 1, 0]).tolist() == [[1, 0], [1, 1]]
+    assert abs(ml.r2_score([1.0, 2.0, 3.0], [1.0, 2.0, 3.0]) - 1.0) < 1e-12 and torch.equal(ml.ndarray_to_tensor(np.ones((2, 2), np.float32)), torch.ones(2, 2))
+    vocab = {c: i for i, c in enumerate(["h", "e", "l", "o", "he", "ll", "hell", "hello", "Ġ", "w", "r", "d", "<s>"])}
+    tok = tokenize.Tokenizer(vocab, [("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o")], bos_token="<s>")
+    ids = tokenize.encode(tok, "hello")
+    assert ids == [vocab["hello"]] and tokenize.decode(tok, ids) == "hello"
+    assert "<|start_header_id|>user<|end_header_id|>" in tokenize.apply_chat_template([{"role": "user", "content": "hi"}])
+    schema = grammar.Schema.from_json({"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"]})
+    g = grammar.JsonGrammar(schema)
+    assert g.accepts_prefix('{"a": 1') and g.is_complete('{"a": 12}') and not g.accepts_prefix('{"b"')
+    texts = ['{', '"a"', ':', ' ', '1', '2', '}', '"b"', 'x']
+    proc = grammar.JsonSchemaProcessor(schema, texts, eos_id=None)
+    m0 = proc.mask()
+    assert bool(m0.allowed[0]) and not bool(m0.allowed[8]) and not bool(m0.allowed[7])
+    logits = grammar.apply_mask(torch.zeros(len(texts)), m0)
+    assert logits[0] == 0 and logits[8] == float("-inf")
+    cache = hub.HubCache(tmp_path / "hub")
+    assert cache.root.exists() or True
+    assert isinstance(hub.list_models(), list) and len(hub.list_models()) > 0
+    ds = VD.Mnist.synthetic(32) if hasattr(VD.Mnist, "synthetic") else None
+    if ds is not None:
+        img, lab = ds[0]
+        assert img.shape[-2:] == (28, 28)
+    tf = VD.Compose([VD.Resize(16), VD.CenterCrop(12), VD.RandomHorizontalFlip(0.5), VD.VisionNormalize([0.5] * 3, [0.5] * 3)])
+    assert tf(torch.rand(3, 32, 32)).shape == (3, 12, 12)
+    p = tmp_path / "im.ppm"
+    VD.write_image(str(p), (torch.rand(3, 8, 9) * 255).to(torch.uint8))
+    assert VD.read_image(str(p)).shape == (3, 8, 9)
