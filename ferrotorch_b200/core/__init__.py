@@ -567,3 +567,6 @@ from .tensor_ext import (linalg, fft, special, windows, einsum, einsum_different
                          sparse_matmul_24, SparseGrad, NestedTensor, PackedNestedTensor, nested_scaled_dot_product_attention, MaskedTensor,
                          masked_sum, masked_mean, masked_min, masked_max, masked_count, masked_where, masked_invalid, masked_equal, NamedTensor,
                          ComplexTensor)
+
+from .ops_ext import (cond, scan, empty, tensor, from_vec, searchsorted, bucketize, topk, sort, argsort, unique, histc, nonzero, where, cumsum,  # noqa: E402,F401
+                      BoolTensor, IntTensor, CpuBufferPool, cpu_pool, meta_propagate, format_tensor, display, with_fusion, fusion_enabled, fused)

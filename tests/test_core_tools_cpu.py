@@ -142,3 +142,34 @@ def test_profiler_ml_tokenizer_grammar_hub_vision_data(tmp_path):
     p = tmp_path / "im.ppm"
     VD.write_image(str(p), (torch.rand(3, 8, 9) * 255).to(torch.uint8))
     assert VD.read_image(str(p)).shape == (3, 8, 9)
+
+
+def test_control_flow_search_wrappers_pool_meta_display_fusion():
+    from ferrotorch_b200 import core as C
+    x = torch.arange(1.0, 5.0, requires_grad=True)
+    carry, ys = C.scan(lambda c, xt: (c * xt, c * xt), torch.tensor(1.0), x)
+    ys[-1].backward()
+    assert float(carry) == 24.0 and torch.allclose(x.grad, 24.0 / x.detach())
+    _, rev = C.scan(lambda c, xt: (c + xt, c + xt), torch.tensor(0.0), x.detach(), reverse=True)
+    assert rev.tolist() == [10.0, 9.0, 7.0, 4.0]
+    assert C.cond(False, lambda a: a + 1, lambda a: a - 1, (torch.zeros(1),)).item() == -1
+    assert C.meta_propagate(lambda a, b: (a @ b).sum(0), ((4, 8), torch.float32), ((8, 3), torch.float32)) == [((3,), torch.float32)]
+    assert C.format_tensor(torch.tensor([1.5, 2.0])) == "tensor([1.5000, 2.0000], shape=[2], dtype=float32, device=cpu)"
+    assert "..." in C.format_tensor(torch.zeros(5000))
+    pool = C.CpuBufferPool()
+    t = pool.take(100)
+    pool.give(t)
+    assert pool.take(120).shape == (120,) and pool.stats()["hits"] == 1
+    f = C.fused(lambda a, b: torch.tanh(a) * b + 1)
+    a, b = torch.randn(4, 8), torch.randn(4, 8)
+    with C.with_fusion():
+        assert C.fusion_enabled() and torch.allclose(f(a, b), torch.tanh(a) * b + 1, atol=1e-6)
+    assert not C.fusion_enabled()
+    assert (C.IntTensor([1, 2, 3]) * 2 == C.IntTensor([2, 4, 7])).data.tolist() == [True, True, False]
+    with pytest.raises(Exception):
+        C.IntTensor([1.5])
+    assert (C.BoolTensor([1, 0, 1]) & ~C.BoolTensor([1, 1, 0])).data.tolist() == [False, False, True]
+    assert C.searchsorted(torch.tensor([1.0, 3.0, 5.0]), torch.tensor([2.0, 5.0])).tolist() == [1, 2]
+    assert C.from_vec([1, 2, 3, 4], (2, 2)).shape == (2, 2)
+    with pytest.raises(Exception):
+        C.from_vec([1, 2, 3], (2, 2))
