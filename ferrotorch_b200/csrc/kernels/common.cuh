@@ -264,6 +264,14 @@ FT_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::
 FT_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its predecessor is still running;
+// pdl_wait() blocks until the predecessor has completed and its writes are visible (it returns at once in an ordinary launch), and
+// pdl_launch_dependents() lets the successor's CTAs be scheduled early (they stop at their own pdl_wait).
+// ---------------------------------------------------------------------------
+FT_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+FT_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // cross-GPU signalling on peer-mapped memory (plain loads/stores, system scope)
 // ---------------------------------------------------------------------------
 FT_DEVICE void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }

@@ -37,6 +37,8 @@ FT_DEVICE float plane_sum(const float* __restrict__ p, int splits, size_t plane_
 template <typename OutT>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int rows, int N, int64_t ldp, size_t plane_stride,
                                      const __nv_bfloat16* __restrict__ bias, OutT* __restrict__ out, int64_t ldo) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t total = (size_t)rows * N;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / N), n = (int)(i % N);
@@ -55,6 +57,8 @@ __global__ void qkv_rope_kvwrite_kernel(const float* __restrict__ partial, int s
                                         const float* __restrict__ sin_t, __nv_bfloat16* __restrict__ q_out,
                                         __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                         const int* __restrict__ block_table, int max_blocks) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, i = threadIdx.x, half = D >> 1;
   const int pos = positions[b];
   const size_t base = (size_t)b * ldp + (size_t)h * D;
@@ -134,6 +138,8 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloa
                                                                 int max_blocks, const int* __restrict__ seq_lens, int Hq, int Hkv, float scale,
                                                                 float* __restrict__ ws, int* __restrict__ counters,
                                                                 __nv_bfloat16* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int D = 128;
   extern __shared__ __align__(128) uint8_t pa_smem[];
   const int G = Hq / Hkv;
@@ -335,6 +341,8 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloa
 // ------------------------------------------------------------------------------------------------------------
 __global__ void decode_swiglu_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride, int rows, int F,
                                      __nv_bfloat16* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t total = (size_t)rows * F;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / F), f = (int)(i % F);
@@ -380,6 +388,8 @@ __global__ void __launch_bounds__(256) decode_ar_residual_norm_kernel(const floa
                                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h,
                                                                       float* __restrict__ sumsq, int rows, int rows_pad, int d, int chunks, float eps,
                                                                       uint32_t* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float red[32];
   const int row = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
   const int cols = d / chunks, c0 = chunk * cols;
@@ -437,9 +447,8 @@ FT_EXPORT int ft_splitk_reduce(const float* partial, int splits, int rows, int N
                                int64_t ldo, int out_f32, cudaStream_t st) {
   if (splits < 1 || rows < 1 || N < 1) return FT_ERR_ARG;
   const int grid = small_grid((size_t)rows * N, 256);
-  if (out_f32) splitk_reduce_kernel<float><<<grid, 256, 0, st>>>(partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (float*)out, ldo);
-  else splitk_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, ldo);
-  return (int)cudaGetLastError();
+  if (out_f32) return (int)ft_launch_pdl(splitk_reduce_kernel<float>, dim3(grid), dim3(256), 0, st, partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (float*)out, ldo);
+  return (int)ft_launch_pdl(splitk_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, partial, splits, rows, N, ldp, (size_t)plane_stride, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, ldo);
 }
 
 // positions[b] = index of the token being decoded in sequence b; caches are [num_blocks, 16, Hkv, D] bf16.
@@ -447,10 +456,8 @@ FT_EXPORT int ft_decode_qkv_rope_kvwrite(const float* partial, int splits, int64
                                          const int* positions, const float* cos_t, const float* sin_t, void* q_out, void* k_cache,
                                          void* v_cache, const int* block_table, int max_blocks, cudaStream_t st) {
   if (B < 1 || D % 2 || D / 2 > 1024) return FT_ERR_ARG;
-  qkv_rope_kvwrite_kernel<<<dim3(B, Hq + 2 * Hkv), D / 2, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, Hq, Hkv, D, positions, cos_t, sin_t,
-                                                                  (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-                                                                  block_table, max_blocks);
-  return (int)cudaGetLastError();
+  return (int)ft_launch_pdl(qkv_rope_kvwrite_kernel, dim3(B, Hq + 2 * Hkv), dim3(D / 2), 0, st, partial, splits, ldp, (size_t)plane_stride, Hq, Hkv, D, positions,
+                            cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, block_table, max_blocks);
 }
 
 FT_EXPORT int ft_paged_kv_write(const void* qkv, int64_t ld, int B, int S, int Hq, int Hkv, int D, void* k_cache, void* v_cache,
@@ -476,16 +483,14 @@ FT_EXPORT int ft_paged_attn_decode(const void* q, const void* k_cache, const voi
     if (e != cudaSuccess) return (int)e;
     attr_set[dev] = true;
   }
-  paged_attn_decode_kernel<<<dim3(nsplit, Hkv, B), 128, PA_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                                                       block_table, max_blocks, seq_lens, Hq, Hkv, scale, ws, counters,
-                                                                       (__nv_bfloat16*)out);
-  return (int)cudaGetLastError();
+  return (int)ft_launch_pdl(paged_attn_decode_kernel, dim3(nsplit, Hkv, B), dim3(128), (size_t)PA_SMEM, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache,
+                            (const __nv_bfloat16*)v_cache, block_table, max_blocks, seq_lens, Hq, Hkv, scale, ws, counters, (__nv_bfloat16*)out);
 }
 
 FT_EXPORT int ft_decode_swiglu(const float* partial, int splits, int64_t ldp, int64_t plane_stride, int rows, int F, void* out, cudaStream_t st) {
   if (rows < 1 || F < 1) return FT_ERR_ARG;
-  decode_swiglu_kernel<<<small_grid((size_t)rows * F, 256), 256, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, rows, F, (__nv_bfloat16*)out);
-  return (int)cudaGetLastError();
+  return (int)ft_launch_pdl(decode_swiglu_kernel, dim3(small_grid((size_t)rows * F, 256)), dim3(256), 0, st, partial, splits, ldp, (size_t)plane_stride, rows, F,
+                            (__nv_bfloat16*)out);
 }
 
 // sym_ptrs / flag_ptrs: `world` mappings of every rank's staging buffer (2 * rows_pad * d floats) and flag block (u32[8], zeroed once).
@@ -499,8 +504,6 @@ FT_EXPORT int ft_decode_ar_residual_norm(const float* partial, int splits, int64
   for (int i = 0; i < MAXR; i++) { a.sym[i] = i < world ? (float*)sym_ptrs[i] : nullptr; a.flags[i] = i < world ? (uint32_t*)flag_ptrs[i] : nullptr; }
   a.rank = rank;
   a.world = world;
-  decode_ar_residual_norm_kernel<<<rows * chunks, 256, 0, st>>>(partial, splits, ldp, (size_t)plane_stride, a, sync, (__nv_bfloat16*)x,
-                                                              (const __nv_bfloat16*)w, (__nv_bfloat16*)h, sumsq, rows, rows_pad, d, chunks, eps,
-                                                              ft_status_ptr());
-  return (int)cudaGetLastError();
+  return (int)ft_launch_pdl(decode_ar_residual_norm_kernel, dim3(rows * chunks), dim3(256), 0, st, partial, splits, ldp, (size_t)plane_stride, a, sync,
+                            (__nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)h, sumsq, rows, rows_pad, d, chunks, eps, ft_status_ptr());
 }

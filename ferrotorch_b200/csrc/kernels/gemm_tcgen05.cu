@@ -115,6 +115,9 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared memory and TMEM; from here on the kernel reads what its predecessor wrote
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -319,9 +322,8 @@ int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, 
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                  k_splits, ft_status_ptr(), epi);
-  return (int)cudaGetLastError();
+  return (int)ft_launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream, tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
+                            k_splits, ft_status_ptr(), epi);
 }
 
 int g_num_sms[64] = {0};

@@ -101,3 +101,12 @@ FT_EXPORT int ft_status_read_clear(uint32_t* out) {
 }
 
 FT_EXPORT int ft_abi_version() { return 1; }
+
+static bool g_pdl = false;
+bool ft_pdl_enabled() { return g_pdl; }
+// Switch programmatic dependent launch on or off for the kernels that support it (the decode path). Returns the previous setting.
+FT_EXPORT int ft_set_pdl(int enabled) {
+  const int prev = g_pdl ? 1 : 0;
+  g_pdl = enabled != 0;
+  return prev;
+}

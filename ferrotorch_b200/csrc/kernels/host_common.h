@@ -51,3 +51,23 @@ cudaError_t ft_bind_context(int dev);
 
 // Per-device status word in device memory (lazily allocated, zeroed).
 uint32_t* ft_status_ptr();
+
+// Launch with the programmatic-stream-serialization attribute when programmatic dependent launch is switched on (ft_set_pdl), else an ordinary
+// launch. Only kernels that call pdl_wait() before touching memory a predecessor may still be writing (or reading) go through this.
+bool ft_pdl_enabled();
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t ft_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ft_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif

@@ -220,6 +220,17 @@ class LlamaTPEngine:
         self.tokens.copy_(allv[best, torch.arange(self.B, device=self.dev), 1].long())
 
     def _decode_body(self) -> None:
+        """One decode step. The step's kernels are launched as programmatic dependents (each waits on the device for its predecessor before
+        touching memory, but is scheduled while the predecessor drains), which hides the launch gaps between the ~9 small kernels of a layer.
+        ``FT_DECODE_PDL=0`` switches to ordinary launches."""
+        import os
+        prev = _lib.kernels().ft_set_pdl(int(os.environ.get("FT_DECODE_PDL", "1") != "0"))
+        try:
+            self._decode_body_inner()
+        finally:
+            _lib.kernels().ft_set_pdl(prev)
+
+    def _decode_body_inner(self) -> None:
         cfg, B = self.cfg, self.B
         self.x[:B] = self.embed[self.tokens]
         _lib.call("ft_rmsnorm_fwd", self.x, None, self.layers[0]["n1"], self.h, None, None, B, self.d, float(cfg.rms_norm_eps), _lib.S())
