@@ -12,3 +12,5 @@ from . import attention
 __all__ = [n for n in dir() if not n.startswith("_")]
 from . import tensor_ops  # noqa: E402
 from . import nn_ops  # noqa: E402
+from . import conv  # noqa: E402
+from .conv import conv3x3, conv3x3_nhwc_raw  # noqa: E402

@@ -1,0 +1,73 @@
+"""3x3 convolution (stride 1, padding 1) on the implicit-GEMM tcgen05 kernel, channels-last bf16, with autograd.
+
+Forward and data gradient run on ``ft_conv3x3_nhwc`` (the data gradient is the same convolution with the weights flipped and their channel axes
+swapped); the weight gradient is evaluated by the library routine (``torch.nn.grad.conv2d_weight``) until its tcgen05 kernel lands.
+``FT_CONV_BACKEND=cudnn`` forces the library path everywhere (A/B switch).
+
+Reference parity: ferrotorch-nn/src/conv.rs:261 (Conv2d; CUDA forward :584-597, host backward :888-903), ferrotorch-gpu/src/conv.rs:504.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from .. import _lib
+from ..errors import InvalidArgument
+
+_FORCE_LIBRARY = os.environ.get("FT_CONV_BACKEND", "") == "cudnn"
+
+
+def conv3x3_eligible(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, groups) -> bool:
+    as2 = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)          # noqa: E731
+    return (not _FORCE_LIBRARY and x.is_cuda and x.dim() == 4 and x.dtype == torch.bfloat16 and weight.shape[-2:] == (3, 3) and as2(stride) == (1, 1)
+            and as2(padding) == (1, 1) and as2(dilation) == (1, 1) and groups == 1 and x.shape[1] % 64 == 0 and weight.shape[0] % 8 == 0
+            and x.is_contiguous(memory_format=torch.channels_last))
+
+
+def _krsc(weight: torch.Tensor) -> torch.Tensor:
+    """[Cout, Cin, 3, 3] (any memory format) -> dense bf16 [Cout, 3, 3, Cin]."""
+    return weight.to(torch.bfloat16).permute(0, 2, 3, 1).contiguous()
+
+
+def conv3x3_nhwc_raw(x: torch.Tensor, w_krsc: torch.Tensor, relu: bool = False) -> torch.Tensor:
+    """``x``: channels_last ``[N, Cin, H, W]`` bf16; ``w_krsc``: dense ``[Cout, 3, 3, Cin]`` bf16. Returns channels_last ``[N, Cout, H, W]``."""
+    N, Cin, H, W = x.shape
+    Cout = w_krsc.shape[0]
+    if w_krsc.shape != (Cout, 3, 3, Cin) or not w_krsc.is_contiguous():
+        raise InvalidArgument("weights must be dense [Cout, 3, 3, Cin]")
+    y = torch.empty((N, Cout, H, W), device=x.device, dtype=torch.bfloat16, memory_format=torch.channels_last)
+    with torch.cuda.device(x.device):
+        _lib.call("ft_conv3x3_nhwc", x, w_krsc, y, N, H, W, Cin, Cout, int(relu), _lib.S())
+    return y
+
+
+class _Conv3x3Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight):
+        wk = _krsc(weight)
+        ctx.save_for_backward(x, weight)
+        return conv3x3_nhwc_raw(x, wk)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            if dy.shape[1] % 64 == 0 and x.shape[1] % 8 == 0:
+                # W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci]
+                wt = weight.to(torch.bfloat16).permute(1, 2, 3, 0).flip(1, 2).contiguous()
+                dx = conv3x3_nhwc_raw(dy, wt)
+            else:
+                dx = torch.nn.grad.conv2d_input(x.shape, weight.to(dy.dtype), dy, padding=1)
+        if ctx.needs_input_grad[1]:
+            dw = torch.nn.grad.conv2d_weight(x, weight.shape, dy, padding=1).to(weight.dtype)
+        return dx, dw
+
+
+def conv3x3(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Differentiable 3x3 / stride 1 / padding 1 convolution of a channels-last bf16 activation with ``weight [Cout, Cin, 3, 3]``."""
+    if not conv3x3_eligible(x, weight, 1, 1, 1, 1):
+        raise InvalidArgument("conv3x3 needs a channels_last CUDA bf16 input with Cin % 64 == 0 and Cout % 8 == 0")
+    return _Conv3x3Fn.apply(x, weight)

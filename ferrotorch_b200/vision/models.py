@@ -66,8 +66,22 @@ def max_pool(x: torch.Tensor, k: int, s: int, p: int) -> torch.Tensor:
     return F.max_pool2d(x, k, s, p)
 
 
+class Conv3x3(nn.Conv2d):
+    """3x3 convolution; stride-1 bf16 channels-last CUDA inputs (autocast included) run on the implicit-GEMM tcgen05 kernel."""
+
+    def __init__(self, cin, cout, stride=1, groups=1, dilation=1):
+        super().__init__(cin, cout, 3, stride, dilation, dilation, groups, bias=False)
+
+    def forward(self, x):
+        if x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16 and x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        if ops.conv.conv3x3_eligible(x, self.weight, self.stride, self.padding, self.dilation, self.groups):
+            return ops.conv3x3(x, self.weight)
+        return super().forward(x)
+
+
 def conv3x3(cin, cout, stride=1, groups=1, dilation=1):
-    return nn.Conv2d(cin, cout, 3, stride, dilation, dilation, groups, bias=False)
+    return Conv3x3(cin, cout, stride, groups, dilation)
 
 
 class BasicBlock(nn.Module):

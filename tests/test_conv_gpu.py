@@ -1,0 +1,48 @@
+"""Implicit-GEMM 3x3 convolution kernel against an f32 PyTorch convolution (forward, fused ReLU, data gradient, ragged patches)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("N,Cin,Cout,H,W", [(2, 64, 64, 56, 56), (3, 128, 128, 28, 28), (2, 256, 256, 14, 14), (4, 512, 512, 7, 7), (1, 64, 200, 19, 13),
+                                            (1, 192, 24, 5, 40)])
+def test_conv3x3_forward_and_input_gradient(N, Cin, Cout, H, W):
+    from ferrotorch_b200 import _lib, ops
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(N, Cin, H, W, device="cuda", generator=g).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_()
+    w = (torch.randn(Cout, Cin, 3, 3, device="cuda", generator=g) * (2.0 / (9 * Cin)) ** 0.5).requires_grad_()
+    y = ops.conv3x3(x, w)
+    ref = F.conv2d(x.detach().float(), w.detach().bfloat16().float(), padding=1)
+    assert y.shape == ref.shape and y.is_contiguous(memory_format=torch.channels_last)
+    assert (y.float() - ref).abs().max() < 0.06, float((y.float() - ref).abs().max())
+    dy = torch.randn(N, Cout, H, W, device="cuda", generator=g).bfloat16().contiguous(memory_format=torch.channels_last)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    F.conv2d(xr, wr, padding=1).backward(dy.float())
+    tol = 0.08 * max(1.0, float(xr.grad.abs().max()))
+    assert (x.grad.float() - xr.grad).abs().max() < tol
+    assert (w.grad - wr.grad).abs().max() < 0.05 * float(wr.grad.abs().max()) + 0.05
+    yr = ops.conv3x3_nhwc_raw(x.detach(), w.detach().bfloat16().permute(0, 2, 3, 1).contiguous(), relu=True)
+    assert (yr.float() - ref.relu()).abs().max() < 0.06
+    assert _lib.read_status() == 0
+
+
+def test_resnet_block_uses_the_kernel_and_matches_library_path():
+    from ferrotorch_b200 import _lib
+    from ferrotorch_b200.vision.models import BasicBlock
+    torch.manual_seed(0)
+    blk = BasicBlock(64, 64).cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(4, 64, 28, 28, device="cuda").contiguous(memory_format=torch.channels_last)
+    l0 = _lib.launch_calls
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = blk(x)
+    assert _lib.launch_calls > l0
+    ref_blk = torch.nn.Sequential()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        o = torch.relu(F.batch_norm(F.conv2d(x, blk.conv1.weight, padding=1), None, None, blk.bn1.weight, blk.bn1.bias, True))
+        o = F.batch_norm(F.conv2d(o, blk.conv2.weight, padding=1), None, None, blk.bn2.weight, blk.bn2.bias, True)
+        ref = torch.relu(o + x)
+    assert (y.float() - ref.float()).abs().max() < 0.1
