@@ -342,6 +342,59 @@ int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, 
   return FT_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// point-to-point: put into a slot of the receiver's ring + flag; the receiver waits for the flag and copies out
+// ---------------------------------------------------------------------------------------------------------
+// ring slot layout on the receiver: [payload bytes ...]; flags: u32 per slot holding the message number that filled it (1, 2, ...),
+// ack: u32 per slot on the SENDER holding the number of the last message the receiver consumed from that slot.
+__global__ void __launch_bounds__(512) p2p_put_kernel(const uint4* __restrict__ src, uint4* __restrict__ peer_slot, size_t nvec, uint32_t* __restrict__ peer_flag,
+                                                      const uint32_t* __restrict__ my_ack, uint32_t msg, uint32_t prev_msg_in_slot, unsigned int* __restrict__ counter,
+                                                      uint32_t* status) {
+  // the slot must have been drained by the receiver (its ack names the previous message that used this slot)
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) {
+    ok_sh = 1;
+    if (prev_msg_in_slot != 0 && !wait_flag_ge(my_ack, prev_msg_in_slot, COMM_TIMEOUT_NS)) {
+      ft_set_status(status, FT_K_COMM, 21, msg);
+      ok_sh = 0;
+    }
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) peer_slot[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *counter = 0;
+      __threadfence_system();
+      st_release_sys(peer_flag, msg);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) p2p_get_kernel(uint4* __restrict__ dst, const uint4* __restrict__ my_slot, size_t nvec, const uint32_t* __restrict__ my_flag,
+                                                      uint32_t* __restrict__ peer_ack, uint32_t msg, unsigned int* __restrict__ counter, uint32_t* status) {
+  __shared__ int ok_sh;
+  if (threadIdx.x == 0) {
+    ok_sh = wait_flag_ge(my_flag, msg, COMM_TIMEOUT_NS) ? 1 : 0;
+    if (!ok_sh) ft_set_status(status, FT_K_COMM, 22, msg);
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) dst[i] = __ldcg(my_slot + i);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *counter = 0;
+      st_release_sys(peer_ack, msg);                       // the sender may overwrite the slot
+    }
+  }
+}
+
 }  // namespace
 
 // Size in bytes of the per-rank flag block the kernels expect (zero-initialised symmetric memory).
@@ -449,6 +502,27 @@ FT_EXPORT int ft_comm_broadcast(void* const* buf_ptrs, void* out, void* const* f
   const int grid = comm_grid((size_t)n / V, max_ctas > 0 ? max_ctas : 64);
   if (dtype == 0) broadcast_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, root, (size_t)n, ft_status_ptr());
   else broadcast_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, root, (size_t)n, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// Sender side of a point-to-point message: copies `bytes` (multiple of 16) from src into the receiver's ring slot (peer mapping) and then sets the
+// receiver's flag to `msg` (1, 2, ... per channel). If the slot was used before (prev_msg_in_slot != 0) the kernel first waits, bounded, until the
+// receiver acknowledged that message in `my_ack` (local memory the receiver writes through its mapping). counter: local u32, zero between launches.
+FT_EXPORT int ft_comm_p2p_put(const void* src, void* peer_slot, int64_t bytes, void* peer_flag, const void* my_ack, uint32_t msg, uint32_t prev_msg_in_slot,
+                              uint32_t* counter, cudaStream_t st) {
+  if (bytes <= 0 || bytes % 16 || msg == 0) return FT_ERR_ARG;
+  const int grid = comm_grid((size_t)bytes / 16, 32);
+  p2p_put_kernel<<<grid, 512, 0, st>>>((const uint4*)src, (uint4*)peer_slot, (size_t)bytes / 16, (uint32_t*)peer_flag, (const uint32_t*)my_ack, msg, prev_msg_in_slot,
+                                       counter, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// Receiver side: waits (bounded) until the local flag reaches `msg`, copies the slot into dst and acknowledges on the sender.
+FT_EXPORT int ft_comm_p2p_get(void* dst, const void* my_slot, int64_t bytes, const void* my_flag, void* peer_ack, uint32_t msg, uint32_t* counter, cudaStream_t st) {
+  if (bytes <= 0 || bytes % 16 || msg == 0) return FT_ERR_ARG;
+  const int grid = comm_grid((size_t)bytes / 16, 32);
+  p2p_get_kernel<<<grid, 512, 0, st>>>((uint4*)dst, (const uint4*)my_slot, (size_t)bytes / 16, (const uint32_t*)my_flag, (uint32_t*)peer_ack, msg, counter,
+                                       ft_status_ptr());
   return (int)cudaGetLastError();
 }
 

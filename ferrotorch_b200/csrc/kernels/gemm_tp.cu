@@ -118,17 +118,21 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!wait_flag_ge(a.flags[a.rank] + MAXR + q, a.seq - 2, WAIT_NS)) { ft_set_status(status, FT_K_TP, 1, q); ok = false; }
         }
       }
-      for (int item = blockIdx.x; item < tpr * a.split && ok; item += a.ncopy) {
-        const int t = item / a.split, part = item % a.split;
+      // destination-major order: everything for the peer that consumes this rank's rows first (rank - 1), then rank - 2, ... At any moment the
+      // ranks send to distinct destinations, and a consumer receives the shards in the order its tile loop visits them.
+      const int per_dst = tpr * a.split;
+      for (int item = blockIdx.x; item < (W - 1) * per_dst && ok; item += a.ncopy) {
+        const int q = (a.rank - 1 - item / per_dst + 2 * W) % W;
+        const int t = (item % per_dst) / a.split, part = item % a.split;
         const int c_begin = (int)((long long)nchunks * part / a.split), c_end = (int)((long long)nchunks * (part + 1) / a.split);
         const int n_it = c_end - c_begin;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x_local) + (size_t)t * tile_bytes;
-        const size_t dst_off = ((size_t)par * tiles_m + (size_t)(a.rank * tpr + t)) * tile_bytes;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(a.xg[q]) + ((size_t)par * tiles_m + (size_t)(a.rank * tpr + t)) * tile_bytes;
         const uint32_t base = issued;
         for (int c = 0; c < n_it + COPY_AHEAD && ok; c++) {
           if (c < n_it) {
             const uint32_t g = base + c, s = g % COPY_STAGES;
-            if (g >= (uint32_t)COPY_STAGES) tma_store_wait_read<COPY_STAGES - COPY_AHEAD - 1>();   // the stores that last read this stage are done with it
+            if (g >= (uint32_t)COPY_STAGES) tma_store_wait_read<COPY_STAGES - COPY_AHEAD - 1>();   // the store that last read this stage is done with it
             const size_t off = (size_t)(c_begin + c) * COPY_CHUNK;
             const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - off);
             mbar_expect_tx(&full[s], bytes);
@@ -141,18 +145,14 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             if (!mbar_wait_deadline(&full[s], (g / COPY_STAGES) & 1)) { ft_set_status(status, FT_K_TP, 2, s); ok = false; break; }
             const size_t off = (size_t)(c_begin + cc) * COPY_CHUNK;
             const uint32_t bytes = (uint32_t)min((size_t)COPY_CHUNK, tile_bytes - off);
-            for (int d = 1; d < W; d++) {                                          // one posted write per peer, starting at a different peer per chunk
-              const int q = (a.rank + 1 + (d - 1 + cc) % (W - 1)) % W;
-              bulk_store(reinterpret_cast<uint8_t*>(a.xg[q]) + dst_off + off, smem + s * COPY_CHUNK, bytes);
-            }
+            bulk_store(dst + off, smem + s * COPY_CHUNK, bytes);
             tma_store_commit();
           }
         }
         if (!ok) break;
-        tma_store_wait<0>();                                                       // every peer has this item's bytes
+        tma_store_wait<0>();                                                       // the peer has this item's bytes
         __threadfence_system();
-        for (int q = 0; q < W; q++)
-          if (q != a.rank) red_release_sys_add(a.tile_cnt[q] + (size_t)par * tiles_m + (a.rank * tpr + t), 1u);
+        red_release_sys_add(a.tile_cnt[q] + (size_t)par * tiles_m + (a.rank * tpr + t), 1u);
       }
       if (!ok) {
         tma_store_wait<0>();
@@ -260,7 +260,6 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     constexpr int CHUNKS = BN / 64;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
-    int pend_p = -1, pend_idx = 0;                                 // MODE 2: tile whose stores are issued but not yet announced
     for (int tile = g_id; tile < num_tiles && ok; tile += g_n) {
       int p, tin, ni;
       tile_map(tile, p, tin, ni);
@@ -308,22 +307,19 @@ ft_tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
-      if (MODE == 2 && lane == 0) {
-        // announce the PREVIOUS tile: its four store groups are complete once at most the four newest (this tile's) are pending
-        if (pend_p >= 0) {
-          tma_store_wait<CHUNKS>();
-          __threadfence_system();
-          red_release_sys_add(a.cnt[pend_p] + (size_t)par * tpr * tiles_n + pend_idx, 1u);
-        }
-        pend_p = p;
-        pend_idx = tin * tiles_n + ni;
-      }
     }
     if (lane == 0) {
+      // the partial tiles are only needed once every rank is through its GEMM phase, so nothing is gained by announcing them one by one (and
+      // waiting for a store to complete across NVLink in the middle of the epilogue costs a round trip per tile): wait once, then bump every
+      // counter this warp owes
       tma_store_wait<0>();
-      if (MODE == 2 && pend_p >= 0) {
+      if (MODE == 2 && ok) {
         __threadfence_system();
-        red_release_sys_add(a.cnt[pend_p] + (size_t)par * tpr * tiles_n + pend_idx, 1u);
+        for (int tile = g_id; tile < num_tiles; tile += g_n) {
+          int p, tin, ni;
+          tile_map(tile, p, tin, ni);
+          red_release_sys_add(a.cnt[p] + (size_t)par * tpr * tiles_n + tin * tiles_n + ni, 1u);
+        }
       }
     }
     __syncwarp();

@@ -304,9 +304,48 @@ def case_cp():
         print("CP_OK")
 
 
+def case_pipeline():
+    """Device point-to-point channel (more messages than slots, so slots are re-used behind acknowledgements) and a two-stage GPipe step whose
+    parameter gradients equal the single-process ones (the upstream stage receives the real input gradient)."""
+    from ferrotorch_b200 import _lib
+    from ferrotorch_b200.parallel import GpuPipelineStage, P2PChannel
+    rank, world, dev = _init()
+    ch = P2PChannel(4096, slots=2, device=dev)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    for i in range(7):
+        msg = torch.full((1024,), float(rank * 100 + i), device=dev)
+        ch.send(msg, nxt)
+        got = ch.recv(torch.empty(1024, device=dev), prv)
+        assert float(got[0]) == prv * 100 + i and float(got[-1]) == prv * 100 + i, (i, float(got[0]))
+    torch.manual_seed(0)
+    full = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 48), torch.nn.Tanh(), torch.nn.Linear(48, 8)).to(dev)
+    cut = 2 if world == 2 else None
+    assert world == 2
+    stage_mod = torch.nn.Sequential(*list(full.children())[:cut]) if rank == 0 else torch.nn.Sequential(*list(full.children())[cut:])
+    import copy
+    stage_mod = copy.deepcopy(stage_mod)
+    stage = GpuPipelineStage(stage_mod, (32,) if rank == 0 else (64,), (64,) if rank == 0 else (8,), micro_batch=4)
+    g = torch.Generator(device=dev).manual_seed(1)
+    X = torch.randn(3, 4, 32, device=dev, generator=g)
+    T = torch.randn(3, 4, 8, device=dev, generator=g)
+    losses = stage.forward_backward([X[i] for i in range(3)] if rank == 0 else None, 3, (lambda o, i: ((o - T[i]) ** 2).mean()) if rank == 1 else None)
+    torch.cuda.synchronize()
+    for i in range(3):
+        ((full(X[i]) - T[i]) ** 2).mean().backward()
+    ref = list(full.children())[:cut] if rank == 0 else list(full.children())[cut:]
+    for a, b in zip(stage_mod.parameters(), torch.nn.Sequential(*ref).parameters()):
+        assert torch.allclose(a.grad, b.grad, atol=1e-5), float((a.grad - b.grad).abs().max())
+    if rank == 1:
+        assert len(losses) == 3
+    assert _lib.read_status() == 0
+    dist.barrier()
+    if rank == 0:
+        print("PIPELINE_OK")
+
+
 if __name__ == "__main__":
     try:
-        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp, "tp_gemm": case_tp_gemm, "cp": case_cp}[sys.argv[1]]()
+        {"collectives": case_collectives, "fsdp": case_fsdp, "timeout": case_timeout, "tp_decode": case_tp_decode, "ddp": case_ddp, "tp_gemm": case_tp_gemm, "cp": case_cp, "pipeline": case_pipeline}[sys.argv[1]]()
     finally:
         if dist.is_initialized():
             dist.destroy_process_group()

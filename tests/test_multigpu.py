@@ -47,6 +47,10 @@ def test_context_parallel_attention_and_exchange_kernels():
     assert "CP_OK" in _run("cp", 2, 29617)
 
 
+def test_device_p2p_channel_and_pipeline_stage():
+    assert "PIPELINE_OK" in _run("pipeline", 2, 29618)
+
+
 def test_tp_decode_engine_matches_reference():
     assert "TP_DECODE_OK" in _run("tp_decode", 2, 29614)
 
