@@ -462,3 +462,172 @@ class HostFusedKernel:
         args = [ctypes.c_void_p(t.data_ptr()) for t in inputs] + [ctypes.c_void_p(t.data_ptr()) for t in outs] + [ctypes.c_longlong(n), ctypes.byref(st)]
         self.fn(*args)
         return outs
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# fused elementwise region + reduction over the last dimension
+# ----------------------------------------------------------------------------------------------------------------------
+_RED = {"sum": ("0", "{a} + {b}"), "mean": ("0", "{a} + {b}"), "amax": ("-INFINITY", "(({b} > {a} || {b} != {b}) ? {b} : {a})"),
+        "amin": ("INFINITY", "(({b} < {a} || {b} != {b}) ? {b} : {a})")}
+
+
+def _offset_lines(n_in: int, ptr_prefix: str, indent: str) -> List[str]:
+    lines = [f"{indent}long long rem = i, off[{max(n_in, 1)}] = {{}};", f"{indent}for (int d = {ptr_prefix}ndim - 1; d >= 0; d--) {{",
+             f"{indent}  const long long c = rem % {ptr_prefix}shape[d];", f"{indent}  rem /= {ptr_prefix}shape[d];"]
+    lines += [f"{indent}  off[{k}] += c * {ptr_prefix}stride[{k}][d];" for k in range(n_in)]
+    lines.append(f"{indent}}}")
+    return lines
+
+
+def generate_cuda_reduce(body: IrGraph, name: str, red_op: str, red_index: int) -> str:
+    """One CTA per row of the region's ``[rows, cols]`` view: every thread evaluates the fused body for its columns, the reduced output goes through
+    a warp-shuffle + shared-memory block reduction, the other outputs are stored elementwise. Signature: (in..., red_out, other outs..., rows, cols, strides)."""
+    ins = [body.values[i] for i in body.inputs]
+    outs = [body.values[o] for o in body.outputs]
+    red_v = outs[red_index]
+    acc = _acc_type(red_v.dtype)
+    ident, comb = _RED[red_op]
+    others = [(k, v) for k, v in enumerate(outs) if k != red_index]
+    params = [f"const {_CTYPE[v.dtype]}* __restrict__ in{k}" for k, v in enumerate(ins)] + [f"{_CTYPE[red_v.dtype]}* __restrict__ red_out"]
+    params += [f"{_CTYPE[v.dtype]}* __restrict__ out{k}" for k, v in others] + ["long long rows", "int cols", "const FtStrides st"]
+    src = ["#include <cuda_bf16.h>", "#include <cuda_fp16.h>", f"struct FtStrides {{ int ndim; long long shape[{MAX_DIMS}]; long long stride[{max(len(ins), 1)}][{MAX_DIMS}]; }};",
+           f'extern "C" __global__ void __launch_bounds__(256) {name}({", ".join(params)}) {{', f"  __shared__ {acc} red[8];", "  const long long row = blockIdx.x;",
+           f"  {acc} acc = {ident};", "  for (int col = threadIdx.x; col < cols; col += 256) {", "    const long long i = row * cols + col;"]
+    src += _offset_lines(len(ins), "st.", "    ")
+    names = {}
+    for k, v in enumerate(ins):
+        src.append(f"    const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'off[{k}]')};")
+        names[body.inputs[k]] = f"x{k}"
+    lines, var = _body_lines(body, names)
+    src += ["    " + l for l in lines]
+    rv = var[body.outputs[red_index]]
+    src.append("    acc = " + comb.format(a="acc", b=f"(({acc}){rv})") + ";")
+    for k, v in others:
+        src.append("    " + _store(v.dtype, f"out{k}", "i", var[body.outputs[k]]))
+    src.append("  }")
+    src += ["  for (int o = 16; o > 0; o >>= 1) { const " + acc + " other = __shfl_xor_sync(0xffffffffu, acc, o); acc = " + comb.format(a="acc", b="other") + "; }",
+            "  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;", "  __syncthreads();", "  if (threadIdx.x < 32) {",
+            f"    acc = threadIdx.x < 8 ? red[threadIdx.x] : ({acc}){ident};",
+            "    for (int o = 4; o > 0; o >>= 1) { const " + acc + " other = __shfl_xor_sync(0xffffffffu, acc, o); acc = " + comb.format(a="acc", b="other") + "; }",
+            "    if (threadIdx.x == 0) " + _store(red_v.dtype, "red_out", "row", "acc / cols" if red_op == "mean" else "acc"), "  }", "}"]
+    return "\n".join(src) + "\n"
+
+
+def generate_host_reduce(body: IrGraph, name: str, red_op: str, red_index: int) -> str:
+    ins = [body.values[i] for i in body.inputs]
+    outs = [body.values[o] for o in body.outputs]
+    red_v = outs[red_index]
+    acc = _acc_type(red_v.dtype)
+    ident, comb = _RED[red_op]
+    others = [(k, v) for k, v in enumerate(outs) if k != red_index]
+    params = [f"const {_HOST_CTYPE[v.dtype]}* __restrict__ in{k}" for k, v in enumerate(ins)] + [f"{_HOST_CTYPE[red_v.dtype]}* __restrict__ red_out"]
+    params += [f"{_HOST_CTYPE[v.dtype]}* __restrict__ out{k}" for k, v in others] + ["long long rows", "int cols", "const FtStrides* stp"]
+    src = [_HOST_PRELUDE % (MAX_DIMS, max(len(ins), 1), MAX_DIMS), f'extern "C" void {name}({", ".join(params)}) {{', "  const FtStrides& st = *stp;",
+           "  for (long long row = 0; row < rows; row++) {", f"    {acc} acc = {ident};", "    for (int col = 0; col < cols; col++) {", "      const long long i = row * cols + col;"]
+    src += _offset_lines(len(ins), "st.", "      ")
+    names = {-1: "__HOST__"}
+    for k, v in enumerate(ins):
+        src.append(f"      const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'off[{k}]', host=True)};")
+        names[body.inputs[k]] = f"x{k}"
+    lines, var = _body_lines(body, names)
+    src += ["      " + l for l in lines]
+    src.append("      acc = " + comb.format(a="acc", b=f"(({acc}){var[body.outputs[red_index]]})") + ";")
+    for k, v in others:
+        src.append("      " + _store(v.dtype, f"out{k}", "i", var[body.outputs[k]], host=True))
+    src += ["    }", "    " + _store(red_v.dtype, "red_out", "row", "acc / cols" if red_op == "mean" else "acc", host=True), "  }", "}"]
+    return "\n".join(src) + "\n"
+
+
+class _FusedReduceBase:
+    def __init__(self, body: IrGraph, red_op: str, red_index: int, keepdim: bool):
+        self.body, self.red_op, self.red_index, self.keepdim = body, red_op, red_index, keepdim
+        self.fp = hashlib.sha256((body.fingerprint() + red_op + str(red_index)).encode()).hexdigest()[:16]
+        self.shape = tuple(body.values[body.outputs[0]].shape)
+        if len(self.shape) < 1 or len(self.shape) > MAX_DIMS:
+            raise InvalidArgument("fused reduction needs 1 to 6 dimensions")
+        self.cols = self.shape[-1]
+        self.rows = 1
+        for s in self.shape[:-1]:
+            self.rows *= s
+
+    def _alloc(self, device):
+        body = self.body
+        rshape = self.shape[:-1] + ((1,) if self.keepdim else ())
+        red = torch.empty(rshape, device=device, dtype=dtype_of(body.values[body.outputs[self.red_index]].dtype))
+        others = [torch.empty(self.shape, device=device, dtype=dtype_of(body.values[o].dtype)) for k, o in enumerate(body.outputs) if k != self.red_index]
+        return red, others
+
+    def _strides(self, inputs):
+        nin = max(len(inputs), 1)
+
+        class St(ctypes.Structure):
+            _fields_ = [("ndim", ctypes.c_int), ("shape", ctypes.c_longlong * MAX_DIMS), ("stride", (ctypes.c_longlong * MAX_DIMS) * nin)]
+        st = St()
+        st.ndim = len(self.shape)
+        for d, s in enumerate(self.shape):
+            st.shape[d] = s
+        for k, t in enumerate(inputs):
+            e = t.expand(self.shape)
+            for d in range(len(self.shape)):
+                st.stride[k][d] = e.stride(d)
+        return st
+
+
+class CudaFusedReduceKernel(_FusedReduceBase):
+    def __init__(self, body, red_op, red_index, keepdim):
+        super().__init__(body, red_op, red_index, keepdim)
+        self.name = f"ft_fusedred_{self.fp}"
+        self.source = generate_cuda_reduce(body, self.name, red_op, red_index)
+        self.image = compile_cuda(self.source)
+        self._kern = None
+
+    def __call__(self, inputs: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        from .. import _lib
+        dev = next(t.device for t in inputs if t.is_cuda)
+        ins = [t if t.device == dev else t.to(dev) for t in inputs]
+        red, others = self._alloc(dev)
+        if self.rows == 0 or self.cols == 0:
+            return [red] + others
+        if self._kern is None:
+            lib, fn = ctypes.c_void_p(), ctypes.c_void_p()
+            self._img = ctypes.create_string_buffer(self.image, len(self.image))
+            _lib.call("ft_jit_load", ctypes.addressof(self._img), ctypes.addressof(lib))
+            nb = ctypes.create_string_buffer(self.name.encode())
+            _lib.call("ft_jit_get_kernel", lib.value, ctypes.addressof(nb), ctypes.addressof(fn))
+            self._lib_handle, self._kern = lib, fn.value
+        args = [ctypes.c_void_p(t.data_ptr()) for t in ins] + [ctypes.c_void_p(red.data_ptr())] + [ctypes.c_void_p(t.data_ptr()) for t in others]
+        args += [ctypes.c_longlong(self.rows), ctypes.c_int(self.cols), self._strides(ins)]
+        arr = (ctypes.c_void_p * len(args))(*[ctypes.addressof(a) for a in args])
+        _lib.call("ft_jit_launch", self._kern, self.rows, 256, 0, ctypes.addressof(arr), _lib.S())
+        return [red] + others
+
+
+class HostFusedReduceKernel(_FusedReduceBase):
+    def __init__(self, body, red_op, red_index, keepdim):
+        super().__init__(body, red_op, red_index, keepdim)
+        self.name = f"ft_fusedred_{self.fp}_h"
+        self.source = generate_host_reduce(body, self.name, red_op, red_index)
+        key = hashlib.sha256(self.source.encode()).hexdigest()
+        _cache_dir.mkdir(parents=True, exist_ok=True)
+        so = _cache_dir / f"{key}.so"
+        if not so.exists():
+            cpp = _cache_dir / f"{key}.cpp"
+            cpp.write_text(self.source)
+            tmp = _cache_dir / f"{key}.{os.getpid()}.tmp.so"
+            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-pthread", "-shared", "-fPIC", "-std=c++17", str(cpp), "-o", str(tmp)],
+                               capture_output=True, text=True)
+            if r.returncode != 0:
+                raise FerrotorchError("host codegen compilation failed:\n" + r.stderr + "\n--- source ---\n" + self.source)
+            os.replace(tmp, so)
+        self.lib = ctypes.CDLL(str(so))
+        self.fn = getattr(self.lib, self.name)
+        self.fn.restype = None
+
+    def __call__(self, inputs: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        red, others = self._alloc("cpu")
+        if self.rows == 0 or self.cols == 0:
+            return [red] + others
+        st = self._strides(inputs)
+        args = [ctypes.c_void_p(t.data_ptr()) for t in inputs] + [ctypes.c_void_p(red.data_ptr())] + [ctypes.c_void_p(t.data_ptr()) for t in others]
+        self.fn(*args, ctypes.c_longlong(self.rows), ctypes.c_int(self.cols), ctypes.byref(st))
+        return [red] + others

@@ -109,6 +109,10 @@ def eval_node(n: IrNode, ins: List[torch.Tensor], g: IrGraph):
         return ins[0]                                   # traced graphs are inference graphs
     if op == "fused":
         return run_graph(a["body"], ins)
+    if op == "fused_reduce":
+        outs = run_graph(a["body"], ins)
+        red = getattr(torch, a["red_op"])(outs[a["red_index"]], [-1], keepdim=a["keepdim"])
+        return [red] + [o for i, o in enumerate(outs) if i != a["red_index"]]
     if op == "opaque":
         flat = list(a["skeleton"])
         for slot, t in zip(a["slots"], ins):

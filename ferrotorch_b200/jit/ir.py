@@ -24,7 +24,7 @@ REDUCTIONS = {"sum", "mean", "amax", "amin", "prod", "argmax", "argmin", "var", 
 SHAPE_OPS = {"reshape", "permute", "transpose", "expand", "squeeze", "unsqueeze", "slice", "select", "cat", "stack", "contiguous", "flatten", "index_select",
              "gather", "split_item"}
 CONTRACTIONS = {"matmul", "linear", "bmm", "addmm", "conv2d", "embedding"}
-COMPOSITE = {"softmax", "log_softmax", "layer_norm", "rms_norm", "dropout", "cross_entropy", "attention", "fused"}
+COMPOSITE = {"softmax", "log_softmax", "layer_norm", "rms_norm", "dropout", "cross_entropy", "attention", "fused", "fused_reduce"}
 ALL_OPS = ELEMENTWISE | REDUCTIONS | SHAPE_OPS | CONTRACTIONS | COMPOSITE | {"input", "constant", "output", "opaque"}
 
 _DT = {"f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16, "f16": torch.float16, "i64": torch.int64, "i32": torch.int32, "bool": torch.bool,

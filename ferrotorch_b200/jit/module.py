@@ -16,7 +16,7 @@ import torch
 
 from ..errors import FerrotorchError, InvalidArgument
 from . import passes
-from .codegen import CudaFusedKernel, HostFusedKernel
+from .codegen import CudaFusedKernel, CudaFusedReduceKernel, HostFusedKernel, HostFusedReduceKernel
 from .interpreter import eval_node
 from .ir import IrGraph, dtype_name
 from .trace import trace
@@ -132,12 +132,16 @@ class _Executable:
         stats.graph_breaks += sum(1 for s in self.segments if not s.compiled)
         if backend in ("cuda", "host"):
             for n in self.order:
-                if n.op == "fused":
-                    try:
+                try:
+                    if n.op == "fused":
                         self.kernels[n.id] = (CudaFusedKernel if backend == "cuda" else HostFusedKernel)(n.attrs["body"])
                         stats.fused_kernels += 1
-                    except InvalidArgument:
-                        pass                                       # ops without a code template stay on the interpreter
+                    elif n.op == "fused_reduce":
+                        cls = CudaFusedReduceKernel if backend == "cuda" else HostFusedReduceKernel
+                        self.kernels[n.id] = cls(n.attrs["body"], n.attrs["red_op"], n.attrs["red_index"], n.attrs["keepdim"])
+                        stats.fused_kernels += 1
+                except InvalidArgument:
+                    pass                                           # ops without a code template stay on the interpreter
         users = g.users()
         self.last_use: Dict[int, int] = {}
         for i, n in enumerate(self.order):

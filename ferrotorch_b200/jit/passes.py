@@ -300,9 +300,42 @@ def plan_memory(g: IrGraph) -> MemoryPlan:
     return MemoryPlan(slot_of, slot_bytes, naive)
 
 
+def fuse_reductions(g: IrGraph) -> int:
+    """A sum / mean / amax / amin over the last dimension whose only producer is a fused elementwise region (and which is the only consumer of that
+    value) is folded into the region: the node becomes ``fused_reduce`` (outputs: the reduced value first, then the region's other outputs)."""
+    users = g.users()
+    n_done = 0
+    for r in list(g.topo_order()):
+        if r.id not in g.nodes or r.op not in ("sum", "mean", "amax", "amin"):
+            continue
+        src = r.inputs[0]
+        v = g.values[src]
+        if tuple(r.attrs["dims"]) != (len(v.shape) - 1,) or len(v.shape) < 1:
+            continue
+        pid = v.producer
+        if pid is None or pid not in g.nodes or g.nodes[pid].op != "fused" or src in g.outputs or users.get(src, []) != [r.id]:
+            continue
+        f = g.nodes[pid]
+        idx = f.outputs.index(src)
+        rest = [o for o in f.outputs if o != src]
+        node = g.add_node("fused_reduce", f.inputs, [(g.values[r.outputs[0]].shape, g.values[r.outputs[0]].dtype)] + [(g.values[o].shape, g.values[o].dtype) for o in rest],
+                          body=f.attrs["body"], red_op=r.op, red_index=idx, keepdim=bool(r.attrs.get("keepdim", False)), size=f.attrs.get("size", 0) + 1)
+        for new in list(node.outputs):
+            g.values.pop(new)
+        node.outputs = [r.outputs[0]] + rest
+        for o in node.outputs:
+            g.values[o].producer = node.id
+        g.values.pop(src, None)
+        del g.nodes[f.id], g.nodes[r.id]
+        users = g.users()
+        n_done += 1
+    return n_done
+
+
 def optimize(g: IrGraph, fuse: bool = True) -> Dict[str, int]:
     stats = {"folded": constant_folding(g), "simplified": algebraic_simplification(g), "cse": common_subexpression_elimination(g),
              "dce": dead_code_elimination(g)}
     stats["fused_groups"] = fuse_elementwise(g) if fuse else 0
+    stats["fused_reductions"] = fuse_reductions(g) if fuse else 0
     g.validate()
     return stats

@@ -83,7 +83,7 @@ def test_cuda_codegen_compiles_for_sm100a_without_a_gpu():
     x, y, b = _inputs()
     g = jit.trace(_f, (x.bfloat16(), y.bfloat16(), b.bfloat16()))
     jit.optimize(g)
-    body = next(n for n in g.nodes.values() if n.op == "fused").attrs["body"]
+    body = next(n for n in g.nodes.values() if n.op in ("fused", "fused_reduce")).attrs["body"]
     for vec in (True, False):
         src = jit.generate_cuda(body, "k", vec)
         assert "__nv_bfloat16" in src and ("uint4" in src) == vec
@@ -145,3 +145,25 @@ def test_graph_breaks_memory_plan_autotune():
     import time
     r = at.tune("k", [{"sleep": 0.002}, {"sleep": 0.0}], lambda c: (lambda: time.sleep(c["sleep"])))
     assert r.best == {"sleep": 0.0} and jit.Autotuner(os.path.join(d, "tune.json")).tune("k", [], None).best == {"sleep": 0.0}
+
+
+def test_fused_elementwise_plus_row_reduction():
+    def f(x, b):
+        e = torch.exp(x - 1.0) * b
+        return e.sum(-1, keepdim=True), torch.tanh(e)
+    x, b = torch.randn(6, 33), torch.randn(33)
+    g = jit.trace(f, (x, b))
+    stats = jit.optimize(g)
+    assert stats["fused_reductions"] == 1 and [n.op for n in g.nodes.values()] == ["fused_reduce"]
+    for a, r in zip(jit.run_graph(g, (x, b)), f(x, b)):
+        assert torch.allclose(a, r, atol=1e-5)
+    cf = jit.compile(f, backend="host")
+    for a, r in zip(cf(x, b), f(x, b)):
+        assert torch.allclose(a, r, atol=1e-5)
+    assert cf.stats.fused_kernels == 1 and cf.stats.kernel_launches == 1
+    for op in ("mean", "amax", "amin"):
+        fn = lambda t: getattr(torch, op)(torch.sigmoid(t) * t, -1)       # noqa: E731,B023
+        assert torch.allclose(jit.compile(fn, backend="host")(x), fn(x), atol=1e-6)
+    n = next(n for n in g.nodes.values() if n.op == "fused_reduce")
+    img = jit.compile_cuda(jit.generate_cuda_reduce(n.attrs["body"], "k", "sum", n.attrs["red_index"]))
+    assert img[:4] == b"\x7fELF"

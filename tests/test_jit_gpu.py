@@ -41,3 +41,18 @@ def test_compiled_mlp_block_matches_eager():
     f = lambda t: F.silu(m(t)) * torch.sigmoid(t) + t     # noqa: E731
     cf = jit.compile(f, backend="cuda")
     assert (cf(x) - f(x)).abs().max() < 1e-4 and cf.stats.fused_kernels >= 1
+
+
+def test_fused_row_reduction_kernel():
+    from ferrotorch_b200 import jit
+
+    def f(x, b):
+        e = torch.exp(x * 0.1) * b
+        return e.sum(-1, keepdim=True), torch.tanh(e)
+    x, b = torch.randn(300, 1027, device="cuda"), torch.randn(1027, device="cuda")
+    cf = jit.compile(f, backend="cuda")
+    out, ref = cf(x, b), f(x, b)
+    assert cf.stats.fused_kernels == 1
+    assert (out[0] - ref[0]).abs().max() < 1e-2 and (out[1] - ref[1]).abs().max() < 1e-5
+    sm = lambda t: torch.exp(t - t.amax(-1, keepdim=True))                 # noqa: E731
+    assert (jit.compile(sm, backend="cuda")(x) - sm(x)).abs().max() < 1e-5
