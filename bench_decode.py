@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--decode", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="after the timed run, report eager per-kernel-class device time per step")
     a = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -73,6 +74,10 @@ def main():
         t = torch.tensor([ms, prefill_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, prefill_ms = float(t[0]), float(t[1])
+    breakdown = None
+    if a.profile:
+        prof = eng.profile_decode(8)                     # eager launches with CUDA events around each kernel class (after the timed region)
+        breakdown = {k: round(v, 1) for k, v in sorted(prof.items(), key=lambda kv: -kv[1])}
     status = _lib.read_status()
     if rank == 0:
         full = a.layers is None and a.model == "70b" and a.batch == 8 and a.prompt == 2048
@@ -88,6 +93,7 @@ def main():
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(a.batch * a.prompt / (prefill_ms / 1e3), 1),
             "weight_bytes_per_gpu": weight_bytes, "hbm_gbs_streamed": round(weight_bytes / (ms / a.decode / 1e3) / 1e9, 1),
             "gpu_launches": (_lib.launch_calls - l0) if a.no_graph else "graph replay", "kernel_status": status, "impl": "ours",
+            **({"eager_us_per_step_by_kernel": breakdown} if breakdown else {}),
         }))
     if world > 1:
         dist.destroy_process_group()

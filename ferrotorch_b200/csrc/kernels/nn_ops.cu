@@ -49,11 +49,17 @@ template <> FT_DEVICE void store_vec<__nv_bfloat16, 8>(__nv_bfloat16* p, const f
 
 // ---- column sums over [M, C]: MODE 0: (sum x, sum x^2); MODE 1: (sum dy', sum dy' * xhat) with dy' = relu-masked dy ---------------------
 // block = 256 threads = TXW column-groups x (256 / TXW) row lanes; grid = (C / VEC / TXW, row blocks). partial: [gridDim.y][2][C].
+// The last CTA of every column block (arrival counter, self-resetting) adds the partials in block order and writes sums[2][C], so the result is
+// bit-stable and no second launch is needed. The counters are one static array per device: statistics launches on one device must not overlap.
+__device__ unsigned int g_col_counters[512];
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) col_stats_kernel(const T* __restrict__ a, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mean,
-                                                        const float* __restrict__ invstd, size_t M, int C, int txw, float* __restrict__ partial) {
+                                                        const float* __restrict__ invstd, size_t M, int C, int txw, float* __restrict__ partial,
+                                                        float* __restrict__ sums) {
   constexpr int N = VecT<T>::N;
   extern __shared__ float sm[];                        // [2][rows_lanes][txw * N]
+  __shared__ int is_last;
   const int tx = threadIdx.x % txw, ty = threadIdx.x / txw, tyn = 256 / txw;
   const int c0 = (blockIdx.x * txw + tx) * N;
   float s0[N], s1[N], mu[N], is[N];
@@ -95,16 +101,33 @@ __global__ void __launch_bounds__(256) col_stats_kernel(const T* __restrict__ a,
     for (int k = 0; k < tyn; k++) acc += src[k * W + c];
     partial[((size_t)blockIdx.y * 2 + which) * C + blockIdx.x * W + c] = acc;
   }
-}
-
-// sums[2][C] = sum over the nblk partial blocks
-__global__ void __launch_bounds__(256) col_stats_reduce_kernel(const float* __restrict__ partial, int nblk, int C, float* __restrict__ sums) {
-  const int i = blockIdx.x * 256 + threadIdx.x;
-  if (i >= 2 * C) return;
-  const int which = i / C, c = i % C;
-  float acc = 0.f;
-  for (int k = 0; k < nblk; k++) acc += partial[((size_t)k * 2 + which) * C + c];
-  sums[i] = acc;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&g_col_counters[blockIdx.x], 1u);
+    is_last = prev == gridDim.y - 1;
+    if (is_last) g_col_counters[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // 2 * W (which, column) pairs; the 256 threads split the block range of every pair into 256 / (2 W) slices (>= 1), combined in slice order
+  const int pairs = 2 * W, slices = pairs >= 256 ? 1 : 256 / pairs, nblk = gridDim.y;
+  float* red = sm;                                     // [slices][pairs] (fits: slices * pairs <= 256 floats, or pairs when slices == 1)
+  for (int i = threadIdx.x; i < pairs * slices; i += 256) {
+    const int pr = i % pairs, sl = i / pairs, which = pr / W, c = pr % W;
+    const int k0 = (int)((long long)nblk * sl / slices), k1 = (int)((long long)nblk * (sl + 1) / slices);
+    float acc = 0.f;
+#pragma unroll 8
+    for (int k = k0; k < k1; k++) acc += __ldcg(partial + ((size_t)k * 2 + which) * C + blockIdx.x * W + c);
+    red[sl * pairs + pr] = acc;
+  }
+  __syncthreads();
+  for (int pr = threadIdx.x; pr < pairs; pr += 256) {
+    float acc = 0.f;
+    for (int sl = 0; sl < slices; sl++) acc += red[sl * pairs + pr];
+    sums[(pr / W) * C + blockIdx.x * W + (pr % W)] = acc;
+  }
 }
 
 // mean / invstd from (sum, sumsq) over `count` elements per channel; running stats updated with the unbiased variance
@@ -120,24 +143,32 @@ __global__ void __launch_bounds__(256) bn_finalize_kernel(const float* __restric
   if (running_var) running_var[c] = (1.f - momentum) * running_var[c] + momentum * var * (count > 1.f ? count / (count - 1.f) : 1.f);
 }
 
+// y = relu?(x * a + b (+ residual)) with a = invstd * gamma, b = beta - mean * a held in registers: a thread owns one 16-byte channel group and walks
+// down the rows (block = TXW groups x 256 / TXW row lanes, as in the statistics kernel), so the per-channel constants are read once per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, const float* __restrict__ mean, const float* __restrict__ invstd,
                                                        const float* __restrict__ gamma, const float* __restrict__ beta, const T* __restrict__ residual, int relu,
-                                                       size_t M, int C, T* __restrict__ y) {
+                                                       size_t M, int C, int txw, T* __restrict__ y) {
   constexpr int N = VecT<T>::N;
-  const size_t nvec = M * (size_t)C / N;
-  for (size_t i = blockIdx.x * (size_t)256 + threadIdx.x; i < nvec; i += (size_t)gridDim.x * 256) {
-    const int c0 = (int)((i * N) % C);
-    float v[N], r[N];
-    load_vec<T, N>(x + i * N, v);
-    if (residual) load_vec<T, N>(residual + i * N, r);
+  const int tx = threadIdx.x % txw, ty = threadIdx.x / txw, tyn = 256 / txw;
+  const int c0 = (blockIdx.x * txw + tx) * N;
+  float a[N], b[N];
+#pragma unroll
+  for (int e = 0; e < N; e++) {
+    a[e] = invstd[c0 + e] * (gamma ? gamma[c0 + e] : 1.f);
+    b[e] = (beta ? beta[c0 + e] : 0.f) - mean[c0 + e] * a[e];
+  }
+  for (size_t r = (size_t)blockIdx.y * tyn + ty; r < M; r += (size_t)gridDim.y * tyn) {
+    float v[N], rs[N];
+    load_vec<T, N>(x + r * C + c0, v);
+    if (residual) load_vec<T, N>(residual + r * C + c0, rs);
 #pragma unroll
     for (int e = 0; e < N; e++) {
-      float o = (v[e] - mean[c0 + e]) * invstd[c0 + e] * (gamma ? gamma[c0 + e] : 1.f) + (beta ? beta[c0 + e] : 0.f);
-      if (residual) o += r[e];
+      float o = v[e] * a[e] + b[e];
+      if (residual) o += rs[e];
       v[e] = relu ? fmaxf(o, 0.f) : o;
     }
-    store_vec<T, N>(y + i * N, v);
+    store_vec<T, N>(y + r * C + c0, v);
   }
 }
 
@@ -145,34 +176,43 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const T* __restrict__ x, 
 template <typename T>
 __global__ void __launch_bounds__(256) bn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ mean,
                                                            const float* __restrict__ invstd, const float* __restrict__ gamma, const float* __restrict__ sums, float count,
-                                                           size_t M, int C, T* __restrict__ dx, T* __restrict__ dres) {
+                                                           size_t M, int C, int txw, T* __restrict__ dx, T* __restrict__ dres) {
   constexpr int N = VecT<T>::N;
-  const size_t nvec = M * (size_t)C / N;
+  const int tx = threadIdx.x % txw, ty = threadIdx.x / txw, tyn = 256 / txw;
+  const int c0 = (blockIdx.x * txw + tx) * N;
   const float inv_count = 1.f / count;
-  for (size_t i = blockIdx.x * (size_t)256 + threadIdx.x; i < nvec; i += (size_t)gridDim.x * 256) {
-    const int c0 = (int)((i * N) % C);
+  float k1[N], k2[N], k3[N], mu[N], is[N];
+#pragma unroll
+  for (int e = 0; e < N; e++) {
+    const int c = c0 + e;
+    mu[e] = mean[c];
+    is[e] = invstd[c];
+    k1[e] = (gamma ? gamma[c] : 1.f) * is[e];
+    k2[e] = sums[c] * inv_count;
+    k3[e] = sums[C + c] * inv_count;
+  }
+  for (size_t r = (size_t)blockIdx.y * tyn + ty; r < M; r += (size_t)gridDim.y * tyn) {
     float g[N], xv[N], yv[N], o[N];
-    load_vec<T, N>(dy + i * N, g);
-    load_vec<T, N>(x + i * N, xv);
+    load_vec<T, N>(dy + r * C + c0, g);
+    load_vec<T, N>(x + r * C + c0, xv);
     if (y) {
-      load_vec<T, N>(y + i * N, yv);
+      load_vec<T, N>(y + r * C + c0, yv);
 #pragma unroll
       for (int e = 0; e < N; e++) if (!(yv[e] > 0.f)) g[e] = 0.f;
     }
 #pragma unroll
-    for (int e = 0; e < N; e++) {
-      const int c = c0 + e;
-      const float xhat = (xv[e] - mean[c]) * invstd[c];
-      o[e] = (gamma ? gamma[c] : 1.f) * invstd[c] * (g[e] - sums[c] * inv_count - xhat * sums[C + c] * inv_count);
-    }
-    store_vec<T, N>(dx + i * N, o);
-    if (dres) store_vec<T, N>(dres + i * N, g);
+    for (int e = 0; e < N; e++) o[e] = k1[e] * (g[e] - k2[e] - (xv[e] - mu[e]) * is[e] * k3[e]);
+    store_vec<T, N>(dx + r * C + c0, o);
+    if (dres) store_vec<T, N>(dres + r * C + c0, g);
   }
 }
 
 // ---- max pooling, NHWC -----------------------------------------------------------------------------------------------------------------
+// forward: a thread handles one 16-byte channel group of one output pixel; it also records, per channel, which window position (dh * k + dw, first
+// maximum in row-major order) won, so the backward never re-reads the input.
 template <typename T>
-__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int Nb, int H, int W, int C, int Ho, int Wo, int k, int s, int p) {
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ idx, int Nb, int H, int W, int C, int Ho, int Wo,
+                                                          int k, int s, int p) {
   constexpr int N = VecT<T>::N;
   const size_t total = (size_t)Nb * Ho * Wo * (C / N);
   for (size_t i = blockIdx.x * (size_t)256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
@@ -182,8 +222,9 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ 
     r /= Wo;
     const int ho = (int)(r % Ho), n = (int)(r / Ho);
     float m[N];
+    uint8_t am[N];
 #pragma unroll
-    for (int e = 0; e < N; e++) m[e] = -CUDART_INF_F;
+    for (int e = 0; e < N; e++) { m[e] = -CUDART_INF_F; am[e] = 0; }
     for (int dh = 0; dh < k; dh++) {
       const int h = ho * s - p + dh;
       if (h < 0 || h >= H) continue;
@@ -193,46 +234,49 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const T* __restrict__ 
         float v[N];
         load_vec<T, N>(x + (((size_t)n * H + h) * W + w) * C + cg * N, v);
 #pragma unroll
-        for (int e = 0; e < N; e++) m[e] = fmaxf(m[e], v[e]);
+        for (int e = 0; e < N; e++)
+          if (v[e] > m[e] || (v[e] != v[e] && m[e] == m[e])) { m[e] = v[e]; am[e] = (uint8_t)(dh * k + dw); }
       }
     }
     store_vec<T, N>(y + i * N, m);
+    if (idx) {
+#pragma unroll
+      for (int e = 0; e < N; e++) idx[i * N + e] = am[e];
+    }
   }
 }
 
-// dx[n,h,w,c] = sum over the windows that contain (h,w) and whose first maximum (row-major scan) is (h,w) of dy
+// backward from the recorded positions: a thread owns one channel group of one INPUT pixel and visits the (at most ceil(k/s)^2) windows that contain it
 template <typename T>
-__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ dx, int Nb, int H, int W, int C, int Ho, int Wo,
-                                                          int k, int s, int p) {
-  const size_t total = (size_t)Nb * H * W * C;
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const uint8_t* __restrict__ idx, const T* __restrict__ dy, T* __restrict__ dx, int Nb, int H, int W, int C, int Ho,
+                                                          int Wo, int k, int s, int p) {
+  constexpr int N = VecT<T>::N;
+  const size_t total = (size_t)Nb * H * W * (C / N);
   for (size_t i = blockIdx.x * (size_t)256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
-    const int c = (int)(i % C);
-    size_t r = i / C;
+    const int cg = (int)(i % (C / N));
+    size_t r = i / (C / N);
     const int w = (int)(r % W);
     r /= W;
     const int h = (int)(r % H), n = (int)(r / H);
-    const float xv = (float)x[i];
-    float acc = 0.f;
+    float acc[N];
+#pragma unroll
+    for (int e = 0; e < N; e++) acc[e] = 0.f;
     const int ho_lo = max(0, (h + p - k + s) / s), ho_hi = min(Ho - 1, (h + p) / s);
     const int wo_lo = max(0, (w + p - k + s) / s), wo_hi = min(Wo - 1, (w + p) / s);
     for (int ho = ho_lo; ho <= ho_hi; ho++)
       for (int wo = wo_lo; wo <= wo_hi; wo++) {
-        // is (h, w) the first maximum of window (ho, wo)?
-        bool first = true;
-        for (int dh = 0; dh < k && first; dh++) {
-          const int hh = ho * s - p + dh;
-          if (hh < 0 || hh >= H) continue;
-          for (int dw = 0; dw < k; dw++) {
-            const int ww = wo * s - p + dw;
-            if (ww < 0 || ww >= W) continue;
-            const float v = (float)x[(((size_t)n * H + hh) * W + ww) * C + c];
-            const bool before = hh < h || (hh == h && ww < w);
-            if (v > xv || (before && v == xv)) { first = false; break; }
-          }
-        }
-        if (first) acc += (float)dy[(((size_t)n * Ho + ho) * Wo + wo) * C + c];
+        const int want = (h - (ho * s - p)) * k + (w - (wo * s - p));
+        const size_t o = (((size_t)n * Ho + ho) * Wo + wo) * C + cg * N;
+        uint8_t am[N];
+        if (N == 8) *reinterpret_cast<uint2*>(am) = *reinterpret_cast<const uint2*>(idx + o);
+        else *reinterpret_cast<uint32_t*>(am) = *reinterpret_cast<const uint32_t*>(idx + o);
+        float g[N];
+        load_vec<T, N>(dy + o, g);
+#pragma unroll
+        for (int e = 0; e < N; e++)
+          if (am[e] == want) acc[e] += g[e];
       }
-    dx[i] = (T)acc;
+    store_vec<T, N>(dx + i * N, acc);
   }
 }
 
@@ -371,15 +415,30 @@ inline int grid_for(size_t work) {
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
 }
 
+// grid of the column-resident apply kernels: x = column-group blocks, y = row blocks (about 16 CTAs per SM in total, bounded by the rows)
+inline dim3 apply_grid(int64_t M, int C, int vec, int& txw) {
+  const int groups = C / vec;
+  txw = 32;
+  while (txw > 1 && groups % txw) txw >>= 1;
+  const int gx = groups / txw, tyn = 256 / txw;
+  int64_t gy = (148 * 16 + gx - 1) / gx;
+  const int64_t maxy = (M + tyn - 1) / tyn;
+  gy = gy > maxy ? maxy : gy;
+  if (gy > 65535) gy = 65535;
+  return dim3((unsigned)gx, (unsigned)(gy < 1 ? 1 : gy));
+}
+
 template <typename T, int MODE>
-int col_stats_launch(const T* a, const T* x, const T* y, const float* mean, const float* invstd, size_t M, int C, float* partial, int nblk, cudaStream_t st) {
+int col_stats_launch(const T* a, const T* x, const T* y, const float* mean, const float* invstd, size_t M, int C, float* partial, float* sums, int nblk, cudaStream_t st) {
   constexpr int N = VecT<T>::N;
   if (C % N) return FT_ERR_ARG;
   const int groups = C / N;
   int txw = 32;
   while (txw > 1 && groups % txw) txw >>= 1;
   const size_t smem = 2 * (size_t)(256 / txw) * txw * N * sizeof(float);
-  col_stats_kernel<T, MODE><<<dim3(groups / txw, nblk), 256, smem, st>>>(a, x, y, mean, invstd, M, C, txw, partial);
+  if (groups / txw > 512) return FT_ERR_TOO_LARGE;
+  size_t smem_need = smem < 256 * sizeof(float) ? 256 * sizeof(float) : smem;
+  col_stats_kernel<T, MODE><<<dim3(groups / txw, nblk), 256, smem_need, st>>>(a, x, y, mean, invstd, M, C, txw, partial, sums);
   return (int)cudaGetLastError();
 }
 
@@ -391,7 +450,7 @@ FT_EXPORT int ft_bn_num_blocks(int64_t M, int C, int elem_bytes) {
   int txw = 32;
   while (txw > 1 && (C / vec) % txw) txw >>= 1;
   const int gx = C / vec / txw;
-  int64_t nb = (148 * 4 + gx - 1) / (gx < 1 ? 1 : gx);
+  int64_t nb = (148 * 2 + gx - 1) / (gx < 1 ? 1 : gx);
   const int64_t rows_per = 256 / txw;
   const int64_t maxb = (M + rows_per - 1) / rows_per;
   nb = nb > maxb ? maxb : nb;
@@ -402,11 +461,8 @@ FT_EXPORT int ft_bn_num_blocks(int64_t M, int C, int elem_bytes) {
 FT_EXPORT int ft_bn_stats(int is_bf16, const void* x, int64_t M, int C, float* partial, float* sums, cudaStream_t st) {
   if (M < 1 || C < 1) return FT_ERR_ARG;
   const int nblk = ft_bn_num_blocks(M, C, is_bf16 ? 2 : 4);
-  int e = is_bf16 ? col_stats_launch<__nv_bfloat16, 0>((const __nv_bfloat16*)x, nullptr, nullptr, nullptr, nullptr, (size_t)M, C, partial, nblk, st)
-                  : col_stats_launch<float, 0>((const float*)x, nullptr, nullptr, nullptr, nullptr, (size_t)M, C, partial, nblk, st);
-  if (e) return e;
-  col_stats_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, st>>>(partial, nblk, C, sums);
-  return (int)cudaGetLastError();
+  return is_bf16 ? col_stats_launch<__nv_bfloat16, 0>((const __nv_bfloat16*)x, nullptr, nullptr, nullptr, nullptr, (size_t)M, C, partial, sums, nblk, st)
+                 : col_stats_launch<float, 0>((const float*)x, nullptr, nullptr, nullptr, nullptr, (size_t)M, C, partial, sums, nblk, st);
 }
 
 // mean / invstd from sums over `count` elements per channel (count = M * world for SyncBatchNorm after the sums were all-reduced).
@@ -420,9 +476,10 @@ FT_EXPORT int ft_bn_finalize(const float* sums, int C, double count, float eps, 
 FT_EXPORT int ft_bn_apply(int is_bf16, const void* x, const float* mean, const float* invstd, const float* gamma, const float* beta, const void* residual, int relu,
                           int64_t M, int C, void* y, cudaStream_t st) {
   if (C % (is_bf16 ? 8 : 4)) return FT_ERR_ARG;
-  const size_t nvec = (size_t)M * C / (is_bf16 ? 8 : 4);
-  if (is_bf16) bn_apply_kernel<__nv_bfloat16><<<grid_for(nvec), 256, 0, st>>>((const __nv_bfloat16*)x, mean, invstd, gamma, beta, (const __nv_bfloat16*)residual, relu, (size_t)M, C, (__nv_bfloat16*)y);
-  else bn_apply_kernel<float><<<grid_for(nvec), 256, 0, st>>>((const float*)x, mean, invstd, gamma, beta, (const float*)residual, relu, (size_t)M, C, (float*)y);
+  int txw;
+  const dim3 grid = apply_grid(M, C, is_bf16 ? 8 : 4, txw);
+  if (is_bf16) bn_apply_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, mean, invstd, gamma, beta, (const __nv_bfloat16*)residual, relu, (size_t)M, C, txw, (__nv_bfloat16*)y);
+  else bn_apply_kernel<float><<<grid, 256, 0, st>>>((const float*)x, mean, invstd, gamma, beta, (const float*)residual, relu, (size_t)M, C, txw, (float*)y);
   return (int)cudaGetLastError();
 }
 
@@ -430,37 +487,36 @@ FT_EXPORT int ft_bn_apply(int is_bf16, const void* x, const float* mean, const f
 FT_EXPORT int ft_bn_bwd_stats(int is_bf16, const void* dy, const void* x, const void* y, const float* mean, const float* invstd, int64_t M, int C, float* partial,
                               float* sums, cudaStream_t st) {
   const int nblk = ft_bn_num_blocks(M, C, is_bf16 ? 2 : 4);
-  int e = is_bf16 ? col_stats_launch<__nv_bfloat16, 1>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, mean, invstd, (size_t)M, C, partial, nblk, st)
-                  : col_stats_launch<float, 1>((const float*)dy, (const float*)x, (const float*)y, mean, invstd, (size_t)M, C, partial, nblk, st);
-  if (e) return e;
-  col_stats_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, st>>>(partial, nblk, C, sums);
-  return (int)cudaGetLastError();
+  return is_bf16 ? col_stats_launch<__nv_bfloat16, 1>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, mean, invstd, (size_t)M, C, partial, sums, nblk, st)
+                 : col_stats_launch<float, 1>((const float*)dy, (const float*)x, (const float*)y, mean, invstd, (size_t)M, C, partial, sums, nblk, st);
 }
 
 FT_EXPORT int ft_bn_bwd_apply(int is_bf16, const void* dy, const void* x, const void* y, const float* mean, const float* invstd, const float* gamma, const float* sums,
                               double count, int64_t M, int C, void* dx, void* dres, cudaStream_t st) {
   if (C % (is_bf16 ? 8 : 4)) return FT_ERR_ARG;
-  const size_t nvec = (size_t)M * C / (is_bf16 ? 8 : 4);
-  if (is_bf16) bn_bwd_apply_kernel<__nv_bfloat16><<<grid_for(nvec), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, mean, invstd, gamma, sums, (float)count, (size_t)M, C, (__nv_bfloat16*)dx, (__nv_bfloat16*)dres);
-  else bn_bwd_apply_kernel<float><<<grid_for(nvec), 256, 0, st>>>((const float*)dy, (const float*)x, (const float*)y, mean, invstd, gamma, sums, (float)count, (size_t)M, C, (float*)dx, (float*)dres);
+  int txw;
+  const dim3 grid = apply_grid(M, C, is_bf16 ? 8 : 4, txw);
+  if (is_bf16) bn_bwd_apply_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, mean, invstd, gamma, sums, (float)count, (size_t)M, C, txw, (__nv_bfloat16*)dx, (__nv_bfloat16*)dres);
+  else bn_bwd_apply_kernel<float><<<grid, 256, 0, st>>>((const float*)dy, (const float*)x, (const float*)y, mean, invstd, gamma, sums, (float)count, (size_t)M, C, txw, (float*)dx, (float*)dres);
   return (int)cudaGetLastError();
 }
 
-FT_EXPORT int ft_maxpool2d_nhwc(int is_bf16, const void* x, void* y, int N, int H, int W, int C, int k, int s, int p, cudaStream_t st) {
+// idx (optional, u8 [N, Ho, Wo, C]): winning window position of every output element, consumed by ft_maxpool2d_nhwc_bwd. k * k <= 255.
+FT_EXPORT int ft_maxpool2d_nhwc(int is_bf16, const void* x, void* y, void* idx, int N, int H, int W, int C, int k, int s, int p, cudaStream_t st) {
   const int Ho = (H + 2 * p - k) / s + 1, Wo = (W + 2 * p - k) / s + 1;
-  if (C % (is_bf16 ? 8 : 4) || Ho < 1 || Wo < 1 || p >= k) return FT_ERR_ARG;
+  if (C % (is_bf16 ? 8 : 4) || Ho < 1 || Wo < 1 || p >= k || k * k > 255) return FT_ERR_ARG;
   const size_t total = (size_t)N * Ho * Wo * (C / (is_bf16 ? 8 : 4));
-  if (is_bf16) maxpool_fwd_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C, Ho, Wo, k, s, p);
-  else maxpool_fwd_kernel<float><<<grid_for(total), 256, 0, st>>>((const float*)x, (float*)y, N, H, W, C, Ho, Wo, k, s, p);
+  if (is_bf16) maxpool_fwd_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)idx, N, H, W, C, Ho, Wo, k, s, p);
+  else maxpool_fwd_kernel<float><<<grid_for(total), 256, 0, st>>>((const float*)x, (float*)y, (uint8_t*)idx, N, H, W, C, Ho, Wo, k, s, p);
   return (int)cudaGetLastError();
 }
 
-FT_EXPORT int ft_maxpool2d_nhwc_bwd(int is_bf16, const void* x, const void* dy, void* dx, int N, int H, int W, int C, int k, int s, int p, cudaStream_t st) {
+FT_EXPORT int ft_maxpool2d_nhwc_bwd(int is_bf16, const void* idx, const void* dy, void* dx, int N, int H, int W, int C, int k, int s, int p, cudaStream_t st) {
   const int Ho = (H + 2 * p - k) / s + 1, Wo = (W + 2 * p - k) / s + 1;
-  if (Ho < 1 || Wo < 1 || p >= k) return FT_ERR_ARG;
-  const size_t total = (size_t)N * H * W * C;
-  if (is_bf16) maxpool_bwd_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, Ho, Wo, k, s, p);
-  else maxpool_bwd_kernel<float><<<grid_for(total), 256, 0, st>>>((const float*)x, (const float*)dy, (float*)dx, N, H, W, C, Ho, Wo, k, s, p);
+  if (C % (is_bf16 ? 8 : 4) || Ho < 1 || Wo < 1 || p >= k || !idx) return FT_ERR_ARG;
+  const size_t total = (size_t)N * H * W * (C / (is_bf16 ? 8 : 4));
+  if (is_bf16) maxpool_bwd_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, st>>>((const uint8_t*)idx, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, N, H, W, C, Ho, Wo, k, s, p);
+  else maxpool_bwd_kernel<float><<<grid_for(total), 256, 0, st>>>((const uint8_t*)idx, (const float*)dy, (float*)dx, N, H, W, C, Ho, Wo, k, s, p);
   return (int)cudaGetLastError();
 }
 

@@ -230,26 +230,63 @@ class LlamaTPEngine:
         finally:
             _lib.kernels().ft_set_pdl(prev)
 
+    @torch.no_grad()
+    def profile_decode(self, steps: int = 10) -> Dict[str, float]:
+        """Per-kernel-class device time of an eager (no graph, ordinary launches) decode step, in microseconds per step, from CUDA events around
+        every launch: where a step's time goes when it is latency-bound. Advances the sequence by ``steps`` tokens."""
+        import os
+        old_env = os.environ.get("FT_DECODE_PDL")
+        os.environ["FT_DECODE_PDL"] = "0"
+        totals: Dict[str, float] = {}
+        try:
+            for it in range(steps + 2):
+                self._prof = []
+                self._decode_body()
+                torch.cuda.synchronize(self.dev)
+                if it >= 2:
+                    for name, e0, e1 in self._prof:
+                        totals[name] = totals.get(name, 0.0) + e0.elapsed_time(e1) * 1e3 / steps
+        finally:
+            self._prof = None
+            if old_env is None:
+                os.environ.pop("FT_DECODE_PDL", None)
+            else:
+                os.environ["FT_DECODE_PDL"] = old_env
+        totals["sum"] = sum(totals.values())
+        return totals
+
+    def _timed(self, name: str, fn, *args) -> None:
+        prof = getattr(self, "_prof", None)
+        if prof is None:
+            fn(*args)
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(*args)
+        e1.record()
+        prof.append((name, e0, e1))
+
     def _decode_body_inner(self) -> None:
         cfg, B = self.cfg, self.B
         self.x[:B] = self.embed[self.tokens]
         _lib.call("ft_rmsnorm_fwd", self.x, None, self.layers[0]["n1"], self.h, None, None, B, self.d, float(cfg.rms_norm_eps), _lib.S())
         scale = 1.0 / math.sqrt(self.D)
+        T = self._timed
         for li, L in enumerate(self.layers):
-            L["g_qkv"](self.h)
+            T("gemm_qkv", L["g_qkv"], self.h)
             g = L["g_qkv"]
-            _lib.call("ft_decode_qkv_rope_kvwrite", g.planes, g.splits, g.ldp, g.plane_stride, B, self.Hq, self.Hkv, self.D, self.positions,
-                      self.cos, self.sin, self.q, self.k_cache[li], self.v_cache[li], self.block_table, self.max_blocks, _lib.S())
-            _lib.call("ft_paged_attn_decode", self.q, self.k_cache[li], self.v_cache[li], self.block_table, self.max_blocks, self.seq_lens, B,
-                      self.Hq, self.Hkv, self.D, float(scale), self.nsplit, self.attn_ws, self.attn_ctr, self.attn, _lib.S())
-            L["g_o"](self.attn)
-            self._ar_norm(L["g_o"], L["n2"])
-            L["g_gu"](self.h)
+            T("rope_kvwrite", _lib.call, "ft_decode_qkv_rope_kvwrite", g.planes, g.splits, g.ldp, g.plane_stride, B, self.Hq, self.Hkv, self.D, self.positions,
+              self.cos, self.sin, self.q, self.k_cache[li], self.v_cache[li], self.block_table, self.max_blocks, _lib.S())
+            T("paged_attention", _lib.call, "ft_paged_attn_decode", self.q, self.k_cache[li], self.v_cache[li], self.block_table, self.max_blocks, self.seq_lens, B,
+              self.Hq, self.Hkv, self.D, float(scale), self.nsplit, self.attn_ws, self.attn_ctr, self.attn, _lib.S())
+            T("gemm_o", L["g_o"], self.attn)
+            T("allreduce_residual_norm", self._ar_norm, L["g_o"], L["n2"])
+            T("gemm_gate_up", L["g_gu"], self.h)
             g = L["g_gu"]
-            _lib.call("ft_decode_swiglu", g.planes, g.splits, g.ldp, g.plane_stride, B, self.F, self.act, _lib.S())
-            L["g_d"](self.act)
+            T("swiglu", _lib.call, "ft_decode_swiglu", g.planes, g.splits, g.ldp, g.plane_stride, B, self.F, self.act, _lib.S())
+            T("gemm_down", L["g_d"], self.act)
             nxt = self.layers[li + 1]["n1"] if li + 1 < len(self.layers) else self.final_norm
-            self._ar_norm(L["g_d"], nxt)
+            T("allreduce_residual_norm", self._ar_norm, L["g_d"], nxt)
         self.g_head(self.h)
         g = self.g_head
         _lib.call("ft_splitk_reduce", g.planes, g.splits, B, self.V, g.ldp, g.plane_stride, None, self.logits, self.V, 1, _lib.S())

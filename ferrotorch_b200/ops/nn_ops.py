@@ -109,19 +109,20 @@ class _MaxPoolNHWC(torch.autograd.Function):
         N, C, H, W = x.shape
         Ho, Wo = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
         y = torch.empty((N, C, Ho, Wo), device=x.device, dtype=x.dtype, memory_format=torch.channels_last)
-        _lib.call("ft_maxpool2d_nhwc", int(x.dtype == torch.bfloat16), x, y, N, H, W, C, k, s, p, _lib.S())
-        ctx.save_for_backward(x)
-        ctx.cfg = (k, s, p)
+        idx = torch.empty((N, Ho, Wo, C), device=x.device, dtype=torch.uint8) if ctx.needs_input_grad[0] else None
+        _lib.call("ft_maxpool2d_nhwc", int(x.dtype == torch.bfloat16), x, y, idx, N, H, W, C, k, s, p, _lib.S())
+        ctx.save_for_backward(idx)
+        ctx.cfg = (k, s, p, tuple(x.shape), x.dtype)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        (x,) = ctx.saved_tensors
-        k, s, p = ctx.cfg
-        N, C, H, W = x.shape
+        (idx,) = ctx.saved_tensors
+        k, s, p, shape, dtype = ctx.cfg
+        N, C, H, W = shape
         dy = dy.contiguous(memory_format=torch.channels_last)
-        dx = torch.empty_like(x)
-        _lib.call("ft_maxpool2d_nhwc_bwd", int(x.dtype == torch.bfloat16), x, dy, dx, N, H, W, C, k, s, p, _lib.S())
+        dx = torch.empty(shape, device=dy.device, dtype=dtype, memory_format=torch.channels_last)
+        _lib.call("ft_maxpool2d_nhwc_bwd", int(dtype == torch.bfloat16), idx, dy, dx, N, H, W, C, k, s, p, _lib.S())
         return dx, None, None, None
 
 
