@@ -10,10 +10,13 @@
 
 namespace {
 
+// Every product, sum and the quotient are individually rounded (no fused multiply-add, no approximate division), so the value equals the host
+// sweep's bit for bit and a pair sitting exactly at the threshold is classified the same way on both.
 FT_DEVICE float iou_of(const float4 a, const float4 b) {
   const float w = fmaxf(fminf(a.z, b.z) - fmaxf(a.x, b.x), 0.f), h = fmaxf(fminf(a.w, b.w) - fmaxf(a.y, b.y), 0.f);
-  const float inter = w * h;
-  return inter / ((a.z - a.x) * (a.w - a.y) + (b.z - b.x) * (b.w - b.y) - inter);
+  const float inter = __fmul_rn(w, h);
+  const float area_a = __fmul_rn(a.z - a.x, a.w - a.y), area_b = __fmul_rn(b.z - b.x, b.w - b.y);
+  return __fdiv_rn(inter, __fsub_rn(__fadd_rn(area_a, area_b), inter));
 }
 
 // mask[i * words + w] bit b = box (w*64+b) is suppressed by box i (only j > i are set). grid (words, words), 64 threads.

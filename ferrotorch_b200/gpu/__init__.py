@@ -664,6 +664,8 @@ class CudaRngManager:
 
     def fork_rng(self) -> None:
         """Remembers every generator's state; :meth:`join_rng` restores it, so the forked region can be replayed with identical draws."""
+        if torch.cuda.is_available():
+            self.generator(torch.cuda.current_device())            # the current device's generator exists from here on, so its state is captured
         self._stack.append({d: PhiloxState(*g.state()) for d, g in self._gens.items()})
 
     def join_rng(self) -> None:

@@ -46,18 +46,18 @@ class _Conv3x3Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight):
         wk = _krsc(weight)
-        ctx.save_for_backward(x, weight)
+        ctx.save_for_backward(x, weight, wk)
         return conv3x3_nhwc_raw(x, wk)
 
     @staticmethod
     def backward(ctx, dy):
-        x, weight = ctx.saved_tensors
+        x, weight, wk = ctx.saved_tensors
         dy = dy.contiguous(memory_format=torch.channels_last)
         dx = dw = None
         if ctx.needs_input_grad[0]:
             if dy.shape[1] % 64 == 0 and x.shape[1] % 8 == 0:
-                # W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci]
-                wt = weight.to(torch.bfloat16).permute(1, 2, 3, 0).flip(1, 2).contiguous()
+                # W'[ci, r, s, co] = W[co, 2 - r, 2 - s, ci], from the bf16 [co, r, s, ci] copy made in the forward
+                wt = wk.flip(1, 2).permute(3, 1, 2, 0).contiguous()
                 dx = conv3x3_nhwc_raw(dy, wt)
             else:
                 dx = torch.nn.grad.conv2d_input(x.shape, weight.to(dy.dtype), dy, padding=1)
