@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--decode", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ab-ar", action="store_true", help="after the timed run, time the same steps again with the other all-reduce+norm kernel form")
     ap.add_argument("--profile", action="store_true", help="after the timed run, report eager per-kernel-class device time per step")
     a = ap.parse_args()
     import torch
@@ -45,7 +46,7 @@ def main():
     cfg = LlamaConfig.llama3_70b() if a.model == "70b" else LlamaConfig.llama3_8b()
     if a.layers is not None:
         cfg.num_hidden_layers = a.layers
-    eng = LlamaTPEngine(cfg, TPContext(dev), max_batch=a.batch, max_seq=a.prompt + a.decode + a.warmup + 8, device=dev, seed=0, use_graph=not a.no_graph)
+    eng = LlamaTPEngine(cfg, TPContext(dev), max_batch=a.batch, max_seq=a.prompt + (a.decode + a.warmup) * (2 if a.ab_ar else 1) + 8, device=dev, seed=0, use_graph=not a.no_graph)
     g = torch.Generator().manual_seed(7)
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.prompt), generator=g).to(dev)
 
@@ -74,6 +75,22 @@ def main():
         t = torch.tensor([ms, prefill_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, prefill_ms = float(t[0]), float(t[1])
+    alt = None
+    if a.ab_ar:
+        eng.ar_cluster, eng.graph = not eng.ar_cluster, None
+        for _ in range(a.warmup):
+            eng.decode_step()
+        sync()
+        e0.record()
+        for _ in range(a.decode):
+            eng.decode_step()
+        e1.record()
+        sync()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        alt = {"ar_form": "cluster" if eng.ar_cluster else "grid-barrier", "ms_per_step": round(float(t[0]) / a.decode, 4)}
+        eng.ar_cluster, eng.graph = not eng.ar_cluster, None
     breakdown = None
     if a.profile:
         prof = eng.profile_decode(8)                     # eager launches with CUDA events around each kernel class (after the timed region)
@@ -93,7 +110,7 @@ def main():
             "prefill_ms": round(prefill_ms, 2), "prefill_tokens_per_s": round(a.batch * a.prompt / (prefill_ms / 1e3), 1),
             "weight_bytes_per_gpu": weight_bytes, "hbm_gbs_streamed": round(weight_bytes / (ms / a.decode / 1e3) / 1e9, 1),
             "gpu_launches": (_lib.launch_calls - l0) if a.no_graph else "graph replay", "kernel_status": status, "impl": "ours",
-            **({"eager_us_per_step_by_kernel": breakdown} if breakdown else {}),
+            **({"eager_us_per_step_by_kernel": breakdown} if breakdown else {}), **({"other_allreduce_form": alt} if alt else {}),
         }))
     if world > 1:
         dist.destroy_process_group()

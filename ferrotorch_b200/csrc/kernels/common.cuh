@@ -295,6 +295,25 @@ FT_DEVICE uint64_t globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+// Device-scope forms of the same handshake, for CTAs of one grid that hand data to one another through this GPU's memory.
+FT_DEVICE void red_release_gpu_add(uint32_t* p, uint32_t v) { asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+FT_DEVICE uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+FT_DEVICE bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t want, uint64_t timeout_ns) {
+  if ((int32_t)(ld_acquire_gpu(flag) - want) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if ((int32_t)(ld_acquire_gpu(flag) - want) >= 0) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (globaltimer_ns() - t0 > timeout_ns) return false;
+      __nanosleep(64);
+    }
+  }
+}
 // Wait until *flag >= want, giving up after timeout_ns. Returns false on timeout.
 FT_DEVICE bool wait_flag_ge(const uint32_t* flag, uint32_t want, uint64_t timeout_ns) {
   uint64_t t0 = globaltimer_ns();

@@ -16,6 +16,8 @@
 // Capability parity: KVPage/PagePool/PagedKVCache bookkeeping exists only on the CPU in the reference
 // (ferrotorch-nn/src/paged_attention.rs:59-518); its GPU inferencer has no KV cache and re-prefills every token
 // (ferrotorch-llama/examples/llama3_8b_gpu.rs:118-122, ferrotorch-llama/src/gpu.rs:518-700).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -435,6 +437,106 @@ __global__ void __launch_bounds__(256) decode_ar_residual_norm_kernel(const floa
   if (blockIdx.x == 0 && threadIdx.x == 0) sync[0] = seq;    // everybody is past barrier B, so nobody still needs the old value
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// plane sum -> all-reduce -> + residual -> RMSNorm, second form: no grid-wide barrier.
+//   A thread-block cluster of AR_CL CTAs owns one token row (each CTA d / AR_CL columns). The cross-rank handshake is per (row, column chunk):
+//   a CTA announces its chunk to every peer and waits only for the peers' same chunk; the row-wide sum of squares for the norm is combined
+//   inside the cluster through distributed shared memory. A step of this kernel costs one launch, one peer round trip and two cluster barriers,
+//   where the first form paid two grid barriers on top.
+//   flags[r] = rank r's flag block u32[MAXR][rows_pad * AR_CL]: flags[r][q][row * AR_CL + chunk] = last launch number rank q announced.
+//   sync: int[4] zeroed once: [0] launch number, [1] finished-CTA counter (self-resetting).
+// ------------------------------------------------------------------------------------------------------------
+constexpr int AR_CL = 4, AR_THREADS = 512;
+
+__global__ void __cluster_dims__(AR_CL, 1, 1) __launch_bounds__(AR_THREADS)
+decode_ar_residual_norm_cluster_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride, ArNormArgs a, int* __restrict__ sync,
+                                       __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, int rows, int rows_pad,
+                                       int d, float eps, uint32_t* status) {
+  namespace cg = cooperative_groups;
+  pdl_wait();
+  pdl_launch_dependents();
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ float red[32];
+  __shared__ float cta_ss;
+  const int row = blockIdx.x / AR_CL, chunk = blockIdx.x % AR_CL;
+  const int cols = d / AR_CL, c0 = chunk * cols;
+  const int seq = *reinterpret_cast<volatile int*>(sync) + 1;
+  const size_t slot = (size_t)(seq & 1) * rows_pad * d;
+  const int nflag = rows_pad * AR_CL, fidx = row * AR_CL + chunk;
+  // phase A: plane sum of this chunk into this rank's staging slot (float4 columns; the splits are independent loads)
+  float* mine = a.sym[a.rank] + slot + (size_t)row * d + c0;
+  const float* prow = partial + (size_t)row * ldp + c0;
+  for (int i = threadIdx.x * 4; i < cols; i += AR_THREADS * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int s = 0; s < splits; s++) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(prow + (size_t)s * plane_stride + i));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(mine + i) = acc;
+  }
+  bool ok = true;
+  if (a.world > 1) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < a.world) {
+      st_release_sys(a.flags[threadIdx.x] + (size_t)a.rank * nflag + fidx, (uint32_t)seq);
+      ok = wait_flag_ge(a.flags[a.rank] + (size_t)threadIdx.x * nflag + fidx, (uint32_t)seq, DEC_TIMEOUT_NS);
+      if (!ok) ft_set_status(status, FT_K_COMM, 14, threadIdx.x);
+    }
+    ok = !__syncthreads_or(!ok);              // on a timeout the CTA still walks through the cluster barriers below (its partners wait there)
+  } else {
+    __syncthreads();
+  }
+  // phase B: cross-rank sum in fixed rank order + residual; this chunk's share of the row's sum of squares
+  float ss = 0.f;
+  __nv_bfloat16* xr = x + (size_t)row * d + c0;
+  for (int i = threadIdx.x * 4; i < cols; i += AR_THREADS * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < a.world; r++) {
+      const float4 p = *reinterpret_cast<const float4*>(a.sym[r] + slot + (size_t)row * d + c0 + i);
+      v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    }
+    const uint2 raw = *reinterpret_cast<const uint2*>(xr + i);
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    __nv_bfloat162 o0 = __floats2bfloat162_rn(v.x + x0.x, v.y + x0.y), o1 = __floats2bfloat162_rn(v.z + x1.x, v.w + x1.y);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&o0);
+    pk.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(xr + i) = pk;
+    const float2 f0 = __bfloat1622float2(o0), f1 = __bfloat1622float2(o1);
+    ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) cta_ss = ss;
+  cluster.sync();
+  float tot = 0.f;
+  for (int r = 0; r < AR_CL; r++) tot += *cluster.map_shared_rank(&cta_ss, r);
+  cluster.sync();                             // nobody leaves while a partner may still read its shared memory
+  const float rstd = rsqrtf(tot / (float)d + eps);
+  __nv_bfloat16* hr = h + (size_t)row * d + c0;
+  for (int i = threadIdx.x * 4; i < cols; i += AR_THREADS * 4) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(xr + i), wr = *reinterpret_cast<const uint2*>(w + c0 + i);
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.x)), w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.y));
+    __nv_bfloat162 o0 = __floats2bfloat162_rn(x0.x * rstd * w0.x, x0.y * rstd * w0.y), o1 = __floats2bfloat162_rn(x1.x * rstd * w1.x, x1.y * rstd * w1.y);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&o0);
+    pk.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(hr + i) = pk;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(&sync[1], 1);
+    if (prev == (int)gridDim.x - 1) {         // every CTA has read the launch number: advance it for the next launch (or graph replay)
+      sync[1] = 0;
+      __threadfence();
+      sync[0] = seq;
+    }
+  }
+}
+
 inline int small_grid(size_t work, int block) {
   size_t g = (work + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > 592 ? 592 : g));
@@ -506,4 +608,18 @@ FT_EXPORT int ft_decode_ar_residual_norm(const float* partial, int splits, int64
   a.world = world;
   return (int)ft_launch_pdl(decode_ar_residual_norm_kernel, dim3(rows * chunks), dim3(256), 0, st, partial, splits, ldp, (size_t)plane_stride, a, sync,
                             (__nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)h, sumsq, rows, rows_pad, d, chunks, eps, ft_status_ptr());
+}
+
+// Cluster form of ft_decode_ar_residual_norm (no grid barriers). flag blocks: u32[8][rows_pad * 4] per rank, zeroed once; sync: int[4] zeroed once.
+// d must be a multiple of 16. Launch numbers live in sync[0], so a captured launch advances on every graph replay.
+FT_EXPORT int ft_decode_ar_residual_norm_cluster(const float* partial, int splits, int64_t ldp, int64_t plane_stride, void* const* sym_ptrs, void* const* flag_ptrs,
+                                                 int rank, int world, int* sync, void* x, const void* w, void* h, int rows, int rows_pad, int d, float eps,
+                                                 cudaStream_t st) {
+  if (world < 1 || world > MAXR || rows < 1 || rows > rows_pad || d % (AR_CL * 4) || (ldp & 3) || (plane_stride & 3)) return FT_ERR_ARG;
+  ArNormArgs a;
+  for (int i = 0; i < MAXR; i++) { a.sym[i] = i < world ? (float*)sym_ptrs[i] : nullptr; a.flags[i] = i < world ? (uint32_t*)flag_ptrs[i] : nullptr; }
+  a.rank = rank;
+  a.world = world;
+  return (int)ft_launch_pdl(decode_ar_residual_norm_cluster_kernel, dim3(rows * AR_CL), dim3(AR_THREADS), 0, st, partial, splits, ldp, (size_t)plane_stride, a, sync,
+                            (__nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)h, rows, rows_pad, d, eps, ft_status_ptr());
 }

@@ -77,11 +77,52 @@ FT_DEVICE float epi_act(int act, float x) {
   }
 }
 
+// Tail balancing. With T output tiles on G persistent CTAs the last round holds T % G tiles and the other CTAs idle through it. When that
+// remainder is at most G / 2 the launcher cuts each of those tiles into S = G / remainder K slices, one per otherwise idle CTA: slices 1..S-1
+// ("helpers") leave their f32 accumulators in a workspace and bump a counter per (tile, TMEM lane quarter); slice 0 (the "owner") adds them to
+// its own accumulator and runs the ordinary epilogue. All slices of a tile are the last work item of distinct CTAs of one resident grid and
+// helpers never wait, so the owner's (deadline-bounded) wait cannot deadlock. The counters are reset by the owner: the workspace is reusable
+// by the next launch on the same stream.
+struct TailArgs {
+  int tiles;                     // number of output tiles cut into slices (they are the last `tiles` of the tile order); 0 = off
+  int slices;                    // S
+  float* ws;                     // [tiles][S-1][4 quarters][chunks][EPI_COLS/4][32 lanes] float4
+  uint32_t* cnt;                 // [tiles][4], zero between launches
+};
+
+struct WorkItem {
+  int tile, split, kb0, kb1;
+  int tail;                      // index of the tail tile or -1
+  int slice;                     // K slice of a tail tile (0 = owner)
+};
+
+FT_DEVICE WorkItem decode_item(int item, int k_splits, int kb_per, int num_kb_total, int full_items, const TailArgs& t) {
+  WorkItem w;
+  if (item < full_items) {
+    w.tile = item / k_splits;
+    w.split = item % k_splits;
+    w.kb0 = w.split * kb_per;
+    w.kb1 = min(num_kb_total, w.kb0 + kb_per);
+    w.tail = -1;
+    w.slice = 0;
+  } else {
+    const int j = item - full_items;
+    const int per = (num_kb_total + t.slices - 1) / t.slices;
+    w.tail = j / t.slices;
+    w.slice = j % t.slices;
+    w.tile = full_items + w.tail;          // tail balancing runs with k_splits == 1 only
+    w.split = 0;
+    w.kb0 = w.slice * per;
+    w.kb1 = min(num_kb_total, w.kb0 + per);
+  }
+  return w;
+}
+
 template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmD, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-               int k_splits, uint32_t* status, const EpiArgs epi) {
+               int k_splits, uint32_t* status, const EpiArgs epi, const TailArgs tail) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -102,7 +143,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   // spread the weight stream over every SM. k_splits == 1 is the ordinary GEMM.
   const int num_kb_total = (K + BK - 1) / BK;
   const int kb_per = (num_kb_total + k_splits - 1) / k_splits;
-  const int num_tiles = tiles_m * tiles_n * k_splits;
+  const int full_items = tiles_m * tiles_n * k_splits - tail.tiles;
+  const int num_tiles = full_items + tail.tiles * tail.slices;          // work items
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -126,8 +168,9 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m0, n0;
-        tile_coords(tile / k_splits, tiles_m, tiles_n, m0, n0);
-        const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
+        const WorkItem wi = decode_item(tile, k_splits, kb_per, num_kb_total, full_items, tail);
+        tile_coords(wi.tile, tiles_m, tiles_n, m0, n0);
+        const int kb0 = wi.kb0, kb1 = wi.kb1;
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait_deadline(&empty_bar[s], phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 1, s); ok = false; break; }
           mbar_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
@@ -164,7 +207,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait_deadline(&tempty_bar[acc], acc_phase ^ 1)) { ft_set_status(status, FT_K_GEMM, 2, acc); ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
+        const WorkItem wi = decode_item(tile, k_splits, kb_per, num_kb_total, full_items, tail);
+        const int kb0 = wi.kb0, kb1 = wi.kb1;
         if (kb0 >= kb1) {   // an empty split (K not divisible): nothing to accumulate; the epilogue stores zeros for it
           umma_commit(&tfull_bar[acc]);
           acc ^= 1;
@@ -208,12 +252,28 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int m0, n0;
-      tile_coords(tile / k_splits, tiles_m, tiles_n, m0, n0);
-      const int split = tile % k_splits;
-      const bool empty_split = split * kb_per >= num_kb_total;
+      const WorkItem wi = decode_item(tile, k_splits, kb_per, num_kb_total, full_items, tail);
+      tile_coords(wi.tile, tiles_m, tiles_n, m0, n0);
+      const int split = wi.split;
+      const bool empty_split = wi.kb0 >= wi.kb1;
       if (!mbar_wait_deadline(&tfull_bar[acc], acc_phase)) { if (lane == 0) ft_set_status(status, FT_K_GEMM, 4, acc); ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      // tail tile: where this warp's quarter of every helper slice lives, and (owner) the wait for the helpers
+      constexpr int WS_CHUNK = (OUT_F32 ? 32 : 64) * 32;          // floats per (quarter, chunk)
+      constexpr int WS_SLICE = 4 * (BN / (OUT_F32 ? 32 : 64)) * WS_CHUNK;
+      float* ws_q = nullptr;
+      if (wi.tail >= 0) {
+        ws_q = tail.ws + (size_t)wi.tail * (tail.slices - 1) * WS_SLICE + (size_t)q * (BN / (OUT_F32 ? 32 : 64)) * WS_CHUNK;
+        if (wi.slice == 0) {
+          uint32_t* c = tail.cnt + wi.tail * 4 + q;
+          if (lane == 0) {
+            if (!wait_flag_ge_gpu(c, (uint32_t)(tail.slices - 1), 2000000000ull)) ft_set_status(status, FT_K_GEMM, 5, q);
+            *c = 0u;
+          }
+          __syncwarp();
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < CHUNKS; c++) {
         uint8_t* buf = my_buf + (nstore % EPI_BUFS) * EPI_BUF_BYTES;
@@ -227,6 +287,25 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (empty_split) {
 #pragma unroll
           for (int i = 0; i < (OUT_F32 ? 32 : 64); i++) v[i] = 0u;
+        }
+        if (wi.tail >= 0) {
+          if (wi.slice != 0) {                 // helper: park the partial accumulator, nothing else
+            uint4* dst = reinterpret_cast<uint4*>(ws_q + (size_t)(wi.slice - 1) * WS_SLICE + (size_t)c * WS_CHUNK);
+#pragma unroll
+            for (int i = 0; i < EPI_COLS / 4; i++) dst[i * 32 + lane] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            continue;
+          }
+          for (int hs = 0; hs < tail.slices - 1; hs++) {
+            const uint4* src = reinterpret_cast<const uint4*>(ws_q + (size_t)hs * WS_SLICE + (size_t)c * WS_CHUNK);
+#pragma unroll
+            for (int i = 0; i < EPI_COLS / 4; i++) {
+              const uint4 p = __ldcg(src + i * 32 + lane);
+              v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + __uint_as_float(p.x));
+              v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + __uint_as_float(p.y));
+              v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + __uint_as_float(p.z));
+              v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + __uint_as_float(p.w));
+            }
+          }
         }
         const int col0 = n0 + c * EPI_COLS;
         if (bias != nullptr) {
@@ -293,6 +372,11 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) tma_store_commit();
         nstore++;
       }
+      if (wi.tail >= 0 && wi.slice != 0) {   // helper: publish this quarter of the slice to the owner
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) red_release_gpu_add(tail.cnt + wi.tail * 4 + q, 1u);
+      }
       // all TMEM reads of this accumulator are complete (tmem_ld_wait above)
       tc_fence_before();
       __syncwarp();
@@ -311,9 +395,60 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+// Workspace of the tail slices: one per (device, stream) that launches GEMMs, so that launches on different streams never share one.
+struct TailWs {
+  cudaStream_t stream;
+  float* ws;
+  uint32_t* cnt;
+  int sms;
+};
+constexpr int TAIL_SLOTS = 4, TAIL_MAX_SLICES = 8;
+TailWs g_tail_ws[64][TAIL_SLOTS] = {};
+int g_tail_enabled = -1;
+
+TailArgs plan_tail(int dev, int tiles, int num_kb, int k_splits, int sms, cudaStream_t stream) {
+  TailArgs t{0, 1, nullptr, nullptr};
+  if (g_tail_enabled < 0) {
+    const char* e = getenv("FT_GEMM_TAIL");
+    g_tail_enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (!g_tail_enabled || k_splits != 1 || tiles <= sms) return t;
+  const int rem = tiles % sms;
+  if (rem == 0) return t;
+  int slices = sms / rem;
+  if (slices > TAIL_MAX_SLICES) slices = TAIL_MAX_SLICES;
+  if (slices > num_kb / 4) slices = num_kb / 4;
+  if (slices < 2) return t;
+  TailWs* slot = nullptr;
+  for (int i = 0; i < TAIL_SLOTS && !slot; i++)
+    if (g_tail_ws[dev][i].ws && g_tail_ws[dev][i].stream == stream && g_tail_ws[dev][i].sms == sms) slot = &g_tail_ws[dev][i];
+  if (!slot) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return t; }
+    for (int i = 0; i < TAIL_SLOTS && !slot; i++)
+      if (!g_tail_ws[dev][i].ws) slot = &g_tail_ws[dev][i];
+    if (!slot) return t;
+    // slices * rem <= sms, so (slices - 1) * rem tile-sized f32 partials fit in sms tiles
+    float* ws = nullptr;
+    uint32_t* cnt = nullptr;
+    if (cudaMalloc(&ws, (size_t)sms * BM * BN * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return t; }
+    if (cudaMalloc(&cnt, (size_t)sms * 4 * sizeof(uint32_t)) != cudaSuccess || cudaMemset(cnt, 0, (size_t)sms * 4 * sizeof(uint32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(ws);
+      return t;
+    }
+    *slot = TailWs{stream, ws, cnt, sms};
+  }
+  t.tiles = rem;
+  t.slices = slices;
+  t.ws = slot->ws;
+  t.cnt = slot->cnt;
+  return t;
+}
+
 template <bool A_MN, bool B_MN, bool OUT_F32>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, const void* bias, int M, int N, int K,
-           int k_splits, int num_sms, cudaStream_t stream, const EpiArgs& epi) {
+           int k_splits, int num_sms, cudaStream_t stream, const EpiArgs& epi, const TailArgs& tail) {
   auto kern = ft_gemm_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
@@ -323,7 +458,7 @@ int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
   return (int)ft_launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream, tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                            k_splits, ft_status_ptr(), epi);
+                            k_splits, ft_status_ptr(), epi, tail);
 }
 
 int g_num_sms[64] = {0};
@@ -356,12 +491,19 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
   if (r) return r;
 
   const int sms = g_num_sms[dev];
+  const TailArgs tail = plan_tail(dev, ((M + BM - 1) / BM) * ((N + BN - 1) / BN), (K + BK - 1) / BK, k_splits, sms, stream);
 #define FT_GEMM_CASE(AM, BMN, OF) \
-  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream, epi);
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream, epi, tail);
   FT_GEMM_CASE(0, 0, 0) FT_GEMM_CASE(0, 1, 0) FT_GEMM_CASE(1, 0, 0) FT_GEMM_CASE(1, 1, 0)
   FT_GEMM_CASE(0, 0, 1) FT_GEMM_CASE(0, 1, 1) FT_GEMM_CASE(1, 0, 1) FT_GEMM_CASE(1, 1, 1)
 #undef FT_GEMM_CASE
   return FT_ERR_ARG;
+}
+
+// Switches the tail balancing of ft_gemm_kernel on (1) or off (0). The environment variable FT_GEMM_TAIL=0 turns it off from the start.
+FT_EXPORT int ft_gemm_set_tail(int on) {
+  g_tail_enabled = on ? 1 : 0;
+  return FT_OK;
 }
 
 // D[M,N] = A (x) B (+bias). All pointers are device pointers; lda/ldb/ldd in elements.

@@ -108,3 +108,30 @@ def test_exact_gemm_gemv_and_split_k_path():
     assert (dw - ref).abs().max() < 0.05 * ref.abs().max().clamp_min(1)
     bb = ops.bmm(torch.randn(4, 128, 64, device="cuda", generator=g).bfloat16(), torch.randn(4, 64, 96, device="cuda", generator=g).bfloat16())
     assert bb.shape == (4, 128, 96)
+
+
+@pytest.mark.parametrize("M,N,K,f32_out", [(4096, 4096, 512, False), (4096, 6144, 1024, False), (4096, 4096, 768, True), (4000, 4072, 520, False)])
+def test_gemm_tail_slices_match_unsplit(M, N, K, f32_out):
+    """Output-tile counts that leave a short last round: the K-sliced tail tiles must reproduce the unsplit result (f32 sums in a different
+    order: equal up to rounding of the output dtype) and stay deterministic."""
+    from ferrotorch_b200 import _lib
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    res = torch.randn(M, N, device="cuda").to(torch.float32 if f32_out else torch.bfloat16)
+    kw = dict(bias=bias, residual=res, act="relu", out_dtype=torch.float32 if f32_out else None)
+    _lib.call("ft_gemm_set_tail", 0)
+    try:
+        plain = ops.gemm(a, b, **kw)
+        _lib.call("ft_gemm_set_tail", 1)
+        t1 = ops.gemm(a, b, **kw)
+        t2 = ops.gemm(a, b, **kw)
+    finally:
+        _lib.call("ft_gemm_set_tail", 1)
+    assert _lib.read_status() == 0
+    assert torch.equal(t1, t2)
+    ref = torch.relu(a.float() @ b.float().t() + bias.float()) + res.float()
+    scale = ref.abs().max().item()
+    assert (t1.float() - ref).abs().max().item() <= (2e-3 if f32_out else 1e-2) * scale + 1e-2
+    assert (t1.float() - plain.float()).abs().max().item() <= (1e-5 if f32_out else 8e-3) * scale
