@@ -410,7 +410,7 @@ TailArgs plan_tail(int dev, int tiles, int num_kb, int k_splits, int sms, cudaSt
   TailArgs t{0, 1, nullptr, nullptr};
   if (g_tail_enabled < 0) {
     const char* e = getenv("FT_GEMM_TAIL");
-    g_tail_enabled = (e && e[0] == '0') ? 0 : 1;
+    g_tail_enabled = (e && e[0] == '1') ? 1 : 0;
   }
   if (!g_tail_enabled || k_splits != 1 || tiles <= sms) return t;
   const int rem = tiles % sms;
@@ -500,7 +500,9 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
   return FT_ERR_ARG;
 }
 
-// Switches the tail balancing of ft_gemm_kernel on (1) or off (0). The environment variable FT_GEMM_TAIL=0 turns it off from the start.
+// Switches the tail balancing of ft_gemm_kernel on (1) or off (0). It is off unless the environment variable FT_GEMM_TAIL=1 is set when the
+// first GEMM is launched: the sliced schedule has been checked on the host (coverage of every (tile, k-block) exactly once, tail items last
+// on distinct CTAs) but not yet timed on hardware.
 FT_EXPORT int ft_gemm_set_tail(int on) {
   g_tail_enabled = on ? 1 : 0;
   return FT_OK;

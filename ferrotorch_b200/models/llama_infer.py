@@ -183,9 +183,12 @@ class LlamaTPEngine:
         self.attn_ctr = torch.zeros(B * self.Hkv, device=dev, dtype=torch.int32)
         # all-reduce staging: two slots of [PAD_ROWS, d] floats per rank + flag block + grid-barrier ints
         self.ar_sym, self.ar_sym_ptrs, self._ar_sym_buf = self.ctx.symmetric(2 * PAD_ROWS * d, torch.float32)
-        self.ar_flags, self.ar_flag_ptrs, self._ar_flag_buf = self.ctx.symmetric(8 * PAD_ROWS * 4, torch.int32)
+        self.ar_flags, self.ar_flag_ptrs, self._ar_flag_buf = self.ctx.symmetric(8, torch.int32)
+        # the cluster form of the kernel numbers its launches and keeps its flags apart from the grid-barrier form: either may run at any step
+        self.ar_flags_cl, self.ar_flag_ptrs_cl, self._ar_flag_buf_cl = self.ctx.symmetric(8 * PAD_ROWS * 4, torch.int32)
+        self.ar_sync_cl = torch.zeros(4, device=dev, dtype=torch.int32)
         import os
-        self.ar_cluster = d % 16 == 0 and os.environ.get("FT_DECODE_AR", "cluster") == "cluster"
+        self.ar_cluster = d % 16 == 0 and os.environ.get("FT_DECODE_AR", "grid") == "cluster"
         self.ar_sync = torch.zeros(4, device=dev, dtype=torch.int32)
         self.ar_chunks = max(1, min(16, 128 // max(B, 1)))
         while d % self.ar_chunks:
@@ -202,8 +205,8 @@ class LlamaTPEngine:
     # ------------------------------------------------------------------ pieces -------------------------------------------------------------------
     def _ar_norm(self, gemm: _SplitKGemm, w: torch.Tensor) -> None:
         if self.ar_cluster:
-            _lib.call("ft_decode_ar_residual_norm_cluster", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride, self.ar_sym_ptrs, self.ar_flag_ptrs,
-                      self.ctx.rank, self.ctx.world, self.ar_sync, self.x, w, self.h, self.B, PAD_ROWS, self.d, float(self.cfg.rms_norm_eps), _lib.S())
+            _lib.call("ft_decode_ar_residual_norm_cluster", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride, self.ar_sym_ptrs, self.ar_flag_ptrs_cl,
+                      self.ctx.rank, self.ctx.world, self.ar_sync_cl, self.x, w, self.h, self.B, PAD_ROWS, self.d, float(self.cfg.rms_norm_eps), _lib.S())
             return
         _lib.call("ft_decode_ar_residual_norm", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride, self.ar_sym_ptrs, self.ar_flag_ptrs,
                   self.ctx.rank, self.ctx.world, self.ar_sync, self.x, w, self.h, self.ar_sumsq, self.B, PAD_ROWS, self.d, self.ar_chunks,

@@ -71,9 +71,12 @@ def bench_gemm(results):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         med, best = time_fn(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
         from ferrotorch_b200 import _lib
-        _lib.call("ft_gemm_set_tail", 0)                 # the same launch with the last round of tiles left unsliced
-        nmed, _ = time_fn(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
-        _lib.call("ft_gemm_set_tail", 1)
+        nmed = None
+        if os.environ.get("FT_GEMM_TAIL") == "1":        # opt-in: the same launch with the last round of tiles cut into K slices
+            nmed = med
+            _lib.call("ft_gemm_set_tail", 1)
+            med, best = time_fn(lambda: ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out))
+            _lib.call("ft_gemm_set_tail", 0)
         A = a.t() if a_mn else a
         Bm = b if b_mn else b.t()
         lmed, lbest = time_fn(lambda: torch.matmul(A, Bm, out=out))

@@ -1,4 +1,6 @@
 """tcgen05 GEMM against an f32 PyTorch reference, every operand-layout combination, ragged sizes."""
+import os
+
 import pytest
 import torch
 
@@ -110,6 +112,7 @@ def test_exact_gemm_gemv_and_split_k_path():
     assert bb.shape == (4, 128, 96)
 
 
+@pytest.mark.skipif(os.environ.get("FT_GEMM_TAIL") != "1", reason="tail slices are opt-in (FT_GEMM_TAIL=1)")
 @pytest.mark.parametrize("M,N,K,f32_out", [(4096, 4096, 512, False), (4096, 6144, 1024, False), (4096, 4096, 768, True), (4000, 4072, 520, False)])
 def test_gemm_tail_slices_match_unsplit(M, N, K, f32_out):
     """Output-tile counts that leave a short last round: the K-sliced tail tiles must reproduce the unsplit result (f32 sums in a different
