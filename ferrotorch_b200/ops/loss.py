@@ -18,7 +18,9 @@ def cross_entropy_fwd_bwd(logits2: torch.Tensor, targets: torch.Tensor, *, ignor
     """
     rows, V = logits2.shape
     t = targets.reshape(-1).contiguous()
-    if logits2.is_cuda and logits2.dtype in (torch.bfloat16, torch.float32):
+    # the kernel reads rows with 16-byte loads: the row pitch must be a multiple of 16 bytes (pad the vocabulary dimension otherwise)
+    aligned = logits2.stride(1) == 1 and logits2.stride(0) % (8 if logits2.dtype == torch.bfloat16 else 4) == 0 and logits2.data_ptr() % 16 == 0
+    if logits2.is_cuda and logits2.dtype in (torch.bfloat16, torch.float32) and aligned:
         loss_rows = torch.empty(rows, device=logits2.device, dtype=torch.float32)
         out = torch.empty(2, device=logits2.device, dtype=torch.float32)
         dl = None
