@@ -7,7 +7,7 @@ transforms (``grad``, ``jacobian``, ``hessian``, ``jvp``, ``vjp``, ``jacfwd``, f
 implicit differentiation, the dispatcher keys, and the op profiler hook.
 
 Reference parity: ferrotorch-core/src/{device.rs, dtype.rs, tensor.rs, creation.rs, autograd/*.rs, vmap.rs, dispatch.rs,
-profiler_hook.rs, error.rs} (file:line index in the survey's component table).
+profiler_hook.rs, error.rs}.
 """
 from __future__ import annotations
 

@@ -3,7 +3,7 @@ hand-written sm_100a kernels for bf16 CUDA tensors; the long tail re-uses PyTorc
 reference's names.
 
 Reference parity: ferrotorch-nn/src/{activation,linear,lazy_linear,lora,se,conv,lazy_conv,lazy_conv_transpose,lazy_norm,norm,
-pooling,dropout,embedding,identity,padding,rnn,rnn_utils,attention,transformer,loss,upsample}.rs (symbol index in the survey appendix).
+pooling,dropout,embedding,identity,padding,rnn,rnn_utils,attention,transformer,loss,upsample}.rs.
 """
 from __future__ import annotations
 
