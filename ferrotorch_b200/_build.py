@@ -109,6 +109,29 @@ def build_runtime(verbose=False):
     return lib
 
 
+SANITIZERS = {"thread": "thread", "address": "address,undefined"}
+
+
+def build_runtime_selftest(sanitizer: str, out_path) -> Path:
+    """Builds the host runtime together with its self-test driver (``csrc/runtime/selftest/runtime_selftest.cpp``: ranks as threads over the
+    in-process fabric and loopback TCP, the loader and planner entry points) as one executable under ThreadSanitizer (``"thread"``) or
+    AddressSanitizer + UBSan (``"address"``). Raises ``subprocess.CalledProcessError`` with the compiler output if the toolchain lacks the
+    sanitizer runtime."""
+    out_path = Path(out_path)
+    # the configured compiler may ship without the sanitizer runtimes; the system compiler usually has them
+    compilers = list(dict.fromkeys(c for c in (CXX, shutil.which("g++"), "/usr/bin/g++", shutil.which("clang++")) if c))
+    last = None
+    for cxx in compilers:
+        cmd = [cxx, "-std=c++20", "-O1", "-g", f"-fsanitize={SANITIZERS[sanitizer]}", "-fno-omit-frame-pointer", "-pthread",
+               *[str(s) for s in runtime_sources()], str(CSRC / "runtime" / "selftest" / "runtime_selftest.cpp"), "-o", str(out_path)]
+        try:
+            subprocess.run(cmd, check=True, capture_output=True, text=True)
+            return out_path
+        except (subprocess.CalledProcessError, FileNotFoundError) as e:
+            last = e
+    raise last
+
+
 def build_all(verbose=False):
     OUT.mkdir(parents=True, exist_ok=True)
     k = build_kernels(verbose)
@@ -118,7 +141,11 @@ def build_all(verbose=False):
 
 if __name__ == "__main__":
     v = "-v" in sys.argv
-    if "--ptxas" in sys.argv:
+    if "--selftest" in sys.argv:
+        kind = sys.argv[sys.argv.index("--selftest") + 1]
+        exe = build_runtime_selftest(kind, OUT / f"runtime_selftest_{kind}")
+        sys.exit(subprocess.run([str(exe)]).returncode)
+    elif "--ptxas" in sys.argv:
         for o in OBJ.glob("*_cu.o"):
             o.unlink()
         build_kernels(ptxas_info=True)

@@ -285,7 +285,7 @@ class SimBackend : public Backend {
     std::vector<uint8_t> m = std::move(c.msgs.front());
     c.msgs.pop_front();
     if (m.size() != n) return E_SIZE_MISMATCH;
-    std::memcpy(data, m.data(), n);
+    if (n) std::memcpy(data, m.data(), n);
     return OK;
   }
  private:
@@ -356,13 +356,13 @@ static int allreduce_star(Backend& b, T* data, size_t n, int op, int64_t timeout
   return b.recv(data, bytes, 0, timeout_ms);
 }
 
-// Ring all-reduce (sum/mean): chunk i = [i*n/N, (i+1)*n/N); N-1 reduce-scatter steps then N-1 all-gather steps;
+// Ring all-reduce (every reduce op): chunk i = [i*n/N, (i+1)*n/N); N-1 reduce-scatter steps then N-1 all-gather steps;
 // needs a backend where neighbours are connected (full mesh TCP or the simulated fabric).
 template <typename T>
 static int allreduce_ring(Backend& b, T* data, size_t n, int op, int64_t timeout_ms) {
   const int r = b.rank(), w = b.world();
   if (w == 1) return OK;
-  if (op != SUM && op != MEAN) return E_UNSUPPORTED;
+  if (op < SUM || op > PROD) return E_UNSUPPORTED;
   auto lo = [&](int i) { return (size_t)((uint64_t)n * (uint64_t)i / (uint64_t)w); };
   const int next = (r + 1) % w, prev = (r + w - 1) % w;
   std::vector<T> tmp(n / w + 2);
@@ -377,8 +377,7 @@ static int allreduce_ring(Backend& b, T* data, size_t n, int op, int64_t timeout
     const int sc = (r - s + w) % w, rc = (r - s - 1 + w) % w;
     int e = exchange(data + lo(sc), lo(sc + 1) - lo(sc), tmp.data(), lo(rc + 1) - lo(rc));
     if (e) return e;
-    T* dst = data + lo(rc);
-    for (size_t i = 0, m = lo(rc + 1) - lo(rc); i < m; i++) dst[i] += tmp[i];
+    reduce_into(data + lo(rc), tmp.data(), lo(rc + 1) - lo(rc), op);
   }
   for (int s = 0; s < w - 1; s++) {
     const int sc = (r + 1 - s + w) % w, rc = (r - s + w) % w;
