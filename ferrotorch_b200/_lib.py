@@ -27,7 +27,8 @@ _runtime = None
 c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
 _ERR_NAMES = {-1: "invalid argument / unsupported shape or alignment", -2: "CUDA driver entry point unavailable",
-              -3: "tensor-map encode refused", -4: "request exceeds a compiled-in maximum"}
+              -3: "tensor-map encode refused", -4: "request exceeds a compiled-in maximum",
+              -5: "guard bytes behind an allocation were overwritten"}
 
 
 def _load(name: str):

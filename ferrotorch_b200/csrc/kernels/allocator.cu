@@ -12,6 +12,7 @@
 
 #include <cstdint>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <set>
@@ -50,6 +51,11 @@ struct Allocator {
   std::vector<Block*> deferred;              // freed blocks still in use on another stream
   int64_t allocated = 0, reserved = 0, peak_allocated = 0, peak_reserved = 0, n_alloc = 0, n_free = 0, n_segment_alloc = 0, n_cache_hit = 0, n_oom = 0;
   int64_t budget = -1;                       // max reserved bytes, -1 = unlimited
+  // Debug aid: with canary > 0 every block gets `canary` extra bytes behind the requested size, filled with 0xA5 when the block is handed out
+  // and compared when it is freed; a mismatch (a write past the end of the allocation) is counted and reported by the free call.
+  size_t canary = 0;
+  int64_t n_canary_bad = 0;
+  static constexpr unsigned char kCanaryByte = 0xA5;
 
   static size_t round_size(size_t n) { return n < kMinBlock ? kMinBlock : (n + kMinBlock - 1) / kMinBlock * kMinBlock; }
   static size_t segment_size(size_t n) {
@@ -121,7 +127,7 @@ struct Allocator {
     std::lock_guard<std::mutex> lk(mu);
     if (n == 0) { *out = nullptr; return 0; }
     poll_deferred();
-    const size_t size = round_size(n);
+    const size_t size = round_size(n + canary);
     const bool small = size <= kSmallSize;
     auto& pool = small ? small_free : large_free;
     Block key{nullptr, size, stream};
@@ -165,7 +171,21 @@ struct Allocator {
     if (allocated > peak_allocated) peak_allocated = allocated;
     n_alloc++;
     *out = b->ptr;
+    if (canary) {
+      if (host_mode) std::memset(b->ptr + n, kCanaryByte, canary);
+      else if (cudaMemsetAsync(b->ptr + n, kCanaryByte, canary, stream) != cudaSuccess) cudaGetLastError();
+    }
     return 0;
+  }
+
+  // true if the guard bytes behind the block's requested size are intact (device blocks: a synchronous copy back, debug builds only)
+  bool canary_intact(const Block* b) {
+    if (!canary || b->requested + canary > b->size) return true;
+    std::vector<unsigned char> host(canary);
+    if (host_mode) std::memcpy(host.data(), b->ptr + b->requested, canary);
+    else if (cudaMemcpy(host.data(), b->ptr + b->requested, canary, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return true; }
+    for (unsigned char c : host) if (c != kCanaryByte) return false;
+    return true;
   }
 
   int free_(void* p) {
@@ -174,6 +194,8 @@ struct Allocator {
     auto it = live.find(p);
     if (it == live.end()) return FT_ERR_ARG;
     Block* b = it->second;
+    const bool intact = canary_intact(b);
+    if (!intact) n_canary_bad++;
     live.erase(it);
     allocated -= b->size;
     n_free++;
@@ -183,7 +205,7 @@ struct Allocator {
     } else {
       release(b);
     }
-    return 0;
+    return intact ? 0 : FT_ERR_CORRUPT;
   }
 
   int record_stream(void* p, cudaStream_t s) {
@@ -263,6 +285,22 @@ FT_EXPORT int ft_alloc_set_budget(void* h, int64_t max_reserved_bytes) {
   if (!h) return FT_ERR_ARG;
   std::lock_guard<std::mutex> lk(((Allocator*)h)->mu);
   ((Allocator*)h)->budget = max_reserved_bytes;
+  return 0;
+}
+// Debug aid: guard bytes behind every later allocation, checked on free (ft_alloc_free then returns FT_ERR_CORRUPT and the block is still
+// released). bytes = 0 switches it off. Blocks that are live when the setting changes are not checked.
+FT_EXPORT int ft_alloc_set_canary(void* h, int64_t bytes) {
+  if (!h || bytes < 0 || bytes > (1 << 20)) return FT_ERR_ARG;
+  Allocator* a = (Allocator*)h;
+  std::lock_guard<std::mutex> lk(a->mu);
+  if (!a->live.empty()) return FT_ERR_ARG;
+  a->canary = (size_t)bytes;
+  return 0;
+}
+FT_EXPORT int ft_alloc_canary_violations(void* h, int64_t* out) {
+  if (!h || !out) return FT_ERR_ARG;
+  std::lock_guard<std::mutex> lk(((Allocator*)h)->mu);
+  *out = ((Allocator*)h)->n_canary_bad;
   return 0;
 }
 FT_EXPORT int ft_alloc_empty_cache(void* h, int64_t* freed) {

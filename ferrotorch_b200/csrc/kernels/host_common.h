@@ -18,6 +18,7 @@ enum FtError : int {
   FT_ERR_DRIVER = -2,      // driver entry point unavailable
   FT_ERR_TMAP = -3,        // cuTensorMapEncodeTiled refused the descriptor
   FT_ERR_TOO_LARGE = -4,   // request exceeds a compiled-in maximum
+  FT_ERR_CORRUPT = -5,     // a guard region was overwritten (allocator debug mode)
 };
 
 #define FT_CUDA_TRY(expr)                                  \

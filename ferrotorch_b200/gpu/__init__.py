@@ -194,7 +194,17 @@ class CudaAllocator:
         return out.value or 0
 
     def free(self, ptr: int) -> None:
+        """Returns the block to its pool. In canary mode a write past the end of the allocation raises (the block is released all the same)."""
         _lib.call("ft_alloc_free", self._h, ptr)
+
+    def set_canary(self, nbytes: int) -> None:
+        """Debug aid: ``nbytes`` guard bytes behind every later allocation, filled on malloc and verified on free. Only while nothing is live."""
+        _lib.call("ft_alloc_set_canary", self._h, int(nbytes))
+
+    def canary_violations(self) -> int:
+        out = ctypes.c_int64()
+        _lib.call("ft_alloc_canary_violations", self._h, ctypes.addressof(out))
+        return out.value
 
     def record_stream(self, ptr: int, stream: int) -> None:
         _lib.call("ft_alloc_record_stream", self._h, ptr, stream)

@@ -6,6 +6,7 @@ import time
 import pytest
 
 from ferrotorch_b200 import gpu
+from ferrotorch_b200.errors import FerrotorchError
 
 
 def test_allocator_split_coalesce_reuse_and_budget():
@@ -100,3 +101,24 @@ def test_memory_guard_policies_hooks_pressure_and_watchdog():
 def test_buffer_pool_rounding():
     assert gpu.BufferPool.round_len(1000) == 1024 and gpu.BufferPool.round_len(1 << 20) == 1 << 20 and gpu.BufferPool.round_len((1 << 20) + 1) == 2 << 20
     assert gpu.BufferPool.round_len(0) == 0
+
+
+def test_allocator_canary_catches_a_write_past_the_end():
+    import ctypes
+    a = gpu.CudaAllocator(host_mode=True)
+    a.set_canary(64)
+    p = a.malloc(1000)
+    ctypes.memset(p, 0x11, 1000)                 # exactly the requested bytes: fine
+    a.free(p)
+    assert a.canary_violations() == 0
+    q = a.malloc(1000)
+    ctypes.memset(q, 0x22, 1001)                 # one byte too far
+    with pytest.raises(FerrotorchError, match="guard bytes"):
+        a.free(q)
+    assert a.canary_violations() == 1 and a.stats().allocated == 0     # the block went back to the pool all the same
+    r = a.malloc(100)
+    with pytest.raises(FerrotorchError):
+        a.set_canary(0)                          # not while a block is live
+    a.free(r)
+    a.set_canary(0)
+    a.close()
