@@ -110,11 +110,39 @@ def full(shape, value, dtype=torch.float32, device=None):
     return torch.full(tuple(shape), value, dtype=dtype, device=_dev(device))
 
 
+def _host_philox(kind: str, shape, generator):
+    """Large f32 host tensors are filled by the native threaded Philox4x32-10 (the stream of the device kernels). The key of a call is one
+    64-bit draw from the torch generator in charge, so ``torch.manual_seed`` / an explicit generator still makes the values reproducible."""
+    import ctypes
+    from .. import _lib
+    if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+        shape = tuple(shape[0])
+    out = torch.empty(*shape, dtype=torch.float32)
+    seed = int(torch.empty((), dtype=torch.int64).random_(generator=generator)) & 0xFFFFFFFFFFFFFFFF
+    fn = _lib.runtime().ft_philox_uniform_mt if kind == "uniform" else _lib.runtime().ft_philox_normal_mt
+    fn(ctypes.c_uint64(seed), ctypes.c_uint64(0), ctypes.c_int64(out.numel()), ctypes.c_void_p(out.data_ptr()), ctypes.c_int(torch.get_num_threads()))
+    return out
+
+
+def _host_philox_ok(shape, dtype, device, generator) -> bool:
+    if dtype != torch.float32 or _dev(device).type != "cpu" or (generator is not None and generator.device.type != "cpu"):
+        return False
+    dims = shape[0] if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)) else shape
+    n = 1
+    for d in dims:
+        n *= int(d)
+    return n >= (1 << 16)
+
+
 def rand(*shape, dtype=torch.float32, device=None, generator=None):
+    if _host_philox_ok(shape, dtype, device, generator):
+        return _host_philox("uniform", shape, generator)
     return torch.rand(*shape, dtype=dtype, device=_dev(device), generator=generator)
 
 
 def randn(*shape, dtype=torch.float32, device=None, generator=None):
+    if _host_philox_ok(shape, dtype, device, generator):
+        return _host_philox("normal", shape, generator)
     return torch.randn(*shape, dtype=dtype, device=_dev(device), generator=generator)
 
 
