@@ -12,6 +12,7 @@
 #include <netinet/tcp.h>
 #include <poll.h>
 #include <sys/socket.h>
+#include <sys/uio.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -74,6 +75,13 @@ static int read_full(int fd, void* buf, size_t n, int64_t timeout_ms) {
   uint8_t* p = static_cast<uint8_t*>(buf);
   auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms < 0 ? 0 : timeout_ms);
   while (n > 0) {
+    // data that is already in the socket buffer is taken without a poll; the poll (with what is left of the deadline) only runs when the
+    // socket is empty
+    ssize_t got = ::recv(fd, p, n, MSG_DONTWAIT);
+    if (got > 0) { p += got; n -= (size_t)got; continue; }
+    if (got == 0) return E_CHANNEL_CLOSED;
+    if (errno == EINTR) continue;
+    if (errno != EAGAIN && errno != EWOULDBLOCK) return E_IO;
     int wait_ms = -1;
     if (timeout_ms >= 0) {
       auto left = std::chrono::duration_cast<std::chrono::milliseconds>(deadline - Clock::now()).count();
@@ -84,10 +92,6 @@ static int read_full(int fd, void* buf, size_t n, int64_t timeout_ms) {
     int pr = ::poll(&pfd, 1, wait_ms);
     if (pr == 0) return E_TIMEOUT;
     if (pr < 0) { if (errno == EINTR) continue; return E_IO; }
-    ssize_t got = ::recv(fd, p, n, 0);
-    if (got == 0) return E_CHANNEL_CLOSED;
-    if (got < 0) { if (errno == EINTR || errno == EAGAIN) continue; return E_IO; }
-    p += got; n -= (size_t)got;
   }
   return OK;
 }
@@ -131,9 +135,23 @@ class TcpBackend : public Backend {
     uint8_t hdr[8];
     put_u64le(hdr, f == F_CORRUPT_LENGTH ? (uint64_t)n + 1 : (uint64_t)n);
     if (f == F_CORRUPT_LENGTH) fault = F_NONE;
-    int e = write_full(fd, hdr, 8);
-    if (e) return e;
-    return write_full(fd, data, n);
+    // header and payload leave in one call: with TCP_NODELAY a separate 8-byte write would travel as a packet of its own
+    iovec iov[2] = {{hdr, 8}, {const_cast<void*>(data), n}};
+    msghdr msg{};
+    msg.msg_iov = iov;
+    msg.msg_iovlen = n ? 2 : 1;
+    size_t left = 8 + n;
+    while (left > 0) {
+      ssize_t put = ::sendmsg(fd, &msg, MSG_NOSIGNAL);
+      if (put < 0) { if (errno == EINTR) continue; return (errno == EPIPE || errno == ECONNRESET) ? E_CHANNEL_CLOSED : E_IO; }
+      left -= (size_t)put;
+      size_t adv = (size_t)put;
+      while (adv > 0 && msg.msg_iovlen > 0) {
+        if (adv >= msg.msg_iov[0].iov_len) { adv -= msg.msg_iov[0].iov_len; msg.msg_iov++; msg.msg_iovlen--; }
+        else { msg.msg_iov[0].iov_base = (uint8_t*)msg.msg_iov[0].iov_base + adv; msg.msg_iov[0].iov_len -= adv; adv = 0; }
+      }
+    }
+    return OK;
   }
 
   int recv(void* data, size_t n, int src, int64_t timeout_ms) override {
@@ -157,6 +175,13 @@ class TcpBackend : public Backend {
   }
 
  private:
+  // no Nagle delay; socket buffers large enough that a gradient bucket's send returns while the peer is still reducing the previous one
+  static void tune_socket(int fd) {
+    int one = 1, buf = 8 << 20;
+    ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    ::setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &buf, sizeof(buf));
+    ::setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof(buf));
+  }
   int listen_on(int port, int* out_fd) {
     int fd = ::socket(AF_INET, SOCK_STREAM, 0);
     if (fd < 0) return E_IO;
@@ -180,8 +205,7 @@ class TcpBackend : public Backend {
       if (pr <= 0) return pr == 0 ? E_TIMEOUT : E_IO;
       int fd = ::accept(lfd, nullptr, nullptr);
       if (fd < 0) return E_IO;
-      int one = 1;
-      ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+      tune_socket(fd);
       uint8_t hdr[8];
       int e = read_full(fd, hdr, 8, 5000);
       if (e) { ::close(fd); return e; }
@@ -201,8 +225,7 @@ class TcpBackend : public Backend {
       int fd = ::socket(AF_INET, SOCK_STREAM, 0);
       if (fd < 0) return E_IO;
       if (::connect(fd, (sockaddr*)&a, sizeof(a)) == 0) {
-        int one = 1;
-        ::setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+        tune_socket(fd);
         uint8_t hdr[8];
         put_u64le(hdr, (uint64_t)rank_);
         int e = write_full(fd, hdr, 8);

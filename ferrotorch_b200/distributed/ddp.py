@@ -41,8 +41,10 @@ class DDP:
     """Wraps a module; gradients are averaged across ranks by :meth:`sync_gradients` after ``backward``."""
 
     def __init__(self, module: torch.nn.Module, backend: Backend, bucket_size_bytes: int = DEFAULT_BUCKET_SIZE_BYTES,
-                 timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT):
-        self._module, self.backend, self.timeout = module, backend, timeout
+                 timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT, algorithm: str = "star"):
+        """``algorithm``: "star" (the reference's gather-to-rank-0 all-reduce, works on every backend) or "ring" (needs links between
+        neighbours: a full-mesh TCP backend or the simulated fabric)."""
+        self._module, self.backend, self.timeout, self.algorithm = module, backend, timeout, algorithm
         self.params = [p for p in module.parameters() if p.requires_grad]
         self.buckets = compute_buckets(self.params, bucket_size_bytes)
 
@@ -75,7 +77,7 @@ class DDP:
     def _sync_one_bucket(self, idx: List[int]) -> None:
         ps = [self.params[i] for i in idx]
         flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in ps])
-        red = allreduce(flat, self.backend, ReduceOp.Mean, self.timeout)
+        red = allreduce(flat, self.backend, ReduceOp.Mean, self.timeout, self.algorithm)
         off = 0
         for p in ps:
             n = p.numel()
