@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--comm", default=None)
+    ap.add_argument("--compute-copies", action="store_true", help="bf16 weight copies maintained by the optimizer instead of a cast per forward")
     a = ap.parse_args()
     import torch
     import torch.distributed as dist
@@ -38,6 +39,8 @@ def main():
     from ferrotorch_b200.vision import resnet50
     torch.manual_seed(0)
     model = resnet50().to(dev).to(memory_format=torch.channels_last)
+    if a.compute_copies:
+        nn.attach_compute_copies(model)
     ddp = DDP(model, comm=a.comm)
     opt = optim.Sgd(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
     lossf = nn.CrossEntropyLoss()
@@ -92,7 +95,7 @@ def main():
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms / a.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast, f32 master", "data": "synthetic (N(0,1) images, uniform labels)",
             "config": {"model": "resnet50", "global_batch": a.batch * world, "image": "224x224x3", "parallelism": f"ddp{world}",
-                       "optimizer": "SGD(lr=0.1,momentum=0.9,wd=1e-4)", "bucket_mb": 25, "comm": ddp.comm_mode if world > 1 else "none",
+                       "optimizer": "SGD(lr=0.1,momentum=0.9,wd=1e-4)", "bucket_mb": 25, "compute_copies": bool(a.compute_copies), "comm": ddp.comm_mode if world > 1 else "none",
                        "library_ops": ["conv3x3/7x7 (cuDNN)", "global avg pool"], "l2": "inputs_larger_than_L2 (154 MB of images per step)"},
             "e2e": {"value": round(a.batch * world * a.steps / (ms2 / 1e3), 1), "unit": "images/s", "h2d_bytes_per_step": a.batch * (3 * 224 * 224 * 4 + 8),
                     "d2h_bytes_per_step": 4},

@@ -10,4 +10,5 @@ from .extras import (KVPage, PagePool, PagedKVCache, PagedAttentionManager, Bloc
                      pack_padded_sequence, pad_packed_sequence, interpolate, grid_sample, affine_grid, functional_pad_1d,
                      functional_pad_2d, functional_pad_3d, ObserverType, QatConfig, FakeQuantize, QuantizedModel, prepare_qat)
 from . import functional
+from .compute_copy import attach_compute_copies, detach_compute_copies, compute_copy
 from . import utils

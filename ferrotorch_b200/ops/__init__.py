@@ -1,6 +1,6 @@
 """Hot-path operators: each one is a thin launcher around a hand-written sm_100a kernel
 (with an f32 PyTorch evaluation of the same math for CPU tensors, used as the test oracle)."""
-from .gemm import gemm, linear, matmul_exact, mv, dot, bmm
+from .gemm import gemm, linear, linear_master, matmul_exact, mv, dot, bmm
 from .norm import rms_norm, layer_norm, rmsnorm_fwd, rmsnorm_bwd
 from .llama import (rope_tables, rope_inplace, apply_rope, swiglu, swiglu_fwd, swiglu_bwd, embedding, embedding_fwd,
                     embedding_bwd, add_)

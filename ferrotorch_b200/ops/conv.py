@@ -36,6 +36,11 @@ def conv3x3_nhwc_raw(x: torch.Tensor, w_krsc: torch.Tensor, relu: bool = False) 
     Cout = w_krsc.shape[0]
     if w_krsc.shape != (Cout, 3, 3, Cin) or not w_krsc.is_contiguous():
         raise InvalidArgument("weights must be dense [Cout, 3, 3, Cin]")
+    if not x.is_cuda:                 # host restatement (tests of the autograd plumbing): f32 accumulation, bf16 result
+        y = torch.nn.functional.conv2d(x.float(), w_krsc.permute(0, 3, 1, 2).float(), padding=1)
+        if relu:
+            y = torch.relu(y)
+        return y.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
     y = torch.empty((N, Cout, H, W), device=x.device, dtype=torch.bfloat16, memory_format=torch.channels_last)
     with torch.cuda.device(x.device):
         _lib.call("ft_conv3x3_nhwc", x, w_krsc, y, N, H, W, Cin, Cout, int(relu), _lib.S())
@@ -64,6 +69,47 @@ class _Conv3x3Fn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = torch.nn.grad.conv2d_weight(x, weight.shape, dy, padding=1).to(weight.dtype)
         return dx, dw
+
+
+class _Conv3x3MasterFn(torch.autograd.Function):
+    """The same convolution evaluated with the bf16 compute copy of an f32 master weight. A channels-last copy is already laid out as
+    ``[Cout, 3, 3, Cin]``, so the forward pass launches nothing but the convolution; the master's gradient is returned in f32."""
+
+    @staticmethod
+    def forward(ctx, x, w_master, w_compute):
+        wk = w_compute.permute(0, 2, 3, 1)
+        if not wk.is_contiguous():
+            wk = wk.contiguous()
+        ctx.save_for_backward(x, wk)
+        ctx.wshape, ctx.wstride = w_master.shape, w_master.stride()
+        return conv3x3_nhwc_raw(x, wk)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wk = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            if dy.shape[1] % 64 == 0 and x.shape[1] % 8 == 0:
+                dx = conv3x3_nhwc_raw(dy, wk.flip(1, 2).permute(3, 1, 2, 0).contiguous())
+            else:
+                dx = torch.nn.grad.conv2d_input(x.shape, wk.permute(0, 3, 1, 2), dy, padding=1)
+        if ctx.needs_input_grad[1]:
+            if x.is_cuda:
+                dw = torch.nn.grad.conv2d_weight(x, ctx.wshape, dy, padding=1)
+            else:
+                dw = torch.nn.grad.conv2d_weight(x.float(), ctx.wshape, dy.float(), padding=1)
+            # f32, in the master's memory layout, so the optimizer can walk parameter and gradient in one order
+            dw = torch.empty_strided(ctx.wshape, ctx.wstride, device=dw.device, dtype=torch.float32).copy_(dw)
+        return dx, dw, None
+
+
+def conv3x3_master(x: torch.Tensor, w_master: torch.Tensor, w_compute: torch.Tensor) -> torch.Tensor:
+    """3x3 / stride 1 / padding 1 convolution of a channels-last bf16 activation with the bf16 compute copy ``w_compute`` of the f32
+    ``w_master`` (both ``[Cout, Cin, 3, 3]``); the gradient goes to ``w_master`` in f32."""
+    if w_compute.dtype != torch.bfloat16 or w_master.shape != w_compute.shape or x.dtype != torch.bfloat16:
+        raise InvalidArgument("conv3x3_master needs a bf16 activation and a bf16 copy shaped like the master weight")
+    return _Conv3x3MasterFn.apply(x, w_master, w_compute)
 
 
 def conv3x3(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

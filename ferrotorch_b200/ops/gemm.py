@@ -168,6 +168,45 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class _MasterLinearFn(torch.autograd.Function):
+    """``x @ w_compute.T`` where ``w_compute`` is the low-precision copy of the f32 master ``w_master``: the master receives its gradient in
+    f32 straight from the weight-gradient GEMM (no bf16 round trip, no cast launches)."""
+
+    @staticmethod
+    def forward(ctx, x, w_master, w_compute, bias):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        w2 = w_compute.reshape(w_compute.shape[0], -1)
+        y = gemm(x2, w2, bias=bias)
+        ctx.save_for_backward(x2, w2)
+        ctx.has_bias = bias is not None
+        ctx.shp, ctx.wshape = shp, w_master.shape
+        return y.reshape(*shp[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w2 = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w2, b_mn=True).reshape(ctx.shp)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32).reshape(ctx.wshape)
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            db = dy2.float().sum(0)
+        return dx, dw, None, db
+
+
+def linear_master(x: torch.Tensor, w_master: torch.Tensor, w_compute: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T + bias`` computed with ``w_compute`` (the bf16 copy of the f32 ``w_master``, same shape); gradients flow to ``w_master``
+    (f32) and to ``bias`` (f32 sum, cast by autograd to the bias dtype if needed). ``x`` must have ``w_compute``'s dtype."""
+    if x.dtype != w_compute.dtype or w_master.shape != w_compute.shape:
+        raise InvalidArgument("linear_master: x and the compute copy must share a dtype, master and copy a shape")
+    return _MasterLinearFn.apply(x, w_master, w_compute, bias)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ w.T + bias`` for ``w`` of shape ``[out, in]`` with autograd; bf16 CUDA tensors run on the tcgen05 GEMM."""
     if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:

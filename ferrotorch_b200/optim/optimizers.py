@@ -16,6 +16,7 @@ import torch
 
 from .. import ops
 from ..errors import InvalidArgument
+from ..nn.compute_copy import mark_synced, optimizer_target
 
 
 class _Cfg:
@@ -96,6 +97,22 @@ def _fused_ok(p: torch.Tensor, g: torch.Tensor) -> bool:
             and g.dtype in (torch.float32, torch.bfloat16))
 
 
+def _dense(t: torch.Tensor) -> bool:
+    return t.is_contiguous() or (t.dim() == 4 and t.is_contiguous(memory_format=torch.channels_last))
+
+
+def _flat(t: torch.Tensor) -> torch.Tensor:
+    """1-D view over the storage of a dense tensor in memory order (row-major, or NHWC order for a channels-last tensor)."""
+    return t.view(-1) if t.is_contiguous() else t.permute(0, 2, 3, 1).reshape(-1)
+
+
+def _flat_pair_ok(p: torch.Tensor, g: torch.Tensor, need_cuda: bool = True) -> bool:
+    """Parameters with a compute copy take the flat kernels in any dense layout (convolution weights of a channels-last model included):
+    parameter, gradient, momentum buffer and compute copy are then all walked in the parameter's memory order."""
+    return ((p.is_cuda or not need_cuda) and _dense(p) and not g.is_sparse and p.dtype in (torch.float32, torch.bfloat16)
+            and g.dtype in (torch.float32, torch.bfloat16))
+
+
 class Sgd(Optimizer):
     """SGD: weight decay folded into the gradient, momentum buffer seeded with the first gradient, dampening and Nesterov as in PyTorch."""
 
@@ -119,15 +136,27 @@ class Sgd(Optimizer):
                     continue
                 st = self.state[p]
                 first = "buf" not in st
-                if _fused_ok(p, p.grad):
+                target = optimizer_target(p) if p.dtype == torch.float32 else None
+                if _fused_ok(p, p.grad) or (target is not None and _flat_pair_ok(p, p.grad, need_cuda=False)):
+                    grad = p.grad
+                    if grad.stride() != p.stride():                      # bring the gradient into the parameter's memory order
+                        grad = torch.empty_like(p, dtype=grad.dtype).copy_(grad)
                     if first:
                         st["buf"] = torch.zeros(p.numel(), device=p.device, dtype=torch.float32) if g["momentum"] else None
                         if p.dtype == torch.bfloat16:
-                            st["master"] = p.detach().float().reshape(-1).clone()
-                    master = st.get("master", p.view(-1))
-                    ops.sgd_flat_(master, p.view(-1) if p.dtype == torch.bfloat16 else None, st["buf"], p.grad.reshape(-1), lr=g["lr"],
+                            st["master"] = _flat(p.detach()).float().clone()
+                    elif st.get("layout", p.stride()) != p.stride() and st["buf"] is not None:
+                        # the parameter was re-laid-out since the last step: re-order the momentum buffer to match
+                        old = torch.as_strided(st["buf"], p.shape, st["layout"])
+                        st["buf"] = _flat(torch.empty_like(p, dtype=torch.float32).copy_(old)).clone()
+                    st["layout"] = p.stride()
+                    master = st.get("master", _flat(p.detach()))
+                    low = _flat(p.detach()) if p.dtype == torch.bfloat16 else (_flat(target) if target is not None else None)
+                    ops.sgd_flat_(master, low, st["buf"], _flat(grad), lr=g["lr"],
                                   momentum=g["momentum"], dampening=g["dampening"], weight_decay=g["weight_decay"], nesterov=g["nesterov"],
                                   first_step=first, maximize=g["maximize"])
+                    if target is not None:
+                        mark_synced(p)
                     continue
                 d = -p.grad if g["maximize"] else p.grad
                 if g["weight_decay"]:

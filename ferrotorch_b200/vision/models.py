@@ -20,6 +20,11 @@ import torch.nn.functional as F
 
 from .. import nn, ops
 from ..errors import InvalidArgument
+from ..nn.compute_copy import compute_copy
+
+
+def _autocast_bf16() -> bool:
+    return torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16
 
 
 class Conv1x1(nn.Conv2d):
@@ -30,6 +35,16 @@ class Conv1x1(nn.Conv2d):
 
     def forward(self, x):
         w = self.weight
+        wc = compute_copy(w) if (x.is_cuda and w.dtype == torch.float32 and _autocast_bf16()) else None
+        if wc is not None and wc.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and self.out_channels % 8 == 0:
+            # bf16 copy kept current by the optimizer: no cast launch here, f32 weight gradient straight from the GEMM
+            x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            if self.stride[0] > 1:
+                x = x[:, :, :: self.stride[0], :: self.stride[1]].contiguous(memory_format=torch.channels_last)
+            N, C, H, W = x.shape
+            rows = x.permute(0, 2, 3, 1).reshape(N * H * W, C)
+            y = ops.linear_master(rows, w, wc, None if self.bias is None else self.bias.to(torch.bfloat16))
+            return y.view(N, H, W, self.out_channels).permute(0, 3, 1, 2)
         if x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16:
             x, w = x.to(torch.bfloat16), w.to(torch.bfloat16)        # autocast policy: convolutions run in the reduced dtype
         if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and self.out_channels % 8 == 0 \
@@ -76,6 +91,9 @@ class Conv3x3(nn.Conv2d):
         if x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16 and x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
         if ops.conv.conv3x3_eligible(x, self.weight, self.stride, self.padding, self.dilation, self.groups):
+            wc = compute_copy(self.weight) if self.weight.dtype == torch.float32 else None
+            if wc is not None and wc.dtype == torch.bfloat16:
+                return ops.conv.conv3x3_master(x, self.weight, wc)
             return ops.conv3x3(x, self.weight)
         return super().forward(x)
 
