@@ -40,7 +40,17 @@ struct CommSync {
   uint32_t seq;                 // sequence number of this launch (same on every rank)
   uint32_t* seq_dev;            // optional: the sequence lives in device memory (seq = *seq_dev + 1, written back by the last CTA), so a
                                 // launch captured in a CUDA graph advances it on every replay
+  // optional per-launch phase stamps (globaltimer ns): record (seq % trace_cap) = {seq | kind << 32, entered, peers ready, body done, retired}
+  unsigned long long* trace;
+  uint32_t trace_cap, trace_kind;
 };
+constexpr int TRACE_WORDS = 5;
+FT_DEVICE void trace_stamp(const CommSync& s, int word) {
+  if (s.trace == nullptr) return;
+  unsigned long long* rec = s.trace + (size_t)(s.seq % s.trace_cap) * TRACE_WORDS;
+  if (word == 1) rec[0] = (unsigned long long)s.seq | ((unsigned long long)s.trace_kind << 32);
+  rec[word] = globaltimer_ns();
+}
 
 // One thread per peer: tell every peer that this rank reached `phase` of launch `seq`.
 FT_DEVICE void signal_peers(const CommSync& s, int phase) {
@@ -61,10 +71,12 @@ FT_DEVICE bool comm_begin(CommSync& s, uint32_t* status) {
   if (s.seq_dev) s.seq = *reinterpret_cast<volatile uint32_t*>(s.seq_dev) + 1;   // read before any CTA can reach comm_end's write-back
   __shared__ int ok_sh;
   if (threadIdx.x == 0) ok_sh = 1;
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_stamp(s, 1);
   __syncthreads();
   if (blockIdx.x == 0) signal_peers(s, 0);
   if (!wait_peers(s, 0, status, 1)) ok_sh = 0;
   __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) trace_stamp(s, 2);
   return ok_sh != 0;
 }
 
@@ -81,10 +93,11 @@ FT_DEVICE void comm_end(const CommSync& s, uint32_t* status) {
   }
   __syncthreads();
   if (!last) return;
-  if (threadIdx.x == 0) *s.counter = 0;    // ready for the next launch on this stream
+  if (threadIdx.x == 0) { *s.counter = 0; trace_stamp(s, 3); }    // counter: ready for the next launch on this stream
   __threadfence_system();
   signal_peers(s, 1);
   wait_peers(s, 1, status, 2);
+  if (threadIdx.x == 0) trace_stamp(s, 4);
   if (s.seq_dev && threadIdx.x == 0) *s.seq_dev = s.seq;
 }
 
@@ -331,8 +344,17 @@ inline int comm_grid(size_t work, int max_ctas) {
   return (int)(g < (size_t)max_ctas ? g : (size_t)max_ctas);
 }
 
-int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq) {
+// Phase-stamp ring of the current device (null = off), set by ft_comm_set_trace.
+unsigned long long* g_trace[64] = {nullptr};
+uint32_t g_trace_cap[64] = {0};
+
+int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq, uint32_t kind = 0) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return FT_ERR_ARG;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  s.trace = g_trace[dev];
+  s.trace_cap = g_trace_cap[dev];
+  s.trace_kind = kind;
   for (int i = 0; i < MAX_RANKS; i++) s.flags[i] = i < world ? reinterpret_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
   s.counter = counter;
   s.rank = rank;
@@ -397,6 +419,19 @@ __global__ void __launch_bounds__(512) p2p_get_kernel(uint4* __restrict__ dst, c
 
 }  // namespace
 
+// Phase stamps of the collective kernels launched on the current device from now on: `ring` is device memory for `capacity` records of five
+// u64 words {launch number | kind << 32, entered, peers ready, body done, retired} in globaltimer nanoseconds; record index = launch number
+// modulo capacity. kind: 1 all-reduce, 2 one-shot all-reduce, 3 reduce-scatter, 4 all-gather, 5 all-to-all, 6 broadcast, 7 barrier,
+// 8 fused reduce-scatter + AdamW + all-gather. ring = null switches the stamps off (the default).
+FT_EXPORT int ft_comm_set_trace(void* ring, int capacity) {
+  int dev = 0;
+  FT_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || (ring != nullptr && capacity < 1)) return FT_ERR_ARG;
+  g_trace[dev] = (unsigned long long*)ring;
+  g_trace_cap[dev] = ring ? (uint32_t)capacity : 0u;
+  return FT_OK;
+}
+
 // Size in bytes of the per-rank flag block the kernels expect (zero-initialised symmetric memory).
 FT_EXPORT int ft_comm_flag_bytes() { return 4 * MAX_RANKS * 4; }
 
@@ -406,7 +441,7 @@ FT_EXPORT int ft_comm_flag_bytes() { return 4 * MAX_RANKS * 4; }
 FT_EXPORT int ft_comm_allreduce(void* const* buf_ptrs, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
                                 int64_t n, int dtype, float scale, void* mc_ptr, int max_ctas, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 1);
   if (r) return r;
   if (n <= 0) return FT_ERR_ARG;
   PeerPtrs b;
@@ -428,7 +463,7 @@ FT_EXPORT int ft_comm_allreduce(void* const* buf_ptrs, void* const* flag_ptrs, u
 FT_EXPORT int ft_comm_allreduce_1shot(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
                                       uint32_t seq, int64_t n, int dtype, float scale, int max_ctas, uint32_t* seq_dev, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 2);
   if (r) return r;
   s.seq_dev = seq_dev;
   if (n <= 0) return FT_ERR_ARG;
@@ -445,7 +480,7 @@ FT_EXPORT int ft_comm_allreduce_1shot(void* const* buf_ptrs, void* out, void* co
 FT_EXPORT int ft_comm_reduce_scatter(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
                                      uint32_t seq, int64_t chunk, int dtype, float scale, int max_ctas, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 3);
   if (r) return r;
   const int V = dtype == 0 ? 8 : 4;
   if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
@@ -461,7 +496,7 @@ FT_EXPORT int ft_comm_reduce_scatter(void* const* buf_ptrs, void* out, void* con
 FT_EXPORT int ft_comm_allgather(void* const* buf_ptrs, const void* src, void* const* flag_ptrs, uint32_t* counter, int rank, int world,
                                 uint32_t seq, int64_t chunk, int dtype, int max_ctas, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 4);
   if (r) return r;
   const int V = dtype == 0 ? 8 : 4;
   if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
@@ -477,7 +512,7 @@ FT_EXPORT int ft_comm_allgather(void* const* buf_ptrs, const void* src, void* co
 FT_EXPORT int ft_comm_alltoall(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
                                int64_t chunk, int dtype, int max_ctas, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 5);
   if (r) return r;
   const int V = dtype == 0 ? 8 : 4;
   if (chunk <= 0 || chunk % V) return FT_ERR_ARG;
@@ -493,7 +528,7 @@ FT_EXPORT int ft_comm_alltoall(void* const* buf_ptrs, void* out, void* const* fl
 FT_EXPORT int ft_comm_broadcast(void* const* buf_ptrs, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
                                 int root, int64_t n, int dtype, int max_ctas, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 6);
   if (r) return r;
   const int V = dtype == 0 ? 8 : 4;
   if (n <= 0 || n % V || root < 0 || root >= world) return FT_ERR_ARG;
@@ -528,7 +563,7 @@ FT_EXPORT int ft_comm_p2p_get(void* dst, const void* my_slot, int64_t bytes, con
 
 FT_EXPORT int ft_comm_barrier(void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq, cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 7);
   if (r) return r;
   comm_barrier_kernel<<<1, 32, 0, st>>>(s, ft_status_ptr());
   return (int)cudaGetLastError();
@@ -541,7 +576,7 @@ FT_EXPORT int ft_fsdp_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptr
                                   float beta2, float eps, float weight_decay, int step, const float* grad_scale_ptr, int max_ctas,
                                   cudaStream_t st) {
   CommSync s;
-  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq);
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 8);
   if (r) return r;
   if (chunk <= 0 || chunk % 8 || step < 1) return FT_ERR_ARG;
   PeerPtrs g, p;

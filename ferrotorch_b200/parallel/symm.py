@@ -58,6 +58,75 @@ class SymmetricBuffer:
         return self.multicast_ptr + elem_offset * self.itemsize if self.multicast_ptr else 0
 
 
+class CommTrace:
+    """Device-side phase stamps of the peer-memory collectives launched on one device: every launch writes, from inside the kernel, the
+    ``globaltimer`` time at which it entered, saw all peers arrive, finished its own part and retired after the closing handshake. The ring
+    keeps the last ``capacity`` launches (indexed by launch number). Used as a context manager::
+
+        with CommTrace(device) as tr:
+            ...training steps...
+        for r in tr.records(): print(r["kind"], r["wait_peers_us"], r["body_us"], r["drain_us"])
+
+    ``chrome_events`` renders the same records as Chrome-trace slices that can be merged into a profiler report (one row per phase)."""
+
+    KINDS = {1: "all_reduce", 2: "all_reduce_1shot", 3: "reduce_scatter", 4: "all_gather", 5: "all_to_all", 6: "broadcast", 7: "barrier",
+             8: "fsdp_rs_adamw_ag"}
+    WORDS = 5
+
+    def __init__(self, device, capacity: int = 4096):
+        self.device = torch.device(device)
+        self.capacity = int(capacity)
+        self.ring = torch.zeros(self.capacity * self.WORDS, device=self.device, dtype=torch.int64)
+
+    def enable(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.call("ft_comm_set_trace", self.ring, self.capacity)
+
+    def disable(self) -> None:
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            _lib.call("ft_comm_set_trace", None, 0)
+
+    def __enter__(self):
+        self.enable()
+        return self
+
+    def __exit__(self, *exc):
+        self.disable()
+        return False
+
+    @staticmethod
+    def decode(words) -> List[dict]:
+        """Records from the raw ring (a flat sequence of int64, five per record); empty and half-written records are skipped."""
+        out = []
+        w = [int(v) & 0xFFFFFFFFFFFFFFFF for v in words]
+        for i in range(0, len(w) - CommTrace.WORDS + 1, CommTrace.WORDS):
+            head, t_in, t_ready, t_body, t_out = w[i: i + CommTrace.WORDS]
+            if head == 0 or not (0 < t_in <= t_ready <= t_body <= t_out):
+                continue
+            kind = head >> 32
+            out.append({"seq": head & 0xFFFFFFFF, "kind": CommTrace.KINDS.get(kind, f"kind{kind}"), "start_ns": t_in,
+                        "wait_peers_us": (t_ready - t_in) / 1e3, "body_us": (t_body - t_ready) / 1e3, "drain_us": (t_out - t_body) / 1e3,
+                        "total_us": (t_out - t_in) / 1e3})
+        out.sort(key=lambda r: r["start_ns"])
+        return out
+
+    def records(self) -> List[dict]:
+        torch.cuda.synchronize(self.device)
+        return self.decode(self.ring.cpu().tolist())
+
+    @staticmethod
+    def chrome_events(records: List[dict], pid: int = 0, tid: str = "comm kernels") -> List[dict]:
+        ev = []
+        for r in records:
+            t = r["start_ns"] / 1e3
+            for phase in ("wait_peers", "body", "drain"):
+                d = r[phase + "_us"]
+                ev.append({"name": f"{r['kind']}:{phase}", "ph": "X", "ts": t, "dur": d, "pid": pid, "tid": tid, "args": {"seq": r["seq"]}})
+                t += d
+        return ev
+
+
 class SymmComm:
     """Launcher of the peer-memory collectives for one process group (at most 8 ranks on one NVSwitch domain)."""
 

@@ -73,6 +73,19 @@ def case_collectives():
     dist.all_gather(gathered, buf.tensor)
     for g in gathered[1:]:
         assert torch.equal(g, gathered[0])
+    if os.environ.get("FT_STAGED") == "1":
+        # phase stamps written from inside the kernels (opt-in until run on hardware): four launches, four ordered records
+        from ferrotorch_b200.parallel.symm import CommTrace
+        with CommTrace(dev, capacity=64) as tr:
+            for _ in range(3):
+                comm.all_reduce_(buf, n, scale=1.0, use_nvls=False)
+            comm.barrier()
+        recs = tr.records()
+        assert [r["kind"] for r in recs] == ["all_reduce"] * 3 + ["barrier"], recs
+        assert all(0 <= r["wait_peers_us"] < 2e6 and r["total_us"] > 0 for r in recs)
+        comm.all_reduce_(buf, n, scale=1.0, use_nvls=False)          # stamps off again: the ring stays as it was
+        assert len(tr.records()) == 4
+        comm.check()
     if rank == 0:
         print("COLLECTIVES_OK")
 

@@ -435,3 +435,17 @@ def test_heartbeat_failure_detection_and_elastic_restart(tmp_path):
         mon.end_step(1000)
     s = mon.summary(skip=1)
     assert s["tokens_per_s"] > 0 and 0 < s["comm_to_compute"] < 2 and 0 < s["fraction_of_roofline"] < 1
+
+
+def test_comm_trace_decoding_and_chrome_events():
+    """The phase-stamp ring of the collective kernels, decoded on the host: empty and torn records are dropped, phases add up."""
+    from ferrotorch_b200.parallel.symm import CommTrace
+    ring = [0] * (4 * CommTrace.WORDS)
+    ring[0:5] = [7 | (1 << 32), 1_000_000, 1_004_000, 1_054_000, 1_056_000]          # all-reduce, launch 7
+    ring[5:10] = [8 | (8 << 32), 2_000_000, 2_001_000, 2_301_000, 2_302_500]         # fused FSDP kernel, launch 8
+    ring[10:15] = [9 | (3 << 32), 3_000_000, 2_999_000, 0, 0]                        # torn: still running when the ring was read
+    recs = CommTrace.decode(ring)
+    assert [r["kind"] for r in recs] == ["all_reduce", "fsdp_rs_adamw_ag"] and recs[0]["seq"] == 7
+    assert recs[0]["wait_peers_us"] == 4.0 and recs[0]["body_us"] == 50.0 and recs[0]["drain_us"] == 2.0 and recs[0]["total_us"] == 56.0
+    ev = CommTrace.chrome_events(recs, pid=3)
+    assert len(ev) == 6 and ev[0]["name"] == "all_reduce:wait_peers" and ev[1]["ts"] == 1004.0 and ev[5]["dur"] == 1.5 and ev[0]["pid"] == 3
