@@ -20,6 +20,8 @@
 // Capability parity: star all-reduce / all-gather / reduce-scatter on host vectors (ferrotorch-distributed/src/
 // collective.rs:64-410), NCCL wrappers (nccl_collective.rs:75-260), FSDP sync_gradients + broadcast_updated_params
 // (fsdp.rs:627-845).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host_common.h"
 
@@ -43,6 +45,7 @@ struct CommSync {
   // optional per-launch phase stamps (globaltimer ns): record (seq % trace_cap) = {seq | kind << 32, entered, peers ready, body done, retired}
   unsigned long long* trace;
   uint32_t trace_cap, trace_kind;
+  uint64_t timeout_ns;          // deadline of every wait on a peer in this launch
 };
 constexpr int TRACE_WORDS = 5;
 FT_DEVICE void trace_stamp(const CommSync& s, int word) {
@@ -60,7 +63,7 @@ FT_DEVICE void signal_peers(const CommSync& s, int phase) {
 FT_DEVICE bool wait_peers(const CommSync& s, int phase, uint32_t* status, int site) {
   bool ok = true;
   if (threadIdx.x < s.world) {
-    ok = wait_flag_ge(s.flags[s.rank] + phase * MAX_RANKS + threadIdx.x, s.seq, COMM_TIMEOUT_NS);
+    ok = wait_flag_ge(s.flags[s.rank] + phase * MAX_RANKS + threadIdx.x, s.seq, s.timeout_ns);
     if (!ok) ft_set_status(status, FT_K_COMM, site, threadIdx.x);
   }
   return ok;
@@ -347,6 +350,16 @@ inline int comm_grid(size_t work, int max_ctas) {
 // Phase-stamp ring of the current device (null = off), set by ft_comm_set_trace.
 unsigned long long* g_trace[64] = {nullptr};
 uint32_t g_trace_cap[64] = {0};
+// Deadline of the waits on peers inside the collective kernels: 2 s unless FT_COMM_TIMEOUT_MS or ft_comm_set_timeout_ms says otherwise.
+uint64_t g_timeout_ns = 0;
+uint64_t comm_timeout_ns() {
+  if (g_timeout_ns == 0) {
+    const char* e = getenv("FT_COMM_TIMEOUT_MS");
+    const long long ms = e ? atoll(e) : 0;
+    g_timeout_ns = ms > 0 ? (uint64_t)ms * 1000000ull : COMM_TIMEOUT_NS;
+  }
+  return g_timeout_ns;
+}
 
 int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq, uint32_t kind = 0) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return FT_ERR_ARG;
@@ -355,6 +368,7 @@ int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, 
   s.trace = g_trace[dev];
   s.trace_cap = g_trace_cap[dev];
   s.trace_kind = kind;
+  s.timeout_ns = comm_timeout_ns();
   for (int i = 0; i < MAX_RANKS; i++) s.flags[i] = i < world ? reinterpret_cast<uint32_t*>(flag_ptrs[i]) : nullptr;
   s.counter = counter;
   s.rank = rank;
@@ -429,6 +443,14 @@ FT_EXPORT int ft_comm_set_trace(void* ring, int capacity) {
   if (dev < 0 || dev >= 64 || (ring != nullptr && capacity < 1)) return FT_ERR_ARG;
   g_trace[dev] = (unsigned long long*)ring;
   g_trace_cap[dev] = ring ? (uint32_t)capacity : 0u;
+  return FT_OK;
+}
+
+// Deadline (milliseconds, 1 .. 600 000) of the waits on peers in the collective kernels launched from now on; every rank of a group should
+// use the same value. The environment variable FT_COMM_TIMEOUT_MS sets the initial value (default 2000).
+FT_EXPORT int ft_comm_set_timeout_ms(int ms) {
+  if (ms < 1 || ms > 600000) return FT_ERR_ARG;
+  g_timeout_ns = (uint64_t)ms * 1000000ull;
   return FT_OK;
 }
 

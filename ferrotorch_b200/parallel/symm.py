@@ -186,6 +186,12 @@ class SymmComm:
                   _lib.S())
         return out
 
+    @staticmethod
+    def set_timeout(seconds: float) -> None:
+        """Deadline of the device-side waits on peers for collectives launched from now on (default 2 s, or ``FT_COMM_TIMEOUT_MS``). Every rank
+        of a group should use the same value."""
+        _lib.call("ft_comm_set_timeout_ms", max(1, int(seconds * 1000)))
+
     def barrier(self) -> None:
         _lib.call("ft_comm_barrier", self.flag_ptrs, self.counter, self.rank, self.world, self._next(), _lib.S())
 
