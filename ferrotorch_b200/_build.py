@@ -132,10 +132,70 @@ def build_runtime_selftest(sanitizer: str, out_path) -> Path:
     raise last
 
 
+_DECL_RE = None
+
+
+def _exports(path: Path, macros):
+    """(comment, declaration) of every exported function of a source file: the contiguous ``//`` block directly above the definition and its
+    signature up to the opening brace."""
+    import re
+    global _DECL_RE
+    text = path.read_text()
+    pat = re.compile(r"^(?:" + "|".join(re.escape(m) for m in macros) + r")\s+([^;{]*?\))\s*\{", re.M | re.S)
+    out = []
+    for m in pat.finditer(text):
+        head = text[: m.start()].rstrip("\n").split("\n")
+        comment = []
+        while head and head[-1].lstrip().startswith("//"):
+            comment.insert(0, head.pop().strip())
+        out.append((comment, " ".join(m.group(1).split())))
+    return out
+
+
+def generate_headers() -> list:
+    """Writes ``csrc/include/ferrotorch/kernels.h`` and ``runtime.h``: the C ABI of ``libft_kernels.so`` (every ``FT_EXPORT`` launcher of
+    ``csrc/kernels/*.cu``) and of ``libft_runtime.so`` (every ``FT_API`` function of ``csrc/runtime/*.cpp``), with the comment that stands above
+    each definition. The Python loader parses the same definitions, so the headers and the bindings cannot drift apart."""
+    inc = CSRC / "include" / "ferrotorch"
+    inc.mkdir(parents=True, exist_ok=True)
+    written = []
+    for name, sources, macros, includes, intro in (
+            ("kernels.h", kernel_sources() + [CSRC / "kernels" / "host_common.cu"], ("FT_EXPORT", 'extern "C" __attribute__((visibility("default")))'),
+             ["<cuda_runtime.h>", "<stdint.h>", "<sys/types.h>"],
+             "C ABI of libft_kernels.so: launchers of the sm_100a kernels. Every function returns 0 when the work was launched, a negative FtError\n"
+             "// code (-1 argument, -2 driver entry point, -3 tensor map, -4 too large, -5 guard bytes overwritten) when it refused before launching,\n"
+             "// or a positive CUDA runtime error code. Pointers are device pointers unless a comment says otherwise; `stream` arguments take the\n"
+             "// CUDA stream to launch on."),
+            ("runtime.h", runtime_sources(), ("FT_API", "FT_EXPORT"), ["<stdint.h>"],
+             "C ABI of libft_runtime.so: host-side distributed runtime (backends, collectives, bucket planner), data-loader helpers and the\n"
+             "// host NMS sweep. Functions that return int return 0 on success or the error code documented in dist_runtime.cpp (1 invalid world,\n"
+             "// 2 invalid rank, 3 self send, 4 size mismatch, 5 io, 7 channel closed, 8 unsupported, 9 timeout, 10 no connection, 12 argument).")):
+        seen, body = set(), []
+        for src in sorted(set(sources)):
+            ex = [e for e in _exports(src, macros) if e[1] not in seen]
+            if not ex:
+                continue
+            body.append(f"// ---- {src.name} " + "-" * max(4, 100 - len(src.name)))
+            for comment, decl in ex:
+                seen.add(decl)
+                body.extend(comment)
+                body.append(decl + ";")
+                body.append("")
+        text = ("// Generated by `python -m ferrotorch_b200._build` from the definitions in the sources; do not edit.\n// " + intro + "\n#pragma once\n"
+                + "".join(f"#include {i}\n" for i in includes) + "\n#ifdef __cplusplus\nextern \"C\" {\n#endif\n\n" + "\n".join(body)
+                + "\n#ifdef __cplusplus\n}  // extern \"C\"\n#endif\n")
+        path = inc / name
+        if not path.exists() or path.read_text() != text:
+            path.write_text(text)
+        written.append(path)
+    return written
+
+
 def build_all(verbose=False):
     OUT.mkdir(parents=True, exist_ok=True)
     k = build_kernels(verbose)
     r = build_runtime(verbose)
+    generate_headers()
     return k, r
 
 
