@@ -448,6 +448,10 @@ __global__ void __launch_bounds__(256) decode_ar_residual_norm_kernel(const floa
 // ------------------------------------------------------------------------------------------------------------
 constexpr int AR_CL = 4, AR_THREADS = 512;
 
+// PUSH = false: every rank stages its own partial rows and reads the peers' staging buffers after the handshake (one flag trip plus one remote
+// load trip). PUSH = true: every rank stores its partial rows into every peer's staging buffer (slot [rank] of a [world][rows_pad][d] layout)
+// before it raises the flags, so after the handshake all operands are in local memory (one trip).
+template <bool PUSH>
 __global__ void __cluster_dims__(AR_CL, 1, 1) __launch_bounds__(AR_THREADS)
 decode_ar_residual_norm_cluster_kernel(const float* __restrict__ partial, int splits, int64_t ldp, size_t plane_stride, ArNormArgs a, int* __restrict__ sync,
                                        __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h, int rows, int rows_pad,
@@ -461,10 +465,11 @@ decode_ar_residual_norm_cluster_kernel(const float* __restrict__ partial, int sp
   const int row = blockIdx.x / AR_CL, chunk = blockIdx.x % AR_CL;
   const int cols = d / AR_CL, c0 = chunk * cols;
   const int seq = *reinterpret_cast<volatile int*>(sync) + 1;
-  const size_t slot = (size_t)(seq & 1) * rows_pad * d;
+  const size_t slot = (size_t)(seq & 1) * rows_pad * d * (PUSH ? a.world : 1);
   const int nflag = rows_pad * AR_CL, fidx = row * AR_CL + chunk;
   // phase A: plane sum of this chunk into this rank's staging slot (float4 columns; the splits are independent loads)
-  float* mine = a.sym[a.rank] + slot + (size_t)row * d + c0;
+  const size_t my_off = slot + (PUSH ? (size_t)a.rank * rows_pad * d : 0) + (size_t)row * d + c0;
+  float* mine = a.sym[a.rank] + my_off;
   const float* prow = partial + (size_t)row * ldp + c0;
   for (int i = threadIdx.x * 4; i < cols; i += AR_THREADS * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -473,7 +478,11 @@ decode_ar_residual_norm_cluster_kernel(const float* __restrict__ partial, int sp
       const float4 v = __ldcg(reinterpret_cast<const float4*>(prow + (size_t)s * plane_stride + i));
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
-    *reinterpret_cast<float4*>(mine + i) = acc;
+    if constexpr (PUSH) {
+      for (int q = 0; q < a.world; q++) *reinterpret_cast<float4*>(a.sym[q] + my_off + i) = acc;
+    } else {
+      *reinterpret_cast<float4*>(mine + i) = acc;
+    }
   }
   bool ok = true;
   if (a.world > 1) {
@@ -494,7 +503,8 @@ decode_ar_residual_norm_cluster_kernel(const float* __restrict__ partial, int sp
   for (int i = threadIdx.x * 4; i < cols; i += AR_THREADS * 4) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < a.world; r++) {
-      const float4 p = *reinterpret_cast<const float4*>(a.sym[r] + slot + (size_t)row * d + c0 + i);
+      const float* src = PUSH ? a.sym[a.rank] + slot + ((size_t)r * rows_pad + row) * d + c0 + i : a.sym[r] + slot + (size_t)row * d + c0 + i;
+      const float4 p = PUSH ? __ldcg(reinterpret_cast<const float4*>(src)) : *reinterpret_cast<const float4*>(src);
       v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
     }
     const uint2 raw = *reinterpret_cast<const uint2*>(xr + i);
@@ -612,14 +622,19 @@ FT_EXPORT int ft_decode_ar_residual_norm(const float* partial, int splits, int64
 
 // Cluster form of ft_decode_ar_residual_norm (no grid barriers). flag blocks: u32[8][rows_pad * 4] per rank, zeroed once; sync: int[4] zeroed once.
 // d must be a multiple of 16. Launch numbers live in sync[0], so a captured launch advances on every graph replay.
+// push = 0: staging buffers hold 2 * rows_pad * d floats per rank and peers are read after the handshake;
+// push = 1: staging buffers hold 2 * world * rows_pad * d floats per rank and every rank stores its rows into all of them before the handshake.
 FT_EXPORT int ft_decode_ar_residual_norm_cluster(const float* partial, int splits, int64_t ldp, int64_t plane_stride, void* const* sym_ptrs, void* const* flag_ptrs,
                                                  int rank, int world, int* sync, void* x, const void* w, void* h, int rows, int rows_pad, int d, float eps,
-                                                 cudaStream_t st) {
+                                                 int push, cudaStream_t st) {
   if (world < 1 || world > MAXR || rows < 1 || rows > rows_pad || d % (AR_CL * 4) || (ldp & 3) || (plane_stride & 3)) return FT_ERR_ARG;
   ArNormArgs a;
   for (int i = 0; i < MAXR; i++) { a.sym[i] = i < world ? (float*)sym_ptrs[i] : nullptr; a.flags[i] = i < world ? (uint32_t*)flag_ptrs[i] : nullptr; }
   a.rank = rank;
   a.world = world;
-  return (int)ft_launch_pdl(decode_ar_residual_norm_cluster_kernel, dim3(rows * AR_CL), dim3(AR_THREADS), 0, st, partial, splits, ldp, (size_t)plane_stride, a, sync,
+  if (push)
+    return (int)ft_launch_pdl(decode_ar_residual_norm_cluster_kernel<true>, dim3(rows * AR_CL), dim3(AR_THREADS), 0, st, partial, splits, ldp, (size_t)plane_stride, a,
+                              sync, (__nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)h, rows, rows_pad, d, eps, ft_status_ptr());
+  return (int)ft_launch_pdl(decode_ar_residual_norm_cluster_kernel<false>, dim3(rows * AR_CL), dim3(AR_THREADS), 0, st, partial, splits, ldp, (size_t)plane_stride, a, sync,
                             (__nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)h, rows, rows_pad, d, eps, ft_status_ptr());
 }

@@ -188,7 +188,12 @@ class LlamaTPEngine:
         self.ar_flags_cl, self.ar_flag_ptrs_cl, self._ar_flag_buf_cl = self.ctx.symmetric(8 * PAD_ROWS * 4, torch.int32)
         self.ar_sync_cl = torch.zeros(4, device=dev, dtype=torch.int32)
         import os
-        self.ar_cluster = d % 16 == 0 and os.environ.get("FT_DECODE_AR", "grid") == "cluster"
+        form = os.environ.get("FT_DECODE_AR", "grid")
+        self.ar_cluster = d % 16 == 0 and form in ("cluster", "push")
+        # push form: every rank stores its partial rows into all staging buffers ([world][PAD_ROWS][d] per slot) and reads only local memory
+        self.ar_push = self.ar_cluster and form == "push" and self.ctx.world > 1
+        if self.ar_push:
+            self.ar_sym_push, self.ar_sym_push_ptrs, self._ar_sym_push_buf = self.ctx.symmetric(2 * self.ctx.world * PAD_ROWS * d, torch.float32)
         self.ar_sync = torch.zeros(4, device=dev, dtype=torch.int32)
         self.ar_chunks = max(1, min(16, 128 // max(B, 1)))
         while d % self.ar_chunks:
@@ -205,8 +210,9 @@ class LlamaTPEngine:
     # ------------------------------------------------------------------ pieces -------------------------------------------------------------------
     def _ar_norm(self, gemm: _SplitKGemm, w: torch.Tensor) -> None:
         if self.ar_cluster:
-            _lib.call("ft_decode_ar_residual_norm_cluster", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride, self.ar_sym_ptrs, self.ar_flag_ptrs_cl,
-                      self.ctx.rank, self.ctx.world, self.ar_sync_cl, self.x, w, self.h, self.B, PAD_ROWS, self.d, float(self.cfg.rms_norm_eps), _lib.S())
+            _lib.call("ft_decode_ar_residual_norm_cluster", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride,
+                      self.ar_sym_push_ptrs if self.ar_push else self.ar_sym_ptrs, self.ar_flag_ptrs_cl, self.ctx.rank, self.ctx.world, self.ar_sync_cl,
+                      self.x, w, self.h, self.B, PAD_ROWS, self.d, float(self.cfg.rms_norm_eps), int(self.ar_push), _lib.S())
             return
         _lib.call("ft_decode_ar_residual_norm", gemm.planes, gemm.splits, gemm.ldp, gemm.plane_stride, self.ar_sym_ptrs, self.ar_flag_ptrs,
                   self.ctx.rank, self.ctx.world, self.ar_sync, self.x, w, self.h, self.ar_sumsq, self.B, PAD_ROWS, self.d, self.ar_chunks,
