@@ -235,6 +235,8 @@ class FusedShardedAdamW:
                     p.data = view
                 self.offset[u.name] = off
                 off += u.padded
+        # CTAs of the fused reduce-scatter + AdamW + all-gather launch (0 = the kernel's default of 96): it shares the SMs with the backward GEMMs
+        self.max_ctas = int(os.environ.get("FT_FSDP_CTAS", "0"))
         nbuf = len(engine._grad_pool)
         self.maxn = max(u.padded for u in units)
         self.grads = SymmetricBuffer(nbuf * self.maxn, torch.bfloat16, dev, group)
@@ -248,4 +250,4 @@ class FusedShardedAdamW:
         c = self.comm
         _lib.call("ft_fsdp_rs_adamw_ag", self.grads.ptr_array(slot * self.maxn), self.params.ptr_array(self.offset[unit.name]),
                   c.flag_ptrs, c.counter, c.rank, c.world, c._next(), unit.master, unit.exp_avg, unit.exp_avg_sq, unit.chunk, o.lr,
-                  o.betas[0], o.betas[1], o.eps, o.weight_decay, unit.step, None, 0, _lib.S())
+                  o.betas[0], o.betas[1], o.eps, o.weight_decay, unit.step, None, self.max_ctas, _lib.S())
