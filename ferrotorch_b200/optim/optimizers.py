@@ -139,17 +139,19 @@ class Sgd(Optimizer):
                 target = optimizer_target(p) if p.dtype == torch.float32 else None
                 if _fused_ok(p, p.grad) or (target is not None and _flat_pair_ok(p, p.grad, need_cuda=False)):
                     grad = p.grad
-                    if grad.stride() != p.stride():                      # bring the gradient into the parameter's memory order
-                        grad = torch.empty_like(p, dtype=grad.dtype).copy_(grad)
+                    if not (p.is_contiguous() and grad.is_contiguous()) and grad.stride() != p.stride():
+                        grad = torch.empty_like(p, dtype=grad.dtype).copy_(grad)      # bring the gradient into the parameter's memory order
                     if first:
                         st["buf"] = torch.zeros(p.numel(), device=p.device, dtype=torch.float32) if g["momentum"] else None
                         if p.dtype == torch.bfloat16:
                             st["master"] = _flat(p.detach()).float().clone()
-                    elif st.get("layout", p.stride()) != p.stride() and st["buf"] is not None:
+                    layout = None if p.is_contiguous() else p.stride()          # None: row-major order
+                    if not first and st.get("layout") != layout and st["buf"] is not None:
                         # the parameter was re-laid-out since the last step: re-order the momentum buffer to match
-                        old = torch.as_strided(st["buf"], p.shape, st["layout"])
+                        old_stride = st.get("layout") or torch.empty(p.shape, device="meta").stride()
+                        old = torch.as_strided(st["buf"], p.shape, old_stride)
                         st["buf"] = _flat(torch.empty_like(p, dtype=torch.float32).copy_(old)).clone()
-                    st["layout"] = p.stride()
+                    st["layout"] = layout
                     master = st.get("master", _flat(p.detach()))
                     low = _flat(p.detach()) if p.dtype == torch.bfloat16 else (_flat(target) if target is not None else None)
                     ops.sgd_flat_(master, low, st["buf"], _flat(grad), lr=g["lr"],
