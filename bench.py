@@ -194,6 +194,7 @@ def main():
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": "llama-3-8b" if args.layers is None else f"llama-3-8b-{args.layers}layers", "global_batch": B * world,
                        "seq_len": S, "parallelism": f"fsdp{world}-full-shard", "optimizer": "AdamW(lr=3e-4,betas=0.9/0.95), f32 master+moments",
+                       "sharding": "f32 master weights, AdamW moments and reduced gradients sharded over all ranks; gathered bf16 copy cached between steps",
                        "l2": "inputs_larger_than_L2 (16 GB of weights streamed per step)", "comm": engine.comm if world > 1 else "none",
                        "attention_backend": ft.ops.attention.backend()},
             "clocks": clocks,

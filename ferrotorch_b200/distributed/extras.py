@@ -289,26 +289,41 @@ class ShardingStrategy(enum.Enum):
     FullShard = "full_shard"
     ShardGradOp = "shard_grad_op"
     NoShard = "no_shard"
+    HybridShard = "hybrid_shard"      # shard inside a node, replicate across nodes (needs ``intra_node_size``)
 
 
 class FSDP:
-    """Each parameter is split evenly (flat) across ranks. ``forward`` all-gathers the shards into the module, ``sync_gradients``
-    reduce-scatters (mean) the full gradients back to shard gradients; the optimizer runs on ``shard_parameters()``."""
+    """Each parameter is split evenly (flat) across the ranks of its shard group. ``forward`` all-gathers the shards into the module,
+    ``sync_gradients`` reduce-scatters (mean) the full gradients back to shard gradients; the optimizer runs on ``shard_parameters()``.
+
+    ``HybridShard``: ranks ``[n*k, (n+1)*k)`` (``k = intra_node_size``) form node ``n``; parameters are sharded over the ``k`` ranks of a
+    node (contiguous block of ranks) and replicated across nodes; gradients are reduce-scattered inside the node and then averaged over the
+    ranks with the same local index in every node (strided group), as in ferrotorch-distributed/src/fsdp.rs:173-191,761-773."""
 
     def __init__(self, module: torch.nn.Module, backend: Backend, strategy: ShardingStrategy = ShardingStrategy.FullShard,
-                 timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT):
+                 timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT, intra_node_size: Optional[int] = None):
         self.module, self.b, self.strategy, self.timeout = module, backend, strategy, timeout
         self.world, self.rank = backend.world_size(), backend.rank()
+        self.shard_b, self.repl_b = backend, None              # group the shards live in; group the shards are replicated over
+        if strategy == ShardingStrategy.HybridShard:
+            k = intra_node_size
+            if not k or k < 1 or self.world % k:
+                raise errors.InvalidArgument(f"HybridShard needs an intra_node_size that divides the world size {self.world}, got {k}")
+            node, local = divmod(self.rank, k)
+            from .backend import SubBackend
+            self.shard_b = SubBackend(backend, list(range(node * k, (node + 1) * k)))
+            self.repl_b = SubBackend(backend, list(range(local, self.world, k))) if self.world > k else None
+        self.shard_world, self.shard_rank = self.shard_b.world_size(), self.shard_b.rank()
         self.params = [p for p in module.parameters()]
         self.shards: List[torch.nn.Parameter] = []
         for p in self.params:
             if strategy == ShardingStrategy.NoShard:
                 self.shards.append(torch.nn.Parameter(p.detach().clone().reshape(-1)))
                 continue
-            if p.numel() % self.world:
-                raise errors.ShapeMismatch(f"parameter of {p.numel()} elements is not divisible by world size {self.world}")
-            c = p.numel() // self.world
-            self.shards.append(torch.nn.Parameter(p.detach().reshape(-1)[self.rank * c:(self.rank + 1) * c].clone()))
+            if p.numel() % self.shard_world:
+                raise errors.ShapeMismatch(f"parameter of {p.numel()} elements is not divisible by the shard group size {self.shard_world}")
+            c = p.numel() // self.shard_world
+            self.shards.append(torch.nn.Parameter(p.detach().reshape(-1)[self.shard_rank * c:(self.shard_rank + 1) * c].clone()))
 
     def shard_parameters(self) -> List[torch.nn.Parameter]:
         return self.shards
@@ -316,7 +331,7 @@ class FSDP:
     def _gather_into_module(self) -> None:
         with torch.no_grad():
             for p, s in zip(self.params, self.shards):
-                full = s.detach() if self.strategy == ShardingStrategy.NoShard else all_gather(s.detach(), self.b, self.timeout)
+                full = s.detach() if self.strategy == ShardingStrategy.NoShard else all_gather(s.detach(), self.shard_b, self.timeout)
                 p.copy_(full.view_as(p))
 
     def forward(self, *a, **k):
@@ -332,6 +347,9 @@ class FSDP:
                 s.grad = allreduce(g, self.b, ReduceOp.Mean, self.timeout)
             elif self.strategy == ShardingStrategy.FullShard:
                 s.grad = reduce_scatter(g, self.b, ReduceOp.Mean, self.timeout)
+            elif self.strategy == ShardingStrategy.HybridShard:
+                sg = reduce_scatter(g, self.shard_b, ReduceOp.Mean, self.timeout)               # mean over the node
+                s.grad = allreduce(sg, self.repl_b, ReduceOp.Mean, self.timeout) if self.repl_b is not None else sg   # mean over nodes
             else:   # ZeRO-2: reduce the full gradient, keep only this rank's slice
                 full = allreduce(g, self.b, ReduceOp.Mean, self.timeout)
                 c = p.numel() // self.world

@@ -76,13 +76,23 @@ class _EngineOwner:
 
 class FSDP:
     """Training engine: ``loss = engine.train_step(ids, labels)`` runs forward, backward, gradient
-    reduce-scatter, sharded AdamW and parameter all-gather for one micro-batch per rank."""
+    reduce-scatter, sharded AdamW and parameter all-gather for one micro-batch per rank.
+
+    What is sharded: the f32 master weights, both AdamW moments and the reduced gradients live only on the owner of each slice (every
+    parameter is owned, updated and checkpointed in shards). The bf16 all-gathered copy that the GEMMs read is kept resident between steps
+    as a cache (16 GB of an 8B model per GPU, out of 180 GB) and is refreshed by the all-gather that follows each unit's update, so a step
+    moves every parameter across the fabric once (after the update) instead of twice (before forward and again before backward) and the
+    gather is hidden behind the rest of the backward pass. ``FULL_SHARD`` and ``SHARD_GRAD_OP`` therefore run the same schedule here;
+    ``NO_SHARD`` (use :class:`ferrotorch_b200.parallel.DDP`) and ``HYBRID_SHARD`` (one NVSwitch domain has no second level) are refused."""
 
     def __init__(self, model, optim: AdamWConfig | None = None, process_group=None, strategy: ShardingStrategy = ShardingStrategy.FULL_SHARD,
                  comm: str | None = None, grad_buffers: int = 2, overlap_optimizer: bool = True):
         import torch.distributed as dist
         self.model = model
         self.optim = optim or AdamWConfig()
+        if strategy not in (ShardingStrategy.FULL_SHARD, ShardingStrategy.SHARD_GRAD_OP):
+            raise InvalidArgument(f"{strategy} is not available in the device engine: use parallel.DDP for NO_SHARD; HYBRID_SHARD needs more than "
+                                  "one NVSwitch domain (the host-side distributed.FSDP implements both)")
         self.strategy = strategy
         self.pg = process_group
         self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
@@ -142,7 +152,7 @@ class FSDP:
         return unit.views()
 
     def _release_params(self, unit: FlatUnit, after_forward: bool) -> None:
-        pass  # compute copies stay resident (16 GB for an 8B model); see `reshard` in the class docstring
+        pass  # the gathered bf16 copy stays resident as a cache (see the class docstring)
 
     def _acquire_grads(self, unit: FlatUnit) -> Dict[str, torch.Tensor]:
         slot = self._unit_grad_slot.get(unit.name)

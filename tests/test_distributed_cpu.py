@@ -449,3 +449,31 @@ def test_comm_trace_decoding_and_chrome_events():
     assert recs[0]["wait_peers_us"] == 4.0 and recs[0]["body_us"] == 50.0 and recs[0]["drain_us"] == 2.0 and recs[0]["total_us"] == 56.0
     ev = CommTrace.chrome_events(recs, pid=3)
     assert len(ev) == 6 and ev[0]["name"] == "all_reduce:wait_peers" and ev[1]["ts"] == 1004.0 and ev[5]["dur"] == 1.5 and ev[0]["pid"] == 3
+
+
+def test_cpu_fsdp_hybrid_shard_world4_nodes_of_2():
+    """HybridShard on 4 ranks with nodes of 2: shards live inside a node (contiguous ranks), are replicated across nodes (strided ranks),
+    and the shard gradients are the global mean."""
+    torch.manual_seed(3)
+    base = torch.nn.Linear(4, 2)
+    xs = [torch.randn(3, 4) for _ in range(4)]
+    ref = torch.nn.Linear(4, 2)
+    ref.load_state_dict(base.state_dict())
+    sum(ref(x).sum() / 4 for x in xs).backward()
+
+    def fn(b, r):
+        m = torch.nn.Linear(4, 2)
+        m.load_state_dict(base.state_dict())
+        f = fd.FSDP(m, b, fd.ShardingStrategy.HybridShard, timeout=20, intra_node_size=2)
+        assert f.shard_world == 2 and f.shard_rank == r % 2 and f.shard_parameters()[0].numel() == 4
+        f(xs[r]).sum().backward()
+        f.sync_gradients()
+        return [s.grad.clone() for s in f.shard_parameters()], [s.detach().clone() for s in f.shard_parameters()]
+    res = _threads(4, fn)
+    full_w = ref.weight.grad.reshape(-1)
+    for node in range(2):
+        assert torch.allclose(torch.cat([res[2 * node][0][0], res[2 * node + 1][0][0]]), full_w, atol=1e-6)
+    assert torch.equal(res[0][1][0], res[2][1][0]) and torch.equal(res[1][1][0], res[3][1][0])          # replicas across nodes
+    assert torch.equal(res[0][0][0], res[2][0][0])                                                         # and their gradients
+    with pytest.raises(Exception):
+        _threads(4, lambda b, r: fd.FSDP(torch.nn.Linear(4, 2), b, fd.ShardingStrategy.HybridShard, intra_node_size=3))
