@@ -89,7 +89,16 @@ class Linear(Module):
             torch.nn.init.zeros_(self.bias)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias)
+        w = self.weight
+        if w.dtype == torch.float32 and x.dim() >= 2 and self.in_features % 8 == 0 and self.out_features % 8 == 0 \
+                and torch.is_autocast_enabled(x.device.type) and torch.get_autocast_dtype(x.device.type) == torch.bfloat16:
+            from .compute_copy import compute_copy
+            wc = compute_copy(w)
+            if wc is not None and wc.dtype == torch.bfloat16:
+                # f32 master with an optimizer-maintained bf16 copy: no cast launch, f32 weight gradient straight from the GEMM
+                b = None if self.bias is None else self.bias.to(torch.bfloat16)
+                return ops.linear_master(x.to(torch.bfloat16), w, wc, b)
+        return ops.linear(x, w, self.bias)
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}"

@@ -75,3 +75,33 @@ def test_conv3x3_master_matches_reference_and_trains():
     before = w.detach().clone()
     opt.step()
     assert not torch.equal(before, w.detach()) and torch.equal(compute_copy(w), w.detach().bfloat16())
+
+
+def test_linear_module_uses_the_copy_under_autocast_and_training_follows_the_plain_run():
+    """An MLP with f32 masters under bf16 autocast, trained with and without compute copies: same losses up to bf16 rounding of the weight
+    gradients, f32 gradients on the masters, copies equal to the rounded masters after every step."""
+    def run(copies: bool):
+        torch.manual_seed(4)
+        m = nn.Sequential(nn.Linear(32, 64), nn.ReLU(), nn.Linear(64, 8))
+        if copies:
+            assert nn.attach_compute_copies(m) == 2
+        opt = optim.Sgd(m.parameters(), lr=0.05, momentum=0.9)
+        g = torch.Generator().manual_seed(5)
+        x, y = torch.randn(64, 32, generator=g), torch.randint(0, 8, (64,), generator=g)
+        losses = []
+        for _ in range(5):
+            opt.zero_grad()
+            with torch.autocast("cpu", dtype=torch.bfloat16):
+                loss = torch.nn.functional.cross_entropy(m(x).float(), y)
+            loss.backward()
+            assert all(p.grad.dtype == torch.float32 for p in m.parameters())
+            opt.step()
+            losses.append(float(loss.detach()))
+            if copies:
+                for p in m.parameters():
+                    if p.dim() == 2:
+                        assert torch.equal(compute_copy(p), p.detach().bfloat16())
+        return losses
+    plain, shadow = run(False), run(True)
+    assert shadow[-1] < shadow[0]
+    assert all(abs(a - b) < 0.05 for a, b in zip(plain, shadow)), (plain, shadow)
