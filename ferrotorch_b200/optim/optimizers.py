@@ -209,11 +209,16 @@ class AdamW(Optimizer):
                 st["step"] += 1
                 t = st["step"]
                 grad = p.grad
-                if self._decoupled and not g["amsgrad"] and _fused_ok(p, grad):
+                # a row-major f32 parameter with a compute copy takes the flat kernel on any device: the copy is rewritten with the master
+                target = optimizer_target(p) if (p.dtype == torch.float32 and p.is_contiguous() and grad.is_contiguous()) else None
+                if self._decoupled and not g["amsgrad"] and (_fused_ok(p, grad) or (target is not None and not grad.is_sparse)):
                     master = st.get("master", p.view(-1))
-                    ops.adamw_flat_(master, p.view(-1) if p.dtype == torch.bfloat16 else None, st["exp_avg"], st["exp_avg_sq"],
+                    low = p.view(-1) if p.dtype == torch.bfloat16 else (target.view(-1) if target is not None else None)
+                    ops.adamw_flat_(master, low, st["exp_avg"], st["exp_avg_sq"],
                                     grad.reshape(-1), lr=g["lr"], beta1=b1, beta2=b2, eps=g["eps"], weight_decay=g["weight_decay"], step=t,
                                     maximize=g["maximize"])
+                    if target is not None:
+                        mark_synced(p)
                     continue
                 gr = grad.detach().float().reshape(-1)
                 if g["maximize"]:

@@ -105,3 +105,18 @@ def test_linear_module_uses_the_copy_under_autocast_and_training_follows_the_pla
     plain, shadow = run(False), run(True)
     assert shadow[-1] < shadow[0]
     assert all(abs(a - b) < 0.05 for a, b in zip(plain, shadow)), (plain, shadow)
+
+
+def test_adamw_keeps_the_copy_in_step_and_matches_torch():
+    torch.manual_seed(6)
+    w = torch.nn.Parameter(torch.randn(16, 8))
+    ref = torch.nn.Parameter(w.detach().clone())
+    nn.attach_compute_copies([w])
+    a, b = optim.AdamW([w], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1), torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    for _ in range(4):
+        g = torch.randn(16, 8)
+        w.grad, ref.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+        assert torch.allclose(w.detach(), ref.detach(), atol=1e-6)
+        assert torch.equal(compute_copy(w), w.detach().bfloat16())
