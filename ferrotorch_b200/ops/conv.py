@@ -16,6 +16,45 @@ from .. import _lib
 from ..errors import InvalidArgument
 
 _FORCE_LIBRARY = os.environ.get("FT_CONV_BACKEND", "") == "cudnn"
+_WGRAD_GEMM = os.environ.get("FT_CONV_WGRAD", "") == "gemm"          # weight gradients as nine shifted GEMMs instead of the library routine
+
+
+def conv3x3_wgrad_gemm(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """Weight gradient of the 3x3 / stride 1 / padding 1 convolution as nine GEMMs on the tcgen05 kernel, no im2col buffer.
+
+    Pad both the activation and the output gradient by one pixel (zeros) and flatten them to row matrices ``Xp [J, Cin]`` and ``dYp [J, Cout]``
+    with ``J = N (H+2) (W+2)``. Because ``dYp`` is zero on the halo, the gradient of filter tap ``(r, s)`` is a plain product with one of the
+    operands shifted by a constant number of rows::
+
+        dW[:, r, s, :] = dYp[j]^T  Xp[j + (r-1)(W+2) + (s-1)]        summed over all rows j
+
+    i.e. ``gemm(dYp, Xp_shifted, a_mn=True, b_mn=True)`` with K = J (split over the SMs as f32 planes, like the 1x1 weight gradient).
+    ``x``, ``dy``: channels-last bf16 ``[N, C, H, W]`` / ``[N, Cout, H, W]``. Returns f32 ``[Cout, 3, 3, Cin]``.
+    (The reference has no device-side convolution backward at all: ferrotorch-nn/src/conv.rs:888-903.)"""
+    from .gemm import gemm
+    N, C, H, W = x.shape
+    Co = dy.shape[1]
+    if dy.shape != (N, Co, H, W) or C % 8 or Co % 8:
+        raise InvalidArgument("conv3x3_wgrad_gemm needs matching [N, C, H, W] tensors with channel counts that are multiples of 8")
+    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, C)
+    dyp = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, Co)
+    J = xp.shape[0]
+    out = torch.empty((3, 3, Co, C), device=x.device, dtype=torch.float32)
+    for r in range(3):
+        for s in range(3):
+            delta = (r - 1) * (W + 2) + (s - 1)
+            k0, k1 = max(0, -delta), J - max(0, delta)          # the clipped rows are halo rows of dYp (zeros)
+            gemm(dyp[k0:k1], xp[k0 + delta: k1 + delta], a_mn=True, b_mn=True, out=out[r, s])
+    return out.permute(2, 0, 1, 3).contiguous()
+
+
+def _weight_grad(x: torch.Tensor, dy: torch.Tensor, wshape) -> torch.Tensor:
+    """dW in the logical ``[Cout, Cin, 3, 3]`` shape (dtype of the route taken: f32 from the GEMMs, the activation dtype from the library)."""
+    if _WGRAD_GEMM and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and dy.shape[1] % 8 == 0:
+        return conv3x3_wgrad_gemm(x, dy).permute(0, 3, 1, 2)
+    if x.is_cuda:
+        return torch.nn.grad.conv2d_weight(x, wshape, dy, padding=1)
+    return torch.nn.grad.conv2d_weight(x.float(), wshape, dy.float(), padding=1)
 
 
 def conv3x3_eligible(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, groups) -> bool:
@@ -67,7 +106,7 @@ class _Conv3x3Fn(torch.autograd.Function):
             else:
                 dx = torch.nn.grad.conv2d_input(x.shape, weight.to(dy.dtype), dy, padding=1)
         if ctx.needs_input_grad[1]:
-            dw = torch.nn.grad.conv2d_weight(x, weight.shape, dy, padding=1).to(weight.dtype)
+            dw = _weight_grad(x, dy, weight.shape).to(weight.dtype)
         return dx, dw
 
 
@@ -95,10 +134,7 @@ class _Conv3x3MasterFn(torch.autograd.Function):
             else:
                 dx = torch.nn.grad.conv2d_input(x.shape, wk.permute(0, 3, 1, 2), dy, padding=1)
         if ctx.needs_input_grad[1]:
-            if x.is_cuda:
-                dw = torch.nn.grad.conv2d_weight(x, ctx.wshape, dy, padding=1)
-            else:
-                dw = torch.nn.grad.conv2d_weight(x.float(), ctx.wshape, dy.float(), padding=1)
+            dw = _weight_grad(x, dy, ctx.wshape)
             # f32, in the master's memory layout, so the optimizer can walk parameter and gradient in one order
             dw = torch.empty_strided(ctx.wshape, ctx.wstride, device=dw.device, dtype=torch.float32).copy_(dw)
         return dx, dw, None

@@ -120,3 +120,15 @@ def test_adamw_keeps_the_copy_in_step_and_matches_torch():
         b.step()
         assert torch.allclose(w.detach(), ref.detach(), atol=1e-6)
         assert torch.equal(compute_copy(w), w.detach().bfloat16())
+
+
+@pytest.mark.parametrize("N,C,Co,H,W", [(2, 8, 16, 5, 7), (3, 16, 8, 4, 4), (1, 8, 8, 1, 1), (2, 8, 8, 3, 9)])
+def test_conv3x3_weight_gradient_as_shifted_gemms(N, C, Co, H, W):
+    """dW of a padded 3x3 convolution = nine products of the zero-padded output gradient with row-shifted views of the zero-padded input."""
+    torch.manual_seed(N + C + H)
+    x = torch.randn(N, C, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(N, Co, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    got = ops.conv.conv3x3_wgrad_gemm(x, dy)
+    ref = torch.nn.grad.conv2d_weight(x.float(), (Co, C, 3, 3), dy.float(), padding=1).permute(0, 2, 3, 1)
+    assert got.shape == (Co, 3, 3, C) and got.dtype == torch.float32
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-4)
