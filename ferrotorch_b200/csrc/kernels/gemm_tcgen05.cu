@@ -88,6 +88,10 @@ struct TailArgs {
   int slices;                    // S
   float* ws;                     // [tiles][S-1][4 quarters][chunks][EPI_COLS/4][32 lanes] float4
   uint32_t* cnt;                 // [tiles][4], zero between launches
+  // Row-shift table of the B operand (MN-major B only; 0 = off), used by the 3x3 convolution weight gradient: the N axis is [tap][channel] with
+  // b_atoms_per_tap 64-channel atoms per filter tap, and the atom of tap t = 3r + s is fetched from B's columns of that channel block at rows
+  // k + (r - 1) * b_row_pitch + (s - 1). Atoms past the ninth tap and rows outside B read as zeros (TMA fill).
+  int b_atoms_per_tap, b_row_pitch;
 };
 
 struct WorkItem {
@@ -184,9 +188,18 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if constexpr (!B_MN) {
             tma_load_2d(b_dst, &tmB, &full_bar[s], kb * BK, n0);
-          } else {
+          } else if (tail.b_atoms_per_tap == 0) {
 #pragma unroll
             for (int j = 0; j < BN / 64; j++) tma_load_2d(b_dst + j * (BK * 128), &tmB, &full_bar[s], n0 + j * 64, kb * BK);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++) {
+              const int g = n0 / 64 + j, tap = g / tail.b_atoms_per_tap;
+              // beyond the ninth tap: a column past B's width, so the box is zero filled and the full byte count still arrives
+              const int col = tap < 9 ? (g % tail.b_atoms_per_tap) * 64 : tail.b_atoms_per_tap * 64;
+              const int row = kb * BK + (tap < 9 ? (tap / 3 - 1) * tail.b_row_pitch + (tap % 3 - 1) : 0);
+              tma_load_2d(b_dst + j * (BK * 128), &tmB, &full_bar[s], col, row);
+            }
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -407,7 +420,7 @@ TailWs g_tail_ws[64][TAIL_SLOTS] = {};
 int g_tail_enabled = -1;
 
 TailArgs plan_tail(int dev, int tiles, int num_kb, int k_splits, int sms, cudaStream_t stream) {
-  TailArgs t{0, 1, nullptr, nullptr};
+  TailArgs t{0, 1, nullptr, nullptr, 0, 0};
   if (g_tail_enabled < 0) {
     const char* e = getenv("FT_GEMM_TAIL");
     g_tail_enabled = (e && e[0] == '1') ? 1 : 0;
@@ -465,8 +478,10 @@ int g_num_sms[64] = {0};
 
 }  // namespace
 
+// b_cols > 0 (with b_atoms_per_tap, b_row_pitch): B is a [K, b_cols] matrix read through the row-shift table of TailArgs while N spans nine taps.
 static int gemm_impl(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb,
-                     int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream, EpiArgs epi = EpiArgs{0, nullptr, 0, 0}) {
+                     int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream, EpiArgs epi = EpiArgs{0, nullptr, 0, 0},
+                     int b_cols = 0, int b_atoms_per_tap = 0, int b_row_pitch = 0) {
   if (epi.act < 0 || epi.act > 4) return FT_ERR_ARG;
   const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
@@ -483,7 +498,7 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
   else       r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
-  else       r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)(b_cols > 0 ? b_cols : N), (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   const uint64_t eb = out_f32 ? 4 : 2;
   r = ft_make_tmap_3d(&tD, D, (int)eb, !out_f32 && in_bf16, (uint64_t)N, (uint64_t)M, (uint64_t)k_splits, (uint64_t)ldd * eb, (uint64_t)M * ldd * eb,
@@ -491,7 +506,12 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
   if (r) return r;
 
   const int sms = g_num_sms[dev];
-  const TailArgs tail = plan_tail(dev, ((M + BM - 1) / BM) * ((N + BN - 1) / BN), (K + BK - 1) / BK, k_splits, sms, stream);
+  TailArgs tail = plan_tail(dev, ((M + BM - 1) / BM) * ((N + BN - 1) / BN), (K + BK - 1) / BK, k_splits, sms, stream);
+  if (b_atoms_per_tap > 0) {
+    if (!b_mn || b_cols != b_atoms_per_tap * 64 || N != 9 * b_cols || b_row_pitch < 3) return FT_ERR_ARG;
+    tail.b_atoms_per_tap = b_atoms_per_tap;
+    tail.b_row_pitch = b_row_pitch;
+  }
 #define FT_GEMM_CASE(AM, BMN, OF) \
   if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream, epi, tail);
   FT_GEMM_CASE(0, 0, 0) FT_GEMM_CASE(0, 1, 0) FT_GEMM_CASE(1, 0, 0) FT_GEMM_CASE(1, 1, 0)
@@ -529,4 +549,16 @@ FT_EXPORT int ft_gemm_ex(const void* A, const void* B, void* D, const void* bias
 FT_EXPORT int ft_gemm_bf16_splitk(const void* A, const void* B, float* partial, int M, int N, int K, int64_t lda, int64_t ldb,
                                   int64_t ldd, int a_mn, int b_mn, int k_splits, cudaStream_t stream) {
   return gemm_impl(A, B, partial, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, 1, k_splits, stream);
+}
+
+// Weight gradient of the 3x3 / stride 1 / padding 1 convolution as ONE split-K GEMM: dW[co][tap][ci] = sum_j dYp[j][co] * Xp[j + shift(tap)][ci].
+// dyp: bf16 [J, Cout] and xp: bf16 [J, Cin], the output gradient and the input zero-padded by one pixel per side and flattened to rows
+// (J = N (H+2) (W+2), row_pitch = W + 2); because dYp is zero on the halo, every tap is the same product with Xp shifted by a constant
+// number of rows, which the B loads of the GEMM apply through its row-shift table (rows outside Xp read as zeros).
+// planes: f32 [k_splits][Cout][9 * Cin]; the caller sums them (ft_splitk_reduce). Cin must be a multiple of 64, Cout of 8.
+FT_EXPORT int ft_conv3x3_wgrad_splitk(const void* dyp, const void* xp, float* planes, int Cout, int Cin, int64_t J, int row_pitch, int k_splits,
+                                      cudaStream_t stream) {
+  if (Cin <= 0 || Cin % 64 || Cout <= 0 || Cout % 8 || J <= 0 || J > 0x7fffffffll) return FT_ERR_ARG;
+  return gemm_impl(dyp, xp, planes, nullptr, Cout, 9 * Cin, (int)J, Cout, Cin, 9 * (int64_t)Cin, 1, 1, 1, k_splits, stream, EpiArgs{0, nullptr, 0, 0}, Cin, Cin / 64,
+                   row_pitch);
 }

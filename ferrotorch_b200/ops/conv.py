@@ -8,6 +8,7 @@ Reference parity: ferrotorch-nn/src/conv.rs:261 (Conv2d; CUDA forward :584-597, 
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -16,7 +17,8 @@ from .. import _lib
 from ..errors import InvalidArgument
 
 _FORCE_LIBRARY = os.environ.get("FT_CONV_BACKEND", "") == "cudnn"
-_WGRAD_GEMM = os.environ.get("FT_CONV_WGRAD", "") == "gemm"          # weight gradients as nine shifted GEMMs instead of the library routine
+# weight gradients: "" = library routine, "gemm" = nine shifted launches of the GEMM, "fused" = one launch with the GEMM's row-shift table
+_WGRAD_MODE = os.environ.get("FT_CONV_WGRAD", "")
 
 
 def conv3x3_wgrad_gemm(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
@@ -48,9 +50,44 @@ def conv3x3_wgrad_gemm(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
     return out.permute(2, 0, 1, 3).contiguous()
 
 
+def _wgrad_splits(Cout: int, Cin: int, J: int) -> int:
+    """K slices of the fused weight-gradient GEMM: its [Cout, 9 Cin] output has few tiles, so the J rows are spread over the SMs."""
+    tiles = -(-Cout // 128) * -(-9 * Cin // 256)
+    num_kb = -(-J // 64)
+    splits = max(1, min(148 // max(tiles, 1) if tiles < 148 else 1, num_kb // 8, 64))
+    while splits > 1 and -(-num_kb // splits) * (splits - 1) >= num_kb:
+        splits -= 1
+    return splits
+
+
+def conv3x3_wgrad_fused(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+    """The nine shifted products of :func:`conv3x3_wgrad_gemm` as one split-K launch of the tcgen05 GEMM: its N axis is ``[tap][Cin]`` and the
+    producer warp fetches the B atoms of tap ``(r, s)`` from rows ``k + (r-1)(W+2) + (s-1)`` of the padded input (zero fill outside), so the
+    output ``[Cout, 9 Cin]`` is the gradient in ``[Cout, 3, 3, Cin]`` order. Needs ``Cin % 64 == 0`` and ``Cout % 8 == 0``; CUDA only."""
+    from .gemm import _plane_cache
+    N, C, H, W = x.shape
+    Co = dy.shape[1]
+    if dy.shape != (N, Co, H, W) or C % 64 or Co % 8 or not x.is_cuda or x.dtype != torch.bfloat16 or dy.dtype != torch.bfloat16:
+        raise InvalidArgument("conv3x3_wgrad_fused needs CUDA bf16 [N, C, H, W] tensors with Cin % 64 == 0 and Cout % 8 == 0")
+    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, C)
+    dyp = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, Co)
+    J = xp.shape[0]
+    splits = _wgrad_splits(Co, C, J)
+    n_out = Co * 9 * C
+    planes = _plane_cache(x.device, splits * n_out)[: splits * n_out]
+    out = torch.empty((Co, 3, 3, C), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        _lib.call("ft_conv3x3_wgrad_splitk", dyp, xp, planes, Co, C, J, W + 2, splits, _lib.S())
+        _lib.call("ft_splitk_reduce", planes, splits, Co, 9 * C, ctypes.c_int64(9 * C), ctypes.c_int64(n_out), None, out,
+                  ctypes.c_int64(9 * C), 1, _lib.S())
+    return out
+
+
 def _weight_grad(x: torch.Tensor, dy: torch.Tensor, wshape) -> torch.Tensor:
     """dW in the logical ``[Cout, Cin, 3, 3]`` shape (dtype of the route taken: f32 from the GEMMs, the activation dtype from the library)."""
-    if _WGRAD_GEMM and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and dy.shape[1] % 8 == 0:
+    if _WGRAD_MODE == "fused" and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 64 == 0 and dy.shape[1] % 8 == 0:
+        return conv3x3_wgrad_fused(x, dy).permute(0, 3, 1, 2)
+    if _WGRAD_MODE in ("gemm", "fused") and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and dy.shape[1] % 8 == 0:
         return conv3x3_wgrad_gemm(x, dy).permute(0, 3, 1, 2)
     if x.is_cuda:
         return torch.nn.grad.conv2d_weight(x, wshape, dy, padding=1)

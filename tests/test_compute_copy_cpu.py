@@ -132,3 +132,38 @@ def test_conv3x3_weight_gradient_as_shifted_gemms(N, C, Co, H, W):
     ref = torch.nn.grad.conv2d_weight(x.float(), (Co, C, 3, 3), dy.float(), padding=1).permute(0, 2, 3, 1)
     assert got.shape == (Co, 3, 3, C) and got.dtype == torch.float32
     assert torch.allclose(got, ref, rtol=1e-5, atol=1e-4)
+
+
+def test_row_shift_table_of_the_fused_weight_gradient_gemm():
+    """Host restatement of what the GEMM's producer does for the fused 3x3 weight gradient: 64-channel atom g of the N axis belongs to tap
+    g // atoms_per_tap, reads channel block g % atoms_per_tap of the padded input at rows k + (r-1) * pitch + (s-1) (zeros outside, zeros for
+    atoms past the ninth tap); the [Cout, 9 Cin] product must be the convolution's weight gradient in [Cout, 3, 3, Cin] order."""
+    torch.manual_seed(11)
+    N, C, Co, H, W = 2, 128, 16, 5, 6
+    x = torch.randn(N, C, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(N, Co, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).reshape(-1, C).float()
+    dyp = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).reshape(-1, Co).float()
+    J, apt, pitch = xp.shape[0], C // 64, W + 2
+    n_tiles = -(-9 * C // 256)
+    out = torch.zeros(Co, n_tiles * 256)
+    for n0 in range(0, n_tiles * 256, 256):
+        for j in range(4):
+            g = n0 // 64 + j
+            tap = g // apt
+            if tap >= 9:
+                continue                                             # zero-filled box
+            col = (g % apt) * 64
+            shift = (tap // 3 - 1) * pitch + (tap % 3 - 1)
+            b = torch.zeros(J, 64)
+            lo, hi = max(0, -shift), J - max(0, shift)
+            b[lo:hi] = xp[lo + shift: hi + shift, col: col + 64]
+            out[:, n0 + j * 64: n0 + (j + 1) * 64] = dyp.t() @ b
+    got = out[:, : 9 * C].reshape(Co, 3, 3, C)
+    ref = torch.nn.grad.conv2d_weight(x.float(), (Co, C, 3, 3), dy.float(), padding=1).permute(0, 2, 3, 1)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-4)
+    from ferrotorch_b200.ops.conv import _wgrad_splits
+    for co, ci, j in [(64, 64, 861184), (128, 128, 230400), (512, 512, 20736), (8, 64, 100)]:
+        s = _wgrad_splits(co, ci, j)
+        nkb = -(-j // 64)
+        assert 1 <= s <= 64 and (s == 1 or -(-nkb // s) * (s - 1) < nkb)
