@@ -88,10 +88,16 @@ struct TailArgs {
   int slices;                    // S
   float* ws;                     // [tiles][S-1][4 quarters][chunks][EPI_COLS/4][32 lanes] float4
   uint32_t* cnt;                 // [tiles][4], zero between launches
-  // Row-shift table of the B operand (MN-major B only; 0 = off), used by the 3x3 convolution weight gradient: the N axis is [tap][channel] with
-  // b_atoms_per_tap 64-channel atoms per filter tap, and the atom of tap t = 3r + s is fetched from B's columns of that channel block at rows
-  // k + (r - 1) * b_row_pitch + (s - 1). Atoms past the ninth tap and rows outside B read as zeros (TMA fill).
-  int b_atoms_per_tap, b_row_pitch;
+  // Row-shift table of the B operand (MN-major B only; b_atoms_per_tap = 0: off), used by convolution weight gradients: the N axis is
+  // [tap][channel] with b_atoms_per_tap 64-channel atoms per filter tap, and the atom of tap t is fetched from B's columns of that channel block
+  // at rows k + b_shift[t]. Atoms past the ninth tap and rows outside B read as zeros (TMA fill).
+  int b_atoms_per_tap;
+  int b_shift[9];
+  // The same for a K-major A operand (a_atoms_per_tap = 0: off), used by convolutions evaluated as one GEMM over pixel rows: the K axis is
+  // [tap][channel] with a_atoms_per_tap 64-channel k-blocks per filter tap, and k-block kb of tap t = kb / a_atoms_per_tap is fetched from
+  // A's columns (kb % a_atoms_per_tap) * 64 at rows m + a_shift[t] (zeros outside A).
+  int a_atoms_per_tap;
+  int a_shift[9];
 };
 
 struct WorkItem {
@@ -99,6 +105,14 @@ struct WorkItem {
   int tail;                      // index of the tail tile or -1
   int slice;                     // K slice of a tail tile (0 = owner)
 };
+
+// shift[t] by a chain of selects: the tables are kernel parameters and a run-time index would make the compiler copy them to local memory
+FT_DEVICE int pick_shift(const int (&shift)[9], int t) {
+  int v = shift[0];
+#pragma unroll
+  for (int i = 1; i < 9; i++) v = (t == i) ? shift[i] : v;
+  return v;
+}
 
 FT_DEVICE WorkItem decode_item(int item, int k_splits, int kb_per, int num_kb_total, int full_items, const TailArgs& t) {
   WorkItem w;
@@ -181,7 +195,8 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* a_dst = sA + s * A_STAGE_BYTES;
           uint8_t* b_dst = sB + s * B_STAGE_BYTES;
           if constexpr (!A_MN) {
-            tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BK, m0);
+            if (tail.a_atoms_per_tap == 0) tma_load_2d(a_dst, &tmA, &full_bar[s], kb * BK, m0);
+            else tma_load_2d(a_dst, &tmA, &full_bar[s], (kb % tail.a_atoms_per_tap) * 64, m0 + pick_shift(tail.a_shift, kb / tail.a_atoms_per_tap));
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; j++) tma_load_2d(a_dst + j * (BK * 128), &tmA, &full_bar[s], m0 + j * 64, kb * BK);
@@ -197,7 +212,7 @@ ft_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const int g = n0 / 64 + j, tap = g / tail.b_atoms_per_tap;
               // beyond the ninth tap: a column past B's width, so the box is zero filled and the full byte count still arrives
               const int col = tap < 9 ? (g % tail.b_atoms_per_tap) * 64 : tail.b_atoms_per_tap * 64;
-              const int row = kb * BK + (tap < 9 ? (tap / 3 - 1) * tail.b_row_pitch + (tap % 3 - 1) : 0);
+              const int row = kb * BK + (tap < 9 ? pick_shift(tail.b_shift, tap) : 0);
               tma_load_2d(b_dst + j * (BK * 128), &tmB, &full_bar[s], col, row);
             }
           }
@@ -420,7 +435,7 @@ TailWs g_tail_ws[64][TAIL_SLOTS] = {};
 int g_tail_enabled = -1;
 
 TailArgs plan_tail(int dev, int tiles, int num_kb, int k_splits, int sms, cudaStream_t stream) {
-  TailArgs t{0, 1, nullptr, nullptr, 0, 0};
+  TailArgs t{0, 1, nullptr, nullptr, 0, {0, 0, 0, 0, 0, 0, 0, 0, 0}, 0, {0, 0, 0, 0, 0, 0, 0, 0, 0}};
   if (g_tail_enabled < 0) {
     const char* e = getenv("FT_GEMM_TAIL");
     g_tail_enabled = (e && e[0] == '1') ? 1 : 0;
@@ -478,10 +493,11 @@ int g_num_sms[64] = {0};
 
 }  // namespace
 
-// b_cols > 0 (with b_atoms_per_tap, b_row_pitch): B is a [K, b_cols] matrix read through the row-shift table of TailArgs while N spans nine taps.
+// b_cols > 0 (with b_atoms_per_tap, b_shift[9]): B is a [K, b_cols] matrix read through the row-shift table of TailArgs while N spans nine taps.
 static int gemm_impl(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb,
                      int64_t ldd, int a_mn, int b_mn, int out_f32, int k_splits, cudaStream_t stream, EpiArgs epi = EpiArgs{0, nullptr, 0, 0},
-                     int b_cols = 0, int b_atoms_per_tap = 0, int b_row_pitch = 0) {
+                     int b_cols = 0, int b_atoms_per_tap = 0, const int* b_shift = nullptr, int a_cols = 0, int64_t a_rows = 0, int a_taps = 0,
+                     const int* a_shift = nullptr, int64_t b_rows = 0) {
   if (epi.act < 0 || epi.act > 4) return FT_ERR_ARG;
   const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
@@ -494,11 +510,15 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
 
   CUtensorMap tA, tB, tD;
   int r;
-  if (!a_mn) r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+  // a_cols > 0: A is an [a_rows, a_cols] matrix read through the A row-shift table (K = a_taps * a_cols)
+  if (a_cols > 0 && (a_mn || a_cols % 64 || a_taps < 1 || a_taps > 9 || K != a_taps * a_cols || a_shift == nullptr || a_rows < 1)) return FT_ERR_ARG;
+  if (!a_mn) r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)(a_cols > 0 ? a_cols : K), (uint64_t)(a_cols > 0 ? a_rows : M), (uint64_t)lda * 2, BK, BM,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
   else       r = ft_make_tmap_2d(&tA, A, 2, in_bf16, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   if (!b_mn) r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
-  else       r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)(b_cols > 0 ? b_cols : N), (uint64_t)K, (uint64_t)ldb * 2, 64, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else       r = ft_make_tmap_2d(&tB, B, 2, in_bf16, (uint64_t)(b_cols > 0 ? b_cols : N), (uint64_t)(b_rows > 0 ? b_rows : K), (uint64_t)ldb * 2, 64, BK,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
   const uint64_t eb = out_f32 ? 4 : 2;
   r = ft_make_tmap_3d(&tD, D, (int)eb, !out_f32 && in_bf16, (uint64_t)N, (uint64_t)M, (uint64_t)k_splits, (uint64_t)ldd * eb, (uint64_t)M * ldd * eb,
@@ -507,10 +527,14 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
 
   const int sms = g_num_sms[dev];
   TailArgs tail = plan_tail(dev, ((M + BM - 1) / BM) * ((N + BN - 1) / BN), (K + BK - 1) / BK, k_splits, sms, stream);
+  if (a_cols > 0) {
+    tail.a_atoms_per_tap = a_cols / 64;
+    for (int t = 0; t < 9; t++) tail.a_shift[t] = t < a_taps ? a_shift[t] : 0;
+  }
   if (b_atoms_per_tap > 0) {
-    if (!b_mn || b_cols != b_atoms_per_tap * 64 || N != 9 * b_cols || b_row_pitch < 3) return FT_ERR_ARG;
+    if (!b_mn || b_cols != b_atoms_per_tap * 64 || N != 9 * b_cols || b_shift == nullptr) return FT_ERR_ARG;
     tail.b_atoms_per_tap = b_atoms_per_tap;
-    tail.b_row_pitch = b_row_pitch;
+    for (int t = 0; t < 9; t++) tail.b_shift[t] = b_shift[t];
   }
 #define FT_GEMM_CASE(AM, BMN, OF) \
   if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, sms, stream, epi, tail);
@@ -558,7 +582,34 @@ FT_EXPORT int ft_gemm_bf16_splitk(const void* A, const void* B, float* partial, 
 // planes: f32 [k_splits][Cout][9 * Cin]; the caller sums them (ft_splitk_reduce). Cin must be a multiple of 64, Cout of 8.
 FT_EXPORT int ft_conv3x3_wgrad_splitk(const void* dyp, const void* xp, float* planes, int Cout, int Cin, int64_t J, int row_pitch, int k_splits,
                                       cudaStream_t stream) {
-  if (Cin <= 0 || Cin % 64 || Cout <= 0 || Cout % 8 || J <= 0 || J > 0x7fffffffll) return FT_ERR_ARG;
+  if (Cin <= 0 || Cin % 64 || Cout <= 0 || Cout % 8 || J <= 0 || J > 0x7fffffffll || row_pitch < 3) return FT_ERR_ARG;
+  int shift[9];
+  for (int t = 0; t < 9; t++) shift[t] = (t / 3 - 1) * row_pitch + (t % 3 - 1);
   return gemm_impl(dyp, xp, planes, nullptr, Cout, 9 * Cin, (int)J, Cout, Cin, 9 * (int64_t)Cin, 1, 1, 1, k_splits, stream, EpiArgs{0, nullptr, 0, 0}, Cin, Cin / 64,
-                   row_pitch);
+                   shift);
+}
+
+// General form: dW[co][t][ci] = sum_{j < J} A[j][co] * B[j + shift[t]][ci] for nine caller-given row shifts (host array of 9 ints); B has b_rows
+// rows and reads as zeros outside them. With the input stored as stacked planes (for a stride-2 convolution: the four pixel-parity planes of
+// the padded input, one below the other), a tap's plane and its offset inside the plane are both just rows, so the same launch covers strided
+// convolutions.
+FT_EXPORT int ft_conv_wgrad_shift_splitk(const void* a, const void* b, float* planes, int Cout, int Cin, int64_t J, int64_t b_rows, const int* shift9,
+                                         int k_splits, cudaStream_t stream) {
+  if (Cin <= 0 || Cin % 64 || Cout <= 0 || Cout % 8 || J <= 0 || J > 0x7fffffffll || b_rows <= 0 || b_rows > 0x7fffffffll || shift9 == nullptr) return FT_ERR_ARG;
+  return gemm_impl(a, b, planes, nullptr, Cout, 9 * Cin, (int)J, Cout, Cin, 9 * (int64_t)Cin, 1, 1, 1, k_splits, stream, EpiArgs{0, nullptr, 0, 0}, Cin, Cin / 64,
+                   shift9, 0, 0, 0, nullptr, b_rows);
+}
+
+// Convolution as one GEMM over pixel rows: Y[j][co] = act(sum_t sum_ci X[j + shift[t]][ci] * W[co][t][ci] + bias[co]) for `taps` <= 9 filter
+// taps. x: bf16 [x_rows, Cin] (pixel rows of a zero-padded activation, or stacked parity planes of one for a strided convolution), w: bf16
+// [Cout, taps * Cin], y: bf16 [rows, Cout], bias: bf16 [Cout] or null, shift: host array of `taps` row offsets, act as in ft_gemm_ex.
+// Rows j + shift[t] outside x read as zeros. Cin must be a multiple of 64, Cout of 8. The caller crops the rows of y that belong to halo
+// positions of the padded grid.
+FT_EXPORT int ft_conv_rows_gemm(const void* x, const void* w, void* y, const void* bias, int64_t rows, int64_t x_rows, int Cin, int Cout, int taps,
+                                const int* shift, int act, cudaStream_t stream) {
+  if (Cin <= 0 || Cin % 64 || Cout <= 0 || Cout % 8 || rows <= 0 || rows > 0x7fffffffll || x_rows <= 0 || x_rows > 0x7fffffffll || taps < 1 || taps > 9 ||
+      shift == nullptr)
+    return FT_ERR_ARG;
+  return gemm_impl(x, w, y, bias, (int)rows, Cout, taps * Cin, Cin, (int64_t)taps * Cin, Cout, 0, 0, 0, 1, stream, EpiArgs{act, nullptr, 0, 0}, 0, 0, nullptr, Cin,
+                   x_rows, taps, shift);
 }

@@ -19,6 +19,8 @@ from ..errors import InvalidArgument
 _FORCE_LIBRARY = os.environ.get("FT_CONV_BACKEND", "") == "cudnn"
 # weight gradients: "" = library routine, "gemm" = nine shifted launches of the GEMM, "fused" = one launch with the GEMM's row-shift table
 _WGRAD_MODE = os.environ.get("FT_CONV_WGRAD", "")
+# FT_CONV_ROWS=1: strided (and plain) 3x3 convolutions as row GEMMs with the GEMM's row-shift tables, forward and both gradients
+_ROWS_MODE = os.environ.get("FT_CONV_ROWS", "") == "1"
 
 
 def conv3x3_wgrad_gemm(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
@@ -60,27 +62,173 @@ def _wgrad_splits(Cout: int, Cin: int, J: int) -> int:
     return splits
 
 
-def conv3x3_wgrad_fused(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
+def _wgrad_rows(a_rows: torch.Tensor, b_rows: torch.Tensor, shifts) -> torch.Tensor:
+    """``dW[co, t, ci] = sum_j A[j, co] * B[j + shifts[t], ci]`` over the rows of ``A`` (rows of ``B`` outside the matrix count as zeros), for
+    nine shifts. ``a_rows``: bf16 ``[J, Cout]``, ``b_rows``: bf16 ``[R, Cin]``. CUDA: one split-K launch of the tcgen05 GEMM with its B row-shift
+    table and a fixed-order plane sum; host: the same nine products. Returns f32 ``[Cout, 9, Cin]``."""
+    J, Co = a_rows.shape
+    R, C = b_rows.shape
+    if a_rows.is_cuda:
+        from .gemm import _plane_cache
+        splits = _wgrad_splits(Co, C, J)
+        n_out = Co * 9 * C
+        planes = _plane_cache(a_rows.device, splits * n_out)[: splits * n_out]
+        out = torch.empty((Co, 9, C), device=a_rows.device, dtype=torch.float32)
+        arr = (ctypes.c_int * 9)(*[int(v) for v in shifts])
+        with torch.cuda.device(a_rows.device):
+            _lib.call("ft_conv_wgrad_shift_splitk", a_rows, b_rows, planes, Co, C, J, R, arr, splits, _lib.S())
+            _lib.call("ft_splitk_reduce", planes, splits, Co, 9 * C, ctypes.c_int64(9 * C), ctypes.c_int64(n_out), None, out,
+                      ctypes.c_int64(9 * C), 1, _lib.S())
+        return out
+    out = torch.zeros(Co, 9, C)
+    af, bf = a_rows.float(), b_rows.float()
+    for t, sh in enumerate(shifts):
+        lo, hi = max(0, -sh), min(J, R - sh)
+        if hi > lo:
+            out[:, t, :] = af[lo:hi].t() @ bf[lo + sh: hi + sh]
+    return out
+
+
+def conv3x3_wgrad_fused(x: torch.Tensor, dy: torch.Tensor, stride: int = 1) -> torch.Tensor:
     """The nine shifted products of :func:`conv3x3_wgrad_gemm` as one split-K launch of the tcgen05 GEMM: its N axis is ``[tap][Cin]`` and the
-    producer warp fetches the B atoms of tap ``(r, s)`` from rows ``k + (r-1)(W+2) + (s-1)`` of the padded input (zero fill outside), so the
-    output ``[Cout, 9 Cin]`` is the gradient in ``[Cout, 3, 3, Cin]`` order. Needs ``Cin % 64 == 0`` and ``Cout % 8 == 0``; CUDA only."""
-    from .gemm import _plane_cache
+    producer warp fetches the B atoms of tap ``(r, s)`` from shifted rows of the padded input (zero fill outside), so the output
+    ``[Cout, 9 Cin]`` is the gradient in ``[Cout, 3, 3, Cin]`` order. Stride 1: rows of the padded input, shift ``(r-1)(W+2) + (s-1)``, output
+    gradient zero-padded to the same grid. Stride 2 (even H, W): the four pixel-parity planes of the padded input stacked below one another,
+    shift = plane ``(r % 2, s % 2)`` + offset ``(r // 2, s // 2)``, output gradient placed on the planes' grid (zero last row and column).
+    Needs ``Cin % 64 == 0`` and ``Cout % 8 == 0``. ``x``: ``[N, Cin, H, W]``, ``dy``: ``[N, Cout, H / stride, W / stride]``, channels-last bf16."""
     N, C, H, W = x.shape
     Co = dy.shape[1]
-    if dy.shape != (N, Co, H, W) or C % 64 or Co % 8 or not x.is_cuda or x.dtype != torch.bfloat16 or dy.dtype != torch.bfloat16:
-        raise InvalidArgument("conv3x3_wgrad_fused needs CUDA bf16 [N, C, H, W] tensors with Cin % 64 == 0 and Cout % 8 == 0")
-    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, C)
-    dyp = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, Co)
-    J = xp.shape[0]
-    splits = _wgrad_splits(Co, C, J)
-    n_out = Co * 9 * C
-    planes = _plane_cache(x.device, splits * n_out)[: splits * n_out]
-    out = torch.empty((Co, 3, 3, C), device=x.device, dtype=torch.float32)
-    with torch.cuda.device(x.device):
-        _lib.call("ft_conv3x3_wgrad_splitk", dyp, xp, planes, Co, C, J, W + 2, splits, _lib.S())
-        _lib.call("ft_splitk_reduce", planes, splits, Co, 9 * C, ctypes.c_int64(9 * C), ctypes.c_int64(n_out), None, out,
-                  ctypes.c_int64(9 * C), 1, _lib.S())
-    return out
+    if dy.shape != (N, Co, H // stride, W // stride) or C % 64 or Co % 8 or x.dtype != torch.bfloat16 or dy.dtype != torch.bfloat16 or stride not in (1, 2):
+        raise InvalidArgument("conv3x3_wgrad_fused needs bf16 [N, C, H, W] / [N, Cout, H/stride, W/stride] tensors with Cin % 64 == 0 and Cout % 8 == 0")
+    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1))
+    if stride == 1:
+        dyp = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1)).contiguous().view(-1, Co)
+        shifts = [(r - 1) * (W + 2) + (s - 1) for r in range(3) for s in range(3)]
+        return _wgrad_rows(dyp, xp.contiguous().view(-1, C), shifts).view(Co, 3, 3, C)
+    if H % 2 or W % 2:
+        raise InvalidArgument("stride 2 needs even H and W")
+    Hh, Wh = (H + 2) // 2, (W + 2) // 2
+    rows = N * Hh * Wh
+    planes = torch.stack([xp[:, pr::2, ps::2] for pr in range(2) for ps in range(2)]).contiguous().view(4 * rows, C)
+    dyg = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 0, 1, 0, 1)).contiguous().view(rows, Co)           # zero last row / column
+    shifts = [((r % 2) * 2 + (s % 2)) * rows + (r // 2) * Wh + (s // 2) for r in range(3) for s in range(3)]
+    return _wgrad_rows(dyg, planes, shifts).view(Co, 3, 3, C)
+
+
+def _rows_gemm(x_rows: torch.Tensor, w: torch.Tensor, rows: int, shifts, bias=None, relu: bool = False) -> torch.Tensor:
+    """``Y[j] = act(sum_t X[j + shifts[t]] @ W[:, t, :]^T + bias)`` for ``j < rows``; ``X`` rows outside the matrix count as zeros.
+    ``x_rows``: bf16 ``[R, Cin]``, ``w``: bf16 ``[Cout, taps, Cin]``. CUDA: one launch of the tcgen05 GEMM with its A row-shift table; host: the same sum."""
+    R, Cin = x_rows.shape
+    Cout, taps = w.shape[0], w.shape[1]
+    if x_rows.is_cuda:
+        y = torch.empty((rows, Cout), device=x_rows.device, dtype=torch.bfloat16)
+        arr = (ctypes.c_int * taps)(*[int(v) for v in shifts])
+        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        with torch.cuda.device(x_rows.device):
+            _lib.call("ft_conv_rows_gemm", x_rows, w.contiguous(), y, b, rows, R, Cin, Cout, taps, arr, 1 if relu else 0, _lib.S())
+        return y
+    acc = torch.zeros(rows, Cout)
+    xf, wf = x_rows.float(), w.float()
+    for t, sh in enumerate(shifts):
+        lo, hi = max(0, -sh), min(rows, R - sh)
+        if hi > lo:
+            acc[lo:hi] += xf[lo + sh: hi + sh] @ wf[:, t, :].t()
+    if bias is not None:
+        acc += bias.float()
+    if relu:
+        acc = torch.relu(acc)
+    return acc.to(torch.bfloat16)
+
+
+def conv3x3_rows(x: torch.Tensor, w_krsc: torch.Tensor, stride: int = 1, bias=None, relu: bool = False) -> torch.Tensor:
+    """3x3 / padding 1 convolution with stride 1 or 2 as ONE GEMM over pixel rows of the zero-padded activation.
+
+    Stride 1: with the padded activation flattened to rows ``Xp [N (H+2) (W+2), Cin]``, the input of filter tap ``(r, s)`` for the output at
+    padded position ``j`` is row ``j + (r-1)(W+2) + (s-1)``: a constant shift per tap, which the GEMM's producer warp applies to its A loads
+    (K axis = ``[tap][Cin]``, weights ``[Cout, 3, 3, Cin]`` as they are). Stride 2 (even H, W): the padded activation is first split into
+    its four pixel-parity planes stacked below one another; tap ``(r, s)`` then reads plane ``(r % 2, s % 2)`` at offset ``(r // 2, s // 2)``,
+    again a constant row shift. The result is computed on the padded grid and cropped. ``x``: channels-last bf16 ``[N, Cin, H, W]`` with
+    ``Cin % 64 == 0``; returns channels-last bf16 ``[N, Cout, H / stride, W / stride]``.
+    (Reference: ferrotorch-gpu/src/conv.rs:218-504 materialises the im2col matrix and calls SGEMM.)"""
+    N, C, H, W = x.shape
+    Co = w_krsc.shape[0]
+    if w_krsc.shape != (Co, 3, 3, C) or x.dtype != torch.bfloat16 or C % 64 or Co % 8 or stride not in (1, 2):
+        raise InvalidArgument("conv3x3_rows needs a bf16 [N, C, H, W] input with C % 64 == 0, [Cout, 3, 3, C] weights and stride 1 or 2")
+    xp = torch.nn.functional.pad(x.permute(0, 2, 3, 1), (0, 0, 1, 1, 1, 1))                    # [N, H+2, W+2, C]
+    w3 = w_krsc.reshape(Co, 9, C)
+    if stride == 1:
+        Wp = W + 2
+        rows = N * (H + 2) * Wp
+        shifts = [(r - 1) * Wp + (s - 1) for r in range(3) for s in range(3)]
+        y = _rows_gemm(xp.reshape(rows, C), w3, rows, shifts, bias, relu).view(N, H + 2, Wp, Co)[:, 1: H + 1, 1: W + 1]
+    else:
+        if H % 2 or W % 2:
+            raise InvalidArgument("conv3x3_rows with stride 2 needs even H and W")
+        Hh, Wh = (H + 2) // 2, (W + 2) // 2
+        planes = torch.stack([xp[:, pr::2, ps::2] for pr in range(2) for ps in range(2)]).contiguous()          # [4, N, Hh, Wh, C]
+        rows = N * Hh * Wh
+        shifts = [((r % 2) * 2 + (s % 2)) * rows + (r // 2) * Wh + (s // 2) for r in range(3) for s in range(3)]
+        y = _rows_gemm(planes.view(4 * rows, C), w3, rows, shifts, bias, relu).view(N, Hh, Wh, Co)[:, : Hh - 1, : Wh - 1]
+    return y.permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+
+
+def conv3x3_dgrad_rows(dy: torch.Tensor, w_krsc: torch.Tensor, stride: int, H: int, W: int) -> torch.Tensor:
+    """Input gradient of :func:`conv3x3_rows`. Stride 1: the same row GEMM on ``dy`` with the filter flipped and its channel axes swapped.
+    Stride 2: one row GEMM per pixel-parity plane of the padded input: plane ``(pr, ps)`` only receives the taps with ``r = pr``, ``s = ps``
+    (mod 2), each reading the output gradient (laid on the planes' grid with a zero last row and column) at offset ``-(r // 2, s // 2)``;
+    the four planes are interleaved back and the padding is cropped. ``dy``: channels-last bf16 ``[N, Cout, H/stride, W/stride]`` with
+    ``Cout % 64 == 0``; returns channels-last bf16 ``[N, Cin, H, W]``."""
+    N, Co = dy.shape[0], dy.shape[1]
+    C = w_krsc.shape[3]
+    if stride == 1:
+        return conv3x3_rows(dy, w_krsc.flip(1, 2).permute(3, 1, 2, 0).contiguous(), 1)
+    Hh, Wh = (H + 2) // 2, (W + 2) // 2
+    rows = N * Hh * Wh
+    dyg = torch.nn.functional.pad(dy.permute(0, 2, 3, 1), (0, 0, 0, 1, 0, 1)).contiguous().view(rows, Co)
+    dxp = torch.empty((N, H + 2, W + 2, C), device=dy.device, dtype=torch.bfloat16)
+    for pr in range(2):
+        for ps in range(2):
+            taps = [(r, s) for r in range(3) for s in range(3) if r % 2 == pr and s % 2 == ps]
+            wt = torch.stack([w_krsc[:, r, s, :].t() for r, s in taps], 1).contiguous()                       # [Cin, taps, Cout]
+            shifts = [-((r // 2) * Wh + (s // 2)) for r, s in taps]
+            dxp[:, pr::2, ps::2] = _rows_gemm(dyg, wt, rows, shifts).view(N, Hh, Wh, C)
+    return dxp[:, 1: H + 1, 1: W + 1].permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+
+
+class _Conv3x3RowsFn(torch.autograd.Function):
+    """3x3 / padding 1 convolution with stride 1 or 2 whose forward, input gradient and weight gradient all run on the tcgen05 GEMM through
+    its row-shift tables (no library convolution anywhere)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, stride):
+        wk = _krsc(weight)
+        ctx.save_for_backward(x, wk)
+        ctx.stride, ctx.wdtype = stride, weight.dtype
+        return conv3x3_rows(x, wk, stride)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wk = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = conv3x3_dgrad_rows(dy, wk, ctx.stride, x.shape[2], x.shape[3])
+        if ctx.needs_input_grad[1]:
+            dw = conv3x3_wgrad_fused(x, dy, ctx.stride).permute(0, 3, 1, 2).to(ctx.wdtype)
+        return dx, dw, None
+
+
+def conv3x3_rows_eligible(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, groups) -> bool:
+    as2 = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)          # noqa: E731
+    st = as2(stride)
+    return (_ROWS_MODE and x.dim() == 4 and x.dtype == torch.bfloat16 and weight.shape[-2:] == (3, 3) and st in ((1, 1), (2, 2)) and as2(padding) == (1, 1)
+            and as2(dilation) == (1, 1) and groups == 1 and x.shape[1] % 64 == 0 and weight.shape[0] % 64 == 0
+            and (st == (1, 1) or (x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0)) and x.is_contiguous(memory_format=torch.channels_last))
+
+
+def conv3x3_autograd_rows(x: torch.Tensor, weight: torch.Tensor, stride: int = 1) -> torch.Tensor:
+    """Differentiable form of :func:`conv3x3_rows` (``weight``: ``[Cout, Cin, 3, 3]``, Cin and Cout multiples of 64)."""
+    return _Conv3x3RowsFn.apply(x, weight, stride)
 
 
 def _weight_grad(x: torch.Tensor, dy: torch.Tensor, wshape) -> torch.Tensor:

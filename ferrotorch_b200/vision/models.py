@@ -90,6 +90,8 @@ class Conv3x3(nn.Conv2d):
     def forward(self, x):
         if x.is_cuda and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16 and x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
+        if ops.conv.conv3x3_rows_eligible(x, self.weight, self.stride, self.padding, self.dilation, self.groups):
+            return ops.conv.conv3x3_autograd_rows(x, self.weight, self.stride[0])          # opt-in: every pass on the GEMM's row-shift tables
         if ops.conv.conv3x3_eligible(x, self.weight, self.stride, self.padding, self.dilation, self.groups):
             wc = compute_copy(self.weight) if self.weight.dtype == torch.float32 else None
             if wc is not None and wc.dtype == torch.bfloat16:

@@ -167,3 +167,47 @@ def test_row_shift_table_of_the_fused_weight_gradient_gemm():
         s = _wgrad_splits(co, ci, j)
         nkb = -(-j // 64)
         assert 1 <= s <= 64 and (s == 1 or -(-nkb // s) * (s - 1) < nkb)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+@pytest.mark.parametrize("N,C,Co,H,W", [(2, 64, 16, 6, 8), (1, 128, 8, 4, 4), (3, 64, 24, 2, 10)])
+def test_conv3x3_as_one_row_gemm(N, C, Co, H, W, stride):
+    """Stride 1 and stride 2 convolutions as a sum of row-shifted products on the padded (for stride 2: parity-split) activation."""
+    torch.manual_seed(N * 7 + H + stride)
+    x = torch.randn(N, C, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(Co, C, 3, 3) * 0.1).bfloat16()
+    bias = torch.randn(Co).bfloat16()
+    y = ops.conv.conv3x3_rows(x, w.permute(0, 2, 3, 1).contiguous(), stride=stride, bias=bias, relu=True)
+    ref = torch.relu(torch.nn.functional.conv2d(x.float(), w.float(), bias.float(), stride=stride, padding=1))
+    assert y.shape == ref.shape and y.is_contiguous(memory_format=torch.channels_last)
+    assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_conv3x3_weight_gradient_by_row_shifts_both_strides(stride):
+    torch.manual_seed(20 + stride)
+    N, C, Co, H, W = 2, 64, 16, 6, 8
+    x = torch.randn(N, C, H, W).bfloat16().contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(N, Co, H // stride, W // stride).bfloat16().contiguous(memory_format=torch.channels_last)
+    got = ops.conv.conv3x3_wgrad_fused(x, dy, stride=stride)
+    ref = torch.nn.grad.conv2d_weight(x.float(), (Co, C, 3, 3), dy.float(), stride=stride, padding=1).permute(0, 2, 3, 1)
+    assert got.shape == (Co, 3, 3, C) and torch.allclose(got, ref, rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_conv3x3_rows_autograd_matches_reference(stride):
+    """Forward, input gradient (stride 2: one product per pixel-parity plane) and weight gradient of the row-GEMM convolution."""
+    torch.manual_seed(30 + stride)
+    N, C, Co, H, W = 2, 64, 64, 6, 8
+    x = (torch.randn(N, C, H, W) * 0.5).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (torch.randn(Co, C, 3, 3) * 0.05).requires_grad_(True)
+    y = ops.conv.conv3x3_autograd_rows(x, w, stride)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x.detach().float().requires_grad_(True)
+    w2 = w.detach().bfloat16().float().requires_grad_(True)
+    y2 = torch.nn.functional.conv2d(x2, w2, stride=stride, padding=1)
+    y2.backward(g.float())
+    assert torch.allclose(y.float(), y2, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(x.grad.float(), x2.grad, rtol=3e-2, atol=3e-2)
+    assert w.grad.dtype == torch.float32 and torch.allclose(w.grad, w2.grad, rtol=2e-2, atol=2e-2)

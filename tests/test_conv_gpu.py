@@ -73,3 +73,24 @@ def test_conv3x3_weight_gradient_fused_gemm_on_device(N, C, Co, H, W):
     assert (got - ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 1e-2
     assert torch.equal(got, ops.conv.conv3x3_wgrad_fused(x, dy))            # planes summed in a fixed order
     assert _lib.read_status() == 0
+
+
+@pytest.mark.skipif(__import__("os").environ.get("FT_STAGED") != "1", reason="row-GEMM convolution is opt-in until run on hardware (FT_STAGED=1)")
+@pytest.mark.parametrize("stride", [1, 2])
+@pytest.mark.parametrize("N,C,Co,H,W", [(4, 64, 64, 56, 56), (8, 128, 256, 14, 14), (2, 256, 128, 6, 10)])
+def test_conv3x3_rows_forward_and_gradients_on_device(N, C, Co, H, W, stride):
+    from ferrotorch_b200 import _lib, ops
+    torch.manual_seed(C + W + stride)
+    x = (torch.randn(N, C, H, W, device="cuda") * 0.5).bfloat16().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w = (torch.randn(Co, C, 3, 3, device="cuda") * 0.05).requires_grad_(True)
+    y = ops.conv.conv3x3_autograd_rows(x, w, stride)
+    g = torch.randn_like(y)
+    y.backward(g)
+    x2 = x.detach().float().requires_grad_(True)
+    w2 = w.detach().bfloat16().float().requires_grad_(True)
+    y2 = F.conv2d(x2, w2, stride=stride, padding=1)
+    y2.backward(g.float())
+    for got, ref, what in ((y, y2, "y"), (x.grad, x2.grad, "dx"), (w.grad, w2.grad, "dw")):
+        err, scale = (got.float() - ref).abs().max().item(), ref.abs().max().item()
+        assert err <= 2e-2 * scale + 2e-2, (what, err, scale)
+    assert _lib.read_status() == 0
