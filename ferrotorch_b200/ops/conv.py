@@ -19,8 +19,9 @@ from ..errors import InvalidArgument
 _FORCE_LIBRARY = os.environ.get("FT_CONV_BACKEND", "") == "cudnn"
 # weight gradients: "" = library routine, "gemm" = nine shifted launches of the GEMM, "fused" = one launch with the GEMM's row-shift table
 _WGRAD_MODE = os.environ.get("FT_CONV_WGRAD", "")
-# FT_CONV_ROWS=1: strided (and plain) 3x3 convolutions as row GEMMs with the GEMM's row-shift tables, forward and both gradients
-_ROWS_MODE = os.environ.get("FT_CONV_ROWS", "") == "1"
+# FT_CONV_ROWS: 3x3 convolutions as row GEMMs with the GEMM's row-shift tables, forward and both gradients: "1" = the stride-2 ones (which
+# otherwise go to the library), "all" = stride 1 too (instead of the dedicated implicit-GEMM kernel)
+_ROWS_MODE = os.environ.get("FT_CONV_ROWS", "")
 
 
 def conv3x3_wgrad_gemm(x: torch.Tensor, dy: torch.Tensor) -> torch.Tensor:
@@ -221,7 +222,9 @@ class _Conv3x3RowsFn(torch.autograd.Function):
 def conv3x3_rows_eligible(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, groups) -> bool:
     as2 = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)          # noqa: E731
     st = as2(stride)
-    return (_ROWS_MODE and x.dim() == 4 and x.dtype == torch.bfloat16 and weight.shape[-2:] == (3, 3) and st in ((1, 1), (2, 2)) and as2(padding) == (1, 1)
+    if not (_ROWS_MODE == "all" or (_ROWS_MODE == "1" and st == (2, 2))):
+        return False
+    return (x.dim() == 4 and x.dtype == torch.bfloat16 and weight.shape[-2:] == (3, 3) and st in ((1, 1), (2, 2)) and as2(padding) == (1, 1)
             and as2(dilation) == (1, 1) and groups == 1 and x.shape[1] % 64 == 0 and weight.shape[0] % 64 == 0
             and (st == (1, 1) or (x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0)) and x.is_contiguous(memory_format=torch.channels_last))
 
