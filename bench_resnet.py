@@ -7,7 +7,8 @@
 bf16 autocast with f32 master weights, 224x224x3 synthetic images ~N(0,1), batch 256 per GPU, labels uniform in [0,1000),
 SGD lr 0.1 momentum 0.9 weight decay 1e-4 (fused flat kernel). Gradients are all-reduced in 25 MiB buckets by the peer-memory
 all-reduce kernel, overlapped with backward. 1x1 convolutions run on the tcgen05 GEMM (channels-last, split-K weight gradients), batch norm
-(+ residual + ReLU) and max pooling on the channels-last kernels; 3x3/7x7 convolutions go through cuDNN (reported in `config.library_ops`).
+(+ residual + ReLU) and max pooling on the channels-last kernels, stride-1 3x3 convolutions (forward, input gradient) on the implicit-GEMM
+kernel; what still goes through a library is listed in `config.library_ops` (it shrinks with FT_CONV_WGRAD / FT_CONV_ROWS).
 """
 from __future__ import annotations
 
@@ -89,6 +90,12 @@ def main():
         return ms, _lib.launch_calls - l0, last
     ms, launches, last = timed(False)
     ms2, _, last2 = timed(True)
+    from ferrotorch_b200.ops import conv as _conv
+    library_ops = ["conv 7x7 stem (cuDNN)", "global avg pool", "classifier GEMM (cuBLAS via autocast)"]
+    if _conv._ROWS_MODE not in ("1", "all"):
+        library_ops.insert(1, "conv 3x3 stride 2: forward and both gradients (cuDNN)")
+    if _conv._WGRAD_MODE not in ("gemm", "fused") and _conv._ROWS_MODE != "all":
+        library_ops.insert(1, "conv 3x3 stride 1: weight gradient (cuDNN)")
     if rank == 0:
         print(json.dumps({
             "metric": "resnet50_ddp_train_images_per_s", "value": round(a.batch * world * a.steps / (ms / 1e3), 1), "unit": "images/s",
@@ -96,7 +103,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 autocast, f32 master", "data": "synthetic (N(0,1) images, uniform labels)",
             "config": {"model": "resnet50", "global_batch": a.batch * world, "image": "224x224x3", "parallelism": f"ddp{world}",
                        "optimizer": "SGD(lr=0.1,momentum=0.9,wd=1e-4)", "bucket_mb": 25, "compute_copies": bool(a.compute_copies), "comm": ddp.comm_mode if world > 1 else "none",
-                       "library_ops": ["conv3x3/7x7 (cuDNN)", "global avg pool"], "l2": "inputs_larger_than_L2 (154 MB of images per step)"},
+                       "library_ops": library_ops, "l2": "inputs_larger_than_L2 (154 MB of images per step)"},
             "e2e": {"value": round(a.batch * world * a.steps / (ms2 / 1e3), 1), "unit": "images/s", "h2d_bytes_per_step": a.batch * (3 * 224 * 224 * 4 + 8),
                     "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches), "last_loss": float(last), "kernel_status": _lib.read_status(), "impl": "ours"}))
