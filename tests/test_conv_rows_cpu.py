@@ -96,3 +96,22 @@ def test_conv3x3_rows_autograd_matches_reference(stride):
     assert torch.allclose(y.float(), y2, rtol=2e-2, atol=2e-2)
     assert torch.allclose(x.grad.float(), x2.grad, rtol=3e-2, atol=3e-2)
     assert w.grad.dtype == torch.float32 and torch.allclose(w.grad, w2.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_row_shift_launchers_refuse_bad_arguments_before_touching_the_device():
+    """Argument checks of the new launchers run on the host (no GPU needed): misaligned channel counts, too many taps, missing tables."""
+    import ctypes
+    from ferrotorch_b200 import _lib
+    from ferrotorch_b200.errors import FerrotorchError
+    buf = torch.zeros(64 * 64, dtype=torch.bfloat16)
+    out = torch.zeros(64 * 9 * 64, dtype=torch.float32)
+    shifts = (ctypes.c_int * 9)(*range(9))
+    for args in (("ft_conv_rows_gemm", buf, buf, buf, None, 64, 64, 63, 64, 9, shifts, 0, 0),          # Cin not a multiple of 64
+                 ("ft_conv_rows_gemm", buf, buf, buf, None, 64, 64, 64, 64, 10, shifts, 0, 0),         # more than nine taps
+                 ("ft_conv_rows_gemm", buf, buf, buf, None, 64, 64, 64, 60, 9, shifts, 0, 0),          # Cout not a multiple of 8
+                 ("ft_conv_rows_gemm", buf, buf, buf, None, 64, 64, 64, 64, 9, None, 0, 0),            # no shift table
+                 ("ft_conv3x3_wgrad_splitk", buf, buf, out, 64, 96, 64, 10, 1, 0),                      # Cin not a multiple of 64
+                 ("ft_conv3x3_wgrad_splitk", buf, buf, out, 64, 64, 64, 2, 1, 0),                       # row pitch below 3
+                 ("ft_conv_wgrad_shift_splitk", buf, buf, out, 64, 64, 64, 0, shifts, 1, 0)):           # B without rows
+        with pytest.raises(FerrotorchError, match="invalid argument"):
+            _lib.call(*args)
