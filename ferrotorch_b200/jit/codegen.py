@@ -19,6 +19,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import subprocess
 import tempfile
 import threading
@@ -377,6 +378,43 @@ static inline float ft_bf16_to_float(unsigned short h) { uint32_t u = (uint32_t)
 static inline unsigned short ft_float_to_bf16(float f) { uint32_t u; std::memcpy(&u, &f, 4); if ((u & 0x7fffffffu) > 0x7f800000u) return (unsigned short)((u >> 16) | 0x40);
   u += 0x7fffu + ((u >> 16) & 1u); return (unsigned short)(u >> 16); }
 static inline float ft_round_bf16(float f) { return ft_bf16_to_float(ft_float_to_bf16(f)); }
+// Branch-free expf / tanhf (Cephes polynomials, about 1-2 ulp) used by the dense loop: plain arithmetic and selects, so the compiler vectorises
+// the whole fused body. Infinities, NaN and exp(-inf) == 0 behave as in libm; results between 1e-45 and 1.2e-38 come out as the smallest normal.
+static inline float ft_expf(float x) {
+  const float xc = x > 88.72283935546875f ? 88.72283935546875f : (x < -87.33654022216797f ? -87.33654022216797f : x);
+  const float n = nearbyintf(xc * 1.44269504088896341f);
+  float r = fmaf(n, -0.693359375f, xc);
+  r = fmaf(n, 2.12194440e-4f, r);
+  float p = 1.9875691500e-4f;
+  p = fmaf(p, r, 1.3981999507e-3f);
+  p = fmaf(p, r, 8.3334519073e-3f);
+  p = fmaf(p, r, 4.1665795894e-2f);
+  p = fmaf(p, r, 1.6666665459e-1f);
+  p = fmaf(p, r, 5.0000001201e-1f);
+  const float e = fmaf(p, r * r, r) + 1.0f;
+  const int32_t ni = (int32_t)n;
+  // 2^n in two factors so that n = 128 (the top of the range) does not overflow the exponent field before the multiply
+  const int32_t h = ni >> 1;
+  uint32_t b0 = (uint32_t)(h + 127) << 23, b1 = (uint32_t)(ni - h + 127) << 23;
+  float s0, s1;
+  std::memcpy(&s0, &b0, 4);
+  std::memcpy(&s1, &b1, 4);
+  const float v = e * s0 * s1;
+  return x > 88.72283935546875f ? INFINITY : (x < -103.972084045410f ? 0.0f : v);
+}
+static inline float ft_tanhf(float x) {
+  const float ax = fabsf(x);
+  const float z = x * x;
+  float p = -5.70498872745e-3f;
+  p = fmaf(p, z, 2.06390887954e-2f);
+  p = fmaf(p, z, -5.37397155531e-2f);
+  p = fmaf(p, z, 1.33314422036e-1f);
+  p = fmaf(p, z, -3.33332819422e-1f);
+  const float small = fmaf(p * z, x, x);
+  const float big = 1.0f - 2.0f / (ft_expf(2.0f * ax) + 1.0f);
+  const float r = ax < 0.625f ? small : copysignf(big, x);
+  return r;
+}
 struct FtStrides { int ndim; long long shape[%d]; long long stride[%d][%d]; };
 """
 
@@ -391,6 +429,20 @@ def generate_host(body: IrGraph, name: str) -> str:
     params += ["long long n", "const FtStrides* st"]
     src = [_HOST_PRELUDE % (MAX_DIMS, max(len(ins), 1), MAX_DIMS), f'extern "C" void {name}({", ".join(params)}) {{']
     src.append("  auto body = [&](long long begin, long long end) {")
+    # st == nullptr: every input is contiguous with the output's shape - a plain indexed loop the compiler can vectorise (libmvec for the
+    # transcendental calls); otherwise the general strided / broadcasting walk below
+    src.append("  if (st == nullptr) {")
+    src.append("    for (long long i = begin; i < end; i++) {")
+    dnames = {-1: "__HOST__"}
+    for k, v in enumerate(ins):
+        src.append(f"      const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), 'i', host=True)};")
+        dnames[body.inputs[k]] = f"x{k}"
+    dlines, dvar = _body_lines(body, dnames)
+    dlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in dlines]        # the vectorisable versions of the prelude
+    src += ["      " + l for l in dlines]
+    for k, v in enumerate(outs):
+        src.append("      " + _store(v.dtype, f"out{k}", "i", dvar[body.outputs[k]], host=True))
+    src += ["    }", "    return;", "  }"]
     src.append("  for (long long i = begin; i < end; i++) {")
     src.append(f"    long long rem = i, off[{max(len(ins), 1)}] = {{}};")
     src.append("    for (int d = st->ndim - 1; d >= 0; d--) { const long long c = rem % st->shape[d]; rem /= st->shape[d];")
@@ -430,7 +482,8 @@ class HostFusedKernel:
             cpp = _cache_dir / f"{key}.cpp"
             cpp.write_text(self.source)
             tmp = _cache_dir / f"{key}.{os.getpid()}.tmp.so"
-            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-pthread", "-shared", "-fPIC", "-std=c++17", str(cpp), "-o", str(tmp)],
+            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-pthread", "-shared", "-fPIC",
+                                "-std=c++17", str(cpp), "-o", str(tmp)],
                                capture_output=True, text=True)
             if r.returncode != 0:
                 raise FerrotorchError("host codegen compilation failed:\n" + r.stderr + "\n--- source ---\n" + self.source)
@@ -444,6 +497,9 @@ class HostFusedKernel:
         outs = [torch.empty(self.shape, dtype=dtype_of(body.values[o].dtype)) for o in body.outputs]
         n = outs[0].numel()
         if n == 0:
+            return outs
+        if all(tuple(t.shape) == self.shape and t.is_contiguous() for t in inputs):
+            self.fn(*([ctypes.c_void_p(t.data_ptr()) for t in inputs] + [ctypes.c_void_p(t.data_ptr()) for t in outs] + [ctypes.c_longlong(n), None]))
             return outs
         nd = max(len(self.shape), 1)
         nin = max(len(inputs), 1)
@@ -614,7 +670,8 @@ class HostFusedReduceKernel(_FusedReduceBase):
             cpp = _cache_dir / f"{key}.cpp"
             cpp.write_text(self.source)
             tmp = _cache_dir / f"{key}.{os.getpid()}.tmp.so"
-            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-pthread", "-shared", "-fPIC", "-std=c++17", str(cpp), "-o", str(tmp)],
+            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-pthread", "-shared", "-fPIC",
+                                "-std=c++17", str(cpp), "-o", str(tmp)],
                                capture_output=True, text=True)
             if r.returncode != 0:
                 raise FerrotorchError("host codegen compilation failed:\n" + r.stderr + "\n--- source ---\n" + self.source)

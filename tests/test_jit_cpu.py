@@ -167,3 +167,18 @@ def test_fused_elementwise_plus_row_reduction():
     n = next(n for n in g.nodes.values() if n.op == "fused_reduce")
     img = jit.compile_cuda(jit.generate_cuda_reduce(n.attrs["body"], "k", "sum", n.attrs["red_index"]))
     assert img[:4] == b"\x7fELF"
+
+
+def test_host_dense_loop_special_values_and_accuracy():
+    """The dense host loop uses its own vectorisable expf / tanhf: infinities, NaN, exp(-inf) == 0 and accuracy against eager execution."""
+    import torch
+    from ferrotorch_b200 import jit
+    x = torch.cat([torch.linspace(-110, 95, 200001), torch.tensor([float("inf"), -float("inf"), float("nan"), 0.0, -0.0, 88.7228, 88.723, -87.3,
+                                                                    -103.9, -104.1, 1e-30, -1e-30]), torch.randn(70000) * 3]).contiguous()
+    for f, tol in ((lambda a: torch.exp(a) * 0.5 + 0.25, 3e-7), (lambda a: torch.tanh(a) * 0.5 + 0.25, 2e-7), (lambda a: torch.sigmoid(a) * 0.5 + 0.25, 3e-7)):
+        cf = jit.compile(f, example_inputs=[x], backend="auto")
+        got, ref = cf(x), f(x)
+        assert cf.stats.fused_kernels == 1
+        assert torch.equal(torch.isnan(got), torch.isnan(ref)) and torch.equal(torch.isinf(got), torch.isinf(ref))
+        fin = torch.isfinite(ref)
+        assert ((got[fin] - ref[fin]).abs() <= tol * ref[fin].abs() + 1e-7).all()
