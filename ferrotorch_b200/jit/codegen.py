@@ -443,20 +443,53 @@ def generate_host(body: IrGraph, name: str) -> str:
     for k, v in enumerate(outs):
         src.append("      " + _store(v.dtype, f"out{k}", "i", dvar[body.outputs[k]], host=True))
     src += ["    }", "    return;", "  }"]
-    src.append("  for (long long i = begin; i < end; i++) {")
-    src.append(f"    long long rem = i, off[{max(len(ins), 1)}] = {{}};")
-    src.append("    for (int d = st->ndim - 1; d >= 0; d--) { const long long c = rem % st->shape[d]; rem /= st->shape[d];")
+    # general case: walk the last dimension row by row. The offsets of the leading dimensions are computed once per row; inputs whose last
+    # dimension is broadcast (statically known from the traced shapes) are loaded once per row, the others are expected to have unit stride
+    # there (checked at run time), which leaves a vectorisable inner loop; anything else takes the strided inner loop.
+    nin = max(len(ins), 1)
+    out_last = outs[0].shape[-1] if len(outs[0].shape) else 1
+    full = [len(v.shape) > 0 and v.shape[-1] == out_last and out_last > 1 for v in ins]
+    src.append("  const int nd = st->ndim;")
+    src.append("  const long long cols = st->shape[nd - 1];")
+    cond = " && ".join([f"st->stride[{k}][nd - 1] == {1 if full[k] else 0}" for k in range(len(ins))]) or "true"
+    src.append(f"  const bool rowfast = {cond};")
+    src.append("  long long i = begin;")
+    src.append("  while (i < end) {")
+    src.append("    const long long row = i / cols, c0 = i % cols, c1 = std::min(cols, c0 + (end - i));")
+    src.append(f"    long long rem = row, base[{nin}] = {{}};")
+    src.append("    for (int d = nd - 2; d >= 0; d--) { const long long c = rem % st->shape[d]; rem /= st->shape[d];")
     for k in range(len(ins)):
-        src.append(f"      off[{k}] += c * st->stride[{k}][d];")
+        src.append(f"      base[{k}] += c * st->stride[{k}][d];")
     src.append("    }")
+    src.append("    const long long o = row * cols;")
+    src.append("    if (rowfast) {")
+    rnames = {-1: "__HOST__"}
+    for k, v in enumerate(ins):
+        if full[k]:
+            src.append(f"      const {_HOST_CTYPE[v.dtype]}* __restrict__ p{k} = in{k} + base[{k}];")
+        else:
+            src.append(f"      const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'base[{k}]', host=True)};")
+        rnames[body.inputs[k]] = f"x{k}"
+    src.append("      for (long long col = c0; col < c1; col++) {")
+    for k, v in enumerate(ins):
+        if full[k]:
+            src.append(f"        const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'p' + str(k), 'col', host=True)};")
+    rlines, rvar = _body_lines(body, rnames)
+    rlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in rlines]
+    src += ["        " + l for l in rlines]
+    for k, v in enumerate(outs):
+        src.append("        " + _store(v.dtype, f"out{k}", "o + col", rvar[body.outputs[k]], host=True))
+    src += ["      }", "    } else {"]
+    src.append("      for (long long col = c0; col < c1; col++) {")
     names = {-1: "__HOST__"}
     for k, v in enumerate(ins):
-        src.append(f"    const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'off[{k}]', host=True)};")
+        src.append(f"        const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'base[{k}] + col * st->stride[{k}][nd - 1]', host=True)};")
         names[body.inputs[k]] = f"x{k}"
     lines, var = _body_lines(body, names)
-    src += ["    " + l for l in lines]
+    src += ["        " + l for l in lines]
     for k, v in enumerate(outs):
-        src.append("    " + _store(v.dtype, f"out{k}", "i", var[body.outputs[k]], host=True))
+        src.append("        " + _store(v.dtype, f"out{k}", "o + col", var[body.outputs[k]], host=True))
+    src += ["      }", "    }", "    i += c1 - c0;"]
     src += ["  }", "  };"]
     src.append("  const long long grain = 1 << 16;")
     src.append("  long long nt = std::min<long long>((n + grain - 1) / grain, (long long)std::max(1u, std::thread::hardware_concurrency()));")
