@@ -367,6 +367,8 @@ class CudaFusedKernel:
 # ----------------------------------------------------------------------------------------------------------------------
 # host C++
 # ----------------------------------------------------------------------------------------------------------------------
+_HOST_FLAGS_TAG = "// g++ -O3 -march=native -fno-math-errno -fno-trapping-math -fopenmp-simd\n"      # part of the cache key of compiled host kernels
+
 _HOST_PRELUDE = r"""
 #include <cmath>
 #include <cstdint>
@@ -508,14 +510,14 @@ class HostFusedKernel:
         self.shape = tuple(body.values[body.outputs[0]].shape)
         self.name = f"ft_fused_{self.fp}_h"
         self.source = generate_host(body, self.name)
-        key = hashlib.sha256(self.source.encode()).hexdigest()
+        key = hashlib.sha256((_HOST_FLAGS_TAG + self.source).encode()).hexdigest()
         _cache_dir.mkdir(parents=True, exist_ok=True)
         so = _cache_dir / f"{key}.so"
         if not so.exists():
             cpp = _cache_dir / f"{key}.cpp"
             cpp.write_text(self.source)
             tmp = _cache_dir / f"{key}.{os.getpid()}.tmp.so"
-            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-pthread", "-shared", "-fPIC",
+            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-fopenmp-simd", "-pthread", "-shared", "-fPIC",
                                 "-std=c++17", str(cpp), "-o", str(tmp)],
                                capture_output=True, text=True)
             if r.returncode != 0:
@@ -603,27 +605,74 @@ def generate_cuda_reduce(body: IrGraph, name: str, red_op: str, red_index: int) 
 
 
 def generate_host_reduce(body: IrGraph, name: str, red_op: str, red_index: int) -> str:
+    """Host form of the fused region + last-dimension reduction: rows are split over threads; per row the offsets of the leading dimensions are
+    computed once, inputs whose last dimension is broadcast are loaded once, and the others are walked with unit stride when they have it (the
+    vectorisable loop) or with their run-time stride otherwise."""
     ins = [body.values[i] for i in body.inputs]
     outs = [body.values[o] for o in body.outputs]
     red_v = outs[red_index]
     acc = _acc_type(red_v.dtype)
     ident, comb = _RED[red_op]
     others = [(k, v) for k, v in enumerate(outs) if k != red_index]
+    nin = max(len(ins), 1)
+    out_last = outs[0].shape[-1] if len(outs[0].shape) else 1
+    full = [len(v.shape) > 0 and v.shape[-1] == out_last and out_last > 1 for v in ins]
     params = [f"const {_HOST_CTYPE[v.dtype]}* __restrict__ in{k}" for k, v in enumerate(ins)] + [f"{_HOST_CTYPE[red_v.dtype]}* __restrict__ red_out"]
     params += [f"{_HOST_CTYPE[v.dtype]}* __restrict__ out{k}" for k, v in others] + ["long long rows", "int cols", "const FtStrides* stp"]
-    src = [_HOST_PRELUDE % (MAX_DIMS, max(len(ins), 1), MAX_DIMS), f'extern "C" void {name}({", ".join(params)}) {{', "  const FtStrides& st = *stp;",
-           "  for (long long row = 0; row < rows; row++) {", f"    {acc} acc = {ident};", "    for (int col = 0; col < cols; col++) {", "      const long long i = row * cols + col;"]
-    src += _offset_lines(len(ins), "st.", "      ")
-    names = {-1: "__HOST__"}
-    for k, v in enumerate(ins):
-        src.append(f"      const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'off[{k}]', host=True)};")
-        names[body.inputs[k]] = f"x{k}"
-    lines, var = _body_lines(body, names)
-    src += ["      " + l for l in lines]
-    src.append("      acc = " + comb.format(a="acc", b=f"(({acc}){var[body.outputs[red_index]]})") + ";")
-    for k, v in others:
-        src.append("      " + _store(v.dtype, f"out{k}", "i", var[body.outputs[k]], host=True))
-    src += ["    }", "    " + _store(red_v.dtype, "red_out", "row", "acc / cols" if red_op == "mean" else "acc", host=True), "  }", "}"]
+    src = [_HOST_PRELUDE % (MAX_DIMS, nin, MAX_DIMS), f'extern "C" void {name}({", ".join(params)}) {{', "  const FtStrides& st = *stp;", "  const int nd = st.ndim;"]
+    cond = " && ".join([f"st.stride[{k}][nd - 1] == {1 if full[k] else 0}" for k in range(len(ins))]) or "true"
+    src.append(f"  const bool rowfast = {cond};")
+    src.append("  auto work = [&](long long r0, long long r1) {")
+    src.append("  for (long long row = r0; row < r1; row++) {")
+    src.append(f"    long long rem = row, base[{nin}] = {{}};")
+    src.append("    for (int d = nd - 2; d >= 0; d--) { const long long c = rem % st.shape[d]; rem /= st.shape[d];")
+    for k in range(len(ins)):
+        src.append(f"      base[{k}] += c * st.stride[{k}][d];")
+    src.append("    }")
+    src.append(f"    {acc} acc = {ident};")
+    src.append("    const long long o = row * cols;")
+
+    def inner(fast: bool, indent: str) -> List[str]:
+        out = []
+        names = {-1: "__HOST__"}
+        if fast:
+            for k, v in enumerate(ins):
+                if full[k]:
+                    out.append(f"{indent}const {_HOST_CTYPE[v.dtype]}* __restrict__ p{k} = in{k} + base[{k}];")
+                else:
+                    out.append(f"{indent}const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'base[{k}]', host=True)};")
+        if fast and red_op in ("sum", "mean"):
+            out.append(f"{indent}#pragma omp simd reduction(+:acc)")          # lets the compiler keep one partial sum per vector lane
+        out.append(f"{indent}for (int col = 0; col < cols; col++) {{")
+        for k, v in enumerate(ins):
+            if fast and full[k]:
+                out.append(f"{indent}  const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'p' + str(k), 'col', host=True)};")
+            elif not fast:
+                out.append(f"{indent}  const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), f'base[{k}] + col * st.stride[{k}][nd - 1]', host=True)};")
+            names[body.inputs[k]] = f"x{k}"
+        lines, var = _body_lines(body, names)
+        if fast:
+            lines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in lines]
+        out += [indent + "  " + l for l in lines]
+        out.append(f"{indent}  acc = " + comb.format(a="acc", b=f"(({acc}){var[body.outputs[red_index]]})") + ";")
+        for k, v in others:
+            out.append(f"{indent}  " + _store(v.dtype, f"out{k}", "o + col", var[body.outputs[k]], host=True))
+        out.append(f"{indent}}}")
+        return out
+    src.append("    if (rowfast) {")
+    src += inner(True, "      ")
+    src.append("    } else {")
+    src += inner(False, "      ")
+    src.append("    }")
+    src.append("    " + _store(red_v.dtype, "red_out", "row", "acc / cols" if red_op == "mean" else "acc", host=True))
+    src += ["  }", "  };"]
+    src.append("  const long long grain = std::max<long long>(1, (1 << 16) / std::max(cols, 1));")
+    src.append("  long long nt = std::min<long long>((rows + grain - 1) / grain, (long long)std::max(1u, std::thread::hardware_concurrency()));")
+    src.append("  if (nt <= 1) { work(0, rows); return; }")
+    src.append("  std::vector<std::thread> th; const long long per = (rows + nt - 1) / nt;")
+    src.append("  for (long long t = 0; t < nt; t++) th.emplace_back(work, t * per, std::min(rows, (t + 1) * per));")
+    src.append("  for (auto& x : th) x.join();")
+    src.append("}")
     return "\n".join(src) + "\n"
 
 
@@ -696,14 +745,14 @@ class HostFusedReduceKernel(_FusedReduceBase):
         super().__init__(body, red_op, red_index, keepdim)
         self.name = f"ft_fusedred_{self.fp}_h"
         self.source = generate_host_reduce(body, self.name, red_op, red_index)
-        key = hashlib.sha256(self.source.encode()).hexdigest()
+        key = hashlib.sha256((_HOST_FLAGS_TAG + self.source).encode()).hexdigest()
         _cache_dir.mkdir(parents=True, exist_ok=True)
         so = _cache_dir / f"{key}.so"
         if not so.exists():
             cpp = _cache_dir / f"{key}.cpp"
             cpp.write_text(self.source)
             tmp = _cache_dir / f"{key}.{os.getpid()}.tmp.so"
-            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-pthread", "-shared", "-fPIC",
+            r = subprocess.run([os.environ.get("CXX", "g++"), "-O3", "-march=native", "-fno-math-errno", "-fno-trapping-math", "-fopenmp-simd", "-pthread", "-shared", "-fPIC",
                                 "-std=c++17", str(cpp), "-o", str(tmp)],
                                capture_output=True, text=True)
             if r.returncode != 0:
