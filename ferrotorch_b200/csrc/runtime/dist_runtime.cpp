@@ -363,6 +363,46 @@ static int allreduce_star(Backend& b, T* data, size_t n, int op, int64_t timeout
   const int r = b.rank(), w = b.world();
   if (w == 1) return OK;
   const size_t bytes = n * sizeof(T);
+  // Large vectors go through in chunks so that the peers' uploads, the reduction on rank 0 and the downloads overlap: a peer sends its chunks
+  // from a helper thread while its calling thread already receives reduced chunks. Element-wise the arithmetic (order of the ranks) is
+  // that of the one-piece form, so the results stay bit-identical across ranks and across the two forms.
+  constexpr size_t kChunkBytes = 256 << 10;
+  if (bytes >= 8 * kChunkBytes) {   // from 2 MiB: below that the per-chunk frames cost more than the overlap saves
+    const size_t ce = kChunkBytes / sizeof(T), nchunks = (n + ce - 1) / ce;
+    if (r == 0) {
+      std::vector<T> tmp(ce);
+      for (size_t c = 0; c < nchunks; c++) {
+        const size_t lo = c * ce, len = std::min(ce, n - lo);
+        for (int p = 1; p < w; p++) {
+          int e = b.recv(tmp.data(), len * sizeof(T), p, timeout_ms);
+          if (e) return e;
+          reduce_into(data + lo, tmp.data(), len, op);
+        }
+        if (op == MEAN) { const T inv = (T)w; for (size_t i = 0; i < len; i++) data[lo + i] /= inv; }
+        for (int p = 1; p < w; p++) { int e = b.send(data + lo, len * sizeof(T), p); if (e) return e; }
+      }
+      return OK;
+    }
+    std::atomic<size_t> sent{0};
+    std::atomic<int> send_err{OK};
+    std::thread sender([&] {
+      for (size_t c = 0; c < nchunks; c++) {
+        const size_t lo = c * ce, len = std::min(ce, n - lo);
+        int e = b.send(data + lo, len * sizeof(T), 0);
+        if (e) { send_err.store(e, std::memory_order_release); return; }
+        sent.store(c + 1, std::memory_order_release);
+      }
+    });
+    int err = OK;
+    for (size_t c = 0; c < nchunks && !err; c++) {
+      const size_t lo = c * ce, len = std::min(ce, n - lo);
+      // chunk c comes back only after it went out; the wait makes that order visible to this thread before it overwrites the chunk
+      while (sent.load(std::memory_order_acquire) <= c && !(err = send_err.load(std::memory_order_acquire))) std::this_thread::yield();
+      if (!err) err = b.recv(data + lo, len * sizeof(T), 0, timeout_ms);
+    }
+    sender.join();
+    return err ? err : send_err.load();
+  }
   if (r == 0) {
     std::vector<T> tmp(n);
     for (int p = 1; p < w; p++) {

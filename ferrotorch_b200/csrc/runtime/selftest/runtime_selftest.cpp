@@ -65,7 +65,7 @@ static void collectives(const std::vector<int64_t>& hs, int world, bool neighbou
   run_ranks(hs, [world, neighbours_connected](int64_t h, int r) {
     CHECK(ft_backend_rank(h) == r && ft_backend_world(h) == world);
     for (int algo = 0; algo < (neighbours_connected ? 2 : 1); algo++) {
-      for (int64_t n : {1, 7, 1000, 40001}) {
+      for (int64_t n : {1, 7, 1000, 40001, 600011}) {          // the last one takes the chunked star path (2.4 MB)
         std::vector<float> v((size_t)n);
         for (int64_t i = 0; i < n; i++) v[(size_t)i] = (float)(r + 1) + (float)(i % 13);
         CHECK(ft_allreduce(h, v.data(), n, 0, 0, algo, TMO) == 0);
