@@ -166,3 +166,34 @@ def test_gcn_matches_dense_and_policy_shapes():
     loss = rl.ppo_loss(pol, torch.randn(5, 4), torch.randint(0, 2, (5,)), torch.zeros(5), torch.randn(5), torch.randn(5))
     loss.backward()
     assert all(p.grad is not None for n, p in pol.named_parameters())
+
+
+def test_llama_training_model_matches_hf_transformers_through_hf_state_dict():
+    """The training model (flat per-layer units) against transformers' LlamaForCausalLM: weights go across under the HF key names in both
+    directions and the losses agree (half-rotation RoPE, GQA, pre-norm residual blocks, untied head)."""
+    import torch
+    from transformers import LlamaConfig as HFConfig, LlamaForCausalLM as HFModel
+    from ferrotorch_b200.models import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=1024)
+    ours = LlamaForCausalLM(cfg, device="cpu", seed=0)
+    hf_cfg = HFConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                      num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads, num_key_value_heads=cfg.num_key_value_heads,
+                      rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta, max_position_embeddings=cfg.max_position_embeddings,
+                      tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
+    hf = HFModel(hf_cfg).to(torch.bfloat16)
+    missing, unexpected = hf.load_state_dict(ours.hf_state_dict(), strict=False)
+    assert not missing and not unexpected
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (2, 33), generator=g)
+    with torch.no_grad():
+        loss = float(ours(ids[:, :-1], labels=ids[:, 1:]))
+        ref = float(torch.nn.functional.cross_entropy(hf(input_ids=ids[:, :-1]).logits.float().reshape(-1, cfg.vocab_size), ids[:, 1:].reshape(-1)))
+    assert abs(loss - ref) < 5e-3 * ref, (loss, ref)
+    # and back: a freshly initialised HF model loaded into a second instance of ours
+    hf2 = HFModel(hf_cfg).to(torch.bfloat16)
+    other = LlamaForCausalLM(cfg, device="cpu", seed=1)
+    other.load_hf_state_dict(hf2.state_dict())
+    with torch.no_grad():
+        loss2 = float(other(ids[:, :-1], labels=ids[:, 1:]))
+        ref2 = float(torch.nn.functional.cross_entropy(hf2(input_ids=ids[:, :-1]).logits.float().reshape(-1, cfg.vocab_size), ids[:, 1:].reshape(-1)))
+    assert abs(loss2 - ref2) < 5e-3 * ref2, (loss2, ref2)
