@@ -404,6 +404,64 @@ static inline float ft_expf(float x) {
   const float v = e * s0 * s1;
   return x > 88.72283935546875f ? INFINITY : (x < -103.972084045410f ? 0.0f : v);
 }
+// logf: exponent / mantissa split on the bit pattern, mantissa folded to [sqrt(1/2), sqrt(2)), degree-9 polynomial (Cephes). Zero -> -inf,
+// negative -> NaN, inf and NaN pass through, denormals are rescaled first.
+static inline float ft_logf(float x) {
+  const bool den = x < 1.17549435e-38f;
+  const float xs = den ? x * 8388608.0f : x;
+  uint32_t b;
+  std::memcpy(&b, &xs, 4);
+  int32_t e = (int32_t)((b >> 23) & 0xffu) - 126 - (den ? 23 : 0);
+  uint32_t mb = (b & 0x807fffffu) | 0x3f000000u;
+  float m;
+  std::memcpy(&m, &mb, 4);
+  const bool lo = m < 0.707106781186547524f;
+  e -= lo ? 1 : 0;
+  m = lo ? m + m - 1.0f : m - 1.0f;
+  const float z = m * m;
+  float p = 7.0376836292e-2f;
+  p = fmaf(p, m, -1.1514610310e-1f);
+  p = fmaf(p, m, 1.1676998740e-1f);
+  p = fmaf(p, m, -1.2420140846e-1f);
+  p = fmaf(p, m, 1.4249322787e-1f);
+  p = fmaf(p, m, -1.6668057665e-1f);
+  p = fmaf(p, m, 2.0000714765e-1f);
+  p = fmaf(p, m, -2.4999993993e-1f);
+  p = fmaf(p, m, 3.3333331174e-1f);
+  const float fe = (float)e;
+  float y = p * m * z;
+  y = fmaf(fe, -2.12194440e-4f, y);
+  y = fmaf(-0.5f, z, y);
+  const float r = fmaf(fe, 0.693359375f, m + y);
+  return x > 3.4028234e38f ? x : (x == 0.0f ? -INFINITY : (x < 0.0f ? NAN : (x != x ? x : r)));
+}
+// erff: odd Taylor polynomial below 1 (relative accuracy near zero), 1 - poly(t) * exp(-x^2) with t = 1 / (1 + p |x|) above (absolute error
+// about 1.5e-7, i.e. 1-2 ulp of a value between 0.84 and 1).
+static inline float ft_expf(float x);
+static inline float ft_erff(float x) {
+  const float ax = fabsf(x), z = x * x;
+  float s = -1.0892221020000000e-9f;                // -1 / 918086400: Taylor terms (-1)^k / (k! (2k+1)) of erf(x) sqrt(pi) / (2x), k = 11 .. 0
+  s = fmaf(s, z, 1.3122532963802806e-8f);           // 1 / 76204800
+  s = fmaf(s, z, -1.4503852223150468e-7f);          // -1 / 6894720
+  s = fmaf(s, z, 1.4589169000933707e-6f);           // 1 / 685440
+  s = fmaf(s, z, -1.3227513227513228e-5f);          // -1 / 75600
+  s = fmaf(s, z, 1.0683760683760684e-4f);           // 1 / 9360
+  s = fmaf(s, z, -7.5757575757575758e-4f);          // -1 / 1320
+  s = fmaf(s, z, 4.6296296296296294e-3f);           // 1 / 216
+  s = fmaf(s, z, -2.3809523809523808e-2f);          // -1 / 42
+  s = fmaf(s, z, 0.1f);
+  s = fmaf(s, z, -0.33333333333333331f);
+  s = fmaf(s, z, 1.0f);
+  const float small = 1.1283791670955126f * x * s;
+  const float t = 1.0f / fmaf(0.3275911f, ax, 1.0f);
+  float q = 1.061405429f;
+  q = fmaf(q, t, -1.453152027f);
+  q = fmaf(q, t, 1.421413741f);
+  q = fmaf(q, t, -0.284496736f);
+  q = fmaf(q, t, 0.254829592f);
+  const float big = 1.0f - q * t * ft_expf(-z);
+  return ax < 1.0f ? small : (x != x ? x : copysignf(big, x));
+}
 static inline float ft_tanhf(float x) {
   const float ax = fabsf(x);
   const float z = x * x;
@@ -440,7 +498,7 @@ def generate_host(body: IrGraph, name: str) -> str:
         src.append(f"      const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'in' + str(k), 'i', host=True)};")
         dnames[body.inputs[k]] = f"x{k}"
     dlines, dvar = _body_lines(body, dnames)
-    dlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in dlines]        # the vectorisable versions of the prelude
+    dlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf|logf|erff)\(", r"ft_\1(", l) for l in dlines]        # the vectorisable versions of the prelude
     src += ["      " + l for l in dlines]
     for k, v in enumerate(outs):
         src.append("      " + _store(v.dtype, f"out{k}", "i", dvar[body.outputs[k]], host=True))
@@ -477,7 +535,7 @@ def generate_host(body: IrGraph, name: str) -> str:
         if full[k]:
             src.append(f"        const {_acc_type(v.dtype)} x{k} = {_load(v.dtype, 'p' + str(k), 'col', host=True)};")
     rlines, rvar = _body_lines(body, rnames)
-    rlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in rlines]
+    rlines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf|logf|erff)\(", r"ft_\1(", l) for l in rlines]
     src += ["        " + l for l in rlines]
     for k, v in enumerate(outs):
         src.append("        " + _store(v.dtype, f"out{k}", "o + col", rvar[body.outputs[k]], host=True))
@@ -652,7 +710,7 @@ def generate_host_reduce(body: IrGraph, name: str, red_op: str, red_index: int) 
             names[body.inputs[k]] = f"x{k}"
         lines, var = _body_lines(body, names)
         if fast:
-            lines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf)\(", r"ft_\1(", l) for l in lines]
+            lines = [re.sub(r"(?<![A-Za-z0-9_])(expf|tanhf|logf|erff)\(", r"ft_\1(", l) for l in lines]
         out += [indent + "  " + l for l in lines]
         out.append(f"{indent}  acc = " + comb.format(a="acc", b=f"(({acc}){var[body.outputs[red_index]]})") + ";")
         for k, v in others:

@@ -182,3 +182,12 @@ def test_host_dense_loop_special_values_and_accuracy():
         assert torch.equal(torch.isnan(got), torch.isnan(ref)) and torch.equal(torch.isinf(got), torch.isinf(ref))
         fin = torch.isfinite(ref)
         assert ((got[fin] - ref[fin]).abs() <= tol * ref[fin].abs() + 1e-7).all()
+    xl = torch.cat([torch.logspace(-44, 38, 100001), torch.linspace(0.5, 2.0, 50001), torch.tensor([0.0, -0.0, -1.0, float("inf"), float("nan"), 1.0])]).contiguous()
+    xe = torch.cat([torch.linspace(-5, 5, 100001), torch.tensor([0.0, -0.0, float("inf"), -float("inf"), float("nan"), 1e-20, -1e-30, 30.0])]).contiguous()
+    for f, x in ((lambda a: torch.log(a) * 1.5, xl), (lambda a: torch.erf(a) * 1.5, xe)):
+        cf = jit.compile(f, example_inputs=[x], backend="auto")
+        got, ref = cf(x), f(x)
+        assert cf.stats.fused_kernels == 1
+        assert torch.equal(torch.isnan(got), torch.isnan(ref)) and torch.equal(got[torch.isinf(ref)], ref[torch.isinf(ref)])
+        fin = torch.isfinite(ref)
+        assert ((got[fin] - ref[fin]).abs() <= 6e-7 * ref[fin].abs() + 1e-37).all()
