@@ -1,8 +1,9 @@
 """Probability distributions, KL registry, transforms and constraints (API names follow ferrotorch-distributions).
 
-The 27 distribution families, ``kl_divergence`` with its pairwise registry, bijective transforms and support constraints carry
-PyTorch's reference semantics (``sample`` / ``rsample`` / ``log_prob`` / ``entropy``); sampling on CUDA tensors uses the
-device Philox stream.
+The 27 distribution families, ``kl_divergence`` with its pairwise registry, bijective transforms and support constraints are PyTorch's
+own implementations under the reference's names (``sample`` / ``rsample`` / ``log_prob`` / ``entropy``): this is a cold path that rides the
+host substrate's tensor ops, on any device. Sampling draws from the substrate's generators (``torch.manual_seed``), not from the Philox
+streams of ``ferrotorch_b200.gpu.CudaRngManager``.
 
 Reference parity: ferrotorch-distributions/src/lib.rs:138 (Distribution trait), kl.rs:66, transforms.rs, constraints.rs and one
 file per family.
