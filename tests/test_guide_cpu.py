@@ -1,0 +1,40 @@
+"""The snippets of docs/GUIDE.md that are marked as checked, executed as written (host side)."""
+import torch
+
+
+def test_guide_snippets(tmp_path):
+    from ferrotorch_b200 import gpu, jit, nn, optim, profiler, serialize, train
+    torch.manual_seed(0)
+    # 1. Learner
+    model = nn.Sequential(nn.Linear(20, 64), nn.ReLU(), nn.Linear(64, 3))
+    opt = optim.AdamW(model.parameters(), lr=1e-2)
+    x, y = torch.randn(256, 20), torch.randint(0, 3, (256,))
+    batches = [(x[i:i + 32], y[i:i + 32]) for i in range(0, 256, 32)]
+    learner = train.Learner(model, opt, nn.CrossEntropyLoss()).with_metric(train.AccuracyMetric())
+    history = learner.fit(batches, epochs=3, val_data=batches)
+    assert history.epochs[-1].train_loss < history.epochs[0].train_loss
+    # 2. compute copies under autocast
+    assert nn.attach_compute_copies(model) == 2
+    opt2 = optim.Sgd(model.parameters(), lr=0.1, momentum=0.9)
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        loss = torch.nn.functional.cross_entropy(model(x).float(), y)
+    loss.backward()
+    opt2.step()
+    assert all(torch.equal(nn.compute_copy(p), p.detach().bfloat16()) for p in model.parameters() if p.dim() == 2)
+    # 5. JIT
+    def f(a, b):
+        return torch.nn.functional.gelu(a + b) * 1.5 + torch.log(a * a + 1.0)
+    x2, bias = torch.randn(256, 512), torch.randn(512)
+    fast = jit.compile(f, example_inputs=[x2, bias])
+    assert torch.allclose(fast(x2, bias), f(x2, bias), atol=1e-5)
+    # 6. checkpoints
+    path = tmp_path / "model.safetensors"
+    serialize.save_safetensors(model.state_dict(), path)
+    state = serialize.load_safetensors(path)
+    assert set(state) == set(model.state_dict()) and all(torch.equal(state[k], v) for k, v in model.state_dict().items())
+    # 7. profiler and memory guard
+    result, report = profiler.with_profiler(profiler.ProfileConfig(), lambda: model(x))
+    assert result.shape == (256, 3) and isinstance(report.table(), str)
+    guard = gpu.MemoryGuardBuilder().with_budget(8 << 30).with_policy(gpu.OomPolicy.RETRY_AFTER_FREE).with_query(lambda: (0, 16 << 30)).build()
+    with guard.reserve(1 << 20):
+        assert guard.stats().reserved_by_guard == 1 << 20
