@@ -36,7 +36,9 @@ NVCC_FLAGS = [
 ]
 # bandwidth-bound generic kernels keep IEEE-accurate transcendentals (they are compared against f32 / f64 references at tight tolerances)
 PRECISE_MATH = {"elementwise.cu", "reduce_index.cu", "nn_ops.cu"}
-CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread", "-I", str(CSRC / "include"), "-I", str(CSRC / "runtime")]
+# no errno / trap bookkeeping for the math builtins (lets the Box-Muller and Philox loops vectorise); no FMA contraction, so the random streams are
+# the same on every x86-64 machine whatever instruction set the vector path picks
+CXX_FLAGS = ["-O3", "-fno-math-errno", "-fno-trapping-math", "-ffp-contract=off", "-std=c++20", "-fPIC", "-fvisibility=hidden", "-pthread", "-I", str(CSRC / "include"), "-I", str(CSRC / "runtime")]
 
 
 def _newest_header_mtime(dirs) -> float:

@@ -8,6 +8,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -110,7 +111,7 @@ static void philox_uniform32_avx2(uint64_t seed, uint64_t offset, float* out) {
 #endif
 static bool have_avx2() {
 #if defined(__x86_64__)
-  static const bool v = __builtin_cpu_supports("avx2");
+  static const bool v = __builtin_cpu_supports("avx2") && std::getenv("FT_NO_AVX2") == nullptr;      // FT_NO_AVX2: force the generic code (tests)
   return v;
 #else
   return false;
@@ -130,16 +131,78 @@ FT_API void ft_philox_uniform(uint64_t seed, uint64_t offset, int64_t n, float* 
     for (int e = 0; e < 4 && i + e < n; e++) out[i + e] = ((r[e] >> 8) + 0.5f) * (1.0f / 16777216.0f);   // (0,1)
   }
 }
+// Box-Muller on pairs of the uniform stream: z[2p] = r cos(2 pi u[2p+1]), z[2p+1] = r sin(2 pi u[2p+1]) with r = sqrt(-2 ln u[2p]). The logarithm
+// and the sine / cosine are branch-free polynomials (Cephes coefficients, 1-2 ulp) written as plain arithmetic and selects, so that the pair
+// loop vectorises; the same code runs for every element, whatever the block or thread split, so the values depend only on (seed, offset, index).
+static inline __attribute__((always_inline)) float bm_log(float x) {                       // x in (0, 1)
+  uint32_t b;
+  std::memcpy(&b, &x, 4);
+  int32_t e = (int32_t)((b >> 23) & 0xffu) - 126;
+  uint32_t mb = (b & 0x807fffffu) | 0x3f000000u;
+  float m;
+  std::memcpy(&m, &mb, 4);
+  const bool lo = m < 0.707106781186547524f;
+  e -= lo ? 1 : 0;
+  m = lo ? m + m - 1.0f : m - 1.0f;
+  const float z = m * m;
+  float p = 7.0376836292e-2f;
+  p = p * m - 1.1514610310e-1f;
+  p = p * m + 1.1676998740e-1f;
+  p = p * m - 1.2420140846e-1f;
+  p = p * m + 1.4249322787e-1f;
+  p = p * m - 1.6668057665e-1f;
+  p = p * m + 2.0000714765e-1f;
+  p = p * m - 2.4999993993e-1f;
+  p = p * m + 3.3333331174e-1f;
+  const float fe = (float)e;
+  float y = p * m * z;
+  y += fe * -2.12194440e-4f;
+  y -= 0.5f * z;
+  return m + y + fe * 0.693359375f;
+}
+static inline __attribute__((always_inline)) void bm_sincos_2pi(float u, float& sn, float& cs) {      // u in (0, 1): angle 2 pi u
+  const float t = u - 0.5f;                                            // sin(2 pi u) = -sin(2 pi t), cos(2 pi u) = -cos(2 pi t), t in (-1/2, 1/2)
+  const float k = __builtin_nearbyintf(4.0f * t);                            // quadrant: -2 .. 2
+  const float phi = 6.283185307179586f * (t - 0.25f * k);              // [-pi/4, pi/4]
+  const float z = phi * phi;
+  const float s0 = phi + phi * z * ((-1.9515295891e-4f * z + 8.3321608736e-3f) * z - 1.6666654611e-1f);
+  const float c0 = 1.0f - 0.5f * z + z * z * ((2.443315711809948e-5f * z - 1.388731625493765e-3f) * z + 4.166664568298827e-2f);
+  const int q = (int)k & 3;                                            // rotate by k quarter turns: (c, s) -> (c, s), (-s, c), (-c, -s), (s, -c)
+  const bool sw = (q & 1) != 0;
+  const float a = sw ? c0 : s0, b = sw ? s0 : c0;
+  const float s1 = (q & 2) ? -a : a;
+  const float c1 = ((q + 1) & 2) ? -b : b;
+  sn = -s1;
+  cs = -c1;
+}
+#define FT_BM_PAIRS_BODY                                        \
+  for (int p = 0; p < pairs; p++) {                             \
+    const float r = __builtin_sqrtf(-2.0f * bm_log(u[2 * p]));  \
+    float sn, cs;                                               \
+    bm_sincos_2pi(u[2 * p + 1], sn, cs);                        \
+    z[2 * p] = r * cs;                                          \
+    z[2 * p + 1] = r * sn;                                      \
+  }
+// the same loop compiled twice (no FMA contraction in either, so both give the same bits); the AVX2 build is picked at run time
+static void bm_pairs_generic(const float* __restrict__ u, float* __restrict__ z, int pairs) { FT_BM_PAIRS_BODY }
+#if defined(__x86_64__)
+__attribute__((target("avx2"))) static void bm_pairs_avx2(const float* __restrict__ u, float* __restrict__ z, int pairs) { FT_BM_PAIRS_BODY }
+#endif
+static void bm_pairs(const float* u, float* z, int pairs) {
+#if defined(__x86_64__)
+  if (have_avx2()) { bm_pairs_avx2(u, z, pairs); return; }
+#endif
+  bm_pairs_generic(u, z, pairs);
+}
 FT_API void ft_philox_normal(uint64_t seed, uint64_t offset, int64_t n, float* out) {
-  for (int64_t i = 0; i < n; i += 4) {
-    uint32_t r[4];
-    philox4x32_10(seed, offset + (uint64_t)(i / 4), 0, r);
-    float u[4];
-    for (int e = 0; e < 4; e++) u[e] = ((r[e] >> 8) + 0.5f) * (1.0f / 16777216.0f);
-    const float r0 = std::sqrt(-2.0f * std::log(u[0])), r1 = std::sqrt(-2.0f * std::log(u[2]));
-    const float z[4] = {r0 * std::cos(6.283185307179586f * u[1]), r0 * std::sin(6.283185307179586f * u[1]),
-                        r1 * std::cos(6.283185307179586f * u[3]), r1 * std::sin(6.283185307179586f * u[3])};
-    for (int e = 0; e < 4 && i + e < n; e++) out[i + e] = z[e];
+  constexpr int BLK = 1024;                                  // uniforms per block (a multiple of 32)
+  float u[BLK], z[BLK];
+  for (int64_t i0 = 0; i0 < n; i0 += BLK) {
+    const int64_t len = std::min<int64_t>(BLK, n - i0);
+    const int64_t padded = (len + 3) / 4 * 4;
+    ft_philox_uniform(seed, offset + (uint64_t)(i0 / 4), padded, u);
+    bm_pairs(u, z, (int)(padded / 2));
+    std::memcpy(out + i0, z, (size_t)len * sizeof(float));
   }
 }
 

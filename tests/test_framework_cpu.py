@@ -343,3 +343,32 @@ def test_learner_fit_checkpoint_resume_tensorboard(tmp_path):
     L2.load_checkpoint(tmp_path / "checkpoint_epoch_3.ftc")
     assert L2.epoch == 4 and L2.step == L.step and torch.equal(m2[0].weight, m[0].weight)
     assert T.crc32c(b"123456789") == 0xE3069283
+
+
+def test_host_philox_streams_do_not_depend_on_the_vector_path_or_thread_count():
+    """Large host rand / randn come from the native Philox fill: same seed -> same values, with the AVX2 code or the generic code (no FMA
+    contraction in either), with one thread or eight; the normal stream has unit moments."""
+    import subprocess
+    import sys
+    code = ("import torch, hashlib\nfrom ferrotorch_b200 import core\ntorch.manual_seed(123)\n"
+            "a = core.rand([300, 1001]); b = core.randn([300, 1001])\n"
+            "print(hashlib.sha256(a.numpy().tobytes() + b.numpy().tobytes()).hexdigest())\n")
+    import os
+    outs = []
+    for env in ({}, {"FT_NO_AVX2": "1"}):
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=dict(os.environ, **env),
+                           cwd=str(__import__("pathlib").Path(__file__).resolve().parents[1]))
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(r.stdout.strip().splitlines()[-1])
+    assert outs[0] == outs[1]
+    import torch
+    from ferrotorch_b200 import core
+    torch.manual_seed(5)
+    one = core.randn([512, 513])
+    torch.set_num_threads(1)
+    try:
+        torch.manual_seed(5)
+        assert torch.equal(one, core.randn([512, 513]))
+    finally:
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+    assert abs(float(one.mean())) < 0.01 and abs(float(one.std()) - 1.0) < 0.01 and abs(float((one ** 4).mean()) - 3.0) < 0.1
