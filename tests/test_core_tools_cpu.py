@@ -173,3 +173,29 @@ def test_control_flow_search_wrappers_pool_meta_display_fusion():
     assert C.from_vec([1, 2, 3, 4], (2, 2)).shape == (2, 2)
     with pytest.raises(Exception):
         C.from_vec([1, 2, 3], (2, 2))
+
+
+def test_tokenizer_matches_hf_tokenizers_on_a_trained_byte_level_bpe(tmp_path):
+    """A byte-level BPE trained with the HF ``tokenizers`` library on this package's own sources, saved as ``tokenizer.json`` and read back by
+    ``tokenize.load_tokenizer``: identical ids (code, unicode, runs of whitespace, special tokens) and identical round trips."""
+    import glob
+    from pathlib import Path
+    tk = pytest.importorskip("tokenizers")
+    from tokenizers import decoders, models, pre_tokenizers, trainers
+    from ferrotorch_b200 import tokenize
+    root = Path(__file__).resolve().parents[1] / "ferrotorch_b200"
+    files = sorted(glob.glob(str(root / "**" / "*.py"), recursive=True))[:25]
+    hf = tk.Tokenizer(models.BPE())
+    hf.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    hf.decoder = decoders.ByteLevel()
+    hf.train(files, trainers.BpeTrainer(vocab_size=1200, special_tokens=["<|begin|>", "<|end|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                        show_progress=False))
+    path = tmp_path / "tokenizer.json"
+    hf.save(str(path))
+    ours = tokenize.load_tokenizer(path)
+    texts = ["hello world", "def f(x):\n    return x + 1  # comment", "naïve café — ünïcödé ✓ 你好", "  multiple   spaces\tand\ttabs\n\nnewlines",
+             "<|begin|>special<|end|> tokens", "12345 67890 3.14159", Path(files[3]).read_text()[:4000]]
+    for t in texts:
+        a, b = ours.encode(t), hf.encode(t).ids
+        assert a == b, t[:40]
+        assert ours.decode(a, skip_special_tokens=False) == hf.decode(b, skip_special_tokens=False)
