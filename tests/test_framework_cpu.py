@@ -372,3 +372,44 @@ def test_host_philox_streams_do_not_depend_on_the_vector_path_or_thread_count():
     finally:
         torch.set_num_threads(max(1, os.cpu_count() or 1))
     assert abs(float(one.mean())) < 0.01 and abs(float(one.std()) - 1.0) < 0.01 and abs(float((one ** 4).mean()) - 3.0) < 0.1
+
+
+def test_gguf_reader_matches_the_official_writer(tmp_path):
+    """A file written by the ``gguf`` package (metadata of every kind used by Llama exports, f32 / f16 / q4_0 / q4_1 / q5_0 / q5_1 / q8_0 tensors):
+    metadata read back as written, tensors dequantised to exactly what the package's own dequantiser gives."""
+    import numpy as np
+    gguf = pytest.importorskip("gguf")
+    from gguf import GGMLQuantizationType as T, quants
+    from ferrotorch_b200 import serialize as S
+    rng = np.random.default_rng(0)
+    path = tmp_path / "parity.gguf"
+    w = gguf.GGUFWriter(str(path), "llama")
+    w.add_uint32("llama.block_count", 2)
+    w.add_string("general.name", "parity")
+    w.add_float32("llama.rope.freq_base", 500000.0)
+    w.add_array("tokenizer.ggml.tokens", ["a", "b", "c"])
+    want = {}
+    for name, q, shape in (("f32", T.F32, (3, 64)), ("f16", T.F16, (2, 64)), ("q4_0", T.Q4_0, (4, 64)), ("q4_1", T.Q4_1, (4, 64)), ("q5_0", T.Q5_0, (2, 128)),
+                           ("q5_1", T.Q5_1, (2, 128)), ("q8_0", T.Q8_0, (5, 32))):
+        x = rng.standard_normal(shape).astype(np.float32)
+        if q == T.F32:
+            data, want[name] = x, x
+            w.add_tensor(name, data)
+        elif q == T.F16:
+            data = x.astype(np.float16)
+            want[name] = data.astype(np.float32)
+            w.add_tensor(name, data)
+        else:
+            data = quants.quantize(x, q)
+            want[name] = quants.dequantize(data, q)
+            w.add_tensor(name, data, raw_shape=data.shape, raw_dtype=q)
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+    g = S.parse_gguf(path)
+    assert g.metadata["llama.block_count"] == 2 and g.metadata["general.name"] == "parity" and g.metadata["tokenizer.ggml.tokens"] == ["a", "b", "c"]
+    assert abs(g.metadata["llama.rope.freq_base"] - 500000.0) < 1e-3
+    for k, v in want.items():
+        t = g.load_tensor(k)
+        assert tuple(t.shape) == v.shape and np.array_equal(t.numpy(), v), k
