@@ -413,3 +413,24 @@ def test_gguf_reader_matches_the_official_writer(tmp_path):
     for k, v in want.items():
         t = g.load_tensor(k)
         assert tuple(t.shape) == v.shape and np.array_equal(t.numpy(), v), k
+
+
+def test_tensorboard_event_files_are_read_by_tensorboard(tmp_path):
+    """The hand-written event-file writer (record framing with masked CRC32C, Event / Summary protobufs) against TensorBoard's own reader."""
+    pytest.importorskip("tensorboard")
+    from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+    w = T.TensorBoardWriter(tmp_path / "run")
+    for s in range(5):
+        w.add_scalar("loss", 1.0 / (s + 1), s)
+    w.add_scalars("m", {"a": 1.5, "b": -2.0}, 3)
+    w.add_histogram("h", torch.arange(100.0), 7)
+    for name in ("flush", "close"):
+        getattr(w, name, lambda: None)()
+    ea = EventAccumulator(str(tmp_path / "run"), size_guidance={"histograms": 0, "scalars": 0})
+    ea.Reload()
+    tags = ea.Tags()
+    assert sorted(tags["scalars"]) == ["loss", "m/a", "m/b"] and tags["histograms"] == ["h"]
+    assert [(e.step, round(e.value, 4)) for e in ea.Scalars("loss")] == [(0, 1.0), (1, 0.5), (2, 0.3333), (3, 0.25), (4, 0.2)]
+    assert [(e.step, e.value) for e in ea.Scalars("m/b")] == [(3, -2.0)]
+    h = ea.Histograms("h")[0]
+    assert h.step == 7 and h.histogram_value.min == 0.0 and h.histogram_value.max == 99.0 and h.histogram_value.num == 100 and h.histogram_value.sum == 4950.0
