@@ -172,7 +172,12 @@ def precision_recall_f1(y_true, y_pred, average: str = "macro"):
     if average == "micro":
         a = tp.sum() / max(cm.sum(), 1)
         return float(a), float(a), float(a)
-    return prec, rec, f1
+    if average == "weighted":                       # class means weighted by the number of true samples of each class
+        w = cm.sum(1) / max(cm.sum(), 1)
+        return float((prec * w).sum()), float((rec * w).sum()), float((f1 * w).sum())
+    if average is None or average == "none":
+        return prec, rec, f1
+    raise InvalidArgument(f"unknown average {average!r} (macro, micro, weighted or None)")
 
 
 def precision_score(y_true, y_pred, average="macro"):
@@ -189,9 +194,16 @@ def f1_score(y_true, y_pred, average="macro"):
 
 def roc_auc_score(y_true, scores) -> float:
     y, s = _np(y_true).astype(np.int64), _np(scores).astype(np.float64)
-    order = np.argsort(s)
+    # mid-ranks: tied scores share the mean of the ranks they span (the Mann-Whitney statistic with ties counted as one half)
+    order = np.argsort(s, kind="mergesort")
+    ss = s[order]
+    first = np.r_[True, ss[1:] != ss[:-1]]
+    group = np.cumsum(first) - 1
+    starts = np.flatnonzero(first)
+    ends = np.r_[starts[1:], len(ss)]
+    mid = (starts + 1 + ends) / 2.0
     ranks = np.empty(len(s))
-    ranks[order] = np.arange(1, len(s) + 1)
+    ranks[order] = mid[group]
     npos, nneg = y.sum(), (1 - y).sum()
     if npos == 0 or nneg == 0:
         raise InvalidArgument("ROC AUC needs both classes")

@@ -199,3 +199,26 @@ def test_tokenizer_matches_hf_tokenizers_on_a_trained_byte_level_bpe(tmp_path):
         a, b = ours.encode(t), hf.encode(t).ids
         assert a == b, t[:40]
         assert ours.decode(a, skip_special_tokens=False) == hf.decode(b, skip_special_tokens=False)
+
+
+def test_ml_metrics_match_scikit_learn():
+    """The metric functions of the sklearn-style adapter against scikit-learn itself on random multi-class and binary problems."""
+    skm = pytest.importorskip("sklearn.metrics")
+    import numpy as np
+    from ferrotorch_b200 import ml
+    rng = np.random.default_rng(0)
+    y, p = rng.integers(0, 4, 500), rng.integers(0, 4, 500)
+    assert abs(ml.accuracy_score(y, p) - skm.accuracy_score(y, p)) < 1e-12
+    assert np.array_equal(ml.confusion_matrix(y, p), skm.confusion_matrix(y, p))
+    for avg in ("macro", "micro", "weighted"):
+        assert abs(ml.precision_score(y, p, average=avg) - skm.precision_score(y, p, average=avg, zero_division=0)) < 1e-9, avg
+        assert abs(ml.recall_score(y, p, average=avg) - skm.recall_score(y, p, average=avg, zero_division=0)) < 1e-9, avg
+        assert abs(ml.f1_score(y, p, average=avg) - skm.f1_score(y, p, average=avg, zero_division=0)) < 1e-9, avg
+    yb, s = rng.integers(0, 2, 400), rng.random(400)
+    s[:200:2] = s[1:200:2]                                              # some tied scores
+    assert abs(ml.roc_auc_score(yb, s) - skm.roc_auc_score(yb, s)) < 1e-9
+    proba = rng.dirichlet(np.ones(4), 500)
+    assert abs(ml.log_loss(y, proba) - skm.log_loss(y, proba, labels=[0, 1, 2, 3])) < 1e-9
+    t, q = rng.standard_normal(300), rng.standard_normal(300)
+    assert abs(ml.r2_score(t, q) - skm.r2_score(t, q)) < 1e-9 and abs(ml.mean_squared_error(t, q) - skm.mean_squared_error(t, q)) < 1e-12
+    assert abs(ml.mean_absolute_error(t, q) - skm.mean_absolute_error(t, q)) < 1e-12
