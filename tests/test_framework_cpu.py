@@ -434,3 +434,24 @@ def test_tensorboard_event_files_are_read_by_tensorboard(tmp_path):
     assert [(e.step, e.value) for e in ea.Scalars("m/b")] == [(3, -2.0)]
     h = ea.Histograms("h")[0]
     assert h.step == 7 and h.histogram_value.min == 0.0 and h.histogram_value.max == 99.0 and h.histogram_value.num == 100 and h.histogram_value.sum == 4950.0
+
+
+@pytest.mark.parametrize("kw", [dict(lr=1e-3, scale_parameter=True, relative_step=False),
+                                dict(lr=1e-2, scale_parameter=False, relative_step=False, beta1=0.9, weight_decay=0.01),
+                                dict(lr=None, scale_parameter=True, relative_step=True)])
+def test_adafactor_matches_the_transformers_implementation(kw):
+    """Factored second moments, update clipping, parameter-scaled and relative step sizes: six steps on a matrix and a vector against
+    ``transformers.optimization.Adafactor``."""
+    hf = pytest.importorskip("transformers.optimization")
+    torch.manual_seed(0)
+    w0, b0 = torch.randn(6, 5), torch.randn(5)
+    pa = [torch.nn.Parameter(w0.clone()), torch.nn.Parameter(b0.clone())]
+    pb = [torch.nn.Parameter(w0.clone()), torch.nn.Parameter(b0.clone())]
+    a = O.Adafactor(pa, **kw)
+    b = hf.Adafactor(pb, **dict(kw, warmup_init=False) if kw.get("relative_step") else kw)
+    for _ in range(6):
+        for p, q, g in zip(pa, pb, (torch.randn(6, 5), torch.randn(5))):
+            p.grad, q.grad = g.clone(), g.clone()
+        a.step()
+        b.step()
+    assert max(float((p - q).abs().max()) for p, q in zip(pa, pb)) < 2e-6
