@@ -61,6 +61,8 @@ class LlamaConfig:
     def llama3_3_70b_instruct() -> "LlamaConfig":
         c = LlamaConfig.llama3_70b()
         c.max_position_embeddings = 131072
+        # the published checkpoint's config.json carries the frequency-dependent rope scaling of Llama 3.1 and later
+        c.rope_scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}
         return c
 
     @staticmethod

@@ -9,31 +9,64 @@ import math
 
 import torch
 
+from ..errors import InvalidArgument
+
 from .. import _lib
 
 
-def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None):
-    """cos/sin tables ``[max_pos, head_dim/2]`` in f32. ``scaling``: {"type": "linear"|"ntk"|"yarn", "factor": f, ...}."""
+def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
+    """Inverse frequencies ``[head_dim / 2]`` (f64) and the factor that multiplies the cos / sin tables, for a rope-scaling description.
+
+    ``scaling`` is either this framework's form ``{"type": "linear" | "ntk" | "yarn", "factor": f, ...}`` (the variants of
+    ferrotorch-nn/src/transformer.rs:210-266: linear position interpolation, static NTK-aware base scaling, YaRN) or a HF ``rope_scaling``
+    dict ``{"rope_type": "default" | "linear" | "llama3" | "yarn", ...}`` as found in ``config.json`` (``llama3``: the frequency-dependent
+    scaling of Llama 3.1 and later; the reference ignores ``rope_scaling`` altogether). HF YaRN dicts also scale the tables by
+    ``0.1 ln(factor) + 1`` (or their ``attention_factor``), as the HF implementation does. Unknown types are refused, not ignored."""
     half = head_dim // 2
     base = float(theta)
-    if scaling and scaling.get("type") == "ntk":
-        base = base * scaling["factor"] ** (head_dim / (head_dim - 2))
+    hf = bool(scaling) and "rope_type" in scaling
+    kind = (scaling.get("rope_type") or scaling.get("type") or "none") if scaling else "none"
+    att = 1.0
+    if kind in ("none", "default"):
+        return 1.0 / (base ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim)), att
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "ntk":
+        base = base * factor ** (head_dim / (head_dim - 2))
     inv = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim))
-    pos = torch.arange(max_pos, dtype=torch.float64)
-    if scaling and scaling.get("type") == "linear":
-        pos = pos / scaling["factor"]
-    if scaling and scaling.get("type") == "yarn":
-        f = scaling["factor"]
-        orig = scaling.get("original_max_position", max_pos)
-        beta_fast, beta_slow = scaling.get("beta_fast", 32.0), scaling.get("beta_slow", 1.0)
+    if kind == "ntk":
+        return inv, att
+    if kind == "linear":
+        return inv / factor, att
+    if kind == "llama3":
+        lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv
+        inv_l = torch.where(wavelen > old / lo_f, inv / factor, inv)
+        smooth = (old / wavelen - lo_f) / (hi_f - lo_f)
+        smoothed = (1 - smooth) * inv_l / factor + smooth * inv_l
+        medium = ~(wavelen < old / hi_f) & ~(wavelen > old / lo_f)
+        return torch.where(medium, smoothed, inv_l), att
+    if kind == "yarn":
+        orig = scaling.get("original_max_position", scaling.get("original_max_position_embeddings"))
+        if orig is None:
+            raise InvalidArgument("yarn rope scaling needs the original maximum position")
+        beta_fast, beta_slow = float(scaling.get("beta_fast", 32.0)), float(scaling.get("beta_slow", 1.0))
 
         def corr(n):
             return head_dim * math.log(orig / (n * 2 * math.pi)) / (2 * math.log(base))
-        lo, hi = max(math.floor(corr(beta_fast)), 0), min(math.ceil(corr(beta_slow)), half - 1)
-        ramp = ((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
-        inv = inv / f * ramp + inv * (1 - ramp)
-    ang = torch.outer(pos, inv)
-    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+        lo, hi = max(math.floor(corr(beta_fast)), 0), min(math.ceil(corr(beta_slow)), head_dim - 1)
+        ramp = ((torch.arange(half, dtype=torch.float64) - lo) / (hi - lo if hi != lo else 1e-3)).clamp(0, 1)
+        if hf or "attention_factor" in scaling:
+            att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+        return inv / factor * ramp + inv * (1 - ramp), att
+    raise InvalidArgument(f"unknown rope scaling type {kind!r} (none, default, linear, ntk, llama3, yarn)")
+
+
+def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None):
+    """cos/sin tables ``[max_pos, head_dim/2]`` in f32 for the scaling description of :func:`rope_inv_freq`."""
+    inv, att = rope_inv_freq(head_dim, theta, scaling)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv)
+    return (ang.cos() * att).float().to(device).contiguous(), (ang.sin() * att).float().to(device).contiguous()
 
 
 def rope_inplace(x2: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int, head0: int, nheads: int, head_dim: int,

@@ -197,3 +197,33 @@ def test_llama_training_model_matches_hf_transformers_through_hf_state_dict():
         loss2 = float(other(ids[:, :-1], labels=ids[:, 1:]))
         ref2 = float(torch.nn.functional.cross_entropy(hf2(input_ids=ids[:, :-1]).logits.float().reshape(-1, cfg.vocab_size), ids[:, 1:].reshape(-1)))
     assert abs(loss2 - ref2) < 5e-3 * ref2, (loss2, ref2)
+
+
+def test_rope_scaling_types_match_transformers():
+    """Inverse frequencies and table scale of the rope-scaling descriptions found in HF configs (linear, llama3 as in Llama 3.1+, yarn) against
+    transformers' rotary embedding; unknown types are refused."""
+    import pytest
+    import torch
+    from transformers import LlamaConfig as HFConfig
+    from transformers.models.llama.modeling_llama import LlamaRotaryEmbedding
+    from ferrotorch_b200 import ops
+    from ferrotorch_b200.errors import InvalidArgument
+    D = 128
+    for rs in (None, dict(rope_type="linear", factor=4.0),
+               dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=8192),
+               dict(rope_type="yarn", factor=8.0, original_max_position_embeddings=2048, beta_fast=32.0, beta_slow=1.0)):
+        emb = LlamaRotaryEmbedding(HFConfig(hidden_size=D * 4, num_attention_heads=4, rope_theta=500000.0, max_position_embeddings=16384,
+                                            rope_scaling=dict(rs) if rs else None))
+        inv, att = ops.llama.rope_inv_freq(D, 500000.0, rs)
+        assert float(((emb.inv_freq.double() - inv).abs() / inv).max()) < 1e-6, rs
+        assert abs(float(emb.attention_scaling) - att) < 1e-9
+        cos, sin = ops.rope_tables(64, D, 500000.0, "cpu", rs)
+        ang = torch.outer(torch.arange(64, dtype=torch.float64), inv)
+        assert torch.allclose(cos.double(), ang.cos() * att, atol=1e-6) and torch.allclose(sin.double(), ang.sin() * att, atol=1e-6)
+    # this framework's own descriptions: static NTK base scaling, YaRN without a table scale (ferrotorch-nn/src/transformer.rs:210-266)
+    inv_ntk, _ = ops.llama.rope_inv_freq(D, 10000.0, {"type": "ntk", "factor": 4.0})
+    assert abs(float(inv_ntk[0]) - 1.0) < 1e-12 and float(inv_ntk[-1]) < 1.0 / 10000.0 ** ((D - 2) / D) / 3.9
+    _, att = ops.llama.rope_inv_freq(D, 10000.0, {"type": "yarn", "factor": 8.0, "original_max_position": 2048})
+    assert att == 1.0
+    with pytest.raises(InvalidArgument):
+        ops.rope_tables(8, D, 10000.0, "cpu", {"rope_type": "longrope", "factor": 2.0})
