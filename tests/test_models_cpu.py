@@ -227,3 +227,26 @@ def test_rope_scaling_types_match_transformers():
     assert att == 1.0
     with pytest.raises(InvalidArgument):
         ops.rope_tables(8, D, 10000.0, "cpu", {"rope_type": "longrope", "factor": 2.0})
+
+
+def test_cached_generation_and_sampling_filters_match_transformers():
+    """Greedy generation with the KV-cache model from a transformers checkpoint equals ``generate(do_sample=False)``; the top-k, top-p and
+    repetition-penalty filters equal transformers' logits processors."""
+    import torch
+    from transformers import LlamaConfig as HFConfig, LlamaForCausalLM as HFModel
+    from transformers.generation.logits_process import RepetitionPenaltyLogitsProcessor, TopKLogitsWarper, TopPLogitsWarper
+    from ferrotorch_b200.models import LlamaConfig, llama_gen as G
+    torch.manual_seed(0)
+    cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=512)
+    hf = HFModel(HFConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size, num_hidden_layers=2,
+                          num_attention_heads=2, num_key_value_heads=1, rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta,
+                          max_position_embeddings=2048, tie_word_embeddings=False)).float().eval()
+    model = G.CachedLlama(cfg, {k: v.clone() for k, v in hf.state_dict().items()})
+    ids = torch.randint(0, 512, (2, 9))
+    out = G.generate(model, model.new_cache, ids, G.GenerationConfig().with_max_new_tokens(12))
+    ref = hf.generate(ids, max_new_tokens=12, do_sample=False, pad_token_id=0)
+    assert torch.equal(out[:, -12:], ref[:, -12:])
+    logits, seq = torch.randn(3, 512), torch.randint(0, 512, (3, 20))
+    assert torch.equal(G.top_k_filter(logits.clone(), 7), TopKLogitsWarper(7)(seq, logits.clone()))
+    assert torch.equal(G.top_p_filter(logits.clone(), 0.8), TopPLogitsWarper(0.8)(seq, logits.clone()))
+    assert torch.allclose(G.apply_repetition_penalty(logits.clone(), seq, 1.3), RepetitionPenaltyLogitsProcessor(1.3)(seq, logits.clone()))
