@@ -14,13 +14,14 @@ from ..errors import InvalidArgument
 from .. import _lib
 
 
-def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
+def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None, seq_len: int | None = None):
     """Inverse frequencies ``[head_dim / 2]`` (f64) and the factor that multiplies the cos / sin tables, for a rope-scaling description.
 
     ``scaling`` is either this framework's form ``{"type": "linear" | "ntk" | "yarn", "factor": f, ...}`` (the variants of
     ferrotorch-nn/src/transformer.rs:210-266: linear position interpolation, static NTK-aware base scaling, YaRN) or a HF ``rope_scaling``
-    dict ``{"rope_type": "default" | "linear" | "llama3" | "yarn", ...}`` as found in ``config.json`` (``llama3``: the frequency-dependent
-    scaling of Llama 3.1 and later; the reference ignores ``rope_scaling`` altogether). HF YaRN dicts also scale the tables by
+    dict ``{"rope_type": "default" | "linear" | "dynamic" | "llama3" | "yarn", ...}`` as found in ``config.json`` (``llama3``: the
+    frequency-dependent scaling of Llama 3.1 and later; ``dynamic``: NTK base scaling that grows with ``seq_len`` beyond
+    ``original_max_position_embeddings``; the reference ignores ``rope_scaling`` altogether). HF YaRN dicts also scale the tables by
     ``0.1 ln(factor) + 1`` (or their ``attention_factor``), as the HF implementation does. Unknown types are refused, not ignored."""
     half = head_dim // 2
     base = float(theta)
@@ -37,6 +38,13 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
         return inv, att
     if kind == "linear":
         return inv / factor, att
+    if kind == "dynamic":
+        orig = scaling.get("original_max_position_embeddings", scaling.get("max_position_embeddings"))
+        if orig is None:
+            raise InvalidArgument("dynamic rope scaling needs original_max_position_embeddings")
+        n = max(int(seq_len or orig), int(orig))
+        b = base * ((factor * n / orig) - (factor - 1)) ** (head_dim / (head_dim - 2))
+        return 1.0 / (b ** (torch.arange(0, half, dtype=torch.float64) * 2.0 / head_dim)), att
     if kind == "llama3":
         lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
         old = float(scaling.get("original_max_position_embeddings", 8192))
@@ -59,12 +67,12 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None):
         if hf or "attention_factor" in scaling:
             att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
         return inv / factor * ramp + inv * (1 - ramp), att
-    raise InvalidArgument(f"unknown rope scaling type {kind!r} (none, default, linear, ntk, llama3, yarn)")
+    raise InvalidArgument(f"unknown rope scaling type {kind!r} (none, default, linear, ntk, dynamic, llama3, yarn)")
 
 
 def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling: dict | None = None):
     """cos/sin tables ``[max_pos, head_dim/2]`` in f32 for the scaling description of :func:`rope_inv_freq`."""
-    inv, att = rope_inv_freq(head_dim, theta, scaling)
+    inv, att = rope_inv_freq(head_dim, theta, scaling, seq_len=max_pos)
     ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv)
     return (ang.cos() * att).float().to(device).contiguous(), (ang.sin() * att).float().to(device).contiguous()
 

@@ -220,6 +220,12 @@ def test_rope_scaling_types_match_transformers():
         cos, sin = ops.rope_tables(64, D, 500000.0, "cpu", rs)
         ang = torch.outer(torch.arange(64, dtype=torch.float64), inv)
         assert torch.allclose(cos.double(), ang.cos() * att, atol=1e-6) and torch.allclose(sin.double(), ang.sin() * att, atol=1e-6)
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    dyn = HFConfig(hidden_size=D * 4, num_attention_heads=4, rope_theta=10000.0, max_position_embeddings=2048, rope_scaling=dict(rope_type="dynamic", factor=4.0))
+    for length in (1024, 2048, 5000, 16384):
+        inv_hf, _ = ROPE_INIT_FUNCTIONS["dynamic"](dyn, "cpu", seq_len=length)
+        inv, _ = ops.llama.rope_inv_freq(D, 10000.0, dict(rope_type="dynamic", factor=4.0, original_max_position_embeddings=2048), seq_len=length)
+        assert float(((inv_hf.double() - inv).abs() / inv).max()) < 1e-6
     # this framework's own descriptions: static NTK base scaling, YaRN without a table scale (ferrotorch-nn/src/transformer.rs:210-266)
     inv_ntk, _ = ops.llama.rope_inv_freq(D, 10000.0, {"type": "ntk", "factor": 4.0})
     assert abs(float(inv_ntk[0]) - 1.0) < 1e-12 and float(inv_ntk[-1]) < 1.0 / 10000.0 ** ((D - 2) / D) / 3.9
