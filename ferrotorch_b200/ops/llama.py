@@ -25,7 +25,8 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None = None, seq_
     ``0.1 ln(factor) + 1`` (or their ``attention_factor``), as the HF implementation does. Unknown types are refused, not ignored."""
     half = head_dim // 2
     base = float(theta)
-    hf = bool(scaling) and "rope_type" in scaling
+    # older HF configs spell the key "type"; what tells them from this framework's own dicts is the HF name of the original-length field
+    hf = bool(scaling) and ("rope_type" in scaling or "original_max_position_embeddings" in scaling)
     kind = (scaling.get("rope_type") or scaling.get("type") or "none") if scaling else "none"
     att = 1.0
     if kind in ("none", "default"):
