@@ -326,10 +326,12 @@ _AWQ_ORDER = [0, 4, 1, 5, 2, 6, 3, 7]
 
 
 def dequantize_awq_q4(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
-    """AWQ 4-bit (GEMM layout): ``qweight`` int32 ``[in, out/8]`` with the interleaved nibble order 0,4,1,5,2,6,3,7."""
-    inv = torch.tensor(_AWQ_ORDER, device=qweight.device).argsort()
-    w = _unpack_int4(qweight, 1).view(qweight.shape[0], -1, 8)[:, :, inv].reshape(qweight.shape[0], -1).float()
-    z = _unpack_int4(qzeros, 1).view(qzeros.shape[0], -1, 8)[:, :, inv].reshape(qzeros.shape[0], -1).float()
+    """AWQ 4-bit (GEMM layout): ``qweight`` int32 ``[in, out/8]``. Output channel ``c`` of a word sits in nibble ``[0, 4, 1, 5, 2, 6, 3, 7][c]``
+    (AutoAWQ packs the channels of a word in the order 0, 2, 4, 6, 1, 3, 5, 7; ferrotorch-llama/src/quant_loaders.rs:244-331 reads them back the
+    same way)."""
+    order = torch.tensor(_AWQ_ORDER, device=qweight.device)
+    w = _unpack_int4(qweight, 1).view(qweight.shape[0], -1, 8)[:, :, order].reshape(qweight.shape[0], -1).float()
+    z = _unpack_int4(qzeros, 1).view(qzeros.shape[0], -1, 8)[:, :, order].reshape(qzeros.shape[0], -1).float()
     gi = torch.arange(w.shape[0], device=w.device) // group_size
     return ((w - z[gi]) * scales.float()[gi]).t().contiguous()
 

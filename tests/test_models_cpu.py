@@ -82,7 +82,7 @@ def test_quant_loaders_and_gguf_names():
     wa = torch.randint(0, 16, (32, 8), generator=gen)
     za = torch.randint(0, 16, (1, 8), generator=gen)
     sa = torch.rand(1, 8, generator=gen)
-    order = [0, 4, 1, 5, 2, 6, 3, 7]
+    order = [0, 2, 4, 6, 1, 3, 5, 7]                 # AutoAWQ's packing order: nibble i of a word holds channel order[i]
     qwa, qza = torch.zeros(32, 1, dtype=torch.int32), torch.zeros(1, 1, dtype=torch.int32)
     for i, o in enumerate(order):
         qwa[:, 0] |= wa[:, o].to(torch.int32) << (4 * i)
@@ -256,3 +256,25 @@ def test_cached_generation_and_sampling_filters_match_transformers():
     assert torch.equal(G.top_k_filter(logits.clone(), 7), TopKLogitsWarper(7)(seq, logits.clone()))
     assert torch.equal(G.top_p_filter(logits.clone(), 0.8), TopPLogitsWarper(0.8)(seq, logits.clone()))
     assert torch.allclose(G.apply_repetition_penalty(logits.clone(), seq, 1.3), RepetitionPenaltyLogitsProcessor(1.3)(seq, logits.clone()))
+
+
+def test_gptq_and_awq_dequantisation_match_vllm_reference_packers():
+    """Weights quantised and packed by vLLM's reference utilities (GPTQ: rows of eight along the input dimension, stored zero = zero point - 1;
+    AWQ: interleaved channel order, explicit zero points) come back as the reference's dequantised weights."""
+    import pytest
+    import torch
+    try:
+        from vllm.model_executor.layers.quantization.utils import quant_utils as Q
+        from vllm.scalar_type import scalar_types
+    except Exception as e:                            # the library is an optional oracle
+        pytest.skip(f"vllm quantisation utilities not importable: {e}")
+    from ferrotorch_b200.models import llama_gen as G
+    torch.manual_seed(0)
+    K, N, gs = 256, 64, 128
+    w = torch.randn(K, N)
+    w_ref, q_w, s, _, _ = Q.gptq_quantize_weights(w, scalar_types.uint4b8, gs, act_order=False)
+    qzeros = Q.pack_cols(torch.full((K // gs, N), 7, dtype=torch.int32), 4, K // gs, N)
+    assert torch.equal(G.dequantize_gptq_q4(Q.gptq_pack(q_w, 4, K, N), qzeros, s, None, gs), w_ref.t().contiguous())
+    w_ref, q_w, s, zp = Q.quantize_weights(w, scalar_types.uint4, gs, zero_points=True)
+    out = G.dequantize_awq_q4(Q.awq_pack(q_w, 4, K, N), Q.awq_pack(zp.to(torch.int32), 4, K // gs, N), s, gs)
+    assert torch.allclose(out, w_ref.t(), atol=1e-6)
