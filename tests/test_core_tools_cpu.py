@@ -222,3 +222,55 @@ def test_ml_metrics_match_scikit_learn():
     t, q = rng.standard_normal(300), rng.standard_normal(300)
     assert abs(ml.r2_score(t, q) - skm.r2_score(t, q)) < 1e-9 and abs(ml.mean_squared_error(t, q) - skm.mean_squared_error(t, q)) < 1e-12
     assert abs(ml.mean_absolute_error(t, q) - skm.mean_absolute_error(t, q)) < 1e-12
+
+
+def test_json_grammar_agrees_with_the_jsonschema_validator():
+    """Random documents, valid and broken in five ways, serialised with both separator styles: the incremental grammar accepts exactly those
+    the ``jsonschema`` validator accepts, and every prefix of an accepted document is an accepted prefix."""
+    import json
+    import random
+    jsonschema = pytest.importorskip("jsonschema")
+    from ferrotorch_b200 import grammar as G
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"}, "tags": {"type": "array", "items": {"type": "string"}},
+                                               "ok": {"type": "boolean"}, "score": {"type": "number"}, "kind": {"enum": ["a", "b"]},
+                                               "inner": {"type": "object", "properties": {"x": {"type": "number"}}, "required": ["x"]}},
+              "required": ["name", "age"]}
+    g = G.JsonGrammar(G.Schema.from_json(schema))
+    rnd = random.Random(0)
+
+    def instance(valid):
+        d = {"name": rnd.choice(["bob", "ali ce", "é\\"q\\\\"]), "age": rnd.randint(-5, 99)}
+        if rnd.random() < .5:
+            d["tags"] = [rnd.choice(["x", "y z"]) for _ in range(rnd.randint(0, 3))]
+        if rnd.random() < .5:
+            d["ok"] = rnd.random() < .5
+        if rnd.random() < .5:
+            d["score"] = rnd.choice([1.5, -2e-3, 7, 0.0])
+        if rnd.random() < .5:
+            d["kind"] = rnd.choice(["a", "b"])
+        if rnd.random() < .5:
+            d["inner"] = {"x": rnd.random()}
+        if not valid:
+            k = rnd.choice(["age_str", "missing", "bad_enum", "bad_item", "inner_missing"])
+            if k == "age_str":
+                d["age"] = "12"
+            elif k == "missing":
+                d.pop("name")
+            elif k == "bad_enum":
+                d["kind"] = "c"
+            elif k == "bad_item":
+                d["tags"] = [1]
+            else:
+                d["inner"] = {}
+        return d
+    for i in range(300):
+        inst = instance(i % 2 == 0)
+        text = json.dumps(inst, ensure_ascii=False) if i % 4 < 2 else json.dumps(inst, separators=(",", ":"))
+        try:
+            jsonschema.validate(inst, schema)
+            ok = True
+        except jsonschema.ValidationError:
+            ok = False
+        assert g.is_complete(text) == ok, text
+        if ok:
+            assert all(g.accepts_prefix(text[:k]) for k in range(0, len(text) + 1, 3)), text
