@@ -197,7 +197,10 @@ class VisionNormalize:
 
 
 class Resize:
-    def __init__(self, size, mode="bilinear"):
+    """Resize a ``[C, H, W]`` image. The default is the reference's rule, nearest neighbour with source index ``floor(dst * in / out)``
+    (ferrotorch-vision/src/transforms/resize.rs:44-52); ``mode="bilinear"`` / ``"bicubic"`` are extensions."""
+
+    def __init__(self, size, mode="nearest"):
         self.size, self.mode = (size, size) if isinstance(size, int) else tuple(size), mode
 
     def __call__(self, x):
@@ -211,7 +214,9 @@ class CenterCrop:
     def __call__(self, x):
         h, w = x.shape[-2:]
         th, tw = self.size
-        i, j = max((h - th) // 2, 0), max((w - tw) // 2, 0)
+        if th > h or tw > w:               # ferrotorch-vision/src/transforms/center_crop.rs:43-49
+            raise InvalidArgument(f"CenterCrop: crop size ({th}x{tw}) is larger than input spatial size ({h}x{w})")
+        i, j = (h - th) // 2, (w - tw) // 2
         return x[..., i: i + th, j: j + tw]
 
 

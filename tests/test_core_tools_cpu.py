@@ -274,3 +274,17 @@ def test_json_grammar_agrees_with_the_jsonschema_validator():
         assert g.is_complete(text) == ok, text
         if ok:
             assert all(g.accepts_prefix(text[:k]) for k in range(0, len(text) + 1, 3)), text
+
+
+def test_resize_and_center_crop_follow_the_reference_rules():
+    """Resize defaults to nearest neighbour with source index floor(dst * in / out); CenterCrop floors its offsets and refuses a crop larger
+    than the image (ferrotorch-vision/src/transforms/resize.rs:44-52, center_crop.rs:43-53)."""
+    from ferrotorch_b200.errors import InvalidArgument
+    from ferrotorch_b200.vision import data as VD
+    x = torch.arange(3 * 5 * 7.0).view(3, 5, 7)
+    want = torch.stack([torch.stack([x[c, (oh * 5) // 3, [(ow * 7) // 4 for ow in range(4)]] for oh in range(3)]) for c in range(3)])
+    assert torch.equal(VD.Resize((3, 4))(x), want)
+    assert VD.Resize((3, 4), mode="bilinear")(x).shape == (3, 3, 4)
+    assert torch.equal(VD.CenterCrop((2, 4))(x), x[:, 1:3, 1:5])
+    with pytest.raises(InvalidArgument):
+        VD.CenterCrop(9)(x)
