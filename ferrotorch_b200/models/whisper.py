@@ -9,14 +9,18 @@ import json
 import math
 import os
 from dataclasses import dataclass
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 import torch.nn.functional as F
 
 from .. import nn
+from ..errors import InvalidArgument, ShapeMismatch
+from .bert import DropReport
 
 SAMPLE_RATE, N_FFT, HOP_LENGTH, CHUNK_SECONDS = 16000, 400, 160, 30
+# ferrotorch-whisper/src/audio.rs:34-49
+CHUNK_LENGTH, N_MELS, N_FRAMES, N_SAMPLES, N_FREQS = CHUNK_SECONDS, 80, 3000, CHUNK_SECONDS * SAMPLE_RATE, N_FFT // 2 + 1
 
 
 @dataclass
@@ -34,8 +38,72 @@ class WhisperConfig:
     def base(cls): return cls(d_model=512, encoder_layers=6, encoder_attention_heads=8, encoder_ffn_dim=2048)
     @classmethod
     def small(cls): return cls(d_model=768, encoder_layers=12, encoder_attention_heads=12, encoder_ffn_dim=3072)
+    whisper_tiny = tiny                                  # ferrotorch-whisper/src/config.rs:52
+
     @classmethod
-    def from_hf(cls, d: Dict): return cls(**{k: d[k] for k in cls.__dataclass_fields__ if k in d})
+    def from_hf(cls, d):
+        if isinstance(d, HfWhisperConfig):
+            d.validate()
+            d = d.__dict__
+        c = cls(**{k: d[k] for k in cls.__dataclass_fields__ if k in d})
+        c.validate()
+        return c
+
+    def encoder_head_dim(self) -> int:
+        return self.d_model // self.encoder_attention_heads
+
+    def validate(self) -> None:
+        """ferrotorch-whisper/src/config.rs:104-129."""
+        if min(self.num_mel_bins, self.d_model, self.encoder_layers, self.encoder_attention_heads, self.encoder_ffn_dim, self.max_source_positions) <= 0:
+            raise InvalidArgument("WhisperConfig: num_mel_bins / d_model / encoder_layers / encoder_attention_heads / encoder_ffn_dim / "
+                                  "max_source_positions must all be positive")
+        if self.d_model % self.encoder_attention_heads:
+            raise InvalidArgument(f"WhisperConfig: d_model ({self.d_model}) must be divisible by encoder_attention_heads ({self.encoder_attention_heads})")
+
+
+@dataclass
+class HfWhisperConfig:
+    """The fields of a Hugging Face Whisper ``config.json`` (ferrotorch-whisper/src/config.rs:137-236); the decoder sizes are carried but only
+    the encoder is built here."""
+    vocab_size: int
+    num_mel_bins: int
+    d_model: int
+    encoder_layers: int
+    encoder_attention_heads: int
+    encoder_ffn_dim: int
+    decoder_layers: int
+    decoder_attention_heads: int
+    decoder_ffn_dim: int
+    max_source_positions: int
+    max_target_positions: int
+    activation_function: str = "gelu"
+    architectures: tuple = ()
+    model_type: Optional[str] = None
+
+    @classmethod
+    def from_json_str(cls, s: str) -> "HfWhisperConfig":
+        try:
+            d = json.loads(s)
+            return cls(**{k: (tuple(d[k]) if k == "architectures" else d[k]) for k in cls.__dataclass_fields__ if k in d})
+        except (ValueError, TypeError) as e:
+            raise InvalidArgument(f"failed to parse Whisper config JSON: {e}") from None
+
+    @classmethod
+    def from_file(cls, path) -> "HfWhisperConfig":
+        try:
+            text = open(path, "rb").read().decode("utf-8")
+        except (OSError, UnicodeDecodeError) as e:
+            raise InvalidArgument(f"failed to read config file {path}: {e}") from None
+        return cls.from_json_str(text)
+
+    def validate(self) -> None:
+        if min(self.vocab_size, self.num_mel_bins, self.d_model, self.encoder_layers, self.encoder_attention_heads, self.encoder_ffn_dim,
+               self.max_source_positions) <= 0:
+            raise InvalidArgument("HfWhisperConfig: sizes must all be positive")
+        if self.d_model % self.encoder_attention_heads:
+            raise InvalidArgument(f"HfWhisperConfig: d_model ({self.d_model}) must be divisible by encoder_attention_heads ({self.encoder_attention_heads})")
+        if self.activation_function != "gelu":
+            raise InvalidArgument(f"HfWhisperConfig: unsupported activation_function {self.activation_function!r}")
 
 
 def _hz_to_mel(f):
@@ -96,7 +164,9 @@ class WhisperConvStem(nn.Module):
         return F.gelu(self.conv2(F.gelu(self.conv1(mel)))).transpose(1, 2)
 
 
-class _WhisperAttention(nn.Module):
+class WhisperEncoderSelfAttention(nn.Module):
+    """Bidirectional self-attention with Whisper's bias-free key projection (ferrotorch-whisper/src/attention.rs:37)."""
+
     def __init__(self, c):
         super().__init__()
         self.h = c.encoder_attention_heads
@@ -113,7 +183,7 @@ class _WhisperAttention(nn.Module):
 class WhisperEncoderLayer(nn.Module):
     def __init__(self, c: WhisperConfig):
         super().__init__()
-        self.self_attn = _WhisperAttention(c)
+        self.self_attn = WhisperEncoderSelfAttention(c)
         self.self_attn_layer_norm, self.final_layer_norm = nn.LayerNorm(c.d_model), nn.LayerNorm(c.d_model)
         self.fc1, self.fc2 = nn.Linear(c.d_model, c.encoder_ffn_dim), nn.Linear(c.encoder_ffn_dim, c.d_model)
 
@@ -141,12 +211,41 @@ class WhisperEncoder(nn.Module):
             x = l(x)
         return self.layer_norm(x)
 
+    forward_from_mel = forward
 
-def load_whisper_encoder(path: str, device="cpu", dtype=torch.float32) -> WhisperEncoder:
+    def load_hf_state_dict(self, hf_state: Dict[str, torch.Tensor], strict: bool = True) -> DropReport:
+        """Takes the ``encoder.*`` / ``model.encoder.*`` keys of a Hugging Face checkpoint; every other key (decoder, ``proj_out``) is refused
+        under ``strict`` and otherwise listed in the report (ferrotorch-whisper/src/encoder.rs:257-290)."""
+        own, keep, dropped = self.state_dict(), {}, []
+        for k, v in hf_state.items():
+            rest = k[8:] if k.startswith("encoder.") else (k[14:] if k.startswith("model.encoder.") else None)
+            if rest is None:
+                if strict:
+                    raise InvalidArgument(f"WhisperEncoder.load_hf_state_dict: key {k!r} is not under `encoder.*` or `model.encoder.*`; "
+                                          "pass strict=False to drop decoder / proj_out keys")
+                dropped.append(k)
+            elif rest in own:
+                if tuple(v.shape) != tuple(own[rest].shape):
+                    raise ShapeMismatch(f"{rest}: checkpoint {tuple(v.shape)} vs model {tuple(own[rest].shape)}")
+                keep[rest] = v
+            elif strict:
+                raise InvalidArgument(f'unexpected key in WhisperEncoder state_dict: "{rest}"')
+        if strict and len(keep) != len(own):
+            raise InvalidArgument(f"WhisperEncoder.load_hf_state_dict: missing keys {[k for k in own if k not in keep][:4]}")
+        self.load_state_dict(keep, strict=False)
+        return DropReport(dropped=tuple(sorted(dropped)))
+
+
+def load_whisper_encoder(path: str, cfg: Optional[WhisperConfig] = None, strict: bool = False, device="cpu", dtype=torch.float32):
+    """``load_whisper_encoder(directory)`` reads ``config.json`` + ``model.safetensors`` and returns the encoder;
+    ``load_whisper_encoder(weights_file, cfg, strict)`` is the reference's form and also returns the :class:`DropReport`
+    (ferrotorch-whisper/src/safetensors_loader.rs:31)."""
     from ..serialize import load_safetensors
-    cfg = WhisperConfig.from_hf(json.load(open(os.path.join(path, "config.json"))))
-    sd = load_safetensors(os.path.join(path, "model.safetensors"))
-    pre = "model.encoder."
+    if cfg is None:
+        cfg = WhisperConfig.from_hf(json.load(open(os.path.join(path, "config.json"))))
+        m = WhisperEncoder(cfg)
+        m.load_hf_state_dict(load_safetensors(os.path.join(path, "model.safetensors")), strict=False)
+        return m.to(device=device, dtype=dtype)
     m = WhisperEncoder(cfg)
-    m.load_state_dict({k[len(pre):]: v for k, v in sd.items() if k.startswith(pre)}, strict=False)
-    return m.to(device=device, dtype=dtype)
+    report = m.load_hf_state_dict(load_safetensors(str(path)), strict=strict)
+    return m.to(device=device, dtype=dtype), report

@@ -7,7 +7,7 @@ from .ops import (box_convert, box_area, box_iou, generalized_box_iou, distance_
                   nms, batched_nms, sigmoid_focal_loss, focal_loss, roi_align, roi_pool)
 from .data import (read_image, write_image, Mnist, Cifar10, Cifar100, DatasetFolder, ImageFolder, Compose, ToTensor, VisionNormalize, Resize,
                    CenterCrop, RandomCrop, RandomHorizontalFlip, RandomVerticalFlip, RandomResizedCrop, RandomRotation, ColorJitter, GaussianNoise,
-                   RandomGaussianBlur, RandomApply, ElasticTransform, TrivialAugmentWide)
+                   RandomGaussianBlur, RandomApply, RandomChoice, ElasticTransform, TrivialAugmentWide, VisionToTensor, vision_manual_seed)
 from . import models2, segmentation, detection  # noqa: E402
 from .models2 import MobileNetV3, MobileNetV3Small, MobileNetV3Large, mobilenet_v3_small, mobilenet_v3_large, InceptionV3, inception_v3, SwinTransformer, swin_tiny  # noqa: E402
 from .segmentation import Fcn, DeepLabV3, Lraspp, Aspp, fcn_resnet50, deeplabv3_resnet50, lraspp_mobilenet_v3_large  # noqa: E402

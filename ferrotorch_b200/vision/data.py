@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import gzip
 import math
+import threading
 import os
 import pickle
 import struct
@@ -169,6 +170,50 @@ class ImageFolder(DatasetFolder):
 
 
 # -- transforms (operate on [C,H,W] tensors) ----------------------------------------------------------------------------------------------------
+# -- random source of the augmentation transforms ---------------------------------------------------------------------------------------
+class _VisionRng:
+    """Counter-based splitmix64 stream with its own seed (default 42), separate from the tensor RNGs so that augmentation can be replayed on
+    its own: draw number n after ``vision_manual_seed(s)`` is a pure function of (s, n), as in
+    ferrotorch-vision/src/transforms/rng.rs:17-47 (same mixing constants, same mapping to [0, 1])."""
+    _M = (1 << 64) - 1
+
+    def __init__(self):
+        self.seed, self.draw = 42, 0
+        self._lock = threading.Lock()
+
+    def manual_seed(self, seed: int) -> None:
+        with self._lock:
+            self.seed, self.draw = int(seed) & self._M, 0
+
+    def random(self) -> float:
+        with self._lock:
+            d = self.draw
+            self.draw += 1
+        z = (self.seed + d * 0x9E3779B97F4A7C15) & self._M
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & self._M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & self._M
+        z ^= z >> 31
+        return z / float(self._M)
+
+    def uniform(self, lo: float, hi: float) -> float:
+        return lo + (hi - lo) * self.random()
+
+    def randint(self, upper: int) -> int:                # rng.rs:45-47
+        return int(self.random() * upper) % upper
+
+    def generator(self) -> torch.Generator:
+        """A torch generator keyed by the next draw, for transforms that need whole random tensors (noise, displacement fields)."""
+        return torch.Generator().manual_seed(int(self.random() * (1 << 62)))
+
+
+_vision_rng = _VisionRng()
+
+
+def vision_manual_seed(seed: int) -> None:
+    """Seed the augmentation stream (ferrotorch-vision/src/transforms/rng.rs:24-30)."""
+    _vision_rng.manual_seed(seed)
+
+
 class Compose:
     def __init__(self, ts):
         self.ts = list(ts)
@@ -186,6 +231,18 @@ class ToTensor:
             if x.dim() == 3 and x.shape[-1] in (1, 3, 4):
                 x = x.permute(2, 0, 1)
         return x.float().div(255) if x.dtype == torch.uint8 else x.float()
+
+
+class VisionToTensor:
+    """``[H, W, C]`` image with values in 0..255 (any dtype) -> float ``[C, H, W]`` in 0..1: always transposes and always divides by 255, as
+    ferrotorch-vision/src/transforms/to_tensor.rs:24-57 does (:class:`ToTensor` only rescales 8-bit input)."""
+
+    def __call__(self, x):
+        if isinstance(x, np.ndarray):
+            x = torch.from_numpy(x)
+        if x.dim() != 3:
+            raise InvalidArgument(f"VisionToTensor: expected 3-D tensor [H, W, C], got shape {list(x.shape)}")
+        return x.permute(2, 0, 1).float().div(255).contiguous()
 
 
 class VisionNormalize:
@@ -229,7 +286,7 @@ class RandomCrop:
             x = F.pad(x, [self.padding] * 4)
         h, w = x.shape[-2:]
         th, tw = self.size
-        i, j = int(torch.randint(0, h - th + 1, (1,))), int(torch.randint(0, w - tw + 1, (1,)))
+        i, j = _vision_rng.randint(h - th + 1), _vision_rng.randint(w - tw + 1)
         return x[..., i: i + th, j: j + tw]
 
 
@@ -238,12 +295,12 @@ class RandomHorizontalFlip:
         self.p = p
 
     def __call__(self, x):
-        return x.flip(-1) if torch.rand(1).item() < self.p else x
+        return x.flip(-1) if _vision_rng.random() < self.p else x
 
 
 class RandomVerticalFlip(RandomHorizontalFlip):
     def __call__(self, x):
-        return x.flip(-2) if torch.rand(1).item() < self.p else x
+        return x.flip(-2) if _vision_rng.random() < self.p else x
 
 
 class RandomResizedCrop:
@@ -253,11 +310,11 @@ class RandomResizedCrop:
     def __call__(self, x):
         h, w = x.shape[-2:]
         for _ in range(10):
-            area = h * w * float(torch.empty(1).uniform_(*self.scale))
-            r = math.exp(float(torch.empty(1).uniform_(math.log(self.ratio[0]), math.log(self.ratio[1]))))
+            area = h * w * _vision_rng.uniform(*self.scale)
+            r = math.exp(_vision_rng.uniform(math.log(self.ratio[0]), math.log(self.ratio[1])))
             cw, ch = int(round(math.sqrt(area * r))), int(round(math.sqrt(area / r)))
             if 0 < cw <= w and 0 < ch <= h:
-                i, j = int(torch.randint(0, h - ch + 1, (1,))), int(torch.randint(0, w - cw + 1, (1,)))
+                i, j = _vision_rng.randint(h - ch + 1), _vision_rng.randint(w - cw + 1)
                 return Resize(self.size)(x[..., i: i + ch, j: j + cw])
         return Resize(self.size)(CenterCrop(min(h, w))(x))
 
@@ -267,7 +324,7 @@ class RandomRotation:
         self.degrees = degrees
 
     def __call__(self, x):
-        a = math.radians(float(torch.empty(1).uniform_(-self.degrees, self.degrees)))
+        a = math.radians(_vision_rng.uniform(-self.degrees, self.degrees))
         theta = torch.tensor([[math.cos(a), -math.sin(a), 0.0], [math.sin(a), math.cos(a), 0.0]]).unsqueeze(0)
         grid = F.affine_grid(theta, [1, *x.shape], align_corners=False)
         return F.grid_sample(x.unsqueeze(0).float(), grid, align_corners=False).squeeze(0)
@@ -279,13 +336,13 @@ class ColorJitter:
 
     def __call__(self, x):
         if self.b:
-            x = x * float(torch.empty(1).uniform_(max(0, 1 - self.b), 1 + self.b))
+            x = x * _vision_rng.uniform(max(0, 1 - self.b), 1 + self.b)
         if self.c:
             m = x.mean()
-            x = (x - m) * float(torch.empty(1).uniform_(max(0, 1 - self.c), 1 + self.c)) + m
+            x = (x - m) * _vision_rng.uniform(max(0, 1 - self.c), 1 + self.c) + m
         if self.s and x.shape[0] == 3:
             g = (0.299 * x[0] + 0.587 * x[1] + 0.114 * x[2]).unsqueeze(0)
-            x = (x - g) * float(torch.empty(1).uniform_(max(0, 1 - self.s), 1 + self.s)) + g
+            x = (x - g) * _vision_rng.uniform(max(0, 1 - self.s), 1 + self.s) + g
         return x.clamp(0, 1)
 
 
@@ -294,7 +351,7 @@ class GaussianNoise:
         self.std = std
 
     def __call__(self, x):
-        return x + self.std * torch.randn_like(x)
+        return x + self.std * torch.randn(x.shape, generator=_vision_rng.generator()).to(x)
 
 
 class RandomGaussianBlur:
@@ -302,9 +359,9 @@ class RandomGaussianBlur:
         self.k, self.sigma, self.p = kernel_size, sigma, p
 
     def __call__(self, x):
-        if torch.rand(1).item() >= self.p:
+        if _vision_rng.random() >= self.p:
             return x
-        s = float(torch.empty(1).uniform_(*self.sigma))
+        s = _vision_rng.uniform(*self.sigma)
         ax = torch.arange(self.k, dtype=torch.float32) - (self.k - 1) / 2
         k1 = torch.exp(-ax ** 2 / (2 * s * s))
         k1 = k1 / k1.sum()
@@ -318,7 +375,19 @@ class RandomApply:
         self.t, self.p = Compose(ts), p
 
     def __call__(self, x):
-        return self.t(x) if torch.rand(1).item() < self.p else x
+        return self.t(x) if _vision_rng.random() < self.p else x
+
+
+class RandomChoice:
+    """Applies exactly one of the given transforms, picked uniformly (ferrotorch-vision/src/transforms/random_apply.rs:35-57)."""
+
+    def __init__(self, ts):
+        if not ts:
+            raise InvalidArgument("RandomChoice: transforms list must not be empty")
+        self.ts = list(ts)
+
+    def __call__(self, x):
+        return self.ts[min(int(_vision_rng.random() * len(self.ts)), len(self.ts) - 1)](x)
 
 
 class ElasticTransform:
@@ -327,7 +396,7 @@ class ElasticTransform:
 
     def __call__(self, x):
         c, h, w = x.shape
-        d = torch.randn(1, 2, h, w)
+        d = torch.randn(1, 2, h, w, generator=_vision_rng.generator())
         k = int(2 * round(3 * self.sigma) + 1)
         ax = torch.arange(k, dtype=torch.float32) - (k - 1) / 2
         g = torch.exp(-ax ** 2 / (2 * self.sigma ** 2))
@@ -348,5 +417,5 @@ class TrivialAugmentWide:
                     lambda x, m: (x > m).to(x) * x + (x <= m).to(x) * (1 - x)]
 
     def __call__(self, x):
-        i = int(torch.randint(0, len(self.ops), (1,)))
-        return self.ops[i](x, float(torch.rand(1)))
+        i = _vision_rng.randint(len(self.ops))
+        return self.ops[i](x, _vision_rng.random())

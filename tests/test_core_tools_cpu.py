@@ -288,3 +288,53 @@ def test_resize_and_center_crop_follow_the_reference_rules():
     assert torch.equal(VD.CenterCrop((2, 4))(x), x[:, 1:3, 1:5])
     with pytest.raises(InvalidArgument):
         VD.CenterCrop(9)(x)
+
+
+def test_vision_rng_choice_and_to_tensor():
+    """The augmentation stream is a splitmix64 counter keyed by (seed, draw) with default seed 42 (ferrotorch-vision/src/transforms/rng.rs:17-47);
+    RandomChoice applies exactly one transform; VisionToTensor transposes [H, W, C] and always divides by 255 (to_tensor.rs:24-57)."""
+    from ferrotorch_b200.errors import InvalidArgument
+    from ferrotorch_b200 import vision as V
+    from ferrotorch_b200.vision import data as VD
+
+    def splitmix(seed, n):                                   # the published splitmix64 finaliser, written out independently
+        m = (1 << 64) - 1
+        z = (seed + n * 0x9E3779B97F4A7C15) & m
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        return (z ^ (z >> 31)) / float(m)
+
+    V.vision_manual_seed(7)
+    a = [VD._vision_rng.random() for _ in range(5)]
+    assert a == [splitmix(7, n) for n in range(5)] and all(0.0 <= v <= 1.0 for v in a)
+    V.vision_manual_seed(7)
+    assert [VD._vision_rng.random() for _ in range(5)] == a
+    V.vision_manual_seed(8)
+    assert [VD._vision_rng.random() for _ in range(5)] != a
+    assert all(0 <= VD._vision_rng.randint(3) < 3 for _ in range(50))
+
+    x = torch.rand(3, 16, 16)
+    aug = V.Compose([V.RandomCrop(8), V.RandomHorizontalFlip(), V.ColorJitter(0.3, 0.3, 0.3), V.GaussianNoise(0.1)])
+    V.vision_manual_seed(3)
+    y1 = aug(x)
+    torch.manual_seed(999)                                  # the tensor RNG does not feed the augmentations
+    V.vision_manual_seed(3)
+    assert torch.equal(aug(x), y1)
+
+    with pytest.raises(InvalidArgument):
+        V.RandomChoice([])
+    hits = [0, 0, 0]
+    rc = V.RandomChoice([lambda t, i=i: (hits.__setitem__(i, hits[i] + 1), t + i)[1] for i in range(3)])
+    V.vision_manual_seed(0)
+    outs = [float(rc(torch.zeros(1))) for _ in range(300)]
+    assert sum(hits) == 300 and min(hits) > 60 and set(outs) == {0.0, 1.0, 2.0}
+    V.vision_manual_seed(0)
+    want = [min(int(splitmix(0, n) * 3), 2) for n in range(300)]
+    assert [int(o) for o in outs] == want
+
+    img = torch.arange(4 * 5 * 3.0).view(4, 5, 3)
+    t = V.VisionToTensor()(img)
+    assert t.shape == (3, 4, 5) and torch.allclose(t, img.permute(2, 0, 1) / 255)
+    assert V.VisionToTensor()(np.full((2, 2, 3), 255, np.uint8)).max() == 1.0
+    with pytest.raises(InvalidArgument):
+        V.VisionToTensor()(torch.zeros(4, 5))
