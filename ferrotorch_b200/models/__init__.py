@@ -7,8 +7,15 @@ from .bert import (BertConfig, HfBertConfig, BertModel, BertEmbeddings, BertSelf
                    BertLayer, BertEncoder, BertPooler, DropReport, SentenceTransformer, load_bert_model, load_sentence_transformer)
 from .whisper import (WhisperConfig, HfWhisperConfig, WhisperEncoder, WhisperConvStem, WhisperEncoderLayer, WhisperEncoderSelfAttention,
                       log_mel_spectrogram, load_whisper_encoder, SAMPLE_RATE, N_MELS, N_FRAMES, N_FFT, HOP_LENGTH, CHUNK_LENGTH, N_SAMPLES, N_FREQS)
-from .diffusion import (UNet2DConditionModel, UNetConfig, AutoencoderKL, VaeConfig, VaeEncoder, VaeDecoder, ClipTextEncoder, ClipTextConfig,
-                        DDIMScheduler, StableDiffusionPipeline)
+from .diffusion import (UNet2DConditionModel, UNetConfig, UNet2DConditionConfig, AutoencoderKL, VaeConfig, VaeDecoderConfig, VaeEncoderConfig, VaeEncoder,
+                        VaeDecoder, Encoder, Decoder, DiagonalGaussianDistribution, ClipTextEncoder, ClipTextConfig, ClipTextEmbeddings,
+                        ClipSelfAttention, ClipMlp, ClipEncoderLayer, ClipEncoder, DDIMScheduler, DDIMConfig, BetaSchedule, TimestepSpacing,
+                        PredictionType, StableDiffusionPipeline, PipelineStepDump, Timesteps, TimestepEmbedding, Attention, FeedForward,
+                        BasicTransformerBlock, Transformer2DModel, ResnetBlock2D, ResnetBlock2DTime, AttnBlock2D, Upsample2D, Downsample2D,
+                        UpDecoderBlock2D, DownEncoderBlock2D, UNetMidBlock2D, UNetMidBlock2DCrossAttn, CrossAttnDownBlock2D, DownBlock2D,
+                        CrossAttnUpBlock2D, UpBlock2D, AnyDownBlock, AnyUpBlock, load_unet, load_clip_text_encoder, load_vae_decoder,
+                        load_vae_encoder, load_sd_component, GpuUNet2DConditional, GpuVaeDecoder, GpuVaeEncoder, GpuClipTextEncoder,
+                        GpuStableDiffusionPipeline)
 from .graph import Graph, GcnConv, GcnNet, load_gcn_net
 from .rl import MlpPolicy, MlpPolicyConfig, MlpExtractor, ActionNet, ValueHead, PolicyOutput, load_ppo_policy, ppo_loss
 
