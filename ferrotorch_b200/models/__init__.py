@@ -1,8 +1,13 @@
 """Model zoo: Llama (training, tensor-parallel inference, generation), BERT, Whisper, Stable Diffusion, GCN, RL policies."""
 from . import llama, llama_gen, bert, whisper, diffusion, graph, rl
 from .llama import LlamaConfig, LlamaModel, LlamaForCausalLM, LlamaDecoderLayer
-from .llama_gen import (CachedLlama, KvCache, LayerKvCache, GenerationConfig, generate, beam_search, SpecDecodeConfig, SpecDecodeStats,
-                        speculative_generate, dequantize_gptq_q4, dequantize_awq_q4, dequantize_hqq, gguf_to_hf_name, remap_gguf_state_dict)
+from .llama_gen import (CachedLlama, KvCache, LlamaKvCache, LayerKvCache, GenerationConfig, generate, generate_with_streamer, beam_search, SpecDecodeConfig,
+                        SpecDecodeStats, SpecDecodeOutput, ModelHandle, LlamaHandle, speculative_generate, speculative_decode, XorShift64, apply_temperature,
+                        apply_repetition_penalty, top_k_filter, top_p_filter, argmax, sample_softmax, sample_next, GptqQ4, AwqQ4, HqqWeights,
+                        dequantize_gptq_q4, dequantize_awq_q4, dequantize_hqq, load_quantized_linear_weights, gguf_to_hf_name, gguf_key_to_hf,
+                        remap_gguf_state_dict, gguf_to_hf_state_dict)
+from .llama_blocks import LlamaActivation, LlamaMLP, LlamaAttention, LlamaGpuLayer, LlamaGpuInferencer, ProfiledForwardResult
+from .. import grammar  # noqa: E402  (ferrotorch-llama re-exports the constrained-decoding package)
 from .bert import (BertConfig, HfBertConfig, BertModel, BertEmbeddings, BertSelfAttention, BertSelfOutput, BertAttention, BertIntermediate, BertOutput,
                    BertLayer, BertEncoder, BertPooler, DropReport, SentenceTransformer, load_bert_model, load_sentence_transformer)
 from .whisper import (WhisperConfig, HfWhisperConfig, WhisperEncoder, WhisperConvStem, WhisperEncoderLayer, WhisperEncoderSelfAttention,

@@ -41,11 +41,20 @@ class LlamaConfig:
     max_position_embeddings: int = 8192
     tie_word_embeddings: bool = False
     rope_scaling: Optional[dict] = None
-    hidden_act: str = "silu"
+    hidden_act: str = "silu"                      # silu | swish | relu | fatrelu (ferrotorch-llama/src/config.rs:12-19, 122-141)
+    hidden_act_param: Optional[float] = None      # FATReLU threshold (0.01 when absent)
 
     @property
     def head_dim(self) -> int:
         return self.hidden_size // self.num_attention_heads
+
+    def kv_group_size(self) -> int:
+        return self.num_attention_heads // self.num_key_value_heads
+
+    @property
+    def activation(self):
+        from .llama_blocks import LlamaActivation
+        return LlamaActivation.parse(self.hidden_act, self.hidden_act_param)
 
     # -- presets (ferrotorch-llama/src/config.rs:50-113) ------------------------
     @staticmethod
@@ -89,6 +98,8 @@ class LlamaConfig:
             raise InvalidArgument("head_dim must be even for rotary embeddings")
         if min(self.vocab_size, self.hidden_size, self.intermediate_size, self.num_hidden_layers) <= 0:
             raise InvalidArgument("sizes must be positive")
+        if self.hidden_act not in ("silu", "swish", "relu", "fatrelu"):
+            raise InvalidArgument(f"LlamaConfig: unsupported hidden_act {self.hidden_act!r}")
 
     def num_parameters(self) -> int:
         d, F, V, L = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
@@ -330,6 +341,8 @@ class LlamaModel(torch.nn.Module):
     def __init__(self, cfg: LlamaConfig, device="cuda", world: int = 1, rank: int = 0):
         super().__init__()
         cfg.validate()
+        if cfg.hidden_act not in ("silu", "swish"):
+            raise InvalidArgument(f"the fused training layer implements SwiGLU only; build {cfg.hidden_act!r} models from models.llama_blocks")
         self.cfg = cfg
         d, V = cfg.hidden_size, cfg.vocab_size
         self.embed_unit = FlatUnit("embed_tokens", [("weight", (V, d))], device, torch.bfloat16, world, rank)

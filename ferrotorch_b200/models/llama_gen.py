@@ -16,7 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import ops
-from ..errors import InvalidArgument
+from ..errors import InvalidArgument, ShapeMismatch
 from .llama import LlamaConfig
 
 
@@ -65,6 +65,7 @@ class CachedLlama:
 
     def __init__(self, cfg: LlamaConfig, weights: Dict[str, torch.Tensor]):
         self.cfg, self.W = cfg, weights
+        self.act = cfg.activation
         dev = weights["model.embed_tokens.weight"].device
         self.cos, self.sin = ops.rope_tables(cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta, dev, cfg.rope_scaling)
 
@@ -103,7 +104,7 @@ class CachedLlama:
             a = torch.matmul(torch.softmax(sc, -1), vv.repeat_interleave(rep, 1).float()).to(x.dtype)
             x = x + F.linear(a.transpose(1, 2).reshape(B, S, Hq * D), W[p + "self_attn.o_proj.weight"])
             h2 = self._rms(x, W[p + "post_attention_layernorm.weight"])
-            x = x + F.linear(F.silu(F.linear(h2, W[p + "mlp.gate_proj.weight"])) * F.linear(h2, W[p + "mlp.up_proj.weight"]), W[p + "mlp.down_proj.weight"])
+            x = x + F.linear(self.act(F.linear(h2, W[p + "mlp.gate_proj.weight"])) * F.linear(h2, W[p + "mlp.up_proj.weight"]), W[p + "mlp.down_proj.weight"])
         head = W["model.embed_tokens.weight"] if cfg.tie_word_embeddings else W["lm_head.weight"]
         return F.linear(self._rms(x, W["model.norm.weight"]), head).float()
 
@@ -123,6 +124,23 @@ class GenerationConfig:
     seed: Optional[int] = None
     num_beams: int = 1
     length_penalty: float = 1.0
+    eos_token_ids: List[int] = field(default_factory=list)        # several stop tokens (Llama 3: 128001 and 128009)
+
+    @classmethod
+    def greedy(cls, max_new_tokens: int) -> "GenerationConfig":
+        """ferrotorch-llama/src/generation.rs:67."""
+        return cls(max_new_tokens=max_new_tokens, do_sample=False, temperature=0.0)
+
+    @classmethod
+    def sampling(cls, max_new_tokens: int, temperature: float) -> "GenerationConfig":
+        return cls(max_new_tokens=max_new_tokens, do_sample=temperature > 0.0, temperature=temperature)
+
+    @classmethod
+    def nucleus(cls, max_new_tokens: int, top_p: float, temperature: float) -> "GenerationConfig":
+        return cls(max_new_tokens=max_new_tokens, do_sample=temperature > 0.0, temperature=temperature, top_p=top_p)
+
+    def stop_ids(self) -> List[int]:
+        return list(self.eos_token_ids) + ([self.eos_token_id] if self.eos_token_id is not None else [])
 
     def with_temperature(self, t): self.temperature, self.do_sample = t, True; return self
     def with_top_k(self, k): self.top_k, self.do_sample = k, True; return self
@@ -154,6 +172,62 @@ def top_p_filter(logits: torch.Tensor, p: float) -> torch.Tensor:
     return torch.full_like(logits, float("-inf")).scatter(-1, si, sl)
 
 
+def apply_temperature(logits: torch.Tensor, temperature: float) -> torch.Tensor:
+    """``logits / temperature`` (ferrotorch-llama/src/generation.rs:238)."""
+    return logits * (1.0 / temperature)
+
+
+def argmax(logits) -> int:
+    """Index of the largest logit of one row, the first one on ties (generation.rs:311)."""
+    t = torch.as_tensor(logits).reshape(-1)
+    return int((t == t.max()).nonzero()[0]) if t.numel() and not bool(torch.isnan(t.max())) else 0
+
+
+class XorShift64:
+    """The 13 / 7 / 17 xorshift generator that drives the reference's samplers (generation.rs:581, spec_decode.rs:497); a run with the same
+    seed draws the same uniforms in the same order."""
+    DEFAULT_SEED = 0xDEADBEEFCAFEBABE
+    _M = (1 << 64) - 1
+
+    def __init__(self, seed: Optional[int] = None):
+        self.state = (self.DEFAULT_SEED if seed is None else int(seed)) & self._M
+        if self.state == 0:
+            raise InvalidArgument("XorShift64: the seed must be non-zero")
+
+    def next_u64(self) -> int:
+        x = self.state
+        x ^= (x << 13) & self._M
+        x ^= x >> 7
+        x ^= (x << 17) & self._M
+        self.state = x
+        return x
+
+    def uniform(self) -> float:
+        return self.next_u64() / float(self._M)
+
+
+def _softmax64(logits) -> torch.Tensor:
+    t = torch.as_tensor(logits).reshape(-1).to(torch.float64)
+    m = t.max()
+    if not bool(torch.isfinite(m)):
+        return torch.zeros_like(t)
+    e = (t - m).exp()
+    return e / e.sum()
+
+
+def _sample_weights(w: torch.Tensor, rng: XorShift64, fallback) -> int:
+    total = float(w.sum())
+    if not (total > 0.0 and math.isfinite(total)):
+        return fallback()
+    u = rng.uniform() * total
+    return min(int(torch.searchsorted(w.cumsum(0), torch.tensor(u, dtype=w.dtype))), w.numel() - 1)      # first i with u <= cum[i]
+
+
+def sample_softmax(logits, rng: XorShift64) -> int:
+    """One draw from ``softmax(logits)`` by inverse CDF in f64; when every logit is ``-inf`` the argmax is returned (generation.rs:324)."""
+    return _sample_weights(_softmax64(logits), rng, lambda: argmax(logits))
+
+
 def sample_next(logits: torch.Tensor, seq: torch.Tensor, cfg: GenerationConfig, gen: Optional[torch.Generator] = None) -> torch.Tensor:
     logits = apply_repetition_penalty(logits, seq, cfg.repetition_penalty)
     if not cfg.do_sample:
@@ -178,17 +252,19 @@ def generate(model: Callable[[torch.Tensor, KvCache], torch.Tensor], new_cache: 
     seq = ids
     logits = model(ids, cache)[:, -1]
     done = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+    stops = cfg.stop_ids()
+    stop_t = torch.tensor(stops, dtype=torch.long, device=ids.device)
     for _ in range(cfg.max_new_tokens):
         if logits_processor is not None:
             logits = logits_processor(logits, seq)
         nxt = sample_next(logits, seq, cfg, gen)
-        if cfg.eos_token_id is not None:
-            nxt = torch.where(done, torch.full_like(nxt, cfg.eos_token_id), nxt)
-            done |= nxt == cfg.eos_token_id
+        if stops:
+            nxt = torch.where(done, torch.full_like(nxt, stops[0]), nxt)
+            done |= torch.isin(nxt, stop_t)
         seq = torch.cat([seq, nxt[:, None]], 1)
         if streamer is not None:
             streamer(nxt)
-        if cfg.eos_token_id is not None and bool(done.all()):
+        if stops and bool(done.all()):
             break
         logits = model(nxt[:, None], cache)[:, -1]
     return seq
@@ -230,6 +306,51 @@ def beam_search(model, new_cache, ids: torch.Tensor, cfg: GenerationConfig) -> t
     return max(finished, key=lambda t: t[0])[1][None]
 
 
+@torch.no_grad()
+def generate_with_streamer(model, prompt_ids: Sequence[int], config: GenerationConfig, streamer: Callable[[int], bool],
+                           new_cache: Optional[Callable[[], "KvCache"]] = None) -> List[int]:
+    """Single-prompt generation in the reference's form (ferrotorch-llama/src/generation.rs:145-232): returns the new tokens only, the stop
+    token included; ``streamer(token)`` sees every token as it is chosen and ends the run by returning ``False``. ``temperature == 0`` is greedy;
+    otherwise repetition penalty, temperature, top-k, top-p, then an inverse-CDF draw in f64 from :class:`XorShift64` seeded by
+    ``config.seed``, so a (prompt, config) pair always gives the same tokens. ``model(ids, cache)`` returns ``[1, S, vocab]`` logits and keeps
+    its KV cache, so each step feeds one token instead of the whole prefix."""
+    if len(prompt_ids) == 0:
+        raise InvalidArgument("generate: prompt_ids must not be empty")
+    if config.temperature < 0.0:
+        raise InvalidArgument(f"generate: temperature must be >= 0, got {config.temperature}")
+    if not 0.0 <= config.top_p <= 1.0:
+        raise InvalidArgument(f"generate: top_p must be in [0, 1], got {config.top_p}")
+    if config.repetition_penalty <= 0.0:
+        raise InvalidArgument(f"generate: repetition_penalty must be > 0, got {config.repetition_penalty}")
+    cache = (new_cache or model.new_cache)()
+    dev = getattr(model, "W", {}).get("model.embed_tokens.weight").device if hasattr(model, "W") else "cpu"
+    rng = XorShift64(config.seed)
+    ids, produced, stops = list(int(t) for t in prompt_ids), [], set(config.stop_ids())
+    feed = ids
+    greedy = config.temperature == 0.0 or not config.do_sample
+    for _ in range(config.max_new_tokens):
+        out = model(torch.tensor([feed], dtype=torch.long, device=dev), cache)
+        if out.dim() != 3:
+            raise InvalidArgument(f"generate: expected logits shape [1, S, V], got {list(out.shape)}")
+        logits = out[0, -1].to(torch.float64).cpu()
+        if abs(config.repetition_penalty - 1.0) > 2.3e-16:
+            seen = torch.tensor([t for t in set(ids) if t < logits.numel()], dtype=torch.long)
+            g = logits[seen]
+            logits[seen] = torch.where(g > 0, g / config.repetition_penalty, g * config.repetition_penalty)
+        if greedy:
+            nxt = argmax(logits)
+        else:
+            logits = apply_temperature(logits, config.temperature)
+            logits = top_p_filter(top_k_filter(logits[None], config.top_k), config.top_p)[0]
+            nxt = sample_softmax(logits, rng)
+        produced.append(nxt)
+        if not streamer(nxt) or nxt in stops:
+            break
+        ids.append(nxt)
+        feed = [nxt]
+    return produced
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # speculative decoding
 # ----------------------------------------------------------------------------------------------------------------------
@@ -238,6 +359,144 @@ class SpecDecodeConfig:
     num_draft_tokens: int = 4
     max_new_tokens: int = 64
     eos_token_id: Optional[int] = None
+    draft_k: Optional[int] = None                                  # the reference's name for ``num_draft_tokens`` (spec_decode.rs:167)
+    seed: Optional[int] = None
+    eos_token_ids: List[int] = field(default_factory=list)
+
+    def __post_init__(self):
+        if self.draft_k is None:
+            self.draft_k = self.num_draft_tokens
+        else:
+            self.num_draft_tokens = self.draft_k
+
+    def validate(self) -> None:
+        if self.draft_k < 1:
+            raise InvalidArgument("SpecDecodeConfig: draft_k must be >= 1")
+        if self.max_new_tokens < 1:
+            raise InvalidArgument("SpecDecodeConfig: max_new_tokens must be >= 1")
+
+    def stop_ids(self) -> List[int]:
+        return list(self.eos_token_ids) + ([self.eos_token_id] if self.eos_token_id is not None else [])
+
+
+@dataclass
+class SpecDecodeOutput:
+    """New tokens (prompt excluded) and the draft-token bookkeeping of one run (spec_decode.rs:218)."""
+    tokens: List[int]
+    accepted_count: int
+    proposed_count: int
+
+    def acceptance_rate(self) -> float:
+        return 1.0 if self.proposed_count == 0 else self.accepted_count / self.proposed_count
+
+
+class ModelHandle:
+    """What speculative decoding needs from a model (spec_decode.rs:42): last-position logits for a token list, per-position logits for the
+    verify pass (the default loops over prefixes; real handles override it with one forward), and the vocabulary size."""
+
+    def forward_ids(self, ids: Sequence[int]) -> torch.Tensor:
+        raise NotImplementedError
+
+    def forward_ids_all_positions(self, ids: Sequence[int]) -> torch.Tensor:
+        return torch.stack([self.forward_ids(ids[:j]) for j in range(1, len(ids) + 1)])
+
+    def vocab_size(self) -> int:
+        raise NotImplementedError
+
+
+class LlamaHandle(ModelHandle):
+    """:class:`ModelHandle` over a cached decoder ``model(ids, cache) -> [1, S, vocab]`` (spec_decode.rs:101). ``forward_ids`` keeps one KV cache
+    and re-feeds only the tokens after the longest prefix it has already seen, so drafting K tokens costs K single-token steps."""
+
+    def __init__(self, model, new_cache: Optional[Callable[[], "KvCache"]] = None, vocab_size: Optional[int] = None):
+        self.model, self._new_cache = model, new_cache or model.new_cache
+        self._vocab = vocab_size if vocab_size is not None else model.cfg.vocab_size
+        self._dev = model.W["model.embed_tokens.weight"].device if hasattr(model, "W") else "cpu"
+        self._seen: List[int] = []
+        self._cache = None
+
+    def vocab_size(self) -> int:
+        return self._vocab
+
+    @torch.no_grad()
+    def forward_ids(self, ids: Sequence[int]) -> torch.Tensor:
+        ids = [int(t) for t in ids]
+        n = 0
+        if self._cache is not None:
+            while n < min(len(ids) - 1, len(self._seen)) and ids[n] == self._seen[n]:
+                n += 1
+        if self._cache is None or n == 0:
+            self._cache, n = self._new_cache(), 0
+        else:
+            self._cache.truncate(n)
+        out = self.model(torch.tensor([ids[n:]], dtype=torch.long, device=self._dev), self._cache)
+        self._seen = ids
+        return out[0, -1].to(torch.float64).cpu()
+
+    @torch.no_grad()
+    def forward_ids_all_positions(self, ids: Sequence[int]) -> torch.Tensor:
+        out = self.model(torch.tensor([[int(t) for t in ids]], dtype=torch.long, device=self._dev), self._new_cache())
+        return out[0].to(torch.float64).cpu()
+
+
+@torch.no_grad()
+def speculative_decode(draft: ModelHandle, target: ModelHandle, prompt_ids: Sequence[int], config: Optional[SpecDecodeConfig] = None) -> SpecDecodeOutput:
+    """Speculative sampling (Leviathan et al. 2023, Algorithm 1) as in ferrotorch-llama/src/spec_decode.rs:264-420: the draft samples ``K``
+    tokens from its own distributions ``q``; one target forward over ``context + draft`` gives ``p`` at the ``K + 1`` positions; token ``j`` is
+    kept with probability ``min(1, p_j / q_j)``; the first rejected position is redrawn from ``norm(max(0, p - q))``; if all are kept a bonus
+    token is drawn from ``p_K``. The emitted tokens are distributed exactly as samples from the target alone. All draws come from one
+    :class:`XorShift64` (``config.seed``), in the reference's order."""
+    config = config or SpecDecodeConfig()
+    if len(prompt_ids) == 0:
+        raise InvalidArgument("speculative_decode: prompt_ids must not be empty")
+    config.validate()
+    vocab = draft.vocab_size()
+    if target.vocab_size() != vocab:
+        raise InvalidArgument(f"speculative_decode: draft vocab_size ({vocab}) != target vocab_size ({target.vocab_size()})")
+    rng = XorShift64(config.seed)
+    stops = set(config.stop_ids())
+    context, produced = [int(t) for t in prompt_ids], []
+    accepted = proposed = 0
+    pick = lambda w: _sample_weights(w, rng, lambda: argmax(w))
+    while len(produced) < config.max_new_tokens:
+        k = min(config.draft_k, config.max_new_tokens - len(produced))
+        d_tok, d_prob, ctx = [], [], list(context)
+        for _ in range(k):
+            q = _softmax64(draft.forward_ids(ctx))
+            t = pick(q)
+            d_tok.append(t)
+            d_prob.append(q)
+            ctx.append(t)
+        rows = target.forward_ids_all_positions(context + d_tok)
+        if rows.shape[0] != len(context) + k:
+            raise InvalidArgument(f"speculative_decode: forward_ids_all_positions returned {rows.shape[0]} rows for input length {len(context) + k}")
+        t_prob = [_softmax64(rows[len(context) - 1 + j]) for j in range(k + 1)]
+        proposed += k
+        n_ok, corrected = 0, None
+        for j in range(k):
+            q, p = float(d_prob[j][d_tok[j]]), float(t_prob[j][d_tok[j]])
+            if rng.uniform() < (0.0 if q <= 0.0 else min(p / q, 1.0)):
+                n_ok += 1
+            else:
+                resid = (t_prob[j] - d_prob[j]).clamp_min(0.0)
+                corrected = _sample_weights(resid, rng, lambda: pick(t_prob[j]))
+                break
+        accepted += n_ok
+        stop = False
+        for t in d_tok[:n_ok]:
+            produced.append(t)
+            context.append(t)
+            if t in stops or len(produced) >= config.max_new_tokens:
+                stop = True
+                break
+        if stop:
+            break
+        extra = corrected if corrected is not None else pick(t_prob[k])
+        produced.append(extra)
+        context.append(extra)
+        if extra in stops:
+            break
+    return SpecDecodeOutput(produced[: config.max_new_tokens], accepted, proposed)
 
 
 @dataclass
@@ -312,10 +571,66 @@ def _unpack_int4(packed: torch.Tensor, dim: int) -> torch.Tensor:
     return vals.reshape(out_shape).to(torch.uint8)
 
 
-def dequantize_gptq_q4(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, g_idx: Optional[torch.Tensor] = None,
+@dataclass
+class GptqQ4:
+    """One GPTQ 4-bit linear weight as stored in a checkpoint (ferrotorch-llama/src/quant_loaders.rs:34): ``qweight`` int32 ``[K/8, N]``,
+    ``qzeros`` int32 ``[K/G, N/8]``, ``scales`` ``[K/G, N]``, optional ``g_idx`` ``[K]`` (``act_order``)."""
+    qweight: torch.Tensor
+    qzeros: torch.Tensor
+    scales: torch.Tensor
+    g_idx: Optional[torch.Tensor]
+    in_features: int
+    out_features: int
+    group_size: int
+
+
+@dataclass
+class AwqQ4:
+    """One AWQ 4-bit linear weight (GEMM layout; quant_loaders.rs:203): ``qweight`` int32 ``[K, N/8]``, ``qzeros`` int32 ``[K/G, N/8]``,
+    ``scales`` ``[K/G, N]``."""
+    qweight: torch.Tensor
+    qzeros: torch.Tensor
+    scales: torch.Tensor
+    in_features: int
+    out_features: int
+    group_size: int
+
+
+@dataclass
+class HqqWeights:
+    """One HQQ weight (quant_loaders.rs:355): packed ``w_q`` bytes, per-group ``scale`` / ``zero``, and the dense shape."""
+    bits: int
+    w_q: torch.Tensor
+    scale: torch.Tensor
+    zero: torch.Tensor
+    out_features: int
+    in_features: int
+
+
+def _check_q4(name: str, K: int, N: int, G: int, shapes) -> None:
+    if K % 8 or N % 8:
+        raise InvalidArgument(f"{name}: in_features ({K}) and out_features ({N}) must be multiples of 8")
+    if G <= 0 or K % G:
+        raise InvalidArgument(f"{name}: in_features ({K}) must be divisible by group_size ({G})")
+    for what, t, want in shapes:
+        if t.numel() != want:
+            raise InvalidArgument(f"{name}: {what} has {t.numel()} elements, expected {want}")
+
+
+def dequantize_gptq_q4(qweight, qzeros: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None, g_idx: Optional[torch.Tensor] = None,
                        group_size: int = 128) -> torch.Tensor:
-    """GPTQ 4-bit: ``qweight`` int32 ``[in/8, out]``, ``qzeros`` int32 ``[groups, out/8]``, ``scales`` ``[groups, out]`` -> weight ``[out, in]``.
+    """Also takes one :class:`GptqQ4` (buffers may be flat; sizes are checked as in quant_loaders.rs:90-120).
+
+    GPTQ 4-bit: ``qweight`` int32 ``[in/8, out]``, ``qzeros`` int32 ``[groups, out/8]``, ``scales`` ``[groups, out]`` -> weight ``[out, in]``.
     The stored zero is one less than the actual zero point (AutoGPTQ convention)."""
+    if isinstance(qweight, GptqQ4):
+        t = qweight
+        K, N, G = t.in_features, t.out_features, t.group_size
+        _check_q4("dequantize_gptq_q4", K, N, G, (("qweight", t.qweight, K // 8 * N), ("qzeros", t.qzeros, K // max(G, 1) * (N // 8)),
+                                                    ("scales", t.scales, K // max(G, 1) * N)))
+        if t.g_idx is not None and t.g_idx.numel() != K:
+            raise InvalidArgument(f"dequantize_gptq_q4: g_idx has {t.g_idx.numel()} elements, expected {K}")
+        return dequantize_gptq_q4(t.qweight.reshape(K // 8, N), t.qzeros.reshape(K // G, N // 8), t.scales.reshape(K // G, N), t.g_idx, G)
     w = _unpack_int4(qweight, 0).float()                             # [in, out]
     z = _unpack_int4(qzeros, 1).float() + 1.0                        # [groups, out]
     gi = g_idx.long() if g_idx is not None else torch.arange(w.shape[0], device=w.device) // group_size
@@ -325,10 +640,16 @@ def dequantize_gptq_q4(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torc
 _AWQ_ORDER = [0, 4, 1, 5, 2, 6, 3, 7]
 
 
-def dequantize_awq_q4(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, group_size: int = 128) -> torch.Tensor:
-    """AWQ 4-bit (GEMM layout): ``qweight`` int32 ``[in, out/8]``. Output channel ``c`` of a word sits in nibble ``[0, 4, 1, 5, 2, 6, 3, 7][c]``
+def dequantize_awq_q4(qweight, qzeros: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None, group_size: int = 128) -> torch.Tensor:
+    """Also takes one :class:`AwqQ4`. AWQ 4-bit (GEMM layout): ``qweight`` int32 ``[in, out/8]``. Output channel ``c`` of a word sits in nibble ``[0, 4, 1, 5, 2, 6, 3, 7][c]``
     (AutoAWQ packs the channels of a word in the order 0, 2, 4, 6, 1, 3, 5, 7; ferrotorch-llama/src/quant_loaders.rs:244-331 reads them back the
     same way)."""
+    if isinstance(qweight, AwqQ4):
+        t = qweight
+        K, N, G = t.in_features, t.out_features, t.group_size
+        _check_q4("dequantize_awq_q4", K, N, G, (("qweight", t.qweight, K * (N // 8)), ("qzeros", t.qzeros, K // max(G, 1) * (N // 8)),
+                                                   ("scales", t.scales, K // max(G, 1) * N)))
+        return dequantize_awq_q4(t.qweight.reshape(K, N // 8), t.qzeros.reshape(K // G, N // 8), t.scales.reshape(K // G, N), G)
     order = torch.tensor(_AWQ_ORDER, device=qweight.device)
     w = _unpack_int4(qweight, 1).view(qweight.shape[0], -1, 8)[:, :, order].reshape(qweight.shape[0], -1).float()
     z = _unpack_int4(qzeros, 1).view(qzeros.shape[0], -1, 8)[:, :, order].reshape(qzeros.shape[0], -1).float()
@@ -336,8 +657,25 @@ def dequantize_awq_q4(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch
     return ((w - z[gi]) * scales.float()[gi]).t().contiguous()
 
 
-def dequantize_hqq(w_q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, shape: Sequence[int], nbits: int = 4, group_size: int = 64) -> torch.Tensor:
-    """HQQ: ``w_q`` uint8 with two 4-bit values per byte (first half of the rows in the high nibble), per-group ``scale``/``zero``."""
+def dequantize_hqq(w_q, scale: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None, shape: Optional[Sequence[int]] = None, nbits: int = 4,
+                   group_size: int = 64) -> torch.Tensor:
+    """Tensor form: ``w_q`` uint8 with two 4-bit values per byte (first half of the rows in the high nibble), per-group ``scale``/``zero``. One :class:`HqqWeights` argument selects the
+    reference's packed form instead (1, 2, 3, 4 or 8 bits)."""
+    if isinstance(w_q, HqqWeights):
+        # reference form (quant_loaders.rs:335-570): one little-endian bit stream, element i in bits [i*b, i*b + b); scale / zero per output row
+        t = w_q
+        if t.bits not in (1, 2, 3, 4, 8):
+            raise InvalidArgument(f"HQQ: bits must be 1/2/3/4/8, got {t.bits}")
+        if t.scale.numel() != t.out_features or t.zero.numel() != t.out_features:
+            raise ShapeMismatch(f"HQQ: scale len {t.scale.numel()} / zero len {t.zero.numel()} != out_features {t.out_features}")
+        total = t.out_features * t.in_features
+        need = -(-total // 8) * 3 if t.bits == 3 else -(-total * t.bits // 8)
+        raw = t.w_q.reshape(-1).to(torch.uint8)
+        if raw.numel() < need:
+            raise ShapeMismatch(f"HQQ {t.bits}-bit: packed buffer too short ({raw.numel()} bytes for {total} weights, need {need})")
+        bits = (raw[:need, None] >> torch.arange(8, device=raw.device, dtype=torch.uint8)) & 1
+        q = (bits.reshape(-1)[: total * t.bits].reshape(total, t.bits).float() * (2.0 ** torch.arange(t.bits, device=raw.device))).sum(1)
+        return (q.view(t.out_features, t.in_features) - t.zero.float().view(-1, 1)) * t.scale.float().view(-1, 1)
     if nbits == 4:
         hi, lo = (w_q >> 4) & 0xF, w_q & 0xF
         q = torch.cat([hi, lo], 0).float()
@@ -377,6 +715,9 @@ def gguf_to_hf_name(name: str) -> Optional[str]:
     return None
 
 
+gguf_key_to_hf = gguf_to_hf_name                                  # the reference's name (ferrotorch-llama/src/gguf_remap.rs:23)
+
+
 def gguf_unpermute_qk(w: torch.Tensor, n_heads: int) -> torch.Tensor:
     """llama.cpp stores q/k projections with the interleaved rotary layout; this restores the HF half-rotation row order."""
     out, d = w.shape
@@ -395,3 +736,7 @@ def remap_gguf_state_dict(tensors: Dict[str, torch.Tensor], cfg: LlamaConfig) ->
             v = gguf_unpermute_qk(v, cfg.num_key_value_heads)
         out[hf] = v
     return out
+
+
+gguf_to_hf_state_dict = remap_gguf_state_dict                     # ferrotorch-llama/src/gguf_remap.rs:66
+LlamaKvCache = KvCache                                            # ferrotorch-llama/src/kv_cache.rs

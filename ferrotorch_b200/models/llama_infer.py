@@ -102,6 +102,8 @@ class LlamaTPEngine:
     def __init__(self, cfg: LlamaConfig, ctx: Optional[TPContext] = None, max_batch: int = 8, max_seq: int = 2304, device="cuda", seed: int = 0,
                  weights: Optional[Dict[str, torch.Tensor]] = None, use_graph: bool = True):
         cfg.validate()
+        if cfg.hidden_act not in ("silu", "swish"):
+            raise InvalidArgument(f"the tensor-parallel decode kernels implement SwiGLU only; use models.LlamaGpuInferencer for {cfg.hidden_act!r}")
         self.cfg, self.ctx = cfg, ctx or TPContext(device)
         self.dev = self.ctx.device
         tp, r = self.ctx.world, self.ctx.rank

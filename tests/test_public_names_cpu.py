@@ -196,3 +196,203 @@ def test_diffusion_configs_blocks_and_loaders(tmp_path):
         assert torch.allclose(image, dec.decode_with_scaling(dumps[-1].latent_after_step))
     with pytest.raises(FerrotorchError):
         pipe.generate(cond, unc[:, :2], lat, 2, 5.0)
+
+
+def _tiny_llama(act="silu", param=None):
+    cfg = M.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        max_position_embeddings=64, rope_theta=10000.0, hidden_act=act, hidden_act_param=param)
+    g = torch.Generator().manual_seed(0)
+    W = {"model.embed_tokens.weight": torch.randn(64, 32, generator=g) * 0.5, "model.norm.weight": torch.rand(32, generator=g) + 0.5,
+         "lm_head.weight": torch.randn(64, 32, generator=g) * 0.3}
+    for i in range(2):
+        p = f"model.layers.{i}."
+        for n, shp in (("self_attn.q_proj", (32, 32)), ("self_attn.k_proj", (16, 32)), ("self_attn.v_proj", (16, 32)), ("self_attn.o_proj", (32, 32)),
+                       ("mlp.gate_proj", (48, 32)), ("mlp.up_proj", (48, 32)), ("mlp.down_proj", (32, 48))):
+            W[p + n + ".weight"] = torch.randn(*shp, generator=g) * 0.2
+        W[p + "input_layernorm.weight"] = torch.rand(32, generator=g) + 0.5
+        W[p + "post_attention_layernorm.weight"] = torch.rand(32, generator=g) + 0.5
+    return cfg, W
+
+
+def test_llama_activation_variants_match_transformers():
+    transformers = pytest.importorskip("transformers")
+    a = M.LlamaActivation.FatRelu(0.5)
+    assert torch.equal(a(torch.tensor([-1.0, 0.4, 0.5, 2.0])), torch.tensor([0.0, 0.0, 0.5, 2.0])) and a == M.LlamaActivation.parse("fatrelu", 0.5)
+    assert M.LlamaActivation.parse("swish") is M.LlamaActivation.Silu and M.LlamaActivation.parse("fatrelu").threshold == 0.01
+    with pytest.raises(InvalidArgument):
+        M.LlamaActivation.parse("gelu")
+    with pytest.raises(InvalidArgument):
+        M.LlamaConfig(hidden_act="gelu").validate()
+    cfg, W = _tiny_llama("relu")
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2,
+                                                                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                                                rope_theta=10000.0, hidden_act="relu", rms_norm_eps=cfg.rms_norm_eps)).eval()
+    hf.load_state_dict(W, strict=False)
+    ids = torch.randint(0, 64, (1, 9), generator=torch.Generator().manual_seed(1))
+    ours = M.CachedLlama(cfg, W)
+    with torch.no_grad():
+        want = hf(ids).logits
+    assert torch.allclose(ours(ids, ours.new_cache()), want, atol=2e-4)
+    with pytest.raises(InvalidArgument):                      # the fused training layer is SwiGLU only and says so
+        M.LlamaModel(cfg, device="cpu")
+
+
+def test_llama_blocks_and_inferencer_taps():
+    cfg, W = _tiny_llama("fatrelu", 0.05)
+    ref = M.CachedLlama(cfg, W)
+    ids = [3, 9, 27, 1, 50, 7]
+    want = ref(torch.tensor([ids]), ref.new_cache())[0]
+    inf = M.LlamaGpuInferencer(cfg, W, device="cpu", dtype=torch.float32)
+    assert torch.allclose(inf.forward_logits_from_ids_all(ids), want, atol=1e-5)
+    assert torch.allclose(inf.forward_from_ids(ids), want[-1], atol=1e-5)
+    L0 = inf.layers[0]
+    assert L0.self_attn.num_heads() == 4 and L0.self_attn.num_kv_heads() == 2 and L0.self_attn.head_dim() == 8
+    # attention with a cache fed token by token equals the whole-sequence pass
+    x = torch.randn(1, 6, 32)
+    cache = M.LayerKvCache()
+    step = torch.cat([L0.self_attn.forward_with_cache(x[:, i: i + 1], cache) for i in range(6)], 1)
+    assert torch.allclose(step, L0.self_attn(x), atol=1e-5)
+    r = inf.forward_from_ids_profiled_with_bootstrap(ids, 12, 4, bootstrap_k=1)
+    assert r.attn_magnitudes.shape == (2, 6, 4) and r.mlp_magnitudes.shape == (2, 6, 4) and r.seq_len == 6 and r.hidden_size == 32
+    # layer 0 by hand
+    x0 = W["model.embed_tokens.weight"][torch.tensor([ids])]
+    rms = lambda v, w: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * w
+    x1 = x0 + L0.self_attn(rms(x0, W["model.layers.0.input_layernorm.weight"]))
+    gated = L0.mlp.gated(rms(x1, W["model.layers.0.post_attention_layernorm.weight"]))
+    assert torch.allclose(r.mlp_magnitudes[0], gated[0].abs().view(6, 4, 12).amax(-1), atol=1e-5)
+    assert torch.allclose(r.bootstrap_hidden, (x1 + L0.mlp.down_proj(gated))[0], atol=1e-5)
+    assert (gated == 0).float().mean() > 0.3                 # the thresholded gate really zeroes activations
+    rp = inf.forward_from_ids_profiled_with_bootstrap(ids, 12, 4, None, True)
+    y = x1 + L0.mlp.down_proj(gated)
+    assert torch.allclose(rp.mlp_magnitudes[0], (gated * (y @ L0.mlp.down_proj.weight))[0].abs().view(6, 4, 12).amax(-1), atol=1e-5)
+    for bad in ((10, 4, None), (12, 4, 3), (12, 4, 0)):
+        with pytest.raises(InvalidArgument):
+            inf.forward_from_ids_profiled_with_bootstrap(ids, *bad)
+
+
+def test_generation_primitives_and_streamer():
+    r = M.XorShift64(1)
+    x = 1
+    x ^= (x << 13) & (2 ** 64 - 1); x ^= x >> 7; x ^= (x << 17) & (2 ** 64 - 1)          # noqa: E702
+    assert r.next_u64() == x and 0.0 <= r.uniform() <= 1.0
+    assert M.argmax(torch.tensor([1.0, 5.0, 5.0, 2.0])) == 1 and M.argmax([float("-inf")] * 3) == 0
+    assert torch.equal(M.apply_temperature(torch.tensor([2.0, 4.0]), 2.0), torch.tensor([1.0, 2.0]))
+    assert M.sample_softmax(torch.tensor([float("-inf"), float("-inf")]), M.XorShift64(3)) == 0
+    rng, counts = M.XorShift64(7), [0, 0, 0]
+    lg = torch.log(torch.tensor([0.2, 0.5, 0.3]))
+    for _ in range(4000):
+        counts[M.sample_softmax(lg, rng)] += 1
+    assert abs(counts[0] / 4000 - 0.2) < 0.03 and abs(counts[1] / 4000 - 0.5) < 0.03
+
+    cfg, W = _tiny_llama()
+    model = M.CachedLlama(cfg, W)
+    prompt = [5, 6, 7]
+    seen = []
+    out = M.generate_with_streamer(model, prompt, M.GenerationConfig.greedy(8), lambda t: (seen.append(t), True)[1])
+    full = M.generate(model, model.new_cache, torch.tensor([prompt]), M.GenerationConfig(max_new_tokens=8))
+    assert out == full[0, 3:].tolist() == seen
+    assert M.generate_with_streamer(model, prompt, M.GenerationConfig.greedy(8), lambda t: len(seen) < 0) == out[:1]      # streamer says stop
+    stop = M.GenerationConfig.greedy(8)
+    stop.eos_token_ids = [out[2]]
+    assert M.generate_with_streamer(model, prompt, stop, lambda t: True) == out[: out.index(out[2]) + 1]
+    c = M.GenerationConfig.nucleus(12, 0.9, 0.8)
+    c.seed, c.top_k, c.repetition_penalty = 11, 20, 1.3
+    a, b = M.generate_with_streamer(model, prompt, c, lambda t: True), M.generate_with_streamer(model, prompt, c, lambda t: True)
+    c.seed = 12
+    assert a == b and len(a) == 12 and a != M.generate_with_streamer(model, prompt, c, lambda t: True)
+    for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(repetition_penalty=0.0)):
+        with pytest.raises(InvalidArgument):
+            M.generate_with_streamer(model, prompt, M.GenerationConfig(**bad), lambda t: True)
+    with pytest.raises(InvalidArgument):
+        M.generate_with_streamer(model, [], M.GenerationConfig(), lambda t: True)
+
+
+class _FixedHandle(M.ModelHandle):
+    """Context-free distribution, with call counters."""
+
+    def __init__(self, probs):
+        self.logits, self.calls, self.batched = torch.log(torch.tensor(probs, dtype=torch.float64)), 0, 0
+
+    def vocab_size(self):
+        return self.logits.numel()
+
+    def forward_ids(self, ids):
+        self.calls += 1
+        return self.logits
+
+    def forward_ids_all_positions(self, ids):
+        self.batched += 1
+        return self.logits.expand(len(ids), -1)
+
+
+def test_speculative_decode_samples_from_the_target():
+    p, q = [0.1, 0.2, 0.3, 0.4], [0.4, 0.3, 0.2, 0.1]
+    first, second, acc, prop = [0] * 4, [0] * 4, 0, 0
+    import random
+    seeds = random.Random(0)                                  # xorshift needs well-mixed seeds: a small seed gives a tiny first draw
+    for _ in range(1500):
+        d, t = _FixedHandle(q), _FixedHandle(p)
+        o = M.speculative_decode(d, t, [0], M.SpecDecodeConfig(draft_k=3, max_new_tokens=6, seed=seeds.getrandbits(64) | 1))
+        assert len(o.tokens) == 6 and t.calls == 0 and t.batched <= 6 and d.calls == o.proposed_count
+        first[o.tokens[0]] += 1
+        second[o.tokens[3]] += 1
+        acc, prop = acc + o.accepted_count, prop + o.proposed_count
+    for cnt in (first, second):
+        assert all(abs(cnt[i] / 1500 - p[i]) < 0.04 for i in range(4)), cnt
+    a1 = sum(min(a, b) for a, b in zip(p, q))                 # one draft token survives with probability sum min(p, q); a round stops at the
+    assert abs(acc / prop - (a1 + a1 ** 2 + a1 ** 3) / 3) < 0.05          # first rejection, so of 3 proposals a1 + a1^2 + a1^3 are kept on average
+    same = M.speculative_decode(_FixedHandle(p), _FixedHandle(p), [0], M.SpecDecodeConfig(draft_k=4, max_new_tokens=9, seed=5))
+    assert same.acceptance_rate() == 1.0 and len(same.tokens) == 9
+    a = M.speculative_decode(_FixedHandle(q), _FixedHandle(p), [0], M.SpecDecodeConfig(draft_k=2, max_new_tokens=7, seed=9))
+    b = M.speculative_decode(_FixedHandle(q), _FixedHandle(p), [0], M.SpecDecodeConfig(draft_k=2, max_new_tokens=7, seed=9))
+    assert a.tokens == b.tokens
+    eos = M.speculative_decode(_FixedHandle(q), _FixedHandle(p), [0], M.SpecDecodeConfig(draft_k=2, max_new_tokens=50, seed=9, eos_token_ids=[a.tokens[1]]))
+    assert eos.tokens[-1] == a.tokens[1] and a.tokens[1] not in eos.tokens[:-1]
+    assert M.SpecDecodeOutput([], 0, 0).acceptance_rate() == 1.0
+    with pytest.raises(InvalidArgument):
+        M.speculative_decode(_FixedHandle(q), _FixedHandle(p), [], M.SpecDecodeConfig())
+    with pytest.raises(InvalidArgument):
+        M.speculative_decode(_FixedHandle(q), _FixedHandle(p), [0], M.SpecDecodeConfig(draft_k=0))
+    with pytest.raises(InvalidArgument):
+        M.speculative_decode(_FixedHandle(q[:3] + [0.1]), _FixedHandle([0.5, 0.5]), [0])
+
+    # real models: a handle re-feeds only the unseen suffix, and draft == target accepts everything
+    cfg, W = _tiny_llama()
+    h = M.LlamaHandle(M.CachedLlama(cfg, W))
+    ref = M.CachedLlama(cfg, W)
+    ids = [4, 8, 15, 16, 23]
+    want = ref(torch.tensor([ids]), ref.new_cache())[0].double()
+    assert torch.allclose(h.forward_ids(ids[:3]), want[2], atol=1e-5) and torch.allclose(h.forward_ids(ids), want[4], atol=1e-5)
+    assert h._cache.len() == 5 and torch.allclose(h.forward_ids(ids[:4]), want[3], atol=1e-5)
+    assert torch.allclose(h.forward_ids_all_positions(ids), want, atol=1e-5) and h.vocab_size() == 64
+    o = M.speculative_decode(M.LlamaHandle(M.CachedLlama(cfg, W)), h, ids, M.SpecDecodeConfig(draft_k=3, max_new_tokens=8, seed=3))
+    assert o.acceptance_rate() == 1.0 and len(o.tokens) == 8
+
+
+def test_quantised_weight_structs():
+    g = torch.Generator().manual_seed(0)
+    K, N, G = 32, 16, 16
+    qw, qz = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), generator=g, dtype=torch.int64).int(), torch.randint(-2 ** 31, 2 ** 31 - 1, (K // G, N // 8), generator=g, dtype=torch.int64).int()
+    sc = torch.rand(K // G, N, generator=g)
+    assert torch.equal(M.dequantize_gptq_q4(M.GptqQ4(qw.reshape(-1), qz.reshape(-1), sc.reshape(-1), None, K, N, G)), M.dequantize_gptq_q4(qw, qz, sc, None, G))
+    aw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), generator=g, dtype=torch.int64).int()
+    assert torch.equal(M.dequantize_awq_q4(M.AwqQ4(aw.reshape(-1), qz.reshape(-1), sc.reshape(-1), K, N, G)), M.dequantize_awq_q4(aw, qz, sc, G))
+    with pytest.raises(InvalidArgument):
+        M.dequantize_gptq_q4(M.GptqQ4(qw.reshape(-1)[:-1], qz.reshape(-1), sc.reshape(-1), None, K, N, G))
+    with pytest.raises(InvalidArgument):
+        M.dequantize_awq_q4(M.AwqQ4(aw.reshape(-1), qz.reshape(-1), sc.reshape(-1), K, N, 5))
+    for bits in (1, 2, 3, 4, 8):
+        rows, cols = 3, 8
+        vals = torch.randint(0, 2 ** bits, (rows * cols,), generator=g)
+        stream = 0
+        for i, v in enumerate(vals.tolist()):
+            stream |= v << (i * bits)
+        packed = torch.tensor(list(stream.to_bytes(rows * cols * bits // 8, "little")), dtype=torch.uint8)
+        scale, zero = torch.rand(rows, generator=g) + 0.5, torch.rand(rows, generator=g)
+        got = M.dequantize_hqq(M.HqqWeights(bits, packed, scale, zero, rows, cols))
+        assert torch.allclose(got, (vals.view(rows, cols).float() - zero[:, None]) * scale[:, None]), bits
+    with pytest.raises(InvalidArgument):
+        M.dequantize_hqq(M.HqqWeights(5, packed, scale, zero, 3, 8))
+    with pytest.raises(FerrotorchError):
+        M.dequantize_hqq(M.HqqWeights(8, packed[:5], scale, zero, 3, 8))
+    assert M.gguf_key_to_hf("blk.3.attn_q.weight") == "model.layers.3.self_attn.q_proj.weight" and M.LlamaKvCache is M.KvCache
