@@ -5,6 +5,7 @@ Reference parity: ferrotorch-vision/src/{mnist.rs:58, cifar.rs:81-197, folder.rs
 """
 from __future__ import annotations
 
+import enum
 import gzip
 import math
 import threading
@@ -12,7 +13,8 @@ import os
 import pickle
 import struct
 from pathlib import Path
-from typing import Callable, List, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Callable, List, NamedTuple, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -57,6 +59,93 @@ def write_image(path, img: torch.Tensor) -> None:
     Image.fromarray(a.squeeze(-1) if a.shape[-1] == 1 else a).save(p)
 
 
+@dataclass
+class RawImage:
+    """Decoded 8-bit image in row-major ``[H, W, C]`` byte order (ferrotorch-vision/src/io.rs:23)."""
+    data: bytes
+    width: int
+    height: int
+    channels: int
+
+
+def _raw(t: torch.Tensor) -> RawImage:                       # [C, H, W] uint8
+    return RawImage(t.permute(1, 2, 0).contiguous().numpy().tobytes(), int(t.shape[2]), int(t.shape[1]), int(t.shape[0]))
+
+
+def read_image_raw(path) -> RawImage:
+    """RGB bytes of an image file; the reference's ``read_image`` (io.rs:41; :func:`read_image` here returns the ``[C, H, W]`` tensor directly)."""
+    try:
+        return _raw(read_image(path))
+    except Exception as e:
+        raise InvalidArgument(f"failed to read image '{path}': {e}") from None
+
+
+def read_image_rgba(path) -> RawImage:
+    """RGBA bytes; images without an alpha channel get alpha 255 (io.rs:62)."""
+    try:
+        from PIL import Image
+        a = np.asarray(Image.open(str(path)).convert("RGBA"))
+    except Exception as e:
+        raise InvalidArgument(f"failed to read image '{path}': {e}") from None
+    return RawImage(a.tobytes(), a.shape[1], a.shape[0], 4)
+
+
+def raw_image_to_tensor(raw: RawImage, dtype=torch.float32) -> torch.Tensor:
+    """``[C, H, W]`` float tensor in [0, 1] (io.rs:106)."""
+    n = raw.height * raw.width * raw.channels
+    if len(raw.data) != n:
+        raise InvalidArgument(f"raw_image_to_tensor: {len(raw.data)} bytes for {raw.height}x{raw.width}x{raw.channels}")
+    a = torch.frombuffer(bytearray(raw.data), dtype=torch.uint8).view(raw.height, raw.width, raw.channels)
+    return a.permute(2, 0, 1).to(dtype).div(255).contiguous()
+
+
+def read_image_as_tensor(path, dtype=torch.float32) -> torch.Tensor:
+    return raw_image_to_tensor(read_image_raw(path), dtype)
+
+
+def tensor_to_raw_image(t: torch.Tensor) -> RawImage:
+    """``[C, H, W]`` with 3 or 4 channels, values clamped to [0, 1], times 255, rounded (io.rs:203)."""
+    if t.dim() != 3:
+        raise InvalidArgument(f"tensor_to_raw_image: expected 3-D tensor [C, H, W], got shape {list(t.shape)}")
+    if t.shape[0] not in (3, 4):
+        raise InvalidArgument(f"tensor_to_raw_image: expected 3 or 4 channels, got {t.shape[0]}")
+    return _raw((t.detach().cpu().double().clamp(0, 1) * 255).round().to(torch.uint8))
+
+
+def write_raw_image(path, raw: RawImage) -> None:
+    a = torch.frombuffer(bytearray(raw.data), dtype=torch.uint8).view(raw.height, raw.width, raw.channels).permute(2, 0, 1)
+    try:
+        write_image(path, a)
+    except Exception as e:
+        raise InvalidArgument(f"failed to write image '{path}': {e}") from None
+
+
+def write_tensor_as_image(path, t: torch.Tensor) -> None:
+    write_raw_image(path, tensor_to_raw_image(t))
+
+
+class Split(enum.Enum):
+    """Which half of a dataset to load (ferrotorch-vision/src/datasets/mnist.rs:43)."""
+    Train = "train"
+    Test = "test"
+
+
+class MnistSample(NamedTuple):
+    """``(image [1, 28, 28], label)`` (datasets/mnist.rs:34); unpacks like the plain tuple it is."""
+    image: torch.Tensor
+    label: int
+
+
+class CifarSample(NamedTuple):
+    """``(image [3, 32, 32], label)`` (datasets/cifar.rs:53)."""
+    image: torch.Tensor
+    label: int
+
+
+IMAGENET_MEAN = (0.485, 0.456, 0.406)                        # ferrotorch-vision/src/transforms/mod.rs:38-41
+IMAGENET_STD = (0.229, 0.224, 0.225)
+
+
 # -- datasets ---------------------------------------------------------------------------------------------------------------------------
 class Mnist(Dataset):
     """MNIST from the IDX files under ``root`` or a deterministic synthetic stand-in (class-dependent blob patterns)."""
@@ -65,7 +154,8 @@ class Mnist(Dataset):
         self.images, self.labels, self.transform = images, labels, transform
 
     @staticmethod
-    def from_dir(root, train: bool = True, transform=None) -> "Mnist":
+    def from_dir(root, train=True, transform=None) -> "Mnist":
+        train = train is Split.Train if isinstance(train, Split) else bool(train)
         pre = "train" if train else "t10k"
 
         def idx(name):
@@ -98,7 +188,7 @@ class Mnist(Dataset):
 
     def __getitem__(self, i):
         x = self.images[i]
-        return (self.transform(x) if self.transform else x), self.labels[i]
+        return MnistSample((self.transform(x) if self.transform else x), self.labels[i])
 
 
 class Cifar10(Dataset):
@@ -108,7 +198,8 @@ class Cifar10(Dataset):
         self.images, self.labels, self.transform = images, labels, transform
 
     @classmethod
-    def from_dir(cls, root, train: bool = True, transform=None):
+    def from_dir(cls, root, train=True, transform=None):
+        train = train is Split.Train if isinstance(train, Split) else bool(train)
         files = [f"data_batch_{i}" for i in range(1, 6)] if train else ["test_batch"]
         if cls.classes == 100:
             files = ["train"] if train else ["test"]
@@ -133,7 +224,7 @@ class Cifar10(Dataset):
 
     def __getitem__(self, i):
         x = self.images[i]
-        return (self.transform(x) if self.transform else x), self.labels[i]
+        return CifarSample((self.transform(x) if self.transform else x), self.labels[i])
 
 
 class Cifar100(Cifar10):

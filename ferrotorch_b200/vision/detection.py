@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import math
 from collections import OrderedDict
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -208,6 +209,47 @@ class DetectionTransform(nn.Module):
 # ----------------------------------------------------------------------------------------------------------------------
 # RPN
 # ----------------------------------------------------------------------------------------------------------------------
+class Detections(dict):
+    """Detections of one image: a dict with ``boxes [N, 4]`` (xyxy, image pixels), ``scores [N]``, ``labels [N]`` that also reads as attributes
+    (ferrotorch-vision/src/models/detection/faster_rcnn.rs:92, retinanet.rs:612, fcos.rs:467)."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError:
+            raise AttributeError(k) from None
+
+
+class MaskDetections(Detections):
+    """:class:`Detections` plus ``masks [N, 1, H, W]`` pasted into the image (mask_rcnn.rs:192)."""
+
+
+class SsdDetections(Detections):
+    """ssd.rs:1325."""
+
+
+FPN_OUT_CHANNELS = 256                                       # fpn.rs:39
+SSD_ANCHORS_PER_SCALE = (4, 6, 6, 6, 4, 4)                   # ssd.rs:436-465
+SSD_FM_SIZES = (38, 19, 10, 5, 3, 1)
+SSD_TOTAL_ANCHORS = 8732
+SSD_SCORE_THRESH, SSD_NMS_THRESH, SSD_TOPK_CANDIDATES, SSD_DETECTIONS_PER_IMG = 0.01, 0.45, 400, 200
+
+
+@dataclass
+class RpnConfig:
+    """Proposal filtering knobs (rpn.rs:115); ``default_eval`` carries torchvision's inference values."""
+    pre_nms_top_n: int = 1000
+    post_nms_top_n: int = 1000
+    nms_thresh: float = 0.7
+    min_size: float = 1e-3
+    score_thresh: float = 0.0
+    image_size: Tuple[int, int] = (800, 800)
+
+    @classmethod
+    def default_eval(cls, image_size) -> "RpnConfig":
+        return cls(image_size=tuple(image_size))
+
+
 class RPNHead(nn.Module):
     def __init__(self, ch, num_anchors):
         super().__init__()
@@ -227,6 +269,9 @@ def _flatten_levels(xs: Sequence[torch.Tensor], c: int) -> torch.Tensor:
 class Rpn(nn.Module):
     def __init__(self, anchor_generator: AnchorGenerator, head: RPNHead, pre_nms_top_n=1000, post_nms_top_n=1000, nms_thresh=0.7, score_thresh=0.0, min_size=1e-3):
         super().__init__()
+        if isinstance(pre_nms_top_n, RpnConfig):
+            c = pre_nms_top_n
+            pre_nms_top_n, post_nms_top_n, nms_thresh, score_thresh, min_size = c.pre_nms_top_n, c.post_nms_top_n, c.nms_thresh, c.score_thresh, c.min_size
         self.anchor_generator, self.head = anchor_generator, head
         self.pre, self.post, self.nms_thresh, self.score_thresh, self.min_size = pre_nms_top_n, post_nms_top_n, nms_thresh, score_thresh, min_size
 
@@ -405,12 +450,13 @@ class RoIHeads(nn.Module):
         x = self.box_head(self.box_roi_pool(feats, proposals, image_sizes))
         logits, reg = self.box_predictor(x)
         dets = postprocess_detections(logits, reg, proposals, image_sizes, self.score_thresh, self.nms_thresh, self.detections_per_img)
-        out = [{"boxes": b, "scores": s, "labels": l} for b, s, l, _ in dets]
+        out = [Detections(boxes=b, scores=s, labels=l) for b, s, l, _ in dets]
         if self.mask_head is not None:
             bl = [d["boxes"] for d in out]
             ml = self.mask_predictor(self.mask_head(self.mask_roi_pool(feats, bl, image_sizes)))
             for d, m, size in zip(out, ml.split([len(b) for b in bl]), image_sizes):
                 d["masks"] = postprocess_masks(m, d["labels"], d["boxes"], size, None)
+                d.__class__ = MaskDetections
         if self.keypoint_head is not None:
             bl = [d["boxes"] for d in out]
             kl = self.keypoint_predictor(self.keypoint_head(self.keypoint_roi_pool(feats, bl, image_sizes)))
@@ -522,7 +568,7 @@ def _one_stage_postprocess(scores_per_level, boxes_fn, image_size, score_thresh,
         ll.append(labels)
     b, s, l = torch.cat(bl), torch.cat(sl), torch.cat(ll)
     k = V.batched_nms(b, s, l, nms_thresh)[:dets]
-    return {"boxes": b[k], "scores": s[k], "labels": l[k]}
+    return Detections(boxes=b[k], scores=s[k], labels=l[k])
 
 
 class RetinaNet(nn.Module):
@@ -723,8 +769,12 @@ class Ssd300(nn.Module):
                 ll.append(torch.full_like(t.values, c, dtype=torch.int64))
             bx, sc, lb = torch.cat(bl), torch.cat(sl), torch.cat(ll)
             k = V.batched_nms(bx, sc, lb, nt)[:dets]
-            out.append({"boxes": DetectionTransform.rescale(bx[k], (300, 300), orig[b]), "scores": sc[k], "labels": lb[k]})
+            out.append(SsdDetections(boxes=DetectionTransform.rescale(bx[k], (300, 300), orig[b]), scores=sc[k], labels=lb[k]))
         return out
 
 
 def ssd300_vgg16(num_classes=91, **kw): return Ssd300(num_classes, **kw)                    # noqa: E704
+
+
+# the reference's names for the heads (rpn.rs, faster_rcnn.rs:105, mask_rcnn.rs)
+RpnHead, TwoMlpHead, MaskHead, MaskPredictor = RPNHead, TwoMLPHead, MaskRCNNHeads, MaskRCNNPredictor

@@ -540,23 +540,32 @@ def register_model(name: str, ctor: Callable) -> None:
     _REG.register(name, ctor)
 
 
-def create_feature_extractor(model: torch.nn.Module, return_nodes: Sequence[str]) -> torch.nn.Module:
-    """Wrap ``model`` so that ``forward`` returns a dict of the outputs of the named submodules (forward hooks)."""
+class FeatureExtractor(nn.Module):
+    """``forward`` returns ``{node: output}`` for the named submodules, captured by forward hooks during one pass of ``model``
+    (ferrotorch-vision/src/models/feature_extractor.rs:63)."""
 
-    class _FE(nn.Module):
-        def __init__(self):
-            super().__init__()
-            self.model, self.nodes = model, list(return_nodes)
-            mods = dict(model.named_modules())
-            missing = [n for n in self.nodes if n not in mods]
-            if missing:
-                raise InvalidArgument(f"no submodule named {missing}")
-            self._out: Dict[str, torch.Tensor] = {}
-            for n in self.nodes:
-                mods[n].register_forward_hook(lambda m, i, o, n=n: self._out.__setitem__(n, o))
+    def __init__(self, model: torch.nn.Module, return_nodes: Sequence[str]):
+        super().__init__()
+        self.model, self.nodes = model, list(return_nodes)
+        mods = dict(model.named_modules())
+        missing = [n for n in self.nodes if n not in mods]
+        if missing:
+            raise InvalidArgument(f"no submodule named {missing}")
+        self._out: Dict[str, torch.Tensor] = {}
+        for n in self.nodes:
+            mods[n].register_forward_hook(lambda m, i, o, n=n: self._out.__setitem__(n, o))
 
-        def forward(self, x):
-            self._out.clear()
-            self.model(x)
-            return dict(self._out)
-    return _FE()
+    def return_nodes(self) -> List[str]:
+        return list(self.nodes)
+
+    def forward(self, x):
+        self._out.clear()
+        self.model(x)
+        return dict(self._out)
+
+
+def create_feature_extractor(model: torch.nn.Module, return_nodes: Sequence[str]) -> FeatureExtractor:
+    return FeatureExtractor(model, return_nodes)
+
+
+ModelConstructor = Callable[..., torch.nn.Module]            # what the registry stores (ferrotorch-vision/src/models/registry.rs:71)

@@ -92,6 +92,17 @@ class DeepLabV3(_SegModel):
     pass
 
 
+FcnHead, DeepLabV3Head = FCNHead, DeepLabHead                 # ferrotorch-vision/src/models/segmentation/{fcn.rs, deeplabv3.rs}
+
+
+class ResNet50Dilated(_ResNetBody):
+    """ResNet-50 trunk with layers 3 and 4 dilated instead of strided (output stride 8); ``forward`` returns ``{"aux": layer3, "out": layer4}``
+    (ferrotorch-vision/src/models/segmentation/backbone.rs)."""
+
+    def __init__(self):
+        super().__init__(M.ResNet(M.Bottleneck, [3, 4, 6, 3], replace_stride_with_dilation=(False, True, True)))
+
+
 def _dilated_resnet50():
     return _ResNetBody(M.ResNet(M.Bottleneck, [3, 4, 6, 3], replace_stride_with_dilation=(False, True, True)))
 

@@ -396,3 +396,44 @@ def test_quantised_weight_structs():
     with pytest.raises(FerrotorchError):
         M.dequantize_hqq(M.HqqWeights(8, packed[:5], scale, zero, 3, 8))
     assert M.gguf_key_to_hf("blk.3.attn_q.weight") == "model.layers.3.self_attn.q_proj.weight" and M.LlamaKvCache is M.KvCache
+
+
+def test_vision_io_structs_samples_and_detection_names(tmp_path):
+    from ferrotorch_b200 import vision as V
+    img = torch.rand(3, 5, 7)
+    raw = V.tensor_to_raw_image(img * 1.5 - 0.2)              # out-of-range values clamp
+    assert (raw.width, raw.height, raw.channels) == (7, 5, 3) and len(raw.data) == 105
+    back = V.raw_image_to_tensor(raw)
+    assert torch.equal(back, ((img * 1.5 - 0.2).double().clamp(0, 1) * 255).round().float().div(255))
+    V.write_tensor_as_image(tmp_path / "a.png", img)
+    got = V.read_image_as_tensor(tmp_path / "a.png")
+    assert got.shape == (3, 5, 7) and (got - img).abs().max() <= 0.5 / 255 + 1e-6
+    rgba = V.read_image_rgba(tmp_path / "a.png")
+    assert rgba.channels == 4 and rgba.data[3] == 255 and rgba.data[:3] == V.read_image_raw(tmp_path / "a.png").data[:3]
+    for bad in (torch.rand(5, 7), torch.rand(2, 5, 7)):
+        with pytest.raises(InvalidArgument):
+            V.tensor_to_raw_image(bad)
+    with pytest.raises(InvalidArgument):
+        V.read_image_rgba(tmp_path / "missing.png")
+    s = V.Mnist.synthetic(4)[0]
+    assert isinstance(s, V.MnistSample) and s.image.shape == (1, 28, 28) and s[1] == s.label
+    x, y = V.Cifar10.synthetic(4)[1]
+    assert x.shape == (3, 32, 32) and isinstance(V.Cifar10.synthetic(2)[0], V.CifarSample)
+    assert V.Split.Train is not V.Split.Test and V.IMAGENET_MEAN == (0.485, 0.456, 0.406) and V.FPN_OUT_CHANNELS == 256
+    assert sum(a * f * f for a, f in zip(V.SSD_ANCHORS_PER_SCALE, V.SSD_FM_SIZES)) == V.SSD_TOTAL_ANCHORS == 8732
+    d = V.Detections(boxes=torch.zeros(2, 4), scores=torch.ones(2), labels=torch.tensor([1, 2]))
+    assert d.boxes is d["boxes"] and d.labels.tolist() == [1, 2] and isinstance(V.MaskDetections(d), V.Detections)
+    with pytest.raises(AttributeError):
+        d.masks
+    c = V.RpnConfig.default_eval((64, 96))
+    assert (c.pre_nms_top_n, c.post_nms_top_n, c.nms_thresh, c.min_size, c.score_thresh, c.image_size) == (1000, 1000, 0.7, 1e-3, 0.0, (64, 96))
+    rpn = V.Rpn(V.AnchorGenerator(((32,),), ((1.0,),)), V.RpnHead(8, 1), V.RpnConfig(pre_nms_top_n=5, post_nms_top_n=3))
+    assert (rpn.pre, rpn.post) == (5, 3)
+    fe = V.create_feature_extractor(V.resnet18(num_classes=3).eval(), ["layer1", "layer3"])
+    out = fe(torch.randn(1, 3, 32, 32))
+    assert isinstance(fe, V.FeatureExtractor) and fe.return_nodes() == ["layer1", "layer3"] and out["layer3"].shape[1] == 256
+    body = V.ResNet50Dilated().eval()
+    with torch.no_grad():
+        f = body(torch.randn(1, 3, 64, 64))
+    assert f["out"].shape == (1, 2048, 8, 8) and f["aux"].shape == (1, 1024, 8, 8)
+    assert V.FcnHead(16, 3)(torch.randn(2, 16, 4, 4)).shape == (2, 3, 4, 4) and V.TwoMlpHead is not None and V.MaskPredictor is not None
