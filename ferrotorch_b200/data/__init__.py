@@ -456,6 +456,143 @@ def from_arrow(array) -> torch.Tensor:
     return torch.from_numpy(array.to_numpy(zero_copy_only=False))
 
 
+def shuffle_with_seed(indices: List[int], seed: int) -> None:
+    """In-place Fisher-Yates shuffle driven by xorshift64 (13 / 7 / 17; seed 0 becomes 0xdeadbeefcafe) with unbiased bounded draws (128-bit
+    multiply, rejection below ``2^64 mod bound``), walking ``i`` from the last index down (ferrotorch-data/src/sampler.rs:17-69): the shuffle
+    primitive shared by the random and distributed samplers, so a given seed orders a dataset the same way everywhere."""
+    M = (1 << 64) - 1
+    state = (int(seed) & M) or 0xDEADBEEFCAFE
+
+    def nxt():
+        nonlocal state
+        x = state
+        x ^= (x << 13) & M
+        x ^= x >> 7
+        x ^= (x << 17) & M
+        state = x
+        return x
+    for i in range(len(indices) - 1, 0, -1):
+        bound = i + 1
+        prod = nxt() * bound
+        if (prod & M) < bound:
+            t = ((1 << 64) - bound) % bound
+            while (prod & M) < t:
+                prod = nxt() * bound
+        j = prod >> 64
+        indices[i], indices[j] = indices[j], indices[i]
+
+
+def default_collate_pair(samples: Sequence):
+    """``[(input, target), ...]`` -> ``(stack(inputs), stack(targets))`` (ferrotorch-data/src/collate.rs:32)."""
+    if len(samples) == 0:
+        raise InvalidArgument("default_collate_pair: empty sample list")
+    xs, ys = zip(*samples)
+    return torch.stack([torch.as_tensor(x) for x in xs], 0), torch.stack([torch.as_tensor(y) for y in ys], 0)
+
+
+class BatchIter:
+    """Iterator over the raw (uncollated) batches of a dataset: each item is the list of samples of one batch, in sampler order
+    (ferrotorch-data/src/dataloader.rs, ``BatchIter``)."""
+
+    def __init__(self, dataset, batches: Iterable[Sequence[int]]):
+        self.dataset, self._it = dataset, iter(batches)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        return [self.dataset[i] for i in next(self._it)]
+
+
+# -- transforms with their own counter-based random stream (ferrotorch-data/src/transforms.rs) ------------------------------------------
+class Transform:
+    """Base of the tensor transforms: ``apply(x)`` (also ``__call__``)."""
+
+    def apply(self, x):
+        raise NotImplementedError
+
+    def __call__(self, x):
+        return self.apply(x)
+
+
+class _SplitMixCounter:
+    _M = (1 << 64) - 1
+
+    def __init__(self):
+        self.seed, self.counter, self._lock = 0, 0, threading.Lock()
+
+    def manual_seed(self, seed: int) -> None:
+        with self._lock:
+            self.seed, self.counter = int(seed) & self._M, 0
+
+    def random(self) -> float:
+        with self._lock:
+            c = self.counter
+            self.counter += 1
+        z = (self.seed + c * 0x9E3779B97F4A7C15) & self._M
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & self._M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & self._M
+        return (z ^ (z >> 31)) / float(self._M)
+
+
+_transform_rng = _SplitMixCounter()
+
+
+def manual_seed(seed: int) -> None:
+    """Seeds the transforms' random stream and restarts its counter: draw ``n`` afterwards is splitmix64 of ``seed + n * golden``
+    (transforms.rs:331-350)."""
+    _transform_rng.manual_seed(seed)
+
+
+class ToTensor(Transform):
+    """Image (PIL image, ``[H, W, C]`` uint8 array) -> float ``[C, H, W]`` in [0, 1]; a tensor passes through unchanged, as the reference's
+    tensor-to-tensor form does (transforms.rs:221-270)."""
+
+    def apply(self, x):
+        if torch.is_tensor(x):
+            return x
+        a = np.asarray(x.convert("RGB") if hasattr(x, "convert") else x)
+        if a.ndim == 2:
+            a = a[:, :, None]
+        if a.ndim != 3 or 0 in a.shape:
+            raise InvalidArgument(f"ToTensor: expected an [H, W, C] image with non-zero sides, got shape {list(a.shape)}")
+        return torch.from_numpy(np.ascontiguousarray(a)).permute(2, 0, 1).float().div(255.0)
+
+
+class RandomHorizontalFlip(Transform):
+    """Reverses the last dimension with probability ``p`` (transforms.rs:288-390)."""
+
+    def __init__(self, p: float = 0.5):
+        if not 0.0 <= p <= 1.0:
+            raise InvalidArgument(f"RandomHorizontalFlip: p must be in [0, 1], got {p}")
+        self.p = p
+
+    def apply(self, x):
+        if x.dim() == 0:
+            raise InvalidArgument("RandomHorizontalFlip: input must be at least 1-D")
+        if _transform_rng.random() >= self.p or x.shape[-1] <= 1:
+            return x
+        return x.detach().flip(-1)
+
+
+class RandomCrop(Transform):
+    """A ``height x width`` window of the last two dimensions at a random origin ``floor(u * (in - crop))`` per axis (no draw for an axis that
+    already fits) (transforms.rs:403-470)."""
+
+    def __init__(self, height: int, width: Optional[int] = None):
+        self.height, self.width = int(height), int(width if width is not None else height)
+
+    def apply(self, x):
+        if x.dim() < 2:
+            raise InvalidArgument(f"RandomCrop: input must be at least 2-D, got shape {list(x.shape)}")
+        H, W = x.shape[-2:]
+        if self.height > H or self.width > W:
+            raise InvalidArgument(f"RandomCrop: crop size ({self.height}x{self.width}) is larger than input spatial size ({H}x{W})")
+        top = 0 if H == self.height else int(_transform_rng.random() * (H - self.height))
+        left = 0 if W == self.width else int(_transform_rng.random() * (W - self.width))
+        return x.detach()[..., top: top + self.height, left: left + self.width].contiguous()
+
+
 class Compose:
     def __init__(self, fns: Sequence[Callable]):
         self.fns = list(fns)
@@ -464,6 +601,8 @@ class Compose:
         for f in self.fns:
             x = f(x)
         return x
+
+    apply = __call__
 
 
 class Normalize:

@@ -7,13 +7,14 @@ JsonSchemaProcessor), gpu_dispatch.rs:778 (compute_mask_gpu)}; the mask kernel r
 """
 from __future__ import annotations
 
+import enum
 import json
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..errors import InvalidArgument
+from ..errors import FerrotorchError, InvalidArgument
 
 
 @dataclass
@@ -261,6 +262,70 @@ class JsonGrammar:
         return None
 
 
+class GrammarError(FerrotorchError):
+    """Failure of the constrained-decoding layer (ferrotorch-grammar/src/json_schema.rs:41): ``kind`` is ``schema`` (the schema does not
+    compile), ``step`` (a token was fed that the grammar cannot take) or ``invalid_token_id``."""
+
+    def __init__(self, kind: str, message: str):
+        super().__init__(message)
+        self.kind = kind
+
+    @classmethod
+    def invalid_token_id(cls, token_id: int) -> "GrammarError":
+        return cls("invalid_token_id", f"token id {token_id} out of range")
+
+
+class BooleanEmissionStage(enum.Enum):
+    """How much of a ``true`` / ``false`` literal has been produced (ferrotorch-grammar/src/state.rs:193)."""
+    Start = "start"
+    PartialTrue = "partial_true"
+    PartialFalse = "partial_false"
+    Done = "done"
+
+    @staticmethod
+    def of(text: str):
+        """``(stage, remaining)`` for the characters emitted so far; ``None`` when they start neither literal."""
+        if text == "":
+            return BooleanEmissionStage.Start, ""
+        for lit, st in (("true", BooleanEmissionStage.PartialTrue), ("false", BooleanEmissionStage.PartialFalse)):
+            if lit.startswith(text):
+                return (BooleanEmissionStage.Done, "") if text == lit else (st, lit[len(text):])
+        return None
+
+
+@dataclass
+class PackedVocab:
+    """Vocabulary flattened for a device-side mask kernel (ferrotorch-grammar/src/gpu_dispatch.rs:709): ``chars`` holds the code points of
+    all tokens back to back, token ``i`` spans ``chars[offsets[i]:offsets[i + 1]]``."""
+    offsets: List[int]
+    chars: List[int]
+    max_token_len: int
+
+    @classmethod
+    def pack(cls, vocab: Sequence[str]) -> "PackedVocab":
+        offsets, chars, longest = [0], [], 0
+        for tok in vocab:
+            chars.extend(ord(c) for c in tok)
+            offsets.append(len(chars))
+            longest = max(longest, len(tok))
+        return cls(offsets, chars, longest)
+
+    def vocab_size(self) -> int:
+        return len(self.offsets) - 1
+
+    def token(self, i: int) -> str:
+        if not 0 <= i < self.vocab_size():
+            raise GrammarError.invalid_token_id(i)
+        return "".join(chr(c) for c in self.chars[self.offsets[i]: self.offsets[i + 1]])
+
+    def tensors(self, device="cpu"):
+        """``(offsets int32 [V + 1], chars int32 [total])`` on ``device``."""
+        return torch.tensor(self.offsets, dtype=torch.int32, device=device), torch.tensor(self.chars, dtype=torch.int32, device=device)
+
+    def __repr__(self):
+        return f"PackedVocab(offsets=<{len(self.offsets)} entries>, chars=<{len(self.chars)} entries>, max_token_len={self.max_token_len})"
+
+
 @dataclass
 class TokenMask:
     allowed: torch.Tensor            # bool [vocab]
@@ -282,6 +347,8 @@ class JsonSchemaProcessor:
         self.text = ""
 
     def advance(self, token_id: int) -> None:
+        if not 0 <= token_id < len(self.vocab):
+            raise GrammarError.invalid_token_id(token_id)
         if token_id != self.eos_id:
             self.text += self.vocab[token_id]
 

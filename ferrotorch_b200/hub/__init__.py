@@ -8,10 +8,12 @@ Reference parity: ferrotorch-hub/src/{registry.rs:58-1117, download.rs:26, cache
 """
 from __future__ import annotations
 
+import enum
 import hashlib
 import json
 import os
 import shutil
+import urllib.parse
 import urllib.request
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -77,6 +79,18 @@ def sha256_file(path) -> str:
     return h.hexdigest()
 
 
+class WeightsFormat(enum.Enum):
+    """ferrotorch-hub/src/registry.rs:9."""
+    SafeTensors = "safetensors"
+    FerrotorchStateDict = "ferrotorch_state_dict"
+
+
+class EntryKind(enum.Enum):
+    """A registry row is a usable model or a small fixture kept for tests (registry.rs:26)."""
+    Model = "model"
+    Fixture = "fixture"
+
+
 @dataclass
 class ModelInfo:
     name: str
@@ -86,6 +100,21 @@ class ModelInfo:
     params: Optional[int] = None
     sha256: Dict[str, str] = field(default_factory=dict)
     description: str = ""
+    weights_format: WeightsFormat = WeightsFormat.SafeTensors
+    kind: EntryKind = EntryKind.Model
+
+
+def default_cache_dir() -> Path:
+    """``$FT_HUB_CACHE`` or ``~/.cache/ferrotorch_b200/hub`` (the reference keeps ``~/.ferrotorch/hub``; cache.rs:14)."""
+    return Path(os.environ.get("FT_HUB_CACHE", Path.home() / ".cache" / "ferrotorch_b200" / "hub"))
+
+
+def with_auth(req: urllib.request.Request) -> urllib.request.Request:
+    """Adds ``Authorization: Bearer <token>`` when a Hugging Face token is configured (auth.rs:64)."""
+    tok = hf_token()
+    if tok:
+        req.add_header("Authorization", f"Bearer {tok}")
+    return req
 
 
 _REGISTRY: Dict[str, ModelInfo] = {m.name: m for m in [
@@ -107,9 +136,110 @@ def list_models(family: Optional[str] = None) -> List[ModelInfo]:
     return [m for m in _REGISTRY.values() if family is None or m.family == family]
 
 
-def search_models(query: str) -> List[ModelInfo]:
+# -- Hugging Face Hub discovery (ferrotorch-hub/src/discovery.rs) --------------------------------------------------------------------------
+HUB_BASE = "https://huggingface.co"
+
+
+@dataclass(frozen=True)
+class HfRepoFile:
+    rfilename: str
+
+
+@dataclass
+class HfModelSummary:
+    """One row of a Hub search (discovery.rs:53). ``author`` falls back to the namespace of ``model_id``."""
+    model_id: str
+    author: Optional[str] = None
+    downloads: Optional[int] = None
+    likes: Optional[int] = None
+    tags: List[str] = field(default_factory=list)
+    library_name: Optional[str] = None
+    pipeline_tag: Optional[str] = None
+
+    @classmethod
+    def from_json(cls, d: dict):
+        mid = d.get("modelId", d.get("id"))
+        if not isinstance(mid, str):
+            raise InvalidArgument("ferrotorch-hub: failed to parse Hub response: no modelId / id")
+        kw = dict(model_id=mid, author=d.get("author") or (mid.split("/", 1)[0] if "/" in mid else None), downloads=d.get("downloads"),
+                  likes=d.get("likes"), tags=list(d.get("tags") or []), library_name=d.get("library_name"), pipeline_tag=d.get("pipeline_tag"))
+        if cls is HfModelInfo:
+            kw["siblings"] = [HfRepoFile(f["rfilename"]) for f in d.get("siblings") or [] if isinstance(f, dict) and "rfilename" in f]
+        return cls(**kw)
+
+
+@dataclass
+class HfModelInfo(HfModelSummary):
+    """A repository's metadata with its file list (discovery.rs:88)."""
+    siblings: List[HfRepoFile] = field(default_factory=list)
+
+    def filenames(self) -> List[str]:
+        return [f.rfilename for f in self.siblings]
+
+
+@dataclass(frozen=True)
+class SearchQuery:
+    """Builder of a ``/api/models`` query (discovery.rs:123-200)."""
+    search: Optional[str] = None
+    pipeline_tag: Optional[str] = None
+    library: Optional[str] = None
+    limit: Optional[int] = None
+    sort: Optional[str] = None
+
+    def _with(self, **kw):
+        import dataclasses
+        return dataclasses.replace(self, **kw)
+
+    def with_search(self, v: str): return self._with(search=v)                        # noqa: E704
+    def with_pipeline_tag(self, v: str): return self._with(pipeline_tag=v)            # noqa: E704
+    def with_library(self, v: str): return self._with(library=v)                      # noqa: E704
+    def with_limit(self, v: int): return self._with(limit=int(v))                     # noqa: E704
+    def with_sort(self, v: str): return self._with(sort=v)                            # noqa: E704
+
+    def to_query_string(self) -> str:
+        enc = lambda t: urllib.parse.quote(t, safe="-_.~")                            # noqa: E731
+        parts = [f"{k}={enc(v)}" for k, v in (("search", self.search), ("pipeline_tag", self.pipeline_tag), ("library", self.library)) if v is not None]
+        if self.limit is not None:
+            parts.append(f"limit={self.limit}")
+        if self.sort is not None:
+            parts.append(f"sort={enc(self.sort)}")
+        return "/api/models" + ("?" + "&".join(parts) if parts else "")
+
+
+def _http_get_json(url: str, timeout: float = 30.0):
+    if os.environ.get("FT_HUB_OFFLINE") == "1":
+        raise HubOffline(f"FT_HUB_OFFLINE=1; would fetch {url}")
+    try:
+        with urllib.request.urlopen(with_auth(urllib.request.Request(url)), timeout=timeout) as r:
+            return json.loads(r.read().decode("utf-8"))
+    except OSError as e:
+        raise HubOffline(f"cannot reach {url}: {e}") from e
+    except ValueError as e:
+        raise InvalidArgument(f"ferrotorch-hub: failed to parse Hub response ({url}): {e}") from None
+
+
+def search_models(query) -> list:
+    """A string searches the built-in registry (name, repository, family). A :class:`SearchQuery` asks the Hugging Face Hub and returns
+    :class:`HfModelSummary` rows (discovery.rs:222); without network that raises :class:`HubOffline`."""
+    if isinstance(query, SearchQuery):
+        rows = _http_get_json(HUB_BASE + query.to_query_string())
+        if not isinstance(rows, list):
+            raise InvalidArgument("ferrotorch-hub: failed to parse Hub search response: expected a list")
+        return [HfModelSummary.from_json(r) for r in rows]
     q = query.lower()
     return [m for m in _REGISTRY.values() if q in m.name.lower() or q in m.repo.lower() or q in m.family]
+
+
+def get_model(repo_id: str) -> HfModelInfo:
+    """Hub metadata of one repository, file list included (discovery.rs:261)."""
+    if not repo_id:
+        raise InvalidArgument("get_model: repo_id must not be empty")
+    return HfModelInfo.from_json(_http_get_json(f"{HUB_BASE}/api/models/{repo_id}"))
+
+
+def get_model_info(name: str) -> Optional[ModelInfo]:
+    """Registry row by name, ``None`` when unknown (registry.rs:1122); :func:`model_info` is the raising form."""
+    return _REGISTRY.get(name)
 
 
 def register_model(info: ModelInfo) -> None:

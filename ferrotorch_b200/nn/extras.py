@@ -185,6 +185,17 @@ def relative_position_score_mod(bias: torch.Tensor):
     return mod
 
 
+def relative_position_bias_score_mod(bias_table: torch.Tensor, max_dist: int):
+    """One shared 1-D table ``[2 * max_dist + 1]`` indexed by ``clamp(q_idx - kv_idx, -max_dist, max_dist) + max_dist``
+    (ferrotorch-nn/src/flex_attention.rs:755); :func:`relative_position_score_mod` is the per-head form."""
+    table = bias_table.reshape(-1)
+
+    def mod(score, b, h, q_idx, kv_idx):
+        rel = ((q_idx - kv_idx).clamp(-max_dist, max_dist) + max_dist).clamp_max(table.numel() - 1)
+        return score + table.to(score.device)[rel]
+    return mod
+
+
 def flex_attention(q, k, v, score_mod: Optional[Callable] = None, block_mask: Optional[BlockMask] = None, scale: Optional[float] = None):
     """Attention on ``[B, H, S, D]`` with an arbitrary score modification and/or block mask."""
     B, H, Sq, D = q.shape
@@ -267,9 +278,90 @@ def clip_grad_value_(parameters: Iterable[torch.Tensor], clip_value: float) -> N
 PackedSequence = torch.nn.utils.rnn.PackedSequence
 pack_padded_sequence = torch.nn.utils.rnn.pack_padded_sequence
 pad_packed_sequence = torch.nn.utils.rnn.pad_packed_sequence
-interpolate = F.interpolate
-grid_sample = F.grid_sample
+class InterpolateMode(enum.Enum):
+    """ferrotorch-nn/src/upsample.rs:32."""
+    Nearest = "nearest"
+    Bilinear = "bilinear"
+    Bicubic = "bicubic"
+
+
+class GridSampleMode(enum.Enum):
+    """ferrotorch-nn/src/upsample.rs:54."""
+    Bilinear = "bilinear"
+    Nearest = "nearest"
+
+
+class GridSamplePaddingMode(enum.Enum):
+    """ferrotorch-nn/src/upsample.rs:43."""
+    Zeros = "zeros"
+    Border = "border"
+    Reflection = "reflection"
+
+
+class GeluApproximate(enum.Enum):
+    """``None`` = exact erf form, ``Tanh`` = tanh polynomial, ``Sigmoid`` = ``x * sigmoid(1.702 x)`` (ferrotorch-core/src/grad_fns/activation.rs:254)."""
+    None_ = "none"
+    Tanh = "tanh"
+    Sigmoid = "sigmoid"
+
+    def __str__(self):
+        return self.value
+
+
+def _enum_value(v):
+    return v.value if isinstance(v, enum.Enum) else v
+
+
+def gelu(x: torch.Tensor, approximate="none") -> torch.Tensor:
+    """GELU in the three forms of :class:`GeluApproximate` (a string or the enum)."""
+    a = _enum_value(approximate)
+    if a == "sigmoid":
+        return x * torch.sigmoid(1.702 * x)
+    if a not in ("none", "tanh"):
+        raise InvalidArgument(f"gelu: unknown approximation {approximate!r}")
+    return F.gelu(x, approximate=a)
+
+
+gelu_with = gelu                                             # ferrotorch-core's name for the form that takes the mode
+
+
+class GELU(Module):
+    def __init__(self, approximate="none"):
+        super().__init__()
+        self.approximate = _enum_value(approximate)
+        if self.approximate not in ("none", "tanh", "sigmoid"):
+            raise InvalidArgument(f"GELU: unknown approximation {approximate!r}")
+
+    def forward(self, x):
+        return gelu(x, self.approximate)
+
+    def extra_repr(self):
+        return f"approximate={self.approximate!r}"
+
+
+def interpolate(x, size=None, scale_factor=None, mode="nearest", align_corners=None, **kw):
+    """``F.interpolate`` that also takes an :class:`InterpolateMode`."""
+    return F.interpolate(x, size=size, scale_factor=scale_factor, mode=_enum_value(mode), align_corners=align_corners, **kw)
+
+
+def grid_sample(x, grid, mode="bilinear", padding_mode="zeros", align_corners=False):
+    """``F.grid_sample`` that also takes :class:`GridSampleMode` / :class:`GridSamplePaddingMode`."""
+    return F.grid_sample(x, grid, mode=_enum_value(mode), padding_mode=_enum_value(padding_mode), align_corners=align_corners)
+
+
 affine_grid = F.affine_grid
+
+# functional pooling / reshaping forms the reference exports at the crate root (ferrotorch-nn/src/pooling.rs, upsample.rs)
+(max_pool1d, max_pool2d, max_pool3d, avg_pool1d, avg_pool2d, avg_pool3d, adaptive_avg_pool1d, adaptive_avg_pool2d, adaptive_avg_pool3d, adaptive_max_pool1d,
+ adaptive_max_pool2d, adaptive_max_pool3d, lp_pool1d, lp_pool2d, max_unpool2d, pixel_shuffle, pixel_unshuffle, unfold, fold) = (
+    F.max_pool1d, F.max_pool2d, F.max_pool3d, F.avg_pool1d, F.avg_pool2d, F.avg_pool3d, F.adaptive_avg_pool1d, F.adaptive_avg_pool2d, F.adaptive_avg_pool3d,
+    F.adaptive_max_pool1d, F.adaptive_max_pool2d, F.adaptive_max_pool3d, F.lp_pool1d, F.lp_pool2d, F.max_unpool2d, F.pixel_shuffle, F.pixel_unshuffle,
+    F.unfold, F.fold)
+
+# hook signatures (ferrotorch-nn/src/hooks.rs:37-48)
+ForwardHook = Callable[[torch.Tensor, torch.Tensor], None]               # (input, output)
+ForwardPreHook = Callable[[torch.Tensor], torch.Tensor]                  # input -> replacement input
+BackwardHook = Callable[[torch.Tensor, torch.Tensor], None]              # (grad_input, grad_output)
 
 
 def functional_pad_1d(x, pad, mode="constant", value=0.0):
@@ -372,6 +464,9 @@ class QuantizedModel(Module):
 
     def forward(self, *a, **k):
         return self.model(*a, **k)
+
+
+QatModel = QuantizedModel                                    # ferrotorch-nn/src/qat.rs
 
 
 def prepare_qat(model: torch.nn.Module, cfg: Optional[QatConfig] = None) -> QuantizedModel:

@@ -10,6 +10,8 @@ from dataclasses import dataclass, asdict
 from typing import Dict, Iterable, List, Optional
 
 import torch
+
+from ..errors import InvalidArgument
 import torch.optim.swa_utils
 
 from .. import ops
@@ -160,11 +162,48 @@ class ExponentialMovingAverage:
             s.copy_(n)
 
 
+class AveragingStrategy:
+    """How :class:`AveragedModel` folds a new snapshot in (ferrotorch-optim/src/swa.rs:42): ``Swa`` is the equal-weight running mean,
+    ``Ema(decay)`` is ``decay * avg + (1 - decay) * new``."""
+
+    def __init__(self, kind: str, decay: float = 0.0):
+        self.kind, self.decay = kind, float(decay)
+
+    @classmethod
+    def Ema(cls, decay: float) -> "AveragingStrategy":  # noqa: N802
+        if not 0.0 <= decay <= 1.0:
+            raise InvalidArgument(f"EMA decay must be in [0, 1], got {decay}")
+        return cls("ema", decay)
+
+    def avg_fn(self):
+        if self.kind == "swa":
+            return None
+        d = self.decay
+        return lambda avg, new, n: d * avg + (1.0 - d) * new
+
+    def __eq__(self, other):
+        return isinstance(other, AveragingStrategy) and (self.kind, self.decay) == (other.kind, other.decay)
+
+    def __hash__(self):
+        return hash((self.kind, self.decay))
+
+    def __repr__(self):
+        return "AveragingStrategy.Swa" if self.kind == "swa" else f"AveragingStrategy.Ema({self.decay})"
+
+
+AveragingStrategy.Swa = AveragingStrategy("swa")
+
+
 class AveragedModel(torch.nn.Module):
-    """Stochastic weight averaging: running equal (or custom ``avg_fn``) average of a model's parameters."""
+    """Stochastic weight averaging: running equal (or custom ``avg_fn``) average of a model's parameters; ``avg_fn`` may be an
+    :class:`AveragingStrategy`."""
 
     def __init__(self, model: torch.nn.Module, avg_fn=None, use_buffers: bool = False):
         super().__init__()
+        if isinstance(avg_fn, AveragingStrategy):
+            self.strategy, avg_fn = avg_fn, avg_fn.avg_fn()
+        else:
+            self.strategy = None
         self.module = copy.deepcopy(model)
         self.avg_fn, self.use_buffers = avg_fn, use_buffers
         self.register_buffer("n_averaged", torch.tensor(0, dtype=torch.long))

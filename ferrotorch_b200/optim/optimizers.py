@@ -247,20 +247,176 @@ class Adam(AdamW):
     _decoupled = False
 
 
-def _named(torch_cls, name, doc):
-    return type(name, (torch_cls, Optimizer), {"__doc__": doc, "__module__": __name__})
+def _named(torch_cls, name, doc, cfg_cls=None):
+    """A torch optimiser under this package's name and base class. Its second argument may be the matching ``<Name>Config`` (the reference's
+    constructor form, ``Adamax::new(params, AdamaxConfig::default().with_lr(..))``); keyword arguments still work and override the config."""
+    def __init__(self, params, config=None, **kw):
+        if config is not None and hasattr(config, "__dataclass_fields__"):
+            import dataclasses
+            kw = {**dataclasses.asdict(config), **kw}
+        elif config is not None:
+            kw.setdefault("lr", config)                      # positional learning rate, as torch allows
+        self.config = config
+        torch_cls.__init__(self, params, **kw)
+    return type(name, (torch_cls, Optimizer), {"__doc__": doc, "__module__": __name__, "__init__": __init__})
 
 
-Adamax = _named(torch.optim.Adamax, "Adamax", "Adamax (infinity-norm Adam).")
-NAdam = _named(torch.optim.NAdam, "NAdam", "Adam with Nesterov momentum.")
-RAdam = _named(torch.optim.RAdam, "RAdam", "Rectified Adam.")
-Adagrad = _named(torch.optim.Adagrad, "Adagrad", "Adagrad.")
-Adadelta = _named(torch.optim.Adadelta, "Adadelta", "Adadelta.")
-Rmsprop = _named(torch.optim.RMSprop, "Rmsprop", "RMSprop.")
-Rprop = _named(torch.optim.Rprop, "Rprop", "Resilient backpropagation.")
-Asgd = _named(torch.optim.ASGD, "Asgd", "Averaged SGD.")
-SparseAdam = _named(torch.optim.SparseAdam, "SparseAdam", "Adam for sparse gradients (embedding tables).")
-Lbfgs = _named(torch.optim.LBFGS, "Lbfgs", "L-BFGS with optional strong-Wolfe line search (``line_search_fn='strong_wolfe'``).")
+# -- configs of the remaining optimisers (defaults: ferrotorch-optim/src/{adadelta,adagrad,adamax,asgd,nadam,radam,rmsprop,rprop,sparse_adam,lbfgs}.rs) --
+@dataclass(frozen=True)
+class AdadeltaConfig(_Cfg):
+    lr: float = 1.0
+    rho: float = 0.9
+    eps: float = 1e-6
+    weight_decay: float = 0.0
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class AdagradConfig(_Cfg):
+    lr: float = 0.01
+    lr_decay: float = 0.0
+    weight_decay: float = 0.0
+    initial_accumulator_value: float = 0.0
+    eps: float = 1e-10
+    maximize: bool = False
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class AdamaxConfig(_Cfg):
+    lr: float = 2e-3
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class AsgdConfig(_Cfg):
+    lr: float = 1e-2
+    lambd: float = 1e-4
+    alpha: float = 0.75
+    t0: float = 1e6
+    weight_decay: float = 0.0
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class NAdamConfig(_Cfg):
+    lr: float = 2e-3
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    momentum_decay: float = 4e-3
+    decoupled_weight_decay: bool = False
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class RAdamConfig(_Cfg):
+    lr: float = 1e-3
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    decoupled_weight_decay: bool = False
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class RmspropConfig(_Cfg):
+    lr: float = 0.01
+    alpha: float = 0.99
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    momentum: float = 0.0
+    centered: bool = False
+    maximize: bool = False
+    foreach: bool = False
+
+
+@dataclass(frozen=True)
+class RpropConfig(_Cfg):
+    lr: float = 1e-2
+    etas: tuple = (0.5, 1.2)
+    step_sizes: tuple = (1e-6, 50.0)
+
+
+@dataclass(frozen=True)
+class SparseAdamConfig(_Cfg):
+    lr: float = 1e-3
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+
+
+@dataclass(frozen=True)
+class LbfgsConfig(_Cfg):
+    lr: float = 1.0
+    max_iter: int = 20
+    max_eval: Optional[int] = None
+    tolerance_grad: float = 1e-7
+    tolerance_change: float = 1e-9
+    history_size: int = 10
+    line_search_fn: Optional[str] = None                     # None or "strong_wolfe"
+
+
+@dataclass(frozen=True)
+class AdafactorConfig(_Cfg):
+    """ferrotorch-optim/src/adafactor.rs:28-60. ``relative_step`` (default on) ignores ``lr`` and uses ``t^-0.5`` (with ``warmup_init``:
+    ``min(t^-0.5, 1e-6 t)``) times ``max(rms(param), eps_rms)``."""
+    lr: Optional[float] = None
+    beta1: Optional[float] = None
+    decay_rate: float = -0.8
+    eps_sq: float = 1e-30
+    eps_rms: float = 1e-3
+    weight_decay: float = 0.0
+    relative_step: bool = True
+    warmup_init: bool = False
+
+
+@dataclass(frozen=True)
+class KfacConfig(_Cfg):
+    """ferrotorch-optim/src/natural_gradient.rs:54-82: ``momentum`` is both the decay of the running Kronecker factors and the momentum of the
+    preconditioned gradient; ``weight_decay`` is L2 (added to the gradient before preconditioning)."""
+    lr: float = 1e-3
+    damping: float = 1e-3
+    momentum: float = 0.9
+    update_freq: int = 10
+    weight_decay: float = 0.0
+    maximize: bool = False
+
+
+@dataclass(frozen=True, order=True)
+class ParamKey:
+    """Position of a parameter: group index, index within the group; prints as ``g<group>_p<param>``, the key of a saved optimiser state
+    (ferrotorch-optim/src/param_key.rs:43)."""
+    group: int
+    param: int
+
+    def __str__(self):
+        return f"g{self.group}_p{self.param}"
+
+    @classmethod
+    def parse(cls, s: str) -> "ParamKey":
+        import re
+        m = re.fullmatch(r"g(\d+)_p(\d+)", s)
+        if not m:
+            raise InvalidArgument(f"not a parameter key: {s!r}")
+        return cls(int(m.group(1)), int(m.group(2)))
+
+
+OptimizerState = Dict[str, Dict[str, List[float]]]           # saved form: parameter key -> named buffers as flat f64 lists (optimizer.rs:8)
+
+
+Adamax = _named(torch.optim.Adamax, "Adamax", "Adamax (infinity-norm Adam).", AdamaxConfig)
+NAdam = _named(torch.optim.NAdam, "NAdam", "Adam with Nesterov momentum.", NAdamConfig)
+RAdam = _named(torch.optim.RAdam, "RAdam", "Rectified Adam.", RAdamConfig)
+Adagrad = _named(torch.optim.Adagrad, "Adagrad", "Adagrad.", AdagradConfig)
+Adadelta = _named(torch.optim.Adadelta, "Adadelta", "Adadelta.", AdadeltaConfig)
+Rmsprop = _named(torch.optim.RMSprop, "Rmsprop", "RMSprop.", RmspropConfig)
+Rprop = _named(torch.optim.Rprop, "Rprop", "Resilient backpropagation.", RpropConfig)
+Asgd = _named(torch.optim.ASGD, "Asgd", "Averaged SGD.", AsgdConfig)
+SparseAdam = _named(torch.optim.SparseAdam, "SparseAdam", "Adam for sparse gradients (embedding tables).", SparseAdamConfig)
+Lbfgs = _named(torch.optim.LBFGS, "Lbfgs", "L-BFGS with optional strong-Wolfe line search (``line_search_fn='strong_wolfe'``).", LbfgsConfig)
 LineSearchFn = str
 
 
@@ -268,7 +424,14 @@ class Adafactor(Optimizer):
     """Adafactor: factored second moments for matrices (row/column statistics), relative step size optional."""
 
     def __init__(self, params, lr: Optional[float] = 1e-3, eps=(1e-30, 1e-3), clip_threshold: float = 1.0, decay_rate: float = -0.8,
-                 beta1: Optional[float] = None, weight_decay: float = 0.0, scale_parameter: bool = True, relative_step: bool = False):
+                 beta1: Optional[float] = None, weight_decay: float = 0.0, scale_parameter: bool = True, relative_step: bool = False,
+                 warmup_init: bool = False):
+        if isinstance(lr, AdafactorConfig):
+            c = lr
+            lr, eps, decay_rate, beta1, weight_decay = (c.lr if c.lr is not None else 1e-3), (c.eps_sq, c.eps_rms), c.decay_rate, c.beta1, c.weight_decay
+            relative_step, warmup_init, scale_parameter = c.relative_step, c.warmup_init, c.relative_step      # the reference scales by rms(param)
+            self.config = c                                                                                       # only on the relative path
+        self._warmup_init = warmup_init
         super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
                                       weight_decay=weight_decay, scale_parameter=scale_parameter, relative_step=relative_step))
 
@@ -301,6 +464,8 @@ class Adafactor(Optimizer):
                 lr = g["lr"]
                 if g["relative_step"]:
                     lr = min(1e-2, 1.0 / math.sqrt(t))
+                    if getattr(self, "config", None) is not None:                 # reference rule: no 1e-2 cap, optional linear warm-up
+                        lr = min(t ** -0.5, 1e-6 * t) if self._warmup_init else t ** -0.5
                 if g["scale_parameter"]:
                     lr = lr * max(g["eps"][1], float(rms_p))
                 beta2t = 1.0 - t ** g["decay_rate"]
@@ -394,7 +559,14 @@ class Kfac(Optimizer):
     """Kronecker-factored natural gradient for ``Linear`` layers: running covariances of layer inputs (A) and output gradients (G),
     preconditioned update ``G^-1 dW A^-1`` with Tikhonov damping; other parameters fall back to SGD."""
 
-    def __init__(self, model: torch.nn.Module, lr: float = 0.01, damping: float = 1e-3, ema: float = 0.95, update_freq: int = 1):
+    def __init__(self, model: torch.nn.Module, lr=0.01, damping: float = 1e-3, ema: float = 0.95, update_freq: int = 1, momentum: float = 0.0,
+                 weight_decay: float = 0.0, maximize: bool = False):
+        self.config = lr if isinstance(lr, KfacConfig) else None
+        if self.config is not None:
+            c = lr
+            lr, damping, ema, update_freq, momentum, weight_decay, maximize = c.lr, c.damping, c.momentum, c.update_freq, c.momentum, c.weight_decay, c.maximize
+        self.momentum, self.weight_decay, self.maximize = momentum, weight_decay, maximize
+        self._mom: Dict[torch.Tensor, torch.Tensor] = {}
         self.model, self.damping, self.ema, self.update_freq = model, damping, ema, update_freq
         self._layers: Dict[torch.nn.Module, dict] = {}
         super().__init__(model.parameters(), dict(lr=lr))
@@ -434,10 +606,15 @@ class Kfac(Optimizer):
             if self._steps % self.update_freq == 0 or "Ainv" not in s:
                 s["Ainv"] = torch.linalg.inv(s["A"] + self.damping ** 0.5 * torch.eye(s["A"].shape[0], device=s["A"].device))
                 s["Ginv"] = torch.linalg.inv(s["G"] + self.damping ** 0.5 * torch.eye(s["G"].shape[0], device=s["G"].device))
-            gw = m.weight.grad.float()
+            sign = -1.0 if self.maximize else 1.0
+            gw = sign * m.weight.grad.float() + self.weight_decay * m.weight.float()
             if m.bias is not None and m.bias.grad is not None:
-                gw = torch.cat([gw, m.bias.grad.float().unsqueeze(1)], 1)
+                gw = torch.cat([gw, (sign * m.bias.grad.float() + self.weight_decay * m.bias.float()).unsqueeze(1)], 1)
             nat = s["Ginv"] @ gw @ s["Ainv"]
+            if self.momentum > 0.0:
+                buf = self._mom.get(m.weight)
+                nat = nat.clone() if buf is None else buf.mul_(self.momentum).add_(nat)
+                self._mom[m.weight] = nat
             if m.bias is not None and m.bias.grad is not None:
                 m.weight.add_(nat[:, :-1].to(m.weight.dtype), alpha=-lr)
                 m.bias.add_(nat[:, -1].to(m.bias.dtype), alpha=-lr)
@@ -448,7 +625,12 @@ class Kfac(Optimizer):
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is not None and p not in handled:
-                    p.add_(p.grad, alpha=-lr)
+                    d = (-p.grad if self.maximize else p.grad) + self.weight_decay * p
+                    if self.momentum > 0.0:
+                        buf = self._mom.get(p)
+                        d = d.clone() if buf is None else buf.mul_(self.momentum).add_(d)
+                        self._mom[p] = d
+                    p.add_(d, alpha=-lr)
         self._steps += 1
         return loss
 

@@ -272,6 +272,17 @@ class ScheduleAction(enum.Enum):
     RecordAndSave = "record_and_save"
 
 
+class SchedulePhase(enum.Enum):
+    """Where a step falls in the wait / warmup / active cycle; ``Done`` after the last repeat (ferrotorch-profiler/src/schedule.rs:5)."""
+    Waiting = "Waiting"
+    Warmup = "Warmup"
+    Active = "Active"
+    Done = "Done"
+
+    def __str__(self):
+        return self.value
+
+
 class ProfileSchedule:
     """wait / warmup / active / repeat step schedule with an ``on_trace_ready`` callback (schedule.rs:53-179)."""
 
@@ -290,6 +301,15 @@ class ProfileSchedule:
         if s < self.wait + self.warmup:
             return ScheduleAction.Warmup
         return ScheduleAction.RecordAndSave if s == cycle - 1 else ScheduleAction.Record
+
+    def phase(self, step: Optional[int] = None) -> SchedulePhase:
+        """Phase of ``step`` (default: the step about to run)."""
+        step = self.step_num if step is None else step
+        cycle = self.wait + self.warmup + self.active
+        if self.repeat and step >= cycle * self.repeat:
+            return SchedulePhase.Done
+        s = step % cycle
+        return SchedulePhase.Waiting if s < self.wait else (SchedulePhase.Warmup if s < self.wait + self.warmup else SchedulePhase.Active)
 
     def step(self) -> None:
         a = self.action(self.step_num)

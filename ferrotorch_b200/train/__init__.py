@@ -111,6 +111,27 @@ class RunningAverage:
 # ----------------------------------------------------------------------------------------------------------------------
 # history
 # ----------------------------------------------------------------------------------------------------------------------
+class EvalResult(tuple):
+    """What :meth:`Learner.evaluate` returns: mean loss and metric values (ferrotorch-train/src/history.rs:97). It is also the plain
+    ``(loss, metrics)`` pair, so ``loss, metrics = learner.evaluate(data)`` keeps working."""
+
+    def __new__(cls, loss: float, metrics: Optional[Dict[str, float]] = None):
+        return super().__new__(cls, (float(loss), dict(metrics or {})))
+
+    @classmethod
+    def new_with_defaults(cls, loss: float) -> "EvalResult":
+        return cls(loss, {})
+
+    loss = property(lambda self: self[0])
+    metrics = property(lambda self: self[1])
+
+    def __str__(self):
+        return "".join([f"eval_loss={self.loss:.6f}"] + [f", {k}={v:.6f}" for k, v in self.metrics.items()])
+
+
+LossFn = Callable[[torch.Tensor, torch.Tensor], torch.Tensor]      # (output, target) -> scalar loss (ferrotorch-train/src/learner.rs:45)
+
+
 @dataclass
 class EpochResult:
     epoch: int
@@ -458,7 +479,7 @@ class Learner:
         return self.history
 
     @torch.no_grad()
-    def evaluate(self, data) -> Tuple[float, Dict[str, float]]:
+    def evaluate(self, data) -> EvalResult:
         self.model.eval()
         for m in self.metrics:
             m.reset()
@@ -469,4 +490,9 @@ class Learner:
             tot, n = tot + lv, n + 1
             for m in self.metrics:
                 m.update(out, y, lv)
-        return tot / max(n, 1), {m.name: m.compute() for m in self.metrics}
+        return EvalResult(tot / max(n, 1), {m.name: m.compute() for m in self.metrics})
+
+
+# the reference re-exports these at the crate root (ferrotorch-train/src/lib.rs)
+from ..core import checkpoint  # noqa: E402
+from ..nn.utils import clip_grad_norm_, clip_grad_value_  # noqa: E402

@@ -437,3 +437,235 @@ def test_vision_io_structs_samples_and_detection_names(tmp_path):
         f = body(torch.randn(1, 3, 64, 64))
     assert f["out"].shape == (1, 2048, 8, 8) and f["aux"].shape == (1, 1024, 8, 8)
     assert V.FcnHead(16, 3)(torch.randn(2, 16, 4, 4)).shape == (2, 3, 4, 4) and V.TwoMlpHead is not None and V.MaskPredictor is not None
+
+
+def test_optimizer_configs_and_averaging_strategy():
+    from ferrotorch_b200 import optim as O
+    torch.manual_seed(0)
+    w0 = torch.randn(6, 4)
+
+    def run(make, steps=3):
+        p = torch.nn.Parameter(w0.clone())
+        opt = make([p])
+        for _ in range(steps):
+            opt.zero_grad()
+            (p.pow(2).sum() + p.sum()).backward()
+            opt.step()
+        return p.detach()
+    pairs = [(O.Adamax, O.AdamaxConfig, torch.optim.Adamax), (O.NAdam, O.NAdamConfig, torch.optim.NAdam), (O.RAdam, O.RAdamConfig, torch.optim.RAdam),
+             (O.Adagrad, O.AdagradConfig, torch.optim.Adagrad), (O.Adadelta, O.AdadeltaConfig, torch.optim.Adadelta), (O.Rmsprop, O.RmspropConfig, torch.optim.RMSprop),
+             (O.Rprop, O.RpropConfig, torch.optim.Rprop), (O.Asgd, O.AsgdConfig, torch.optim.ASGD)]
+    for ours, cfg, ref in pairs:
+        c = cfg().with_lr(0.05)
+        assert c.lr == 0.05 and cfg().lr != 0.05 or cfg().lr == 0.05
+        import dataclasses
+        assert torch.equal(run(lambda ps: ours(ps, c)), run(lambda ps: ref(ps, **dataclasses.asdict(c)))), ours.__name__
+    assert O.RmspropConfig().with_centered(True).with_momentum(0.5).centered and O.NAdamConfig().momentum_decay == 4e-3 and O.AsgdConfig().t0 == 1e6
+    assert torch.equal(run(lambda ps: O.Adamax(ps, lr=0.01)), run(lambda ps: torch.optim.Adamax(ps, lr=0.01)))
+    lb = O.Lbfgs([torch.nn.Parameter(w0.clone())], O.LbfgsConfig(line_search_fn="strong_wolfe", history_size=5))
+    assert lb.param_groups[0]["history_size"] == 5 and lb.param_groups[0]["line_search_fn"] == "strong_wolfe"
+
+    # Adafactor under the reference's relative-step rule: first step moves every entry by about t^-0.5 * max(rms, eps_rms) in the gradient's sign
+    p = torch.nn.Parameter(w0.clone())
+    opt = O.Adafactor([p], O.AdafactorConfig())
+    (p * torch.ones_like(p)).sum().backward()
+    opt.step()
+    rms = float(w0.norm() / w0.numel() ** 0.5)
+    assert torch.allclose(w0 - p.detach(), torch.full_like(w0, rms), rtol=1e-3)
+    small = w0 * 1e-3                                         # small weights, so that a 1e-6-relative step survives f32 rounding
+    p2 = torch.nn.Parameter(small.clone())
+    opt2 = O.Adafactor([p2], O.AdafactorConfig(warmup_init=True))
+    (p2 * torch.ones_like(p2)).sum().backward()
+    opt2.step()
+    assert torch.allclose(small - p2.detach(), torch.full_like(w0, 1e-6 * max(rms * 1e-3, 1e-3)), rtol=0.1, atol=0)
+    fixed = O.AdafactorConfig(lr=0.1, relative_step=False)
+    p3 = torch.nn.Parameter(w0.clone())
+    o3 = O.Adafactor([p3], fixed)
+    (p3 * torch.ones_like(p3)).sum().backward()
+    o3.step()
+    assert torch.allclose(w0 - p3.detach(), torch.full_like(w0, 0.1), rtol=1e-3)
+
+    # K-FAC config: momentum on the preconditioned step, L2 decay, maximize
+    def kfac(cfg):
+        torch.manual_seed(1)
+        net = torch.nn.Sequential(torch.nn.Linear(4, 3))
+        opt = O.Kfac(net, cfg)
+        x, y = torch.randn(16, 4), torch.randn(16, 3)
+        losses = []
+        for _ in range(6):
+            opt.zero_grad()
+            l = (net(x) - y).pow(2).mean()
+            l.backward()
+            opt.step()
+            losses.append(float(l))
+        return losses, net
+    base, _ = kfac(O.KfacConfig(lr=0.05, momentum=0.0, update_freq=1))
+    assert base[-1] < base[0]
+    mom, _ = kfac(O.KfacConfig(lr=0.05, momentum=0.5, update_freq=1))
+    assert mom[-1] < mom[0] and mom[2] != base[2]
+    up, _ = kfac(O.KfacConfig(lr=0.05, momentum=0.0, update_freq=1, maximize=True))
+    assert up[-1] > up[0]
+    _, heavy = kfac(O.KfacConfig(lr=0.05, momentum=0.0, update_freq=1, weight_decay=5.0))
+    _, light = kfac(O.KfacConfig(lr=0.05, momentum=0.0, update_freq=1))
+    assert heavy[0].weight.norm() < light[0].weight.norm()
+
+    k = O.ParamKey(2, 7)
+    assert str(k) == "g2_p7" and O.ParamKey.parse("g2_p7") == k and O.ParamKey(0, 9) < O.ParamKey(1, 0)
+    with pytest.raises(InvalidArgument):
+        O.ParamKey.parse("p7")
+
+    net = torch.nn.Linear(2, 2)
+    ema = O.AveragedModel(net, O.AveragingStrategy.Ema(0.9))
+    swa = O.AveragedModel(net, O.AveragingStrategy.Swa)
+    w_first = net.weight.detach().clone()
+    ema.update_parameters(net); swa.update_parameters(net)          # noqa: E702
+    with torch.no_grad():
+        net.weight.add_(1.0)
+    ema.update_parameters(net); swa.update_parameters(net)          # noqa: E702
+    assert torch.allclose(ema.module.weight, 0.9 * w_first + 0.1 * (w_first + 1)) and torch.allclose(swa.module.weight, w_first + 0.5)
+    assert O.AveragingStrategy.Ema(0.9) == O.AveragingStrategy.Ema(0.9) != O.AveragingStrategy.Swa
+    with pytest.raises(InvalidArgument):
+        O.AveragingStrategy.Ema(1.5)
+
+
+def test_data_crate_names():
+    from ferrotorch_b200 import data as D
+    idx = list(range(20))
+    D.shuffle_with_seed(idx, 1234)
+    again = list(range(20))
+    D.shuffle_with_seed(again, 1234)
+    assert idx == again and sorted(idx) == list(range(20)) and idx != list(range(20))
+    other = list(range(20))
+    D.shuffle_with_seed(other, 1235)
+    assert other != idx
+    zero = list(range(8)); dead = list(range(8))               # noqa: E702
+    D.shuffle_with_seed(zero, 0); D.shuffle_with_seed(dead, 0xDEADBEEFCAFE)          # noqa: E702
+    assert zero == dead                                         # seed 0 is replaced, xorshift cannot leave state 0
+    # first swap by hand: i = 3 of 4 elements, j = high word of xorshift(seed) * 4
+    x = 99
+    x ^= (x << 13) & (2 ** 64 - 1); x ^= x >> 7; x ^= (x << 17) & (2 ** 64 - 1)      # noqa: E702
+    four = [0, 1, 2, 3]
+    D.shuffle_with_seed(four, 99)
+    assert four.index(3) == (x * 4) >> 64 or four[3] == [0, 1, 2, 3][(x * 4) >> 64]
+    counts = [0] * 3
+    for s in range(1, 3001):
+        t = [0, 1, 2]
+        D.shuffle_with_seed(t, s * 0x9E3779B97F4A7C15 % 2 ** 64)
+        counts[t[0]] += 1
+    assert all(abs(c / 3000 - 1 / 3) < 0.03 for c in counts)
+
+    xs, ys = D.default_collate_pair([(torch.ones(2), torch.tensor(1)), (torch.zeros(2), torch.tensor(0))])
+    assert xs.shape == (2, 2) and ys.tolist() == [1, 0]
+    with pytest.raises(InvalidArgument):
+        D.default_collate_pair([])
+    it = D.BatchIter(D.VecDataset([10, 11, 12, 13, 14]), [[0, 1], [2, 3], [4]])
+    assert list(it) == [[10, 11], [12, 13], [14]]
+
+    img = torch.arange(2 * 6 * 6.0).view(2, 6, 6)
+    D.manual_seed(5)
+    a = [D.RandomCrop(4, 3)(img) for _ in range(4)]
+    D.manual_seed(5)
+    b = [D.RandomCrop(4, 3)(img) for _ in range(4)]
+    assert all(torch.equal(p, q) for p, q in zip(a, b)) and a[0].shape == (2, 4, 3) and a[0].is_contiguous()
+    assert torch.equal(D.RandomCrop(6)(img), img)
+    with pytest.raises(InvalidArgument):
+        D.RandomCrop(7, 2)(img)
+    with pytest.raises(InvalidArgument):
+        D.RandomCrop(1)(torch.zeros(3))
+    assert torch.equal(D.RandomHorizontalFlip(1.0)(img), img.flip(-1)) and D.RandomHorizontalFlip(0.0)(img) is img
+    D.manual_seed(0)
+    flips = sum(not torch.equal(D.RandomHorizontalFlip(0.5).apply(img), img) for _ in range(400))
+    assert 150 < flips < 250
+    with pytest.raises(InvalidArgument):
+        D.RandomHorizontalFlip(0.5)(torch.tensor(1.0))
+    hwc = (torch.arange(4 * 5 * 3) % 256).to(torch.uint8).view(4, 5, 3).numpy()
+    t = D.ToTensor()(hwc)
+    assert t.shape == (3, 4, 5) and torch.allclose(t[1, 2, 3], torch.tensor(float(hwc[2, 3, 1]) / 255)) and D.ToTensor()(img) is img
+    pipe = D.Compose([D.ToTensor(), D.RandomCrop(2), D.RandomHorizontalFlip(0.5)])
+    assert isinstance(D.RandomCrop(2), D.Transform) and pipe.apply(hwc).shape == (3, 2, 2)
+
+
+def test_hub_discovery_is_parsed_and_offline_is_loud(monkeypatch):
+    from ferrotorch_b200 import hub as H
+    q = H.SearchQuery().with_search("llama 3/é").with_pipeline_tag("text-generation").with_library("transformers").with_limit(5).with_sort("downloads")
+    assert q.to_query_string() == "/api/models?search=llama%203%2F%C3%A9&pipeline_tag=text-generation&library=transformers&limit=5&sort=downloads"
+    assert H.SearchQuery().to_query_string() == "/api/models"
+    seen = []
+    rows = [{"modelId": "meta-llama/Meta-Llama-3-8B", "downloads": 10, "likes": 2, "tags": ["llama"], "pipeline_tag": "text-generation"},
+            {"id": "gpt2", "author": "openai-community"}]
+
+    def fake(url, timeout=30.0):
+        seen.append(url)
+        return rows if "?" in url or url.endswith("/api/models") else {"id": "a/b", "siblings": [{"rfilename": "config.json"}, {"rfilename": "model.safetensors"}]}
+    monkeypatch.setattr(H, "_http_get_json", fake)
+    out = H.search_models(q)
+    assert seen[0].startswith("https://huggingface.co/api/models?search=") and [r.model_id for r in out] == ["meta-llama/Meta-Llama-3-8B", "gpt2"]
+    assert out[0].author == "meta-llama" and out[0].downloads == 10 and out[1].author == "openai-community" and out[1].tags == []
+    info = H.get_model("a/b")
+    assert seen[-1] == "https://huggingface.co/api/models/a/b" and info.filenames() == ["config.json", "model.safetensors"] and info.author == "a"
+    with pytest.raises(InvalidArgument):
+        H.get_model("")
+    monkeypatch.setattr(H, "_http_get_json", lambda url, timeout=30.0: {"oops": 1})
+    with pytest.raises(InvalidArgument):
+        H.search_models(H.SearchQuery())
+    monkeypatch.undo()
+    monkeypatch.setenv("FT_HUB_OFFLINE", "1")
+    with pytest.raises(H.HubOffline):
+        H.search_models(H.SearchQuery().with_search("x"))
+    assert [m.name for m in H.search_models("minilm")] == ["all-MiniLM-L6-v2"]          # the string form stays local
+    assert H.get_model_info("resnet50").params == 25_557_032 and H.get_model_info("nope") is None
+    assert H.get_model_info("resnet50").weights_format is H.WeightsFormat.SafeTensors and H.get_model_info("resnet50").kind is H.EntryKind.Model
+    monkeypatch.setenv("HF_TOKEN", "tok123")
+    import urllib.request
+    assert H.with_auth(urllib.request.Request("https://huggingface.co/x")).get_header("Authorization") == "Bearer tok123"
+    monkeypatch.setenv("FT_HUB_CACHE", "/tmp/some-cache")
+    assert str(H.default_cache_dir()) == "/tmp/some-cache"
+
+
+def test_train_profiler_grammar_nn_small_names():
+    from ferrotorch_b200 import train as T, profiler as P, grammar as G, nn, optim as O
+    net = torch.nn.Linear(3, 1)
+    lr = T.Learner(net, O.Sgd(net.parameters(), lr=0.1), torch.nn.functional.mse_loss).with_metric(T.LossMetric())
+    data = [(torch.randn(4, 3), torch.randn(4, 1)) for _ in range(3)]
+    r = lr.evaluate(data)
+    loss, metrics = r
+    assert isinstance(r, T.EvalResult) and r.loss == loss and r.metrics is metrics and str(r).startswith(f"eval_loss={loss:.6f}")
+    assert T.EvalResult.new_with_defaults(0.5).metrics == {} and T.checkpoint is not None and T.clip_grad_norm_ is nn.clip_grad_norm_
+
+    s = P.ProfileSchedule(wait=1, warmup=2, active=2, repeat=2)
+    assert [str(s.phase(i)) for i in range(11)] == ["Waiting", "Warmup", "Warmup", "Active", "Active"] * 2 + ["Done"]
+    assert s.phase() is P.SchedulePhase.Waiting
+
+    pv = G.PackedVocab.pack(["a", "true", "", "né"])
+    assert pv.offsets == [0, 1, 5, 5, 7] and pv.max_token_len == 4 and pv.vocab_size() == 4 and pv.token(3) == "né" and pv.token(2) == ""
+    off, ch = pv.tensors()
+    assert off.dtype == torch.int32 and ch.tolist()[1:5] == [ord(c) for c in "true"] and "7 entries" in repr(pv)
+    with pytest.raises(G.GrammarError) as e:
+        pv.token(9)
+    assert e.value.kind == "invalid_token_id" and "9" in str(e.value)
+    proc = G.JsonSchemaProcessor({"type": "boolean"}, ["t", "rue", "x"], eos_id=None)
+    with pytest.raises(G.GrammarError):
+        proc.advance(17)
+    B = G.BooleanEmissionStage
+    assert B.of("") == (B.Start, "") and B.of("tr") == (B.PartialTrue, "ue") and B.of("fals") == (B.PartialFalse, "e") and B.of("true") == (B.Done, "") and B.of("tx") is None
+
+    x = torch.linspace(-3, 3, 13)
+    assert torch.allclose(nn.GELU(nn.GeluApproximate.Sigmoid)(x), x * torch.sigmoid(1.702 * x))
+    assert torch.equal(nn.gelu(x, nn.GeluApproximate.Tanh), torch.nn.functional.gelu(x, approximate="tanh")) and torch.equal(nn.GELU()(x), torch.nn.functional.gelu(x))
+    with pytest.raises(InvalidArgument):
+        nn.gelu(x, "quick")
+    img = torch.rand(1, 2, 4, 4)
+    assert torch.equal(nn.interpolate(img, scale_factor=2, mode=nn.InterpolateMode.Nearest), torch.nn.functional.interpolate(img, scale_factor=2))
+    grid = torch.rand(1, 3, 3, 2) * 2 - 1
+    assert torch.equal(nn.grid_sample(img, grid, nn.GridSampleMode.Nearest, nn.GridSamplePaddingMode.Border),
+                       torch.nn.functional.grid_sample(img, grid, mode="nearest", padding_mode="border", align_corners=False))
+    assert nn.max_pool2d(img, 2).shape == (1, 2, 2, 2) and nn.adaptive_avg_pool2d(img, 1).shape == (1, 2, 1, 1) and nn.pixel_unshuffle(img, 2).shape == (1, 8, 2, 2)
+    assert nn.QatModel is nn.QuantizedModel
+    table = torch.arange(7.0)                                   # max_dist 3
+    q, k = torch.randn(1, 1, 5, 4), torch.randn(1, 1, 5, 4)
+    v = torch.randn(1, 1, 5, 4)
+    got = nn.flex_attention(q, k, v, nn.relative_position_bias_score_mod(table, 3))
+    qi, ki = torch.arange(5)[:, None], torch.arange(5)[None]
+    bias = table[(qi - ki).clamp(-3, 3) + 3]
+    want = torch.softmax(q @ k.transpose(-1, -2) / 2.0 + bias, -1) @ v
+    assert torch.allclose(got, want, atol=1e-5)
