@@ -10,3 +10,9 @@ from ..errors import (DistributedError, InvalidWorldSize, InvalidRank, SelfSend,
                       Timeout, NoConnection, BackendUnavailable)
 from .extras import (DeviceMesh, Placement, Replicate, Shard, Partial, DTensor, PipelineSchedule, Pipeline, RpcAgent, MAX_RPC_BYTES,
                      ShardingStrategy, FSDP, TensorShardSpec, ShardMetadata, save_distributed, load_distributed, reshard, AsyncCheckpointer)
+from .backends_ext import (is_nccl_available, is_gloo_available, is_mpi_available, is_ucc_available, NcclUniqueId, NcclBackend, GlooBackend, MpiBackend,
+                           UccBackend, HybridBackend, nccl_allreduce, nccl_broadcast, nccl_all_gather, nccl_reduce_scatter, gpu_allreduce, gpu_broadcast,
+                           recv_with_timeout, recv_into, recv_into_with_timeout, RpcError, TcpRpcBackend, DistCheckpointError, DistributedCheckpoint,
+                           flat_shard_metadata)
+from ..serialize.formats import CheckpointFuture  # noqa: E402
+from ..parallel.ddp import SyncBatchNorm2d  # noqa: E402
