@@ -15,4 +15,10 @@ from .backends_ext import (is_nccl_available, is_gloo_available, is_mpi_availabl
                            recv_with_timeout, recv_into, recv_into_with_timeout, RpcError, TcpRpcBackend, DistCheckpointError, DistributedCheckpoint,
                            flat_shard_metadata)
 from ..serialize.formats import CheckpointFuture  # noqa: E402
-from ..parallel.ddp import SyncBatchNorm2d  # noqa: E402
+
+
+def __getattr__(name):
+    if name == "SyncBatchNorm2d":                             # lives with the GPU engines, which import this package: resolve on first use
+        from ..parallel.ddp import SyncBatchNorm2d
+        return SyncBatchNorm2d
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
