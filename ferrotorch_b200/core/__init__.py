@@ -598,3 +598,33 @@ from .tensor_ext import (linalg, fft, special, windows, einsum, einsum_different
 
 from .ops_ext import (cond, scan, empty, tensor, from_vec, searchsorted, bucketize, topk, sort, argsort, unique, histc, nonzero, where, cumsum,  # noqa: E402,F401
                       BoolTensor, IntTensor, CpuBufferPool, cpu_pool, meta_propagate, format_tensor, display, with_fusion, fusion_enabled, fused)
+
+from . import names_ext as _nx  # noqa: E402
+from .names_ext import (Float, IntElement, Element, FerrotorchResult, is_float, normalize_axis, broadcast_shapes, exp, expm1, log, log1p, sin, cos, tanh,  # noqa: E402,F401
+                        sigmoid, erf, erfc, erfinv, lgamma, digamma, sinc, xlogy, clamp, where_cond, sum_dim, mean_dim, cat, expand, view_t, permute_t,
+                        contiguous_t, chunk_t, split_t, roll, tril, triu, diag, diagflat, meshgrid, cdist, gather, scatter, scatter_add,
+                        scatter_add_segments, unique_consecutive, CumExtremeResult, cummax, cummin, cumprod, logcumsumexp, ifft, rfft, irfft, fft2, ifft2,
+                        fftn, ifftn, rfftn, irfftn, hfft, ihfft, fftshift, ifftshift, fftfreq, rfftfreq, fft_differentiable, ifft_differentiable,
+                        rfft_differentiable, irfft_differentiable, dual_add, dual_sub, dual_mul, dual_div, dual_neg, dual_matmul, backward_with_grad,
+                        AnomalyMode, ForwardBacktrace, check_gradient_anomaly, AutocastDtype, set_autocast_debug, is_autocast_debug, autocast_dtype,
+                        autocast_guard, DispatchKeySet, Kernel, TensorId, StorageBuffer, TensorStorage, GradFn, EinopsReduction, validate_cond_branches,
+                        AsStridedBackward, Observer)
+
+fft = _nx._CallableNamespace(fft, _nx.fft)                   # ``core.fft(x)`` and ``core.fft.fft2(x)`` (torch complex forms) both work
+
+
+def cuda_rng():
+    """The process-wide Philox state manager of the CUDA generators (ferrotorch-core re-exports ferrotorch-gpu's)."""
+    from ..gpu import CudaRngManager
+    global _cuda_rng
+    try:
+        return _cuda_rng
+    except NameError:
+        _cuda_rng = CudaRngManager()
+        return _cuda_rng
+
+
+def __getattr__(name):
+    if name in _nx._NN_NAMES or name in ("QatLayer", "fake_quantize_differentiable"):
+        return _nx.nn_name(name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
