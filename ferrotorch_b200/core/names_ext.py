@@ -306,7 +306,7 @@ def backward_with_grad(root: torch.Tensor, gradient: Optional[torch.Tensor] = No
     from ..errors import BackwardNonScalar, NoGradFn
     if gradient is None:
         if root.numel() != 1:
-            raise BackwardNonScalar(f"backward on a tensor of shape {list(root.shape)} needs an explicit gradient")
+            raise BackwardNonScalar(root.shape)
     elif gradient.shape != root.shape:
         raise ShapeMismatch(f"gradient shape {list(gradient.shape)} does not match root shape {list(root.shape)}")
     if not root.requires_grad:

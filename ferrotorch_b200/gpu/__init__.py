@@ -772,3 +772,8 @@ def init_cuda_backend(ordinal: int = 0) -> CudaBackendImpl:
 
 def gpu_backend() -> Optional[CudaBackendImpl]:
     return _backend
+
+
+from . import api_ext  # noqa: E402
+from .api_ext import *  # noqa: E402,F401,F403
+from .api_ext import GpuResult, GpuFloat  # noqa: E402,F401
