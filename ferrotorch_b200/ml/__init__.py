@@ -213,3 +213,11 @@ def roc_auc_score(y_true, scores) -> float:
 def log_loss(y_true, proba, eps: float = 1e-12) -> float:
     y, p = _np(y_true).astype(np.int64), np.clip(_np(proba).astype(np.float64), eps, 1 - eps)
     return float(-np.log(p[np.arange(len(y)), y]).mean())
+
+
+from .metrics_ext import (tensor_to_array1, tensor_to_array2, array1_to_tensor, array2_to_tensor, array1_usize_to_tensor, tensor_to_array1_usize,  # noqa: E402,F401
+                          root_mean_squared_error, mean_absolute_percentage_error, median_absolute_error, max_error, explained_variance_score, hamming_loss,
+                          zero_one_loss, balanced_accuracy_score, matthews_corrcoef, cohen_kappa_score, brier_score_loss, d2_brier_score, top_k_accuracy_score,
+                          average_precision_score, dcg_score, ndcg_score, coverage_error, label_ranking_average_precision_score, label_ranking_loss,
+                          adjusted_rand_score, adjusted_mutual_info_score, normalized_mutual_info_score, homogeneity_score, completeness_score,
+                          v_measure_score, fowlkes_mallows_score, silhouette_score, davies_bouldin_score, calinski_harabasz_score)
