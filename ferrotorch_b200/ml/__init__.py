@@ -221,3 +221,4 @@ from .metrics_ext import (tensor_to_array1, tensor_to_array2, array1_to_tensor, 
                           average_precision_score, dcg_score, ndcg_score, coverage_error, label_ranking_average_precision_score, label_ranking_loss,
                           adjusted_rand_score, adjusted_mutual_info_score, normalized_mutual_info_score, homogeneity_score, completeness_score,
                           v_measure_score, fowlkes_mallows_score, silhouette_score, davies_bouldin_score, calinski_harabasz_score)
+from .sk_bridge import preprocess, decomposition, model_selection, TensorEstimator  # noqa: E402,F401

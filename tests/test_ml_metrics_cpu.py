@@ -100,3 +100,32 @@ def test_adapters_round_trip_and_check_rank():
                 lambda: ml.tensor_to_array1_usize(torch.tensor([1.5])), lambda: ml.tensor_to_array1_usize(torch.tensor([-1.0])), lambda: ml.array1_usize_to_tensor(np.array([-2]))):
         with pytest.raises(FerrotorchError):
             bad()
+
+
+def test_classical_estimators_take_and_return_tensors():
+    pytest.importorskip("sklearn")
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(60, 5, generator=g, dtype=torch.float64) * torch.tensor([1.0, 5.0, 0.2, 3.0, 1.0], dtype=torch.float64) + 2.0
+    sc = ml.preprocess.StandardScaler().fit(X)
+    assert isinstance(sc, ml.TensorEstimator) and torch.allclose(sc.mean_, X.mean(0)) and torch.allclose(sc.transform(X), (X - X.mean(0)) / X.std(0, unbiased=False))
+    Z = sc.fit_transform(X.float())
+    assert Z.dtype == torch.float32 and torch.allclose(sc.inverse_transform(Z), X.float(), atol=1e-4)
+    mm = ml.preprocess.MinMaxScaler().fit_transform(X)
+    assert float(mm.min()) == 0.0 and abs(float(mm.max()) - 1.0) < 1e-12
+    filled = ml.preprocess.SimpleImputer(strategy="mean").fit_transform(torch.tensor([[1.0, float("nan")], [3.0, 4.0]]))
+    assert filled.tolist() == [[1.0, 4.0], [3.0, 4.0]]
+    pca = ml.decomposition.PCA(n_components=2).fit(X)
+    U, S, Vh = torch.linalg.svd(X - X.mean(0), full_matrices=False)
+    assert pca.components_.shape == (2, 5) and torch.allclose(pca.components_.abs(), Vh[:2].abs(), atol=1e-8)
+    assert torch.allclose(pca.explained_variance_, S[:2] ** 2 / 59, atol=1e-8) and pca.transform(X).shape == (60, 2)
+    y = (X[:, 1] > 2.0).long()
+    folds = list(ml.model_selection.KFold(n_splits=3).split(X))
+    assert len(folds) == 3 and all(isinstance(tr, torch.Tensor) and len(tr) + len(te) == 60 for tr, te in folds)
+    assert sorted(torch.cat([te for _, te in folds]).tolist()) == list(range(60))
+    Xtr, Xte, ytr, yte = ml.model_selection.train_test_split(X, y, test_size=0.25, random_state=0)
+    assert Xtr.shape == (45, 5) and yte.shape == (15,) and isinstance(Xtr, torch.Tensor)
+    pipe = ml.model_selection.make_pipeline(ml.preprocess.StandardScaler(), ml.model_selection.DummyClassifier(strategy="most_frequent"))
+    pred = pipe.fit(X, y).predict(X)
+    assert isinstance(pred, torch.Tensor) and pred.unique().numel() == 1
+    with pytest.raises(AttributeError):
+        ml.preprocess.NoSuchThing
