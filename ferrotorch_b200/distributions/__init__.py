@@ -9,7 +9,10 @@ Reference parity: ferrotorch-distributions/src/lib.rs:138 (Distribution trait), 
 file per family.
 """
 from torch import distributions as _d
-from torch.distributions import constraints, transforms, kl
+from torch.distributions import kl
+from . import constraints, transforms
+from .constraints import Constraint
+from .transforms import TransformedDistribution, SoftplusTransform, Transform
 from torch.distributions.kl import kl_divergence, register_kl
 
 Distribution = _d.Distribution
@@ -21,7 +24,6 @@ LowRankMultivariateNormal, MixtureSameFamily, Multinomial, MultivariateNormal, N
 OneHotCategorical, Pareto, Poisson, RelaxedBernoulli, RelaxedOneHotCategorical = (_d.OneHotCategorical, _d.Pareto, _d.Poisson,
                                                                                   _d.RelaxedBernoulli, _d.RelaxedOneHotCategorical)
 StudentT, Uniform, VonMises, Weibull = _d.StudentT, _d.Uniform, _d.VonMises, _d.Weibull
-TransformedDistribution = _d.TransformedDistribution
 AffineTransform, ExpTransform, SigmoidTransform, TanhTransform, ComposeTransform, SoftmaxTransform, StickBreakingTransform = (
     transforms.AffineTransform, transforms.ExpTransform, transforms.SigmoidTransform, transforms.TanhTransform, transforms.ComposeTransform,
     transforms.SoftmaxTransform, transforms.StickBreakingTransform)

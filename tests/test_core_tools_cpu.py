@@ -338,3 +338,42 @@ def test_vision_rng_choice_and_to_tensor():
     assert V.VisionToTensor()(np.full((2, 2, 3), 255, np.uint8)).max() == 1.0
     with pytest.raises(InvalidArgument):
         V.VisionToTensor()(torch.zeros(4, 5))
+
+
+def test_distribution_constraints_and_transformed_entropy():
+    """Constraint objects follow ferrotorch-distributions/src/constraints.rs (NaN satisfies nothing, Real accepts infinities, Simplex is
+    per-element with event_dim 1); TransformedDistribution.entropy uses H(Y) = H(X) + E[log|det J|] for affine and exponential maps."""
+    import math
+    from ferrotorch_b200 import distributions as D
+    from ferrotorch_b200.errors import FerrotorchError, InvalidArgument
+    C = D.constraints
+    assert C.positive().check(1.0) and not C.positive().check(-1.0) and not C.positive().check(0.0) and C.nonnegative().check(0.0)
+    assert C.real().check(float("inf")) and not C.real().check(float("nan")) and not C.unit_interval().check(1.5) and C.unit_interval().check(1.0)
+    assert C.boolean().check(1.0) and not C.boolean().check(0.5) and C.boolean().is_discrete() and C.boolean().name() == "Boolean"
+    assert C.greater_than(2.0).check(2.1) and not C.greater_than(2.0).check(2.0) and C.greater_than_eq(2.0).check(2.0) and C.less_than(0.0).check(-1.0)
+    assert not C.open_interval(0.0, 1.0).check(0.0) and C.closed_interval(0.0, 1.0).check(0.0) and C.half_open_interval(0.0, 1.0).check(0.0) and not C.half_open_interval(0.0, 1.0).check(1.0)
+    t = torch.tensor([0.2, float("nan"), -0.1, 0.9])
+    assert C.unit_interval().check(t).tolist() == [True, False, False, True] and C.positive().event_dim() == 0 and C.simplex().event_dim() == 1
+    assert C.simplex().check(torch.tensor([0.3, 0.7])).all() and C.simplex().check_event(torch.tensor([[0.3, 0.7], [0.5, 0.6]])).tolist() == [True, False]
+    assert isinstance(C.positive(), D.Constraint) and repr(C.open_interval(0.0, 2.0)) == "OpenInterval(lower_bound=0.0, upper_bound=2.0)"
+    with pytest.raises(InvalidArgument):
+        C.closed_interval(2.0, 1.0)
+    T = D.transforms
+    x = torch.linspace(-3, 3, 7)
+    sp = D.SoftplusTransform()
+    assert torch.allclose(sp(x), torch.nn.functional.softplus(x)) and torch.allclose(sp.inv(sp(x)), x, atol=1e-5)
+    assert torch.allclose(sp.log_abs_det_jacobian(x, sp(x)), -torch.nn.functional.softplus(-x), atol=1e-6)
+    assert T.transform_name(T.ExpTransform()) == "ExpTransform" and T.is_exp_transform(T.ExpTransform()) and not T.is_exp_transform(sp)
+    assert float(T.constant_entropy_contribution(T.AffineTransform(1.0, -3.0))) == pytest.approx(math.log(3.0)) and T.constant_entropy_contribution(sp) is None
+    base = D.Normal(torch.tensor(0.5), torch.tensor(0.8))
+    aff = D.TransformedDistribution(base, [T.AffineTransform(2.0, 3.0)])
+    assert float(aff.entropy()) == pytest.approx(float(D.Normal(torch.tensor(3.5), torch.tensor(2.4)).entropy()), rel=1e-6)
+    logn = D.TransformedDistribution(base, [T.AffineTransform(1.0, 2.0), T.ExpTransform()])       # exp(2 X + 1) is LogNormal(2 * 0.5 + 1, 1.6)
+    assert float(logn.entropy()) == pytest.approx(float(D.LogNormal(torch.tensor(2.0), torch.tensor(1.6)).entropy()), rel=1e-6)
+    scaled = D.TransformedDistribution(base, [T.ComposeTransform([T.ExpTransform(), T.AffineTransform(0.0, 5.0)])])
+    assert float(scaled.entropy()) == pytest.approx(float(D.LogNormal(torch.tensor(0.5), torch.tensor(0.8)).entropy()) + math.log(5.0), rel=1e-6)
+    for bad in ([T.SigmoidTransform()], [T.ExpTransform(), T.ExpTransform()]):
+        with pytest.raises(FerrotorchError):
+            D.TransformedDistribution(base, bad).entropy()
+    y = logn.rsample((4,))
+    assert y.shape == (4,) and (y > 0).all() and torch.isfinite(logn.log_prob(y)).all()
