@@ -669,3 +669,22 @@ def test_train_profiler_grammar_nn_small_names():
     bias = table[(qi - ki).clamp(-3, 3) + 3]
     want = torch.softmax(q @ k.transpose(-1, -2) / 2.0 + bias, -1) @ v
     assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_umbrella_package_surface():
+    """Top level: sub-packages resolve lazily, the core names are reachable directly, the prelude carries the usual starting set, and the
+    backends this framework does not have answer 'unavailable' instead of failing to import (ferrotorch/src/lib.rs:41-150)."""
+    import ferrotorch_b200 as F
+    from ferrotorch_b200 import prelude
+    from ferrotorch_b200.errors import DeviceUnavailable
+    assert F.zeros(2, 3).shape == (2, 3) and F.normalize_axis(-1, 2) == 1 and F.DispatchKeySet.empty().is_empty()
+    for name in ("Linear", "Conv2d", "BatchNorm2d", "LayerNorm", "Dropout", "Module", "Parameter", "Sequential", "CrossEntropyLoss", "MSELoss", "GELU", "ReLU", "SiLU",
+                 "Sigmoid", "Softmax", "Tanh", "GRU", "LSTM", "Adam", "AdamW", "Optimizer", "Sgd", "zeros", "Device", "no_grad"):
+        assert hasattr(prelude, name), name
+    assert callable(F.jit_script.script) and F.cubecl.GgufBlockKind.Q8_0.block_bytes() == 34 and callable(F.gpu.gpu_softmax)
+    assert not F.mps.is_available() and not F.mps.is_mps_available() and F.mps.MpsDevice.count() == 0 and not F.xpu.is_available()
+    for ctor in (F.mps.MtlBackend, F.mps.MpsDevice, F.xpu.XpuDevice, F.xpu.make_xpu_tensor):
+        with pytest.raises(DeviceUnavailable):
+            ctor()
+    with pytest.raises(AttributeError):
+        F.no_such_thing
