@@ -610,6 +610,9 @@ from .names_ext import (Float, IntElement, Element, FerrotorchResult, is_float, 
                         autocast_guard, DispatchKeySet, Kernel, TensorId, StorageBuffer, TensorStorage, GradFn, EinopsReduction, validate_cond_branches,
                         AsStridedBackward, Observer)
 
+for _n in ("unary_same_shape", "binary_broadcast", "reduce_dim", "reduce_all", "matmul"):      # ``core.meta_propagate.matmul(a, b)``: the per-operation shape rules
+    setattr(meta_propagate, _n, getattr(_nx, "meta_" + _n))
+full_meta, meta_like = _nx.full_meta, _nx.meta_like
 fft = _nx._CallableNamespace(fft, _nx.fft)                   # ``core.fft(x)`` and ``core.fft.fft2(x)`` (torch complex forms) both work
 
 

@@ -624,3 +624,64 @@ def _fake_quantize_differentiable(x: torch.Tensor, scale: float, zero_point: int
     y = (q - zero_point) * scale
     inside = ((x / scale + zero_point) >= qmin) & ((x / scale + zero_point) <= qmax)
     return x * inside + (y - x * inside).detach()
+
+
+# -- meta-device shape propagation (meta_propagate.rs:36-230): ``None`` means "not meta, run the real kernel" -------------------------------
+def _meta(shape, dtype) -> torch.Tensor:
+    return torch.empty(tuple(shape), dtype=dtype, device="meta")
+
+
+def full_meta(shape: Sequence[int], value=0.0, dtype=torch.float32) -> torch.Tensor:
+    """A meta tensor of ``shape``: carries shape and dtype, no storage (the fill value is irrelevant by construction)."""
+    return _meta(shape, dtype)
+
+
+def meta_like(other: torch.Tensor) -> torch.Tensor:
+    return _meta(other.shape, other.dtype)
+
+
+def _both_meta(a: torch.Tensor, b: torch.Tensor) -> Optional[bool]:
+    if a.is_meta != b.is_meta:
+        from ..errors import DeviceMismatch
+        raise DeviceMismatch(a.device, b.device)
+    return a.is_meta
+
+
+def meta_unary_same_shape(x: torch.Tensor) -> Optional[torch.Tensor]:
+    return meta_like(x) if x.is_meta else None
+
+
+def meta_binary_broadcast(a: torch.Tensor, b: torch.Tensor) -> Optional[torch.Tensor]:
+    return _meta(broadcast_shapes(a.shape, b.shape), torch.result_type(a, b)) if _both_meta(a, b) else None
+
+
+def meta_reduce_dim(x: torch.Tensor, dim: int, keepdim: bool = False) -> Optional[torch.Tensor]:
+    if not x.is_meta:
+        return None
+    d = normalize_axis(dim, x.dim())
+    shape = [1 if k == d else s for k, s in enumerate(x.shape)] if keepdim else [s for k, s in enumerate(x.shape) if k != d]
+    return _meta(shape, x.dtype)
+
+
+def meta_reduce_all(x: torch.Tensor) -> Optional[torch.Tensor]:
+    return _meta((), x.dtype) if x.is_meta else None
+
+
+def meta_matmul(a: torch.Tensor, b: torch.Tensor) -> Optional[torch.Tensor]:
+    if not _both_meta(a, b):
+        return None
+    sa, sb = tuple(a.shape), tuple(b.shape)
+    if not sa or not sb:
+        raise InvalidArgument(f"meta_propagate::matmul: scalar operands not supported, got {list(sa)} and {list(sb)}")
+    ka, kb = sa[-1], (sb[0] if len(sb) == 1 else sb[-2])
+    if ka != kb:
+        raise ShapeMismatch(f"meta_propagate::matmul: inner dimensions differ ({ka} vs {kb}) for {list(sa)} @ {list(sb)}")
+    if len(sa) == 1 and len(sb) == 1:
+        out: Tuple[int, ...] = ()
+    elif len(sb) == 1:
+        out = sa[:-1]
+    elif len(sa) == 1:
+        out = sb[:-2] + sb[-1:]
+    else:
+        out = broadcast_shapes(sa[:-2], sb[:-2]) + (sa[-2], sb[-1])
+    return _meta(out, torch.result_type(a, b))

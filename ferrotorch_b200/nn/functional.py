@@ -43,3 +43,47 @@ for _n in ["relu", "gelu", "silu", "sigmoid", "tanh", "softmax", "log_softmax", 
            "triplet_margin_loss", "hinge_embedding_loss", "poisson_nll_loss", "gaussian_nll_loss", "multi_margin_loss",
            "multilabel_soft_margin_loss", "ctc_loss", "cosine_similarity", "pairwise_distance", "normalize"]:
     globals()[_n] = getattr(_F, _n)
+
+
+# -- parameterised forms (ferrotorch-nn/src/functional.rs:158-880) ------------------------------------------------------------------------
+from .extras import gelu, gelu_with  # noqa: E402,F401  (``gelu(x, approximate)`` with the none / tanh / sigmoid forms)
+
+
+def sum(x):  # noqa: A001
+    """Sum of all elements (a 0-D tensor)."""
+    return x.sum()
+
+
+def mean(x):
+    return x.mean()
+
+
+def hardtanh_with(x, min_val: float, max_val: float):
+    if min_val > max_val:
+        from ..errors import InvalidArgument
+        raise InvalidArgument(f"hardtanh: min_val {min_val} > max_val {max_val}")
+    return _F.hardtanh(x, min_val, max_val)
+
+
+def log_sigmoid(x):
+    return _F.logsigmoid(x)
+
+
+def softplus_with(x, beta: float = 1.0, threshold: float = 20.0):
+    if beta <= 0:
+        from ..errors import InvalidArgument
+        raise InvalidArgument(f"softplus: beta must be > 0, got {beta}")
+    return _F.softplus(x, beta, threshold)
+
+
+def elu_with(x, alpha: float = 1.0):
+    return _F.elu(x, alpha)
+
+
+def prelu(x, alpha):
+    """``max(0, x) + alpha * min(0, x)`` with one ``alpha`` or one per channel (dimension 1)."""
+    a = torch.as_tensor(alpha, dtype=x.dtype, device=x.device).reshape(-1)
+    if a.numel() not in (1, x.shape[1] if x.dim() > 1 else 1):
+        from ..errors import ShapeMismatch
+        raise ShapeMismatch(f"prelu: {a.numel()} slopes for input shape {list(x.shape)}")
+    return _F.prelu(x, a)

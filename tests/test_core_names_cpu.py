@@ -175,3 +175,35 @@ def test_key_sets_ids_storage_and_nn_names():
     assert base.grad.tolist() == [1, 2, 3, 3, 2, 1]
     with pytest.raises(AttributeError):
         C.no_such_name
+
+
+def test_meta_rules_and_parameterised_functionals():
+    from ferrotorch_b200.nn import functional as Fn
+    from ferrotorch_b200.errors import DeviceMismatch
+    m = C.full_meta([4, 1, 6], 3.0)
+    assert m.is_meta and m.shape == (4, 1, 6) and C.meta_like(torch.zeros(2, 3)).shape == (2, 3)
+    mp = C.meta_propagate
+    assert mp.unary_same_shape(m).shape == (4, 1, 6) and mp.unary_same_shape(torch.zeros(2)) is None
+    assert mp.binary_broadcast(m, C.full_meta([5, 1])).shape == (4, 5, 6) and mp.binary_broadcast(torch.zeros(2), torch.zeros(2)) is None
+    with pytest.raises(DeviceMismatch):
+        mp.binary_broadcast(m, torch.zeros(6))
+    with pytest.raises(ShapeMismatch):
+        mp.binary_broadcast(m, C.full_meta([7]))
+    assert mp.reduce_dim(m, -1).shape == (4, 1) and mp.reduce_dim(m, 0, True).shape == (1, 1, 6) and mp.reduce_all(m).shape == () and mp.reduce_all(torch.zeros(1)) is None
+    for sa, sb, want in (([3], [3], ()), ([2, 3], [3], (2,)), ([3], [3, 4], (4,)), ([2, 3], [3, 4], (2, 4)), ([5, 1, 2, 3], [7, 3, 4], (5, 7, 2, 4))):
+        assert mp.matmul(C.full_meta(sa), C.full_meta(sb)).shape == want == tuple(torch.matmul(torch.zeros(sa), torch.zeros(sb)).shape)
+    with pytest.raises(ShapeMismatch):
+        mp.matmul(C.full_meta([2, 3]), C.full_meta([4, 5]))
+    with pytest.raises(InvalidArgument):
+        mp.matmul(C.full_meta([]), C.full_meta([3]))
+    assert mp(lambda a, b: a @ b, ((2, 3), torch.float32), ((3, 4), torch.float32)) == [((2, 4), torch.float32)]        # the whole-function form still works
+    x = torch.linspace(-3, 3, 13)
+    assert float(Fn.sum(x)) == pytest.approx(0.0, abs=1e-6) and float(Fn.mean(x)) == pytest.approx(0.0, abs=1e-6)
+    assert torch.equal(Fn.hardtanh_with(x, -0.5, 2.0), x.clamp(-0.5, 2.0)) and torch.allclose(Fn.log_sigmoid(x), torch.log(torch.sigmoid(x)), atol=1e-6)
+    assert torch.allclose(Fn.softplus_with(x, 2.0, 20.0), torch.log1p(torch.exp(2 * x)) / 2, atol=1e-6) and torch.allclose(Fn.elu_with(x, 0.5), torch.where(x > 0, x, 0.5 * (x.exp() - 1)))
+    img = torch.randn(2, 3, 4)
+    assert torch.allclose(Fn.prelu(img, [0.1, 0.2, 0.3]), torch.where(img > 0, img, img * torch.tensor([0.1, 0.2, 0.3]).view(1, 3, 1)))
+    assert torch.allclose(Fn.prelu(img, 0.25), torch.where(img > 0, img, 0.25 * img)) and torch.allclose(Fn.gelu_with(x, "sigmoid"), x * torch.sigmoid(1.702 * x))
+    for bad in (lambda: Fn.hardtanh_with(x, 1.0, 0.0), lambda: Fn.softplus_with(x, 0.0), lambda: Fn.prelu(img, [0.1, 0.2])):
+        with pytest.raises(FerrotorchError):
+            bad()
