@@ -323,3 +323,14 @@ class ProfileSchedule:
             if self.on_trace_ready:
                 self.on_trace_ready(rep)
         self.step_num += 1
+
+
+class flops:  # noqa: N801  (namespace: ``profiler.flops.estimate(op, shapes)``, ferrotorch-profiler/src/flops.rs:41)
+    @staticmethod
+    def estimate(op_name: str, input_shapes):
+        """Integer FLOP estimate of one operation, ``None`` for an operation without a rule."""
+        v = estimate_flops(op_name, [list(s) for s in input_shapes])
+        return None if v is None else int(v)
+
+
+estimate = flops.estimate

@@ -13,7 +13,9 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import regex as _re
 
-from ..errors import InvalidArgument
+from dataclasses import dataclass
+
+from ..errors import Internal, InvalidArgument
 
 _GPT2_SPLIT = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
 _LLAMA3_SPLIT = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"""
@@ -172,8 +174,56 @@ def decode(tok: Tokenizer, ids, skip_special_tokens: bool = True) -> str:
     return tok.decode(ids, skip_special_tokens)
 
 
-def apply_chat_template(messages: Sequence[Dict[str, str]], template: str = "llama3", add_generation_prompt: bool = True) -> str:
-    """Render a conversation. ``template``: "llama3", "chatml", "llama2", "plain", or a format string with ``{role}`` / ``{content}``."""
+@dataclass
+class ChatMessage:
+    """One turn of a conversation (ferrotorch-tokenize/src/lib.rs:167)."""
+    role: str
+    content: str
+
+    def __getitem__(self, k):                                 # the built-in templates index messages like dicts
+        return getattr(self, k)
+
+
+def vocab_size(tok: Tokenizer, with_added_tokens: bool = True) -> int:
+    return len(tok.vocab) if with_added_tokens else len(tok.vocab) - len(tok.added)
+
+
+def token_to_id(tok: Tokenizer, token: str) -> Optional[int]:
+    return tok.token_to_id(token)
+
+
+def id_to_token(tok: Tokenizer, i: int) -> Optional[str]:
+    return tok.id_to_token(i)
+
+
+def _render_jinja(template: str, messages, add_generation_prompt: bool, bos_token: Optional[str], eos_token: Optional[str]) -> str:
+    """Hugging Face chat templates are Jinja2: rendered in a sandbox with ``messages``, ``add_generation_prompt``, ``bos_token``, ``eos_token``
+    and ``raise_exception(msg)`` (lib.rs:225-300). Undefined variables are errors, as in the reference."""
+    try:
+        import jinja2
+        from jinja2.sandbox import ImmutableSandboxedEnvironment
+    except ImportError:
+        raise InvalidArgument("Jinja chat templates need the jinja2 package") from None
+
+    def raise_exception(msg):
+        raise jinja2.exceptions.TemplateError(msg)
+    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, undefined=jinja2.StrictUndefined)
+    env.globals["raise_exception"] = raise_exception
+    msgs = [{"role": m["role"], "content": m["content"]} for m in messages]
+    try:
+        return env.from_string(template).render(messages=msgs, add_generation_prompt=add_generation_prompt, bos_token=bos_token or "", eos_token=eos_token or "")
+    except jinja2.exceptions.TemplateError as e:
+        raise InvalidArgument(f"chat template failed to render: {e}") from None
+
+
+def apply_chat_template(messages, template="llama3", add_generation_prompt: bool = True, bos_token: Optional[str] = None, eos_token: Optional[str] = None) -> str:
+    """Render a conversation. ``template``: "llama3", "chatml", "llama2", "plain", a Jinja2 template (the ``chat_template`` string of a
+    ``tokenizer_config.json``), or a format string with ``{role}`` / ``{content}``. The reference's argument order
+    ``(template, messages, ...)`` is accepted too."""
+    if isinstance(messages, str) and not isinstance(template, str):
+        messages, template = template, messages
+    if "{%" in template or "{{" in template:
+        return _render_jinja(template, messages, add_generation_prompt, bos_token, eos_token)
     if template == "llama3":
         s = "<|begin_of_text|>" + "".join(f"<|start_header_id|>{m['role']}<|end_header_id|>\n\n{m['content']}<|eot_id|>" for m in messages)
         return s + ("<|start_header_id|>assistant<|end_header_id|>\n\n" if add_generation_prompt else "")
@@ -194,3 +244,34 @@ def apply_chat_template(messages: Sequence[Dict[str, str]], template: str = "lla
     if template == "plain":
         return "\n".join(f"{m['role']}: {m['content']}" for m in messages) + ("\nassistant:" if add_generation_prompt else "")
     return "".join(template.format(role=m["role"], content=m["content"]) for m in messages)
+
+
+def apply_chat_template_to_ids(tok: Tokenizer, template: str, messages, add_generation_prompt: bool = True, bos_token: Optional[str] = None,
+                               eos_token: Optional[str] = None, add_special_tokens: bool = False):
+    """``(rendered text, token ids)``. Templates normally write the BOS token themselves, hence ``add_special_tokens=False`` by default
+    (lib.rs:313)."""
+    text = apply_chat_template(messages, template, add_generation_prompt, bos_token if bos_token is not None else tok.bos_token,
+                               eos_token if eos_token is not None else tok.eos_token)
+    return text, tok.encode(text, add_special_tokens)
+
+
+def load_chat_template(tokenizer_config_path) -> Optional[str]:
+    """The ``chat_template`` of a ``tokenizer_config.json``: a string, or the first ``template`` of a list of named templates; ``None`` when the
+    file has none. An unreadable file is an :class:`Internal` error, malformed content an :class:`InvalidArgument` (lib.rs:349)."""
+    import json
+    try:
+        raw = open(tokenizer_config_path, "rb").read()
+    except OSError as e:
+        raise Internal(f"failed to read tokenizer_config {tokenizer_config_path}: {e!r}") from None
+    try:
+        value = json.loads(raw)
+    except ValueError as e:
+        raise InvalidArgument(f"failed to parse tokenizer_config {tokenizer_config_path}: {e}") from None
+    ct = value.get("chat_template") if isinstance(value, dict) else None
+    if ct is None:
+        return None
+    if isinstance(ct, str):
+        return ct
+    if isinstance(ct, list):
+        return next((e["template"] for e in ct if isinstance(e, dict) and isinstance(e.get("template"), str)), None)
+    raise InvalidArgument(f"tokenizer_config {tokenizer_config_path} has chat_template of unexpected type")

@@ -4,7 +4,7 @@ from .models import (BasicBlock, Bottleneck, ResNet, resnet18, resnet34, resnet5
                      MobileNetV2, mobilenet_v2, DenseNet, densenet121, ConvNeXt, convnext_tiny, EfficientNet, efficientnet_b0, UNet, Yolo,
                      ModelRegistry, ModelConstructor, list_models, get_model, register_model, create_feature_extractor, FeatureExtractor, Conv1x1)
 from .ops import (box_convert, box_area, box_iou, generalized_box_iou, distance_box_iou, complete_box_iou, clip_boxes_to_image, remove_small_boxes,
-                  nms, batched_nms, sigmoid_focal_loss, focal_loss, roi_align, roi_pool)
+                  nms, batched_nms, sigmoid_focal_loss, focal_loss, roi_align, roi_align_with_aligned, roi_pool)
 from .data import (read_image, write_image, Mnist, Cifar10, Cifar100, DatasetFolder, ImageFolder, Compose, ToTensor, VisionNormalize, Resize,
                    CenterCrop, RandomCrop, RandomHorizontalFlip, RandomVerticalFlip, RandomResizedCrop, RandomRotation, ColorJitter, GaussianNoise,
                    RandomGaussianBlur, RandomApply, RandomChoice, ElasticTransform, TrivialAugmentWide, VisionToTensor, vision_manual_seed, RawImage,

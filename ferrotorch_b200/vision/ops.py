@@ -199,3 +199,9 @@ def roi_pool(feat: torch.Tensor, rois: torch.Tensor, output_size, spatial_scale:
                 if he > hs and we > ws:
                     out[k, :, i, j] = feat[b, :, hs:he, ws:we].amax((1, 2))
     return out
+
+
+def roi_align_with_aligned(feat, rois, output_size, spatial_scale: float = 1.0, sampling_ratio: int = 2, aligned: bool = True):
+    """:func:`roi_align` with the half-pixel switch spelled out: ``aligned=True`` shifts box coordinates by half a pixel (newer detectors),
+    ``False`` is the legacy rule of the published COCO R-CNN weights (ferrotorch-vision/src/ops.rs:773)."""
+    return roi_align(feat, rois, output_size, spatial_scale, sampling_ratio, aligned)

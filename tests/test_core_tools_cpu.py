@@ -377,3 +377,53 @@ def test_distribution_constraints_and_transformed_entropy():
             D.TransformedDistribution(base, bad).entropy()
     y = logn.rsample((4,))
     assert y.shape == (4,) and (y > 0).all() and torch.isfinite(logn.log_prob(y)).all()
+
+
+def test_chat_templates_jinja_ids_and_config_loading(tmp_path):
+    """Jinja chat templates render as transformers renders them; id helpers, template-to-ids and tokenizer_config loading follow
+    ferrotorch-tokenize/src/lib.rs:143-400."""
+    import json
+    from ferrotorch_b200 import tokenize as T
+    from ferrotorch_b200.errors import Internal, InvalidArgument
+    tpl = ("{{ bos_token }}{% for m in messages %}{% if m['role'] not in ['system', 'user', 'assistant'] %}{{ raise_exception('bad role ' + m['role']) }}{% endif %}"
+           "<|{{ m['role'] }}|>\\n{{ m['content'] | trim }}{{ eos_token }}\\n{% endfor %}{% if add_generation_prompt %}<|assistant|>\\n{% endif %}")
+    msgs = [T.ChatMessage("system", "Be brief."), T.ChatMessage("user", "  Hi there  ")]
+    got = T.apply_chat_template(msgs, tpl, True, "<s>", "</s>")
+    assert got.startswith("<s><|system|>") and got.endswith("<|assistant|>\\n") and "Hi there</s>" in got
+    hf = pytest.importorskip("transformers")
+    from transformers.utils.chat_template_utils import render_jinja_template
+    want = render_jinja_template(conversations=[[{"role": m.role, "content": m.content} for m in msgs]], chat_template=tpl, add_generation_prompt=True,
+                                 bos_token="<s>", eos_token="</s>")[0][0]
+    assert got == want
+    assert T.apply_chat_template(tpl, msgs, False, "<s>", "</s>") == T.apply_chat_template(msgs, tpl, False, "<s>", "</s>") != got      # reference argument order
+    with pytest.raises(InvalidArgument, match="bad role tool"):
+        T.apply_chat_template([T.ChatMessage("tool", "x")], tpl)
+    with pytest.raises(InvalidArgument):
+        T.apply_chat_template(msgs, "{{ undefined_variable }}")
+    with pytest.raises(InvalidArgument):
+        T.apply_chat_template(msgs, "{% for %}")
+    assert T.apply_chat_template([{"role": "user", "content": "q"}], "chatml") == "<|im_start|>user\nq<|im_end|>\n<|im_start|>assistant\n"
+
+    vocab = {chr(0x120 + 0): 0}
+    tok = T.Tokenizer({"a": 0, "b": 1, "ab": 2, "<|user|>": 3}, [("a", "b")], {"<s>": 4, "</s>": 5}, bos_token="<s>", eos_token="</s>")
+    assert T.vocab_size(tok) == 6 and T.vocab_size(tok, with_added_tokens=False) == 4 and T.token_to_id(tok, "ab") == 2 and T.token_to_id(tok, "zz") is None
+    assert T.id_to_token(tok, 5) == "</s>" and T.id_to_token(tok, 99) is None
+    text, ids = T.apply_chat_template_to_ids(tok, "{{ bos_token }}{% for m in messages %}{{ m['content'] }}{% endfor %}{{ eos_token }}", [T.ChatMessage("user", "abab")])
+    assert text == "<s>abab</s>" and ids == [4, 2, 2, 5]
+
+    (tmp_path / "a.json").write_text(json.dumps({"chat_template": tpl}))
+    (tmp_path / "b.json").write_text(json.dumps({"chat_template": [{"name": "default", "template": "X"}, {"name": "tool_use", "template": "Y"}]}))
+    (tmp_path / "c.json").write_text(json.dumps({"model_max_length": 4}))
+    (tmp_path / "d.json").write_text(json.dumps({"chat_template": 7}))
+    (tmp_path / "e.json").write_text("{nope")
+    assert T.load_chat_template(tmp_path / "a.json") == tpl and T.load_chat_template(tmp_path / "b.json") == "X" and T.load_chat_template(tmp_path / "c.json") is None
+    for bad in ("d.json", "e.json"):
+        with pytest.raises(InvalidArgument):
+            T.load_chat_template(tmp_path / bad)
+    with pytest.raises(Internal):
+        T.load_chat_template(tmp_path / "missing.json")
+    from ferrotorch_b200 import profiler as P, vision as V
+    assert P.flops.estimate("matmul", [[4, 5], [5, 6]]) == 240 and P.estimate("my_custom_op", [[3, 4]]) is None
+    feat, rois = torch.randn(1, 2, 8, 8), torch.tensor([[0.0, 1.0, 1.0, 5.0, 6.0]])
+    assert torch.equal(V.roi_align_with_aligned(feat, rois, 2, 1.0, 2, False), V.roi_align(feat, rois, 2, 1.0, 2, False))
+    assert not torch.equal(V.roi_align_with_aligned(feat, rois, 2, 1.0, 2, True), V.roi_align(feat, rois, 2, 1.0, 2, False))
