@@ -1,0 +1,19 @@
+// Launcher of the two-SM (tcgen05 cta_group::2) GEMM, shared between gemm_2sm.cu (definition) and gemm_tcgen05.cu (dispatch).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+struct Gemm2Epi {
+  int act;                 // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh), 4 silu
+  const void* residual;    // [M, N] in the output dtype, rows ldr elements apart, or null
+  int64_t ldr;
+  int in_f16;              // operands are fp16 instead of bf16
+};
+
+// True when the pair kernel should take the problem: enabled, M large enough for 256-row tiles, the device can co-schedule CTA pairs.
+bool ft_gemm2_wanted(int M, int N, int K, int k_splits);
+
+// Same contract as the one-SM launcher: D[splits][M][N] = A (x) B restricted to each K slice (+ bias, activation, residual when k_splits == 1).
+// Returns FT_OK / FT_ERR_* / a CUDA error code.
+int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn,
+                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi);

@@ -20,6 +20,7 @@
 // and the three-launch linear_fused CUDA path of ferrotorch-core/src/grad_fns/linalg.rs:1223-1262.
 #include "common.cuh"
 #include "host_common.h"
+#include "gemm_2sm.h"
 
 namespace {
 
@@ -502,6 +503,12 @@ static int gemm_impl(const void* A, const void* B, void* D, const void* bias, in
   const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
+  // Large-M problems without a row-shift table go to the CTA-pair kernel (256 x 256 tiles, tcgen05 cta_group::2); FT_ERR_DRIVER from it means
+  // that this device cannot co-schedule pairs, and the one-SM kernel below takes over.
+  if (a_cols == 0 && b_atoms_per_tap == 0 && ft_gemm2_wanted(M, N, K, k_splits)) {
+    const int r2 = ft_gemm2_launch(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, k_splits, stream, Gemm2Epi{epi.act, epi.residual, epi.ldr, epi.in_f16});
+    if (r2 != FT_ERR_DRIVER) return r2;
+  }
   int dev = 0;
   FT_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return FT_ERR_ARG;

@@ -97,7 +97,8 @@ def nms(boxes: torch.Tensor, scores: torch.Tensor, iou_threshold: float) -> torc
     CUDA boxes the mask + on-device sweep kernels."""
     if boxes.numel() == 0:
         return torch.empty(0, dtype=torch.long, device=boxes.device)
-    order = scores.argsort(descending=True)
+    # a stable sort: tied scores keep their input order, so the host and the device sweep visit the boxes in the same order
+    order = scores.argsort(descending=True, stable=True)
     b = boxes[order].float().contiguous()
     n = len(b)
     if boxes.is_cuda:
@@ -129,7 +130,7 @@ def batched_nms(boxes, scores, idxs, iou_threshold: float):
         sel = torch.where(idxs == c)[0]
         keep[sel[nms(boxes[sel], scores[sel], iou_threshold)]] = True
     k = torch.where(keep)[0]
-    return k[scores[k].argsort(descending=True)]
+    return k[scores[k].argsort(descending=True, stable=True)]
 
 
 def sigmoid_focal_loss(inputs, targets, alpha: float = 0.25, gamma: float = 2.0, reduction: str = "none"):
