@@ -37,6 +37,9 @@ def _parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then says so and is not a headline number)")
     ap.add_argument("--comm", default=None, choices=[None, "nccl", "fused"])
+    ap.add_argument("--breakdown", action="store_true",
+                    help="after the timed runs, time every kernel class of one step with CUDA events (optimizer serialised on the compute "
+                         "stream so that the classes add up to the step) and add the table to the JSON line")
     return ap.parse_args()
 
 
@@ -93,6 +96,61 @@ def reference_arm(args):
     print(json.dumps({"impl": "reference", "unavailable": "reference is a Rust workspace: not pip-installable "
                       "(no setup.py/pyproject.toml), no cargo/rustc offline, and it has no GPU FSDP/bf16 training path"}))
     return 0
+
+
+def _classify(name, raw):
+    """Kernel class of one native launcher call (GEMMs are split by operand layout: NT = forward, NN = data gradient, TN = weight gradient)."""
+    if name in ("ft_gemm_bf16", "ft_gemm_ex"):
+        a_mn, b_mn = (raw[10], raw[11]) if name == "ft_gemm_bf16" else (raw[12], raw[13])
+        return {(0, 0): "gemm forward", (0, 1): "gemm dgrad", (1, 1): "gemm wgrad", (1, 0): "gemm other"}[(a_mn, b_mn)]
+    if name.startswith("ft_flash_fwd"):
+        return "attention forward"
+    if name.startswith("ft_flash_bwd"):
+        return "attention backward"
+    if "rmsnorm" in name:
+        return "rmsnorm"
+    if "rope" in name:
+        return "rope"
+    if "swiglu" in name:
+        return "swiglu"
+    if "cross_entropy" in name:
+        return "cross entropy"
+    if "adamw" in name or "fsdp" in name:
+        return "optimizer (+collectives)"
+    if "embedding" in name:
+        return "embedding"
+    return "other kernels (" + name + ")"
+
+
+def step_breakdown(engine, step_fn, barrier, _lib, torch):
+    """One step with every launch of this library bracketed by CUDA events. The side stream is switched off for it, so the classes run one
+    after the other and their sum plus the remainder (PyTorch element-wise kernels, allocator, host gaps) is the serialised step time."""
+    side, engine.side = engine.side, None
+    try:
+        for i in range(2):
+            step_fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_fn(2)
+        e1.record()
+        torch.cuda.synchronize()
+        plain_ms = e0.elapsed_time(e1)
+        _lib.trace_begin(_classify)
+        e0.record()
+        step_fn(3)
+        e1.record()
+        table = _lib.trace_end()
+        traced_ms = e0.elapsed_time(e1)
+    finally:
+        engine.side = side
+    barrier()
+    total = sum(v["ms"] for v in table.values())
+    rows = {k: {"ms": round(v["ms"], 3), "calls": v["calls"], "share": round(v["ms"] / traced_ms, 4)}
+            for k, v in sorted(table.items(), key=lambda kv: -kv[1]["ms"])}
+    rows["remainder (torch element-wise, allocator, host gaps)"] = {"ms": round(traced_ms - total, 3), "calls": None,
+                                                                   "share": round((traced_ms - total) / traced_ms, 4)}
+    return {"serialised_step_ms": round(plain_ms, 3), "traced_step_ms": round(traced_ms, 3), "classes": rows}
 
 
 def main():
@@ -181,6 +239,10 @@ def main():
     ms_e2e, wall_e2e, _, clocks_e2e, last_e2e = timed(step_e2e, K)
     ms_e2e = max(ms_e2e, wall_e2e) if world == 1 else ms_e2e
 
+    breakdown = None
+    if args.breakdown:
+        breakdown = step_breakdown(engine, step_device, barrier, _lib, torch)
+
     tokens_per_step = B * S * world
     value = tokens_per_step * K / (ms_dev / 1e3)
     e2e_value = tokens_per_step * K / (ms_e2e / 1e3)
@@ -204,6 +266,8 @@ def main():
             "kernel_status": status, "impl": "ours",
             "mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
         }
+        if breakdown is not None:
+            out["breakdown"] = breakdown
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

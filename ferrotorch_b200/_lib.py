@@ -136,6 +136,32 @@ def _unwrap(a):
     return a
 
 
+_trace = None  # while a launch trace is open: {"events": [(label, start, end)], "classify": callable or None}
+
+
+def trace_begin(classify=None) -> None:
+    """Start timing every native launcher call with a CUDA event pair on its own stream. ``classify(fn_name, args)`` may map a call to a
+    label (default: the launcher's name). Meant for step breakdowns: it adds two event records per launch, so a traced step is a little
+    slower than an untraced one."""
+    global _trace
+    _trace = {"events": [], "classify": classify}
+
+
+def trace_end() -> dict:
+    """Stop the trace, synchronise and return ``{label: {"ms": total, "calls": n}}``."""
+    global _trace
+    t, _trace = _trace, None
+    out: dict = {}
+    if t is None:
+        return out
+    torch.cuda.synchronize()
+    for label, e0, e1 in t["events"]:
+        d = out.setdefault(label, {"ms": 0.0, "calls": 0})
+        d["ms"] += e0.elapsed_time(e1)
+        d["calls"] += 1
+    return out
+
+
 def call(fn_name: str, *args) -> None:
     """Call an exported launcher ``int fn(...)`` and raise on a non-zero return code.
 
@@ -146,7 +172,16 @@ def call(fn_name: str, *args) -> None:
     launch_calls += 1
     if len(args) != len(fn.argtypes):
         raise FerrotorchError(f"{fn_name}: expected {len(fn.argtypes)} arguments, got {len(args)}")
-    check(fn(*[_unwrap(a) for a in args]), fn_name)
+    raw = [_unwrap(a) for a in args]
+    if _trace is None:
+        check(fn(*raw), fn_name)
+        return
+    label = _trace["classify"](fn_name, raw) if _trace["classify"] else fn_name
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    check(fn(*raw), fn_name)
+    e1.record()
+    _trace["events"].append((label or fn_name, e0, e1))
 
 
 def read_status() -> int:

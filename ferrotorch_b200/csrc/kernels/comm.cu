@@ -104,6 +104,21 @@ FT_DEVICE void comm_end(const CommSync& s, uint32_t* status) {
   if (s.seq_dev && threadIdx.x == 0) *s.seq_dev = s.seq;
 }
 
+// A CTA whose opening rendezvous timed out still takes part in the grid's bookkeeping: it is counted, and if it is the last one it zeroes the
+// counter and advances the device-side sequence number. Without this a launch in which only some CTAs time out (or a peer's flag arrives just
+// after the deadline) would leave the counter non-zero and every later collective on the communicator would fail to elect a last CTA.
+// The data phase and the closing handshake are skipped: nothing of a peer is touched after a timeout.
+FT_DEVICE void comm_abort(const CommSync& s) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(s.counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *s.counter = 0;
+      if (s.seq_dev) *s.seq_dev = s.seq;
+    }
+  }
+}
+
 template <typename T> struct Vec16;
 template <> struct Vec16<__nv_bfloat16> {
   static constexpr int N = 8;
@@ -121,7 +136,7 @@ template <> struct Vec16<float> {
 // ---------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(512) allreduce_2shot_kernel(PeerPtrs bufs, CommSync s, size_t n, float scale, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = n / V;
   const size_t per = (nvec + s.world - 1) / s.world;
@@ -161,7 +176,7 @@ __global__ void __launch_bounds__(512) allreduce_2shot_kernel(PeerPtrs bufs, Com
 // mapping of the multicast address of the same symmetric buffer. Accumulation is f32 inside the switch.
 __global__ void __launch_bounds__(512) allreduce_nvls_bf16_kernel(__nv_bfloat16* mc, __nv_bfloat16* local, CommSync s, size_t n,
                                                                   float scale, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   const size_t nvec = n / 8;
   const size_t per = (nvec + s.world - 1) / s.world;
   const size_t lo = per * s.rank, hi = min(nvec, lo + per);
@@ -191,7 +206,7 @@ __global__ void __launch_bounds__(512) allreduce_nvls_bf16_kernel(__nv_bfloat16*
 template <typename T>
 __global__ void __launch_bounds__(512) allreduce_1shot_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t n, float scale,
                                                               uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = n / V;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
@@ -221,7 +236,7 @@ __global__ void __launch_bounds__(512) allreduce_1shot_kernel(PeerPtrs bufs, T* 
 template <typename T>
 __global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t chunk, float scale,
                                                              uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = chunk / V, base = chunk * s.rank;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
@@ -244,7 +259,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerPtrs bufs, T* _
 // all-gather (push): buf_q[rank*chunk + i] = src_local[i] for every q
 template <typename T>
 __global__ void __launch_bounds__(512) allgather_kernel(PeerPtrs bufs, const T* __restrict__ src, CommSync s, size_t chunk, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = chunk / V, base = chunk * s.rank;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
@@ -258,7 +273,7 @@ __global__ void __launch_bounds__(512) allgather_kernel(PeerPtrs bufs, const T* 
 // addressed to itself from every peer. The building block of Ulysses sequence parallelism and of expert dispatch / combine.
 template <typename T>
 __global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, size_t chunk, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = chunk / V, total = nvec * s.world;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -274,7 +289,7 @@ __global__ void __launch_bounds__(512) alltoall_kernel(PeerPtrs bufs, T* __restr
 // broadcast (pull): out[i] = buf_root[i] on every rank
 template <typename T>
 __global__ void __launch_bounds__(512) broadcast_kernel(PeerPtrs bufs, T* __restrict__ out, CommSync s, int root, size_t n, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
   const size_t nvec = n / V;
   if (s.rank != root || out != bufs.p[root]) {
@@ -292,7 +307,7 @@ struct AdamWArgsC { float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
 __global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, CommSync s, float* __restrict__ master,
                                                                float* __restrict__ m, float* __restrict__ v, size_t chunk, AdamWArgsC a,
                                                                const float* __restrict__ grad_scale_ptr, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   const float inv_world = (grad_scale_ptr ? *grad_scale_ptr : 1.f) / (float)s.world;
   const float decay = 1.f - a.lr * a.weight_decay, step = a.lr / a.bias_c1, inv_c2 = rsqrtf(a.bias_c2);
   const size_t nvec = chunk / 8, base = chunk * s.rank;
@@ -337,7 +352,7 @@ __global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, P
 
 // stand-alone device barrier (phase 0 + phase 1 rendezvous, no data)
 __global__ void comm_barrier_kernel(CommSync s, uint32_t* status) {
-  if (!comm_begin(s, status)) return;
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
   comm_end(s, status);
 }
 
@@ -383,52 +398,55 @@ int fill_sync(CommSync& s, void* const* flag_ptrs, uint32_t* counter, int rank, 
 // ---------------------------------------------------------------------------------------------------------
 // ring slot layout on the receiver: [payload bytes ...]; flags: u32 per slot holding the message number that filled it (1, 2, ...),
 // ack: u32 per slot on the SENDER holding the number of the last message the receiver consumed from that slot.
+// Both point-to-point kernels count their CTAs in one u32: the low half counts CTAs that are through, the high half those whose wait ran
+// out. The last CTA always resets the word (so a partial timeout leaves the channel usable) and raises the flag / acknowledgement only when
+// no CTA failed.
+FT_DEVICE void p2p_finish(unsigned int* counter, bool ok, uint32_t* signal, uint32_t msg, bool fence) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(counter, ok ? 1u : 0x10001u);
+    if ((prev & 0xffffu) == gridDim.x - 1) {
+      const unsigned int fails = (prev >> 16) + (ok ? 0u : 1u);
+      *counter = 0;
+      if (fence) __threadfence_system();
+      if (fails == 0) st_release_sys(signal, msg);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(512) p2p_put_kernel(const uint4* __restrict__ src, uint4* __restrict__ peer_slot, size_t nvec, uint32_t* __restrict__ peer_flag,
                                                       const uint32_t* __restrict__ my_ack, uint32_t msg, uint32_t prev_msg_in_slot, unsigned int* __restrict__ counter,
-                                                      uint32_t* status) {
+                                                      uint64_t timeout_ns, uint32_t* status) {
   // the slot must have been drained by the receiver (its ack names the previous message that used this slot)
   __shared__ int ok_sh;
   if (threadIdx.x == 0) {
     ok_sh = 1;
-    if (prev_msg_in_slot != 0 && !wait_flag_ge(my_ack, prev_msg_in_slot, COMM_TIMEOUT_NS)) {
+    if (prev_msg_in_slot != 0 && !wait_flag_ge(my_ack, prev_msg_in_slot, timeout_ns)) {
       ft_set_status(status, FT_K_COMM, 21, msg);
       ok_sh = 0;
     }
   }
   __syncthreads();
-  if (!ok_sh) return;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) peer_slot[i] = src[i];
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(counter, 1u);
-    if (prev == gridDim.x - 1) {
-      *counter = 0;
-      __threadfence_system();
-      st_release_sys(peer_flag, msg);
-    }
-  }
+  const bool ok = ok_sh != 0;
+  if (ok)
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) peer_slot[i] = src[i];
+  p2p_finish(counter, ok, peer_flag, msg, true);
 }
 
 __global__ void __launch_bounds__(512) p2p_get_kernel(uint4* __restrict__ dst, const uint4* __restrict__ my_slot, size_t nvec, const uint32_t* __restrict__ my_flag,
-                                                      uint32_t* __restrict__ peer_ack, uint32_t msg, unsigned int* __restrict__ counter, uint32_t* status) {
+                                                      uint32_t* __restrict__ peer_ack, uint32_t msg, unsigned int* __restrict__ counter, uint64_t timeout_ns,
+                                                      uint32_t* status) {
   __shared__ int ok_sh;
   if (threadIdx.x == 0) {
-    ok_sh = wait_flag_ge(my_flag, msg, COMM_TIMEOUT_NS) ? 1 : 0;
+    ok_sh = wait_flag_ge(my_flag, msg, timeout_ns) ? 1 : 0;
     if (!ok_sh) ft_set_status(status, FT_K_COMM, 22, msg);
   }
   __syncthreads();
-  if (!ok_sh) return;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) dst[i] = __ldcg(my_slot + i);
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int prev = atomicAdd(counter, 1u);
-    if (prev == gridDim.x - 1) {
-      *counter = 0;
-      st_release_sys(peer_ack, msg);                       // the sender may overwrite the slot
-    }
-  }
+  const bool ok = ok_sh != 0;
+  if (ok)
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) dst[i] = __ldcg(my_slot + i);
+  p2p_finish(counter, ok, peer_ack, msg, false);                // the sender may overwrite the slot
 }
 
 }  // namespace
@@ -570,7 +588,7 @@ FT_EXPORT int ft_comm_p2p_put(const void* src, void* peer_slot, int64_t bytes, v
   if (bytes <= 0 || bytes % 16 || msg == 0) return FT_ERR_ARG;
   const int grid = comm_grid((size_t)bytes / 16, 32);
   p2p_put_kernel<<<grid, 512, 0, st>>>((const uint4*)src, (uint4*)peer_slot, (size_t)bytes / 16, (uint32_t*)peer_flag, (const uint32_t*)my_ack, msg, prev_msg_in_slot,
-                                       counter, ft_status_ptr());
+                                       counter, comm_timeout_ns(), ft_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -579,7 +597,7 @@ FT_EXPORT int ft_comm_p2p_get(void* dst, const void* my_slot, int64_t bytes, con
   if (bytes <= 0 || bytes % 16 || msg == 0) return FT_ERR_ARG;
   const int grid = comm_grid((size_t)bytes / 16, 32);
   p2p_get_kernel<<<grid, 512, 0, st>>>((uint4*)dst, (const uint4*)my_slot, (size_t)bytes / 16, (const uint32_t*)my_flag, (uint32_t*)peer_ack, msg, counter,
-                                       ft_status_ptr());
+                                       comm_timeout_ns(), ft_status_ptr());
   return (int)cudaGetLastError();
 }
 

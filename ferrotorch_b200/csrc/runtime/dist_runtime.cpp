@@ -7,6 +7,7 @@
 // length-prefixed frames, read-timeout based recv_timeout, gather/scatter barrier), star collectives with
 // Sum/Mean in fixed rank order (collective.rs:64-682), ring all-reduce / binomial-tree broadcast / ring barrier
 // (gloo_native/collectives.rs:85-300), typed errors (error.rs:8-52).
+#include <cstdlib>
 #include <arpa/inet.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
@@ -182,14 +183,19 @@ class TcpBackend : public Backend {
     ::setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &buf, sizeof(buf));
     ::setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof(buf));
   }
-  int listen_on(int port, int* out_fd) {
+  // The listener binds the rendezvous address itself (the one the peers connect to), not every interface: a rank announcement is all the
+  // authentication the wire format has, so the port must not be reachable from networks the job does not use. FT_TCP_BIND_ANY=1 restores
+  // the wildcard bind for hosts whose rendezvous address is a NAT or load-balancer address that no local interface carries.
+  int listen_on(const std::string& host, int port, int* out_fd) {
     int fd = ::socket(AF_INET, SOCK_STREAM, 0);
     if (fd < 0) return E_IO;
     int one = 1;
     ::setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
     sockaddr_in a{};
     a.sin_family = AF_INET;
-    a.sin_addr.s_addr = htonl(INADDR_ANY);
+    const char* any = ::getenv("FT_TCP_BIND_ANY");
+    if (any && any[0] == '1') a.sin_addr.s_addr = htonl(INADDR_ANY);
+    else if (::inet_pton(AF_INET, host.c_str(), &a.sin_addr) != 1) { ::close(fd); return E_IO; }
     a.sin_port = htons((uint16_t)port);
     if (::bind(fd, (sockaddr*)&a, sizeof(a)) < 0 || ::listen(fd, 64) < 0) { ::close(fd); return E_IO; }
     *out_fd = fd;
@@ -244,7 +250,7 @@ class TcpBackend : public Backend {
     if (world_ == 1) return OK;
     if (!full_mesh) {
       if (rank_ == 0) {
-        int lfd = -1, e = listen_on(port, &lfd);
+        int lfd = -1, e = listen_on(host, port, &lfd);
         if (e) return e;
         e = accept_peers(lfd, world_ - 1, timeout_ms);
         ::close(lfd);
@@ -254,7 +260,7 @@ class TcpBackend : public Backend {
     }
     // full mesh: listen for higher ranks, connect to lower ranks
     int lfd = -1;
-    if (rank_ < world_ - 1) { int e = listen_on(port + rank_, &lfd); if (e) return e; }
+    if (rank_ < world_ - 1) { int e = listen_on(host, port + rank_, &lfd); if (e) return e; }
     for (int p = 0; p < rank_; p++) { int e = connect_to(host, port + p, p, timeout_ms); if (e) { if (lfd >= 0) ::close(lfd); return e; } }
     int e = OK;
     if (lfd >= 0) { e = accept_peers(lfd, world_ - 1 - rank_, timeout_ms); ::close(lfd); }

@@ -222,9 +222,138 @@ class Pipeline:
 MAX_RPC_BYTES = 1 << 30
 
 
+# Wire form of RPC payloads: a tagged, length-prefixed tree of plain data. Nothing on the receiving side is executed or imported
+# (the reference's RPC likewise ships opaque length-prefixed byte payloads and never deserialises objects,
+# ferrotorch-distributed/src/rpc.rs), so a peer that can reach the port can at worst send garbage that fails to parse.
+_WIRE_DT = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5, torch.int16: 6,
+            torch.int8: 7, torch.uint8: 8, torch.bool: 9}
+_WIRE_DT_INV = {v: k for k, v in _WIRE_DT.items()}
+_WIRE_MAX_DEPTH = 64
+
+
+def wire_dumps(obj) -> bytes:
+    """Encode ``None``, bool, int, float, str, bytes, list, tuple, dict (with encodable keys) and CPU/device tensors (shipped as raw bytes)."""
+    out = bytearray()
+
+    def put(o, depth):
+        if depth > _WIRE_MAX_DEPTH:
+            raise errors.InvalidArgument("RPC payload is nested too deeply")
+        if o is None:
+            out.append(ord("N"))
+        elif isinstance(o, bool):
+            out.append(ord("T") if o else ord("F"))
+        elif isinstance(o, int):
+            b = o.to_bytes((o.bit_length() + 8) // 8 or 1, "little", signed=True)
+            out.append(ord("i")); out.extend(struct.pack("<I", len(b))); out.extend(b)
+        elif isinstance(o, float):
+            out.append(ord("d")); out.extend(struct.pack("<d", o))
+        elif isinstance(o, str):
+            b = o.encode()
+            out.append(ord("s")); out.extend(struct.pack("<Q", len(b))); out.extend(b)
+        elif isinstance(o, (bytes, bytearray, memoryview)):
+            b = bytes(o)
+            out.append(ord("b")); out.extend(struct.pack("<Q", len(b))); out.extend(b)
+        elif isinstance(o, torch.Tensor):
+            t = o.detach().cpu().contiguous()
+            if t.dtype not in _WIRE_DT:
+                raise errors.InvalidArgument(f"RPC cannot ship tensors of dtype {t.dtype}")
+            raw = t.view(torch.int16).numpy().tobytes() if t.dtype == torch.bfloat16 else t.numpy().tobytes()
+            out.append(ord("X")); out.extend(struct.pack("<BB", _WIRE_DT[t.dtype], t.dim()))
+            for d in t.shape:
+                out.extend(struct.pack("<Q", d))
+            out.extend(struct.pack("<Q", len(raw))); out.extend(raw)
+        elif isinstance(o, (list, tuple)):
+            out.append(ord("l") if isinstance(o, list) else ord("t")); out.extend(struct.pack("<Q", len(o)))
+            for x in o:
+                put(x, depth + 1)
+        elif isinstance(o, dict):
+            out.append(ord("m")); out.extend(struct.pack("<Q", len(o)))
+            for k, v in o.items():
+                put(k, depth + 1)
+                put(v, depth + 1)
+        else:
+            raise errors.InvalidArgument(f"RPC payloads carry plain data and tensors only, not {type(o).__name__}")
+    put(obj, 0)
+    return bytes(out)
+
+
+def wire_loads(data: bytes):
+    """Inverse of :func:`wire_dumps`. Malformed input raises :class:`~ferrotorch_b200.errors.InvalidArgument`; nothing is executed."""
+    mv = memoryview(data)
+    pos = 0
+
+    def take(n):
+        nonlocal pos
+        if n < 0 or pos + n > len(mv):
+            raise errors.InvalidArgument("RPC payload is truncated")
+        b = mv[pos: pos + n]
+        pos += n
+        return b
+
+    def get(depth):
+        if depth > _WIRE_MAX_DEPTH:
+            raise errors.InvalidArgument("RPC payload is nested too deeply")
+        tag = chr(take(1)[0])
+        if tag == "N":
+            return None
+        if tag in "TF":
+            return tag == "T"
+        if tag == "i":
+            (n,) = struct.unpack("<I", take(4))
+            return int.from_bytes(take(n), "little", signed=True)
+        if tag == "d":
+            return struct.unpack("<d", take(8))[0]
+        if tag == "s":
+            (n,) = struct.unpack("<Q", take(8))
+            return bytes(take(n)).decode()
+        if tag == "b":
+            (n,) = struct.unpack("<Q", take(8))
+            return bytes(take(n))
+        if tag == "X":
+            code, nd = struct.unpack("<BB", take(2))
+            if code not in _WIRE_DT_INV or nd > 16:
+                raise errors.InvalidArgument("RPC payload: bad tensor header")
+            shape = [struct.unpack("<Q", take(8))[0] for _ in range(nd)]
+            (n,) = struct.unpack("<Q", take(8))
+            dt = _WIRE_DT_INV[code]
+            numel = 1
+            for d in shape:
+                numel *= d
+            esz = torch.empty(0, dtype=dt).element_size()
+            if numel * esz != n:
+                raise errors.InvalidArgument("RPC payload: tensor size does not match its shape")
+            raw = bytearray(take(n))
+            if n == 0:
+                return torch.empty(shape, dtype=dt)
+            if dt == torch.bfloat16:
+                return torch.frombuffer(raw, dtype=torch.int16).view(torch.bfloat16).reshape(shape)
+            return torch.frombuffer(raw, dtype=dt).reshape(shape)
+        if tag in "lt":
+            (n,) = struct.unpack("<Q", take(8))
+            if n > len(mv):
+                raise errors.InvalidArgument("RPC payload: sequence longer than the message")
+            items = [get(depth + 1) for _ in range(n)]
+            return items if tag == "l" else tuple(items)
+        if tag == "m":
+            (n,) = struct.unpack("<Q", take(8))
+            if n > len(mv):
+                raise errors.InvalidArgument("RPC payload: mapping longer than the message")
+            d = {}
+            for _ in range(n):
+                k = get(depth + 1)
+                d[k] = get(depth + 1)
+            return d
+        raise errors.InvalidArgument(f"RPC payload: unknown tag {tag!r}")
+    obj = get(0)
+    if pos != len(mv):
+        raise errors.InvalidArgument("RPC payload has trailing bytes")
+    return obj
+
+
 class RpcAgent:
     """Named-handler RPC over a backend: ``serve()`` on the callee, ``rpc_sync`` / ``rpc_async`` on the caller. Arguments and results are
-    restricted to picklable plain data and tensors (tensors travel as raw bytes); messages are capped at 1 GiB."""
+    plain data and tensors in the tagged wire form of :func:`wire_dumps` (no pickle: a received message is parsed, never executed);
+    messages are capped at 1 GiB."""
 
     def __init__(self, backend: Backend, timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT):
         self.b, self.timeout = backend, timeout
@@ -235,7 +364,7 @@ class RpcAgent:
         self.handlers[name] = fn
 
     def _send_obj(self, obj, dst: int) -> None:
-        data = pickle.dumps(obj, protocol=4)
+        data = wire_dumps(obj)
         if len(data) > MAX_RPC_BYTES:
             raise errors.InvalidArgument("RPC message exceeds 1 GiB")
         self.b.send(struct.pack("<Q", len(data)), dst)
@@ -245,7 +374,7 @@ class RpcAgent:
         (n,) = struct.unpack("<Q", self.b.recv_timeout(8, src, timeout))
         if n > MAX_RPC_BYTES:
             raise errors.SizeMismatch("RPC message exceeds 1 GiB")
-        return pickle.loads(self.b.recv_timeout(n, src, timeout))
+        return wire_loads(self.b.recv_timeout(n, src, timeout))
 
     def rpc_sync(self, dst: int, name: str, *args, **kwargs):
         with self._lock:
@@ -267,8 +396,12 @@ class RpcAgent:
                 msg = self._recv_obj(src, idle_timeout)
             except errors.Timeout:
                 break
-            if msg[0] == "shutdown":
+            if not isinstance(msg, tuple) or not msg or msg[0] == "shutdown":
                 break
+            if len(msg) != 4 or msg[0] != "call" or not isinstance(msg[1], str):
+                self._send_obj(("err", "malformed call"), src)
+                n += 1
+                continue
             _, name, args, kwargs = msg
             try:
                 fn = self.handlers[name]

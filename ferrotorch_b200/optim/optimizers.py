@@ -224,7 +224,10 @@ class AdamW(Optimizer):
                 if g["maximize"]:
                     gr = -gr
                 master = st.get("master", None)
-                w = master if master is not None else p.view(-1)
+                # moments and gradient are walked in logical (row-major) order; an f32 parameter whose memory is not row-major (the
+                # convolution weights of a channels-last model) is updated through a row-major copy that is written back below
+                writeback = master is None and not p.is_contiguous()
+                w = master if master is not None else (p.detach().reshape(-1).clone() if writeback else p.view(-1))
                 if self._decoupled:
                     w.mul_(1 - g["lr"] * g["weight_decay"])
                 elif g["weight_decay"]:
@@ -237,8 +240,8 @@ class AdamW(Optimizer):
                     torch.maximum(st["max_exp_avg_sq"], v, out=st["max_exp_avg_sq"])
                     v = st["max_exp_avg_sq"]
                 w.addcdiv_(st["exp_avg"], (v.sqrt() / math.sqrt(c2)).add_(g["eps"]), value=-g["lr"] / c1)
-                if master is not None:
-                    p.copy_(master.view_as(p))
+                if master is not None or writeback:
+                    p.copy_(w.view_as(p))
         return loss
 
 

@@ -27,20 +27,41 @@ from .safetensors_io import _DT, _NAME, _raw_bytes
 # native state dict: one JSON line per tensor, separator, raw little-endian body
 # ----------------------------------------------------------------------------------------------------------------------
 _SEP = b"\n---\n"
+# dtype tags of the header: the reference writes "f32" / "f64" (state_dict.rs:45-53); the other element types follow the same spelling
+_TAG = {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16", torch.float16: "f16", torch.int64: "i64", torch.int32: "i32",
+        torch.int16: "i16", torch.int8: "i8", torch.uint8: "u8", torch.bool: "bool"}
+_FROM_TAG = {v: k for k, v in _TAG.items()}
+
+
+def _dtype_of(tag: str) -> torch.dtype:
+    t = _FROM_TAG.get(tag.lower())
+    if t is None:
+        t = _DT.get(tag.upper())
+    if t is None:
+        raise InvalidArgument(f"state dict: unknown dtype tag {tag!r}")
+    return t
 
 
 def dumps_state_dict(state: Dict[str, torch.Tensor]) -> bytes:
+    """Byte-for-byte the layout of the reference's ``save_state_dict`` (state_dict.rs:59-161): one compact JSON line per tensor with the keys
+    ``name, shape, dtype, byte_offset, byte_length`` in that order, names sorted, every line ended by a newline, then ``\n---\n`` and the raw
+    little-endian bodies in header order."""
     lines, body, off = [], [], 0
-    for k in state:
+    for k in sorted(state):
         t = state[k]
+        if t.dtype not in _TAG:
+            raise InvalidArgument(f"dtype {t.dtype} of {k!r} cannot be stored in a native state dict")
         raw = bytes(_raw_bytes(t))
-        lines.append(json.dumps({"name": k, "dtype": _NAME[t.dtype], "shape": list(t.shape), "offset": off, "nbytes": len(raw)}))
+        shape = "[" + ",".join(str(int(d)) for d in t.shape) + "]"
+        lines.append(f'{{"name":{json.dumps(k)},"shape":{shape},"dtype":"{_TAG[t.dtype]}","byte_offset":{off},"byte_length":{len(raw)}}}\n')
         body.append(raw)
         off += len(raw)
-    return "\n".join(lines).encode() + _SEP + b"".join(body)
+    return "".join(lines).encode() + _SEP + b"".join(body)
 
 
 def loads_state_dict(data: bytes) -> Dict[str, torch.Tensor]:
+    """Reads the reference's layout; files written by earlier versions of this package (keys ``offset`` / ``nbytes``, upper-case dtype
+    tags, no newline before the separator) load as well."""
     i = data.index(_SEP)
     head, body = data[:i].decode(), memoryview(data)[i + len(_SEP):]
     out = {}
@@ -48,8 +69,12 @@ def loads_state_dict(data: bytes) -> Dict[str, torch.Tensor]:
         if not line.strip():
             continue
         m = json.loads(line)
-        raw = bytes(body[m["offset"]: m["offset"] + m["nbytes"]])
-        dt = _DT[m["dtype"]]
+        off = m["byte_offset"] if "byte_offset" in m else m["offset"]
+        n = m["byte_length"] if "byte_length" in m else m["nbytes"]
+        if off < 0 or n < 0 or off + n > len(body):
+            raise InvalidArgument(f"state dict: tensor {m['name']!r} lies outside the body ({off}+{n} > {len(body)})")
+        raw = bytes(body[off: off + n])
+        dt = _dtype_of(m["dtype"])
         if dt == torch.bfloat16:
             t = torch.frombuffer(bytearray(raw), dtype=torch.int16).view(torch.bfloat16) if raw else torch.empty(0, dtype=dt)
         else:
@@ -69,19 +94,124 @@ def load_state_dict(path) -> Dict[str, torch.Tensor]:
 # ----------------------------------------------------------------------------------------------------------------------
 # training checkpoint (.ftc): [u64 len][metadata JSON][u64 len][optimizer JSON][u64 len][state-dict binary]
 # ----------------------------------------------------------------------------------------------------------------------
-def _opt_to_json(osd: dict) -> dict:
-    def enc(v):
-        if isinstance(v, torch.Tensor):
-            return {"__tensor__": v.detach().cpu().double().reshape(-1).tolist(), "shape": list(v.shape), "dtype": _NAME.get(v.dtype, "F32")}
-        if isinstance(v, dict):
-            return {str(k): enc(x) for k, x in v.items()}
-        if isinstance(v, (list, tuple)):
-            return [enc(x) for x in v]
-        return v
-    return enc(osd)
+# The optimizer section has the reference's shape (checkpoint.rs:198-229): {"<param key>": {"<state name>": [numbers...]}}, keys sorted,
+# numbers only. A torch-style optimizer state dict is flattened into that shape; what the flat lists cannot carry (tensor shapes and
+# dtypes, value kinds, parameter groups) goes into reserved entries whose names start with "__" and that again hold number lists only, so
+# a reader that knows only the reference's shape still parses the whole section.
+_KIND_FLOAT, _KIND_INT, _KIND_BOOL, _KIND_NONE, _KIND_TUPLE, _KIND_TENSOR = 0, 1, 2, 3, 4, 5
+_DT_CODE = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2, torch.float16: 3, torch.int64: 4, torch.int32: 5, torch.int16: 6,
+            torch.int8: 7, torch.uint8: 8, torch.bool: 9}
+_CODE_DT = {v: k for k, v in _DT_CODE.items()}
 
 
-def _opt_from_json(j):
+def _num(v) -> str:
+    v = float(v)
+    if v != v:
+        return "NaN"
+    if v in (float("inf"), float("-inf")):
+        return "inf" if v > 0 else "-inf"
+    return repr(int(v)) if v == int(v) and abs(v) < 1e15 else repr(v)
+
+
+def _flat_entry(v):
+    """(numbers, kind, shape, dtype code) of one optimizer-state or parameter-group value, or None when it cannot be written as numbers."""
+    if isinstance(v, torch.Tensor):
+        return v.detach().cpu().double().reshape(-1).tolist(), _KIND_TENSOR, list(v.shape), _DT_CODE.get(v.dtype, 0)
+    if isinstance(v, bool):
+        return [int(v)], _KIND_BOOL, None, None
+    if isinstance(v, int):
+        return [v], _KIND_INT, None, None
+    if isinstance(v, float):
+        return [v], _KIND_FLOAT, None, None
+    if v is None:
+        return [], _KIND_NONE, None, None
+    if isinstance(v, (tuple, list)) and all(isinstance(x, (int, float)) and not isinstance(x, bool) for x in v):
+        return list(v), _KIND_TUPLE, None, None
+    return None
+
+
+def _opt_to_json(osd: dict) -> str:
+    if not osd:
+        return "{}"
+    if "state" not in osd and "param_groups" not in osd:          # already in the reference's shape: {key: {name: [numbers]}}
+        tables = {str(k): {str(n): list(map(float, vals)) for n, vals in inner.items()} for k, inner in osd.items()}
+    else:
+        tables: Dict[str, Dict[str, list]] = {}
+        kinds, shapes, dtypes = {}, {}, {}
+
+        def put(table: str, name: str, v) -> None:
+            e = _flat_entry(v)
+            if e is None:
+                return                                              # not expressible as numbers (a callable, a string): left to the live optimizer
+            vals, kind, shape, code = e
+            tables.setdefault(table, {})[name] = vals
+            kinds[f"{table}/{name}"] = [kind]
+            if shape is not None:
+                shapes[f"{table}/{name}"] = shape
+                dtypes[f"{table}/{name}"] = [code]
+        for pid, st in osd.get("state", {}).items():
+            for name, v in st.items():
+                put(str(pid), str(name), v)
+        for gi, g in enumerate(osd.get("param_groups", [])):
+            for name, v in g.items():
+                put(f"__group_{gi}__", str(name), v)
+        tables["__kinds__"], tables["__shapes__"], tables["__dtypes__"] = kinds, shapes, dtypes
+    parts = []
+    for key in sorted(tables):
+        inner = ",".join(f"{json.dumps(n)}:[{','.join(_num(x) for x in tables[key][n])}]" for n in sorted(tables[key]))
+        parts.append(f"{json.dumps(key)}:{{{inner}}}")
+    return "{" + ",".join(parts) + "}"
+
+
+def _opt_from_json(text) -> dict:
+    j = json.loads(text) if isinstance(text, (str, bytes)) else text
+    if not j:
+        return {}
+    if "__kinds__" not in j:
+        if any(isinstance(v, dict) and "__tensor__" in v for v in _walk(j)):      # section written by an earlier version of this package
+            return _legacy_opt_from_json(j)
+        return j                                                                  # plain reference shape: handed back as it is
+    kinds, shapes, dtypes = j["__kinds__"], j.get("__shapes__", {}), j.get("__dtypes__", {})
+
+    def get(table: str, name: str, vals):
+        kind = int(kinds.get(f"{table}/{name}", [_KIND_FLOAT])[0])
+        if kind == _KIND_TENSOR:
+            dt = _CODE_DT.get(int(dtypes.get(f"{table}/{name}", [0])[0]), torch.float32)
+            return torch.tensor(vals, dtype=torch.float64).reshape([int(d) for d in shapes.get(f"{table}/{name}", [len(vals)])]).to(dt)
+        if kind == _KIND_BOOL:
+            return bool(vals[0])
+        if kind == _KIND_INT:
+            return int(vals[0])
+        if kind == _KIND_NONE:
+            return None
+        if kind == _KIND_TUPLE:
+            return tuple(int(x) if float(x).is_integer() and name == "params" else x for x in vals)
+        return float(vals[0])
+    state, groups = {}, {}
+    for table, inner in j.items():
+        if table in ("__kinds__", "__shapes__", "__dtypes__"):
+            continue
+        if table.startswith("__group_") and table.endswith("__"):
+            g = {name: get(table, name, vals) for name, vals in inner.items()}
+            if "params" in g:
+                g["params"] = [int(x) for x in g["params"]]
+            groups[int(table[len("__group_"):-2])] = g
+        else:
+            state[int(table) if table.lstrip("-").isdigit() else table] = {name: get(table, name, vals) for name, vals in inner.items()}
+    return {"state": state, "param_groups": [groups[i] for i in sorted(groups)]}
+
+
+def _walk(j):
+    if isinstance(j, dict):
+        yield j
+        for v in j.values():
+            yield from _walk(v)
+    elif isinstance(j, list):
+        for v in j:
+            yield from _walk(v)
+
+
+def _legacy_opt_from_json(j):
     def dec(v):
         if isinstance(v, dict) and "__tensor__" in v:
             return torch.tensor(v["__tensor__"], dtype=torch.float64).reshape(v["shape"]).to(_DT.get(v["dtype"], torch.float32))
@@ -102,12 +232,14 @@ class TrainingCheckpoint:
     extra: dict = field(default_factory=dict)
 
     def save(self, path) -> None:
-        meta = json.dumps({"epoch": self.epoch, "step": self.step, "extra": self.extra, "format": "ftc", "version": 1}).encode()
-        opt = json.dumps(_opt_to_json(self.optimizer_state)).encode()
+        # section 1 is the reference's '{"epoch":E,"step":S}' (checkpoint.rs:86-90); user extras follow under one optional key, which the
+        # reference's reader (it looks the two keys up by name, checkpoint.rs:177-196) skips
+        meta = f'{{"epoch":{int(self.epoch)},"step":{int(self.step)}' + (f',"extra":{json.dumps(self.extra)}' if self.extra else "") + "}"
+        opt = _opt_to_json(self.optimizer_state)
         sd = dumps_state_dict({k: v.detach().cpu() for k, v in self.model_state.items()})
         tmp = str(path) + ".tmp"
         with open(tmp, "wb") as f:
-            for sec in (meta, opt, sd):
+            for sec in (meta.encode(), opt.encode(), sd):
                 f.write(struct.pack("<Q", len(sec)))
                 f.write(sec)
         import os
@@ -118,11 +250,15 @@ class TrainingCheckpoint:
         data = Path(path).read_bytes()
         secs, off = [], 0
         for _ in range(3):
+            if off + 8 > len(data):
+                raise InvalidArgument("checkpoint: truncated section header")
             (n,) = struct.unpack_from("<Q", data, off)
+            if off + 8 + n > len(data):
+                raise InvalidArgument("checkpoint: section runs past the end of the file")
             secs.append(data[off + 8: off + 8 + n])
             off += 8 + n
         meta = json.loads(secs[0])
-        return TrainingCheckpoint(loads_state_dict(secs[2]), _opt_from_json(json.loads(secs[1])), meta["epoch"], meta["step"], meta.get("extra", {}))
+        return TrainingCheckpoint(loads_state_dict(secs[2]), _opt_from_json(secs[1].decode()), meta["epoch"], meta["step"], meta.get("extra", {}))
 
 
 def save_checkpoint(path, model: torch.nn.Module, optimizer: Optional[torch.optim.Optimizer] = None, epoch: int = 0, step: int = 0, **extra) -> None:

@@ -147,6 +147,32 @@ def case_timeout():
     # the context is still usable and the fabric still works after the timeout
     comm.barrier()
     comm.check()
+    # the same with a many-CTA collective: every CTA of rank 0's all-reduce runs out of time at its opening rendezvous; the CTA counter and the
+    # sequence numbers must come out of it consistent, so that the next all-reduce (all ranks present) elects its last CTA and succeeds
+    from ferrotorch_b200.parallel.symm import SymmetricBuffer
+    n = 1 << 22
+    buf = SymmetricBuffer(n, torch.float32, dev)
+    buf.tensor.fill_(float(rank + 1))
+    torch.cuda.synchronize(); dist.barrier()
+    SymmComm.set_timeout(0.5)
+    if rank == 0:
+        comm.all_reduce_(buf, n, use_nvls=False)
+        try:
+            comm.check()
+            raise AssertionError("expected a timeout")
+        except Timeout:
+            pass
+        assert float(buf.tensor[0]) == 1.0 and float(buf.tensor[-1]) == 1.0       # nothing was reduced
+    else:
+        comm.seq += 1
+        time.sleep(1.5)
+    torch.cuda.synchronize()
+    dist.barrier()
+    SymmComm.set_timeout(2.0)
+    comm.all_reduce_(buf, n, use_nvls=False)
+    comm.check()
+    want = float(sum(range(1, world + 1)))
+    assert float(buf.tensor[0]) == want and float(buf.tensor[n // 2 + 3]) == want and float(buf.tensor[-1]) == want
     x = torch.ones(4, device=dev)
     dist.all_reduce(x)
     assert x[0].item() == world
