@@ -37,6 +37,9 @@ def _parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then says so and is not a headline number)")
     ap.add_argument("--comm", default=None, choices=[None, "nccl", "fused"])
+    ap.add_argument("--strategy", default="full_shard", choices=["full_shard", "shard_grad_op"],
+                    help="full_shard (ZeRO-3, the configuration the headline names): bf16 parameters sharded and gathered per unit for forward "
+                         "and backward; shard_grad_op (ZeRO-2): a replicated bf16 copy stays resident and is refreshed by the update kernel")
     ap.add_argument("--breakdown", action="store_true",
                     help="after the timed runs, time every kernel class of one step with CUDA events (optimizer serialised on the compute "
                          "stream so that the classes add up to the step) and add the table to the JSON line")
@@ -174,14 +177,15 @@ def main():
     import ferrotorch_b200 as ft
     from ferrotorch_b200 import _lib
     from ferrotorch_b200.models import LlamaConfig, LlamaForCausalLM
-    from ferrotorch_b200.parallel import FSDP, AdamWConfig
+    from ferrotorch_b200.parallel import FSDP, AdamWConfig, ShardingStrategy
 
     cfg = LlamaConfig.llama3_8b()
     if args.layers is not None:
         cfg.num_hidden_layers = args.layers
     B, S = args.micro_batch, args.seq
     model = LlamaForCausalLM(cfg, device=dev, world=world, rank=rank, seed=0)
-    engine = FSDP(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1), comm=args.comm)
+    engine = FSDP(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1), comm=args.comm,
+                  strategy=ShardingStrategy(args.strategy))
     torch.cuda.synchronize()
 
     # synthetic data: a few distinct pinned host batches per rank, cycled
@@ -204,8 +208,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    first_loss = None
     for i in range(args.warmup):
-        step_e2e(i)
+        l = step_e2e(i)
+        first_loss = l if first_loss is None else first_loss
     engine.synchronize()
     barrier()
 
@@ -247,6 +253,27 @@ def main():
     value = tokens_per_step * K / (ms_dev / 1e3)
     e2e_value = tokens_per_step * K / (ms_e2e / 1e3)
     status = _lib.read_status()
+    import math
+    finite = all(v is None or math.isfinite(float(v)) for v in (first_loss, last_loss, last_e2e))
+    if world > 1:
+        f = torch.tensor([1.0 if finite else 0.0], device=dev)
+        dist.all_reduce(f, op=dist.ReduceOp.MIN)
+        finite = bool(f.item() > 0.5)
+    if not finite or status != 0:
+        if rank == 0:
+            print(json.dumps({"error": "training diverged or a device-side wait timed out: no headline number", "first_loss": first_loss,
+                              "last_loss": float(last_loss) if last_loss is not None else None, "kernel_status": status, "impl": "ours"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 1
+    if world == 1:
+        sharding = "single GPU: parameters, gradients and optimizer state whole on the one rank (nothing to shard or gather)"
+    elif args.strategy == "full_shard":
+        sharding = ("full_shard (ZeRO-3): bf16 parameters, f32 master weights, AdamW moments and reduced gradients sharded over all ranks; every unit is "
+                    "gathered into a slot for its forward and again for its backward pass")
+    else:
+        sharding = ("shard_grad_op (ZeRO-2): f32 master weights, AdamW moments and reduced gradients sharded; a replicated bf16 parameter copy stays "
+                    "resident and is refreshed by the all-gather that is part of the update kernel")
     if rank == 0:
         full = args.layers is None and S == 4096 and B == 1
         out = {
@@ -255,14 +282,14 @@ def main():
             "ms_per_step": round(ms_dev / K, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": "llama-3-8b" if args.layers is None else f"llama-3-8b-{args.layers}layers", "global_batch": B * world,
-                       "seq_len": S, "parallelism": f"fsdp{world}-full-shard", "optimizer": "AdamW(lr=3e-4,betas=0.9/0.95), f32 master+moments",
-                       "sharding": "f32 master weights, AdamW moments and reduced gradients sharded over all ranks; gathered bf16 copy cached between steps",
+                       "seq_len": S, "parallelism": f"fsdp{world}-{args.strategy.replace('_', '-')}", "strategy": args.strategy, "optimizer": "AdamW(lr=3e-4,betas=0.9/0.95), f32 master+moments",
+                       "sharding": sharding,
                        "l2": "inputs_larger_than_L2 (16 GB of weights streamed per step)", "comm": engine.comm if world > 1 else "none",
                        "attention_backend": ft.ops.attention.backend()},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "ms_per_step": round(ms_e2e / K, 3),
                     "h2d_bytes_per_step": int(B * (S + 1) * 8), "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
-            "gpu_launches": int(launches), "last_loss": float(last_loss) if last_loss is not None else None,
+            "gpu_launches": int(launches), "first_loss": first_loss, "last_loss": float(last_loss) if last_loss is not None else None,
             "kernel_status": status, "impl": "ours",
             "mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
         }

@@ -304,9 +304,12 @@ __global__ void __launch_bounds__(512) broadcast_kernel(PeerPtrs bufs, T* __rest
 // ---------------------------------------------------------------------------------------------------------
 struct AdamWArgsC { float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2; };
 
+// local_out != null: the fully sharded form. The refreshed bf16 slice is written to this rank's own shard only (local_out[i]); nothing is pushed,
+// the parameters are gathered again when the next forward pass needs them (fsdp_gather.cu).
 __global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, CommSync s, float* __restrict__ master,
                                                                float* __restrict__ m, float* __restrict__ v, size_t chunk, AdamWArgsC a,
-                                                               const float* __restrict__ grad_scale_ptr, uint32_t* status) {
+                                                               const float* __restrict__ grad_scale_ptr, __nv_bfloat16* __restrict__ local_out,
+                                                               uint32_t* status) {
   if (!comm_begin(s, status)) { comm_abort(s); return; }
   const float inv_world = (grad_scale_ptr ? *grad_scale_ptr : 1.f) / (float)s.world;
   const float decay = 1.f - a.lr * a.weight_decay, step = a.lr / a.bias_c1, inv_c2 = rsqrtf(a.bias_c2);
@@ -343,9 +346,13 @@ __global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, P
     mm[0] = make_float4(m1[0], m1[1], m1[2], m1[3]); mm[1] = make_float4(m1[4], m1[5], m1[6], m1[7]);
     vv[0] = make_float4(v1[0], v1[1], v1[2], v1[3]); vv[1] = make_float4(v1[4], v1[5], v1[6], v1[7]);
     const bf16x8 out = float_to_bf16x8(p);
+    if (local_out != nullptr) {
+      *reinterpret_cast<bf16x8*>(local_out + i * 8) = out;
+    } else {
 #pragma unroll
-    for (int q = 0; q < MAX_RANKS; q++)
-      if (q < s.world) *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(params.p[q]) + base + i * 8) = out;
+      for (int q = 0; q < MAX_RANKS; q++)
+        if (q < s.world) *reinterpret_cast<bf16x8*>(reinterpret_cast<__nv_bfloat16*>(params.p[q]) + base + i * 8) = out;
+    }
   }
   comm_end(s, status);
 }
@@ -623,6 +630,23 @@ FT_EXPORT int ft_fsdp_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptr
   for (int i = 0; i < MAX_RANKS; i++) { g.p[i] = i < world ? grad_ptrs[i] : nullptr; p.p[i] = i < world ? param_ptrs[i] : nullptr; }
   AdamWArgsC a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step)};
   const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 96);
-  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, ft_status_ptr());
+  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, nullptr, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// The same without the all-gather (fully sharded parameters): the reduced gradient slice updates master / m / v and the bf16 result goes to
+// `shard_out` [chunk], this rank's own shard of the unit. grad_ptrs as above.
+FT_EXPORT int ft_fsdp_rs_adamw(void* const* grad_ptrs, void* shard_out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                               float* master, float* m, float* v, int64_t chunk, float lr, float beta1, float beta2, float eps, float weight_decay,
+                               int step, const float* grad_scale_ptr, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 8);
+  if (r) return r;
+  if (chunk <= 0 || chunk % 8 || step < 1 || shard_out == nullptr) return FT_ERR_ARG;
+  PeerPtrs g, p;
+  for (int i = 0; i < MAX_RANKS; i++) { g.p[i] = i < world ? grad_ptrs[i] : nullptr; p.p[i] = nullptr; }
+  AdamWArgsC a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step)};
+  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 96);
+  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, (__nv_bfloat16*)shard_out, ft_status_ptr());
   return (int)cudaGetLastError();
 }

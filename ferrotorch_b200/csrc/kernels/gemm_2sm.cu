@@ -118,7 +118,8 @@ FT_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0)
 template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
-                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int k_splits, uint32_t* status, const Gemm2Epi epi) {
+                const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int k_splits, uint32_t* status, const Gemm2Epi epi, const Gemm2Gate gate,
+                long long ldb_bytes) {
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared window starts at the same offset in both CTAs of the pair, so the rounded pointers (and with them every barrier and
   // operand offset) are the same in both: the MMA descriptors built by the leader address the peer's tiles at the same offsets
@@ -164,6 +165,7 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (lane == 0) {
       uint32_t s = 0, phase = 0;
       bool ok = true;
+      long long ready_lo = 0, ready_hi = 0;               // pieces [ready_lo, ready_hi) of the gated operand are known to have arrived
       for (int item = pair; item < num_items && ok; item += num_pairs) {
         int m0, n0;
         tile_coords(item / k_splits, tiles_m, tiles_n, m0, n0);
@@ -171,6 +173,24 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int kb0 = split * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
         const int am0 = m0 + (int)cta_rank * BM;          // this CTA's rows of A (and of D)
         const int bn0 = n0 + (int)cta_rank * BNH;         // this CTA's half of the B tile
+        if (gate.counters != nullptr && (gate.mode == 2 || bn0 < N)) {
+          // the weights of this tile may still be on their way from the peers: wait for the pieces that hold them
+          long long b0, b1;
+          if (gate.mode == 1) { b0 = gate.b_byte_off + (long long)bn0 * ldb_bytes; b1 = gate.b_byte_off + (long long)min(bn0 + BNH, N) * ldb_bytes; }
+          else { b0 = gate.b_byte_off; b1 = gate.b_byte_off + gate.b_bytes; }
+          const long long lo = b0 / gate.piece_bytes, hi = (b1 - 1) / gate.piece_bytes + 1;
+          if (lo < ready_lo || hi > ready_hi) {
+            for (long long p = lo; p < hi && ok; p++) {
+              if (p >= ready_lo && p < ready_hi) continue;
+              if (!wait_flag_ge(gate.counters + p, gate.expected, 2000000000ull)) { ft_set_status(status, FT_K_GEMM2, 5, (uint32_t)p); ok = false; }
+            }
+            if (!ok) break;
+            // the pieces were written by peers with ordinary stores; the loads below go through the async proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            if (lo <= ready_hi && hi >= ready_lo && ready_hi > ready_lo) { ready_lo = min(ready_lo, lo); ready_hi = max(ready_hi, hi); }
+            else { ready_lo = lo; ready_hi = hi; }
+          }
+        }
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait_deadline(&empty_bar[s], phase ^ 1)) { ft_set_status(status, FT_K_GEMM2, 1, s); ok = false; break; }
           if (leader) mbar_expect_tx(&full_bar[s], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
@@ -345,7 +365,7 @@ int g_max_pairs[64] = {0};        // 0 = not queried, -1 = pairs cannot be sched
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, const void* bias, int M, int N, int K, int k_splits, int dev,
-           cudaStream_t stream, const Gemm2Epi& epi) {
+           cudaStream_t stream, const Gemm2Epi& epi, const Gemm2Gate& gate, long long ldb_bytes) {
   auto kern = ft_gemm2_kernel<A_MN, B_MN, OUT_F32>;
   static bool configured = false;
   if (!configured) {
@@ -377,7 +397,7 @@ int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD, 
   if (items < pairs) pairs = items;
   cfg.gridDim = dim3(2 * pairs);
   cfg.numAttrs = ft_pdl_enabled() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, k_splits, ft_status_ptr(), epi);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tA, tB, tD, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, k_splits, ft_status_ptr(), epi, gate, ldb_bytes);
 }
 
 }  // namespace
@@ -403,8 +423,14 @@ FT_EXPORT int ft_gemm_set_2sm(int on) {
 }
 
 int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn,
-                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi) {
+                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi, const Gemm2Gate& gate_in) {
   if (epi.act < 0 || epi.act > 4) return FT_ERR_ARG;
+  Gemm2Gate gate = gate_in;
+  if (gate.counters != nullptr) {
+    if (gate.piece_bytes < 16 || gate.b_byte_off < 0 || (gate.mode != 1 && gate.mode != 2)) return FT_ERR_ARG;
+    if (gate.mode == 1 && b_mn) gate.mode = 2;                       // rows of an MN-major operand are not contiguous per tile
+    if (gate.mode == 2 && gate.b_bytes <= 0) return FT_ERR_ARG;
+  }
   const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
@@ -426,7 +452,7 @@ int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int
                       out_f32 ? 32 : 64, 32, 1, CU_TENSOR_MAP_SWIZZLE_128B);
   if (r) return r;
 #define FT_GEMM2_CASE(AM, BMN, OF) \
-  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, dev, stream, epi);
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF) return launch<AM, BMN, OF>(tA, tB, tD, bias, M, N, K, k_splits, dev, stream, epi, gate, (long long)ldb * 2);
   FT_GEMM2_CASE(0, 0, 0) FT_GEMM2_CASE(0, 1, 0) FT_GEMM2_CASE(1, 0, 0) FT_GEMM2_CASE(1, 1, 0)
   FT_GEMM2_CASE(0, 0, 1) FT_GEMM2_CASE(0, 1, 1) FT_GEMM2_CASE(1, 0, 1) FT_GEMM2_CASE(1, 1, 1)
 #undef FT_GEMM2_CASE

@@ -10,10 +10,22 @@ struct Gemm2Epi {
   int in_f16;              // operands are fp16 instead of bf16
 };
 
+// Arrival gate of the B operand: B lies inside a gather slot that peers fill piece by piece (fsdp_gather.cu). The TMA producer waits (bounded) until
+// the arrival counters of the pieces it is about to read have reached `expected`. counters == null: no gate.
+struct Gemm2Gate {
+  const uint32_t* counters;   // arrival counters of the slot (this GPU's memory, written by the peers)
+  uint32_t expected;
+  int mode;                   // 1: per N tile (B is [N, K], K contiguous, rows ldb apart: a tile's rows are one byte range);
+                              // 2: the whole operand before the first load (any layout)
+  long long b_byte_off;       // offset of B's first element from the start of the slot
+  long long b_bytes;          // extent of the operand in the slot (mode 2)
+  long long piece_bytes;
+};
+
 // True when the pair kernel should take the problem: enabled, M large enough for 256-row tiles, the device can co-schedule CTA pairs.
 bool ft_gemm2_wanted(int M, int N, int K, int k_splits);
 
 // Same contract as the one-SM launcher: D[splits][M][N] = A (x) B restricted to each K slice (+ bias, activation, residual when k_splits == 1).
 // Returns FT_OK / FT_ERR_* / a CUDA error code.
 int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn,
-                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi);
+                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi, const Gemm2Gate& gate = Gemm2Gate{nullptr, 0, 0, 0, 0, 1});

@@ -574,6 +574,31 @@ FT_EXPORT int ft_gemm_ex(const void* A, const void* B, void* D, const void* bias
   return gemm_impl(A, B, D, bias, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream, EpiArgs{act, residual, ldr, in_f16});
 }
 
+extern "C" int ft_fsdp_gate(const void* arrive, int piece_lo, int piece_hi, uint32_t expected, cudaStream_t st);
+
+// GEMM whose B operand (a weight) lies in a gather slot that peers are still filling (parallel/fsdp.py, fsdp_gather.cu): `counters` are the
+// slot's arrival counters (this GPU's memory), `expected` the number of the current gather, `slot_base` the first byte of the slot and
+// `piece_bytes` the arrival granularity. The CTA-pair kernel waits per output-column tile inside its TMA producer, so the product starts on
+// the weights that have landed; problems it does not take wait for the whole operand with a gate kernel first. Output bf16 or f32, no epilogue
+// extras.
+FT_EXPORT int ft_gemm_gated(const void* A, const void* B, void* D, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn, int b_mn,
+                            int out_f32, const void* counters, uint32_t expected, const void* slot_base, int64_t piece_bytes, cudaStream_t stream) {
+  if (counters == nullptr || slot_base == nullptr || piece_bytes < 16) return FT_ERR_ARG;
+  const long long off = (const char*)B - (const char*)slot_base;
+  if (off < 0 || M <= 0 || N <= 0 || K <= 0) return FT_ERR_ARG;
+  const long long rows = b_mn ? K : N, row_len = b_mn ? N : K;
+  const long long bytes = ((rows - 1) * (long long)ldb + row_len) * 2;
+  if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
+  if (ft_gemm2_wanted(M, N, K, 1)) {
+    const Gemm2Gate gate{(const uint32_t*)counters, expected, b_mn ? 2 : 1, off, bytes, (long long)piece_bytes};
+    const int r2 = ft_gemm2_launch(A, B, D, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream, Gemm2Epi{0, nullptr, 0, 0}, gate);
+    if (r2 != FT_ERR_DRIVER) return r2;
+  }
+  const int r = ft_fsdp_gate(counters, (int)(off / piece_bytes), (int)((off + bytes - 1) / piece_bytes) + 1, expected, stream);
+  if (r) return r;
+  return gemm_impl(A, B, D, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream);
+}
+
 // Split-K form: partial[s][M][N] (f32, contiguous planes of M*ldd elements) = A (x) B restricted to the s-th slice of K.
 // The caller (or a fused consumer kernel) sums the planes. Used when M*N is small and K large, e.g. decoding, where the
 // operand stream has to be spread over all SMs.

@@ -114,8 +114,10 @@ class LlamaConfig:
 def layer_shapes(cfg: LlamaConfig):
     d, F, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
     nqkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * D
-    return [("wqkv", (nqkv, d)), ("wo", (d, cfg.num_attention_heads * D)), ("wgu", (2 * F, d)), ("wd", (d, F)),
-            ("norm1", (d,)), ("norm2", (d,))]
+    # in the order the forward pass reads them: a fully sharded engine gathers a unit front to back, so the consumers can start on the first
+    # pieces while the rest is still in flight (the backward pass asks for the pieces in reverse order)
+    return [("norm1", (d,)), ("norm2", (d,)), ("wqkv", (nqkv, d)), ("wo", (d, cfg.num_attention_heads * D)), ("wgu", (2 * F, d)),
+            ("wd", (d, F))]
 
 
 # ---------------------------------------------------------------------------
@@ -124,18 +126,22 @@ def layer_shapes(cfg: LlamaConfig):
 def _layer_forward(x, P, cfg: LlamaConfig, B: int, S: int, rope):
     Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     cos, sin = rope
+    gate = getattr(P, "gate", None)          # fully sharded engine: the weights may still be arriving (see parallel/gather.py)
+    if gate is not None:
+        gate.wait(P["norm1"])
+        gate.wait(P["norm2"])
     h, rstd1, _ = ops.rmsnorm_fwd(x, P["norm1"], cfg.rms_norm_eps)
-    qkv = ops.gemm(h, P["wqkv"])
+    qkv = ops.gemm(h, P["wqkv"], gate=gate)
     del h
     ops.rope_inplace(qkv, cos, sin, S, 0, Hq + Hkv, D)       # q heads and k heads are adjacent in the packed row
     attn, lse = ops.flash_fwd(qkv, B, S, Hq, Hkv, D, True)
-    o = ops.gemm(attn, P["wo"])
+    o = ops.gemm(attn, P["wo"], gate=gate)
     h2, rstd2, x1 = ops.rmsnorm_fwd(o, P["norm2"], cfg.rms_norm_eps, residual=x)   # x1 = x + o
     del o
-    gu = ops.gemm(h2, P["wgu"])
+    gu = ops.gemm(h2, P["wgu"], gate=gate)
     del h2
     a = ops.swiglu_fwd(gu)
-    dn = ops.gemm(a, P["wd"])
+    dn = ops.gemm(a, P["wd"], gate=gate)
     del a
     out = ops.add_(dn, x1)                                    # out = x1 + dn, written over dn
     return out, (x, rstd1, qkv, attn, lse, x1, rstd2, gu)
@@ -145,30 +151,34 @@ def _layer_backward(dout, saved, P, G, cfg: LlamaConfig, B: int, S: int, rope):
     Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     cos, sin = rope
     x, rstd1, qkv, attn, lse, x1, rstd2, gu = saved
+    gate = getattr(P, "gate", None)
+    if gate is not None:
+        gate.wait(P["norm1"])
+        gate.wait(P["norm2"])
     # ---- MLP ----
     a = ops.swiglu_fwd(gu)
     ops.gemm(dout, a, a_mn=True, b_mn=True, out=G["wd"])                 # dWd = dout^T a
     del a
-    da = ops.gemm(dout, P["wd"], b_mn=True)                               # [T, F]
+    da = ops.gemm(dout, P["wd"], b_mn=True, gate=gate)                    # [T, F]
     dgu = ops.swiglu_bwd(gu, da, inplace=True)
     del da
     h2, _, _ = ops.rmsnorm_fwd(x1, P["norm2"], cfg.rms_norm_eps)
     ops.gemm(dgu, h2, a_mn=True, b_mn=True, out=G["wgu"])
     del h2
-    dh2 = ops.gemm(dgu, P["wgu"], b_mn=True)
+    dh2 = ops.gemm(dgu, P["wgu"], b_mn=True, gate=gate)
     del dgu
     dx1, _ = ops.rmsnorm_bwd(x1, P["norm2"], dh2, rstd2, dres=dout, dw_out=G["norm2"])
     del dh2
     # ---- attention ----
     ops.gemm(dx1, attn, a_mn=True, b_mn=True, out=G["wo"])
-    dattn = ops.gemm(dx1, P["wo"], b_mn=True)
+    dattn = ops.gemm(dx1, P["wo"], b_mn=True, gate=gate)
     dqkv = ops.flash_bwd(qkv, attn, lse, dattn, B, S, Hq, Hkv, D, True)
     del dattn
     ops.rope_inplace(dqkv, cos, sin, S, 0, Hq + Hkv, D, inverse=True)
     h, _, _ = ops.rmsnorm_fwd(x, P["norm1"], cfg.rms_norm_eps)
     ops.gemm(dqkv, h, a_mn=True, b_mn=True, out=G["wqkv"])
     del h
-    dh = ops.gemm(dqkv, P["wqkv"], b_mn=True)
+    dh = ops.gemm(dqkv, P["wqkv"], b_mn=True, gate=gate)
     del dqkv
     dx, _ = ops.rmsnorm_bwd(x, P["norm1"], dh, rstd1, dres=dx1, dw_out=G["norm1"])
     return dx
@@ -203,7 +213,7 @@ class _DecoderLayerFn(torch.autograd.Function):
         d2 = dout.reshape(B * S, cfg.hidden_size)
         if not d2.is_contiguous():
             d2 = d2.contiguous()
-        P = owner.acquire_params()
+        P = owner.acquire_params(backward=True)
         saved = ctx.saved
         if owner.recompute:
             _, saved = _layer_forward(saved[0], P, cfg, B, S, rope)
@@ -224,9 +234,11 @@ class _LMHeadLossFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, h, w, owner, targets, ignore_index, chunk_rows):
+    def forward(ctx, h, flat, owner, targets, ignore_index, chunk_rows):
         T, d = h.shape
         t = targets.reshape(-1)
+        P = owner.acquire_params()
+        w, gate = P["weight"], getattr(P, "gate", None)
         G = owner.acquire_grads()
         gw = G["weight"]
         n_valid = T if ignore_index is None else None
@@ -238,17 +250,18 @@ class _LMHeadLossFn(torch.autograd.Function):
         first = True
         for r0 in range(0, T, chunk_rows):
             r1 = min(T, r0 + chunk_rows)
-            logits = ops.gemm(h[r0:r1], w)
+            logits = ops.gemm(h[r0:r1], w, gate=gate)
             loss_c, dl, cnt = ops.cross_entropy_fwd_bwd(logits, t[r0:r1], ignore_index=-100 if ignore_index is None else ignore_index,
                                                         grad_scale=scale, inplace_grad=True)
             total += loss_c * cnt
-            ops.gemm(dl, w, b_mn=True, out=dh[r0:r1])
+            ops.gemm(dl, w, b_mn=True, out=dh[r0:r1], gate=gate)
             if first:
                 ops.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=gw)
                 first = False
             else:
                 gw += ops.gemm(dl, h[r0:r1], a_mn=True, b_mn=True)
             del logits, dl
+        owner.release_params(after_forward=False)
         ctx.save_for_backward(dh)
         ctx.owner = owner
         return total * scale
@@ -272,7 +285,7 @@ class _ParamOwner:
         self.recompute = False
         self.on_grads_ready: Optional[Callable] = None
 
-    def acquire_params(self) -> Dict[str, torch.Tensor]:
+    def acquire_params(self, backward: bool = False) -> Dict[str, torch.Tensor]:
         return self.unit.views()
 
     def release_params(self, after_forward: bool) -> None:
@@ -374,11 +387,10 @@ class LlamaModel(torch.nn.Module):
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         B, S = ids.shape
         self.ensure_rope(S)
-        table = self.embed_unit.view("weight", self.embed_flat)
         if ids.is_cuda:
             x = _EmbedFn.apply(ids, self.embed_flat, self.embed_owner)
         else:
-            x = table[ids]
+            x = self.embed_unit.view("weight", self.embed_flat)[ids]
         for l in self.layers:
             x = l(x)
         if x.is_cuda:
@@ -392,6 +404,8 @@ class _EmbedFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, flat, owner):
         P = owner.acquire_params()
+        if getattr(P, "gate", None) is not None:
+            P.gate.wait(P["weight"])
         out = ops.embedding_fwd(ids, P["weight"])
         owner.release_params(after_forward=True)
         ctx.save_for_backward(ids)
@@ -417,7 +431,10 @@ class _FinalNormFn(torch.autograd.Function):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         P = owner.acquire_params()
+        if getattr(P, "gate", None) is not None:
+            P.gate.wait(P["weight"])
         y, rstd, _ = ops.rmsnorm_fwd(x2, P["weight"], owner.cfg.rms_norm_eps)
+        owner.release_params(after_forward=True)
         ctx.save_for_backward(x2, rstd)
         ctx.owner, ctx.shp = owner, shp
         return y.view(shp)
@@ -426,8 +443,11 @@ class _FinalNormFn(torch.autograd.Function):
     def backward(ctx, dy):
         x2, rstd = ctx.saved_tensors
         owner = ctx.owner
-        P, G = owner.acquire_params(), owner.acquire_grads()
+        P, G = owner.acquire_params(backward=True), owner.acquire_grads()
+        if getattr(P, "gate", None) is not None:
+            P.gate.wait(P["weight"])
         dx, _ = ops.rmsnorm_bwd(x2, P["weight"], dy.reshape(x2.shape).contiguous(), rstd, dw_out=G["weight"])
+        owner.release_params(after_forward=False)
         owner.grads_ready()
         return dx.view(ctx.shp), None, None
 
@@ -484,12 +504,12 @@ class LlamaForCausalLM(torch.nn.Module):
     def forward(self, ids: torch.Tensor, labels: Optional[torch.Tensor] = None, ignore_index: Optional[int] = None):
         h = self.model(ids)
         B, S, d = h.shape
+        if labels is not None and h.is_cuda:
+            return _LMHeadLossFn.apply(h.reshape(B * S, d), self.head_flat, _HeadOwnerView(self.head_owner, self.cfg.tie_word_embeddings), labels,
+                                       ignore_index, self.loss_chunk_rows)
         w = self.head_unit.view("weight", self.head_flat)
         if labels is None:
             return ops.linear(h, w)
-        if h.is_cuda:
-            return _LMHeadLossFn.apply(h.reshape(B * S, d), w, _HeadOwnerView(self.head_owner, self.cfg.tie_word_embeddings), labels, ignore_index,
-                                       self.loss_chunk_rows)
         logits = torch.nn.functional.linear(h.float(), w.float())
         return torch.nn.functional.cross_entropy(logits.reshape(B * S, -1), labels.reshape(-1),
                                                  ignore_index=-100 if ignore_index is None else ignore_index)
@@ -536,6 +556,12 @@ class _HeadOwnerView:
 
     def __init__(self, owner, tied: bool = False):
         self._o, self._tied = owner, tied
+
+    def acquire_params(self, backward: bool = False):
+        return self._o.acquire_params()
+
+    def release_params(self, after_forward: bool):
+        self._o.release_params(after_forward)
 
     def acquire_grads(self):
         return self._o.acquire_grads()

@@ -47,9 +47,13 @@ def _act_torch(r: torch.Tensor, act) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, bias: torch.Tensor | None = None,
          out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, act: str | None = None,
-         residual: torch.Tensor | None = None) -> torch.Tensor:
+         residual: torch.Tensor | None = None, gate=None) -> torch.Tensor:
     """``D = act(A (x) B + bias) + residual``. Operands bf16 or fp16 (both the same); output in the operand dtype or f32. The epilogue order is
-    bias, activation (``relu`` / ``gelu`` / ``gelu_tanh`` / ``silu``), residual add (``residual`` is ``[M, N]`` in the output dtype)."""
+    bias, activation (``relu`` / ``gelu`` / ``gelu_tanh`` / ``silu``), residual add (``residual`` is ``[M, N]`` in the output dtype).
+
+    ``gate`` (a :class:`ferrotorch_b200.parallel.gather.GatherGate`): ``b`` is a weight inside a gather slot that peers may still be filling;
+    the kernel waits for the pieces under each tile of ``b`` inside its TMA producer (or, for forms the gated kernel does not cover, a gate
+    kernel waits for all of ``b`` first)."""
     if act not in _ACT:
         raise InvalidArgument(f"unknown epilogue activation {act!r}")
     if out_dtype is None:
@@ -95,6 +99,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if residual is not None:
         if residual.shape != (M, N) or residual.dtype != out_dtype or residual.stride(1) != 1:
             raise InvalidArgument("residual must be a row-major [M, N] tensor in the output dtype")
+    gated = False
+    if gate is not None and not gate.covered(b):
+        gated = not in_f16 and bias is None and not (act is not None and _ACT[act]) and residual is None and _auto_splits(M, N, K) == 1
+        if not gated:
+            gate.wait(b)
+    if gated:
+        with torch.cuda.device(a.device):
+            _lib.call("ft_gemm_gated", _lib.P(a), _lib.P(b), _lib.P(out), M, N, K, ctypes.c_int64(a.stride(0)), ctypes.c_int64(b.stride(0)),
+                      ctypes.c_int64(out.stride(0)), int(a_mn), int(b_mn), int(out_dtype == torch.float32), ctypes.c_void_p(gate.counters_ptr),
+                      gate.expected, ctypes.c_void_p(gate.slot_ptr), ctypes.c_int64(gate.piece_bytes), _lib.S())
+        gate.mark(b)
+        return out
     if in_f16 or act is not None and _ACT[act] or residual is not None:
         with torch.cuda.device(a.device):
             _lib.call("ft_gemm_ex", _lib.P(a), _lib.P(b), _lib.P(out), _lib.P(bias), _lib.P(residual), M, N, K, ctypes.c_int64(a.stride(0)), ctypes.c_int64(b.stride(0)),

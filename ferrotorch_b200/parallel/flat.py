@@ -66,6 +66,20 @@ class FlatUnit:
         self.momentum: torch.Tensor | None = None
         self.step = 0
 
+    def reshard(self, shard_align: int) -> None:
+        """Re-pad the unit so that every rank's shard is a multiple of ``shard_align`` elements (the arrival granularity of the fully
+        sharded engine's gather). Only before the optimizer state exists; the values are kept, the new tail is zero."""
+        if self.master is not None:
+            raise RuntimeError("FlatUnit.reshard must run before the optimizer state is created")
+        chunk = _round_up(-(-self.numel // self.world), shard_align)
+        padded = chunk * self.world
+        if padded != self.padded:
+            full = torch.zeros(padded, device=self.device, dtype=self.dtype)
+            n = min(self.padded, padded)
+            full[:n].copy_(self.full[:n])
+            self.full = full
+            self.padded, self.chunk = padded, chunk
+
     # -- views -------------------------------------------------------------
     def view(self, name: str, buf: torch.Tensor | None = None) -> torch.Tensor:
         s = self.specs[name]

@@ -1,25 +1,34 @@
 """Fully-sharded data parallel training engine over flat parameter units.
 
-Sharding: every :class:`FlatUnit` (one per decoder layer, plus embedding, final
-norm and head) is split evenly across ranks. Each rank keeps the f32 master
-weights and AdamW moments of its slice only (ZeRO-3 state sharding); the bf16
-compute copy of a unit is produced by an all-gather and its bf16 gradient is
-reduce-scattered (mean) to the owners as soon as the unit's backward finishes,
-where the sharded AdamW update runs at once ("optimizer in backward"), followed
-by the all-gather of the updated slice, which therefore overlaps the rest of
-the backward pass and is complete long before the next forward needs it.
+Sharding: every :class:`FlatUnit` (one per decoder layer, plus embedding, final norm and head) is split evenly across ranks. Each rank keeps
+the f32 master weights and AdamW moments of its slice only; the bf16 gradient of a unit is reduce-scattered (mean) to the owners as soon as
+the unit's backward finishes, where the sharded AdamW update runs at once ("optimizer in backward").
+
+Strategies (``ShardingStrategy``):
+  * ``FULL_SHARD`` (ZeRO-3): the bf16 parameters are sharded too. A unit is gathered into one of a few slots for its forward pass and
+    again for its backward pass, one unit ahead of the compute stream, and the consuming GEMMs wait per tile for the pieces they read
+    (``parallel/gather.py``); after the update only the owner's shard is refreshed. Per-GPU memory is 16 bytes per parameter / world plus a
+    few unit-sized slots.
+  * ``SHARD_GRAD_OP`` (ZeRO-2): the bf16 compute copy stays resident on every rank and is refreshed by the all-gather that is part of the
+    update kernel, so a step moves every parameter across the fabric once instead of twice; costs 2 bytes per parameter per GPU.
+  * ``NO_SHARD``: use :class:`ferrotorch_b200.parallel.DDP`. ``HYBRID_SHARD`` needs more than one NVSwitch domain (the host-side
+    ``distributed.FSDP`` implements both).
 
 Transports:
   * ``comm="nccl"``   - torch.distributed collectives on a side stream (the library baseline).
-  * ``comm="fused"``  - one hand-written kernel per unit over NVLink peer memory:
-                        pull-reduce of the gradient slice from every peer in fixed rank order, AdamW on the
-                        f32 master slice, bf16 result pushed straight into every peer's parameter buffer
-                        (reduce-scatter + optimizer + all-gather in one launch; see ``parallel/symm.py``).
-At world size 1 both reduce to the plain fused AdamW kernel on a side stream.
+  * ``comm="fused"``  - hand-written kernels over NVLink peer memory: pull-reduce of the gradient slice from every peer in fixed rank
+                        order + AdamW on the f32 master slice (+ the push all-gather in shard-grad-op mode) in one launch; the full-shard
+                        parameter gather as peer pushes with per-piece arrival counters that the tcgen05 GEMMs poll (``parallel/symm.py``,
+                        ``parallel/gather.py``).
+At world size 1 everything reduces to the plain fused AdamW kernel on a side stream.
 
-Reference parity: ferrotorch-distributed/src/fsdp.rs:44-61 (ShardingStrategy), :151-288 (construction),
-:389-542 (forward gather), :627-789 (sync_gradients), :806-845 (broadcast_updated_params). The reference gathers
-every parameter of the whole model up front on host vectors; here gathers are per unit, on device, overlapped.
+``state_dict`` / ``save`` / ``load`` write and read the sharded f32 state (one SafeTensors file per rank plus ``metadata.json``); a
+checkpoint loads at any world size.
+
+Reference parity: ferrotorch-distributed/src/fsdp.rs:44-61 (ShardingStrategy), :151-288 (construction), :389-542 (forward gather),
+:586-609 (restore_shards), :627-789 (sync_gradients), :806-845 (broadcast_updated_params); checkpoint.rs:338,388,457 (save_distributed,
+load_distributed, reshard). The reference gathers every parameter of the whole model up front on host vectors; here gathers are per unit,
+on device, overlapped.
 """
 from __future__ import annotations
 
@@ -61,8 +70,8 @@ class _EngineOwner:
         self.grad_preaccumulated = getattr(base_owner, "grad_preaccumulated", False)
         self._base = base_owner
 
-    def acquire_params(self) -> Dict[str, torch.Tensor]:
-        return self.engine._acquire_params(self.unit)
+    def acquire_params(self, backward: bool = False) -> Dict[str, torch.Tensor]:
+        return self.engine._acquire_params(self.unit, backward)
 
     def release_params(self, after_forward: bool) -> None:
         self.engine._release_params(self.unit, after_forward)
@@ -75,18 +84,13 @@ class _EngineOwner:
 
 
 class FSDP:
-    """Training engine: ``loss = engine.train_step(ids, labels)`` runs forward, backward, gradient
-    reduce-scatter, sharded AdamW and parameter all-gather for one micro-batch per rank.
-
-    What is sharded: the f32 master weights, both AdamW moments and the reduced gradients live only on the owner of each slice (every
-    parameter is owned, updated and checkpointed in shards). The bf16 all-gathered copy that the GEMMs read is kept resident between steps
-    as a cache (16 GB of an 8B model per GPU, out of 180 GB) and is refreshed by the all-gather that follows each unit's update, so a step
-    moves every parameter across the fabric once (after the update) instead of twice (before forward and again before backward) and the
-    gather is hidden behind the rest of the backward pass. ``FULL_SHARD`` and ``SHARD_GRAD_OP`` therefore run the same schedule here;
-    ``NO_SHARD`` (use :class:`ferrotorch_b200.parallel.DDP`) and ``HYBRID_SHARD`` (one NVSwitch domain has no second level) are refused."""
+    """Training engine: ``loss = engine.train_step(ids, labels)`` runs forward, backward, gradient reduce-scatter, sharded AdamW and the
+    parameter all-gather for one micro-batch per rank. See the module docstring for what each :class:`ShardingStrategy` keeps where."""
 
     def __init__(self, model, optim: AdamWConfig | None = None, process_group=None, strategy: ShardingStrategy = ShardingStrategy.FULL_SHARD,
-                 comm: str | None = None, grad_buffers: int = 2, overlap_optimizer: bool = True):
+                 comm: str | None = None, grad_buffers: int = 2, overlap_optimizer: bool = True, local: bool = False):
+        """``local=True`` builds a single-rank engine even inside an initialised process group (the model's units must have been built
+        with ``world=1``): used to load a multi-rank checkpoint on one GPU."""
         import torch.distributed as dist
         self.model = model
         self.optim = optim or AdamWConfig()
@@ -95,7 +99,7 @@ class FSDP:
                                   "one NVSwitch domain (the host-side distributed.FSDP implements both)")
         self.strategy = strategy
         self.pg = process_group
-        self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
+        self.dist = dist if (dist.is_available() and dist.is_initialized() and not local) else None
         self.world = self.dist.get_world_size(self.pg) if self.dist else 1
         self.rank = self.dist.get_rank(self.pg) if self.dist else 0
         self.units: List[FlatUnit] = model.units()
@@ -119,6 +123,15 @@ class FSDP:
         self._unit_grad_slot: Dict[str, int] = {}
         self._param_ready_ev: Dict[str, object] = {}
         self._grad_shard = torch.empty(max(u.chunk for u in self.units), device=self.device, dtype=torch.bfloat16) if self.world > 1 else None
+        if self.strategy == ShardingStrategy.FULL_SHARD and self.world > 1:
+            from .gather import PIECE_BYTES
+            for u in self.units:
+                if u.chunk * 2 > PIECE_BYTES:
+                    u.reshard(PIECE_BYTES // 2)          # shards of whole 512 KiB pieces: the arrival granularity of the gather
+        maxn = max(u.padded for u in self.units)
+        if maxn != self._grad_pool[0].numel():
+            self._grad_pool = [torch.empty(maxn, device=self.device, dtype=torch.bfloat16) for _ in range(len(self._grad_pool))]
+        self._grad_shard = torch.empty(max(u.chunk for u in self.units), device=self.device, dtype=torch.bfloat16) if self.world > 1 else None
         for u in self.units:
             u.init_adam()
         # install engine owners
@@ -126,14 +139,34 @@ class FSDP:
             eo = _EngineOwner(self, o.unit, o)
             self._swap_owner(model, o, eo)
         self._fused = None
+        self.sharded = None                       # ShardedParams: FULL_SHARD with peer-memory gathers
+        self._nccl_shard: Dict[str, torch.Tensor] = {}   # FULL_SHARD over NCCL: this rank's bf16 shard of every unit
+        self._nccl_full: Dict[str, torch.Tensor] = {}
+        self._order = list(self.units)
+        self._index = {u.name: i for i, u in enumerate(self._order)}
+        full = self.strategy == ShardingStrategy.FULL_SHARD and self.world > 1
         if self.world > 1 and self.comm == "fused":
             from .symm import FusedShardedAdamW
             try:
-                self._fused = FusedShardedAdamW(self)
+                self._fused = FusedShardedAdamW(self, full_shard=full)
+                if full:
+                    from .gather import ShardedParams
+                    self.sharded = ShardedParams(self)
             except (RuntimeError, ImportError, AttributeError) as e:   # no symmetric memory on this fabric: library collectives
                 import warnings
                 warnings.warn(f"symmetric memory unavailable ({e}); FSDP falls back to NCCL collectives")
                 self.comm = "nccl"
+                self._fused = self.sharded = None
+        if full and self.sharded is None:
+            # library transport: keep the shard, gather a unit with all_gather_into_tensor when it is needed, drop it after use
+            with torch.no_grad():
+                for u in self.units:
+                    self._nccl_shard[u.name] = u.shard_slice(u.full).clone()
+                    u.full = None
+        if full:
+            from .symm import _unit_params
+            for p in _unit_params(model).values():
+                p.data = torch.empty(0, device=self.device, dtype=torch.bfloat16)     # the parameter object only anchors the autograd node
         if self.world == 1:
             self.comm = "none"
 
@@ -145,14 +178,35 @@ class FSDP:
                 if getattr(mod, attr, None) is old:
                     setattr(mod, attr, new)
 
-    def _acquire_params(self, unit: FlatUnit) -> Dict[str, torch.Tensor]:
+    def _acquire_params(self, unit: FlatUnit, backward: bool = False) -> Dict[str, torch.Tensor]:
+        if self.sharded is not None:
+            # fully sharded: the unit sits (or is arriving) in a gather slot; start the gather of the unit the pass needs next
+            views = self.sharded.acquire(unit, reverse=backward)
+            i = self._index[unit.name]
+            nxt = i - 1 if backward else i + 1
+            if (backward and nxt >= 1) or (not backward and nxt < len(self._order)):      # the embedding's backward reads no parameters
+                self.sharded.prefetch(self._order[nxt], reverse=backward)
+            return views
+        if self._nccl_shard:
+            full = self._nccl_full.get(unit.name)
+            if full is None:
+                full = torch.empty(unit.padded, device=self.device, dtype=torch.bfloat16)
+                ev = self._param_ready_ev.pop(unit.name, None)
+                if ev is not None:
+                    torch.cuda.current_stream().wait_event(ev)
+                self.dist.all_gather_into_tensor(full, self._nccl_shard[unit.name], group=self.pg)
+                self._nccl_full[unit.name] = full
+            return unit.views(full)
         ev = self._param_ready_ev.pop(unit.name, None)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
         return unit.views()
 
     def _release_params(self, unit: FlatUnit, after_forward: bool) -> None:
-        pass  # the gathered bf16 copy stays resident as a cache (see the class docstring)
+        # shard-grad-op: the gathered bf16 copy stays resident. Full shard over peer memory: the slot is recycled (and released to the
+        # pushers) when a later gather needs it. Full shard over NCCL: drop the gathered copy now.
+        if self._nccl_shard:
+            self._nccl_full.pop(unit.name, None)
 
     def _acquire_grads(self, unit: FlatUnit) -> Dict[str, torch.Tensor]:
         slot = self._unit_grad_slot.get(unit.name)
@@ -188,20 +242,33 @@ class FSDP:
                                 beta2=o.betas[1], eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize,
                                 max_ctas=self._opt_ctas)
             elif self._fused is not None:
+                if self.sharded is not None:
+                    pushed = self.sharded.push_done.get(unit.name)
+                    if pushed is not None:
+                        torch.cuda.current_stream().wait_event(pushed)      # the last gather has finished reading this rank's shard
                 self._fused.step(unit, slot)
+                if self.sharded is not None:
+                    ready = torch.cuda.Event()
+                    ready.record(torch.cuda.current_stream())
+                    self.sharded.shard_ready[unit.name] = ready
             else:
                 gs = self._grad_shard[: unit.chunk]
                 self.dist.reduce_scatter_tensor(gs, unit.grad, op=self.dist.ReduceOp.AVG, group=self.pg)
-                mine = unit.shard_slice(unit.full)
+                mine = self._nccl_shard[unit.name] if self._nccl_shard else unit.shard_slice(unit.full)
                 ops.adamw_flat_(unit.master, mine, unit.exp_avg, unit.exp_avg_sq, gs, lr=o.lr, beta1=o.betas[0], beta2=o.betas[1],
                                 eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize, max_ctas=self._opt_ctas)
-                self.dist.all_gather_into_tensor(unit.full, mine, group=self.pg)
+                if not self._nccl_shard:
+                    self.dist.all_gather_into_tensor(unit.full, mine, group=self.pg)
             if self.side is not None:
                 ev = torch.cuda.Event()
                 ev.record(self.side)
                 self._grad_free_ev[slot] = ev
                 self._param_ready_ev[unit.name] = ev
         unit.grad = None
+        if self.sharded is not None:
+            self.sharded.invalidate(unit)            # a copy gathered before this update is stale
+            if self._index[unit.name] == 0:
+                self.sharded.prefetch(unit)          # the last update of the step: the next forward pass starts with this unit
 
     # -- public API -----------------------------------------------------------------------
     def train_step(self, ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
@@ -217,3 +284,105 @@ class FSDP:
 
     def state_bytes(self) -> int:
         return sum(u.nbytes_state() for u in self.units)
+
+    # -- sharded checkpoints ----------------------------------------------------------------------------------------------
+    _STATE = ("master", "exp_avg", "exp_avg_sq")
+
+    def state_dict(self) -> dict:
+        """This rank's shard of the training state: ``{"tensors": {"<unit>.master" | ".exp_avg" | ".exp_avg_sq": f32 [chunk]}, "meta": {...}}``.
+        The tensors are the live device tensors (no copy); ``meta`` records the layout needed to load at another world size."""
+        self.synchronize()
+        tensors = {f"{u.name}.{k}": getattr(u, k) for u in self.units for k in self._STATE}
+        meta = {"format": "ferrotorch_b200.fsdp", "version": 1, "world": self.world, "rank": self.rank, "step_count": self.step_count,
+                "strategy": self.strategy.value,
+                "units": {u.name: {"numel": u.numel, "padded": u.padded, "chunk": u.chunk, "step": u.step} for u in self.units}}
+        return {"tensors": tensors, "meta": meta}
+
+    def save(self, directory) -> None:
+        """Every rank writes ``rank_{r}.safetensors`` (its f32 master / moment shards, straight from the device shards through pinned
+        staging), rank 0 also ``metadata.json``. The files of all ranks together are the checkpoint."""
+        import json
+        from pathlib import Path
+        from ..serialize import save_safetensors
+        d = Path(directory)
+        d.mkdir(parents=True, exist_ok=True)
+        sd = self.state_dict()
+        torch.cuda.synchronize(self.device) if self.device.type == "cuda" else None
+        host = {}
+        for k, t in sd["tensors"].items():
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.device.type == "cuda")
+            h.copy_(t, non_blocking=True)
+            host[k] = h
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        save_safetensors(host, d / f"rank_{self.rank}.safetensors", metadata={"rank": str(self.rank), "world": str(self.world)})
+        if self.rank == 0:
+            (d / "metadata.json").write_text(json.dumps(sd["meta"], indent=1))
+        if self.dist is not None:
+            self.dist.barrier(self.pg)
+
+    def load(self, directory) -> None:
+        """Restore the state written by :meth:`save`, at this engine's world size whatever the writer's was: every rank reads, per unit, the
+        parts of the old shards that overlap its new slice ``[rank * chunk, (rank + 1) * chunk)`` of the flat unit, then rebuilds its bf16
+        parameters from the restored master weights."""
+        import json
+        from pathlib import Path
+        from ..serialize import load_safetensors
+        d = Path(directory)
+        meta = json.loads((d / "metadata.json").read_text())
+        if meta.get("format") != "ferrotorch_b200.fsdp":
+            raise InvalidArgument(f"{d} is not an FSDP engine checkpoint")
+        old_world = int(meta["world"])
+        self.synchronize()
+        for u in self.units:
+            mu = meta["units"].get(u.name)
+            if mu is None or int(mu["numel"]) != u.numel:
+                raise InvalidArgument(f"checkpoint unit {u.name!r} is missing or has another size")
+            old_chunk = int(mu["chunk"])
+            lo, hi = self.rank * u.chunk, min((self.rank + 1) * u.chunk, u.numel)      # elements past numel are padding (zero)
+            parts = {k: torch.zeros(u.chunk, dtype=torch.float32) for k in self._STATE}
+            if hi > lo:
+                for r in range(lo // old_chunk, min((hi - 1) // old_chunk, old_world - 1) + 1):
+                    names = {f"{u.name}.{k}" for k in self._STATE}
+                    got = load_safetensors(d / f"rank_{r}.safetensors", filter_fn=lambda n, names=names: n in names)
+                    a, b = max(lo, r * old_chunk), min(hi, (r + 1) * old_chunk)
+                    for k in self._STATE:
+                        parts[k][a - lo: b - lo] = got[f"{u.name}.{k}"][a - r * old_chunk: b - r * old_chunk]
+            with torch.no_grad():
+                for k in self._STATE:
+                    getattr(u, k).copy_(parts[k].to(self.device))
+            u.step = int(mu["step"])
+            self._refresh_compute_copy(u)
+        self.step_count = int(meta.get("step_count", 0))
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if self.dist is not None:
+            self.dist.barrier(self.pg)
+
+    def _refresh_compute_copy(self, u: FlatUnit) -> None:
+        """bf16 parameters of a unit from its (just restored) f32 master shard."""
+        mine = u.master.to(torch.bfloat16)
+        if self.sharded is not None:
+            self.sharded.shard[u.name].copy_(mine)
+            self.sharded.invalidate(u)
+        elif self._nccl_shard:
+            self._nccl_shard[u.name].copy_(mine)
+            self._nccl_full.pop(u.name, None)
+        elif self.world > 1:
+            self.dist.all_gather_into_tensor(u.full, mine, group=self.pg)
+        else:
+            u.full.copy_(mine)
+
+    def full_parameters(self) -> Dict[str, torch.Tensor]:
+        """``{unit name: the whole bf16 unit}`` on every rank (gathered where the strategy shards the parameters): for export and tests."""
+        out = {}
+        for u in self.units:
+            if self.sharded is not None:
+                out[u.name] = self.sharded.full_tensor(u).clone()
+            elif self._nccl_shard:
+                full = torch.empty(u.padded, device=self.device, dtype=torch.bfloat16)
+                self.dist.all_gather_into_tensor(full, self._nccl_shard[u.name], group=self.pg)
+                out[u.name] = full
+            else:
+                out[u.name] = u.full.clone()
+        return out

@@ -204,38 +204,38 @@ class SymmComm:
 
 
 class FusedShardedAdamW:
-    """Reduce-scatter + sharded AdamW + all-gather of one flat unit in a single kernel over peer memory.
+    """Reduce-scatter + sharded AdamW (+ all-gather) of one flat unit in a single kernel over peer memory.
 
-    Owns the symmetric arenas: every unit's bf16 parameter buffer is moved into one symmetric allocation and the
-    engine's rotating gradient buffers into another, so a peer can read any rank's gradients and write any
-    rank's parameters.
+    Owns the symmetric arenas. The engine's rotating gradient buffers always live in one, so a peer can read any rank's gradients.
+    ``full_shard=False`` (shard-grad-op): every unit's bf16 parameter buffer is moved into a second symmetric arena and the kernel pushes
+    the refreshed slice into every rank's copy (the all-gather is part of the update). ``full_shard=True``: there is no replicated copy;
+    the kernel writes the refreshed slice into this rank's shard only (``engine.sharded``, see ``parallel/gather.py``) and the parameters
+    are gathered again when the next pass needs them.
     """
 
-    def __init__(self, engine):
+    def __init__(self, engine, full_shard: bool = False):
         self.e = engine
+        self.full_shard = full_shard
         dev, group = engine.device, engine.pg
         self.comm = SymmComm(dev, group)
         units = engine.units
-        total = sum(u.padded for u in units)
-        self.params = SymmetricBuffer(total, torch.bfloat16, dev, group)
-        off = 0
         self.offset = {}
-        name_to_param = {}
-        for mod in engine.model.modules():
-            for attr, unit_attr in (("flat", "unit"), ("embed_flat", "embed_unit"), ("norm_flat", "norm_unit"), ("head_flat", "head_unit")):
-                if hasattr(mod, attr) and hasattr(mod, unit_attr):
-                    name_to_param[getattr(mod, unit_attr).name] = getattr(mod, attr)
-        with torch.no_grad():
-            for u in units:
-                view = self.params.tensor[off: off + u.padded]
-                view.copy_(u.full)
-                u.full = view
-                p = name_to_param.get(u.name)
-                if p is not None:
-                    p.data = view
-                self.offset[u.name] = off
-                off += u.padded
-        # CTAs of the fused reduce-scatter + AdamW + all-gather launch (0 = the kernel's default of 96): it shares the SMs with the backward GEMMs
+        if not full_shard:
+            total = sum(u.padded for u in units)
+            self.params = SymmetricBuffer(total, torch.bfloat16, dev, group)
+            off = 0
+            name_to_param = _unit_params(engine.model)
+            with torch.no_grad():
+                for u in units:
+                    view = self.params.tensor[off: off + u.padded]
+                    view.copy_(u.full)
+                    u.full = view
+                    p = name_to_param.get(u.name)
+                    if p is not None:
+                        p.data = view
+                    self.offset[u.name] = off
+                    off += u.padded
+        # CTAs of the fused reduce-scatter + AdamW (+ all-gather) launch (0 = the kernel's default of 96): it shares the SMs with the backward GEMMs
         self.max_ctas = int(os.environ.get("FT_FSDP_CTAS", "0"))
         nbuf = len(engine._grad_pool)
         self.maxn = max(u.padded for u in units)
@@ -248,6 +248,21 @@ class FusedShardedAdamW:
     def step(self, unit, slot: int) -> None:
         o = self.e.optim
         c = self.comm
+        if self.full_shard:
+            _lib.call("ft_fsdp_rs_adamw", self.grads.ptr_array(slot * self.maxn), self.e.sharded.shard[unit.name], c.flag_ptrs, c.counter, c.rank,
+                      c.world, c._next(), unit.master, unit.exp_avg, unit.exp_avg_sq, unit.chunk, o.lr, o.betas[0], o.betas[1], o.eps,
+                      o.weight_decay, unit.step, None, self.max_ctas, _lib.S())
+            return
         _lib.call("ft_fsdp_rs_adamw_ag", self.grads.ptr_array(slot * self.maxn), self.params.ptr_array(self.offset[unit.name]),
                   c.flag_ptrs, c.counter, c.rank, c.world, c._next(), unit.master, unit.exp_avg, unit.exp_avg_sq, unit.chunk, o.lr,
                   o.betas[0], o.betas[1], o.eps, o.weight_decay, unit.step, None, self.max_ctas, _lib.S())
+
+
+def _unit_params(model) -> dict:
+    """``unit name -> the nn.Parameter that stands for the unit in the autograd graph``."""
+    out = {}
+    for mod in model.modules():
+        for attr, unit_attr in (("flat", "unit"), ("embed_flat", "embed_unit"), ("norm_flat", "norm_unit"), ("head_flat", "head_unit")):
+            if hasattr(mod, attr) and hasattr(mod, unit_attr):
+                out[getattr(mod, unit_attr).name] = getattr(mod, attr)
+    return out

@@ -91,37 +91,93 @@ def case_collectives():
 
 
 def case_fsdp():
+    """Every sharding strategy and transport of the device engine trains the same model to the same losses and parameters; the fully sharded
+    engine holds no replicated parameter copy; a checkpoint written by one configuration loads into another, also at world size 1."""
+    import shutil
+    from ferrotorch_b200 import _lib
     from ferrotorch_b200.models import LlamaConfig, LlamaForCausalLM
-    from ferrotorch_b200.parallel import FSDP, AdamWConfig
+    from ferrotorch_b200.parallel import FSDP, AdamWConfig, ShardingStrategy
     rank, world, dev = _init()
-    cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=512)
-    results = {}
-    for comm in ("nccl", "fused"):
+    cfg = LlamaConfig.tiny(layers=3, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=512)
+    opt = AdamWConfig(lr=3e-3, betas=(0.9, 0.95), weight_decay=0.01)
+    torch.manual_seed(11 + rank)
+    ids = torch.randint(0, cfg.vocab_size, (2, 129), device=dev)
+    modes = [("nccl", ShardingStrategy.SHARD_GRAD_OP), ("fused", ShardingStrategy.SHARD_GRAD_OP), ("fused", ShardingStrategy.FULL_SHARD),
+             ("nccl", ShardingStrategy.FULL_SHARD)]
+    results, engines = {}, {}
+    for comm, strat in modes:
+        key = f"{comm}/{strat.value}"
         model = LlamaForCausalLM(cfg, device=dev, world=world, rank=rank, seed=0)
-        eng = FSDP(model, AdamWConfig(lr=3e-3, betas=(0.9, 0.95), weight_decay=0.01), comm=comm)
-        torch.manual_seed(11 + rank)
-        ids = torch.randint(0, cfg.vocab_size, (2, 129), device=dev)
-        losses = []
-        for _ in range(6):
-            losses.append(eng.train_step(ids[:, :-1], ids[:, 1:]).item())
+        eng = FSDP(model, opt, comm=comm, strategy=strat)
+        assert eng.comm == comm, (key, eng.comm)
+        losses = [eng.train_step(ids[:, :-1], ids[:, 1:]).item() for _ in range(6)]
         eng.synchronize()
         torch.cuda.synchronize()
-        from ferrotorch_b200 import _lib
-        assert _lib.read_status() == 0
-        w = model.model.layers[0].unit.full.float().clone()
-        results[comm] = (losses, w)
-        # parameters identical on every rank after the updates
+        assert _lib.read_status() == 0, key
+        params = eng.full_parameters()
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0, key
+        w = torch.cat([params[u.name][: u.numel].float() for u in eng.units])
+        results[key] = (losses, w)
+        engines[key] = (model, eng)
         ws = [torch.empty_like(w) for _ in range(world)]
         dist.all_gather(ws, w)
         for o in ws[1:]:
-            assert torch.equal(o, ws[0]), comm
-        assert losses[-1] < losses[0], (comm, losses)
-    la, lb = results["nccl"][0], results["fused"][0]
-    assert all(abs(a - b) < 5e-2 for a, b in zip(la, lb)), (la, lb)
-    rel = (results["nccl"][1] - results["fused"][1]).norm() / results["nccl"][1].norm()
-    assert rel.item() < 2e-2, rel.item()
+            assert torch.equal(o, ws[0]), key                      # parameters identical on every rank after the updates
+        assert losses[-1] < losses[0], (key, losses)
+        if strat == ShardingStrategy.FULL_SHARD:
+            assert all(u.full is None for u in eng.units), key      # no replicated copy is kept
+            if comm == "fused":
+                # units that stay resident between forward and backward are not gathered twice
+                assert eng.sharded.gathers < 6 * 2 * len(eng.units), (eng.sharded.gathers, len(eng.units))
+    base_l, base_w = results["nccl/shard_grad_op"]
+    for key, (l, w) in results.items():
+        assert all(abs(a - b) < 5e-2 for a, b in zip(base_l, l)), (key, base_l, l)
+        rel = (base_w - w).norm() / base_w.norm()
+        assert rel.item() < 2e-2, (key, rel.item())
+    # ---- checkpoints: written by the fully sharded engine, read by a shard-grad-op engine at the same world size and by a single-rank engine ----
+    ck = Path(f"/tmp/ft_fsdp_ck_{os.environ.get('MASTER_PORT', '0')}")
     if rank == 0:
-        print("FSDP_OK", la, lb)
+        shutil.rmtree(ck, ignore_errors=True)
+    dist.barrier()
+    src_model, src = engines["fused/full_shard"]
+    src.save(ck / "a")
+    m2 = LlamaForCausalLM(cfg, device=dev, world=world, rank=rank, seed=123)           # different initial values
+    e2 = FSDP(m2, opt, comm="fused", strategy=ShardingStrategy.SHARD_GRAD_OP)
+    e2.load(ck / "a")
+    la = [src.train_step(ids[:, :-1], ids[:, 1:]).item() for _ in range(2)]
+    lb = [e2.train_step(ids[:, :-1], ids[:, 1:]).item() for _ in range(2)]
+    assert all(abs(a - b) < 2e-2 for a, b in zip(la, lb)), (la, lb)                    # training resumes on the restored state
+    # single-rank engine reads the multi-rank files (every rank does so on its own GPU)
+    src.save(ck / "b")
+    m1 = LlamaForCausalLM(cfg, device=dev, world=1, rank=0, seed=5)
+    e1 = FSDP(m1, opt, local=True)
+    e1.load(ck / "b")
+    for u_src, u1 in zip(src.units, e1.units):
+        parts = [torch.empty_like(u_src.master) for _ in range(world)]
+        dist.all_gather(parts, u_src.master)
+        whole = torch.cat(parts)[: u1.numel]
+        assert torch.equal(whole, u1.master[: u1.numel]), u1.name
+        assert u1.step == u_src.step
+    full_src = src.full_parameters()
+    for u1 in e1.units:
+        assert torch.equal(full_src[u1.name][: u1.numel], u1.full[: u1.numel]), u1.name
+    # and back: a single-rank checkpoint (written by rank 0) loads into the sharded engine
+    if rank == 0:
+        e1.save(ck / "c")
+    dist.barrier()
+    m3 = LlamaForCausalLM(cfg, device=dev, world=world, rank=rank, seed=77)
+    e3 = FSDP(m3, opt, comm="fused", strategy=ShardingStrategy.FULL_SHARD)
+    e3.load(ck / "c")
+    full3 = e3.full_parameters()
+    for u1 in e1.units:
+        assert torch.equal(full3[u1.name][: u1.numel], u1.full[: u1.numel]), u1.name
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    dist.barrier()
+    if rank == 0:
+        shutil.rmtree(ck, ignore_errors=True)
+        print("FSDP_OK", base_l, results["fused/full_shard"][0])
 
 
 def case_timeout():
