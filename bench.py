@@ -187,6 +187,8 @@ def main():
     engine = FSDP(model, AdamWConfig(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1), comm=args.comm,
                   strategy=ShardingStrategy(args.strategy))
     torch.cuda.synchronize()
+    init_peak_gb = torch.cuda.max_memory_allocated() / 2**30      # includes the unsharded bf16 initialisation every rank starts from
+    torch.cuda.reset_peak_memory_stats()
 
     # synthetic data: a few distinct pinned host batches per rank, cycled
     g = torch.Generator().manual_seed(1234 + rank)
@@ -291,7 +293,8 @@ def main():
                     "h2d_bytes_per_step": int(B * (S + 1) * 8), "d2h_bytes_per_step": 4, "clocks": clocks_e2e},
             "gpu_launches": int(launches), "first_loss": first_loss, "last_loss": float(last_loss) if last_loss is not None else None,
             "kernel_status": status, "impl": "ours",
-            "mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+            "mem_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2), "mem_gb_during_init": round(init_peak_gb, 2),
+            "mem_gb_device_in_use": round((torch.cuda.mem_get_info()[1] - torch.cuda.mem_get_info()[0]) / 2**30, 2),
         }
         if breakdown is not None:
             out["breakdown"] = breakdown

@@ -306,7 +306,9 @@ struct AdamWArgsC { float lr, beta1, beta2, eps, weight_decay, bias_c1, bias_c2;
 
 // local_out != null: the fully sharded form. The refreshed bf16 slice is written to this rank's own shard only (local_out[i]); nothing is pushed,
 // the parameters are gathered again when the next forward pass needs them (fsdp_gather.cu).
-__global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, CommSync s, float* __restrict__ master,
+// 256 threads and raw 16-byte gradient loads keep the kernel light (registers, warps per SM sub-partition): it runs on a side stream BESIDE the
+// backward GEMMs, and a CTA that does not fit next to a GEMM CTA would make the GEMM wait for it instead.
+__global__ void __maxnreg__(80) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, PeerPtrs params, CommSync s, float* __restrict__ master,
                                                                float* __restrict__ m, float* __restrict__ v, size_t chunk, AdamWArgsC a,
                                                                const float* __restrict__ grad_scale_ptr, __nv_bfloat16* __restrict__ local_out,
                                                                uint32_t* status) {
@@ -315,18 +317,24 @@ __global__ void __launch_bounds__(512) fsdp_rs_adamw_ag_kernel(PeerPtrs grads, P
   const float decay = 1.f - a.lr * a.weight_decay, step = a.lr / a.bias_c1, inv_c2 = rsqrtf(a.bias_c2);
   const size_t nvec = chunk / 8, base = chunk * s.rank;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-    float f[MAX_RANKS][8];
+    uint4 raw[MAX_RANKS];                                     // every peer's slice is requested before any is used: the loads overlap
 #pragma unroll
     for (int q = 0; q < MAX_RANKS; q++)
-      if (q < s.world) Vec16<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(grads.p[q]) + base + i * 8, f[q]);
+      if (q < s.world) raw[q] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[q]) + base + i * 8);
     float g[8];
 #pragma unroll
     for (int e = 0; e < 8; e++) g[e] = 0.f;
 #pragma unroll
     for (int q = 0; q < MAX_RANKS; q++)
-      if (q < s.world)
+      if (q < s.world) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[q]);
 #pragma unroll
-        for (int e = 0; e < 8; e++) g[e] += f[q][e];          // fixed rank order: identical bits on every rank
+        for (int e = 0; e < 4; e++) {
+          const float2 f2 = __bfloat1622float2(h[e]);
+          g[2 * e] += f2.x;                                   // fixed rank order: identical bits on every rank
+          g[2 * e + 1] += f2.y;
+        }
+      }
     float4* pm = reinterpret_cast<float4*>(master + i * 8);
     float4* mm = reinterpret_cast<float4*>(m + i * 8);
     float4* vv = reinterpret_cast<float4*>(v + i * 8);
@@ -629,8 +637,10 @@ FT_EXPORT int ft_fsdp_rs_adamw_ag(void* const* grad_ptrs, void* const* param_ptr
   PeerPtrs g, p;
   for (int i = 0; i < MAX_RANKS; i++) { g.p[i] = i < world ? grad_ptrs[i] : nullptr; p.p[i] = i < world ? param_ptrs[i] : nullptr; }
   AdamWArgsC a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step)};
-  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 96);
-  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, nullptr, ft_status_ptr());
+  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 148);     // one CTA per SM beside the GEMM
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(fsdp_rs_adamw_ag_kernel); configured = true; }
+  fsdp_rs_adamw_ag_kernel<<<grid, 256, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, nullptr, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -646,7 +656,9 @@ FT_EXPORT int ft_fsdp_rs_adamw(void* const* grad_ptrs, void* shard_out, void* co
   PeerPtrs g, p;
   for (int i = 0; i < MAX_RANKS; i++) { g.p[i] = i < world ? grad_ptrs[i] : nullptr; p.p[i] = nullptr; }
   AdamWArgsC a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step)};
-  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 96);
-  fsdp_rs_adamw_ag_kernel<<<grid, 512, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, (__nv_bfloat16*)shard_out, ft_status_ptr());
+  const int grid = comm_grid((size_t)chunk / 8, max_ctas > 0 ? max_ctas : 148);
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(fsdp_rs_adamw_ag_kernel); configured = true; }
+  fsdp_rs_adamw_ag_kernel<<<grid, 256, 0, st>>>(g, p, s, master, m, v, (size_t)chunk, a, grad_scale_ptr, (__nv_bfloat16*)shard_out, ft_status_ptr());
   return (int)cudaGetLastError();
 }

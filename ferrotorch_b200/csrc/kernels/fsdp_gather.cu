@@ -64,16 +64,16 @@ __global__ void __launch_bounds__(PUSH_THREADS) fsdp_push_kernel(const PushArgs 
     const uint4* s = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.src) + off);
     uint4* t = reinterpret_cast<uint4*>(a.dst[q] + (unsigned long long)a.rank * a.chunk_bytes + off);
     const unsigned long long nvec = n / 16;
-    for (unsigned long long i = threadIdx.x; i < nvec; i += (unsigned long long)PUSH_THREADS * UNROLL) {
+    for (unsigned long long i = threadIdx.x; i < nvec; i += (unsigned long long)blockDim.x * UNROLL) {
       uint4 v[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; u++) {
-        const unsigned long long k = i + (unsigned long long)u * PUSH_THREADS;
+        const unsigned long long k = i + (unsigned long long)u * blockDim.x;
         if (k < nvec) v[u] = __ldcs(s + k);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; u++) {
-        const unsigned long long k = i + (unsigned long long)u * PUSH_THREADS;
+        const unsigned long long k = i + (unsigned long long)u * blockDim.x;
         if (k < nvec) t[k] = v[u];
       }
     }
@@ -97,6 +97,15 @@ __global__ void __launch_bounds__(256) fsdp_gate_kernel(const uint32_t* __restri
   for (int p = lo + threadIdx.x; p < hi; p += blockDim.x) {
     if (!wait_flag_ge(arrive + p, expected, timeout_ns)) ft_set_status(status, FT_K_FSDP, 2, (uint32_t)p);
   }
+}
+
+// Copy-engine form of the push: the shard travels by cudaMemcpyAsync (no SM is occupied while the GEMMs run); these two small kernels frame it.
+__global__ void fsdp_wait_free_kernel(const uint32_t* __restrict__ free_flags, int world, uint32_t need, unsigned long long timeout_ns, uint32_t* status) {
+  if ((int)threadIdx.x < world && !wait_flag_ge(free_flags + threadIdx.x, need, timeout_ns)) ft_set_status(status, FT_K_FSDP, 3, threadIdx.x);
+}
+__global__ void __launch_bounds__(256) fsdp_signal_kernel(uint32_t* __restrict__ arrive, int count, uint32_t value) {
+  __threadfence_system();
+  for (int i = threadIdx.x; i < count; i += blockDim.x) st_release_sys(arrive + i, value);
 }
 
 unsigned long long g_timeout_ns = 0;
@@ -146,7 +155,11 @@ FT_EXPORT int ft_fsdp_push_shard(const void* src, void* const* slot_ptrs, void* 
   int grid = a.pieces_per_chunk * world;
   const int cap = max_ctas > 0 ? max_ctas : 24;
   if (grid > cap) grid = cap;
-  fsdp_push_kernel<<<grid, PUSH_THREADS, 0, st>>>(a, ft_status_ptr());
+  static int threads = 0;
+  if (threads == 0) { const char* e = getenv("FT_FSDP_PUSH_THREADS"); threads = e ? atoi(e) : PUSH_THREADS; if (threads < 32 || threads > PUSH_THREADS) threads = PUSH_THREADS; }
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(fsdp_push_kernel); ft_prefer_max_shared(fsdp_release_kernel); ft_prefer_max_shared(fsdp_gate_kernel); configured = true; }
+  fsdp_push_kernel<<<grid, threads, 0, st>>>(a, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 
@@ -164,5 +177,29 @@ FT_EXPORT int ft_fsdp_release(void* const* free_ptrs, int world, uint32_t value,
 FT_EXPORT int ft_fsdp_gate(const void* arrive, int piece_lo, int piece_hi, uint32_t expected, cudaStream_t st) {
   if (arrive == nullptr || piece_lo < 0 || piece_hi <= piece_lo) return FT_ERR_ARG;
   fsdp_gate_kernel<<<1, 256, 0, st>>>((const uint32_t*)arrive, piece_lo, piece_hi, expected, gather_timeout_ns(), ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// Copy-engine push, step 1: wait (bounded) on the gather stream until every rank has released the slot's previous occupant
+// (free_flags[q] >= need for q < world; local memory).
+FT_EXPORT int ft_fsdp_wait_free(const void* free_flags, int world, uint32_t need, cudaStream_t st) {
+  if (world < 1 || world > MAXR || free_flags == nullptr) return FT_ERR_ARG;
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(fsdp_wait_free_kernel); ft_prefer_max_shared(fsdp_signal_kernel); configured = true; }
+  fsdp_wait_free_kernel<<<1, 32, 0, st>>>((const uint32_t*)free_flags, world, need, gather_timeout_ns(), ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// Step 2: one device-to-device copy per destination (dst may be a peer mapping: the copy engine moves it across NVLink).
+FT_EXPORT int ft_memcpy_d2d_async(void* dst, const void* src, int64_t bytes, cudaStream_t st) {
+  if (bytes <= 0 || dst == nullptr || src == nullptr) return FT_ERR_ARG;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, st);
+}
+
+// Step 3, after the copy to a rank in stream order: set `count` arrival counters of that rank (arrive = this rank's mapping of the first one) to
+// `value`, the number of this gather.
+FT_EXPORT int ft_fsdp_signal(void* arrive, int count, uint32_t value, cudaStream_t st) {
+  if (arrive == nullptr || count < 1) return FT_ERR_ARG;
+  fsdp_signal_kernel<<<1, 256, 0, st>>>((uint32_t*)arrive, count, value);
   return (int)cudaGetLastError();
 }

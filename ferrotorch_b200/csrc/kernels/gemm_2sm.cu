@@ -115,8 +115,10 @@ FT_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0)
   n0 = (local / gm) * BN;
 }
 
+// At most 128 registers per thread: two warps of the CTA share an SM sub-partition (6 warps on 4 sub-partitions), so the CTA claims at most half
+// of each 16K-register sub-partition file and the other half stays available to co-resident kernels of other streams.
 template <bool A_MN, bool B_MN, bool OUT_F32>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __maxnreg__(128)
 ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmD,
                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int k_splits, uint32_t* status, const Gemm2Epi epi, const Gemm2Gate gate,
                 long long ldb_bytes) {
@@ -162,10 +164,22 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
+    // Gated operand: one look at all of its pieces by the whole warp. With the gather running a unit ahead they have normally all arrived, and
+    // the per-tile waits below then cost nothing; if some are still in flight the tiles wait for exactly the pieces they read.
+    long long ready_lo = 0, ready_hi = 0;                 // pieces [ready_lo, ready_hi) of the gated operand are known to have arrived
+    if (gate.counters != nullptr) {
+      const long long op_lo = gate.b_byte_off / gate.piece_bytes, op_hi = (gate.b_byte_off + gate.b_bytes - 1) / gate.piece_bytes + 1;
+      bool mine = true;
+      for (long long p = op_lo + lane; p < op_hi; p += 32) mine = mine && (int32_t)(ld_acquire_sys(gate.counters + p) - gate.expected) >= 0;
+      if (__all_sync(0xffffffffu, mine)) {
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        ready_lo = op_lo;
+        ready_hi = op_hi;
+      }
+    }
     if (lane == 0) {
       uint32_t s = 0, phase = 0;
       bool ok = true;
-      long long ready_lo = 0, ready_hi = 0;               // pieces [ready_lo, ready_hi) of the gated operand are known to have arrived
       for (int item = pair; item < num_items && ok; item += num_pairs) {
         int m0, n0;
         tile_coords(item / k_splits, tiles_m, tiles_n, m0, n0);
@@ -271,67 +285,72 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
       for (int c = 0; c < CHUNKS; c++) {
-        uint32_t v[EPI_COLS];
-        tmem_ld_32x32b_x32(t_row + c * EPI_COLS, v);
-        if constexpr (!OUT_F32) tmem_ld_32x32b_x32(t_row + c * EPI_COLS + 32, v + 32);
+        const int col0 = n0 + c * EPI_COLS;
         if (lane == 0) tma_store_wait_read<0>();          // the previous store from this buffer has been read out
         __syncwarp();
-        tmem_ld_wait();
-        if (empty_split) {
-#pragma unroll
-          for (int i = 0; i < EPI_COLS; i++) v[i] = 0u;
-        }
-        const int col0 = n0 + c * EPI_COLS;
-        if (bias != nullptr) {
-#pragma unroll
-          for (int i = 0; i < EPI_COLS; i++) {
-            float b = 0.f;
-            if (col0 + i < N) b = epi.in_f16 ? __half2float(__ldg(reinterpret_cast<const __half*>(bias) + col0 + i)) : __bfloat162float(__ldg(bias + col0 + i));
-            v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
-          }
-        }
-        if (epi.act != 0) {
-#pragma unroll
-          for (int i = 0; i < EPI_COLS; i++) v[i] = __float_as_uint(epi_act(epi.act, __uint_as_float(v[i])));
-        }
-        if (epi.residual != nullptr && row0 + lane < M) {
-          const size_t roff = (size_t)(row0 + lane) * (size_t)epi.ldr + col0;
-          if constexpr (OUT_F32) {
-            const float* rp = reinterpret_cast<const float*>(epi.residual) + roff;
-#pragma unroll
-            for (int i = 0; i < EPI_COLS; i++)
-              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + rp[i]);
-          } else if (epi.in_f16) {
-            const __half* rp = reinterpret_cast<const __half*>(epi.residual) + roff;
-#pragma unroll
-            for (int i = 0; i < EPI_COLS; i++)
-              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __half2float(rp[i]));
-          } else {
-            const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(epi.residual) + roff;
-#pragma unroll
-            for (int i = 0; i < EPI_COLS; i++)
-              if (col0 + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(rp[i]));
-          }
-        }
         uint8_t* row = buf + lane * 128;
-        if constexpr (OUT_F32) {
+        // 32 accumulator columns at a time: the epilogue warps then need ~100 registers, which keeps the CTA's share of each SM sub-partition's
+        // register file small enough for bandwidth-bound kernels of other streams (optimizer, collectives) to be resident beside the GEMM
+#pragma unroll 1
+        for (int h = 0; h < EPI_COLS / 32; h++) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + c * EPI_COLS + h * 32, v);
+          tmem_ld_wait();
+          if (empty_split) {
 #pragma unroll
-          for (int j = 0; j < 8; j++) *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        } else {
+            for (int i = 0; i < 32; i++) v[i] = 0u;
+          }
+          const int colh = col0 + h * 32;
+          if (bias != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
-            uint32_t p[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-              if (epi.in_f16) {
-                __half2 h = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
-                p[e] = *reinterpret_cast<uint32_t*>(&h);
-              } else {
-                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
-                p[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
+            for (int i = 0; i < 32; i++) {
+              float b = 0.f;
+              if (colh + i < N) b = epi.in_f16 ? __half2float(__ldg(reinterpret_cast<const __half*>(bias) + colh + i)) : __bfloat162float(__ldg(bias + colh + i));
+              v[i] = __float_as_uint(__uint_as_float(v[i]) + b);
             }
-            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+          if (epi.act != 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = __float_as_uint(epi_act(epi.act, __uint_as_float(v[i])));
+          }
+          if (epi.residual != nullptr && row0 + lane < M) {
+            const size_t roff = (size_t)(row0 + lane) * (size_t)epi.ldr + colh;
+            if constexpr (OUT_F32) {
+              const float* rp = reinterpret_cast<const float*>(epi.residual) + roff;
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (colh + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + rp[i]);
+            } else if (epi.in_f16) {
+              const __half* rp = reinterpret_cast<const __half*>(epi.residual) + roff;
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (colh + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __half2float(rp[i]));
+            } else {
+              const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(epi.residual) + roff;
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (colh + i < N) v[i] = __float_as_uint(__uint_as_float(v[i]) + __bfloat162float(rp[i]));
+            }
+          }
+          if constexpr (OUT_F32) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              uint32_t p[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                if (epi.in_f16) {
+                  __half2 hh = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                  p[e] = *reinterpret_cast<uint32_t*>(&hh);
+                } else {
+                  __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(v[8 * j + 2 * e]), __uint_as_float(v[8 * j + 2 * e + 1]));
+                  p[e] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+              }
+              *reinterpret_cast<uint4*>(row + (((h * 4 + j) ^ (lane & 7)) << 4)) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
           }
         }
         fence_proxy_async_smem();
@@ -429,7 +448,7 @@ int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int
   if (gate.counters != nullptr) {
     if (gate.piece_bytes < 16 || gate.b_byte_off < 0 || (gate.mode != 1 && gate.mode != 2)) return FT_ERR_ARG;
     if (gate.mode == 1 && b_mn) gate.mode = 2;                       // rows of an MN-major operand are not contiguous per tile
-    if (gate.mode == 2 && gate.b_bytes <= 0) return FT_ERR_ARG;
+    if (gate.b_bytes <= 0) return FT_ERR_ARG;
   }
   const bool in_bf16 = !epi.in_f16;
   if (M <= 0 || N <= 0 || K <= 0 || k_splits < 1 || k_splits > 256) return FT_ERR_ARG;

@@ -53,6 +53,16 @@ cudaError_t ft_bind_context(int dev);
 // Per-device status word in device memory (lazily allocated, zeroed).
 uint32_t* ft_status_ptr();
 
+// Kernels meant to run BESIDE the persistent GEMM (optimizer, collectives, parameter pushes, all on side streams) ask for the same shared-memory
+// carveout as the GEMM. An SM runs with one L1 / shared-memory split at a time: a kernel that prefers another split is not co-scheduled onto an SM
+// the GEMM occupies and would only get SMs at kernel boundaries, which serialises the "overlapped" work behind the GEMMs.
+#ifdef __CUDACC__
+template <typename K>
+inline void ft_prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+#endif
+
 // Launch with the programmatic-stream-serialization attribute when programmatic dependent launch is switched on (ft_set_pdl), else an ordinary
 // launch. Only kernels that call pdl_wait() before touching memory a predecessor may still be writing (or reading) go through this.
 bool ft_pdl_enabled();

@@ -280,6 +280,8 @@ FT_EXPORT int ft_adamw_flat(float* master, void* p_bf16, float* m, float* v, con
   AdamWArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), maximize};
   int grid = flat_grid(((size_t)n + 3) / 4, 256);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(adamw_kernel<__nv_bfloat16>); ft_prefer_max_shared(adamw_kernel<float>); configured = true; }
   if (grad_dtype == 0)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, (__nv_bfloat16*)p_bf16, m, v, (const __nv_bfloat16*)grad, (size_t)n, a,
                                                       grad_scale_ptr, skip_ptr);

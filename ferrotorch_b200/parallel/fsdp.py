@@ -112,7 +112,7 @@ class FSDP:
         cuda = self.device.type == "cuda"
         if os.environ.get("FT_NO_SIDE_STREAM") == "1":
             overlap_optimizer = False
-        self._opt_ctas = int(os.environ.get("FT_OPT_CTAS", "296")) if (cuda and overlap_optimizer) else 0   # two CTAs per SM beside the GEMM
+        self._opt_ctas = int(os.environ.get("FT_OPT_CTAS", "148")) if (cuda and overlap_optimizer) else 0   # one 256-thread CTA per SM beside the GEMM (measured: two per SM no longer overlap with it)
         self._debug_skip_opt = os.environ.get("FT_DEBUG_SKIP_OPT") == "1"      # diagnosis only: measures the step without any update
         self.side = torch.cuda.Stream(device=self.device, priority=-1) if (cuda and overlap_optimizer) else None
         # gradient buffers: a small rotating pool of full-size bf16 buffers, sized for the largest unit
@@ -132,19 +132,33 @@ class FSDP:
         if maxn != self._grad_pool[0].numel():
             self._grad_pool = [torch.empty(maxn, device=self.device, dtype=torch.bfloat16) for _ in range(len(self._grad_pool))]
         self._grad_shard = torch.empty(max(u.chunk for u in self.units), device=self.device, dtype=torch.bfloat16) if self.world > 1 else None
-        for u in self.units:
-            u.init_adam()
+        full = self.strategy == ShardingStrategy.FULL_SHARD and self.world > 1
+        self._shards: Dict[str, torch.Tensor] = {}        # FULL_SHARD: this rank's bf16 shard of every unit
+        if full:
+            # unit by unit: optimizer state and bf16 shard from the initial values, then the unsharded buffer goes away
+            from .symm import _unit_params
+            anchors = _unit_params(model)
+            for u in self.units:
+                u.init_adam()
+                self._shards[u.name] = u.shard_slice(u.full).clone()
+                p = anchors.get(u.name)
+                if p is not None:
+                    p.data = torch.empty(0, device=self.device, dtype=torch.bfloat16)     # the parameter object only anchors the autograd node
+                u.full = None
+        else:
+            for u in self.units:
+                u.init_adam()
         # install engine owners
         for o in model.owners():
             eo = _EngineOwner(self, o.unit, o)
             self._swap_owner(model, o, eo)
+        self._prefetch_distance = max(1, int(os.environ.get("FT_FSDP_PREFETCH", "1")))   # units gathered ahead of the compute stream
         self._fused = None
         self.sharded = None                       # ShardedParams: FULL_SHARD with peer-memory gathers
         self._nccl_shard: Dict[str, torch.Tensor] = {}   # FULL_SHARD over NCCL: this rank's bf16 shard of every unit
         self._nccl_full: Dict[str, torch.Tensor] = {}
         self._order = list(self.units)
         self._index = {u.name: i for i, u in enumerate(self._order)}
-        full = self.strategy == ShardingStrategy.FULL_SHARD and self.world > 1
         if self.world > 1 and self.comm == "fused":
             from .symm import FusedShardedAdamW
             try:
@@ -159,14 +173,7 @@ class FSDP:
                 self._fused = self.sharded = None
         if full and self.sharded is None:
             # library transport: keep the shard, gather a unit with all_gather_into_tensor when it is needed, drop it after use
-            with torch.no_grad():
-                for u in self.units:
-                    self._nccl_shard[u.name] = u.shard_slice(u.full).clone()
-                    u.full = None
-        if full:
-            from .symm import _unit_params
-            for p in _unit_params(model).values():
-                p.data = torch.empty(0, device=self.device, dtype=torch.bfloat16)     # the parameter object only anchors the autograd node
+            self._nccl_shard = self._shards
         if self.world == 1:
             self.comm = "none"
 
@@ -183,9 +190,10 @@ class FSDP:
             # fully sharded: the unit sits (or is arriving) in a gather slot; start the gather of the unit the pass needs next
             views = self.sharded.acquire(unit, reverse=backward)
             i = self._index[unit.name]
-            nxt = i - 1 if backward else i + 1
-            if (backward and nxt >= 1) or (not backward and nxt < len(self._order)):      # the embedding's backward reads no parameters
-                self.sharded.prefetch(self._order[nxt], reverse=backward)
+            for d in range(1, self._prefetch_distance + 1):
+                nxt = i - d if backward else i + d
+                if (backward and nxt >= 1) or (not backward and nxt < len(self._order)):  # the embedding's backward reads no parameters
+                    self.sharded.prefetch(self._order[nxt], reverse=backward)
             return views
         if self._nccl_shard:
             full = self._nccl_full.get(unit.name)

@@ -97,11 +97,7 @@ class ShardedParams:
         self.arrive = SymmetricBuffer(self.nslots * self.max_pieces, torch.int32, dev, group, zero=True)
         self.free = SymmetricBuffer(self.nslots * 8, torch.int32, dev, group, zero=True)
         # this rank's shard of every unit, in ordinary device memory (only the owner reads it)
-        self.shard: Dict[str, torch.Tensor] = {}
-        with torch.no_grad():
-            for u in units:
-                self.shard[u.name] = u.shard_slice(u.full).clone()
-                u.full = None
+        self.shard: Dict[str, torch.Tensor] = engine._shards
         self.gather_no = [0] * self.nslots
         self.resident: List[Optional[str]] = [None] * self.nslots
         self.where: Dict[str, int] = {}
@@ -112,6 +108,8 @@ class ShardedParams:
         self.push_done: Dict[str, torch.cuda.Event] = {}       # last push that read a unit's shard (the optimizer waits for it)
         self.shard_ready: Dict[str, torch.cuda.Event] = {}     # last optimizer update of a unit's shard (the next push waits for it)
         self.max_ctas = int(os.environ.get("FT_FSDP_PUSH_CTAS", "0"))
+        # "dma": the shards travel by copy engine (cudaMemcpyAsync to the peer mapping); "sm": the push kernel (plain peer stores, per-piece arrival)
+        self.mode = os.environ.get("FT_FSDP_PUSH", "dma")
         self.gathers = 0                                         # pushes issued (a resident unit needs none)
         torch.cuda.synchronize(dev)
         dist.barrier(group)
@@ -146,9 +144,19 @@ class ShardedParams:
         with torch.cuda.stream(self.stream):
             if ready is not None:
                 self.stream.wait_event(ready)
-            _lib.call("ft_fsdp_push_shard", src, self._ptrs(self.slot_buf, s * self.maxn), self._ptrs(self.arrive, s * self.max_pieces),
-                      ctypes.c_void_p(self.free.ptrs[self.rank] + (s * 8) * 4), self.rank, self.world, ctypes.c_int64(unit.chunk * 2),
-                      ctypes.c_int64(pb), n, int(reverse), self.max_ctas, _lib.S())
+            free_local = ctypes.c_void_p(self.free.ptrs[self.rank] + (s * 8) * 4)
+            if self.mode == "sm":
+                _lib.call("ft_fsdp_push_shard", src, self._ptrs(self.slot_buf, s * self.maxn), self._ptrs(self.arrive, s * self.max_pieces),
+                          free_local, self.rank, self.world, ctypes.c_int64(unit.chunk * 2), ctypes.c_int64(pb), n, int(reverse), self.max_ctas,
+                          _lib.S())
+            else:
+                # copy engines: no SM is taken from the GEMMs while the shard travels; arrival is marked per source rank
+                _lib.call("ft_fsdp_wait_free", free_local, self.world, n_prev, _lib.S())
+                for d in range(self.world):
+                    q = (self.rank + 1 + d) % self.world            # peers first, rotated so that the ranks address distinct receivers
+                    dst = self.slot_buf.ptrs[q] + (s * self.maxn + self.rank * unit.chunk) * 2
+                    _lib.call("ft_memcpy_d2d_async", ctypes.c_void_p(dst), src, ctypes.c_int64(unit.chunk * 2), _lib.S())
+                    _lib.call("ft_fsdp_signal", ctypes.c_void_p(self.arrive.ptrs[q] + (s * self.max_pieces + self.rank * ppc) * 4), ppc, n, _lib.S())
             ev = torch.cuda.Event()
             ev.record(self.stream)
             self.push_done[unit.name] = ev
