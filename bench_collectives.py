@@ -82,7 +82,7 @@ def main() -> int:
                 iters = 50 if size <= (1 << 20) else (20 if size <= (64 << 20) else 5)
                 buf.tensor[:n].copy_(src[:n])
                 if op == "all_reduce":
-                    form = "one-shot" if size <= a.oneshot_bytes else ("two-shot" + ("" if (a.no_nvls or dtype != torch.bfloat16 or not buf.multicast_ptr) else " nvls"))
+                    form = "one-shot" if size <= a.oneshot_bytes else ("two-shot" + ("" if (a.no_nvls or not buf.multicast_ptr) else " nvls"))
                     if size <= a.oneshot_bytes:
                         ours = lambda: comm.all_reduce_small(buf, out, n)
                     else:
@@ -90,8 +90,8 @@ def main() -> int:
                     lib = lambda: dist.all_reduce(lib_in[:n])
                     factor = 2.0 * (world - 1) / world
                 elif op == "reduce_scatter":
-                    form = "pull"
-                    ours = lambda: comm.reduce_scatter(buf, out[:chunk], chunk)
+                    form = "pull" if (a.no_nvls or not buf.multicast_ptr) else "nvls"
+                    ours = lambda: comm.reduce_scatter(buf, out[:chunk], chunk, use_nvls=not a.no_nvls)
                     lib = lambda: dist.reduce_scatter_tensor(lib_out[:chunk], lib_in[:n])
                     factor = (world - 1) / world
                 else:

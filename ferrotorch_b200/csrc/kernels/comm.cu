@@ -172,32 +172,67 @@ __global__ void __launch_bounds__(512) allreduce_2shot_kernel(PeerPtrs bufs, Com
   comm_end(s, status);
 }
 
-// NVLS variant (bf16): the switch reduces (multimem.ld_reduce) and broadcasts (multimem.st). `mc` is this rank's
-// mapping of the multicast address of the same symmetric buffer. Accumulation is f32 inside the switch.
-__global__ void __launch_bounds__(512) allreduce_nvls_bf16_kernel(__nv_bfloat16* mc, __nv_bfloat16* local, CommSync s, size_t n,
-                                                                  float scale, uint32_t* status) {
+// NVLS (NVSwitch multicast) helpers: one multimem.ld_reduce returns the sum over every rank's copy of 16 bytes (reduced inside the switch, f32
+// accumulation), one multimem.st writes 16 bytes into every rank's copy. `mc` is this rank's mapping of the multicast address of the buffer.
+template <typename T> struct Nvls;
+template <> struct Nvls<__nv_bfloat16> {
+  static FT_DEVICE uint4 ld_reduce(const void* p) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+  }
+  static FT_DEVICE uint4 scale(uint4 v, float s) {
+    uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&r[e]));
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f.x * s, f.y * s);
+      r[e] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(r[0], r[1], r[2], r[3]);
+  }
+};
+template <> struct Nvls<float> {
+  static FT_DEVICE uint4 ld_reduce(const void* p) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+  }
+  static FT_DEVICE uint4 scale(uint4 v, float s) {
+    return make_uint4(__float_as_uint(__uint_as_float(v.x) * s), __float_as_uint(__uint_as_float(v.y) * s), __float_as_uint(__uint_as_float(v.z) * s),
+                      __float_as_uint(__uint_as_float(v.w) * s));
+  }
+};
+FT_DEVICE void multimem_st_v4(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// NVLS all-reduce, in place: every rank reduces its 1/N slice inside the switch and broadcasts the result through the switch.
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_nvls_kernel(T* mc, CommSync s, size_t n, float scale, uint32_t* status) {
   if (!comm_begin(s, status)) { comm_abort(s); return; }
-  const size_t nvec = n / 8;
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = n / V;
   const size_t per = (nvec + s.world - 1) / s.world;
   const size_t lo = per * s.rank, hi = min(nvec, lo + per);
   for (size_t i = lo + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < hi; i += (size_t)gridDim.x * blockDim.x) {
-    uint32_t r0, r1, r2, r3;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "l"(mc + i * 8)
-                 : "memory");
-    if (scale != 1.f) {
-      uint32_t r[4] = {r0, r1, r2, r3};
-#pragma unroll
-      for (int e = 0; e < 4; e++) {
-        float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&r[e]));
-        __nv_bfloat162 h = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-        r[e] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      r0 = r[0]; r1 = r[1]; r2 = r[2]; r3 = r[3];
-    }
-    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc + i * 8), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-                 : "memory");
+    uint4 r = Nvls<T>::ld_reduce(mc + i * V);
+    if (scale != 1.f) r = Nvls<T>::scale(r, scale);
+    multimem_st_v4(mc + i * V, r);
+  }
+  comm_end(s, status);
+}
+
+// NVLS reduce-scatter: out_local[i] = scale * (sum over ranks of buf_q[rank * chunk + i]), one in-switch reduction per 16 bytes.
+template <typename T>
+__global__ void __launch_bounds__(512) reduce_scatter_nvls_kernel(const T* mc, T* __restrict__ out, CommSync s, size_t chunk, float scale, uint32_t* status) {
+  if (!comm_begin(s, status)) { comm_abort(s); return; }
+  constexpr int V = Vec16<T>::N;
+  const size_t nvec = chunk / V, base = chunk * s.rank;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    uint4 r = Nvls<T>::ld_reduce(mc + base + i * V);
+    if (scale != 1.f) r = Nvls<T>::scale(r, scale);
+    *reinterpret_cast<uint4*>(out + i * V) = r;
   }
   comm_end(s, status);
 }
@@ -240,15 +275,21 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerPtrs bufs, T* _
   constexpr int V = Vec16<T>::N;
   const size_t nvec = chunk / V, base = chunk * s.rank;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    uint4 raw[MAX_RANKS];                                  // every peer's 16 bytes are requested before any is used: the NVLink loads overlap
+#pragma unroll
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) raw[q] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(bufs.p[q]) + base + i * V);
     float acc[V];
 #pragma unroll
     for (int e = 0; e < V; e++) acc[e] = 0.f;
-    for (int q = 0; q < s.world; q++) {
-      float f[V];
-      Vec16<T>::load(reinterpret_cast<const T*>(bufs.p[q]) + base + i * V, f);
 #pragma unroll
-      for (int e = 0; e < V; e++) acc[e] += f[e];
-    }
+    for (int q = 0; q < MAX_RANKS; q++)
+      if (q < s.world) {
+        float f[V];
+        Vec16<T>::load(reinterpret_cast<const T*>(&raw[q]), f);
+#pragma unroll
+        for (int e = 0; e < V; e++) acc[e] += f[e];          // fixed rank order
+      }
 #pragma unroll
     for (int e = 0; e < V; e++) acc[e] *= scale;
     Vec16<T>::store(out + i * V, acc);
@@ -505,7 +546,9 @@ FT_EXPORT int ft_comm_allreduce(void* const* buf_ptrs, void* const* flag_ptrs, u
   const int V = dtype == 0 ? 8 : 4;
   const int grid = comm_grid((size_t)n / V / world + 1, max_ctas > 0 ? max_ctas : 64);
   if (mc_ptr && dtype == 0 && (n % (8 * (int64_t)world)) == 0)
-    allreduce_nvls_bf16_kernel<<<grid, 512, 0, st>>>((__nv_bfloat16*)mc_ptr, (__nv_bfloat16*)buf_ptrs[rank], s, (size_t)n, scale, status);
+    allreduce_nvls_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((__nv_bfloat16*)mc_ptr, s, (size_t)n, scale, status);
+  else if (mc_ptr && dtype == 1 && (n % (4 * (int64_t)world)) == 0)
+    allreduce_nvls_kernel<float><<<grid, 512, 0, st>>>((float*)mc_ptr, s, (size_t)n, scale, status);
   else if (dtype == 0)
     allreduce_2shot_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, s, (size_t)n, scale, status);
   else
@@ -544,6 +587,21 @@ FT_EXPORT int ft_comm_reduce_scatter(void* const* buf_ptrs, void* out, void* con
   const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
   if (dtype == 0) reduce_scatter_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(b, (__nv_bfloat16*)out, s, (size_t)chunk, scale, ft_status_ptr());
   else reduce_scatter_kernel<float><<<grid, 512, 0, st>>>(b, (float*)out, s, (size_t)chunk, scale, ft_status_ptr());
+  return (int)cudaGetLastError();
+}
+
+// The same through the switch: mc_ptr is the multicast mapping of the buffer the ranks exposed (NVLS). One multimem.ld_reduce per 16 bytes replaces
+// `world` peer loads, so the ingress of a rank is one slice instead of `world - 1`.
+FT_EXPORT int ft_comm_reduce_scatter_nvls(void* mc_ptr, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                                          int64_t chunk, int dtype, float scale, int max_ctas, cudaStream_t st) {
+  CommSync s;
+  int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 3);
+  if (r) return r;
+  const int V = dtype == 0 ? 8 : 4;
+  if (mc_ptr == nullptr || chunk <= 0 || chunk % V) return FT_ERR_ARG;
+  const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
+  if (dtype == 0) reduce_scatter_nvls_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((const __nv_bfloat16*)mc_ptr, (__nv_bfloat16*)out, s, (size_t)chunk, scale, ft_status_ptr());
+  else reduce_scatter_nvls_kernel<float><<<grid, 512, 0, st>>>((const float*)mc_ptr, (float*)out, s, (size_t)chunk, scale, ft_status_ptr());
   return (int)cudaGetLastError();
 }
 

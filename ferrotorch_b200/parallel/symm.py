@@ -163,8 +163,17 @@ class SymmComm:
                   seq, numel, dt, float(scale), 0, seq_dev, _lib.S())
         return out
 
-    def reduce_scatter(self, buf: SymmetricBuffer, out: torch.Tensor, chunk: int, elem_offset: int = 0, scale: float = 1.0) -> torch.Tensor:
+    def reduce_scatter(self, buf: SymmetricBuffer, out: torch.Tensor, chunk: int, elem_offset: int = 0, scale: float = 1.0,
+                       use_nvls: bool = True) -> torch.Tensor:
+        """``out[chunk]`` = ``scale`` x the sum over ranks of their ``buf[rank*chunk:(rank+1)*chunk]``. With a multicast mapping the sum is
+        formed inside the switch (one ``multimem.ld_reduce`` per 16 bytes); otherwise the slice is pulled from every peer in fixed rank order
+        (bit-identical on every run)."""
         dt = 0 if buf.tensor.dtype == torch.bfloat16 else 1
+        mc = buf.mc(elem_offset) if use_nvls else 0
+        if mc:
+            _lib.call("ft_comm_reduce_scatter_nvls", ctypes.c_void_p(mc), out, self.flag_ptrs, self.counter, self.rank, self.world, self._next(), chunk, dt,
+                      float(scale), 0, _lib.S())
+            return out
         _lib.call("ft_comm_reduce_scatter", buf.ptr_array(elem_offset), out, self.flag_ptrs, self.counter, self.rank, self.world,
                   self._next(), chunk, dt, float(scale), 0, _lib.S())
         return out

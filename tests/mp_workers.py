@@ -52,9 +52,11 @@ def case_collectives():
                 buf.tensor.copy_(x)
                 torch.cuda.synchronize(); dist.barrier()
                 rs = torch.empty(chunk, device=dev, dtype=dtype)
-                comm.reduce_scatter(buf, rs, chunk)
-                comm.check()
-                assert (rs.float() - ref[rank * chunk:(rank + 1) * chunk]).abs().max().item() <= tol * world
+                for nvls in (False, True):                      # peer pulls in fixed rank order / in-switch reduction
+                    rs.zero_()
+                    comm.reduce_scatter(buf, rs, chunk, use_nvls=nvls)
+                    comm.check()
+                    assert (rs.float() - ref[rank * chunk:(rank + 1) * chunk]).abs().max().item() <= tol * world, (str(dtype), n, nvls)
                 comm.all_gather(buf, rs, chunk)
                 comm.check()
                 assert (buf.tensor.float() - ref).abs().max().item() <= tol * world
