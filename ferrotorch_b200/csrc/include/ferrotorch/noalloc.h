@@ -30,6 +30,8 @@ extern "C" {
 //  * d must be a multiple of 8 and at most ft_rmsnorm_bwd_noalloc_max_d() (8192); a larger d is rejected
 //    with FT_ERR_TOO_LARGE (-4) and a message on stderr, before anything is launched.
 //  * The call performs no cudaMalloc, no cudaFree and calls no allocating library routine.
+//  * `stream` must be a stream of the device that is current in the calling thread (the built-in array that is used is that device's);
+//    a stream of another device is refused with FT_ERR_ARG (-1).
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
 //    device current) and caches it; make that first call outside any stream capture.
 //  * All calls on a device share the one array. Its contents after a call are that call's partial sums;

@@ -130,6 +130,32 @@ __global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids, const __nv
   }
 }
 
+// Deterministic form: the token rows are visited grouped by id (the caller sorted the ids stably and passes the permutation and the segment
+// bounds), one CTA per distinct id, each output element summed in f32 in token order by one thread. No atomics: the same bits on every run.
+template <typename AccT>
+__global__ void __launch_bounds__(128) embedding_bwd_sorted_kernel(const int64_t* __restrict__ uniq_ids, const int64_t* __restrict__ seg_end,
+                                                                   const int64_t* __restrict__ perm, const __nv_bfloat16* __restrict__ dout,
+                                                                   AccT* __restrict__ dtable, int n_uniq, int d, int64_t vocab) {
+  for (int u = blockIdx.x; u < n_uniq; u += gridDim.x) {
+    const int64_t id = uniq_ids[u];
+    if (id < 0 || id >= vocab) continue;
+    const int64_t k0 = u == 0 ? 0 : seg_end[u - 1], k1 = seg_end[u];
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[e] = (float)dtable[(size_t)id * d + c + e];        // running sum already in the table
+      for (int64_t k = k0; k < k1; k++) {
+        float f[8];
+        bf16x8_to_float(*reinterpret_cast<const bf16x8*>(dout + (size_t)perm[k] * d + c), f);
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[e] += f[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; e++) dtable[(size_t)id * d + c + e] = (AccT)acc[e];
+    }
+  }
+}
+
 // out = a + b (bf16, 128-bit vectors, n % 8 == 0)
 __global__ void add_bf16_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, size_t nvec) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
@@ -189,6 +215,19 @@ FT_EXPORT int ft_embedding_bwd(const int64_t* ids, const void* dout, void* dtabl
     embedding_bwd_kernel<float><<<grid, 256, 0, st>>>(ids, (const __nv_bfloat16*)dout, (float*)dtable, tokens, d, vocab);
   else
     embedding_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(ids, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dtable, tokens, d, vocab);
+  return (int)cudaGetLastError();
+}
+
+// uniq_ids [n_uniq]: the distinct ids in ascending order; seg_end [n_uniq]: inclusive prefix sums of their counts; perm [tokens]: token indices
+// sorted stably by id (so perm[seg_end[u-1] .. seg_end[u]) are the tokens of uniq_ids[u] in their original order). d % 8 == 0.
+FT_EXPORT int ft_embedding_bwd_sorted(const int64_t* uniq_ids, const int64_t* seg_end, const int64_t* perm, const void* dout, void* dtable, int n_uniq,
+                                      int d, int64_t vocab, int acc_f32, cudaStream_t st) {
+  if (d % 8 || n_uniq <= 0) return FT_ERR_ARG;
+  const int grid = n_uniq < 148 * 16 ? n_uniq : 148 * 16;
+  if (acc_f32)
+    embedding_bwd_sorted_kernel<float><<<grid, 128, 0, st>>>(uniq_ids, seg_end, perm, (const __nv_bfloat16*)dout, (float*)dtable, n_uniq, d, vocab);
+  else
+    embedding_bwd_sorted_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(uniq_ids, seg_end, perm, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dtable, n_uniq, d, vocab);
   return (int)cudaGetLastError();
 }
 

@@ -366,6 +366,13 @@ FT_EXPORT int ft_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* d
                     "use ft_rmsnorm_bwd with caller-provided scratch\n", d, NOALLOC_MAX_D);
     return FT_ERR_TOO_LARGE;
   }
+  // the scratch array that is used is the current device's: a stream of another device would run the kernels there, on an address of this one
+  if (st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread) {
+    int cur = -1, sdev = -1;
+    FT_CUDA_TRY(cudaGetDevice(&cur));
+    if (cudaStreamGetDevice(st, &sdev) == cudaSuccess && sdev != cur) return FT_ERR_ARG;
+    cudaGetLastError();
+  }
   float* scratch = nullptr;
   int r = noalloc_scratch(&scratch);
   if (r) return r;

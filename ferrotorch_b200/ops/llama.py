@@ -175,11 +175,21 @@ def embedding_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return table[flat].reshape(*ids.shape, table.shape[1])
 
 
-def embedding_bwd(ids: torch.Tensor, dout2: torch.Tensor, dtable: torch.Tensor) -> torch.Tensor:
-    """``dtable[ids] += dout`` (dtable bf16 or f32, already zeroed or holding a running sum)."""
+def embedding_bwd(ids: torch.Tensor, dout2: torch.Tensor, dtable: torch.Tensor, deterministic: bool = True) -> torch.Tensor:
+    """``dtable[ids] += dout`` (dtable bf16 or f32, already zeroed or holding a running sum). The default groups the token rows by id (stable
+    sort) and sums each table row in token order in f32 without atomics, so repeated runs give identical bits; ``deterministic=False`` is the
+    atomic scatter (a little faster, order of the additions left to the hardware)."""
     flat = ids.reshape(-1).contiguous()
     if dtable.is_cuda and dout2.dtype == torch.bfloat16:
-        _lib.call("ft_embedding_bwd", flat, dout2, dtable, flat.numel(), dtable.shape[1], dtable.shape[0],
+        d = dtable.shape[1]
+        if deterministic and d % 8 == 0:
+            sorted_ids, perm = torch.sort(flat, stable=True)
+            uniq, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
+            seg_end = torch.cumsum(counts, 0)
+            _lib.call("ft_embedding_bwd_sorted", uniq, seg_end, perm, dout2, dtable, uniq.numel(), d, dtable.shape[0],
+                      int(dtable.dtype == torch.float32), _lib.S())
+            return dtable
+        _lib.call("ft_embedding_bwd", flat, dout2, dtable, flat.numel(), d, dtable.shape[0],
                   int(dtable.dtype == torch.float32), _lib.S())
         return dtable
     dtable.index_add_(0, flat, dout2.to(dtable.dtype))

@@ -37,10 +37,13 @@ class SymmetricBuffer:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         name = self.group.group_name
-        try:
-            sm.enable_symm_mem_for_group(name)
-        except Exception:
-            pass
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")          # newer torch versions no longer need the call and say so for every buffer
+            try:
+                sm.enable_symm_mem_for_group(name)
+            except Exception:
+                pass
         self.tensor = sm.empty(numel, dtype=dtype, device=device)
         if zero:
             self.tensor.zero_()

@@ -48,7 +48,6 @@ def test_resnet_block_uses_the_kernel_and_matches_library_path():
     assert (y.float() - ref.float()).abs().max() < 0.1
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FT_STAGED") != "1", reason="shifted-GEMM weight gradient is opt-in until timed on hardware (FT_STAGED=1)")
 @pytest.mark.parametrize("N,C,Co,H,W", [(4, 64, 64, 56, 56), (8, 128, 256, 14, 14), (2, 64, 128, 7, 9)])
 def test_conv3x3_weight_gradient_as_shifted_gemms_on_device(N, C, Co, H, W):
     from ferrotorch_b200 import _lib, ops
@@ -61,7 +60,6 @@ def test_conv3x3_weight_gradient_as_shifted_gemms_on_device(N, C, Co, H, W):
     assert _lib.read_status() == 0
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FT_STAGED") != "1", reason="fused weight-gradient GEMM is opt-in until run on hardware (FT_STAGED=1)")
 @pytest.mark.parametrize("N,C,Co,H,W", [(4, 64, 64, 56, 56), (8, 128, 256, 14, 14), (2, 64, 128, 7, 9), (3, 256, 72, 5, 5)])
 def test_conv3x3_weight_gradient_fused_gemm_on_device(N, C, Co, H, W):
     from ferrotorch_b200 import _lib, ops
@@ -75,7 +73,6 @@ def test_conv3x3_weight_gradient_fused_gemm_on_device(N, C, Co, H, W):
     assert _lib.read_status() == 0
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FT_STAGED") != "1", reason="row-GEMM convolution is opt-in until run on hardware (FT_STAGED=1)")
 @pytest.mark.parametrize("stride", [1, 2])
 @pytest.mark.parametrize("N,C,Co,H,W", [(4, 64, 64, 56, 56), (8, 128, 256, 14, 14), (2, 256, 128, 6, 10)])
 def test_conv3x3_rows_forward_and_gradients_on_device(N, C, Co, H, W, stride):

@@ -1,5 +1,6 @@
 """Run-twice bit-comparison of the hot kernels: a data race or an unordered reduction shows up as differing bits (the stand-in for a race detector on this
-hardware). Atomics-based kernels (index_add, scatter_add, embedding backward) are excluded by design and listed here for that reason."""
+hardware). Atomics-based kernels (index_add, scatter_add, the atomic form of the embedding backward) are excluded by design and listed here for that
+reason; the default embedding backward sorts by id and sums in token order, and is checked."""
 import pytest
 import torch
 
@@ -54,3 +55,7 @@ def test_gemm_attention_norm_conv_are_bit_stable():
     logits = torch.randn(512, 32000, device="cuda", generator=g).bfloat16()
     tgt = torch.randint(0, 32000, (512,), device="cuda", generator=g)
     _twice(lambda: ops.cross_entropy_fwd_bwd(logits.clone(), tgt), "cross entropy")
+    # embedding backward with many repeated ids (every id about 60 times): bf16 accumulation in an order left to the hardware would differ run to run
+    ids = torch.randint(0, 70, (4096,), device="cuda", generator=g)
+    dout = torch.randn(4096, 512, device="cuda", generator=g).bfloat16()
+    _twice(lambda: ops.embedding_bwd(ids, dout, torch.zeros(70, 512, device="cuda", dtype=torch.bfloat16)), "embedding backward")

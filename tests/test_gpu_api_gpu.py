@@ -7,7 +7,7 @@ import torch
 
 from ferrotorch_b200 import gpu as G
 
-pytestmark = [pytest.mark.gpu, pytest.mark.skipif(os.environ.get("FT_STAGED") != "1", reason="device path of the buffer-level API: not yet run on a GPU (FT_STAGED=1 runs it)")]
+pytestmark = [pytest.mark.gpu]
 
 
 def test_kernel_backed_wrappers_match_f32_references():
@@ -36,7 +36,8 @@ def test_kernel_backed_wrappers_match_f32_references():
         G.gpu_add(f.cpu(), f.cpu())
     d = G.gpu_dropout(f, 1 << 31, 2.0, 3)
     assert torch.equal(d, G.gpu_dropout(f, 1 << 31, 2.0, 3)) and abs(float((d != 0).float().mean()) - 0.5) < 0.02
-    assert G.get_cuda_device(0).sm_count() > 0 and G.cached_bytes() >= 0
+    sms = G.get_cuda_device(0).sm_count
+    assert int(sms() if callable(sms) else sms) > 0 and G.cached_bytes() >= 0
 
 
 def test_explicit_capture_replays_the_recorded_work():

@@ -13,27 +13,77 @@ def _mk(cfg, device):
 
 
 def test_fused_layer_matches_reference_forward_backward():
+    """The fused bf16 path against the plain PyTorch evaluation of the same model in f32 (weights = the bf16 values, exactly representable)."""
     cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=1024)
     m = _mk(cfg, "cuda")
     ref = _mk(cfg, "cpu")
     with torch.no_grad():
         for ug, uc in zip(m.units(), ref.units()):
             uc.full.copy_(ug.full.cpu())
+    # f32 oracle: every flat buffer of the CPU model becomes an f32 leaf holding the same values
+    for mod in ref.modules():
+        for attr, unit_attr in (("flat", "unit"), ("embed_flat", "embed_unit"), ("norm_flat", "norm_unit"), ("head_flat", "head_unit")):
+            if hasattr(mod, attr) and hasattr(mod, unit_attr):
+                p32 = torch.nn.Parameter(getattr(mod, attr).detach().float())
+                setattr(mod, attr, p32)
+                getattr(mod, unit_attr).full = p32.data
     ids = torch.randint(0, cfg.vocab_size, (2, 128), device="cuda")
     labels = torch.randint(0, cfg.vocab_size, (2, 128), device="cuda")
     loss = m(ids, labels=labels)
     loss.backward()
     torch.cuda.synchronize()
     rl = ref(ids.cpu(), labels=labels.cpu())
+    assert rl.dtype == torch.float32
     rl.backward()
-    assert abs(loss.item() - rl.item()) < 3e-2 * max(1.0, abs(rl.item()))
-    # gradients of the first and last layer, and the head
+    assert abs(loss.item() - rl.item()) < 2e-2 * max(1.0, abs(rl.item()))
+    # gradients of the first and last layer, and the head (bf16 kernels against the f32 gradient)
     for lg, lc in ((m.model.layers[0], ref.model.layers[0]), (m.model.layers[-1], ref.model.layers[-1])):
         g, r = lg.unit.grad.float().cpu(), lc.flat.grad.float()
         rel = (g - r).norm() / (r.norm() + 1e-12)
-        assert rel.item() < 6e-2, rel.item()
+        assert rel.item() < 4e-2, rel.item()
     gh, rh = m.head_unit.grad.float().cpu(), ref.head_flat.grad.float()
-    assert ((gh - rh).norm() / rh.norm()).item() < 6e-2
+    assert ((gh - rh).norm() / rh.norm()).item() < 4e-2
+
+
+def test_engine_trajectory_matches_torch_adamw_on_an_f32_copy():
+    """Twenty steps of the single-GPU engine over four cycled batches against the same model evaluated by plain PyTorch in f32 and stepped by
+    torch.optim.AdamW: the loss curves stay together and the final parameters agree to bf16 resolution of the updates."""
+    cfg = LlamaConfig.tiny(layers=2, hidden=256, heads=2, kv_heads=1, ffn=512, vocab=512)
+    hp = dict(lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m = _mk(cfg, "cuda")
+    ref = _mk(cfg, "cpu")
+    with torch.no_grad():
+        for ug, uc in zip(m.units(), ref.units()):
+            uc.full.copy_(ug.full.cpu())
+    leaves = []
+    for mod in ref.modules():
+        for attr, unit_attr in (("flat", "unit"), ("embed_flat", "embed_unit"), ("norm_flat", "norm_unit"), ("head_flat", "head_unit")):
+            if hasattr(mod, attr) and hasattr(mod, unit_attr):
+                p32 = torch.nn.Parameter(getattr(mod, attr).detach().float())
+                setattr(mod, attr, p32)
+                getattr(mod, unit_attr).full = p32.data
+                leaves.append(p32)
+    eng = FSDP(m, AdamWConfig(**hp))
+    opt = torch.optim.AdamW(leaves, **hp)
+    g = torch.Generator().manual_seed(3)
+    batches = [torch.randint(0, cfg.vocab_size, (2, 129), generator=g) for _ in range(4)]
+    ours, theirs = [], []
+    for i in range(20):
+        t = batches[i % 4]
+        ours.append(eng.train_step(t[:, :-1].cuda(), t[:, 1:].cuda()).item())
+        opt.zero_grad()
+        l = ref(t[:, :-1], labels=t[:, 1:])
+        l.backward()
+        opt.step()
+        theirs.append(l.item())
+    eng.synchronize()
+    torch.cuda.synchronize()
+    assert all(abs(a - b) < 0.06 * max(1.0, b) for a, b in zip(ours, theirs)), (ours, theirs)
+    assert ours[-1] < ours[0] and theirs[-1] < theirs[0]
+    for u, uc in zip(m.units(), ref.units()):
+        a, b = u.master[: u.numel].cpu(), uc.full[: u.numel]
+        rel = ((a - b).norm() / b.norm()).item()
+        assert rel < 0.1, (u.name, rel)      # Adam normalises the step: where a gradient is near zero, bf16 noise decides its sign
 
 
 def test_engine_loss_decreases():

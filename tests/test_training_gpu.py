@@ -53,7 +53,6 @@ def test_resnet18_step_channels_last_autocast():
     assert _lib.read_status() == 0
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FT_STAGED") != "1", reason="compute copies are opt-in until timed on hardware (FT_STAGED=1)")
 def test_resnet50_compute_copies_follow_the_cast_per_step_run():
     """The same four steps with and without optimizer-maintained bf16 weight copies: the losses stay together (the weight gradients differ only
     by the bf16 rounding the copies avoid), the copies equal the rounded masters after every step, and fewer kernels are launched by torch."""
@@ -69,7 +68,7 @@ def test_resnet50_compute_copies_follow_the_cast_per_step_run():
         m = resnet50(num_classes=10).to(dev).to(memory_format=torch.channels_last)
         if copies:
             assert nn.attach_compute_copies(m) > 50
-        opt = optim.Sgd(m.parameters(), lr=0.02, momentum=0.9, weight_decay=1e-4)
+        opt = optim.Sgd(m.parameters(), lr=0.002, momentum=0.9, weight_decay=1e-4)      # small enough that four steps do not diverge
         out = []
         for _ in range(4):
             opt.zero_grad()

@@ -55,6 +55,26 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert rel.item() < 2e-2, rel.item()
 
 
+def test_noalloc_accumulates_into_f32_and_bf16_outputs():
+    """``accumulate = 1`` adds the weight gradient to what the two optional outputs already hold (the f32 one exactly, the bf16 one rounded)."""
+    fn = _sym()
+    rows, d = 300, 2048
+    x, w, dy, rstd, _ = _case(rows, d, 21, False)
+    _, ref_dw = ops.rmsnorm_bwd(x, w, dy, rstd)
+    dx = torch.empty_like(x)
+    base32 = torch.randn(d, device="cuda")
+    base16 = torch.randn(d, device="cuda").to(torch.bfloat16)
+    dw32, dw16 = base32.clone(), base16.clone()
+    st = torch.cuda.current_stream().cuda_stream
+    assert fn(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), dw16.data_ptr(), dw32.data_ptr(), 1, rows, d, st) == 0
+    plain32 = torch.empty(d, device="cuda")
+    assert fn(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), None, plain32.data_ptr(), 0, rows, d, st) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(dw32, base32 + plain32, rtol=1e-5, atol=1e-4)
+    assert ((plain32 - ref_dw.float()).norm() / ref_dw.float().norm()).item() < 2e-2
+    assert torch.allclose(dw16.float(), base16.float() + plain32, rtol=2e-2, atol=5e-2)
+
+
 def test_noalloc_rejects_oversize():
     fn = _sym()
     max_d = _lib.kernels().ft_rmsnorm_bwd_noalloc_max_d()
