@@ -6,9 +6,10 @@ Two shared objects are produced under ``ferrotorch_b200/_C``:
   ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a``), CUDA runtime
   linked statically, no link-time dependency on the driver library, so the
   library imports on a machine without a GPU.
-* ``libft_runtime.so``  - the host runtime in ``csrc/runtime/*.cpp`` (TCP
-  backend, collectives, CPU tensor/autograd core, data loader, serializers,
-  JIT IR ...), plain C++20.
+* ``libft_runtime.so``  - the host runtime in ``csrc/runtime/*.cpp``: the
+  distributed backends and collectives (``dist_runtime.cpp``), the native CPU
+  tensor / autograd core with its SGD (``core.cpp``), the data-loader helpers
+  (``loader.cpp``) and the host NMS sweep (``vision_ops.cpp``), plain C++20.
 
 Objects are rebuilt only when the source (or a header) is newer than the object.
 """

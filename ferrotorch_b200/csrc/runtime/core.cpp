@@ -1,0 +1,570 @@
+// Native CPU tensor + reverse-mode autograd core (f32), the host-side counterpart of the device kernels.
+//
+//   ft::TensorImpl   shape / strides / offset over shared storage, requires_grad, grad, grad_fn, hooks, version counter
+//   ft::Node         one differentiable operation: the inputs it has to send gradients to and its backward rule
+//   ft::backward     graph collection (breadth first from the root), dependency counts, Kahn ordering, reverse sweep; gradient contributions
+//                    are kept per consuming edge and summed in edge order when a node becomes ready, so the serial engine and the parallel one
+//                    (worker threads over the ready queue) give identical bits; tensor hooks (may rewrite a gradient) run before accumulation
+//                    into a leaf, post-accumulate hooks after it (what DDP uses to launch a bucket's all-reduce)
+//   operations       add / sub / mul (row-broadcast of a vector), scale, matmul, transpose, relu, tanh, sigmoid, sum, mean, linear,
+//                    cross-entropy on logits, mse
+//   ft::Sgd          momentum / dampening / nesterov / weight decay, same update rule as the device kernel
+//
+// Everything is exported through a small C ABI (opaque handles) for the Python binding in ferrotorch_b200/native.py.
+//
+// Capability parity: ferrotorch-core/src/tensor.rs:46-103 (GradFn, TensorInner), autograd/graph.rs:20-206 (backward: BFS + Kahn + reverse sweep
+// + hooks), :220-458 (backward_parallel), grad_fns/{arithmetic,linalg,activation,reduction}.rs, ferrotorch-nn/src/{linear,loss}.rs,
+// ferrotorch-optim/src/sgd.rs:30-210.
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <condition_variable>
+#include <cstdint>
+#include <cstring>
+#include <deque>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#define FT_API extern "C" __attribute__((visibility("default")))
+
+namespace ft {
+
+struct Node;
+struct TensorImpl;
+using Tensor = std::shared_ptr<TensorImpl>;
+
+static std::atomic<uint64_t> g_next_id{1};
+static thread_local bool g_grad_enabled = true;
+static thread_local std::string g_last_error;
+
+struct TensorImpl {
+  std::shared_ptr<std::vector<float>> storage;
+  std::vector<int64_t> shape, strides;
+  int64_t offset = 0;
+  bool requires_grad = false;
+  Tensor grad;
+  std::shared_ptr<Node> grad_fn;
+  std::vector<std::function<void(TensorImpl&)>> hooks;             // run on the incoming gradient of this tensor (may modify it)
+  std::vector<std::function<void(TensorImpl&)>> post_acc_hooks;    // run on a leaf after its .grad was updated
+  uint64_t id = g_next_id++;
+  uint32_t version = 0;
+
+  int64_t numel() const { int64_t n = 1; for (auto s : shape) n *= s; return n; }
+  bool is_leaf() const { return grad_fn == nullptr; }
+  bool is_contiguous() const {
+    int64_t expect = 1;
+    for (int i = (int)shape.size() - 1; i >= 0; i--) {
+      if (shape[i] != 1 && strides[i] != expect) return false;
+      expect *= shape[i];
+    }
+    return true;
+  }
+  float* data() { return storage->data() + offset; }
+  const float* data() const { return storage->data() + offset; }
+};
+
+static std::vector<int64_t> row_major(const std::vector<int64_t>& shape) {
+  std::vector<int64_t> st(shape.size());
+  int64_t s = 1;
+  for (int i = (int)shape.size() - 1; i >= 0; i--) { st[i] = s; s *= shape[i]; }
+  return st;
+}
+static Tensor make(const std::vector<int64_t>& shape, float fill = 0.f) {
+  auto t = std::make_shared<TensorImpl>();
+  t->shape = shape;
+  t->strides = row_major(shape);
+  t->storage = std::make_shared<std::vector<float>>((size_t)t->numel(), fill);
+  return t;
+}
+static Tensor contiguous(const Tensor& a) {
+  if (a->is_contiguous()) return a;
+  Tensor o = make(a->shape);
+  const int nd = (int)a->shape.size();
+  std::vector<int64_t> idx(nd, 0);
+  const int64_t n = a->numel();
+  float* d = o->data();
+  const float* s = a->data();
+  for (int64_t i = 0; i < n; i++) {
+    int64_t off = 0;
+    for (int k = 0; k < nd; k++) off += idx[k] * a->strides[k];
+    d[i] = s[off];
+    for (int k = nd - 1; k >= 0; k--) { if (++idx[k] < a->shape[k]) break; idx[k] = 0; }
+  }
+  return o;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// graph
+// ---------------------------------------------------------------------------------------------------------------------------------------
+struct Node {
+  std::vector<Tensor> inputs;                       // null where the input needs no gradient
+  const char* name = "node";
+  virtual ~Node() = default;
+  virtual std::vector<Tensor> backward(const Tensor& grad_out) = 0;   // one gradient per input (null allowed)
+};
+
+static bool needs_grad(std::initializer_list<Tensor> ts) {
+  if (!g_grad_enabled) return false;
+  for (auto& t : ts) if (t && t->requires_grad) return true;
+  return false;
+}
+template <typename N, typename... A>
+static void attach(const Tensor& out, std::initializer_list<Tensor> ins, A&&... args) {
+  if (!needs_grad(ins)) return;
+  auto n = std::make_shared<N>(std::forward<A>(args)...);
+  for (auto& t : ins) n->inputs.push_back(t && t->requires_grad ? t : nullptr);
+  out->requires_grad = true;
+  out->grad_fn = n;
+}
+
+static void accumulate(Tensor& dst, const Tensor& src) {
+  if (!dst) { dst = contiguous(src); if (dst.get() == src.get()) { dst = make(src->shape); std::memcpy(dst->data(), src->data(), sizeof(float) * (size_t)src->numel()); } return; }
+  Tensor s = contiguous(src);
+  float* d = dst->data();
+  const float* p = s->data();
+  const int64_t n = dst->numel();
+  for (int64_t i = 0; i < n; i++) d[i] += p[i];
+}
+
+struct Engine {
+  // per node (and per leaf): the slots of its incoming contributions (one per consuming edge, in discovery order) and how many are still missing
+  struct Info { std::vector<Tensor> slots; int missing = 0; std::mutex mu; };
+  std::unordered_map<Node*, std::unique_ptr<Info>> info;
+  std::unordered_map<TensorImpl*, std::unique_ptr<Info>> leaf_info;
+  std::unordered_map<Node*, std::shared_ptr<Node>> keep;
+  std::unordered_map<const void*, int> slot_of;      // address of a consumer's input entry -> its slot in the producer (node or leaf)
+
+  void collect(const std::shared_ptr<Node>& root) {
+    std::deque<std::shared_ptr<Node>> q{root};
+    keep[root.get()] = root;
+    info[root.get()] = std::make_unique<Info>();
+    while (!q.empty()) {
+      auto n = q.front();
+      q.pop_front();
+      for (size_t i = 0; i < n->inputs.size(); i++) {
+        const Tensor& t = n->inputs[i];
+        if (!t) continue;
+        Info* pi;
+        if (t->grad_fn) {
+          Node* p = t->grad_fn.get();
+          if (!info.count(p)) { info[p] = std::make_unique<Info>(); keep[p] = t->grad_fn; q.push_back(t->grad_fn); }
+          pi = info[p].get();
+        } else {
+          if (!leaf_info.count(t.get())) leaf_info[t.get()] = std::make_unique<Info>();
+          pi = leaf_info[t.get()].get();
+        }
+        slot_of[&n->inputs[i]] = (int)pi->slots.size();
+        pi->slots.emplace_back();
+        pi->missing++;
+      }
+    }
+  }
+  static Tensor sum_slots(Info& in) {
+    Tensor g;
+    for (auto& s : in.slots) if (s) accumulate(g, s);      // edge order: the same sum whatever order the contributions arrived in
+    return g;
+  }
+  // run one node: returns the producers that became ready
+  std::vector<Node*> run(Node* n) {
+    Info& in = *info.at(n);
+    Tensor g = sum_slots(in);
+    in.slots.clear();
+    std::vector<Node*> ready;
+    std::vector<Tensor> gi;
+    if (g) gi = n->backward(g);
+    for (size_t i = 0; i < n->inputs.size(); i++) {
+      Tensor& t = n->inputs[i];
+      if (!t) continue;
+      Tensor gin = i < gi.size() ? gi[i] : nullptr;
+      if (gin && !t->hooks.empty()) {
+        Tensor c = make(gin->shape);                        // hooks may rewrite the gradient: give them a private copy
+        Tensor gc = contiguous(gin);
+        std::memcpy(c->data(), gc->data(), sizeof(float) * (size_t)gc->numel());
+        gin = c;
+        for (auto& h : t->hooks) h(*gin);
+      }
+      Info& pi = t->grad_fn ? *info.at(t->grad_fn.get()) : *leaf_info.at(t.get());
+      bool now_ready;
+      {
+        std::lock_guard<std::mutex> lk(pi.mu);
+        pi.slots[slot_of.at(&t)] = gin;
+        now_ready = --pi.missing == 0;
+      }
+      if (!now_ready) continue;
+      if (t->grad_fn) {
+        ready.push_back(t->grad_fn.get());
+      } else {
+        // every consumer of this leaf has delivered: its gradient is final for this sweep
+        Tensor total = sum_slots(pi);
+        pi.slots.clear();
+        if (total) {
+          accumulate(t->grad, total);
+          for (auto& h : t->post_acc_hooks) h(*t);
+        }
+      }
+    }
+    return ready;
+  }
+};
+
+static void backward(const Tensor& root, const Tensor& grad_root, int threads) {
+  if (!root->grad_fn) {
+    if (root->requires_grad) { accumulate(root->grad, grad_root); for (auto& h : root->post_acc_hooks) h(*root); }
+    return;
+  }
+  Engine e;
+  e.collect(root->grad_fn);
+  Engine::Info& ri = *e.info.at(root->grad_fn.get());
+  ri.slots.push_back(grad_root);
+  if (threads <= 1) {
+    // Kahn: a node runs once every consumer has delivered its contribution; the ready list is a FIFO, so the order is a fixed function of the graph
+    std::deque<Node*> ready{root->grad_fn.get()};
+    while (!ready.empty()) {
+      Node* n = ready.front();
+      ready.pop_front();
+      for (Node* p : e.run(n)) ready.push_back(p);
+    }
+    return;
+  }
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<Node*> ready{root->grad_fn.get()};
+  int running = 0;
+  auto worker = [&] {
+    std::unique_lock<std::mutex> lk(mu);
+    while (true) {
+      cv.wait(lk, [&] { return !ready.empty() || (running == 0); });
+      if (ready.empty()) { if (running == 0) { cv.notify_all(); return; } continue; }
+      Node* n = ready.front();
+      ready.pop_front();
+      running++;
+      lk.unlock();
+      std::vector<Node*> next = e.run(n);
+      lk.lock();
+      running--;
+      for (Node* p : next) ready.push_back(p);
+      cv.notify_all();
+    }
+  };
+  std::vector<std::thread> pool;
+  for (int i = 0; i < threads; i++) pool.emplace_back(worker);
+  for (auto& t : pool) t.join();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// operations (inputs are made contiguous; row-broadcast means b has the shape of a's last dimension)
+// ---------------------------------------------------------------------------------------------------------------------------------------
+static Tensor reduce_to(const Tensor& g, const std::vector<int64_t>& shape) {       // sum a [rows, n] gradient down to [n]
+  if (g->shape == shape) return g;
+  Tensor o = make(shape);
+  const int64_t n = o->numel(), rows = g->numel() / n;
+  Tensor gc = contiguous(g);
+  for (int64_t r = 0; r < rows; r++) for (int64_t i = 0; i < n; i++) o->data()[i] += gc->data()[r * n + i];
+  return o;
+}
+enum class Bin { Add, Sub, Mul };
+struct BinNode : Node {
+  Bin op; Tensor a, b;
+  BinNode(Bin o, Tensor x, Tensor y) : op(o), a(std::move(x)), b(std::move(y)) { name = "binary"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), ga, gb;
+    const int64_t n = gc->numel(), nb = b->numel();
+    if (op == Bin::Mul) {
+      ga = make(a->shape); gb = make(a->shape);
+      for (int64_t i = 0; i < n; i++) { ga->data()[i] = gc->data()[i] * b->data()[i % nb]; gb->data()[i] = gc->data()[i] * a->data()[i]; }
+    } else {
+      ga = gc;
+      gb = gc;
+      if (op == Bin::Sub) { gb = make(a->shape); for (int64_t i = 0; i < n; i++) gb->data()[i] = -gc->data()[i]; }
+    }
+    return {ga, reduce_to(gb, b->shape)};
+  }
+};
+static Tensor binary(Bin op, const Tensor& a0, const Tensor& b0) {
+  Tensor a = contiguous(a0), b = contiguous(b0);
+  const int64_t n = a->numel(), nb = b->numel();
+  if (nb == 0 || n % nb || (nb != n && (b->shape.size() != 1 || a->shape.back() != b->shape[0]))) { g_last_error = "binary: shapes do not match or broadcast"; return nullptr; }
+  Tensor o = make(a->shape);
+  for (int64_t i = 0; i < n; i++) {
+    const float x = a->data()[i], y = b->data()[i % nb];
+    o->data()[i] = op == Bin::Add ? x + y : (op == Bin::Sub ? x - y : x * y);
+  }
+  attach<BinNode>(o, {a0, b0}, op, a, b);
+  return o;
+}
+struct ScaleNode : Node {
+  float s;
+  explicit ScaleNode(float v) : s(v) { name = "scale"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(gc->shape);
+    for (int64_t i = 0; i < gc->numel(); i++) o->data()[i] = gc->data()[i] * s;
+    return {o};
+  }
+};
+static Tensor scale(const Tensor& a0, float s) {
+  Tensor a = contiguous(a0), o = make(a->shape);
+  for (int64_t i = 0; i < a->numel(); i++) o->data()[i] = a->data()[i] * s;
+  attach<ScaleNode>(o, {a0}, s);
+  return o;
+}
+static Tensor transpose(const Tensor& a);
+struct TransposeNode : Node {
+  TransposeNode() { name = "transpose"; }
+  std::vector<Tensor> backward(const Tensor& g) override { return {transpose(g)}; }
+};
+static Tensor transpose(const Tensor& a) {          // a view: no copy
+  if (a->shape.size() != 2) { g_last_error = "transpose expects a matrix"; return nullptr; }
+  auto t = std::make_shared<TensorImpl>();
+  t->storage = a->storage;
+  t->offset = a->offset;
+  t->shape = {a->shape[1], a->shape[0]};
+  t->strides = {a->strides[1], a->strides[0]};
+  attach<TransposeNode>(t, {a});
+  return t;
+}
+// C[M,N] = A[M,K] B[K,N], blocked over k for cache reuse
+static void gemm_raw(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K) {
+  std::fill(C, C + M * N, 0.f);
+  constexpr int64_t KB = 64;
+  for (int64_t k0 = 0; k0 < K; k0 += KB) {
+    const int64_t k1 = std::min(K, k0 + KB);
+    for (int64_t i = 0; i < M; i++) {
+      float* c = C + i * N;
+      for (int64_t k = k0; k < k1; k++) {
+        const float a = A[i * K + k];
+        const float* b = B + k * N;
+        for (int64_t j = 0; j < N; j++) c[j] += a * b[j];
+      }
+    }
+  }
+}
+static Tensor matmul(const Tensor& a0, const Tensor& b0);
+struct MatmulNode : Node {
+  Tensor a, b;
+  MatmulNode(Tensor x, Tensor y) : a(std::move(x)), b(std::move(y)) { name = "matmul"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    const bool prev = g_grad_enabled;
+    g_grad_enabled = false;
+    Tensor ga = inputs[0] ? matmul(g, transpose(b)) : nullptr, gb = inputs[1] ? matmul(transpose(a), g) : nullptr;
+    g_grad_enabled = prev;
+    return {ga, gb};
+  }
+};
+static Tensor matmul(const Tensor& a0, const Tensor& b0) {
+  if (a0->shape.size() != 2 || b0->shape.size() != 2 || a0->shape[1] != b0->shape[0]) { g_last_error = "matmul: shapes do not match"; return nullptr; }
+  Tensor a = contiguous(a0), b = contiguous(b0);
+  Tensor o = make({a->shape[0], b->shape[1]});
+  gemm_raw(a->data(), b->data(), o->data(), a->shape[0], b->shape[1], a->shape[1]);
+  attach<MatmulNode>(o, {a0, b0}, a, b);
+  return o;
+}
+enum class Act { Relu, Tanh, Sigmoid };
+struct ActNode : Node {
+  Act k; Tensor y, x;
+  ActNode(Act kk, Tensor out, Tensor in) : k(kk), y(std::move(out)), x(std::move(in)) { name = "activation"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(gc->shape);
+    for (int64_t i = 0; i < gc->numel(); i++) {
+      const float v = y->data()[i];
+      const float d = k == Act::Relu ? (x->data()[i] > 0.f ? 1.f : 0.f) : (k == Act::Tanh ? 1.f - v * v : v * (1.f - v));
+      o->data()[i] = gc->data()[i] * d;
+    }
+    return {o};
+  }
+};
+static Tensor activation(Act k, const Tensor& a0) {
+  Tensor a = contiguous(a0), o = make(a->shape);
+  for (int64_t i = 0; i < a->numel(); i++) {
+    const float x = a->data()[i];
+    o->data()[i] = k == Act::Relu ? (x > 0.f ? x : 0.f) : (k == Act::Tanh ? std::tanh(x) : 1.f / (1.f + std::exp(-x)));
+  }
+  attach<ActNode>(o, {a0}, k, o, a);
+  return o;
+}
+struct SumNode : Node {
+  std::vector<int64_t> shape; float w;
+  SumNode(std::vector<int64_t> s, float ww) : shape(std::move(s)), w(ww) { name = "sum"; }
+  std::vector<Tensor> backward(const Tensor& g) override { return {make(shape, g->data()[0] * w)}; }
+};
+static Tensor sum(const Tensor& a0, bool mean) {
+  Tensor a = contiguous(a0), o = make({});
+  double s = 0;
+  for (int64_t i = 0; i < a->numel(); i++) s += a->data()[i];
+  const float w = mean ? 1.f / (float)std::max<int64_t>(a->numel(), 1) : 1.f;
+  o->data()[0] = (float)(s * w);
+  attach<SumNode>(o, {a0}, a->shape, w);
+  return o;
+}
+// mean over rows of -log softmax(logits)[target]
+struct CrossEntropyNode : Node {
+  Tensor prob; std::vector<int64_t> tgt;
+  CrossEntropyNode(Tensor p, std::vector<int64_t> t) : prob(std::move(p)), tgt(std::move(t)) { name = "cross_entropy"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    const int64_t R = prob->shape[0], C = prob->shape[1];
+    Tensor o = make(prob->shape);
+    const float s = g->data()[0] / (float)R;
+    for (int64_t r = 0; r < R; r++)
+      for (int64_t c = 0; c < C; c++) o->data()[r * C + c] = (prob->data()[r * C + c] - (c == tgt[r] ? 1.f : 0.f)) * s;
+    return {o};
+  }
+};
+static Tensor cross_entropy(const Tensor& l0, const int64_t* targets, int64_t n) {
+  if (l0->shape.size() != 2 || l0->shape[0] != n) { g_last_error = "cross_entropy: logits [rows, classes] and one target per row"; return nullptr; }
+  Tensor l = contiguous(l0), prob = make(l->shape), o = make({});
+  const int64_t R = l->shape[0], C = l->shape[1];
+  double total = 0;
+  for (int64_t r = 0; r < R; r++) {
+    if (targets[r] < 0 || targets[r] >= C) { g_last_error = "cross_entropy: target out of range"; return nullptr; }
+    const float* x = l->data() + r * C;
+    float m = x[0];
+    for (int64_t c = 1; c < C; c++) m = std::max(m, x[c]);
+    double z = 0;
+    for (int64_t c = 0; c < C; c++) z += std::exp((double)x[c] - m);
+    const double lz = std::log(z) + m;
+    for (int64_t c = 0; c < C; c++) prob->data()[r * C + c] = (float)std::exp((double)x[c] - lz);
+    total += lz - x[targets[r]];
+  }
+  o->data()[0] = (float)(total / (double)R);
+  attach<CrossEntropyNode>(o, {l0}, prob, std::vector<int64_t>(targets, targets + n));
+  return o;
+}
+static Tensor linear(const Tensor& x, const Tensor& w, const Tensor& b) {     // x W^T + b with W [out, in]
+  Tensor y = matmul(x, transpose(w));
+  if (!y) return nullptr;
+  return b ? binary(Bin::Add, y, b) : y;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// SGD
+// ---------------------------------------------------------------------------------------------------------------------------------------
+struct Sgd {
+  std::vector<Tensor> params;
+  std::vector<std::vector<float>> buf;
+  float lr, momentum, dampening, weight_decay;
+  bool nesterov;
+  bool first = true;
+  void step() {
+    if (buf.size() != params.size()) buf.resize(params.size());
+    for (size_t k = 0; k < params.size(); k++) {
+      Tensor& p = params[k];
+      if (!p->grad) continue;
+      Tensor gc = contiguous(p->grad);
+      const int64_t n = p->numel();
+      float* w = p->data();
+      if (!p->is_contiguous()) continue;            // parameters are created contiguous; views are not optimised
+      std::vector<float>& m = buf[k];
+      const bool init = m.empty();
+      if (momentum != 0.f && init) m.assign((size_t)n, 0.f);
+      for (int64_t i = 0; i < n; i++) {
+        float g = gc->data()[i] + weight_decay * w[i];
+        if (momentum != 0.f) {
+          m[i] = init ? g : momentum * m[i] + (1.f - dampening) * g;
+          g = nesterov ? g + momentum * m[i] : m[i];
+        }
+        w[i] -= lr * g;
+      }
+      p->version++;
+    }
+  }
+};
+
+}  // namespace ft
+
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// C ABI: a handle is a heap-allocated ft::Tensor (shared_ptr); every function that returns a handle returns null on error
+// (ftc_last_error gives the reason). Handles are released with ftc_free.
+// ---------------------------------------------------------------------------------------------------------------------------------------
+using ft::Tensor;
+static Tensor* H(const Tensor& t) { return t ? new Tensor(t) : nullptr; }
+static const Tensor& T(const void* h) { return *static_cast<const Tensor*>(h); }
+
+// Last error message of the calling thread ("" if none).
+FT_API const char* ftc_last_error() { return ft::g_last_error.c_str(); }
+// New tensor of the given shape; data (may be null: zeros) is copied. requires_grad marks it as a leaf that accumulates .grad.
+FT_API void* ftc_tensor_new(const float* data, const int64_t* shape, int ndim, int requires_grad) {
+  Tensor t = ft::make(std::vector<int64_t>(shape, shape + ndim));
+  if (data) std::memcpy(t->data(), data, sizeof(float) * (size_t)t->numel());
+  t->requires_grad = requires_grad != 0;
+  return H(t);
+}
+FT_API void ftc_free(void* h) { delete static_cast<Tensor*>(h); }
+FT_API int ftc_ndim(const void* h) { return (int)T(h)->shape.size(); }
+FT_API int64_t ftc_numel(const void* h) { return T(h)->numel(); }
+FT_API void ftc_shape(const void* h, int64_t* out) { for (size_t i = 0; i < T(h)->shape.size(); i++) out[i] = T(h)->shape[i]; }
+FT_API uint64_t ftc_id(const void* h) { return T(h)->id; }
+FT_API int ftc_requires_grad(const void* h) { return T(h)->requires_grad ? 1 : 0; }
+FT_API int ftc_is_leaf(const void* h) { return T(h)->is_leaf() ? 1 : 0; }
+FT_API const char* ftc_grad_fn_name(const void* h) { return T(h)->grad_fn ? T(h)->grad_fn->name : ""; }
+// Pointer to the tensor's own storage when it is contiguous (shared with the caller: writes are visible to the tensor), else null.
+FT_API float* ftc_data_ptr(void* h) { return T(h)->is_contiguous() ? const_cast<float*>(T(h)->data()) : nullptr; }
+// Copies the values out in row-major order.
+FT_API void ftc_copy_out(const void* h, float* out) { Tensor c = ft::contiguous(T(h)); std::memcpy(out, c->data(), sizeof(float) * (size_t)c->numel()); }
+// Handle of .grad (null if none has been accumulated).
+FT_API void* ftc_grad(const void* h) { return H(T(h)->grad); }
+FT_API void ftc_zero_grad(void* h) { T(h)->grad = nullptr; }
+FT_API void* ftc_detach(const void* h) {
+  auto t = std::make_shared<ft::TensorImpl>(*T(h));
+  t->grad_fn = nullptr; t->grad = nullptr; t->requires_grad = false; t->hooks.clear(); t->post_acc_hooks.clear(); t->id = ft::g_next_id++;
+  return H(t);
+}
+// Switches gradient recording on or off for the calling thread (no_grad); returns the previous setting.
+FT_API int ftc_set_grad_enabled(int on) { const int prev = ft::g_grad_enabled; ft::g_grad_enabled = on != 0; return prev; }
+
+FT_API void* ftc_add(const void* a, const void* b) { return H(ft::binary(ft::Bin::Add, T(a), T(b))); }
+FT_API void* ftc_sub(const void* a, const void* b) { return H(ft::binary(ft::Bin::Sub, T(a), T(b))); }
+FT_API void* ftc_mul(const void* a, const void* b) { return H(ft::binary(ft::Bin::Mul, T(a), T(b))); }
+FT_API void* ftc_scale(const void* a, float s) { return H(ft::scale(T(a), s)); }
+FT_API void* ftc_matmul(const void* a, const void* b) { return H(ft::matmul(T(a), T(b))); }
+FT_API void* ftc_transpose(const void* a) { return H(ft::transpose(T(a))); }
+FT_API void* ftc_relu(const void* a) { return H(ft::activation(ft::Act::Relu, T(a))); }
+FT_API void* ftc_tanh(const void* a) { return H(ft::activation(ft::Act::Tanh, T(a))); }
+FT_API void* ftc_sigmoid(const void* a) { return H(ft::activation(ft::Act::Sigmoid, T(a))); }
+FT_API void* ftc_sum(const void* a) { return H(ft::sum(T(a), false)); }
+FT_API void* ftc_mean(const void* a) { return H(ft::sum(T(a), true)); }
+// x W^T + b (b may be null).
+FT_API void* ftc_linear(const void* x, const void* w, const void* b) { return H(ft::linear(T(x), T(w), b ? T(b) : nullptr)); }
+// Mean cross-entropy of logits [rows, classes] against `rows` int64 class indices.
+FT_API void* ftc_cross_entropy(const void* logits, const int64_t* targets, int64_t rows) { return H(ft::cross_entropy(T(logits), targets, rows)); }
+
+// Reverse-mode sweep from `root` (a scalar unless grad is given). threads <= 1: the serial engine; more: worker threads over the ready queue
+// (same result bit for bit). Returns 0, or 1 if root does not require grad / is not a scalar without an explicit gradient.
+FT_API int ftc_backward(void* root, const void* grad, int threads) {
+  const Tensor& r = T(root);
+  if (!r->requires_grad) { ft::g_last_error = "backward: the tensor does not require grad"; return 1; }
+  Tensor g;
+  if (grad) g = T(grad);
+  else {
+    if (r->numel() != 1) { ft::g_last_error = "backward: a gradient must be given for a non-scalar root"; return 1; }
+    g = ft::make(r->shape, 1.f);
+  }
+  ft::backward(r, g, threads);
+  return 0;
+}
+
+typedef void (*ftc_grad_hook)(void* user, float* grad, int64_t numel);
+typedef void (*ftc_post_hook)(void* user, uint64_t tensor_id);
+// fn(user, grad, numel) runs on every gradient that arrives at this tensor during backward and may rewrite it in place.
+FT_API void ftc_register_hook(void* h, ftc_grad_hook fn, void* user) {
+  T(h)->hooks.push_back([fn, user](ft::TensorImpl& g) { fn(user, g.data(), g.numel()); });
+}
+// fn(user, tensor_id) runs after a gradient has been accumulated into this leaf's .grad.
+FT_API void ftc_register_post_accumulate_hook(void* h, ftc_post_hook fn, void* user) {
+  T(h)->post_acc_hooks.push_back([fn, user](ft::TensorImpl& t) { fn(user, t.id); });
+}
+
+// SGD over `n` parameter handles (the optimizer keeps references to them). Released with ftc_sgd_free.
+FT_API void* ftc_sgd_new(void* const* params, int n, float lr, float momentum, float dampening, float weight_decay, int nesterov) {
+  auto* s = new ft::Sgd();
+  for (int i = 0; i < n; i++) s->params.push_back(T(params[i]));
+  s->lr = lr; s->momentum = momentum; s->dampening = dampening; s->weight_decay = weight_decay; s->nesterov = nesterov != 0;
+  return s;
+}
+FT_API void ftc_sgd_step(void* s) { static_cast<ft::Sgd*>(s)->step(); }
+FT_API void ftc_sgd_set_lr(void* s, float lr) { static_cast<ft::Sgd*>(s)->lr = lr; }
+FT_API void ftc_sgd_zero_grad(void* s) { for (auto& p : static_cast<ft::Sgd*>(s)->params) p->grad = nullptr; }
+FT_API void ftc_sgd_free(void* s) { delete static_cast<ft::Sgd*>(s); }

@@ -106,3 +106,52 @@ class DDP:
             t.join()   # untagged channels carry one message stream per peer: keep bucket order identical on every rank
         if errs:
             raise errs[0]
+
+
+class NativeDDP:
+    """The same bucketed gradient averaging for a model built on the native core (:mod:`ferrotorch_b200.native`): parameters are native
+    tensors, buckets are flattened from zero-copy NumPy views of their ``.grad`` and the reduced values are written back in place."""
+
+    class _Meta:
+        def __init__(self, t):
+            self.t = t
+
+        def numel(self):
+            return self.t.numel()
+
+        def element_size(self):
+            return 4
+
+    def __init__(self, module, backend: Backend, bucket_size_bytes: int = DEFAULT_BUCKET_SIZE_BYTES,
+                 timeout: Optional[float] = DEFAULT_COLLECTIVE_TIMEOUT, algorithm: str = "star"):
+        self._module, self.backend, self.timeout, self.algorithm = module, backend, timeout, algorithm
+        self.params = list(module.parameters())
+        self.buckets = compute_buckets([self._Meta(p) for p in self.params], bucket_size_bytes)
+
+    def __call__(self, *a):
+        return self._module(*a)
+
+    def module(self):
+        return self._module
+
+    def parameters(self):
+        return self.params
+
+    def broadcast_parameters(self, root: int = 0) -> None:
+        for p in self.params:
+            v = p.numpy()
+            v[...] = broadcast(torch.from_numpy(v), self.backend, root, self.timeout).numpy()
+
+    def sync_gradients(self) -> None:
+        import numpy as np
+        for idx in self.buckets:
+            ps = [self.params[i] for i in idx]
+            grads = [p.grad for p in ps]
+            flat = np.concatenate([(g.numpy() if g is not None else np.zeros(p.shape, np.float32)).reshape(-1) for p, g in zip(ps, grads)])
+            red = allreduce(torch.from_numpy(flat), self.backend, ReduceOp.Mean, self.timeout, self.algorithm).numpy()
+            off = 0
+            for p, g in zip(ps, grads):
+                n = p.numel()
+                if g is not None:
+                    g.numpy().reshape(-1)[:] = red[off: off + n]
+                off += n

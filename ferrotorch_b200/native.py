@@ -1,0 +1,286 @@
+"""Python binding of the native CPU tensor / autograd core (``csrc/runtime/core.cpp``).
+
+``Tensor`` wraps a handle of the C++ ``ft::Tensor`` (f32, strided, reference counted); the operations record ``ft::Node`` objects and
+``Tensor.backward()`` runs the C++ engine (graph collection, Kahn ordering, reverse sweep, hooks; ``threads > 1`` selects the parallel sweep,
+which produces the same bits). ``Linear`` / ``Sequential`` / ``Sgd`` are the smallest framework layer over it: enough to train the MLP of the
+CPU data-parallel benchmark without ``torch.nn`` / ``torch.autograd`` / ``torch.optim`` on the path. NumPy arrays are the interchange format
+(``Tensor.numpy()`` of a contiguous tensor is a zero-copy view of the native storage).
+
+Reference parity: ferrotorch-core/src/tensor.rs:46-103, autograd/graph.rs:20-458, ferrotorch-nn/src/{module,linear,loss}.rs,
+ferrotorch-optim/src/sgd.rs.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Callable, Iterable, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from .errors import InvalidArgument
+
+_vp, _i, _i64, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+_GRAD_HOOK = ctypes.CFUNCTYPE(None, _vp, ctypes.POINTER(ctypes.c_float), _i64)
+_POST_HOOK = ctypes.CFUNCTYPE(None, _vp, ctypes.c_uint64)
+_SIGS = {
+    "ftc_last_error": (ctypes.c_char_p, []), "ftc_tensor_new": (_vp, [_vp, _vp, _i, _i]), "ftc_free": (None, [_vp]), "ftc_ndim": (_i, [_vp]),
+    "ftc_numel": (_i64, [_vp]), "ftc_shape": (None, [_vp, _vp]), "ftc_id": (ctypes.c_uint64, [_vp]), "ftc_requires_grad": (_i, [_vp]),
+    "ftc_is_leaf": (_i, [_vp]), "ftc_grad_fn_name": (ctypes.c_char_p, [_vp]), "ftc_data_ptr": (_vp, [_vp]), "ftc_copy_out": (None, [_vp, _vp]),
+    "ftc_grad": (_vp, [_vp]), "ftc_zero_grad": (None, [_vp]), "ftc_detach": (_vp, [_vp]), "ftc_set_grad_enabled": (_i, [_i]),
+    "ftc_add": (_vp, [_vp, _vp]), "ftc_sub": (_vp, [_vp, _vp]), "ftc_mul": (_vp, [_vp, _vp]), "ftc_scale": (_vp, [_vp, _f]),
+    "ftc_matmul": (_vp, [_vp, _vp]), "ftc_transpose": (_vp, [_vp]), "ftc_relu": (_vp, [_vp]), "ftc_tanh": (_vp, [_vp]), "ftc_sigmoid": (_vp, [_vp]),
+    "ftc_sum": (_vp, [_vp]), "ftc_mean": (_vp, [_vp]), "ftc_linear": (_vp, [_vp, _vp, _vp]), "ftc_cross_entropy": (_vp, [_vp, _vp, _i64]),
+    "ftc_backward": (_i, [_vp, _vp, _i]), "ftc_register_hook": (None, [_vp, _GRAD_HOOK, _vp]),
+    "ftc_register_post_accumulate_hook": (None, [_vp, _POST_HOOK, _vp]),
+    "ftc_sgd_new": (_vp, [_vp, _i, _f, _f, _f, _f, _i]), "ftc_sgd_step": (None, [_vp]), "ftc_sgd_set_lr": (None, [_vp, _f]),
+    "ftc_sgd_zero_grad": (None, [_vp]), "ftc_sgd_free": (None, [_vp]),
+}
+_bound = {}
+
+
+def _fn(name: str):
+    f = _bound.get(name)
+    if f is None:
+        f = getattr(_lib.runtime(), name)
+        f.restype, f.argtypes = _SIGS[name]
+        _bound[name] = f
+    return f
+
+
+def _check(h):
+    if not h:
+        raise InvalidArgument(_fn("ftc_last_error")().decode() or "native core: operation failed")
+    return h
+
+
+class Tensor:
+    """A handle of a native ``ft::Tensor``."""
+
+    __slots__ = ("_h", "_hooks")
+
+    def __init__(self, data=None, requires_grad: bool = False, *, _handle=None):
+        self._hooks: list = []            # keeps the ctypes callbacks alive as long as the tensor
+        if _handle is not None:
+            self._h = _handle
+            return
+        a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
+        shape = (ctypes.c_int64 * max(a.ndim, 1))(*a.shape)
+        self._h = _check(_fn("ftc_tensor_new")(a.ctypes.data, shape, a.ndim, int(requires_grad)))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _fn("ftc_free")(h)
+            except Exception:
+                pass
+
+    # -- metadata ---------------------------------------------------------------------------------------------------------
+    @property
+    def shape(self) -> tuple:
+        nd = _fn("ftc_ndim")(self._h)
+        out = (ctypes.c_int64 * max(nd, 1))()
+        _fn("ftc_shape")(self._h, out)
+        return tuple(out[i] for i in range(nd))
+
+    def numel(self) -> int:
+        return _fn("ftc_numel")(self._h)
+
+    @property
+    def requires_grad(self) -> bool:
+        return bool(_fn("ftc_requires_grad")(self._h))
+
+    @property
+    def is_leaf(self) -> bool:
+        return bool(_fn("ftc_is_leaf")(self._h))
+
+    @property
+    def grad_fn(self) -> Optional[str]:
+        n = _fn("ftc_grad_fn_name")(self._h).decode()
+        return n or None
+
+    @property
+    def id(self) -> int:
+        return _fn("ftc_id")(self._h)
+
+    @property
+    def grad(self) -> Optional["Tensor"]:
+        h = _fn("ftc_grad")(self._h)
+        return Tensor(_handle=h) if h else None
+
+    def zero_grad(self) -> None:
+        _fn("ftc_zero_grad")(self._h)
+
+    def numpy(self) -> np.ndarray:
+        """The values as a NumPy array: a zero-copy view of the native storage for a contiguous tensor (writes go through), else a copy."""
+        p = _fn("ftc_data_ptr")(self._h)
+        shape = self.shape
+        if p:
+            n = self.numel()
+            arr = np.ctypeslib.as_array(ctypes.cast(p, ctypes.POINTER(ctypes.c_float)), shape=(n,)) if n else np.empty(0, np.float32)
+            arr = arr.reshape(shape)
+            arr_base = arr.base if arr.base is not None else arr
+            try:
+                arr_base._ft_owner = self          # keep the native tensor alive while the view is
+            except AttributeError:
+                pass
+            return arr
+        out = np.empty(shape, np.float32)
+        _fn("ftc_copy_out")(self._h, out.ctypes.data)
+        return out
+
+    def item(self) -> float:
+        return float(self.numpy().reshape(-1)[0])
+
+    def detach(self) -> "Tensor":
+        return Tensor(_handle=_check(_fn("ftc_detach")(self._h)))
+
+    # -- operations -------------------------------------------------------------------------------------------------------
+    def _bin(self, name, other):
+        if not isinstance(other, Tensor):
+            if np.isscalar(other) and name == "ftc_mul":
+                return Tensor(_handle=_check(_fn("ftc_scale")(self._h, float(other))))
+            other = Tensor(np.broadcast_to(np.asarray(other, np.float32), self.shape))
+        return Tensor(_handle=_check(_fn(name)(self._h, other._h)))
+
+    def __add__(self, o): return self._bin("ftc_add", o)
+    def __sub__(self, o): return self._bin("ftc_sub", o)
+    def __mul__(self, o): return self._bin("ftc_mul", o)
+    __rmul__ = __mul__
+    def __neg__(self): return Tensor(_handle=_check(_fn("ftc_scale")(self._h, -1.0)))
+    def __matmul__(self, o): return Tensor(_handle=_check(_fn("ftc_matmul")(self._h, o._h)))
+    def t(self): return Tensor(_handle=_check(_fn("ftc_transpose")(self._h)))
+    def relu(self): return Tensor(_handle=_check(_fn("ftc_relu")(self._h)))
+    def tanh(self): return Tensor(_handle=_check(_fn("ftc_tanh")(self._h)))
+    def sigmoid(self): return Tensor(_handle=_check(_fn("ftc_sigmoid")(self._h)))
+    def sum(self): return Tensor(_handle=_check(_fn("ftc_sum")(self._h)))
+    def mean(self): return Tensor(_handle=_check(_fn("ftc_mean")(self._h)))
+
+    def backward(self, grad: Optional["Tensor"] = None, threads: int = 1) -> None:
+        """Reverse sweep from this tensor. ``threads > 1`` runs independent nodes on worker threads (``backward_parallel``); gradients are
+        summed per consuming edge in a fixed order, so the result does not depend on the number of threads."""
+        if _fn("ftc_backward")(self._h, grad._h if grad is not None else None, int(threads)):
+            raise InvalidArgument(_fn("ftc_last_error")().decode())
+
+    def register_hook(self, fn: Callable[[np.ndarray], Optional[np.ndarray]]) -> None:
+        """``fn(grad)`` sees every gradient that reaches this tensor during backward (a NumPy view; modify it in place or return a replacement)."""
+        def cb(_user, ptr, n):
+            g = np.ctypeslib.as_array(ptr, shape=(n,))
+            r = fn(g)
+            if r is not None:
+                g[:] = np.asarray(r, np.float32).reshape(-1)
+        c = _GRAD_HOOK(cb)
+        self._hooks.append(c)
+        _fn("ftc_register_hook")(self._h, c, None)
+
+    def register_post_accumulate_grad_hook(self, fn: Callable[["Tensor"], None]) -> None:
+        """``fn(tensor)`` runs once this leaf's ``.grad`` is complete for the current sweep (data-parallel wrappers launch a bucket here)."""
+        def cb(_user, _tid):
+            fn(self)
+        c = _POST_HOOK(cb)
+        self._hooks.append(c)
+        _fn("ftc_register_post_accumulate_hook")(self._h, c, None)
+
+
+class no_grad:
+    def __enter__(self):
+        self.prev = _fn("ftc_set_grad_enabled")(0)
+
+    def __exit__(self, *exc):
+        _fn("ftc_set_grad_enabled")(self.prev)
+        return False
+
+
+def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None) -> Tensor:
+    return Tensor(_handle=_check(_fn("ftc_linear")(x._h, w._h, b._h if b is not None else None)))
+
+
+def relu(x: Tensor) -> Tensor:
+    return x.relu()
+
+
+def cross_entropy(logits: Tensor, targets) -> Tensor:
+    t = np.ascontiguousarray(np.asarray(targets, dtype=np.int64))
+    return Tensor(_handle=_check(_fn("ftc_cross_entropy")(logits._h, t.ctypes.data, t.size)))
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# the smallest module layer
+# ----------------------------------------------------------------------------------------------------------------------
+class Module:
+    def parameters(self) -> List[Tensor]:
+        out = []
+        for v in self.__dict__.values():
+            if isinstance(v, Tensor) and v.requires_grad:
+                out.append(v)
+            elif isinstance(v, Module):
+                out += v.parameters()
+            elif isinstance(v, (list, tuple)):
+                for m in v:
+                    if isinstance(m, Module):
+                        out += m.parameters()
+        return out
+
+    def zero_grad(self) -> None:
+        for p in self.parameters():
+            p.zero_grad()
+
+    def __call__(self, *a):
+        return self.forward(*a)
+
+
+class Linear(Module):
+    """``x W^T + b``; Kaiming-uniform weights for a ReLU network (bound ``sqrt(6 / fan_in)``) and zero bias, drawn from ``rng``."""
+
+    def __init__(self, fan_in: int, fan_out: int, bias: bool = True, rng: Optional[np.random.Generator] = None, weight=None, bias_value=None):
+        rng = rng or np.random.default_rng(0)
+        bound = math.sqrt(6.0 / fan_in)
+        w = rng.uniform(-bound, bound, size=(fan_out, fan_in)).astype(np.float32) if weight is None else np.asarray(weight, np.float32)
+        self.weight = Tensor(w, requires_grad=True)
+        self.bias = Tensor(np.zeros(fan_out, np.float32) if bias_value is None else np.asarray(bias_value, np.float32), requires_grad=True) if bias else None
+
+    def forward(self, x: Tensor) -> Tensor:
+        return linear(x, self.weight, self.bias)
+
+
+class ReLU(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.relu()
+
+
+class Sequential(Module):
+    def __init__(self, *mods: Module):
+        self.mods = list(mods)
+
+    def forward(self, x: Tensor) -> Tensor:
+        for m in self.mods:
+            x = m(x)
+        return x
+
+
+class Sgd:
+    """Native SGD (momentum, dampening, Nesterov, coupled weight decay), the update rule of ferrotorch-optim/src/sgd.rs:210."""
+
+    def __init__(self, params: Iterable[Tensor], lr: float, momentum: float = 0.0, dampening: float = 0.0, weight_decay: float = 0.0,
+                 nesterov: bool = False):
+        self.params = list(params)
+        arr = (ctypes.c_void_p * len(self.params))(*[p._h for p in self.params])
+        self._h = _fn("ftc_sgd_new")(arr, len(self.params), lr, momentum, dampening, weight_decay, int(nesterov))
+
+    def step(self) -> None:
+        _fn("ftc_sgd_step")(self._h)
+
+    def zero_grad(self) -> None:
+        _fn("ftc_sgd_zero_grad")(self._h)
+
+    def set_lr(self, lr: float) -> None:
+        _fn("ftc_sgd_set_lr")(self._h, lr)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _fn("ftc_sgd_free")(h)
+            except Exception:
+                pass
