@@ -549,11 +549,15 @@ FT_API int ftc_backward(void* root, const void* grad, int threads) {
 typedef void (*ftc_grad_hook)(void* user, float* grad, int64_t numel);
 typedef void (*ftc_post_hook)(void* user, uint64_t tensor_id);
 // fn(user, grad, numel) runs on every gradient that arrives at this tensor during backward and may rewrite it in place.
-FT_API void ftc_register_hook(void* h, ftc_grad_hook fn, void* user) {
+// (fn is passed as an untyped pointer so that the generated C header needs no typedef: void (*)(void* user, float* grad, int64_t numel).)
+FT_API void ftc_register_hook(void* h, void* fn_ptr, void* user) {
+  ftc_grad_hook fn = reinterpret_cast<ftc_grad_hook>(fn_ptr);
   T(h)->hooks.push_back([fn, user](ft::TensorImpl& g) { fn(user, g.data(), g.numel()); });
 }
 // fn(user, tensor_id) runs after a gradient has been accumulated into this leaf's .grad.
-FT_API void ftc_register_post_accumulate_hook(void* h, ftc_post_hook fn, void* user) {
+// (fn: void (*)(void* user, uint64_t tensor_id), passed as an untyped pointer.)
+FT_API void ftc_register_post_accumulate_hook(void* h, void* fn_ptr, void* user) {
+  ftc_post_hook fn = reinterpret_cast<ftc_post_hook>(fn_ptr);
   T(h)->post_acc_hooks.push_back([fn, user](ft::TensorImpl& t) { fn(user, t.id); });
 }
 
