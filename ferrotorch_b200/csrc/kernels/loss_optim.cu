@@ -325,3 +325,113 @@ FT_EXPORT int ft_scale_inplace(void* x, int64_t n, int dtype, float scale, const
   else scale_inplace_kernel<float><<<grid, 256, 0, st>>>((float*)x, (size_t)n, scale, scale_ptr);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// One element-wise kernel for the optimizers that are a per-element recurrence over up to three state buffers:
+// Adagrad, RMSprop, Adadelta, Adamax, NAdam, RAdam, Rprop, ASGD (ferrotorch-optim/src/{adagrad,rmsprop,adadelta,adamax,nadam,radam,rprop,
+// asgd}.rs run these as chains of tensor operations, a dozen launches per parameter). The step-dependent scalars (bias corrections,
+// decayed learning rates, the NAdam momentum products, the RAdam rectification) are computed on the host and arrive in `h`.
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+struct OptHp { float v[12]; };
+enum OptAlgo : int { OPT_ADAGRAD = 0, OPT_RMSPROP = 1, OPT_ADADELTA = 2, OPT_ADAMAX = 3, OPT_NADAM = 4, OPT_RADAM = 5, OPT_RPROP = 6, OPT_ASGD = 7 };
+
+template <int ALGO>
+__global__ void foreach_opt_kernel(float* __restrict__ p, const float* __restrict__ grad, float* __restrict__ s0, float* __restrict__ s1,
+                                   float* __restrict__ s2, size_t n, OptHp h, float gsign) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float w = p[i], g = grad[i] * gsign;
+    if constexpr (ALGO == OPT_ADAGRAD) {            // h: clr, wd, eps
+      g += h.v[1] * w;
+      const float s = s0[i] + g * g;
+      s0[i] = s;
+      w -= h.v[0] * g / (sqrtf(s) + h.v[2]);
+    } else if constexpr (ALGO == OPT_RMSPROP) {     // h: lr, alpha, eps, wd, momentum, centered
+      g += h.v[3] * w;
+      const float sq = h.v[1] * s0[i] + (1.f - h.v[1]) * g * g;
+      s0[i] = sq;
+      float avg;
+      if (h.v[5] != 0.f) {
+        const float ga = h.v[1] * s2[i] + (1.f - h.v[1]) * g;
+        s2[i] = ga;
+        avg = sqrtf(sq - ga * ga) + h.v[2];
+      } else {
+        avg = sqrtf(sq) + h.v[2];
+      }
+      if (h.v[4] > 0.f) {
+        const float b = h.v[4] * s1[i] + g / avg;
+        s1[i] = b;
+        w -= h.v[0] * b;
+      } else {
+        w -= h.v[0] * g / avg;
+      }
+    } else if constexpr (ALGO == OPT_ADADELTA) {    // h: lr, rho, eps, wd
+      g += h.v[3] * w;
+      const float sq = h.v[1] * s0[i] + (1.f - h.v[1]) * g * g;
+      s0[i] = sq;
+      const float delta = sqrtf(s1[i] + h.v[2]) / sqrtf(sq + h.v[2]) * g;
+      s1[i] = h.v[1] * s1[i] + (1.f - h.v[1]) * delta * delta;
+      w -= h.v[0] * delta;
+    } else if constexpr (ALGO == OPT_ADAMAX) {      // h: clr = lr / (1 - b1^t), b1, b2, eps, wd
+      g += h.v[4] * w;
+      const float m = h.v[1] * s0[i] + (1.f - h.v[1]) * g;
+      const float u = fmaxf(h.v[2] * s1[i], fabsf(g) + h.v[3]);
+      s0[i] = m;
+      s1[i] = u;
+      w -= h.v[0] * m / u;
+    } else if constexpr (ALGO == OPT_NADAM) {       // h: c_grad, c_mom, b1, b2, eps, wd (coupled), bc2, decay factor (decoupled)
+      w *= h.v[7];
+      g += h.v[5] * w;
+      const float m = h.v[2] * s0[i] + (1.f - h.v[2]) * g;
+      const float v = h.v[3] * s1[i] + (1.f - h.v[3]) * g * g;
+      s0[i] = m;
+      s1[i] = v;
+      const float den = sqrtf(v / h.v[6]) + h.v[4];
+      w -= h.v[0] * g / den;
+      w -= h.v[1] * m / den;
+    } else if constexpr (ALGO == OPT_RADAM) {       // h: lr, b1, b2, eps, wd (coupled), bc1, bc2, rect (0: not rectified), decay factor (decoupled)
+      w *= h.v[8];
+      g += h.v[4] * w;
+      const float m = h.v[1] * s0[i] + (1.f - h.v[1]) * g;
+      const float v = h.v[2] * s1[i] + (1.f - h.v[2]) * g * g;
+      s0[i] = m;
+      s1[i] = v;
+      const float mh = m / h.v[5];
+      if (h.v[7] != 0.f) w -= h.v[0] * mh * h.v[7] * sqrtf(h.v[6]) / (sqrtf(v) + h.v[3]);
+      else w -= h.v[0] * mh;
+    } else if constexpr (ALGO == OPT_RPROP) {       // h: eta-, eta+, step min, step max
+      const float sgn = g * s0[i];
+      float st = s1[i];
+      if (sgn > 0.f) st = fminf(st * h.v[1], h.v[3]);
+      else if (sgn < 0.f) { st = fmaxf(st * h.v[0], h.v[2]); g = 0.f; }
+      s1[i] = st;
+      s0[i] = g;
+      w -= (g > 0.f ? st : (g < 0.f ? -st : 0.f));
+    } else {                                        // ASGD; h: eta, lambd, wd, mu
+      g += h.v[2] * w;
+      w *= 1.f - h.v[1] * h.v[0];
+      w -= h.v[0] * g;
+      s0[i] = h.v[3] != 1.f ? s0[i] + (w - s0[i]) * h.v[3] : w;
+    }
+    p[i] = w;
+  }
+}
+}  // namespace
+
+// algo: 0 Adagrad, 1 RMSprop, 2 Adadelta, 3 Adamax, 4 NAdam, 5 RAdam, 6 Rprop, 7 ASGD. p, grad: f32 [n]; s0..s2: the algorithm's state buffers
+// (unused ones may be null); hp: HOST array of 12 floats, the per-step scalars in the order documented beside each branch of the kernel;
+// maximize != 0 negates the gradient.
+FT_EXPORT int ft_foreach_opt(int algo, float* p, const float* grad, float* s0, float* s1, float* s2, int64_t n, const float* hp, int maximize,
+                             cudaStream_t st) {
+  if (n <= 0 || hp == nullptr || algo < 0 || algo > 7) return FT_ERR_ARG;
+  OptHp h;
+  for (int i = 0; i < 12; i++) h.v[i] = hp[i];
+  const int grid = flat_grid((size_t)n, 256);
+  const float gs = maximize ? -1.f : 1.f;
+#define FT_OPT_CASE(A) case A: foreach_opt_kernel<A><<<grid, 256, 0, st>>>(p, grad, s0, s1, s2, (size_t)n, h, gs); break;
+  switch (algo) {
+    FT_OPT_CASE(0) FT_OPT_CASE(1) FT_OPT_CASE(2) FT_OPT_CASE(3) FT_OPT_CASE(4) FT_OPT_CASE(5) FT_OPT_CASE(6) FT_OPT_CASE(7)
+  }
+#undef FT_OPT_CASE
+  return (int)cudaGetLastError();
+}

@@ -410,16 +410,8 @@ class ParamKey:
 OptimizerState = Dict[str, Dict[str, List[float]]]           # saved form: parameter key -> named buffers as flat f64 lists (optimizer.rs:8)
 
 
-Adamax = _named(torch.optim.Adamax, "Adamax", "Adamax (infinity-norm Adam).", AdamaxConfig)
-NAdam = _named(torch.optim.NAdam, "NAdam", "Adam with Nesterov momentum.", NAdamConfig)
-RAdam = _named(torch.optim.RAdam, "RAdam", "Rectified Adam.", RAdamConfig)
-Adagrad = _named(torch.optim.Adagrad, "Adagrad", "Adagrad.", AdagradConfig)
-Adadelta = _named(torch.optim.Adadelta, "Adadelta", "Adadelta.", AdadeltaConfig)
-Rmsprop = _named(torch.optim.RMSprop, "Rmsprop", "RMSprop.", RmspropConfig)
-Rprop = _named(torch.optim.Rprop, "Rprop", "Resilient backpropagation.", RpropConfig)
-Asgd = _named(torch.optim.ASGD, "Asgd", "Averaged SGD.", AsgdConfig)
-SparseAdam = _named(torch.optim.SparseAdam, "SparseAdam", "Adam for sparse gradients (embedding tables).", SparseAdamConfig)
-Lbfgs = _named(torch.optim.LBFGS, "Lbfgs", "L-BFGS with optional strong-Wolfe line search (``line_search_fn='strong_wolfe'``).", LbfgsConfig)
+# Adamax, NAdam, RAdam, Adagrad, Adadelta, Rmsprop, Rprop, Asgd, SparseAdam and Lbfgs are implemented in optim/elementwise.py (one shared
+# element-wise CUDA kernel plus the tensor-operation forms) and re-exported at the end of this module.
 LineSearchFn = str
 
 
@@ -656,3 +648,6 @@ def elemwise_max(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 def scalar_on(value: float, like: torch.Tensor) -> torch.Tensor:
     return torch.full((), value, device=like.device, dtype=like.dtype)
+
+
+from .elementwise import Adamax, NAdam, RAdam, Adagrad, Adadelta, Rmsprop, Rprop, Asgd, SparseAdam, Lbfgs  # noqa: E402,F401

@@ -183,3 +183,13 @@ def test_grad_norm_and_scale():
     a2 = a.clone()
     ops.scale_(a2, 1.0, coef)
     assert torch.allclose(a2, a * coef, rtol=1e-6, atol=1e-7)
+
+
+def test_elementwise_optimizer_kernel_matches_the_tensor_operation_forms():
+    """ft_foreach_opt (one launch per parameter) against the same recurrences evaluated as tensor operations on the CPU."""
+    from ferrotorch_b200 import optim as O
+    from tests.test_optim_elementwise_cpu import CASES, _run
+    for ours, _, kw in CASES:
+        dev, _ = _run(ours, kw, steps=12, device="cuda")
+        cpu, _ = _run(ours, kw, steps=12, device="cpu")
+        assert (dev - cpu).abs().max().item() < 2e-5, (ours.__name__, kw, (dev - cpu).abs().max().item())

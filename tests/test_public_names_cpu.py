@@ -459,9 +459,10 @@ def test_optimizer_configs_and_averaging_strategy():
         c = cfg().with_lr(0.05)
         assert c.lr == 0.05 and cfg().lr != 0.05 or cfg().lr == 0.05
         import dataclasses
-        assert torch.equal(run(lambda ps: ours(ps, c)), run(lambda ps: ref(ps, **dataclasses.asdict(c)))), ours.__name__
+        # own implementations of the update rules: the same numbers up to the rounding of a different operation order
+        assert torch.allclose(run(lambda ps: ours(ps, c)), run(lambda ps: ref(ps, **dataclasses.asdict(c))), rtol=0, atol=1e-6), ours.__name__
     assert O.RmspropConfig().with_centered(True).with_momentum(0.5).centered and O.NAdamConfig().momentum_decay == 4e-3 and O.AsgdConfig().t0 == 1e6
-    assert torch.equal(run(lambda ps: O.Adamax(ps, lr=0.01)), run(lambda ps: torch.optim.Adamax(ps, lr=0.01)))
+    assert torch.allclose(run(lambda ps: O.Adamax(ps, lr=0.01)), run(lambda ps: torch.optim.Adamax(ps, lr=0.01)), rtol=0, atol=1e-6)
     lb = O.Lbfgs([torch.nn.Parameter(w0.clone())], O.LbfgsConfig(line_search_fn="strong_wolfe", history_size=5))
     assert lb.param_groups[0]["history_size"] == 5 and lb.param_groups[0]["line_search_fn"] == "strong_wolfe"
 
