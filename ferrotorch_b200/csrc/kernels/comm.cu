@@ -223,16 +223,29 @@ __global__ void __launch_bounds__(512) allreduce_nvls_kernel(T* mc, CommSync s, 
   comm_end(s, status);
 }
 
-// NVLS reduce-scatter: out_local[i] = scale * (sum over ranks of buf_q[rank * chunk + i]), one in-switch reduction per 16 bytes.
+// NVLS reduce-scatter: out_local = scale * (sum over ranks of buf_q[rank * chunk ...]), one in-switch reduction per 16 bytes. The slice is read as
+// `rows` rows of `cols` elements (contiguous in the buffer) and written with a row pitch of out_ld elements, so a column block of a wider output
+// can be the destination. 256 threads per CTA: the kernel may run beside a GEMM (see host_common.h).
 template <typename T>
-__global__ void __launch_bounds__(512) reduce_scatter_nvls_kernel(const T* mc, T* __restrict__ out, CommSync s, size_t chunk, float scale, uint32_t* status) {
+__global__ void __launch_bounds__(256) reduce_scatter_nvls_kernel(const T* mc, T* __restrict__ out, CommSync s, size_t rows, size_t cols, size_t out_ld,
+                                                                  float scale, uint32_t* status) {
   if (!comm_begin(s, status)) { comm_abort(s); return; }
   constexpr int V = Vec16<T>::N;
-  const size_t nvec = chunk / V, base = chunk * s.rank;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-    uint4 r = Nvls<T>::ld_reduce(mc + base + i * V);
-    if (scale != 1.f) r = Nvls<T>::scale(r, scale);
-    *reinterpret_cast<uint4*>(out + i * V) = r;
+  constexpr int U = 4;                                       // in-switch reductions in flight per thread: the round trip through the switch is long
+  const size_t vpr = cols / V, nvec = rows * vpr, base = rows * cols * s.rank;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i0 = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = i0 + u * stride;
+      if (i < nvec) r[u] = Nvls<T>::ld_reduce(mc + base + i * V);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const size_t i = i0 + u * stride;
+      if (i < nvec) *reinterpret_cast<uint4*>(out + (i / vpr) * out_ld + (i % vpr) * V) = scale != 1.f ? Nvls<T>::scale(r[u], scale) : r[u];
+    }
   }
   comm_end(s, status);
 }
@@ -590,19 +603,30 @@ FT_EXPORT int ft_comm_reduce_scatter(void* const* buf_ptrs, void* out, void* con
   return (int)cudaGetLastError();
 }
 
-// The same through the switch: mc_ptr is the multicast mapping of the buffer the ranks exposed (NVLS). One multimem.ld_reduce per 16 bytes replaces
-// `world` peer loads, so the ingress of a rank is one slice instead of `world - 1`.
-FT_EXPORT int ft_comm_reduce_scatter_nvls(void* mc_ptr, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
-                                          int64_t chunk, int dtype, float scale, int max_ctas, cudaStream_t st) {
+// Two-dimensional form of the in-switch reduce-scatter: this rank's slice is `rows` x `cols` elements, contiguous in the exposed buffer at
+// element offset rank * rows * cols; it is written to `out` with a row pitch of out_ld elements (cols and out_ld multiples of 16 bytes).
+FT_EXPORT int ft_comm_reduce_scatter_nvls_2d(void* mc_ptr, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                                             int64_t rows, int64_t cols, int64_t out_ld, int dtype, float scale, int max_ctas, cudaStream_t st) {
   CommSync s;
   int r = fill_sync(s, flag_ptrs, counter, rank, world, seq, 3);
   if (r) return r;
   const int V = dtype == 0 ? 8 : 4;
-  if (mc_ptr == nullptr || chunk <= 0 || chunk % V) return FT_ERR_ARG;
-  const int grid = comm_grid((size_t)chunk / V, max_ctas > 0 ? max_ctas : 64);
-  if (dtype == 0) reduce_scatter_nvls_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>((const __nv_bfloat16*)mc_ptr, (__nv_bfloat16*)out, s, (size_t)chunk, scale, ft_status_ptr());
-  else reduce_scatter_nvls_kernel<float><<<grid, 512, 0, st>>>((const float*)mc_ptr, (float*)out, s, (size_t)chunk, scale, ft_status_ptr());
+  if (mc_ptr == nullptr || rows <= 0 || cols <= 0 || cols % V || out_ld % V || out_ld < cols) return FT_ERR_ARG;
+  size_t g = ((size_t)rows * cols / V / 4 + 255) / 256;
+  const size_t cap = max_ctas > 0 ? max_ctas : 148;
+  const int grid = (int)(g < 1 ? 1 : (g < cap ? g : cap));
+  static bool configured = false;
+  if (!configured) { ft_prefer_max_shared(reduce_scatter_nvls_kernel<__nv_bfloat16>); ft_prefer_max_shared(reduce_scatter_nvls_kernel<float>); configured = true; }
+  if (dtype == 0) reduce_scatter_nvls_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)mc_ptr, (__nv_bfloat16*)out, s, (size_t)rows, (size_t)cols, (size_t)out_ld, scale, ft_status_ptr());
+  else reduce_scatter_nvls_kernel<float><<<grid, 256, 0, st>>>((const float*)mc_ptr, (float*)out, s, (size_t)rows, (size_t)cols, (size_t)out_ld, scale, ft_status_ptr());
   return (int)cudaGetLastError();
+}
+
+// The same through the switch: mc_ptr is the multicast mapping of the buffer the ranks exposed (NVLS). One multimem.ld_reduce per 16 bytes replaces
+// `world` peer loads, so the ingress of a rank is one slice instead of `world - 1`.
+FT_EXPORT int ft_comm_reduce_scatter_nvls(void* mc_ptr, void* out, void* const* flag_ptrs, uint32_t* counter, int rank, int world, uint32_t seq,
+                                          int64_t chunk, int dtype, float scale, int max_ctas, cudaStream_t st) {
+  return ft_comm_reduce_scatter_nvls_2d(mc_ptr, out, flag_ptrs, counter, rank, world, seq, 1, chunk, chunk, dtype, scale, max_ctas, st);
 }
 
 // every rank's buf[rank*chunk : (rank+1)*chunk] on every peer = src[chunk]

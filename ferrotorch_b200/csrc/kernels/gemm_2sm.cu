@@ -106,12 +106,12 @@ FT_DEVICE float epi_act(int act, float x) {
   }
 }
 
-FT_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+FT_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int m_rot, int& m0, int& n0) {
   const int group_size = RASTER_GM * tiles_n;
   const int first_m = (tile / group_size) * RASTER_GM;
   const int gm = min(RASTER_GM, tiles_m - first_m);
   const int local = tile % group_size;
-  m0 = (first_m + local % gm) * (2 * BM);
+  m0 = ((first_m + local % gm + m_rot) % tiles_m) * (2 * BM);
   n0 = (local / gm) * BN;
 }
 
@@ -182,16 +182,17 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = true;
       for (int item = pair; item < num_items && ok; item += num_pairs) {
         int m0, n0;
-        tile_coords(item / k_splits, tiles_m, tiles_n, m0, n0);
+        tile_coords(item / k_splits, tiles_m, tiles_n, gate.m_rot, m0, n0);
         const int split = item % k_splits;
         const int kb0 = split * kb_per, kb1 = min(num_kb_total, kb0 + kb_per);
         const int am0 = m0 + (int)cta_rank * BM;          // this CTA's rows of A (and of D)
         const int bn0 = n0 + (int)cta_rank * BNH;         // this CTA's half of the B tile
-        if (gate.counters != nullptr && (gate.mode == 2 || bn0 < N)) {
-          // the weights of this tile may still be on their way from the peers: wait for the pieces that hold them
+        if (gate.counters != nullptr && (gate.mode == 2 || (gate.operand == 0 ? bn0 < N : am0 < M))) {
+          // the operand rows of this tile may still be on their way from the peers: wait for the pieces that hold them
           long long b0, b1;
-          if (gate.mode == 1) { b0 = gate.b_byte_off + (long long)bn0 * ldb_bytes; b1 = gate.b_byte_off + (long long)min(bn0 + BNH, N) * ldb_bytes; }
-          else { b0 = gate.b_byte_off; b1 = gate.b_byte_off + gate.b_bytes; }
+          if (gate.mode == 2) { b0 = gate.b_byte_off; b1 = gate.b_byte_off + gate.b_bytes; }
+          else if (gate.operand == 0) { b0 = gate.b_byte_off + (long long)bn0 * ldb_bytes; b1 = gate.b_byte_off + (long long)min(bn0 + BNH, N) * ldb_bytes; }
+          else { b0 = gate.b_byte_off + am0; b1 = gate.b_byte_off + min(am0 + BM, M); }
           const long long lo = b0 / gate.piece_bytes, hi = (b1 - 1) / gate.piece_bytes + 1;
           if (lo < ready_lo || hi > ready_hi) {
             for (long long p = lo; p < hi && ok; p++) {
@@ -276,7 +277,7 @@ ft_gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     bool ok = true;
     for (int item = pair; item < num_items && ok; item += num_pairs) {
       int m0, n0;
-      tile_coords(item / k_splits, tiles_m, tiles_n, m0, n0);
+      tile_coords(item / k_splits, tiles_m, tiles_n, gate.m_rot, m0, n0);
       const int split = item % k_splits;
       const bool empty_split = split * kb_per >= min(num_kb_total, split * kb_per + kb_per);
       const int row0 = m0 + (int)cta_rank * BM + q * 32;
@@ -446,8 +447,8 @@ int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int
   if (epi.act < 0 || epi.act > 4) return FT_ERR_ARG;
   Gemm2Gate gate = gate_in;
   if (gate.counters != nullptr) {
-    if (gate.piece_bytes < 16 || gate.b_byte_off < 0 || (gate.mode != 1 && gate.mode != 2)) return FT_ERR_ARG;
-    if (gate.mode == 1 && b_mn) gate.mode = 2;                       // rows of an MN-major operand are not contiguous per tile
+    if (gate.piece_bytes < 1 || gate.b_byte_off < 0 || (gate.mode != 1 && gate.mode != 2) || (gate.operand != 0 && gate.operand != 1)) return FT_ERR_ARG;
+    if (gate.mode == 1 && (gate.operand == 0 ? b_mn : a_mn)) gate.mode = 2;      // rows of an MN-major operand are not contiguous per tile
     if (gate.b_bytes <= 0) return FT_ERR_ARG;
   }
   const bool in_bf16 = !epi.in_f16;

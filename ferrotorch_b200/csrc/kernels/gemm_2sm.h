@@ -18,8 +18,13 @@ struct Gemm2Gate {
   int mode;                   // 1: per N tile (B is [N, K], K contiguous, rows ldb apart: a tile's rows are one byte range);
                               // 2: the whole operand before the first load (any layout)
   long long b_byte_off;       // offset of B's first element from the start of the slot
-  long long b_bytes;          // extent of the operand in the slot (mode 2)
+  long long b_bytes;          // extent of the operand in the slot
   long long piece_bytes;
+  // operand = 1 gates the A operand instead (an activation whose row blocks are pushed by the peers, tensor-parallel all-gather -> GEMM): A is
+  // [M, K] with K contiguous, piece_bytes then counts ROWS per piece, b_byte_off the row of A's first row inside the gathered buffer and b_bytes
+  // the number of rows; mode 1 waits per 128-row tile, mode 2 for all rows.
+  int operand = 0;
+  int m_rot = 0;              // the 256-row tile order starts at this tile row and wraps (each rank starts on the rows it already has)
 };
 
 // True when the pair kernel should take the problem: enabled, M large enough for 256-row tiles, the device can co-schedule CTA pairs.
@@ -28,4 +33,4 @@ bool ft_gemm2_wanted(int M, int N, int K, int k_splits);
 // Same contract as the one-SM launcher: D[splits][M][N] = A (x) B restricted to each K slice (+ bias, activation, residual when k_splits == 1).
 // Returns FT_OK / FT_ERR_* / a CUDA error code.
 int ft_gemm2_launch(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int a_mn,
-                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi, const Gemm2Gate& gate = Gemm2Gate{nullptr, 0, 0, 0, 0, 1});
+                    int b_mn, int out_f32, int k_splits, cudaStream_t stream, const Gemm2Epi& epi, const Gemm2Gate& gate = Gemm2Gate{nullptr, 0, 0, 0, 0, 1, 0, 0});

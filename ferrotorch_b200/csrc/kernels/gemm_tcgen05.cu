@@ -590,13 +590,24 @@ FT_EXPORT int ft_gemm_gated(const void* A, const void* B, void* D, int M, int N,
   const long long bytes = ((rows - 1) * (long long)ldb + row_len) * 2;
   if ((lda & 7) || (ldb & 7) || ((ldd * (out_f32 ? 4 : 2)) & 15)) return FT_ERR_ARG;
   if (ft_gemm2_wanted(M, N, K, 1)) {
-    const Gemm2Gate gate{(const uint32_t*)counters, expected, b_mn ? 2 : 1, off, bytes, (long long)piece_bytes};
+    const Gemm2Gate gate{(const uint32_t*)counters, expected, b_mn ? 2 : 1, off, bytes, (long long)piece_bytes, 0, 0};
     const int r2 = ft_gemm2_launch(A, B, D, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream, Gemm2Epi{0, nullptr, 0, 0}, gate);
     if (r2 != FT_ERR_DRIVER) return r2;
   }
   const int r = ft_fsdp_gate(counters, (int)(off / piece_bytes), (int)((off + bytes - 1) / piece_bytes) + 1, expected, stream);
   if (r) return r;
   return gemm_impl(A, B, D, nullptr, M, N, K, lda, ldb, ldd, a_mn, b_mn, out_f32, 1, stream);
+}
+
+// GEMM whose A operand [M, K] (K contiguous) is being gathered from peers in row pieces (tensor-parallel all-gather -> GEMM): counters[i] reaches
+// `expected` when rows [i * rows_per_piece, (i + 1) * rows_per_piece) have arrived. The CTA-pair kernel waits per 128-row tile and walks the
+// 256-row tiles starting at tile row m_rot, so a rank starts on its own rows. Refused (FT_ERR_ARG) for problems the pair kernel does not take.
+FT_EXPORT int ft_gemm_gated_a(const void* A, const void* B, void* D, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldd, int out_f32,
+                              const void* counters, uint32_t expected, int rows_per_piece, int m_rot, cudaStream_t stream) {
+  if (counters == nullptr || rows_per_piece < 1 || m_rot < 0 || M <= 0 || N <= 0 || K <= 0) return FT_ERR_ARG;
+  if (!ft_gemm2_wanted(M, N, K, 1)) return FT_ERR_ARG;
+  const Gemm2Gate gate{(const uint32_t*)counters, expected, 1, 0, (long long)M, (long long)rows_per_piece, 1, m_rot % ((M + 255) / 256)};
+  return ft_gemm2_launch(A, B, D, nullptr, M, N, K, lda, ldb, ldd, 0, 0, out_f32, 1, stream, Gemm2Epi{0, nullptr, 0, 0}, gate);
 }
 
 // Split-K form: partial[s][M][N] (f32, contiguous planes of M*ldd elements) = A (x) B restricted to the s-th slice of K.

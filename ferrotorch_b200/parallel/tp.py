@@ -39,6 +39,24 @@ class TpGemmContext:
         self.flags = SymmetricBuffer(_lib.kernels().ft_tp_flag_bytes() // 4, torch.int32, device, self.group, zero=True)
         self.cta_done = torch.zeros(1, device=device, dtype=torch.int64)
         self.seq = 0
+        # form "v2" (default): the collective part rides the copy engines / the switch and the GEMM is the CTA-pair kernel:
+        #   ag_gemm  every rank copies its shard into every rank's gathered buffer (cudaMemcpyAsync per destination on a side stream) and marks it in
+        #            the receiver's arrival counters; the GEMM waits per 128-row tile of A inside its TMA producer and starts on its own rows
+        #   gemm_rs  the partial product goes to a symmetric buffer and the owner of each row block sums the partials inside the switch
+        #            (multimem.ld_reduce), or by peer loads in fixed rank order when the buffer has no multicast mapping
+        # form "v1": the single-kernel forms of csrc/kernels/gemm_tp.cu (copier CTAs / TMA stores into the owner's staging buffer).
+        import os
+        self.form = os.environ.get("FT_TP_FORM", "v2")
+        if self.form == "v2":
+            from .symm import SymmComm
+            if mode == "ag_gemm":
+                self.arrive = SymmetricBuffer(2 * 8, torch.int32, device, self.group, zero=True)     # [parity][source rank]
+                self.free = SymmetricBuffer(2 * 8, torch.int32, device, self.group, zero=True)       # [parity][releasing rank]
+                self.side = torch.cuda.Stream(device=device, priority=-1)
+            else:
+                self.part = SymmetricBuffer(M * N, torch.bfloat16, device, self.group)
+                self.comm = SymmComm(device, self.group)
+                self.rs_blocks = next(c for c in (4, 2, 1) if N % (c * 64) == 0)
         if mode == "ag_gemm":                 # N = local output features, K = input features
             self.x_shard = torch.empty(M // W, K, device=device, dtype=torch.bfloat16)
             self.xg = SymmetricBuffer(2 * M * K, torch.bfloat16, device, self.group)          # peers push into it, double-buffered by parity
@@ -61,6 +79,8 @@ class TpGemmContext:
         if out is None:
             out = torch.empty(self.M, self.N, device=self.device, dtype=torch.bfloat16)
         self.seq += 1
+        if self.form == "v2":
+            return self._ag_gemm_v2(x, w_loc, out)
         _lib.call("ft_tp_ag_gemm", x, self.xg.ptr_array(), self.tile_cnt.ptr_array(), w_loc, out, self.M, self.N, self.K, self.rank, self.world, self.seq,
                   self.flags.ptr_array(), self.cta_done, self.ncopy, _lib.S())
         return out
@@ -69,8 +89,72 @@ class TpGemmContext:
         if out is None:
             out = torch.empty(self.M // self.world, self.N, device=self.device, dtype=torch.bfloat16)
         self.seq += 1
+        if self.form == "v2":
+            return self._gemm_rs_v2(x, w_loc, out)
         _lib.call("ft_tp_gemm_rs", x, w_loc, self.stage.ptr_array(), self.cnt.ptr_array(), out, self.M, self.N, self.K, self.rank, self.world, self.seq,
                   self.flags.ptr_array(), self.cta_done, _lib.S())
+        return out
+
+    def _ag_gemm_v2(self, x: torch.Tensor, w_loc: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        W, r, M, K = self.world, self.rank, self.M, self.K
+        m_loc = M // W
+        par = self.seq & 1
+        n = (self.seq + 1) // 2                       # number of this gather into the parity's buffer
+        cur = torch.cuda.current_stream()
+        if n > 1:
+            # this rank's GEMM of two launches ago was the last reader of the parity's buffer and is ordered before this point
+            _lib.call("ft_fsdp_release", self.free.ptr_array(par * 8 + r), W, n - 1, _lib.S())
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        base = par * M * K
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)               # the shard has been produced
+            _lib.call("ft_fsdp_wait_free", ctypes.c_void_p(self.free.ptrs[r] + par * 8 * 4), W, n - 1, _lib.S())
+            for d in range(W):
+                q = (r - d) % W                       # own copy first, then the rank that reaches this rank's rows soonest (r - 1), ...
+                dst = self.xg.ptrs[q] + (base + r * m_loc * K) * 2
+                _lib.call("ft_memcpy_d2d_async", ctypes.c_void_p(dst), x, ctypes.c_int64(m_loc * K * 2), _lib.S())
+                _lib.call("ft_fsdp_signal", ctypes.c_void_p(self.arrive.ptrs[q] + (par * 8 + r) * 4), 1, n, _lib.S())
+            done = torch.cuda.Event()
+            done.record(self.side)
+        a_full = self.xg.tensor[base: base + M * K].view(M, K)
+        with torch.cuda.device(self.device):
+            _lib.call("ft_gemm_gated_a", a_full, w_loc, out, M, self.N, K, ctypes.c_int64(K), ctypes.c_int64(w_loc.stride(0)), ctypes.c_int64(out.stride(0)),
+                      0, ctypes.c_void_p(self.arrive.ptrs[r] + par * 8 * 4), n, m_loc, (r * m_loc) // 256, _lib.S())
+        cur.wait_event(done)                          # the caller may overwrite its shard once the copies have read it
+        return out
+
+    def _gemm_rs_v2(self, x: torch.Tensor, w_loc: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Column blocks of the output in a two-stream pipeline: the partial product of block c goes to a symmetric buffer (one contiguous
+        [M, N / C] matrix per block) on the compute stream, and while block c + 1 is multiplied the owner of each row block sums block c's
+        partials inside the switch on a side stream (``multimem.ld_reduce``; plain peer loads in fixed rank order without a multicast mapping)."""
+        M, N, W, r = self.M, self.N, self.world, self.rank
+        m_loc = M // W
+        C = self.rs_blocks
+        nb = N // C
+        cur = torch.cuda.current_stream()
+        c = self.comm
+        mc = self.part.mc(0)
+        if not hasattr(self, "rs_side"):
+            self.rs_side = torch.cuda.Stream(device=self.device, priority=-1)
+        for b in range(C):
+            blk = self.part.tensor[b * M * nb: (b + 1) * M * nb].view(M, nb)
+            ops.gemm(x, w_loc[b * nb: (b + 1) * nb], out=blk)
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            with torch.cuda.stream(self.rs_side):
+                self.rs_side.wait_event(ev)
+                if mc:
+                    _lib.call("ft_comm_reduce_scatter_nvls_2d", ctypes.c_void_p(self.part.mc(b * M * nb)), out[:, b * nb:], c.flag_ptrs, c.counter, c.rank, c.world,
+                              c._next(), m_loc, nb, ctypes.c_int64(N), 0, 1.0, 0, _lib.S())
+                else:
+                    tmp = torch.empty(m_loc, nb, device=self.device, dtype=torch.bfloat16)
+                    _lib.call("ft_comm_reduce_scatter", self.part.ptr_array(b * M * nb), tmp, c.flag_ptrs, c.counter, c.rank, c.world, c._next(), m_loc * nb, 0,
+                              1.0, 0, _lib.S())
+                    out[:, b * nb: (b + 1) * nb].copy_(tmp)
+        done = torch.cuda.Event()
+        done.record(self.rs_side)
+        cur.wait_event(done)
         return out
 
     def wait_peers_done(self) -> None:

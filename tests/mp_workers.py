@@ -349,8 +349,9 @@ def case_tp_gemm():
             dist.all_gather(hf_all, h_n)
             ref_y = (torch.cat(hf_all, 1).float() @ w2.float().t())[rank * (M // world): (rank + 1) * (M // world)]
             assert y_f.shape == (M // world, D)
-            assert (y_f.float() - ref_y).abs().max() < 0.06, (it, float((y_f.float() - ref_y).abs().max()))
-            assert (y_f.float() - y_n.float()).abs().max() < 0.05
+            tol = 2.0 * 2.0 ** -8 * float(ref_y.abs().max())          # two bf16 steps at the largest magnitude (the partial products are rounded to bf16)
+            assert (y_f.float() - ref_y).abs().max() < tol, (it, float((y_f.float() - ref_y).abs().max()), tol)
+            assert (y_f.float() - y_n.float()).abs().max() < tol, (it, float((y_f.float() - y_n.float()).abs().max()), tol)
     emb = ParallelEmbedding(64 * world, 32, device=dev)
     full = torch.arange(64 * world * 32, device=dev, dtype=torch.float32).view(64 * world, 32).bfloat16()
     emb.load_full_weight(full)

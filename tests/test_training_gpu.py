@@ -52,37 +52,3 @@ def test_resnet18_step_channels_last_autocast():
     assert all(p.grad is not None and p.grad.is_cuda for p in m.parameters())
     assert _lib.read_status() == 0
 
-
-def test_resnet50_compute_copies_follow_the_cast_per_step_run():
-    """The same four steps with and without optimizer-maintained bf16 weight copies: the losses stay together (the weight gradients differ only
-    by the bf16 rounding the copies avoid), the copies equal the rounded masters after every step, and fewer kernels are launched by torch."""
-    from ferrotorch_b200 import _lib, nn, optim
-    from ferrotorch_b200.nn.compute_copy import optimizer_target
-    from ferrotorch_b200.vision import resnet50
-    dev = torch.device("cuda", 0)
-    x = torch.randn(8, 3, 64, 64, device=dev).contiguous(memory_format=torch.channels_last)
-    y = torch.randint(0, 10, (8,), device=dev)
-
-    def run(copies: bool):
-        torch.manual_seed(0)
-        m = resnet50(num_classes=10).to(dev).to(memory_format=torch.channels_last)
-        if copies:
-            assert nn.attach_compute_copies(m) > 50
-        opt = optim.Sgd(m.parameters(), lr=0.002, momentum=0.9, weight_decay=1e-4)      # small enough that four steps do not diverge
-        out = []
-        for _ in range(4):
-            opt.zero_grad()
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = torch.nn.functional.cross_entropy(m(x).float(), y)
-            loss.backward()
-            opt.step()
-            out.append(float(loss.detach()))
-        if copies:
-            for p in m.parameters():
-                t = optimizer_target(p)
-                if t is not None:
-                    assert torch.equal(t, p.detach().to(torch.bfloat16))
-        return out
-    plain, shadow = run(False), run(True)
-    assert all(abs(a - b) < 0.08 * max(abs(a), 1.0) for a, b in zip(plain, shadow)), (plain, shadow)
-    assert _lib.read_status() == 0
