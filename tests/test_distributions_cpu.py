@@ -1,0 +1,110 @@
+"""The distribution families implemented in distributions/families.py against torch.distributions: log_prob, entropy, moments, cdf, KL,
+sampling statistics and pathwise gradients."""
+import math
+
+import pytest
+import torch
+import torch.distributions as TD
+
+from ferrotorch_b200 import distributions as D
+
+X = torch.tensor([0.3, 1.7, 0.05])
+U = torch.tensor([0.2, 0.9, 0.55])
+A, B = torch.tensor([0.7, 2.0, 3.5]), torch.tensor([1.3, 0.6, 2.2])
+CASES = {
+    "Normal": (lambda m: m.Normal(A, B), X), "LogNormal": (lambda m: m.LogNormal(A * 0.2, B * 0.5), X), "Uniform": (lambda m: m.Uniform(-A, B + 2), X),
+    "Exponential": (lambda m: m.Exponential(A), X), "Laplace": (lambda m: m.Laplace(A, B), X), "Gumbel": (lambda m: m.Gumbel(A, B), X),
+    "Cauchy": (lambda m: m.Cauchy(A, B), X), "HalfNormal": (lambda m: m.HalfNormal(B), X), "Gamma": (lambda m: m.Gamma(A, B), X),
+    "Beta": (lambda m: m.Beta(A, B), U), "StudentT": (lambda m: m.StudentT(A + 2.5, B, A), X), "Weibull": (lambda m: m.Weibull(A, B), X),
+    "Pareto": (lambda m: m.Pareto(A * 0.01, B), X), "Kumaraswamy": (lambda m: m.Kumaraswamy(A, B), U),
+    "Bernoulli": (lambda m: m.Bernoulli(probs=U), torch.tensor([0.0, 1.0, 1.0])), "Poisson": (lambda m: m.Poisson(A), torch.tensor([0.0, 3.0, 2.0])),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_family_matches_torch(name):
+    make, x = CASES[name]
+    ours, ref = make(D), make(TD)
+    assert type(ours).__module__.startswith("ferrotorch_b200")            # implemented here, not the torch class under another name
+    assert torch.allclose(ours.log_prob(x), ref.log_prob(x), atol=1e-5, equal_nan=True), name
+    if name != "Poisson":
+        assert torch.allclose(ours.entropy(), ref.entropy(), atol=1e-5), name
+    for attr in ("mean", "variance"):
+        assert torch.allclose(getattr(ours, attr), getattr(ref, attr), atol=1e-5, equal_nan=True), (name, attr)
+    if hasattr(ours, "cdf") and name not in ("Bernoulli", "Poisson"):
+        try:
+            r = ref.cdf(x)
+        except NotImplementedError:
+            r = None
+        if r is not None:
+            assert torch.allclose(ours.cdf(x), r, atol=1e-5), name
+    assert ours.batch_shape == ref.batch_shape and ours.event_shape == ref.event_shape
+
+
+def test_categorical_dirichlet_mvn_independent():
+    lg = torch.tensor([[0.1, 0.5, -0.3], [1.0, -1.0, 0.0]])
+    c, rc = D.Categorical(logits=lg), TD.Categorical(logits=lg)
+    v = torch.tensor([1, 2])
+    assert torch.allclose(c.log_prob(v), rc.log_prob(v)) and torch.allclose(c.entropy(), rc.entropy()) and torch.equal(c.mode, rc.mode)
+    assert c.sample((5,)).shape == (5, 2) and c.enumerate_support().shape == (3, 2)
+    oh, roh = D.OneHotCategorical(probs=lg.softmax(-1)), TD.OneHotCategorical(probs=lg.softmax(-1))
+    one = torch.nn.functional.one_hot(v, 3).float()
+    assert torch.allclose(oh.log_prob(one), roh.log_prob(one)) and oh.sample().sum(-1).eq(1).all()
+    conc = torch.tensor([[0.7, 2.0, 3.5], [1.0, 1.0, 1.0]])
+    d, rd = D.Dirichlet(conc), TD.Dirichlet(conc)
+    p = torch.tensor([[0.2, 0.3, 0.5], [0.1, 0.1, 0.8]])
+    assert torch.allclose(d.log_prob(p), rd.log_prob(p), atol=1e-5) and torch.allclose(d.entropy(), rd.entropy(), atol=1e-5)
+    assert torch.allclose(d.mean, rd.mean) and torch.allclose(d.variance, rd.variance)
+    cov = torch.tensor([[2.0, 0.3], [0.3, 1.0]])
+    m, rm = D.MultivariateNormal(torch.tensor([0.5, -1.0]), covariance_matrix=cov), TD.MultivariateNormal(torch.tensor([0.5, -1.0]), covariance_matrix=cov)
+    x = torch.tensor([[0.3, 1.7], [-1.0, 0.2]])
+    assert torch.allclose(m.log_prob(x), rm.log_prob(x), atol=1e-5) and torch.allclose(m.entropy(), rm.entropy(), atol=1e-5)
+    assert torch.allclose(m.covariance_matrix, cov, atol=1e-6) and torch.allclose(m.precision_matrix, torch.linalg.inv(cov), atol=1e-5)
+    m2 = D.MultivariateNormal(torch.zeros(2), scale_tril=torch.tensor([[1.0, 0.0], [0.5, 0.8]]))
+    r2 = TD.MultivariateNormal(torch.zeros(2), scale_tril=torch.tensor([[1.0, 0.0], [0.5, 0.8]]))
+    assert torch.allclose(D.kl_divergence(m, m2), TD.kl_divergence(rm, r2), atol=1e-5)
+    ind, rind = D.Independent(D.Normal(torch.zeros(3, 4), torch.ones(3, 4) * 2), 1), TD.Independent(TD.Normal(torch.zeros(3, 4), torch.ones(3, 4) * 2), 1)
+    z = torch.randn(3, 4)
+    assert ind.batch_shape == (3,) and ind.event_shape == (4,) and torch.allclose(ind.log_prob(z), rind.log_prob(z)) and torch.allclose(ind.entropy(), rind.entropy())
+    with pytest.raises(ValueError):
+        D.MultivariateNormal(torch.zeros(2))
+    with pytest.raises(ValueError):
+        D.Categorical()
+
+
+KL_PAIRS = [(lambda m: m.Normal(A, B), lambda m: m.Normal(B, A)), (lambda m: m.Bernoulli(probs=U), lambda m: m.Bernoulli(probs=U.flip(0))),
+            (lambda m: m.Exponential(A), lambda m: m.Exponential(B)), (lambda m: m.Laplace(A, B), lambda m: m.Laplace(B, A)),
+            (lambda m: m.Gamma(A, B), lambda m: m.Gamma(B, A)), (lambda m: m.Beta(A, B), lambda m: m.Beta(B, A)),
+            (lambda m: m.Poisson(A), lambda m: m.Poisson(B)), (lambda m: m.Gumbel(A, B), lambda m: m.Gumbel(B, A)),
+            (lambda m: m.Uniform(-A, A), lambda m: m.Uniform(-A - 1, A + 2)), (lambda m: m.Dirichlet(A), lambda m: m.Dirichlet(B)),
+            (lambda m: m.Categorical(probs=U), lambda m: m.Categorical(probs=U.flip(0)))]
+
+
+@pytest.mark.parametrize("i", range(len(KL_PAIRS)))
+def test_kl_registry_matches_torch(i):
+    p, q = KL_PAIRS[i]
+    assert torch.allclose(D.kl_divergence(p(D), q(D)), TD.kl_divergence(p(TD), q(TD)), atol=1e-5)
+
+
+def test_sampling_statistics_and_pathwise_gradients():
+    torch.manual_seed(0)
+    n = 40000
+    for make in (lambda: D.Normal(1.5, 0.7), lambda: D.Gamma(3.0, 2.0), lambda: D.Beta(2.0, 5.0), lambda: D.Laplace(-1.0, 0.5),
+                 lambda: D.Gumbel(0.3, 1.2), lambda: D.Exponential(1.7), lambda: D.Weibull(1.5, 2.0), lambda: D.Uniform(-1.0, 3.0),
+                 lambda: D.StudentT(8.0, 0.5, 1.5), lambda: D.Kumaraswamy(2.0, 3.0), lambda: D.HalfNormal(1.3), lambda: D.LogNormal(0.1, 0.4)):
+        d = make()
+        s = d.sample((n,))
+        assert abs(float(s.mean()) - float(d.mean)) < 4 * float(d.stddev) / math.sqrt(n) + 1e-3, type(d).__name__
+        assert abs(float(s.var()) / float(d.variance) - 1) < 0.08, type(d).__name__
+    for d, ev in ((D.Bernoulli(probs=torch.tensor(0.3)), 0.3), (D.Poisson(torch.tensor(4.0)), 4.0)):
+        assert abs(float(d.sample((n,)).mean()) - ev) < 0.05
+    # reparameterised samples carry gradients to the parameters
+    loc, scale = torch.tensor(0.5, requires_grad=True), torch.tensor(1.5, requires_grad=True)
+    D.Normal(loc, scale).rsample((1000,)).mean().backward()
+    assert abs(float(loc.grad) - 1.0) < 1e-5 and scale.grad is not None
+    a = torch.tensor(2.0, requires_grad=True)
+    D.Gamma(a, torch.tensor(1.0)).rsample((20000,)).mean().backward()
+    assert abs(float(a.grad) - 1.0) < 0.05                               # d E[x] / d concentration = 1 / rate
+    conc = torch.tensor([1.0, 2.0, 3.0], requires_grad=True)
+    D.Dirichlet(conc).rsample((64,))[:, 0].mean().backward()
+    assert conc.grad is not None and float(conc.grad[0]) > 0 > float(conc.grad[1])
