@@ -275,9 +275,9 @@ def clip_grad_value_(parameters: Iterable[torch.Tensor], clip_value: float) -> N
 # ----------------------------------------------------------------------------------------------------------------------
 # packed sequences / resampling
 # ----------------------------------------------------------------------------------------------------------------------
-PackedSequence = torch.nn.utils.rnn.PackedSequence
-pack_padded_sequence = torch.nn.utils.rnn.pack_padded_sequence
-pad_packed_sequence = torch.nn.utils.rnn.pad_packed_sequence
+from .rnn import PackedSequence, pack_padded_sequence, pad_packed_sequence, pad_sequence, pack_sequence  # noqa: E402,F401
+
+
 class InterpolateMode(enum.Enum):
     """ferrotorch-nn/src/upsample.rs:32."""
     Nearest = "nearest"
@@ -352,11 +352,9 @@ def grid_sample(x, grid, mode="bilinear", padding_mode="zeros", align_corners=Fa
 affine_grid = F.affine_grid
 
 # functional pooling / reshaping forms the reference exports at the crate root (ferrotorch-nn/src/pooling.rs, upsample.rs)
-(max_pool1d, max_pool2d, max_pool3d, avg_pool1d, avg_pool2d, avg_pool3d, adaptive_avg_pool1d, adaptive_avg_pool2d, adaptive_avg_pool3d, adaptive_max_pool1d,
- adaptive_max_pool2d, adaptive_max_pool3d, lp_pool1d, lp_pool2d, max_unpool2d, pixel_shuffle, pixel_unshuffle, unfold, fold) = (
-    F.max_pool1d, F.max_pool2d, F.max_pool3d, F.avg_pool1d, F.avg_pool2d, F.avg_pool3d, F.adaptive_avg_pool1d, F.adaptive_avg_pool2d, F.adaptive_avg_pool3d,
-    F.adaptive_max_pool1d, F.adaptive_max_pool2d, F.adaptive_max_pool3d, F.lp_pool1d, F.lp_pool2d, F.max_unpool2d, F.pixel_shuffle, F.pixel_unshuffle,
-    F.unfold, F.fold)
+from .pooling import (max_pool1d, max_pool2d, max_pool3d, avg_pool1d, avg_pool2d, avg_pool3d, adaptive_avg_pool1d, adaptive_avg_pool2d,  # noqa: E402,F401
+                      adaptive_avg_pool3d, adaptive_max_pool1d, adaptive_max_pool2d, adaptive_max_pool3d, lp_pool1d, lp_pool2d, max_unpool2d,
+                      pixel_shuffle, pixel_unshuffle, unfold, fold)
 
 # hook signatures (ferrotorch-nn/src/hooks.rs:37-48)
 ForwardHook = Callable[[torch.Tensor, torch.Tensor], None]               # (input, output)
@@ -365,7 +363,9 @@ BackwardHook = Callable[[torch.Tensor, torch.Tensor], None]              # (grad
 
 
 def functional_pad_1d(x, pad, mode="constant", value=0.0):
-    return F.pad(x, tuple(pad), mode=mode, value=value) if mode == "constant" else F.pad(x, tuple(pad), mode=mode)
+    """Flat ``(last_lo, last_hi, ...)`` padding amounts; modes constant / reflect / replicate / circular."""
+    from .padding import pad as _pad
+    return _pad(x, pad, _enum_value(mode), value)
 
 
 functional_pad_2d = functional_pad_1d
@@ -439,7 +439,7 @@ class QuantizedModel(Module):
         self.model, self.cfg = model, cfg
         self.observers = torch.nn.ModuleDict()
         for name, m in model.named_modules():
-            if isinstance(m, (torch.nn.Linear, torch.nn.Conv2d)) or type(m).__name__ == "Linear":
+            if isinstance(m, (torch.nn.Linear, torch.nn.Conv2d)) or type(m).__name__ in ("Linear", "Conv2d"):
                 key = name.replace(".", "_") or "root"
                 self.observers[key + "_act"] = FakeQuantize(cfg)
                 self.observers[key + "_w"] = FakeQuantize(cfg)

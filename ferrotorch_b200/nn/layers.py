@@ -1,6 +1,6 @@
 """Layers. Hot layers (Linear, RMSNorm, LayerNorm, Embedding, SwiGLU, rotary embedding, attention, cross-entropy) run on the
-hand-written sm_100a kernels for bf16 CUDA tensors; the long tail re-uses PyTorch's reference semantics under the
-reference's names.
+hand-written sm_100a kernels for bf16 CUDA tensors; the long tail (activations, losses, convolutions, normalisation, pooling,
+padding, recurrent and transformer stacks) lives in the sibling modules of this package and is re-exported here.
 
 Reference parity: ferrotorch-nn/src/{activation,linear,lazy_linear,lora,se,conv,lazy_conv,lazy_conv_transpose,lazy_norm,norm,
 pooling,dropout,embedding,identity,padding,rnn,rnn_utils,attention,transformer,loss,upsample}.rs.
@@ -18,38 +18,21 @@ from .. import ops
 from ..errors import InvalidArgument, ShapeMismatch
 from .module import Module, Parameter, Buffer, Sequential, ModuleList
 
-_tnn = torch.nn
-
-
-def _wrap(name: str, torch_name: Optional[str] = None):
-    base = getattr(_tnn, torch_name or name)
-    return type(name, (base, Module), {"__doc__": f"``{name}`` with PyTorch's ``{torch_name or name}`` semantics.", "__module__": __name__})
-
-
-# -- activations (ferrotorch-nn/src/activation.rs:63-1401) ------------------------------------------------------------------------
-for _n, _t in [("ReLU", None), ("Softmax2d", None), ("GELU", None), ("SiLU", None), ("Sigmoid", None), ("Tanh", None), ("Softmax", None),
-               ("LogSoftmax", None), ("LeakyReLU", None), ("ELU", None), ("Mish", None), ("PReLU", None), ("CELU", None), ("SELU", None),
-               ("HardSigmoid", "Hardsigmoid"), ("HardSwish", "Hardswish"), ("Softplus", None), ("GLU", None), ("ReLU6", None),
-               ("Hardtanh", None), ("LogSigmoid", None), ("Softmin", None), ("Threshold", None), ("Softshrink", None),
-               ("Hardshrink", None), ("Tanhshrink", None), ("Softsign", None), ("RReLU", None)]:
-    globals()[_n] = _wrap(_n, _t)
-
-# -- conv / norm / pooling / dropout / padding / rnn / losses / misc re-used from PyTorch ---------------------------------------------
-for _n in ["Conv1d", "Conv2d", "Conv3d", "ConvTranspose1d", "ConvTranspose2d", "ConvTranspose3d", "LazyConv1d", "LazyConv2d", "LazyConv3d",
-           "LazyConvTranspose1d", "LazyConvTranspose2d", "LazyConvTranspose3d", "LazyBatchNorm1d", "LazyBatchNorm2d", "LazyBatchNorm3d",
-           "GroupNorm", "BatchNorm1d", "BatchNorm2d", "BatchNorm3d", "LocalResponseNorm", "InstanceNorm1d", "InstanceNorm2d",
-           "InstanceNorm3d", "MaxPool1d", "MaxPool2d", "MaxPool3d", "AvgPool1d", "AvgPool2d", "AvgPool3d", "AdaptiveAvgPool1d",
-           "AdaptiveAvgPool2d", "AdaptiveAvgPool3d", "AdaptiveMaxPool1d", "AdaptiveMaxPool2d", "AdaptiveMaxPool3d", "MaxUnpool2d",
-           "FractionalMaxPool2d", "LPPool1d", "LPPool2d", "Dropout", "Dropout1d", "Dropout2d", "Dropout3d", "AlphaDropout",
-           "EmbeddingBag", "Identity", "Flatten", "Unflatten", "ChannelShuffle", "CosineSimilarity", "PairwiseDistance",
-           "ConstantPad1d", "ConstantPad2d", "ConstantPad3d", "ZeroPad1d", "ZeroPad2d", "ZeroPad3d", "ReflectionPad1d", "ReflectionPad2d",
-           "ReflectionPad3d", "ReplicationPad1d", "ReplicationPad2d", "ReplicationPad3d", "CircularPad1d", "CircularPad2d", "CircularPad3d",
-           "LSTM", "GRU", "RNN", "RNNCell", "LSTMCell", "GRUCell", "TransformerEncoderLayer", "TransformerDecoderLayer",
-           "TransformerEncoder", "TransformerDecoder", "Transformer", "MSELoss", "BCEWithLogitsLoss", "HuberLoss", "KLDivLoss",
-           "CosineEmbeddingLoss", "L1Loss", "NLLLoss", "SmoothL1Loss", "BCELoss", "TripletMarginLoss", "MarginRankingLoss", "CTCLoss",
-           "PoissonNLLLoss", "MultiMarginLoss", "MultiLabelSoftMarginLoss", "HingeEmbeddingLoss", "GaussianNLLLoss", "Upsample",
-           "PixelShuffle", "PixelUnshuffle", "Unfold", "Fold"]:
-    globals()[_n] = _wrap(_n)
+# -- the long tail: every layer below is implemented in its own module of this package ------------------------------------------------------
+from .activation import *  # noqa: F401,F403,E402
+from .activation import relu, sigmoid  # noqa: E402
+from .loss import *  # noqa: F401,F403,E402
+from .conv import *  # noqa: F401,F403,E402
+from .normalization import (BatchNorm1d, BatchNorm2d, BatchNorm3d, LazyBatchNorm1d, LazyBatchNorm2d, LazyBatchNorm3d, GroupNorm,  # noqa: F401,E402
+                            InstanceNorm1d, InstanceNorm2d, InstanceNorm3d, LocalResponseNorm)
+from .pooling import (MaxPool1d, MaxPool2d, MaxPool3d, AvgPool1d, AvgPool2d, AvgPool3d, AdaptiveAvgPool1d, AdaptiveAvgPool2d,  # noqa: F401,E402
+                      AdaptiveAvgPool3d, AdaptiveMaxPool1d, AdaptiveMaxPool2d, AdaptiveMaxPool3d, LPPool1d, LPPool2d, MaxUnpool2d,
+                      FractionalMaxPool2d, PixelShuffle, PixelUnshuffle, Unfold, Fold)
+from .padding import (ConstantPad1d, ConstantPad2d, ConstantPad3d, ZeroPad1d, ZeroPad2d, ZeroPad3d, ReflectionPad1d, ReflectionPad2d,  # noqa: F401,E402
+                      ReflectionPad3d, ReplicationPad1d, ReplicationPad2d, ReplicationPad3d, CircularPad1d, CircularPad2d, CircularPad3d)
+from .misc import (Dropout, Dropout1d, Dropout2d, Dropout3d, AlphaDropout, Identity, Flatten, Unflatten, ChannelShuffle, EmbeddingBag,  # noqa: F401,E402
+                   Upsample)
+from .rnn import RNN, LSTM, GRU, RNNCell, LSTMCell, GRUCell  # noqa: F401,E402
 
 
 class PaddingMode(enum.Enum):
@@ -130,7 +113,7 @@ class LoRALinear(Module):
         self.lora_a = Parameter(torch.empty(rank, base.in_features, device=dev, dtype=dt))
         self.lora_b = Parameter(torch.zeros(base.out_features, rank, device=dev, dtype=dt))
         torch.nn.init.kaiming_uniform_(self.lora_a, a=math.sqrt(5))
-        self.drop = torch.nn.Dropout(dropout) if dropout > 0 else None
+        self.drop = Dropout(dropout) if dropout > 0 else None
         self.merged = False
 
     def forward(self, x):
@@ -158,12 +141,12 @@ class SqueezeExcitation(Module):
 
     def __init__(self, channels: int, squeeze_channels: int):
         super().__init__()
-        self.fc1 = torch.nn.Conv2d(channels, squeeze_channels, 1)
-        self.fc2 = torch.nn.Conv2d(squeeze_channels, channels, 1)
+        self.fc1 = Conv2d(channels, squeeze_channels, 1)
+        self.fc2 = Conv2d(squeeze_channels, channels, 1)
 
     def forward(self, x):
-        s = F.adaptive_avg_pool2d(x, 1)
-        return x * torch.sigmoid(self.fc2(F.relu(self.fc1(s))))
+        s = x.mean((-2, -1), keepdim=True)
+        return x * sigmoid(self.fc2(relu(self.fc1(s))))
 
 
 # -- normalisation on our kernels -----------------------------------------------------------------------------------------------------
@@ -401,3 +384,6 @@ class CrossEntropyLoss(Module):
         if self.reduction == "mean" and target.dtype == torch.long and logits.is_cuda and logits.dim() == 2:
             return ops.cross_entropy(logits, target, self.ignore_index, self.label_smoothing)
         return F.cross_entropy(logits, target, reduction=self.reduction, ignore_index=self.ignore_index, label_smoothing=self.label_smoothing)
+
+
+from .transformer import (TransformerEncoderLayer, TransformerDecoderLayer, TransformerEncoder, TransformerDecoder, Transformer)  # noqa: F401,E402

@@ -22,6 +22,7 @@ import torch
 from .. import _lib
 from ..distributed.ddp import compute_buckets, DEFAULT_BUCKET_SIZE_BYTES
 from ..errors import InvalidArgument
+from ..nn.normalization import BatchNorm2d as _BatchNorm2d
 
 
 class _Bucket:
@@ -158,7 +159,7 @@ class DDP(torch.nn.Module):
         self._finalize()
 
 
-class SyncBatchNorm2d(torch.nn.BatchNorm2d):
+class SyncBatchNorm2d(_BatchNorm2d):
     """BatchNorm whose batch statistics are computed over all ranks: the packed ``[sum, sum_sq]`` (2*C floats) and, in backward,
     ``[sum dy, sum dy*xhat]`` are all-reduced (ferrotorch-distributed/src/sync_batch_norm.rs:236,474)."""
 
@@ -175,7 +176,7 @@ class SyncBatchNorm2d(torch.nn.BatchNorm2d):
     @classmethod
     def convert(cls, module: torch.nn.Module, process_group=None) -> torch.nn.Module:
         out = module
-        if isinstance(module, torch.nn.BatchNorm2d) and not isinstance(module, cls):
+        if isinstance(module, (_BatchNorm2d, torch.nn.BatchNorm2d)) and not isinstance(module, cls):
             out = cls(module.num_features, module.eps, module.momentum, process_group)
             out.load_state_dict(module.state_dict())
             out.to(module.weight.device)

@@ -102,7 +102,7 @@ class _ResNetLayers(nn.Module):
 
 def _freeze_bn(m: torch.nn.Module) -> None:
     for name, child in m.named_children():
-        if isinstance(child, torch.nn.BatchNorm2d):
+        if isinstance(child, (nn.BatchNorm2d, torch.nn.BatchNorm2d)):
             setattr(m, name, _FrozenBatchNorm2d(child.num_features, child.eps))
         else:
             _freeze_bn(child)

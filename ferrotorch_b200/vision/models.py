@@ -58,10 +58,10 @@ class Conv1x1(nn.Conv2d):
         return super().forward(x)
 
 
-def bn_act(bn: torch.nn.BatchNorm2d, x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = True) -> torch.Tensor:
+def bn_act(bn: "nn.BatchNorm2d", x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = True) -> torch.Tensor:
     """BatchNorm (+ residual add) (+ ReLU). Channels-last CUDA f32/bf16 activations take the fused two-stage-statistics kernels; everything else
     (CPU, NCHW, SyncBatchNorm subclasses with their own forward) the module's own path."""
-    fused = (type(bn).forward is torch.nn.BatchNorm2d.forward and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float32, torch.bfloat16)
+    fused = (type(bn).forward in (nn.BatchNorm2d.forward, torch.nn.BatchNorm2d.forward) and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float32, torch.bfloat16)
              and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last) and bn.affine and bn.track_running_stats
              and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous(memory_format=torch.channels_last))))
     if not fused:
@@ -152,9 +152,9 @@ class ResNet(nn.Module):
         self.avgpool = nn.AdaptiveAvgPool2d(1)
         self.fc = nn.Linear(512 * block.expansion, num_classes)
         for m in self.modules():
-            if isinstance(m, torch.nn.Conv2d):
+            if isinstance(m, (nn.Conv2d, torch.nn.Conv2d)):
                 torch.nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
-            elif isinstance(m, torch.nn.BatchNorm2d):
+            elif isinstance(m, (nn.BatchNorm2d, torch.nn.BatchNorm2d)):
                 torch.nn.init.ones_(m.weight)
                 torch.nn.init.zeros_(m.bias)
         if zero_init_residual:
