@@ -14,6 +14,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import nn
+from ..nn.functional import scaled_dot_product_attention as sdpa
 from ..errors import InvalidArgument, ShapeMismatch
 
 
@@ -138,7 +139,7 @@ class BertSelfAttention(nn.Module):
         if mask is not None:                                       # [B, S] 1 = keep
             am = (~mask.bool())[:, None, None, :].expand(B, 1, S, S)
             am = torch.zeros(B, 1, S, S, device=x.device, dtype=x.dtype).masked_fill(am, float("-inf"))
-        o = F.scaled_dot_product_attention(sp(self.query(x)), sp(self.key(x)), sp(self.value(x)), attn_mask=am)
+        o = sdpa(sp(self.query(x)), sp(self.key(x)), sp(self.value(x)), attn_mask=am)
         return o.transpose(1, 2).reshape(B, S, E)
 
 

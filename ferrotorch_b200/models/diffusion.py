@@ -17,6 +17,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import nn
+from ..nn.functional import scaled_dot_product_attention as sdpa
 from ..errors import InvalidArgument, ShapeMismatch
 from .bert import DropReport
 
@@ -69,7 +70,7 @@ class Attention(nn.Module):
         ctx = x if context is None else context
         B, S, _ = x.shape
         sp = lambda t: t.view(B, t.shape[1], self.heads, -1).transpose(1, 2)
-        o = F.scaled_dot_product_attention(sp(self.to_q(x)), sp(self.to_k(ctx)), sp(self.to_v(ctx)))
+        o = sdpa(sp(self.to_q(x)), sp(self.to_k(ctx)), sp(self.to_v(ctx)))
         return self.to_out[0](o.transpose(1, 2).reshape(B, S, -1))
 
 
@@ -464,7 +465,7 @@ class AttnBlock2D(nn.Module):
     def forward(self, x):
         B, C, H, W = x.shape
         h = self.group_norm(x).view(B, C, H * W).transpose(1, 2)
-        o = F.scaled_dot_product_attention(self.to_q(h)[:, None], self.to_k(h)[:, None], self.to_v(h)[:, None])[:, 0]
+        o = sdpa(self.to_q(h)[:, None], self.to_k(h)[:, None], self.to_v(h)[:, None])[:, 0]
         return x + self.to_out[0](o).transpose(1, 2).view(B, C, H, W)
 
 
@@ -786,7 +787,7 @@ class ClipSelfAttention(nn.Module):
     def forward(self, x):
         B, S, E = x.shape
         sp = lambda t: t.view(B, S, self.h, E // self.h).transpose(1, 2)
-        o = F.scaled_dot_product_attention(sp(self.q_proj(x)), sp(self.k_proj(x)), sp(self.v_proj(x)), is_causal=True)
+        o = sdpa(sp(self.q_proj(x)), sp(self.k_proj(x)), sp(self.v_proj(x)), is_causal=True)
         return self.out_proj(o.transpose(1, 2).reshape(B, S, E))
 
 

@@ -15,6 +15,7 @@ import torch
 import torch.nn.functional as F
 
 from .. import nn
+from ..nn.functional import scaled_dot_product_attention as sdpa
 from ..errors import InvalidArgument, ShapeMismatch
 from .bert import DropReport
 
@@ -176,7 +177,7 @@ class WhisperEncoderSelfAttention(nn.Module):
     def forward(self, x):
         B, S, E = x.shape
         sp = lambda t: t.view(B, S, self.h, E // self.h).transpose(1, 2)
-        o = F.scaled_dot_product_attention(sp(self.q_proj(x)), sp(self.k_proj(x)), sp(self.v_proj(x)))
+        o = sdpa(sp(self.q_proj(x)), sp(self.k_proj(x)), sp(self.v_proj(x)))
         return self.out_proj(o.transpose(1, 2).reshape(B, S, E))
 
 

@@ -4,7 +4,7 @@ from .module import (Module, Parameter, Buffer, StateDict, Reduction, Sequential
 from .layers import *  # noqa: F401,F403
 from .layers import (Linear, LazyLinear, LoRALinear, SqueezeExcitation, RMSNorm, LayerNorm, Embedding, RoPEConvention, RoPEScaling,
                      RotaryPositionEmbedding, SwiGLU, KVCache, MultiheadAttention, CrossEntropyLoss, repeat_kv, reshape_to_heads,
-                     transpose_heads_to_2d, standard_attention, flash_attention, PaddingMode, RNNNonlinearity, EmbeddingBagMode)
+                     transpose_heads_to_2d, standard_attention, flash_attention, attention_backend, PaddingMode, RNNNonlinearity, EmbeddingBagMode)
 from .extras import (KVPage, PagePool, PagedKVCache, PagedAttentionManager, BlockMask, flex_attention, causal_score_mod, alibi_score_mod,
                      relative_position_score_mod, NonLinearity, init, clip_grad_norm_, clip_grad_value_, PackedSequence,
                      pack_padded_sequence, pad_packed_sequence, interpolate, grid_sample, affine_grid, functional_pad_1d,

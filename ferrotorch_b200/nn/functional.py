@@ -30,10 +30,18 @@ def layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
 
 
 def scaled_dot_product_attention(q, k, v, attn_mask=None, dropout_p=0.0, is_causal=False, scale=None):
+    """``softmax(q k^T * scale + mask) v`` on ``[B, H, S, D]``. Without a mask or dropout this is :func:`flash_attention` (the tcgen05
+    kernels for bf16 CUDA operands with ``D <= 128``); masked CUDA calls go to the library's fused attention, and CPU calls to the
+    materialised-score form."""
     if attn_mask is None and dropout_p == 0.0:
         return flash_attention(q, k, v, is_causal, scale)
+    if q.is_cuda:
+        return _F.scaled_dot_product_attention(q, k, v, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale,
+                                               enable_gqa=q.shape[1] != k.shape[1])
     rep = q.shape[1] // k.shape[1]
-    return standard_attention(q, repeat_kv(k, rep), repeat_kv(v, rep), is_causal, scale, attn_mask)
+    o = standard_attention(q, repeat_kv(k, rep), repeat_kv(v, rep), is_causal, scale,
+                           attn_mask if attn_mask is None or attn_mask.is_floating_point() else attn_mask)
+    return o if dropout_p == 0.0 else dropout(o, dropout_p, True)
 
 
 # -- the forms written out in this package ---------------------------------------------------------------------------------------------------

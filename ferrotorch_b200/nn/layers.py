@@ -319,16 +319,34 @@ def standard_attention(q, k, v, causal: bool = False, scale: Optional[float] = N
 def flash_attention(q, k, v, causal: bool = False, scale: Optional[float] = None):
     """Tiled online-softmax attention on ``[B, H, S, D]`` (GQA when ``k``/``v`` have fewer heads).
 
-    bf16 CUDA inputs with ``D == 128`` and equal query/key lengths run on the tcgen05 kernels; anything else evaluates the
-    same math through :func:`standard_attention`."""
+    bf16 CUDA inputs with equal query/key lengths and a head dimension up to 128 (a multiple of 8) run on the tcgen05 kernels. The
+    kernels are built for ``D = 128``: smaller heads are zero-padded to 128, which changes neither the scores (the padded products are
+    zero) nor the first ``D`` output columns, at the cost of the padded FLOPs. Anything else evaluates the same math through
+    :func:`standard_attention`."""
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
-    if q.is_cuda and q.dtype == torch.bfloat16 and D == 128 and k.shape[2] == S and ops.attention.backend() == "tcgen05":
-        packed = torch.cat([q.transpose(1, 2).reshape(B * S, Hq * D), k.transpose(1, 2).reshape(B * S, Hkv * D),
-                            v.transpose(1, 2).reshape(B * S, Hkv * D)], 1)
-        o = ops.attention_packed(packed, B, S, Hq, Hkv, D, causal, scale)
-        return o.view(B, S, Hq, D).transpose(1, 2)
+    if (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == v.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0 and k.shape[2] == S
+            and v.shape[-1] == D and Hq % Hkv == 0 and ops.attention.backend() == "tcgen05"):
+        pad = 128 - D
+
+        def rows(t, H):
+            t = t.transpose(1, 2)                                           # [B, S, H, D]
+            if pad:
+                t = torch.cat([t, t.new_zeros(B, S, H, pad)], -1)
+            return t.reshape(B * S, H * 128)
+
+        packed = torch.cat([rows(q, Hq), rows(k, Hkv), rows(v, Hkv)], 1)
+        o = ops.attention_packed(packed, B, S, Hq, Hkv, 128, causal, scale if scale is not None else 1.0 / math.sqrt(D))
+        return o.view(B, S, Hq, 128)[..., :D].transpose(1, 2)
     return standard_attention(q, repeat_kv(k, Hq // Hkv), repeat_kv(v, Hq // Hkv), causal, scale)
+
+
+def attention_backend(q: torch.Tensor, k: Optional[torch.Tensor] = None) -> str:
+    """Which implementation :func:`flash_attention` takes for these operands: ``"tcgen05"`` or ``"standard"``."""
+    k = q if k is None else k
+    D = q.shape[-1]
+    ok = (q.is_cuda and q.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0 and k.shape[2] == q.shape[2] and ops.attention.backend() == "tcgen05")
+    return "tcgen05" if ok else "standard"
 
 
 class MultiheadAttention(Module):

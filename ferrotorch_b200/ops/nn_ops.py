@@ -47,9 +47,14 @@ class _BatchNormNHWC(torch.autograd.Function):
         count = float(M)
         if training:
             nb = _nblk(M, C, x.element_size())
-            partial, sums = torch.empty(nb * 2 * C, device=dev), torch.empty(2 * C, device=dev)
+            partial = torch.empty(nb * 2 * C, device=dev)
+            fused = hasattr(group, "stage")                 # a peer-memory reducer: the statistics land in its staging slot
+            sums = group.stage(2 * C) if fused else torch.empty(2 * C, device=dev)
             _lib.call("ft_bn_stats", bf, xr, M, C, partial, sums, _lib.S())
-            if group is not None:
+            if fused:
+                sums = group.reduce()
+                count *= group.world
+            elif group is not None:
                 import torch.distributed as dist
                 dist.all_reduce(sums, group=group)
                 count *= dist.get_world_size(group)
@@ -76,12 +81,16 @@ class _BatchNormNHWC(torch.autograd.Function):
         bf = int(x.dtype == torch.bfloat16)
         dev = x.device
         nb = _nblk(M, C, x.element_size())
-        partial, sums = torch.empty(nb * 2 * C, device=dev), torch.empty(2 * C, device=dev)
+        partial = torch.empty(nb * 2 * C, device=dev)
+        fused = hasattr(group, "stage")
+        sums = group.stage(2 * C) if fused else torch.empty(2 * C, device=dev)
         yr = _rows(y)[0] if y is not None else None
         dyr = _rows(dy)[0]
         _lib.call("ft_bn_bwd_stats", bf, dyr, xr, yr, mean, invstd, M, C, partial, sums, _lib.S())
         dbeta, dgamma = sums[:C].clone(), sums[C:].clone()
-        if group is not None:
+        if fused:
+            sums = group.reduce()
+        elif group is not None:
             import torch.distributed as dist
             dist.all_reduce(sums, group=group)
         dx = _like(x)

@@ -161,16 +161,34 @@ class DDP(torch.nn.Module):
 
 class SyncBatchNorm2d(_BatchNorm2d):
     """BatchNorm whose batch statistics are computed over all ranks: the packed ``[sum, sum_sq]`` (2*C floats) and, in backward,
-    ``[sum dy, sum dy*xhat]`` are all-reduced (ferrotorch-distributed/src/sync_batch_norm.rs:236,474)."""
+    ``[sum dy, sum dy*xhat]`` are summed over the group (ferrotorch-distributed/src/sync_batch_norm.rs:236,474).
 
-    def __init__(self, num_features, eps=1e-5, momentum=0.1, process_group=None):
+    Channels-last CUDA activations run the fused statistics / apply kernels with the two small sums reduced by the one-shot
+    peer-memory kernel (``comm="fused"``, the default on an NVLink box; ``comm="nccl"`` or ``FT_SYNCBN_COMM=nccl`` keeps the library
+    all-reduce); other layouts evaluate the same math with tensor ops."""
+
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, process_group=None, comm: Optional[str] = None):
         super().__init__(num_features, eps, momentum)
         self.pg = process_group
+        self.comm = comm or os.environ.get("FT_SYNCBN_COMM", "fused")
+
+    def _reducer(self, device):
+        if self.comm != "fused":
+            return self.pg if self.pg is not None else torch.distributed.group.WORLD
+        from .symm import stats_reducer
+        return stats_reducer(device, self.pg)
 
     def forward(self, x):
         import torch.distributed as dist
         if not self.training or not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(self.pg) == 1:
             return super().forward(x)
+        self._check(x)
+        if (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.shape[1] % 8 == 0 and self.momentum is not None
+                and x.is_contiguous(memory_format=torch.channels_last) and 2 * x.shape[1] <= 8192):
+            from ..ops import nn_ops
+            self.num_batches_tracked.add_(1)
+            return nn_ops.batch_norm_nhwc(x, self.weight, self.bias, self.running_mean, self.running_var, training=True,
+                                          momentum=self.momentum, eps=self.eps, group=self._reducer(x.device))
         return _SyncBNFn.apply(x, self.weight, self.bias, self, self.pg)
 
     @classmethod
@@ -178,6 +196,7 @@ class SyncBatchNorm2d(_BatchNorm2d):
         out = module
         if isinstance(module, (_BatchNorm2d, torch.nn.BatchNorm2d)) and not isinstance(module, cls):
             out = cls(module.num_features, module.eps, module.momentum, process_group)
+            out.train(module.training)
             out.load_state_dict(module.state_dict())
             out.to(module.weight.device)
         for n, c in module.named_children():

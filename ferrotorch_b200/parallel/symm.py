@@ -215,6 +215,52 @@ class SymmComm:
             raise Timeout(message=f"device-side wait timed out: kernel {kernel}, site {site}, peer {peer}")
 
 
+class SymmStatsReducer:
+    """Sum of a small f32 vector over the ranks of a group by the one-shot peer-memory kernel: the producer kernel writes its partial
+    vector straight into a staging slot in symmetric memory (:meth:`stage`), :meth:`reduce` then reads every peer's slot and returns
+    the total in local memory. Used for the ``[sum, sum_sq]`` and ``[sum dy, sum dy*xhat]`` vectors of synchronised batch norm
+    (ferrotorch-distributed/src/sync_batch_norm.rs:236,474).
+
+    Four slots rotate: a rank can be at most one reduction ahead of its slowest peer (finishing a reduction needs every peer's arrival),
+    so the slot a peer may still be reading is never the one being written."""
+
+    SLOTS = 4
+
+    def __init__(self, device, group=None, capacity: int = 8192):
+        self.comm = SymmComm(device, group)
+        self.group, self.world, self.rank = self.comm.group, self.comm.world, self.comm.rank
+        self.capacity = (capacity + 3) // 4 * 4
+        self.buf = SymmetricBuffer(self.SLOTS * self.capacity, torch.float32, device, group, zero=True)
+        self._i = 0
+        self._staged = None
+
+    def stage(self, numel: int) -> torch.Tensor:
+        if numel > self.capacity:
+            raise ValueError(f"{numel} values exceed the staging capacity {self.capacity}")
+        self._i = (self._i + 1) % self.SLOTS
+        off = self._i * self.capacity
+        self._staged = (off, numel)
+        return self.buf.tensor[off: off + numel]
+
+    def reduce(self) -> torch.Tensor:
+        off, numel = self._staged
+        out = torch.empty(numel, device=self.buf.tensor.device, dtype=torch.float32)
+        return self.comm.all_reduce_small(self.buf, out, numel, off)
+
+
+_stats_reducers: dict = {}
+
+
+def stats_reducer(device, group=None) -> SymmStatsReducer:
+    """One reducer per (device, group), created on first use (collective: every rank of the group must call it at the same point)."""
+    import torch.distributed as dist
+    g = group if group is not None else dist.group.WORLD
+    key = (torch.device(device).index, g.group_name)
+    if key not in _stats_reducers:
+        _stats_reducers[key] = SymmStatsReducer(device, g)
+    return _stats_reducers[key]
+
+
 class FusedShardedAdamW:
     """Reduce-scatter + sharded AdamW (+ all-gather) of one flat unit in a single kernel over peer memory.
 

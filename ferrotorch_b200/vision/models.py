@@ -61,18 +61,25 @@ class Conv1x1(nn.Conv2d):
 def bn_act(bn: "nn.BatchNorm2d", x: torch.Tensor, residual: Optional[torch.Tensor] = None, relu: bool = True) -> torch.Tensor:
     """BatchNorm (+ residual add) (+ ReLU). Channels-last CUDA f32/bf16 activations take the fused two-stage-statistics kernels; everything else
     (CPU, NCHW, SyncBatchNorm subclasses with their own forward) the module's own path."""
-    fused = (type(bn).forward in (nn.BatchNorm2d.forward, torch.nn.BatchNorm2d.forward) and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float32, torch.bfloat16)
-             and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last) and bn.affine and bn.track_running_stats
+    sync = hasattr(bn, "_reducer")                  # SyncBatchNorm2d: same kernels, the two small sums reduced over the group
+    fused = ((sync or type(bn).forward in (nn.BatchNorm2d.forward, torch.nn.BatchNorm2d.forward)) and x.is_cuda and x.dim() == 4
+             and x.dtype in (torch.float32, torch.bfloat16) and x.shape[1] % 8 == 0 and x.is_contiguous(memory_format=torch.channels_last)
+             and bn.affine and bn.track_running_stats and bn.momentum is not None
              and (residual is None or (residual.dtype == x.dtype and residual.is_contiguous(memory_format=torch.channels_last))))
     if not fused:
         out = bn(x)
         if residual is not None:
             out = out + residual
         return torch.relu(out) if relu else out
+    group = None
+    if sync and bn.training:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(bn.pg) > 1:
+            group = bn._reducer(x.device)
     if bn.training and bn.num_batches_tracked is not None:
         bn.num_batches_tracked.add_(1)
     return ops.nn_ops.batch_norm_nhwc(x, bn.weight, bn.bias, bn.running_mean, bn.running_var, residual=residual, relu=relu, training=bn.training,
-                                      momentum=0.1 if bn.momentum is None else bn.momentum, eps=bn.eps)
+                                      momentum=bn.momentum, eps=bn.eps, group=group)
 
 
 def max_pool(x: torch.Tensor, k: int, s: int, p: int) -> torch.Tensor:

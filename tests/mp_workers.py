@@ -315,6 +315,25 @@ def case_ddp():
     ob.square().sum().backward()
     assert torch.allclose(xa.grad, xb.grad, atol=1e-3)
     assert torch.allclose(ours.running_var, theirs.running_var, atol=1e-4)
+    # channels-last activations: fused statistics kernels, sums reduced by the one-shot peer-memory kernel; several layers in a row
+    # (staging slots rotate) and three steps
+    torch.manual_seed(6)
+    fused = [SyncBatchNorm2d(16).to(dev) for _ in range(3)]
+    ref = [torch.nn.SyncBatchNorm(16).to(dev) for _ in range(3)]
+    for step in range(3):
+        xs = (torch.randn(4, 16, 6, 5, device=dev) * (rank + 1) + rank).contiguous(memory_format=torch.channels_last)
+        xa, xb = xs.clone().requires_grad_(True), xs.clone().requires_grad_(True)
+        ha, hb = xa, xb
+        for fa, fb in zip(fused, ref):
+            ha, hb = fa(ha) * 1.5, fb(hb) * 1.5
+        assert torch.allclose(ha, hb, atol=1e-4), (ha - hb).abs().max().item()
+        ha.square().sum().backward()
+        hb.square().sum().backward()
+        assert torch.allclose(xa.grad, xb.grad, atol=2e-3, rtol=1e-3), (xa.grad - xb.grad).abs().max().item()
+        for fa, fb in zip(fused, ref):
+            assert torch.allclose(fa.weight.grad, fb.weight.grad, atol=2e-3, rtol=1e-3)
+            assert torch.allclose(fa.running_mean, fb.running_mean, atol=1e-4) and torch.allclose(fa.running_var, fb.running_var, atol=1e-3)
+            fa.weight.grad = fb.weight.grad = None
     from ferrotorch_b200 import _lib
     assert _lib.read_status() == 0
     if rank == 0:

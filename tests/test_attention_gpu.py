@@ -69,3 +69,28 @@ def test_attention_packed_autograd_any_backend():
     (ref,) = torch.autograd.grad(ro, leaf, g.float())
     assert (o.float() - ro).abs().max().item() < 2e-2
     assert ((qkv.grad.float() - ref).norm() / ref.norm()).item() < 3e-2
+
+
+@pytest.mark.parametrize("D,causal,Hq,Hkv,S", [(64, False, 4, 4, 197), (64, True, 4, 2, 256), (96, False, 2, 2, 130), (32, False, 2, 1, 64)])
+def test_small_head_dims_run_on_the_padded_tcgen05_route(D, causal, Hq, Hkv, S):
+    """Head dimensions below 128 are zero-padded into the D = 128 kernels: values and gradients against the f32 materialised form."""
+    import ferrotorch_b200.nn as nn
+    torch.manual_seed(0)
+    B = 2
+    q = torch.randn(B, Hq, S, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, Hkv, S, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, Hkv, S, D, device="cuda", dtype=torch.bfloat16)
+    assert nn.attention_backend(q, k) == "tcgen05"
+    qa, ka, va = (t.clone().requires_grad_() for t in (q, k, v))
+    qb, kb, vb = (t.float().clone().requires_grad_() for t in (q, k, v))
+    o = nn.flash_attention(qa, ka, va, causal)
+    rep = Hq // Hkv
+    ref = nn.standard_attention(qb, nn.repeat_kv(kb, rep), nn.repeat_kv(vb, rep), causal)
+    assert o.shape == ref.shape
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()  # noqa: E731
+    assert rel(o, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (o.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    for a, b in ((qa, qb), (ka, kb), (va, vb)):
+        assert rel(a.grad, b.grad) < 3e-2
