@@ -41,7 +41,7 @@ def main():
     ids = torch.randint(0, cfg.vocab_size, (1, a.prompt_len), device=a.device, generator=torch.Generator(device=a.device).manual_seed(0))
     if a.engine == "tp":
         from ferrotorch_b200.models.llama_infer import LlamaTPEngine, TPContext
-        eng = LlamaTPEngine(cfg, TPContext(), batch=1, max_seq=a.prompt_len + a.new + 16, weights=W)
+        eng = LlamaTPEngine(cfg, TPContext(a.device), max_batch=1, max_seq=a.prompt_len + a.new + 16, device=a.device, weights=W)
         print("tp engine:", eng.generate(ids, a.new)[0].tolist())
         return
     Wf = {k: v.float() for k, v in W.items()}

@@ -1,0 +1,42 @@
+"""The example entry points run end to end on CPU with the tiny preset; the logits dump agrees with the ``transformers`` evaluation of the
+same checkpoint."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _run(*args, timeout=300):
+    r = subprocess.run([sys.executable, *map(str, args)], cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return r.stdout
+
+
+def test_inference_dump_matches_transformers(tmp_path):
+    pytest.importorskip("transformers")
+    ckpt, dump = tmp_path / "tiny_llama", tmp_path / "dump.bin"
+    _run(ROOT / "examples/llm_inference_dump.py", "--write-random", ckpt)
+    assert (ckpt / "config.json").exists() and (ckpt / "model.safetensors").exists()
+    out = _run(ROOT / "examples/llm_inference_dump.py", "--model-dir", ckpt, "--output", dump)
+    assert "logits [12, 1024]" in out
+    out = _run(ROOT / "examples/verify_llm_inference.py", "--model-dir", ckpt, "--dump", dump, "--tolerance", "1e-4")
+    assert out.strip().splitlines()[-1].startswith("OK"), out
+    # a corrupted dump is rejected
+    raw = bytearray(dump.read_bytes())
+    raw[-4000:] = bytes(4000)
+    dump.write_bytes(bytes(raw))
+    r = subprocess.run([sys.executable, str(ROOT / "examples/verify_llm_inference.py"), "--model-dir", str(ckpt), "--dump", str(dump), "--tolerance", "1e-4"],
+                       cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 1 and "FAIL" in r.stdout
+
+
+def test_llama_entry_point_and_sparsity_report_run_on_cpu():
+    out = _run(ROOT / "examples/llama3_8b_gpu.py", "--preset", "tiny", "--device", "cpu", "hello world")
+    assert "prefill of 11 tokens" in out and "next token" in out
+    out = _run(ROOT / "examples/prosparse_sparsity.py", "--preset", "tiny", "--device", "cpu", "--threshold", "0.02")
+    assert "FatRelu(0.02)" in out and "mean MLP sparsity" in out
+    share = float(out.strip().splitlines()[-1].split(":")[1].split("%")[0])
+    assert 40.0 < share < 65.0          # random weights: about half of the gate pre-activations fall below the threshold
