@@ -180,8 +180,9 @@ def relative_position_score_mod(bias: torch.Tensor):
     max_dist = (bias.shape[1] - 1) // 2
 
     def mod(score, b, h, q_idx, kv_idx):
-        rel = (kv_idx - q_idx).clamp(-max_dist, max_dist) + max_dist
-        return score + bias.to(score.device)[:, rel]
+        rel = (kv_idx - q_idx).clamp(-max_dist, max_dist) + max_dist            # broadcast index grid [..., Sq, Sk]
+        rel = rel.reshape(rel.shape[-2], rel.shape[-1])
+        return score + bias.to(score.device)[:, rel].unsqueeze(0)               # [1, heads, Sq, Sk]
     return mod
 
 

@@ -90,13 +90,20 @@ class HookedModule(Module):
         return self.inner(*a, **k)
 
     def register_forward_hook_fn(self, fn) -> HookHandle:
-        return HookHandle(self.inner.register_forward_hook(fn))
+        """``fn(input, output)`` after every forward; a non-None return value replaces the output (hooks.rs:37)."""
+        return HookHandle(self.inner.register_forward_hook(lambda _m, inp, out: fn(inp[0] if len(inp) == 1 else inp, out)))
 
     def register_forward_pre_hook_fn(self, fn) -> HookHandle:
-        return HookHandle(self.inner.register_forward_pre_hook(fn))
+        """``fn(input) -> replacement input or None`` before every forward (hooks.rs:42)."""
+        def pre(_m, inp):
+            r = fn(inp[0] if len(inp) == 1 else inp)
+            return None if r is None else (r if isinstance(r, tuple) else (r,))
+        return HookHandle(self.inner.register_forward_pre_hook(pre))
 
     def register_backward_hook_fn(self, fn) -> HookHandle:
-        return HookHandle(self.inner.register_full_backward_hook(fn))
+        """``fn(grad_input, grad_output)`` when the gradients of the wrapped module have been computed (hooks.rs:48)."""
+        return HookHandle(self.inner.register_full_backward_hook(
+            lambda _m, gi, go: fn(gi[0] if len(gi) == 1 else gi, go[0] if len(go) == 1 else go)))
 
 
 class Sequential(torch.nn.Sequential, Module):

@@ -11,10 +11,9 @@ from typing import Dict, Iterable, List, Optional
 
 import torch
 
-from ..errors import InvalidArgument
-import torch.optim.swa_utils
-
 from .. import ops
+from ..errors import InvalidArgument
+from .scheduler import LrScheduler
 
 
 @dataclass
@@ -226,5 +225,37 @@ class AveragedModel(torch.nn.Module):
         self.n_averaged += 1
 
 
-class Swalr(torch.optim.swa_utils.SWALR):
-    """Anneals every group's learning rate to a constant SWA value."""
+class Swalr(LrScheduler):
+    """Anneals every group's learning rate from its current value to a constant ``swa_lr`` over ``anneal_epochs`` steps (cosine or linear
+    interpolation) and holds it there (ferrotorch-optim/src/swa.rs; PyTorch's ``SWALR``). Chainable: each step recovers the rate the
+    annealing started from out of the current one."""
+
+    def __init__(self, optimizer, swa_lr, anneal_epochs: int = 10, anneal_strategy: str = "cos", last_epoch: int = -1):
+        strategy = getattr(anneal_strategy, "value", anneal_strategy)
+        if strategy not in ("cos", "linear"):
+            raise ValueError(f"anneal_strategy must be 'cos' or 'linear', got {anneal_strategy!r}")
+        if not isinstance(anneal_epochs, int) or anneal_epochs < 0:
+            raise ValueError(f"anneal_epochs must be a non-negative integer, got {anneal_epochs}")
+        swa = list(swa_lr) if isinstance(swa_lr, (list, tuple)) else [swa_lr] * len(optimizer.param_groups)
+        if len(swa) != len(optimizer.param_groups):
+            raise ValueError("one swa_lr per parameter group")
+        for g, v in zip(optimizer.param_groups, swa):
+            g["swa_lr"] = float(v)
+        self.anneal_epochs, self.anneal_strategy = anneal_epochs, strategy
+        super().__init__(optimizer, last_epoch)
+
+    def _alpha(self, t: float) -> float:
+        t = max(0.0, min(1.0, t))
+        return (1.0 - math.cos(math.pi * t)) / 2.0 if self.anneal_strategy == "cos" else t
+
+    def get_lr(self):
+        step = self.last_epoch
+        if self.anneal_epochs == 0:
+            step = max(1, step)
+        n = max(1, self.anneal_epochs)
+        prev, cur = self._alpha((step - 1) / n), self._alpha(step / n)
+        out = []
+        for g in self.optimizer.param_groups:
+            start = g["swa_lr"] if prev == 1.0 else (g["lr"] - prev * g["swa_lr"]) / (1.0 - prev)
+            out.append(g["swa_lr"] * cur + start * (1.0 - cur))
+        return out
