@@ -137,16 +137,19 @@ class LoRALinear(Module):
 
 
 class SqueezeExcitation(Module):
-    """Channel attention: global average pool -> FC -> ReLU -> FC -> sigmoid gate (ferrotorch-nn/src/se.rs:64)."""
+    """Channel attention: global average pool -> FC -> activation -> FC -> gate (ferrotorch-nn/src/se.rs:64). The two FC layers are 1x1
+    convolutions; ``activation`` (default ReLU) follows the first and ``scale_activation`` (default sigmoid) produces the gate."""
 
-    def __init__(self, channels: int, squeeze_channels: int):
+    def __init__(self, channels: int, squeeze_channels: int, activation=None, scale_activation=None):
         super().__init__()
         self.fc1 = Conv2d(channels, squeeze_channels, 1)
         self.fc2 = Conv2d(squeeze_channels, channels, 1)
+        self._act = activation or relu
+        self._gate = scale_activation or sigmoid
 
     def forward(self, x):
         s = x.mean((-2, -1), keepdim=True)
-        return x * sigmoid(self.fc2(relu(self.fc1(s))))
+        return x * self._gate(self.fc2(self._act(self.fc1(s))))
 
 
 # -- normalisation on our kernels -----------------------------------------------------------------------------------------------------

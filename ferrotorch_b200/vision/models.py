@@ -242,36 +242,69 @@ def vgg16(num_classes=1000):
 
 
 # -- ViT -------------------------------------------------------------------------------------------------------------------------
+class _PackedSelfAttention(nn.Module):
+    """Self-attention with the packed ``in_proj_weight [3E, E]`` / ``in_proj_bias`` / ``out_proj`` parameter layout of published ViT
+    checkpoints. One GEMM produces q, k, v; the attention itself is :func:`nn.flash_attention` (the tcgen05 kernels for bf16 CUDA inputs)."""
+
+    def __init__(self, dim: int, heads: int):
+        super().__init__()
+        self.dim, self.heads = dim, heads
+        self.in_proj_weight = nn.Parameter(torch.empty(3 * dim, dim))
+        self.in_proj_bias = nn.Parameter(torch.zeros(3 * dim))
+        self.out_proj = nn.Linear(dim, dim)
+        torch.nn.init.xavier_uniform_(self.in_proj_weight)
+
+    def forward(self, x):
+        B, S, E = x.shape
+        qkv = ops.linear(x, self.in_proj_weight, self.in_proj_bias).view(B, S, 3, self.heads, E // self.heads)
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        o = nn.flash_attention(q, k, v)
+        return self.out_proj(o.transpose(1, 2).reshape(B, S, E))
+
+
 class _EncoderBlock(nn.Module):
     def __init__(self, dim, heads, mlp_dim, dropout=0.0):
         super().__init__()
         self.ln_1 = nn.LayerNorm(dim, eps=1e-6)
-        self.self_attention = torch.nn.MultiheadAttention(dim, heads, dropout=dropout, batch_first=True)
+        self.self_attention = _PackedSelfAttention(dim, heads)
+        self.dropout = nn.Dropout(dropout)
         self.ln_2 = nn.LayerNorm(dim, eps=1e-6)
         self.mlp = nn.Sequential(nn.Linear(dim, mlp_dim), nn.GELU(), nn.Dropout(dropout), nn.Linear(mlp_dim, dim), nn.Dropout(dropout))
 
     def forward(self, x):
-        h = self.ln_1(x)
-        x = x + self.self_attention(h, h, h, need_weights=False)[0]
+        x = x + self.dropout(self.self_attention(self.ln_1(x)))
         return x + self.mlp(self.ln_2(x))
 
 
+class _ViTEncoder(nn.Module):
+    def __init__(self, seq_len, num_layers, num_heads, hidden_dim, mlp_dim, dropout=0.0):
+        super().__init__()
+        self.pos_embedding = nn.Parameter(torch.empty(1, seq_len, hidden_dim).normal_(std=0.02))
+        self.dropout = nn.Dropout(dropout)
+        self.layers = nn.Sequential(OrderedDict((f"encoder_layer_{i}", _EncoderBlock(hidden_dim, num_heads, mlp_dim, dropout)) for i in range(num_layers)))
+        self.ln = nn.LayerNorm(hidden_dim, eps=1e-6)
+
+    def forward(self, x):
+        return self.ln(self.layers(self.dropout(x + self.pos_embedding)))
+
+
 class VisionTransformer(nn.Module):
+    """ViT with the module tree of the published checkpoints: ``conv_proj``, ``class_token``, ``encoder.{pos_embedding, layers.encoder_layer_N, ln}``,
+    ``heads.head``."""
+
     def __init__(self, image_size=224, patch_size=16, num_layers=12, num_heads=12, hidden_dim=768, mlp_dim=3072, num_classes=1000):
         super().__init__()
         self.patch_size, self.hidden_dim = patch_size, hidden_dim
         self.conv_proj = nn.Conv2d(3, hidden_dim, patch_size, patch_size)
         n = (image_size // patch_size) ** 2 + 1
         self.class_token = nn.Parameter(torch.zeros(1, 1, hidden_dim))
-        self.pos_embedding = nn.Parameter(torch.empty(1, n, hidden_dim).normal_(std=0.02))
-        self.layers = nn.Sequential(*[_EncoderBlock(hidden_dim, num_heads, mlp_dim) for _ in range(num_layers)])
-        self.ln = nn.LayerNorm(hidden_dim, eps=1e-6)
-        self.head = nn.Linear(hidden_dim, num_classes)
+        self.encoder = _ViTEncoder(n, num_layers, num_heads, hidden_dim, mlp_dim)
+        self.heads = nn.Sequential(OrderedDict([("head", nn.Linear(hidden_dim, num_classes))]))
 
     def forward(self, x):
         x = self.conv_proj(x).flatten(2).transpose(1, 2)
-        x = torch.cat([self.class_token.expand(x.shape[0], -1, -1), x], 1) + self.pos_embedding
-        return self.head(self.ln(self.layers(x))[:, 0])
+        x = torch.cat([self.class_token.expand(x.shape[0], -1, -1).to(x.dtype), x], 1)
+        return self.heads(self.encoder(x)[:, 0])
 
 
 def vit_b_16(num_classes=1000, image_size=224):
@@ -425,8 +458,8 @@ class _MBConv(nn.Module):
         if expand != 1:
             layers.append(_cbr(cin, hid, 1, act=nn.SiLU))
         layers.append(_cbr(hid, hid, k, s, hid, act=nn.SiLU))
-        layers.append(nn.SqueezeExcitation(hid, max(1, int(cin * se_ratio))))
-        layers += [nn.Conv2d(hid, cout, 1, bias=False), nn.BatchNorm2d(cout)]
+        layers.append(nn.SqueezeExcitation(hid, max(1, int(cin * se_ratio)), activation=F.silu))
+        layers.append(nn.Sequential(nn.Conv2d(hid, cout, 1, bias=False), nn.BatchNorm2d(cout)))      # projection: no activation
         self.block = nn.Sequential(*layers)
 
     def forward(self, x):

@@ -191,7 +191,8 @@ def roi_pool(feat: torch.Tensor, rois: torch.Tensor, output_size, spatial_scale:
     out = feat.new_zeros(rois.shape[0], C, ph, pw)
     for k in range(rois.shape[0]):
         b = int(rois[k, 0])
-        x1, y1, x2, y2 = [int(round(float(v) * spatial_scale)) for v in rois[k, 1:]]
+        # half-way cases round away from zero (the C rule), not to even
+        x1, y1, x2, y2 = [int(math.copysign(math.floor(abs(float(v) * spatial_scale) + 0.5), float(v))) for v in rois[k, 1:]]
         rw, rh = max(x2 - x1 + 1, 1), max(y2 - y1 + 1, 1)
         for i in range(ph):
             hs, he = min(max(y1 + int(math.floor(i * rh / ph)), 0), H), min(max(y1 + int(math.ceil((i + 1) * rh / ph)), 0), H)
