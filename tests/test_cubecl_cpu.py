@@ -111,3 +111,53 @@ def test_dfa_token_mask_matches_a_per_token_walk():
         kw.update(bad)
         with pytest.raises(InvalidArgument):
             Q.DfaMaskInputs.new(**kw)
+
+
+def test_per_format_split_and_dequantise_entry_points():
+    """The per-format pair (``split_*_blocks`` -> ``dequantize_*_to_gpu``) for every format against the file-format reader."""
+    rng = np.random.default_rng(1)
+    nb = 3
+
+    def blocks(kind, with_min):
+        k = Q.GgufBlockKind[kind]
+        raw = bytearray(rng.integers(0, 256, nb * k.block_bytes(), dtype=np.uint8).tobytes())
+        for b in range(nb):
+            raw[b * k.block_bytes(): b * k.block_bytes() + 2] = np.float16(rng.uniform(0.01, 2.0)).tobytes()
+            if with_min:
+                raw[b * k.block_bytes() + 2: b * k.block_bytes() + 4] = np.float16(rng.uniform(-1.0, 1.0)).tobytes()
+        return bytes(raw)
+    c = _client()
+    assert isinstance(c, Q.CubeClient)
+    raw = blocks("Q4_1", True)
+    s, m, nib = Q.split_q4_1_blocks(raw, nb)
+    assert len(s) == len(m) == nb and len(nib) == 4 * nb
+    assert torch.allclose(Q.dequantize_q4_1_to_gpu(c, s, m, nib, nb * 32), dequantize_gguf(raw, 3, nb * 32), atol=1e-6)
+    raw = blocks("Q5_0", False)
+    s, qh, nib = Q.split_q5_0_blocks(raw, nb)
+    assert len(qh) == nb and len(nib) == 4 * nb
+    assert torch.allclose(Q.dequantize_q5_0_to_gpu(c, s, qh, nib, nb * 32), dequantize_gguf(raw, 6, nb * 32), atol=1e-6)
+    raw = blocks("Q5_1", True)
+    s, m, qh, nib = Q.split_q5_1_blocks(raw, nb)
+    assert torch.allclose(Q.dequantize_q5_1_to_gpu(c, s, m, qh, nib, nb * 32), dequantize_gguf(raw, 7, nb * 32), atol=1e-6)
+    raw = blocks("Q8_0", False)
+    s, packed = Q.split_q8_0_blocks(raw, nb)
+    assert len(packed) == 8 * nb
+    out = Q.dequantize_q8_0_to_gpu(c, s, packed, nb * 32)
+    assert torch.allclose(out, dequantize_gguf(raw, 8, nb * 32), atol=1e-6)
+    h = Q.wrap_kernel_output(out, [nb, 32], Q.CubeRuntime.new(Q.CubeDevice.Cuda(0), allow_host=True))
+    assert isinstance(h, Q.CubeclStorageHandle) and h.len() == nb * 32
+
+
+def test_dfa_walk_kernel_on_raw_tables():
+    T, cc, C, states, reject = _json_bool_dfa()
+    vocab = ["tr", "ue", "x", "false"]
+    offs, chars = [0], []
+    for tok in vocab:
+        chars += [ord(ch) for ch in tok]
+        offs.append(len(chars))
+    lt = lambda a: torch.tensor(a, dtype=torch.long)     # noqa: E731
+    allow = torch.empty(len(vocab), dtype=torch.int32)
+    Q.kernel_compute_token_mask_dfa(lt(T), lt(cc), lt(offs), lt(chars), allow, C, 0, reject, 5)
+    assert allow.tolist() == [1, 0, 0, 1]
+    Q.kernel_compute_token_mask_dfa(lt(T), lt(cc), lt(offs), lt(chars), allow, C, torch.tensor([states["tr"]]), reject, 5)
+    assert allow.tolist() == [0, 1, 0, 0]

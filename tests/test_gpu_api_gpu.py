@@ -62,3 +62,47 @@ def test_explicit_capture_replays_the_recorded_work():
     G.release_graph_pool_handle(h)
     with pytest.raises(Exception):
         G.end_capture(side)
+
+
+def test_buffer_transfers_small_math_and_plain_capture():
+    dev = G.cuda_default()
+    assert isinstance(dev, G.GpuDevice) and dev.sm_count() > 0 and dev.total_memory() > 0
+    z = G.alloc_zeros(1000)
+    assert isinstance(z, G.CudaBuffer) and z.tensor().is_cuda and float(z.tensor().abs().sum()) == 0 and z.device_ptr() != 0
+    assert G.alloc_zeros_f32(8).tensor().dtype == torch.float32 and G.alloc_zeros_f64(8).tensor().dtype == torch.float64
+    z.release()
+    h = torch.arange(16.0)
+    d = G.cpu_to_gpu(h)
+    dp = G.cpu_to_gpu_pinned(h)
+    torch.cuda.synchronize()
+    assert d.is_cuda and torch.equal(d.cpu(), h) and torch.equal(dp.cpu(), h) and G.tensor_to_gpu(d) is d and G.tensor_to_gpu(h).is_cuda
+    back = G.gpu_to_cpu(d, pinned=True)
+    assert back.is_pinned() and torch.equal(back, h) and torch.equal(G.gpu_to_cpu(d), h)
+    a, b = torch.randn(512, device="cuda"), torch.randn(512, device="cuda")
+    out = torch.empty(512, device="cuda")
+    G.gpu_mul_into(a, b, out)
+    assert torch.equal(out, a * b)
+    assert torch.equal(G.gpu_mul_bf16(a.bfloat16(), b.bfloat16()), a.bfloat16() * b.bfloat16())
+    assert torch.allclose(G.gpu_gelu(a), torch.nn.functional.gelu(a), atol=1e-6)
+    A, B = torch.randn(8 * 16, device="cuda"), torch.randn(16 * 4, device="cuda")
+    mm = torch.empty(8 * 4, device="cuda")
+    G.gpu_small_matmul_into(A, B, mm, 8, 16, 4)
+    assert torch.allclose(mm.view(8, 4), A.view(8, 16) @ B.view(16, 4), atol=1e-4)
+    bA, bB = torch.randn(3 * 8 * 16, device="cuda"), torch.randn(3 * 16 * 4, device="cuda")
+    bo = torch.empty(3 * 8 * 4, device="cuda")
+    G.gpu_bmm_f32_into(bA, bB, bo, 3, 8, 16, 4)
+    assert torch.allclose(bo.view(3, 8, 4), torch.bmm(bA.view(3, 8, 16), bB.view(3, 16, 4)), atol=1e-4)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        G.gpu_mul_into(a, b, out)
+    torch.cuda.synchronize()
+    G.begin_capture(side)
+    G.gpu_mul_into(a, b, out)
+    graph = G.end_capture(side)
+    assert isinstance(graph, G.CapturedGraph)
+    a.fill_(2.0)
+    graph.launch()
+    torch.cuda.synchronize()
+    assert torch.equal(out, 2.0 * b)
+    assert G.StreamPriority.HIGH < G.StreamPriority.NORMAL
