@@ -9,7 +9,6 @@ substrate's generators (``torch.manual_seed``), not from the Philox streams of `
 Reference parity: ferrotorch-distributions/src/lib.rs:138 (Distribution trait), kl.rs:66, transforms.rs, constraints.rs and one
 file per family.
 """
-from torch import distributions as _d
 from . import constraints, transforms
 from .constraints import Constraint
 from .transforms import TransformedDistribution, SoftplusTransform, Transform
@@ -18,8 +17,8 @@ from .families import (Distribution, Normal, LogNormal, Uniform, Bernoulli, Cate
                        kl_divergence, register_kl)
 from . import families as kl
 
-LowRankMultivariateNormal, MixtureSameFamily, Multinomial = _d.LowRankMultivariateNormal, _d.MixtureSameFamily, _d.Multinomial
-RelaxedBernoulli, RelaxedOneHotCategorical, VonMises = _d.RelaxedBernoulli, _d.RelaxedOneHotCategorical, _d.VonMises
+from .more_families import (LowRankMultivariateNormal, MixtureSameFamily, Multinomial, RelaxedBernoulli, RelaxedOneHotCategorical,
+                            VonMises)
 AffineTransform, ExpTransform, SigmoidTransform, TanhTransform, ComposeTransform, SoftmaxTransform, StickBreakingTransform = (
     transforms.AffineTransform, transforms.ExpTransform, transforms.SigmoidTransform, transforms.TanhTransform, transforms.ComposeTransform,
     transforms.SoftmaxTransform, transforms.StickBreakingTransform)

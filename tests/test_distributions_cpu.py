@@ -6,6 +6,8 @@ import pytest
 import torch
 import torch.distributions as TD
 
+td = TD
+
 from ferrotorch_b200 import distributions as D
 
 X = torch.tensor([0.3, 1.7, 0.05])
@@ -108,3 +110,123 @@ def test_sampling_statistics_and_pathwise_gradients():
     conc = torch.tensor([1.0, 2.0, 3.0], requires_grad=True)
     D.Dirichlet(conc).rsample((64,))[:, 0].mean().backward()
     assert conc.grad is not None and float(conc.grad[0]) > 0 > float(conc.grad[1])
+
+
+# -- the six families of more_families.py ------------------------------------------------------------------------------------------------
+def _tclose(a, b, tol=1e-5):
+    assert a.shape == b.shape and torch.allclose(a, b, atol=tol, rtol=tol), (a.shape, b.shape, (a - b).abs().max().item() if a.shape == b.shape else None)
+
+
+def test_further_families_are_this_packages():
+    import ferrotorch_b200.distributions as FD
+    for n in ("Multinomial", "MixtureSameFamily", "RelaxedBernoulli", "RelaxedOneHotCategorical", "VonMises", "LowRankMultivariateNormal"):
+        assert getattr(FD, n).__module__ == "ferrotorch_b200.distributions.more_families", n
+
+
+def test_multinomial_matches_torch():
+    import ferrotorch_b200.distributions as FD
+    torch.manual_seed(0)
+    p = torch.softmax(torch.randn(3, 5), -1)
+    ours, ref = FD.Multinomial(7, probs=p), td.Multinomial(7, probs=p)
+    x = ref.sample((4,))
+    _tclose(ours.log_prob(x), ref.log_prob(x))
+    _tclose(ours.mean, ref.mean)
+    _tclose(ours.variance, ref.variance)
+    _tclose(ours.entropy(), ref.entropy(), 1e-4)
+    s = ours.sample((2000,))
+    assert s.shape == (2000, 3, 5) and torch.all(s.sum(-1) == 7) and (s.mean(0) - ours.mean).abs().max() < 0.15
+    z = FD.Multinomial(3, probs=torch.tensor([0.5, 0.5, 0.0]))
+    assert torch.isfinite(z.log_prob(torch.tensor([1.0, 2.0, 0.0]))) and z.log_prob(torch.tensor([1.0, 1.0, 1.0])) == -float("inf")
+    _tclose(FD.Multinomial(4, logits=torch.randn(5)).probs.sum(), torch.tensor(1.0))
+
+
+def test_mixture_same_family_matches_torch():
+    import ferrotorch_b200.distributions as FD
+    torch.manual_seed(1)
+    w = torch.softmax(torch.randn(2, 3), -1)
+    mu, sd = torch.randn(2, 3), torch.rand(2, 3) + 0.3
+    ours = FD.MixtureSameFamily(FD.Categorical(probs=w), FD.Normal(mu, sd))
+    ref = td.MixtureSameFamily(td.Categorical(probs=w), td.Normal(mu, sd))
+    x = torch.randn(5, 2)
+    _tclose(ours.log_prob(x), ref.log_prob(x))
+    _tclose(ours.cdf(x), ref.cdf(x))
+    _tclose(ours.mean, ref.mean)
+    _tclose(ours.variance, ref.variance)
+    s = ours.sample((20000,))
+    assert s.shape == (20000, 2) and (s.mean(0) - ours.mean).abs().max() < 0.05 and (s.var(0) - ours.variance).abs().max() < 0.1
+    # vector-valued components
+    mu2 = torch.randn(3, 4)
+    o2 = FD.MixtureSameFamily(FD.Categorical(probs=w[0]), FD.Independent(FD.Normal(mu2, torch.ones(3, 4)), 1))
+    r2 = td.MixtureSameFamily(td.Categorical(probs=w[0]), td.Independent(td.Normal(mu2, torch.ones(3, 4)), 1))
+    y = torch.randn(6, 4)
+    _tclose(o2.log_prob(y), r2.log_prob(y))
+    _tclose(o2.mean, r2.mean)
+    assert o2.sample((7,)).shape == (7, 4)
+    with pytest.raises(ValueError):
+        FD.MixtureSameFamily(FD.Categorical(probs=torch.ones(4) / 4), FD.Normal(mu, sd))
+
+
+def test_relaxed_distributions_match_torch():
+    import ferrotorch_b200.distributions as FD
+    torch.manual_seed(2)
+    lg, T = torch.randn(4), torch.tensor(0.7)
+    ours, ref = FD.RelaxedBernoulli(T, logits=lg), td.RelaxedBernoulli(T, logits=lg)
+    y = torch.rand(6, 4) * 0.98 + 0.01
+    _tclose(ours.log_prob(y), ref.log_prob(y), 1e-4)
+    lgr = lg.clone().requires_grad_()
+    s = FD.RelaxedBernoulli(T, logits=lgr).rsample((5000,))
+    assert s.shape == (5000, 4) and 0 < s.min() and s.max() < 1
+    s.mean().backward()
+    assert lgr.grad is not None and (lgr.grad > 0).all()                   # larger logits push the relaxed sample towards one
+    assert ((s > 0.5).float().mean(0) - torch.sigmoid(lg)).abs().max() < 0.04
+    lg2 = torch.randn(3, 5)
+    o2, r2 = FD.RelaxedOneHotCategorical(T, logits=lg2), td.RelaxedOneHotCategorical(T, logits=lg2)
+    v = torch.softmax(torch.randn(6, 3, 5), -1)
+    _tclose(o2.log_prob(v), r2.log_prob(v), 1e-4)
+    s2 = o2.rsample((4000,))
+    assert s2.shape == (4000, 3, 5) and torch.allclose(s2.sum(-1), torch.ones(4000, 3), atol=1e-5)
+    freq = torch.zeros(3, 5).scatter_add_(1, s2.argmax(-1).T, torch.ones(3, 4000)) / 4000
+    assert (freq - torch.softmax(lg2, -1)).abs().max() < 0.04                # the arg-max of a Gumbel-softmax sample is categorical
+
+
+def test_von_mises_matches_torch():
+    import ferrotorch_b200.distributions as FD
+    torch.manual_seed(3)
+    mu, k = torch.tensor([0.0, 1.0, -2.5]), torch.tensor([0.5, 4.0, 50.0])
+    ours, ref = FD.VonMises(mu, k), td.VonMises(mu, k)
+    x = torch.rand(7, 3) * 2 * math.pi - math.pi
+    _tclose(ours.log_prob(x), ref.log_prob(x), 1e-5)
+    _tclose(ours.variance, ref.variance, 1e-5)
+    _tclose(ours.mean, ref.mean)
+    s = ours.sample((20000,))
+    assert s.shape == (20000, 3) and s.min() >= -math.pi and s.max() < math.pi
+    circ_mean = torch.atan2(torch.sin(s).mean(0), torch.cos(s).mean(0))
+    assert (torch.remainder(circ_mean - mu + math.pi, 2 * math.pi) - math.pi).abs().max() < 0.05
+    resultant = torch.sqrt(torch.sin(s).mean(0) ** 2 + torch.cos(s).mean(0) ** 2)
+    assert (1 - resultant - ours.variance).abs().max() < 0.02
+    tiny = FD.VonMises(torch.tensor(0.0), torch.tensor(1e-8)).sample((4000,))
+    assert abs(float(tiny.mean())) < 0.15 and float(tiny.std()) > 1.6           # nearly uniform on the circle
+
+
+def test_low_rank_multivariate_normal_matches_torch():
+    import ferrotorch_b200.distributions as FD
+    torch.manual_seed(4)
+    loc, W, d = torch.randn(2, 6), torch.randn(2, 6, 2), torch.rand(2, 6) + 0.2
+    ours, ref = FD.LowRankMultivariateNormal(loc, W, d), td.LowRankMultivariateNormal(loc, W, d)
+    x = torch.randn(5, 2, 6)
+    _tclose(ours.log_prob(x), ref.log_prob(x), 1e-4)
+    _tclose(ours.entropy(), ref.entropy(), 1e-4)
+    _tclose(ours.variance, ref.variance)
+    _tclose(ours.covariance_matrix, ref.covariance_matrix)
+    _tclose(ours.precision_matrix, ref.precision_matrix, 1e-4)
+    _tclose(ours.scale_tril, ref.scale_tril, 1e-4)
+    dense = FD.MultivariateNormal(loc, covariance_matrix=ours.covariance_matrix)
+    _tclose(ours.log_prob(x), dense.log_prob(x), 1e-4)
+    Wg = W.clone().requires_grad_()
+    s = FD.LowRankMultivariateNormal(loc, Wg, d).rsample((30000,))
+    s.pow(2).mean().backward()
+    assert Wg.grad is not None and s.shape == (30000, 2, 6)
+    emp = torch.einsum("nbi,nbj->bij", s.detach() - loc, s.detach() - loc) / 30000
+    assert (emp - ours.covariance_matrix).abs().max() < 0.15
+    with pytest.raises(ValueError):
+        FD.LowRankMultivariateNormal(loc, torch.randn(2, 5, 2), d)
