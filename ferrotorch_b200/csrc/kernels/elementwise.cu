@@ -24,7 +24,7 @@ enum UnaryOp : int {
 // backward codes: grad_in = g * f'(.) where "v" is the saved forward INPUT (x) unless noted
 enum UnaryBwd : int {
   UB_RELU = 0, UB_ABS, UB_SIGMOID_Y /* v = output */, UB_TANH_Y /* v = output */, UB_GELU, UB_GELU_TANH, UB_SILU, UB_ELU, UB_MISH, UB_CLAMP,
-  UB_LEAKY_RELU, UB_EXP_Y /* v = output */, UB_LOG, UB_SQRT_Y /* v = output */, UB_SOFTPLUS, UB_HARDSWISH
+  UB_LEAKY_RELU, UB_EXP_Y /* v = output */, UB_LOG, UB_SQRT_Y /* v = output */, UB_SOFTPLUS, UB_HARDSWISH, UB_HARDTANH
 };
 enum BinaryOp : int { B_ADD = 0, B_SUB, B_MUL, B_DIV, B_POW, B_MAX, B_MIN, B_EQ, B_NE, B_LT, B_LE, B_GT, B_GE, B_ATAN2, B_FMOD };
 
@@ -117,7 +117,9 @@ FT_DEVICE A unary_bwd_apply(int op, A g, A v, A a, A b) {
     case UB_LOG: return g / v;
     case UB_SQRT_Y: return g / ((A)2 * v);
     case UB_SOFTPLUS: return v * a > b ? g : g / ((A)1 + exp(-v * a));
-    case UB_HARDSWISH: return v < (A)-3 ? (A)0 : (v > (A)3 ? g : g * ((A)2 * v + (A)3) / (A)6);
+    // at the kinks x = -3 and x = 3 the outer pieces' derivatives are taken (0 and 1), as PyTorch does
+    case UB_HARDSWISH: return v <= (A)-3 ? (A)0 : (v >= (A)3 ? g : g * ((A)2 * v + (A)3) / (A)6);
+    case UB_HARDTANH: return (v > a && v < b) ? g : (A)0;      // open interval: no gradient at the two bounds (clamp keeps it there)
     default: return g;
   }
 }

@@ -71,7 +71,7 @@ def _ew(x, op, bwd_op, a=0.0, b=0.0, saved="x"):
 
 # -- functional forms (used by the classes below and by nn.functional) ---------------------------------------------------------------
 def relu(x):
-    return _ew(x, "relu", "relu") if _kernel_ok(x) else torch.clamp_min(x, 0)
+    return _ew(x, "relu", "relu") if _kernel_ok(x) else torch.where(x > 0, x, torch.zeros_like(x))        # no gradient at the origin
 
 
 def relu6(x):
@@ -81,7 +81,9 @@ def relu6(x):
 def hardtanh(x, min_val: float = -1.0, max_val: float = 1.0):
     if min_val > max_val:
         raise InvalidArgument(f"hardtanh: min_val {min_val} > max_val {max_val}")
-    return _ew(x, "clamp", "clamp", min_val, max_val) if _kernel_ok(x) else torch.clamp(x, min_val, max_val)
+    if _kernel_ok(x):
+        return _ew(x, "clamp", "hardtanh", min_val, max_val)          # derivative on the open interval, as for the host form below
+    return torch.where(x <= min_val, torch.full_like(x, min_val), torch.where(x >= max_val, torch.full_like(x, max_val), x))
 
 
 def leaky_relu(x, negative_slope: float = 0.01):
@@ -128,11 +130,14 @@ def mish(x):
 
 
 def hardsigmoid(x):
-    return torch.clamp(x / 6.0 + 0.5, 0.0, 1.0)
+    # written piecewise so that the derivative at the kinks x = -3, 3 is that of the flat outer pieces
+    return torch.where(x <= -3, torch.zeros_like(x), torch.where(x >= 3, torch.ones_like(x), x / 6.0 + 0.5))
 
 
 def hardswish(x):
-    return _ew(x, "hardswish", "hardswish") if _kernel_ok(x) else x * hardsigmoid(x)
+    if _kernel_ok(x):
+        return _ew(x, "hardswish", "hardswish")
+    return torch.where(x <= -3, torch.zeros_like(x), torch.where(x >= 3, x, x * (x + 3) / 6.0))
 
 
 def logsigmoid(x):

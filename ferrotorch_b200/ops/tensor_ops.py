@@ -24,7 +24,7 @@ UNARY = {n: i for i, n in enumerate(
      "hardsigmoid", "exp2", "log2", "log1p", "expm1", "copy", "fatrelu"])}
 UNARY_BWD = {n: i for i, n in enumerate(
     ["relu", "abs", "sigmoid_y", "tanh_y", "gelu", "gelu_tanh", "silu", "elu", "mish", "clamp", "leaky_relu", "exp_y", "log", "sqrt_y", "softplus",
-     "hardswish"])}
+     "hardswish", "hardtanh"])}
 BINARY = {n: i for i, n in enumerate(["add", "sub", "mul", "div", "pow", "maximum", "minimum", "eq", "ne", "lt", "le", "gt", "ge", "atan2", "fmod"])}
 REDUCE = {n: i for i, n in enumerate(["sum", "prod", "min", "max", "mean", "sumsq", "absmax", "logsumexp"])}
 SCAN = {n: i for i, n in enumerate(["cumsum", "cumprod", "cummax", "cummin", "logcumsumexp"])}

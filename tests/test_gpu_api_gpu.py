@@ -66,7 +66,7 @@ def test_explicit_capture_replays_the_recorded_work():
 
 def test_buffer_transfers_small_math_and_plain_capture():
     dev = G.cuda_default()
-    assert isinstance(dev, G.GpuDevice) and dev.sm_count() > 0 and dev.total_memory() > 0
+    assert isinstance(dev, G.GpuDevice) and dev.sm_count > 0 and dev.total_memory > 0
     z = G.alloc_zeros(1000)
     assert isinstance(z, G.CudaBuffer) and z.tensor().is_cuda and float(z.tensor().abs().sum()) == 0 and z.device_ptr() != 0
     assert G.alloc_zeros_f32(8).tensor().dtype == torch.float32 and G.alloc_zeros_f64(8).tensor().dtype == torch.float64
