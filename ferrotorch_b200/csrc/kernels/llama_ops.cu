@@ -48,42 +48,48 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
 }
 
 // gu: [rows, 2F] (gate = cols [0,F), up = cols [F,2F)); out[r,c] = silu(gate)*up
+// IDX is the type of the flat (row, vector) index: 32-bit whenever rows * F / 8 fits (a 64-bit divide per element costs as much as the math).
+// The sigmoid uses the fast reciprocal (2 ulp): the result is rounded to bf16 anyway, and the kernel is close to issue-bound otherwise.
+template <typename IDX>
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int F) {
-  const int vecs = F >> 3;
-  const size_t total = (size_t)rows * vecs;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = i / vecs;
-    const int c = (int)(i % vecs) * 8;
+  const IDX vecs = (IDX)(F >> 3);
+  const IDX total = (IDX)rows * vecs;
+  for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IDX)gridDim.x * blockDim.x) {
+    const IDX r = i / vecs;
+    const int c = (int)(i - r * vecs) * 8;
+    const __nv_bfloat16* row = gu + (size_t)r * 2 * F;
     float g[8], u[8], o[8];
-    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + r * 2 * F + c), g);
-    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + r * 2 * F + F + c), u);
+    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(row + c), g);
+    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(row + F + c), u);
 #pragma unroll
-    for (int e = 0; e < 8; e++) o[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
-    *reinterpret_cast<bf16x8*>(out + r * F + c) = float_to_bf16x8(o);
+    for (int e = 0; e < 8; e++) o[e] = __fdividef(g[e], 1.f + __expf(-g[e])) * u[e];
+    *reinterpret_cast<bf16x8*>(out + (size_t)r * F + c) = float_to_bf16x8(o);
   }
 }
 
 // dgu[r, :F] = dout * up * dsilu(gate) ; dgu[r, F:] = dout * silu(gate). May run in place (dgu == gu).
+template <typename IDX>
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* gu, const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* dgu, int rows,
                                   int F) {
-  const int vecs = F >> 3;
-  const size_t total = (size_t)rows * vecs;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = i / vecs;
-    const int c = (int)(i % vecs) * 8;
+  const IDX vecs = (IDX)(F >> 3);
+  const IDX total = (IDX)rows * vecs;
+  for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IDX)gridDim.x * blockDim.x) {
+    const IDX r = i / vecs;
+    const int c = (int)(i - r * vecs) * 8;
+    const size_t ro = (size_t)r * 2 * F;
     float g[8], u[8], d[8], dg[8], du[8];
-    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + r * 2 * F + c), g);
-    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + r * 2 * F + F + c), u);
-    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(dout + r * F + c), d);
+    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + ro + c), g);
+    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(gu + ro + F + c), u);
+    bf16x8_to_float(*reinterpret_cast<const bf16x8*>(dout + (size_t)r * F + c), d);
 #pragma unroll
     for (int e = 0; e < 8; e++) {
-      float sg = 1.f / (1.f + __expf(-g[e]));
+      float sg = __fdividef(1.f, 1.f + __expf(-g[e]));
       float silu = g[e] * sg;
       du[e] = d[e] * silu;
       dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
     }
-    *reinterpret_cast<bf16x8*>(dgu + r * 2 * F + c) = float_to_bf16x8(dg);
-    *reinterpret_cast<bf16x8*>(dgu + r * 2 * F + F + c) = float_to_bf16x8(du);
+    *reinterpret_cast<bf16x8*>(dgu + ro + c) = float_to_bf16x8(dg);
+    *reinterpret_cast<bf16x8*>(dgu + ro + F + c) = float_to_bf16x8(du);
   }
 }
 
@@ -187,14 +193,21 @@ FT_EXPORT int ft_rope_inplace(void* x, const float* cos_t, const float* sin_t, c
 
 FT_EXPORT int ft_swiglu_fwd(const void* gu, void* out, int rows, int F, cudaStream_t st) {
   if (F % 8 || rows <= 0) return FT_ERR_ARG;
-  swiglu_fwd_kernel<<<grid_for((size_t)rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+  const size_t total = (size_t)rows * (F / 8);
+  if (total + (size_t)grid_for(total, 256) * 256 < (1ull << 32))          // the loop counter may pass `total` by one grid stride
+    swiglu_fwd_kernel<uint32_t><<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+  else
+    swiglu_fwd_kernel<size_t><<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
   return (int)cudaGetLastError();
 }
 
 FT_EXPORT int ft_swiglu_bwd(const void* gu, const void* dout, void* dgu, int rows, int F, cudaStream_t st) {
   if (F % 8 || rows <= 0) return FT_ERR_ARG;
-  swiglu_bwd_kernel<<<grid_for((size_t)rows * (F / 8), 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout,
-                                                                            (__nv_bfloat16*)dgu, rows, F);
+  const size_t total = (size_t)rows * (F / 8);
+  if (total + (size_t)grid_for(total, 256) * 256 < (1ull << 32))
+    swiglu_bwd_kernel<uint32_t><<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dgu, rows, F);
+  else
+    swiglu_bwd_kernel<size_t><<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dgu, rows, F);
   return (int)cudaGetLastError();
 }
 

@@ -10,9 +10,9 @@
 
 #define FT_VPT_DISPATCH(d, ...)                              \
   do {                                                      \
-    if ((d) <= 512 * 8) { constexpr int V = 1; __VA_ARGS__; } \
-    else if ((d) <= 512 * 16) { constexpr int V = 2; __VA_ARGS__; } \
-    else { constexpr int V = 4; __VA_ARGS__; }              \
+    if ((d) <= 512 * 8) { constexpr int V = 1; constexpr int R = 4; __VA_ARGS__; } \
+    else if ((d) <= 512 * 16) { constexpr int V = 2; constexpr int R = 2; __VA_ARGS__; } \
+    else { constexpr int V = 4; constexpr int R = 1; __VA_ARGS__; (void)R; } \
   } while (0)
 
 namespace {
@@ -20,61 +20,94 @@ namespace {
 constexpr int NT = 512;          // threads per CTA
 constexpr int MAXV_LIMIT = 4;    // 16-byte vectors per thread  => d <= 512*4*8 = 16384
 
+// R block-wide sums at once (one pair of barriers for all of them); every sum is formed in the order block_sum uses.
+template <int R>
+FT_DEVICE void block_sum_n(float (&v)[R], float* red) {
+#pragma unroll
+  for (int r = 0; r < R; r++) v[r] = warp_sum(v[r]);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) {
+#pragma unroll
+    for (int r = 0; r < R; r++) red[r * 32 + w] = v[r];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; r++) v[r] = warp_sum(l < nw ? red[r * 32 + l] : 0.f);
+}
+
+// Rows of one launch are handed out in groups of R consecutive rows: a CTA issues the loads of all R rows before the one block-wide
+// reduction, so R times as many bytes are in flight per thread and the two barriers are paid once per group.
+inline int norm_rows_per_iter(int d) { return d <= 512 * 8 ? 4 : (d <= 512 * 16 ? 2 : 1); }
+
 // y = (x [+ res]) * rstd * w ;  optionally writes the summed residual stream back to `xout`.
-template <int MAXV, bool HAS_RES>
+template <int MAXV, bool HAS_RES, int R>
 __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                                          const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                          __nv_bfloat16* __restrict__ xout, float* __restrict__ rstd_out,
                                                          int rows, int d, float eps) {
-  __shared__ float red[32];
+  __shared__ float red[32 * R];
   const int nvec = d >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
-    const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * d) : nullptr;
-    float v[MAXV][8];
-    float ss = 0.f;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    float v[R][MAXV][8];
+    float ss[R];
 #pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-      int c = threadIdx.x + i * NT;
-      if (c < nvec) {
-        bf16x8_to_float(xr[c], v[i]);
-        if (HAS_RES) {
-          float r[8];
-          bf16x8_to_float(rr[c], r);
+    for (int r = 0; r < R; r++) {
+      const int row = row0 + r;
+      ss[r] = 0.f;
+      if (row < rows) {
+        const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (size_t)row * d);
+        const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * d) : nullptr;
 #pragma unroll
-          for (int e = 0; e < 8; e++) v[i][e] += r[e];
-          bf16x8 o = float_to_bf16x8(v[i]);
-          reinterpret_cast<bf16x8*>(xout + (size_t)row * d)[c] = o;
-          bf16x8_to_float(o, v[i]);  // normalise exactly what the residual stream stores
+        for (int i = 0; i < MAXV; i++) {
+          int c = threadIdx.x + i * NT;
+          if (c < nvec) {
+            bf16x8_to_float(xr[c], v[r][i]);
+            if (HAS_RES) {
+              float t[8];
+              bf16x8_to_float(rr[c], t);
+#pragma unroll
+              for (int e = 0; e < 8; e++) v[r][i][e] += t[e];
+              bf16x8 o = float_to_bf16x8(v[r][i]);
+              reinterpret_cast<bf16x8*>(xout + (size_t)row * d)[c] = o;
+              bf16x8_to_float(o, v[r][i]);  // normalise exactly what the residual stream stores
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss[r] += v[r][i][e] * v[r][i][e];
+          }
         }
-#pragma unroll
-        for (int e = 0; e < 8; e++) ss += v[i][e] * v[i][e];
       }
     }
-    ss = block_sum(ss, red);
-    const float rstd = rsqrtf(ss / (float)d + eps);
-    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    block_sum_n<R>(ss, red);
 #pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-      int c = threadIdx.x + i * NT;
-      if (c < nvec) {
-        float wv[8], o[8];
-        bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv);
+    for (int r = 0; r < R; r++) {
+      const int row = row0 + r;
+      if (row < rows) {
+        const float rstd = rsqrtf(ss[r] / (float)d + eps);
+        if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
 #pragma unroll
-        for (int e = 0; e < 8; e++) o[e] = v[i][e] * rstd * wv[e];
-        reinterpret_cast<bf16x8*>(y + (size_t)row * d)[c] = float_to_bf16x8(o);
+        for (int i = 0; i < MAXV; i++) {
+          int c = threadIdx.x + i * NT;
+          if (c < nvec) {
+            float wv[8], o[8];
+            bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv);
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[e] = v[r][i][e] * rstd * wv[e];
+            reinterpret_cast<bf16x8*>(y + (size_t)row * d)[c] = float_to_bf16x8(o);
+          }
+        }
       }
     }
   }
 }
 
-// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ dres]; dw partial per CTA in f32.
-template <int MAXV, bool HAS_DRES>
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ dres]; dw partial per CTA in f32. Groups of R rows as in the forward kernel.
+template <int MAXV, bool HAS_DRES, int R>
 __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
                                                          const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                                          float* __restrict__ dw_partial, int rows, int d) {
-  __shared__ float red[32];
+  __shared__ float red[32 * R];
   const int nvec = d >> 3;
   float dwacc[MAXV][8];
 #pragma unroll
@@ -87,41 +120,55 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
     int c = threadIdx.x + i * NT;
     if (c < nvec) bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rstd = rstd_in[row];
-    float xh[MAXV][8], g[MAXV][8];
-    float dot = 0.f;
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    float xh[R][MAXV][8], g[R][MAXV][8];
+    float dot[R], rstd[R];
 #pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-      int c = threadIdx.x + i * NT;
-      if (c < nvec) {
-        float xv[8], dyv[8];
-        bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], xv);
-        bf16x8_to_float(reinterpret_cast<const bf16x8*>(dy + (size_t)row * d)[c], dyv);
+    for (int r = 0; r < R; r++) {
+      const int row = row0 + r;
+      dot[r] = 0.f;
+      rstd[r] = row < rows ? rstd_in[row] : 0.f;
+      if (row < rows) {
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-          xh[i][e] = xv[e] * rstd;
-          g[i][e] = dyv[e] * wv[i][e];
-          dot += g[i][e] * xh[i][e];
-          dwacc[i][e] += dyv[e] * xh[i][e];
+        for (int i = 0; i < MAXV; i++) {
+          int c = threadIdx.x + i * NT;
+          if (c < nvec) {
+            float xv[8], dyv[8];
+            bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], xv);
+            bf16x8_to_float(reinterpret_cast<const bf16x8*>(dy + (size_t)row * d)[c], dyv);
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+              xh[r][i][e] = xv[e] * rstd[r];
+              g[r][i][e] = dyv[e] * wv[i][e];
+              dot[r] += g[r][i][e] * xh[r][i][e];
+              dwacc[i][e] += dyv[e] * xh[r][i][e];
+            }
+          }
         }
       }
     }
-    dot = block_sum(dot, red) / (float)d;
+    block_sum_n<R>(dot, red);
 #pragma unroll
-    for (int i = 0; i < MAXV; i++) {
-      int c = threadIdx.x + i * NT;
-      if (c < nvec) {
-        float o[8];
+    for (int r = 0; r < R; r++) {
+      const int row = row0 + r;
+      if (row < rows) {
+        const float dm = dot[r] / (float)d;
 #pragma unroll
-        for (int e = 0; e < 8; e++) o[e] = rstd * (g[i][e] - xh[i][e] * dot);
-        if (HAS_DRES) {
-          float r[8];
-          bf16x8_to_float(reinterpret_cast<const bf16x8*>(dres + (size_t)row * d)[c], r);
+        for (int i = 0; i < MAXV; i++) {
+          int c = threadIdx.x + i * NT;
+          if (c < nvec) {
+            float o[8];
 #pragma unroll
-          for (int e = 0; e < 8; e++) o[e] += r[e];
+            for (int e = 0; e < 8; e++) o[e] = rstd[r] * (g[r][i][e] - xh[r][i][e] * dm);
+            if (HAS_DRES) {
+              float t[8];
+              bf16x8_to_float(reinterpret_cast<const bf16x8*>(dres + (size_t)row * d)[c], t);
+#pragma unroll
+              for (int e = 0; e < 8; e++) o[e] += t[e];
+            }
+            reinterpret_cast<bf16x8*>(dx + (size_t)row * d)[c] = float_to_bf16x8(o);
+          }
         }
-        reinterpret_cast<bf16x8*>(dx + (size_t)row * d)[c] = float_to_bf16x8(o);
       }
     }
   }
@@ -274,12 +321,13 @@ FT_EXPORT int ft_norm_bwd_parts(int rows) { return rows < 296 ? rows : 296; }
 FT_EXPORT int ft_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xout, float* rstd, int rows, int d,
                              float eps, cudaStream_t st) {
   if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
-  int grid = rows < 148 * 8 ? rows : 148 * 8;
+  const int groups = (rows + norm_rows_per_iter(d) - 1) / norm_rows_per_iter(d);
+  int grid = groups < 148 * 8 ? groups : 148 * 8;
   if (res)
-    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, true, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
                                                   (__nv_bfloat16*)y, (__nv_bfloat16*)xout, rstd, rows, d, eps));
   else
-    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, false, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
                                                    nullptr, rstd, rows, d, eps));
   return (int)cudaGetLastError();
 }
@@ -288,12 +336,13 @@ FT_EXPORT int ft_rmsnorm_fwd(const void* x, const void* res, const void* w, void
 FT_EXPORT int ft_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres, void* dx,
                              float* dw_partial, void* dw_bf16, float* dw_f32, int accumulate, int rows, int d, cudaStream_t st) {
   if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
-  int grid = ft_norm_bwd_parts(rows);
+  const int groups = (rows + norm_rows_per_iter(d) - 1) / norm_rows_per_iter(d);
+  int grid = groups < ft_norm_bwd_parts(rows) ? groups : ft_norm_bwd_parts(rows);      // never more partial rows than the caller's scratch holds
   if (dres)
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
                                                   (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, d));
   else
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
                                                    nullptr, (__nv_bfloat16*)dx, dw_partial, rows, d));
   colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();
@@ -379,10 +428,10 @@ FT_EXPORT int ft_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* d
   const int grid = rows < NOALLOC_PARTS ? rows : NOALLOC_PARTS;
   // every partial row in [0, grid) is fully overwritten by its CTA, so nothing has to be cleared between calls
   if (dres)
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
                                                                       rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, d));
   else
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
                                                                        rstd, nullptr, (__nv_bfloat16*)dx, scratch, rows, d));
   colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(scratch, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();

@@ -13,7 +13,7 @@ def _close(got, ref, rtol=2e-2, atol=2e-2):
     assert torch.allclose(got.float(), ref.float(), rtol=rtol, atol=atol), (got.float() - ref.float()).abs().max().item()
 
 
-@pytest.mark.parametrize("rows,d", [(5, 256), (300, 4096), (17, 8192), (3, 12288)])
+@pytest.mark.parametrize("rows,d", [(5, 256), (300, 4096), (17, 8192), (3, 12288), (1, 4096), (4096, 4096), (5003, 1024), (2401, 8192)])
 def test_rmsnorm_fwd_bwd(rows, d):
     torch.manual_seed(rows + d)
     x = torch.randn(rows, d, device="cuda").to(torch.bfloat16).requires_grad_(True)
@@ -29,10 +29,11 @@ def test_rmsnorm_fwd_bwd(rows, d):
     assert ((w.grad.float() - wr.grad).norm() / wr.grad.norm()).item() < 2e-2
 
 
-def test_rmsnorm_residual_fused():
+@pytest.mark.parametrize("rows", [64, 67, 4801])
+def test_rmsnorm_residual_fused(rows):
     torch.manual_seed(0)
-    x = torch.randn(64, 1024, device="cuda").to(torch.bfloat16)
-    r = torch.randn(64, 1024, device="cuda").to(torch.bfloat16)
+    x = torch.randn(rows, 1024, device="cuda").to(torch.bfloat16)
+    r = torch.randn(rows, 1024, device="cuda").to(torch.bfloat16)
     w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
     y, rstd, xs = ops.rmsnorm_fwd(x, w, 1e-5, residual=r)
     s = (x.float() + r.float()).to(torch.bfloat16)
