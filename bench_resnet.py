@@ -108,7 +108,9 @@ def main():
     ms, launches, last = timed(False)
     ms2, _, last2 = timed(True)
     from ferrotorch_b200.ops import conv as _conv
-    library_ops = ["conv 7x7 stem (cuDNN)", "global avg pool", "classifier GEMM (cuBLAS via autocast)"]
+    library_ops = ["global average pool and flatten (tensor reductions)"]
+    if _conv._STEM_MODE != "gemm":
+        library_ops.insert(0, "conv 7x7 stem (cuDNN)")
     if _conv._ROWS_MODE not in ("1", "all"):
         library_ops.insert(1, "conv 3x3 stride 2: forward and both gradients (cuDNN)")
     if _conv._WGRAD_MODE not in ("gemm", "fused") and _conv._ROWS_MODE != "all":

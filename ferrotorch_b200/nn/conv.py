@@ -154,6 +154,8 @@ class Conv2d(_ConvNd):
         if x.is_cuda and x.dim() == 4 and self.padding_mode == "zeros" and not isinstance(self.padding, str):
             if torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16:
                 x = x.to(torch.bfloat16)
+            if x.dtype == torch.bfloat16 and self.bias is None and ops.conv.conv_stem_eligible(x, w, self.stride, self.padding, self.dilation, self.groups):
+                return ops.conv.conv_stem(x, w, self.stride, self.padding)              # few input channels: patch matrix + GEMM
             if x.dtype == torch.bfloat16 and x.is_contiguous(memory_format=torch.channels_last):
                 if ops.conv.conv3x3_eligible(x, w, self.stride, self.padding, self.dilation, self.groups):
                     y = ops.conv3x3(x, w)

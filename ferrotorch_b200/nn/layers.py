@@ -81,6 +81,10 @@ class Linear(Module):
                 # f32 master with an optimizer-maintained bf16 copy: no cast launch, f32 weight gradient straight from the GEMM
                 b = None if self.bias is None else self.bias.to(torch.bfloat16)
                 return ops.linear_master(x.to(torch.bfloat16), w, wc, b)
+            if x.is_cuda:
+                # f32 master without a maintained copy: cast once here, run this package's GEMM, f32 weight gradient straight from its split-K form
+                b = None if self.bias is None else self.bias.to(torch.bfloat16)
+                return ops.linear_master(x.to(torch.bfloat16), w, w.detach().to(torch.bfloat16), b)
         return ops.linear(x, w, self.bias)
 
     def extra_repr(self) -> str:

@@ -344,3 +344,64 @@ def conv3x3(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     if not conv3x3_eligible(x, weight, 1, 1, 1, 1):
         raise InvalidArgument("conv3x3 needs a channels_last CUDA bf16 input with Cin % 64 == 0 and Cout % 8 == 0")
     return _Conv3x3Fn.apply(x, weight)
+
+
+# -- first-layer convolution of image nets (few input channels, large window): explicit patch matrix + tcgen05 GEMM ----------------------------
+# FT_CONV_STEM: "gemm" (default) = the route below, "library" = torch.nn.functional.conv2d (A/B switch)
+_STEM_MODE = os.environ.get("FT_CONV_STEM", "gemm")
+
+
+def conv_stem_eligible(x: torch.Tensor, weight: torch.Tensor, stride, padding, dilation, groups) -> bool:
+    """Few input channels (``C * kh * kw <= 512``), no dilation / groups, input that needs no gradient: the implicit-GEMM kernels want at
+    least 64 input channels, and with three the patch matrix is small enough to write out (1 GB for 256 images of 224 x 224)."""
+    as2 = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)          # noqa: E731
+    return (_STEM_MODE == "gemm" and not _FORCE_LIBRARY and x.is_cuda and x.dim() == 4 and not x.requires_grad and weight.dim() == 4
+            and x.dtype in (torch.bfloat16, torch.float32) and as2(dilation) == (1, 1) and groups == 1 and not isinstance(padding, str)
+            and weight.shape[1] * weight.shape[2] * weight.shape[3] <= 512 and weight.shape[0] % 8 == 0 and weight.shape[1] < 64
+            and weight.dtype in (torch.float32, torch.bfloat16))
+
+
+class _ConvStemFn(torch.autograd.Function):
+    """``y = patches(x) @ W^T`` with the patch matrix ``[N*Ho*Wo, C*kh*kw]`` (K padded to a multiple of 8) written by one strided copy;
+    the weight gradient is ``dy^T @ patches`` in f32 straight from the split-K GEMM. The input receives no gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w, stride, padding):
+        from .gemm import gemm
+        N, C, H, W = x.shape
+        Co, _, kh, kw = w.shape
+        (sh, sw), (ph, pw) = stride, padding
+        Ho, Wo = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        K = C * kh * kw
+        Kp = (K + 7) // 8 * 8
+        xp = torch.zeros(N, C, H + 2 * ph, W + 2 * pw, device=x.device, dtype=torch.bfloat16)
+        xp[:, :, ph: ph + H, pw: pw + W].copy_(x)
+        win = xp.unfold(2, kh, sh).unfold(3, kw, sw)                         # [N, C, Ho, Wo, kh, kw] view
+        A = torch.empty(N * Ho * Wo, Kp, device=x.device, dtype=torch.bfloat16)
+        A4 = A.view(N, Ho, Wo, Kp)
+        A4[..., :K].unflatten(-1, (C, kh, kw)).copy_(win.permute(0, 2, 3, 1, 4, 5))
+        if Kp > K:
+            A4[..., K:].zero_()
+        wb = torch.zeros(Co, Kp, device=x.device, dtype=torch.bfloat16)
+        wb[:, :K].copy_(w.reshape(Co, K))
+        y = gemm(A, wb)                                                      # [N*Ho*Wo, Co] = the channels-last output
+        ctx.save_for_backward(A)
+        ctx.meta = (w.shape, w.dtype, K)
+        return y.view(N, Ho, Wo, Co).permute(0, 3, 1, 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .gemm import gemm
+        (A,) = ctx.saved_tensors
+        wshape, wdtype, K = ctx.meta
+        dy2 = dy.permute(0, 2, 3, 1).reshape(-1, wshape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dw = gemm(dy2.to(torch.bfloat16), A, a_mn=True, b_mn=True, out_dtype=torch.float32)       # [Co, Kp]
+        return None, dw[:, :K].reshape(wshape).to(wdtype), None, None
+
+
+def conv_stem(x: torch.Tensor, weight: torch.Tensor, stride=(2, 2), padding=(3, 3)) -> torch.Tensor:
+    """First-layer convolution as patch matrix x GEMM; returns a channels-last bf16 ``[N, Cout, Ho, Wo]``."""
+    as2 = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)          # noqa: E731
+    return _ConvStemFn.apply(x, weight, as2(stride), as2(padding))

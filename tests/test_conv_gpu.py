@@ -91,3 +91,45 @@ def test_conv3x3_rows_forward_and_gradients_on_device(N, C, Co, H, W, stride):
         err, scale = (got.float() - ref).abs().max().item(), ref.abs().max().item()
         assert err <= 2e-2 * scale + 2e-2, (what, err, scale)
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("N,C,H,W,Co,k,s,p", [(4, 3, 64, 48, 64, 7, 2, 3), (2, 3, 33, 35, 32, 7, 2, 3), (3, 1, 28, 28, 16, 5, 1, 2), (2, 4, 17, 19, 24, 3, 2, 1)])
+def test_first_layer_convolution_as_patch_gemm(N, C, H, W, Co, k, s, p):
+    """The few-input-channel route (patch matrix + tcgen05 GEMM, f32 weight gradient from the split-K form) against the f32 convolution."""
+    import ferrotorch_b200.nn as nn
+    from ferrotorch_b200.ops import conv as C_
+    torch.manual_seed(0)
+    conv = nn.Conv2d(C, Co, k, s, p, bias=False).cuda()
+    x = torch.randn(N, C, H, W, device="cuda")
+    assert C_.conv_stem_eligible(x.bfloat16(), conv.weight, conv.stride, conv.padding, conv.dilation, conv.groups)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = conv(x)
+    assert y.dtype == torch.bfloat16 and y.is_contiguous(memory_format=torch.channels_last)
+    wf = conv.weight.detach().bfloat16().float().requires_grad_()
+    ref = torch.nn.functional.conv2d(x.bfloat16().float(), wf, None, s, p)
+    assert y.shape == ref.shape and ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    g = torch.randn_like(ref)
+    y.backward(g.to(y.dtype))
+    ref.backward(g.bfloat16().float())
+    assert conv.weight.grad.dtype == torch.float32 and ((conv.weight.grad - wf.grad).norm() / wf.grad.norm()).item() < 1e-2
+
+
+def test_autocast_linear_with_f32_master_runs_on_the_package_gemm():
+    import ferrotorch_b200.nn as nn
+    torch.manual_seed(1)
+    lin = nn.Linear(256, 1000).cuda()
+    with torch.no_grad():
+        lin.bias.uniform_(-0.5, 0.5)
+    x = torch.randn(96, 256, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = lin(x)
+    assert y.dtype == torch.bfloat16
+    xr = x.detach().bfloat16().float().requires_grad_()
+    wr = lin.weight.detach().bfloat16().float().requires_grad_()
+    ref = torch.nn.functional.linear(xr, wr, lin.bias.detach().bfloat16().float())
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    g = torch.randn_like(ref)
+    y.backward(g.to(y.dtype))
+    ref.backward(g.bfloat16().float())
+    assert lin.weight.grad.dtype == torch.float32 and ((lin.weight.grad - wr.grad).norm() / wr.grad.norm()).item() < 1e-2
+    assert ((x.grad - xr.grad).norm() / xr.grad.norm()).item() < 1e-2 and ((lin.bias.grad - g.bfloat16().float().sum(0)).abs().max() < 0.1)

@@ -38,3 +38,13 @@ def test_guide_snippets(tmp_path):
     guard = gpu.MemoryGuardBuilder().with_budget(8 << 30).with_policy(gpu.OomPolicy.RETRY_AFTER_FREE).with_query(lambda: (0, 16 << 30)).build()
     with guard.reserve(1 << 20):
         assert guard.stats().reserved_by_guard == 1 << 20
+    # 9. layers
+    net = nn.Sequential(nn.Conv2d(3, 16, 3, padding=1, padding_mode="reflect"), nn.BatchNorm2d(16), nn.HardSwish(), nn.AdaptiveAvgPool2d(1), nn.Flatten(),
+                        nn.Linear(16, 4))
+    assert net(torch.randn(2, 3, 8, 8)).shape == (2, 4)
+    lstm = nn.LSTM(32, 64, num_layers=2, bidirectional=True)
+    out, (h, c) = lstm(torch.randn(5, 3, 32))
+    assert out.shape == (5, 3, 128) and h.shape == (4, 3, 64)
+    enc = nn.TransformerEncoder(nn.TransformerEncoderLayer(64, 4, 128, dropout=0.0, batch_first=True), 2)
+    assert enc(torch.randn(2, 10, 64), src_key_padding_mask=torch.zeros(2, 10, dtype=torch.bool)).shape == (2, 10, 64)
+    assert nn.attention_backend(torch.randn(1, 2, 8, 64)) == "standard"
