@@ -108,7 +108,7 @@ def main():
     ms, launches, last = timed(False)
     ms2, _, last2 = timed(True)
     from ferrotorch_b200.ops import conv as _conv
-    library_ops = ["global average pool and flatten (tensor reductions)"]
+    library_ops = []
     if _conv._STEM_MODE != "gemm":
         library_ops.insert(0, "conv 7x7 stem (cuDNN)")
     if _conv._ROWS_MODE not in ("1", "all"):

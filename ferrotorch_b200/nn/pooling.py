@@ -155,6 +155,27 @@ def _adaptive_bounds(n: int, o: int) -> List[Tuple[int, int]]:
     return [((i * n) // o, -(-((i + 1) * n) // o)) for i in range(o)]
 
 
+class _GlobalAvgPoolNHWC(torch.autograd.Function):
+    """Mean over the spatial positions of a channels-last ``[N, C, H, W]`` activation on this package's reduction kernel (the rows of one
+    image are ``[H*W, C]`` in memory); the gradient is the broadcast of ``dy / (H*W)``, materialised channels-last by the strided-copy kernel."""
+
+    @staticmethod
+    def forward(ctx, x):
+        from ..ops import tensor_ops as T
+        N, C, H, W = x.shape
+        ctx.shape = (N, C, H, W)
+        rows = x.permute(0, 2, 3, 1).reshape(N, H * W, C)                      # a view of channels-last storage
+        return T.reduce("mean", rows, 1).view(N, C, 1, 1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import tensor_ops as T
+        N, C, H, W = ctx.shape
+        g = T.unary("scale", dy.reshape(N, C).contiguous(), 1.0 / (H * W), 0.0)
+        dense = T.contiguous(g.view(N, 1, C).expand(N, H * W, C))               # [N, H*W, C] = channels-last memory of the result
+        return dense.view(N, H, W, C).permute(0, 3, 1, 2)
+
+
 def _adaptive(x, nd, output_size, kind: str, return_indices: bool = False):
     if x.dim() < nd + 1:
         raise ShapeMismatch(f"expected at least {nd + 1} dimensions, got {list(x.shape)}")
@@ -162,6 +183,9 @@ def _adaptive(x, nd, output_size, kind: str, return_indices: bool = False):
     if len(out) != nd:
         raise InvalidArgument(f"output_size: expected {nd} values, got {len(out)}")
     out = tuple(x.shape[x.dim() - nd + i] if o is None else int(o) for i, o in enumerate(out))        # None keeps the input size
+    if (kind == "avg" and nd == 2 and out == (1, 1) and x.dim() == 4 and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16)
+            and x.is_contiguous(memory_format=torch.channels_last) and x.shape[0] <= 65535):
+        return _GlobalAvgPoolNHWC.apply(x)
     if kind == "avg" or not return_indices:
         y = x
         for i in range(nd):

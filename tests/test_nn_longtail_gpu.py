@@ -133,3 +133,16 @@ def test_derivatives_at_the_kinks_follow_pytorch():
             yb.sum().backward()
             assert torch.equal(a.grad[:4], b.grad[:4]), (type(ours).__name__, a.grad.tolist(), b.grad.tolist())       # the four kink points
             assert torch.allclose(a.grad.float(), b.grad.float(), atol=tol)
+
+
+def test_global_average_pool_channels_last_kernel_route():
+    torch.manual_seed(5)
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        x = torch.randn(6, 32, 7, 5, device="cuda").to(dtype).contiguous(memory_format=torch.channels_last)
+        a, b = x.clone().requires_grad_(), x.float().clone().requires_grad_()
+        ya, yb = nn.AdaptiveAvgPool2d(1)(a), tnn.AdaptiveAvgPool2d(1)(b)
+        assert ya.shape == (6, 32, 1, 1) and torch.allclose(ya.float(), yb, atol=tol)
+        w = torch.randn_like(yb)
+        (ya.float() * w).sum().backward()
+        (yb * w).sum().backward()
+        assert a.grad.is_contiguous(memory_format=torch.channels_last) and torch.allclose(a.grad.float(), b.grad, atol=tol)
