@@ -10,9 +10,9 @@
 
 #define FT_VPT_DISPATCH(d, ...)                              \
   do {                                                      \
-    if ((d) <= 512 * 8) { constexpr int V = 1; constexpr int R = 4; __VA_ARGS__; } \
-    else if ((d) <= 512 * 16) { constexpr int V = 2; constexpr int R = 2; __VA_ARGS__; } \
-    else { constexpr int V = 4; constexpr int R = 1; __VA_ARGS__; (void)R; } \
+    if ((d) <= 512 * 8) { constexpr int V = 1; constexpr int R = 4; (void)R; __VA_ARGS__; } \
+    else if ((d) <= 512 * 16) { constexpr int V = 2; constexpr int R = 2; (void)R; __VA_ARGS__; } \
+    else { constexpr int V = 4; constexpr int R = 1; (void)R; __VA_ARGS__; } \
   } while (0)
 
 namespace {
