@@ -46,7 +46,10 @@ class TpGemmContext:
         #            (multimem.ld_reduce), or by peer loads in fixed rank order when the buffer has no multicast mapping
         # form "v1": the single-kernel forms of csrc/kernels/gemm_tp.cu (copier CTAs / TMA stores into the owner's staging buffer).
         import os
-        self.form = os.environ.get("FT_TP_FORM", "v2")
+        # Default by measurement (8192 tokens x hidden 8192): at 2 GPUs the v2 forms lead (1.10x / 1.06x of NCCL + GEMM); at 8 GPUs the
+        # all-gather GEMM is faster as v1 (0.355 ms against 0.456 ms: seven copy-engine transfers per rank cost more than the copier CTAs) and
+        # the reduce-scatter GEMM as v2 (0.397 ms against 0.420 ms). FT_TP_FORM=v1|v2 forces one form for both.
+        self.form = os.environ.get("FT_TP_FORM") or ("v1" if (mode == "ag_gemm" and W > 4) else "v2")
         if self.form == "v2":
             from .symm import SymmComm
             if mode == "ag_gemm":
