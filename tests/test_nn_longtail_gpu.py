@@ -125,7 +125,7 @@ def test_derivatives_at_the_kinks_follow_pytorch():
     x = torch.tensor([-3.0, 3.0, 0.0, 6.0, -1.0, 1.0, 7.0, -4.0], device="cuda")
     for ours, theirs in ((nn.HardSwish(), tnn.Hardswish()), (nn.ReLU6(), tnn.ReLU6()), (nn.Hardtanh(-3.0, 3.0), tnn.Hardtanh(-3.0, 3.0)), (nn.ReLU(), tnn.ReLU())):
         for dtype in (torch.float32, torch.bfloat16):
-            a, b = x.to(dtype).requires_grad_(), x.to(dtype).requires_grad_()
+            a, b = x.clone().to(dtype).requires_grad_(), x.clone().to(dtype).requires_grad_()
             ya, yb = ours(a), theirs(b)
             tol = 1e-6 if dtype == torch.float32 else 1e-2
             assert torch.allclose(ya.float(), yb.float(), atol=tol), type(ours).__name__
