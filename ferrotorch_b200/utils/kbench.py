@@ -166,6 +166,21 @@ def single_attn():
     print("attn1 done", float(out[0, 0]))
 
 
+def single_norm():
+    """Three launches each of the RMSNorm forward (with residual) and backward at 16384 x 4096 bf16 (128 MB per tensor, larger than L2): a
+    small, self-terminating case for profiler captures."""
+    from ferrotorch_b200 import ops
+    T, d = 16384, 4096
+    x = torch.randn(T, d, device="cuda").to(torch.bfloat16)
+    r = torch.randn(T, d, device="cuda").to(torch.bfloat16)
+    w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        y, rstd, xs = ops.rmsnorm_fwd(x, w, 1e-5, residual=r)
+        dx, dw = ops.rmsnorm_bwd(xs, w, y, rstd)
+    torch.cuda.synchronize()
+    print("norm1 done", float(y[0, 0]), float(dx[0, 0]))
+
+
 def bench_paged(results):
     """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1."""
     import math
@@ -200,6 +215,8 @@ def main():
         return single_gemm()
     if a.what == "attn1":
         return single_attn()
+    if a.what == "norm1":
+        return single_norm()
     if a.what in ("gemm", "all"):
         bench_gemm(res)
     if a.what in ("attn", "all"):
