@@ -42,8 +42,8 @@ FT_DEVICE void block_sum_n(float (&v)[R], float* red) {
 inline int norm_rows_per_iter(int) { return 1; }
 
 // y = (x [+ res]) * rstd * w ;  optionally writes the summed residual stream back to `xout`.
-template <int MAXV, bool HAS_RES, int R>
-__global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+template <int MAXV, bool HAS_RES, int R, int NTT = NT, int MINB = 1>
+__global__ void __launch_bounds__(NTT, MINB) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                                                          const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                          __nv_bfloat16* __restrict__ xout, float* __restrict__ rstd_out,
                                                          int rows, int d, float eps) {
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
         const bf16x8* rr = HAS_RES ? reinterpret_cast<const bf16x8*>(res + (size_t)row * d) : nullptr;
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
-          int c = threadIdx.x + i * NT;
+          int c = threadIdx.x + i * NTT;
           if (c < nvec) {
             bf16x8_to_float(xr[c], v[r][i]);
             if (HAS_RES) {
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
         if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
-          int c = threadIdx.x + i * NT;
+          int c = threadIdx.x + i * NTT;
           if (c < nvec) {
             float wv[8], o[8];
             bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv);
@@ -103,8 +103,8 @@ __global__ void __launch_bounds__(NT) rmsnorm_fwd_kernel(const __nv_bfloat16* __
 }
 
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) [+ dres]; dw partial per CTA in f32. Groups of R rows as in the forward kernel.
-template <int MAXV, bool HAS_DRES, int R>
-__global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+template <int MAXV, bool HAS_DRES, int R, int NTT = NT, int MINB = 1>
+__global__ void __launch_bounds__(NTT, MINB) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
                                                          const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                                                          float* __restrict__ dw_partial, int rows, int d) {
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   float wv[MAXV][8];
 #pragma unroll
   for (int i = 0; i < MAXV; i++) {
-    int c = threadIdx.x + i * NT;
+    int c = threadIdx.x + i * NTT;
     if (c < nvec) bf16x8_to_float(reinterpret_cast<const bf16x8*>(w)[c], wv[i]);
   }
   for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
       if (row < rows) {
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
-          int c = threadIdx.x + i * NT;
+          int c = threadIdx.x + i * NTT;
           if (c < nvec) {
             float xv[8], dyv[8];
             bf16x8_to_float(reinterpret_cast<const bf16x8*>(x + (size_t)row * d)[c], xv);
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
         const float dm = dot[r] / (float)d;
 #pragma unroll
         for (int i = 0; i < MAXV; i++) {
-          int c = threadIdx.x + i * NT;
+          int c = threadIdx.x + i * NTT;
           if (c < nvec) {
             float o[8];
 #pragma unroll
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_bwd_kernel(const __nv_bfloat16* __
   }
 #pragma unroll
   for (int i = 0; i < MAXV; i++) {
-    int c = threadIdx.x + i * NT;
+    int c = threadIdx.x + i * NTT;
     if (c < nvec) {
       float4* p = reinterpret_cast<float4*>(dw_partial + (size_t)blockIdx.x * d + (size_t)c * 8);
       p[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
@@ -317,19 +317,44 @@ __global__ void __launch_bounds__(NT) layernorm_bwd_kernel(const __nv_bfloat16* 
 }  // namespace
 
 // Number of per-CTA partial rows the backward kernels write for `rows` rows.
-FT_EXPORT int ft_norm_bwd_parts(int rows) { return rows < 296 ? rows : 296; }
+FT_EXPORT int ft_norm_bwd_parts(int rows) { return rows < 592 ? rows : 592; }
+
+// Thread / vector shape of the RMSNorm kernels for rows of at most 4096 elements (4096 x 4096 bf16 on a B200, CUDA events):
+//   0  512 threads x 1 vector                    forward 26.6 us (3 CTAs per SM at 38 registers)   backward 42.0 us (2 CTAs per SM, 296 CTAs)
+//   1  forward 512 x 1 held to 32 registers        forward 24.6 us (4 CTAs per SM)
+//   2  256 threads x 2 vectors                    forward 22.5 us (twice the bytes in flight)       backward 46.1 us (up to 444 CTAs)
+// Defaults: forward 2, backward 0. FT_NORM_VARIANT (read once) forces one number for both directions (A/B switch).
+static int norm_variant(int dflt) {
+  static int v = -2;
+  if (v == -2) {
+    const char* e = getenv("FT_NORM_VARIANT");
+    v = e ? atoi(e) : -1;
+  }
+  return v >= 0 ? v : dflt;
+}
 
 FT_EXPORT int ft_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* xout, float* rstd, int rows, int d,
                              float eps, cudaStream_t st) {
   if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
   const int groups = (rows + norm_rows_per_iter(d) - 1) / norm_rows_per_iter(d);
   int grid = groups < 148 * 8 ? groups : 148 * 8;
+  const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *rp = (const __nv_bfloat16*)res, *wp = (const __nv_bfloat16*)w;
+  __nv_bfloat16 *yp = (__nv_bfloat16*)y, *xo = (__nv_bfloat16*)xout;
+  if (d <= 512 * 8 && norm_variant(2) == 1) {
+    if (res) rmsnorm_fwd_kernel<1, true, 1, 512, 4><<<grid, 512, 0, st>>>(xp, rp, wp, yp, xo, rstd, rows, d, eps);
+    else rmsnorm_fwd_kernel<1, false, 1, 512, 4><<<grid, 512, 0, st>>>(xp, nullptr, wp, yp, nullptr, rstd, rows, d, eps);
+    return (int)cudaGetLastError();
+  }
+  if (d <= 512 * 8 && norm_variant(2) == 2) {
+    grid = groups < 148 * 12 ? groups : 148 * 12;
+    if (res) rmsnorm_fwd_kernel<2, true, 1, 256, 6><<<grid, 256, 0, st>>>(xp, rp, wp, yp, xo, rstd, rows, d, eps);
+    else rmsnorm_fwd_kernel<2, false, 1, 256, 6><<<grid, 256, 0, st>>>(xp, nullptr, wp, yp, nullptr, rstd, rows, d, eps);
+    return (int)cudaGetLastError();
+  }
   if (res)
-    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, true, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-                                                  (__nv_bfloat16*)y, (__nv_bfloat16*)xout, rstd, rows, d, eps));
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, true, R><<<grid, NT, 0, st>>>(xp, rp, wp, yp, xo, rstd, rows, d, eps));
   else
-    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, false, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
-                                                   nullptr, rstd, rows, d, eps));
+    FT_VPT_DISPATCH(d, rmsnorm_fwd_kernel<V, false, R><<<grid, NT, 0, st>>>(xp, nullptr, wp, yp, nullptr, rstd, rows, d, eps));
   return (int)cudaGetLastError();
 }
 
@@ -338,13 +363,18 @@ FT_EXPORT int ft_rmsnorm_bwd(const void* x, const void* w, const void* dy, const
                              float* dw_partial, void* dw_bf16, float* dw_f32, int accumulate, int rows, int d, cudaStream_t st) {
   if (d % 8 || d > NT * MAXV_LIMIT * 8 || rows <= 0) return FT_ERR_ARG;
   const int groups = (rows + norm_rows_per_iter(d) - 1) / norm_rows_per_iter(d);
-  int grid = groups < ft_norm_bwd_parts(rows) ? groups : ft_norm_bwd_parts(rows);      // never more partial rows than the caller's scratch holds
-  if (dres)
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
-                                                  (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dw_partial, rows, d));
-  else
-    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false, R><<<grid, NT, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd,
-                                                   nullptr, (__nv_bfloat16*)dx, dw_partial, rows, d));
+  int grid = groups < 296 ? groups : 296;      // never more partial rows than ft_norm_bwd_parts(rows), which sizes the caller's scratch
+  const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w, *dyp = (const __nv_bfloat16*)dy, *drp = (const __nv_bfloat16*)dres;
+  __nv_bfloat16* dxp = (__nv_bfloat16*)dx;
+  if (d <= 512 * 8 && norm_variant(0) == 2) {
+    grid = groups < 444 ? groups : 444;
+    if (dres) rmsnorm_bwd_kernel<2, true, 1, 256, 3><<<grid, 256, 0, st>>>(xp, wp, dyp, rstd, drp, dxp, dw_partial, rows, d);
+    else rmsnorm_bwd_kernel<2, false, 1, 256, 3><<<grid, 256, 0, st>>>(xp, wp, dyp, rstd, nullptr, dxp, dw_partial, rows, d);
+  } else if (dres) {
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, true, R><<<grid, NT, 0, st>>>(xp, wp, dyp, rstd, drp, dxp, dw_partial, rows, d));
+  } else {
+    FT_VPT_DISPATCH(d, rmsnorm_bwd_kernel<V, false, R><<<grid, NT, 0, st>>>(xp, wp, dyp, rstd, nullptr, dxp, dw_partial, rows, d));
+  }
   colsum_partials_kernel<<<(d + 31) / 32, dim3(32, 8), 0, st>>>(dw_partial, (__nv_bfloat16*)dw_bf16, dw_f32, grid, d, accumulate);
   return (int)cudaGetLastError();
 }
