@@ -181,6 +181,29 @@ def single_norm():
     print("norm1 done", float(y[0, 0]), float(dx[0, 0]))
 
 
+def single_elementwise():
+    """Two launches each of SwiGLU forward / backward (4096 x 14336), rotary embedding, the fused cross-entropy (4096 x 128256) and the flat
+    AdamW update (64 M parameters, 1.8 GB of state): every tensor is larger than L2 and the whole case holds about 4 GB, for profiler captures."""
+    from ferrotorch_b200 import ops
+    T, F, V, n = 4096, 14336, 128256, 64 << 20
+    gu = torch.randn(T, 2 * F, device="cuda").to(torch.bfloat16)
+    da = torch.randn(T, F, device="cuda").to(torch.bfloat16)
+    qkv = torch.randn(T, 48 * 128, device="cuda").to(torch.bfloat16)
+    cos, sin = ops.rope_tables(T, 128, 500000.0, "cuda")
+    tg = torch.randint(0, V, (T,), device="cuda")
+    master, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    pb, g = torch.zeros(n, device="cuda", dtype=torch.bfloat16), torch.full((n,), 0.01, device="cuda", dtype=torch.bfloat16)
+    for i in range(2):
+        ops.swiglu_fwd(gu)
+        ops.swiglu_bwd(gu, da)
+        ops.rope_inplace(qkv, cos, sin, T, 0, 40, 128)
+        logits = torch.randn(T, V, device="cuda").to(torch.bfloat16)
+        loss, _, _ = ops.cross_entropy_fwd_bwd(logits, tg, inplace_grad=True)
+        ops.adamw_flat_(master, pb, m, v, g, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=i + 1)
+    torch.cuda.synchronize()
+    print("ew1 done", float(loss), float(master[0]))
+
+
 def bench_paged(results):
     """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1."""
     import math
@@ -217,6 +240,8 @@ def main():
         return single_attn()
     if a.what == "norm1":
         return single_norm()
+    if a.what == "ew1":
+        return single_elementwise()
     if a.what in ("gemm", "all"):
         bench_gemm(res)
     if a.what in ("attn", "all"):
