@@ -113,7 +113,6 @@ class FSDP:
         if os.environ.get("FT_NO_SIDE_STREAM") == "1":
             overlap_optimizer = False
         self._opt_ctas = int(os.environ.get("FT_OPT_CTAS", "148")) if (cuda and overlap_optimizer) else 0   # one 256-thread CTA per SM beside the GEMM (measured: two per SM no longer overlap with it)
-        self._debug_skip_opt = os.environ.get("FT_DEBUG_SKIP_OPT") == "1"      # diagnosis only: measures the step without any update
         self.side = torch.cuda.Stream(device=self.device, priority=-1) if (cuda and overlap_optimizer) else None
         # gradient buffers: a small rotating pool of full-size bf16 buffers, sized for the largest unit
         maxn = max(u.padded for u in self.units)
@@ -243,9 +242,7 @@ class FSDP:
             import contextlib
             ctx = contextlib.nullcontext()
         with ctx:
-            if self._debug_skip_opt:
-                pass
-            elif self.world == 1:
+            if self.world == 1:
                 ops.adamw_flat_(unit.master, unit.full, unit.exp_avg, unit.exp_avg_sq, unit.grad, lr=o.lr, beta1=o.betas[0],
                                 beta2=o.betas[1], eps=o.eps, weight_decay=o.weight_decay, step=unit.step, maximize=o.maximize,
                                 max_ctas=self._opt_ctas)
