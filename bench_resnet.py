@@ -77,10 +77,14 @@ def main():
             ready.record(copy_stream)
         return x, y, ready
 
+    from bench import ClockSampler          # nvidia-smi sampling of SM clock and throttle reasons during the timed region
+
     def timed(e2e: bool):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = _lib.launch_calls
         barrier()
+        sampler = ClockSampler(local)
+        sampler.start()
         e0.record()
         last = None
         nxt = fetch(0) if e2e else None
@@ -99,14 +103,15 @@ def main():
                 last = step(dx[i % 2], dy[i % 2])
         e1.record()
         torch.cuda.synchronize()
+        clocks = sampler.stop()
         ms = e0.elapsed_time(e1)
         if world > 1:
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t)
-        return ms, _lib.launch_calls - l0, last
-    ms, launches, last = timed(False)
-    ms2, _, last2 = timed(True)
+        return ms, _lib.launch_calls - l0, last, clocks
+    ms, launches, last, clocks = timed(False)
+    ms2, _, last2, clocks2 = timed(True)
     from ferrotorch_b200.ops import conv as _conv
     library_ops = []
     if _conv._STEM_MODE != "gemm":
@@ -125,6 +130,7 @@ def main():
                        "library_ops": library_ops, "l2": "inputs_larger_than_L2 (154 MB of images per step)"},
             "e2e": {"value": round(a.batch * world * a.steps / (ms2 / 1e3), 1), "unit": "images/s", "h2d_bytes_per_step": a.batch * (3 * 224 * 224 * 4 + 8),
                     "d2h_bytes_per_step": 4},
+            "clocks": clocks, "clocks_e2e": clocks2,
             "gpu_launches": int(launches), "last_loss": float(last), "kernel_status": _lib.read_status(), "impl": "ours"}))
     if world > 1:
         dist.destroy_process_group()
