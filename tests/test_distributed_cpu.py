@@ -477,3 +477,55 @@ def test_cpu_fsdp_hybrid_shard_world4_nodes_of_2():
     assert torch.equal(res[0][0][0], res[2][0][0])                                                         # and their gradients
     with pytest.raises(Exception):
         _threads(4, lambda b, r: fd.FSDP(torch.nn.Linear(4, 2), b, fd.ShardingStrategy.HybridShard, intra_node_size=3))
+
+
+def _syncbn_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from ferrotorch_b200 import nn
+    from ferrotorch_b200.parallel import SyncBatchNorm2d
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        full = torch.randn(4 * world, 6, 5, 5) * 2 + 1                     # the batch of all ranks; this rank holds its slice
+        w = torch.randn(4 * world, 6, 5, 5)
+        ref_bn = torch.nn.BatchNorm2d(6)
+        with torch.no_grad():
+            ref_bn.weight.uniform_(0.5, 1.5)
+            ref_bn.bias.uniform_(-0.5, 0.5)
+        plain = nn.Sequential(nn.Conv2d(6, 6, 1), nn.BatchNorm2d(6))
+        plain[1].load_state_dict(ref_bn.state_dict())
+        conv = SyncBatchNorm2d.convert(plain)
+        assert isinstance(conv[1], SyncBatchNorm2d) and isinstance(conv[0], nn.Conv2d) and conv[1].training
+        sbn = conv[1]
+        sl = slice(4 * rank, 4 * (rank + 1))
+        x = full[sl].clone().requires_grad_()
+        y = sbn(x)
+        (y * w[sl]).sum().backward()
+        xr = full.clone().requires_grad_()
+        yr = ref_bn(xr)
+        (yr * w).sum().backward()
+        errs = (float((y - yr[sl]).abs().max()), float((x.grad - xr.grad[sl]).abs().max()),
+                float((sbn.running_mean - ref_bn.running_mean).abs().max()), float((sbn.running_var - ref_bn.running_var).abs().max()))
+        gw = sbn.weight.grad.clone()
+        dist.all_reduce(gw)                                                # parameter gradients are local sums: DDP adds them up
+        errs += (float((gw - ref_bn.weight.grad).abs().max()),)
+        sbn.eval()
+        errs += (float((sbn(full[sl]) - ref_bn.eval()(full[sl])).abs().max()),)
+        q.put((rank, errs, int(sbn.num_batches_tracked)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sync_batch_norm_world2_gloo_equals_batch_norm_over_the_global_batch():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_syncbn_worker, args=(r, 2, 29747, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=120) for _ in ps]
+    for p in ps:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, errs, tracked in res:
+        assert max(errs) < 1e-4 and tracked == 1, (rank, errs, tracked)
