@@ -135,7 +135,7 @@ FT_DEVICE void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, u
 }
 FT_DEVICE uint32_t pa_sw(int row, int chunk) { return (uint32_t)(row * 256 + ((chunk ^ (row & 7)) << 4)); }
 
-__global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+__global__ void __launch_bounds__(128, 2) paged_attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                                                 const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                                                                 int max_blocks, const int* __restrict__ seq_lens, int Hq, int Hkv, float scale,
                                                                 float* __restrict__ ws, int* __restrict__ counters,
@@ -320,14 +320,23 @@ __global__ void __launch_bounds__(128) paged_attn_decode_kernel(const __nv_bfloa
     sm_L[g] = ll;
   }
   __syncthreads();
+  // Each thread owns one float4 column of one query head per pass; the partials of sixteen splits are requested before any is used, with
+  // the tail of the split range predicated rather than peeled, so that the pass costs ceil(nsplit / 16) memory round trips whatever
+  // nsplit is (a peeled remainder loop issued its loads one after another: a round trip per leftover split).
   for (int i = threadIdx.x; i < G * (D / 4); i += 128) {
     const int g = i / (D / 4), d4 = (i % (D / 4)) * 4;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 16
-    for (int s = 0; s < nsplit; s++) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(base + ((size_t)s * G + g) * PA_WS_ROW + d4));
-      const float f = sm_pm[s * G + g];
-      a.x += v.x * f; a.y += v.y * f; a.z += v.z * f; a.w += v.w * f;
+    const float* col = base + (size_t)g * PA_WS_ROW + d4;
+    for (int s0 = 0; s0 < nsplit; s0 += 16) {
+      float4 v[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++)
+        v[j] = (s0 + j < nsplit) ? __ldcg(reinterpret_cast<const float4*>(col + (size_t)(s0 + j) * G * PA_WS_ROW)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const float f = (s0 + j < nsplit) ? sm_pm[(s0 + j) * G + g] : 0.f;
+        a.x += v[j].x * f; a.y += v[j].y * f; a.z += v[j].z * f; a.w += v[j].w * f;
+      }
     }
     const float inv = sm_L[g] > 0.f ? 1.f / sm_L[g] : 0.f;
     __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv), hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);

@@ -204,12 +204,38 @@ def single_elementwise():
     print("ew1 done", float(loss), float(master[0]))
 
 
+def single_conv_paged():
+    """Two launches each of the implicit-GEMM 3x3 convolution (forward and input gradient, 64 x 256 x 56 x 56 channels-last bf16: 103 MB per
+    activation tensor) and of the paged decode attention at the per-rank shape of 70B TP=8 (8 query heads, 1 KV head, batch 8, 2304 cached
+    tokens): a small, self-terminating case for profiler captures."""
+    import math
+    from ferrotorch_b200 import _lib, ops
+    x = torch.randn(64, 256, 56, 56, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last).requires_grad_()
+    w = (torch.randn(256, 256, 3, 3, device="cuda") * 0.02).to(torch.bfloat16)
+    Hq, Hkv, B, L, nsplit, D = 8, 1, 8, 2304, 16, 128
+    mb = (L + 15) // 16
+    kc = torch.randn(B * mb, 16, Hkv, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn_like(kc)
+    bt = torch.arange(B * mb, device="cuda", dtype=torch.int32).view(B, mb)
+    lens = torch.full((B,), L, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    ws = torch.zeros(B * Hkv * nsplit * (Hq // Hkv) * 132, device="cuda")
+    ctr = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
+    for _ in range(2):
+        y = ops.conv3x3(x, w)
+        (gx,) = torch.autograd.grad(y, x, torch.ones_like(y))
+        _lib.call("ft_paged_attn_decode", q, kc, vc, bt, mb, lens, B, Hq, Hkv, D, 1 / math.sqrt(D), nsplit, ws, ctr, out, _lib.S())
+    torch.cuda.synchronize()
+    print("conv1 done", float(y[0, 0, 0, 0]), float(gx[0, 0, 0, 0]), float(out[0, 0, 0]))
+
+
 def bench_paged(results):
     """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1."""
     import math
     from ferrotorch_b200 import _lib
     pk = peaks()
-    for Hq, Hkv, B, L, nsplit in [(8, 1, 8, 2304, 16), (8, 1, 8, 2304, 37), (64, 8, 8, 2304, 5), (64, 8, 8, 2304, 16)]:
+    for Hq, Hkv, B, L, nsplit in [(8, 1, 8, 2304, 16), (8, 1, 8, 2304, 37), (64, 8, 8, 2304, 4), (64, 8, 8, 2304, 16)]:
         D, mb = 128, (L + 15) // 16
         kc = torch.randn(B * mb, 16, Hkv, D, device="cuda").to(torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -242,6 +268,8 @@ def main():
         return single_norm()
     if a.what == "ew1":
         return single_elementwise()
+    if a.what == "conv1":
+        return single_conv_paged()
     if a.what in ("gemm", "all"):
         bench_gemm(res)
     if a.what in ("attn", "all"):

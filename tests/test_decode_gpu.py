@@ -28,8 +28,9 @@ def test_splitk_gemm_planes_sum_to_product(N, K, splits):
     assert (out.float() - ref[:5]).abs().max().item() <= 2e-2 * ref.abs().max().item()
 
 
-@pytest.mark.parametrize("Hq,Hkv", [(8, 1), (4, 2), (2, 2)])
-def test_paged_attention_decode(Hq, Hkv):
+@pytest.mark.parametrize("Hq,Hkv,nsplit", [(8, 1, 4), (4, 2, 4), (2, 2, 4), (8, 1, 1), (8, 1, 13), (8, 1, 16), (8, 1, 37), (4, 2, 64)])
+def test_paged_attention_decode(Hq, Hkv, nsplit):
+    """Split counts on both sides of the combining pass's batch of sixteen, and more splits than a short sequence has pages (empty splits)."""
     torch.manual_seed(Hq * 10 + Hkv)
     B, D, max_blocks = 3, 128, 12
     lens = torch.tensor([1, 37, 160], device="cuda", dtype=torch.int32)
@@ -39,7 +40,6 @@ def test_paged_attention_decode(Hq, Hkv):
     perm = torch.randperm(nblk, device="cuda").to(torch.int32).view(B, max_blocks).contiguous()     # scattered pages
     q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
-    nsplit = 4
     ws = torch.zeros(B * Hkv * nsplit * (Hq // Hkv) * 132, device="cuda")
     ctr = torch.zeros(B * Hkv, device="cuda", dtype=torch.int32)
     for _ in range(2):      # second call checks that the counters reset themselves
