@@ -230,12 +230,18 @@ def single_conv_paged():
     print("conv1 done", float(y[0, 0, 0, 0]), float(gx[0, 0, 0, 0]), float(out[0, 0, 0]))
 
 
-def bench_paged(results):
-    """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1."""
+PAGED_CASES = [(8, 1, 8, 2304, 16), (8, 1, 8, 2304, 37), (64, 8, 8, 2304, 4), (64, 8, 8, 2304, 16)]
+PAGED_SWEEP = [(Hq, Hkv, B, L, n) for Hq, Hkv, B, L in [(8, 1, 8, 2304), (8, 1, 8, 640), (8, 1, 1, 2304), (8, 1, 32, 2304), (64, 8, 8, 2304), (32, 8, 8, 2304)]
+               for n in (1, 2, 4, 6, 8, 12, 16, 24, 37, 64)]
+
+
+def bench_paged(results, cases=PAGED_CASES):
+    """Paged decode attention at the per-rank shapes of 70B TP=8 (1 KV head, 8 query heads) and TP=1; `paged_sweep` walks the split
+    count at several batch sizes and lengths (the table the decode engine's choice of split count rests on)."""
     import math
     from ferrotorch_b200 import _lib
     pk = peaks()
-    for Hq, Hkv, B, L, nsplit in [(8, 1, 8, 2304, 16), (8, 1, 8, 2304, 37), (64, 8, 8, 2304, 4), (64, 8, 8, 2304, 16)]:
+    for Hq, Hkv, B, L, nsplit in cases:
         D, mb = 128, (L + 15) // 16
         kc = torch.randn(B * mb, 16, Hkv, D, device="cuda").to(torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -274,6 +280,8 @@ def main():
         bench_gemm(res)
     if a.what in ("attn", "all"):
         bench_attn(res)
+    if a.what == "paged_sweep":
+        bench_paged(res, PAGED_SWEEP)
     if a.what in ("paged", "all"):
         bench_paged(res)
     if a.what in ("elementwise", "all"):
