@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <functional>
+#include <string>
 #include <thread>
 #include <vector>
 
@@ -39,6 +40,14 @@ void ft_permutation(int64_t n, uint64_t seed, int64_t* out);
 void ft_philox_uniform(uint64_t seed, uint64_t offset, int64_t n, float* out);
 void ft_philox_normal(uint64_t seed, uint64_t offset, int64_t n, float* out);
 int64_t ft_nms_sorted_f32(const float* boxes, int64_t n, float thr, uint8_t* keep);
+void ft_tok_set_classes(const uint8_t* cls_table, int64_t n);
+int64_t ft_tok_split(int kind, const uint8_t* s, int64_t n, int64_t* ends, int64_t cap);
+void* ft_bpe_create(const int32_t* left, const int32_t* right, const int32_t* merged, int64_t n_merges, const int32_t* byte_sym, const uint32_t* char_cp,
+                    const int32_t* char_id, int64_t n_chars, const uint8_t* whole_bytes, const int64_t* whole_off, const int32_t* whole_id, int64_t n_whole);
+void ft_bpe_destroy(void* h);
+int64_t ft_bpe_encode(void* h, const uint8_t* bytes, const int64_t* off, int64_t n_pieces, int32_t* out, int64_t out_cap, int64_t* out_off, int nthreads);
+int64_t ft_bpe_encode_texts(void* h, int kind, const uint8_t* bytes, const int64_t* off, int64_t n_texts, int32_t* out, int64_t out_cap, int64_t* out_off,
+                            int nthreads);
 }
 
 static std::atomic<int> g_fail{0};
@@ -184,8 +193,49 @@ static void test_loader_and_planner() {
   CHECK(keep[0] == 1 && keep[1] == 0 && keep[2] == 1);
 }
 
+// Byte-level vocabulary: ids 0..255 are the bytes, 256 = "ab", 257 = "abc", 258 = " a", 259 = " ab" (never reachable: rank order forms
+// "ab" first). Single-threaded and threaded calls must agree, short pieces (array scan) and long ones (heap) too.
+static void test_tokenizer() {
+  std::vector<uint8_t> cls(128, 0);
+  for (int c = 'a'; c <= 'z'; c++) cls[(size_t)c] = 1;
+  for (int c = '0'; c <= '9'; c++) cls[(size_t)c] = 2;
+  cls[' '] = cls['\n'] = cls['\t'] = cls['\r'] = 4;
+  ft_tok_set_classes(cls.data(), (int64_t)cls.size());
+  int32_t byte_sym[256];
+  for (int i = 0; i < 256; i++) byte_sym[i] = i;
+  const int32_t left[4] = {'a', 256, ' ', 258}, right[4] = {'b', 'c', 'a', 'b'}, merged[4] = {256, 257, 258, 259};
+  void* h = ft_bpe_create(left, right, merged, 4, byte_sym, nullptr, nullptr, 0, nullptr, nullptr, nullptr, 0);
+  CHECK(h != nullptr);
+  const char* text = "abc ab  abcabc 12";
+  int64_t ends[32];
+  const int64_t np = ft_tok_split(0, (const uint8_t*)text, (int64_t)std::strlen(text), ends, 32);
+  CHECK(np == 5 && ends[0] == 3 && ends[1] == 6 && ends[2] == 7 && ends[3] == 14 && ends[4] == 17);   // "abc" " ab" " " " abcabc" " 12"
+  std::string big;
+  for (int i = 0; i < 4000; i++) big += (i % 7 == 0) ? std::string(40, 'a') + "b " : "abc ab\n";
+  std::vector<std::string> texts(9, big);
+  texts.push_back(text);
+  std::string blob;
+  std::vector<int64_t> off{0};
+  for (auto& t : texts) { blob += t; off.push_back((int64_t)blob.size()); }
+  std::vector<int32_t> a(blob.size()), b(blob.size());
+  std::vector<int64_t> ao(texts.size() + 1), bo(texts.size() + 1);
+  const int64_t na = ft_bpe_encode_texts(h, 0, (const uint8_t*)blob.data(), off.data(), (int64_t)texts.size(), a.data(), (int64_t)a.size(), ao.data(), 1);
+  const int64_t nb = ft_bpe_encode_texts(h, 0, (const uint8_t*)blob.data(), off.data(), (int64_t)texts.size(), b.data(), (int64_t)b.size(), bo.data(), 4);
+  CHECK(na > 0 && na == nb && ao == bo && std::equal(a.begin(), a.begin() + na, b.begin()));
+  const int64_t last = ao[texts.size() - 1];
+  // "abc" | " ab" -> ' ' 256 ... : " a" (rank 2) loses to "ab" (rank 0)
+  CHECK(a[(size_t)last] == 257 && a[(size_t)last + 1] == ' ' && a[(size_t)last + 2] == 256);
+  const int64_t moff[2] = {0, 2};
+  CHECK(ft_bpe_encode_texts(h, 0, (const uint8_t*)"\xff\xfe", moff, 1, a.data(), 2, nullptr, 1) == -2);   // malformed UTF-8 is refused
+  const int64_t poff[3] = {0, 3, 43};
+  const std::string pieces = "abc" + std::string(39, 'a') + "b";
+  CHECK(ft_bpe_encode(h, (const uint8_t*)pieces.data(), poff, 2, a.data(), (int64_t)a.size(), ao.data(), 2) == 1 + 39 && ao[1] == 1);
+  ft_bpe_destroy(h);
+}
+
 int main() {
   test_loader_and_planner();
+  test_tokenizer();
   test_simulated();
   test_tcp(0);
   test_tcp(1);

@@ -2,15 +2,21 @@
 pre-tokenisation by the GPT-2 / Llama-3 split pattern) plus chat templates.
 
 Reference parity: ferrotorch-tokenize/src/lib.rs:59 (load_tokenizer), :85 (encode), :104 (encode_batch), :131 (decode),
-:225 (apply_chat_template) - a wrapper over the HF ``tokenizers`` crate there; here the BPE merge loop is implemented directly.
+:225 (apply_chat_template) - a wrapper over the HF ``tokenizers`` crate there; here the BPE merge loop is implemented directly: in
+the host runtime library (``csrc/runtime/tokenizer.cpp``: heap-ordered merges, the pieces of a call spread over threads) with the
+direct Python loop as the fallback for vocabularies the native engine cannot take (a merge whose halves are not vocabulary entries)
+and for texts that need the unknown-token rule. ``FT_TOKENIZE_NATIVE=0`` keeps everything on the Python loop.
 """
 from __future__ import annotations
 
+import ctypes
 import json
+import os
 from functools import lru_cache
 from pathlib import Path
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import regex as _re
 
 from dataclasses import dataclass
@@ -19,6 +25,50 @@ from ..errors import Internal, InvalidArgument
 
 _GPT2_SPLIT = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
 _LLAMA3_SPLIT = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"""
+
+
+_classes_installed = False
+
+
+def _install_classes(rt) -> None:
+    """Gives the runtime library the class of every code point (letter, number, white space) as the regular-expression engine used by
+    the Python route sees it, so the native splitter and ``regex`` cut at the same places. Once per process (about 0.2 s)."""
+    global _classes_installed
+    if _classes_installed:
+        return
+    table = np.zeros(0x110000, np.uint8)
+    allc = "".join(map(chr, range(0xD800))) + "".join(map(chr, range(0xE000, 0x110000)))
+
+    def cp(i):                                          # index in ``allc`` -> code point (the surrogate block is left out of the string)
+        return i if i < 0xD800 else i + 0x800
+    for bit, pat in ((1, r"\p{L}+"), (2, r"\p{N}+"), (4, r"\s+")):
+        for m in _re.finditer(pat, allc):
+            table[cp(m.start()): cp(m.end() - 1) + 1] |= bit
+    rt.ft_tok_set_classes.restype = None
+    rt.ft_tok_set_classes(table.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(table.size))
+    _classes_installed = True
+
+
+def pre_tokenize(text: str, pattern: str = "gpt2") -> List[str]:
+    """The pieces the pre-tokeniser cuts ``text`` into, by the native matcher of the ``"gpt2"`` or ``"llama3"`` split pattern (the same
+    cuts as ``regex.findall`` with that pattern)."""
+    kind = {"gpt2": 0, "llama3": 1}.get(pattern)
+    if kind is None:
+        raise InvalidArgument(f"pattern must be 'gpt2' or 'llama3', got {pattern!r}")
+    from .. import _lib
+    rt = _lib.runtime()
+    _install_classes(rt)
+    rt.ft_tok_split.restype = ctypes.c_int64
+    raw = text.encode("utf-8")
+    ends = np.empty(max(len(raw), 1), np.int64)
+    n = rt.ft_tok_split(ctypes.c_int(kind), ctypes.c_char_p(raw), ctypes.c_int64(len(raw)), ends.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(ends.size))
+    if n < 0:
+        raise Internal(f"native splitter failed with code {n}")
+    out, a = [], 0
+    for b in ends[:n].tolist():
+        out.append(raw[a:b].decode("utf-8"))
+        a = b
+    return out
 
 
 @lru_cache(maxsize=1)
@@ -37,8 +87,10 @@ def _bytes_to_unicode() -> Dict[int, str]:
 class Tokenizer:
     def __init__(self, vocab: Dict[str, int], merges: Sequence[Tuple[str, str]], added_tokens: Optional[Dict[str, int]] = None,
                  byte_level: bool = True, split_pattern: Optional[str] = None, bos_token: Optional[str] = None, eos_token: Optional[str] = None,
-                 unk_token: Optional[str] = None):
+                 unk_token: Optional[str] = None, ignore_merges: bool = False):
         self.vocab = dict(vocab)
+        self.model_vocab = dict(vocab)                 # without the added tokens: what ``ignore_merges`` looks whole pieces up in
+        self.ignore_merges = bool(ignore_merges)
         self.added = dict(added_tokens or {})
         self.vocab.update(self.added)
         self.inv = {i: t for t, i in self.vocab.items()}
@@ -50,6 +102,111 @@ class Tokenizer:
         self._u2b = {v: k for k, v in self._b2u.items()}
         self._special_re = _re.compile("|".join(_re.escape(t) for t in sorted(self.added, key=len, reverse=True))) if self.added else None
         self._cache: Dict[str, List[str]] = {}
+        self._native = None
+        pat = split_pattern or _GPT2_SPLIT
+        self._kind = 0 if pat == _GPT2_SPLIT else 1 if pat == _LLAMA3_SPLIT else None      # patterns the native splitter restates
+        if os.environ.get("FT_TOKENIZE_NATIVE", "1") != "0":
+            self._build_native()
+
+    # ------------------------------------------------------------------ native merge engine
+    def _build_native(self) -> None:
+        """Hands the merge table to the runtime library as id triples. Left alone (Python loop) when the library is missing or a merge
+        names a string that is not a vocabulary entry."""
+        try:
+            from .. import _lib
+            rt = _lib.runtime()
+            rt.ft_bpe_create.restype = ctypes.c_void_p
+            rt.ft_bpe_encode.restype = ctypes.c_int64
+            rt.ft_bpe_destroy.restype = None
+        except Exception:
+            return
+        v = self.model_vocab
+        pairs = sorted(self.ranks.items(), key=lambda kv: kv[1])
+        left, right, merged = np.empty(len(pairs), np.int32), np.empty(len(pairs), np.int32), np.empty(len(pairs), np.int32)
+        for r, ((a, b), _) in enumerate(pairs):
+            ia, ib, iab = v.get(a), v.get(b), v.get(a + b)
+            if ia is None or ib is None or iab is None:
+                return
+            left[r], right[r], merged[r] = ia, ib, iab
+        null = ctypes.c_void_p(None)
+        if self.byte_level:
+            byte_sym = np.array([v.get(self._b2u[b], -1) for b in range(256)], np.int32)
+            chars = (null, null, 0)
+        else:
+            single = [(ord(t), i) for t, i in v.items() if len(t) == 1]
+            cp, cid = np.array([c for c, _ in single], np.uint32), np.array([i for _, i in single], np.int32)
+            byte_sym = None
+            chars = (cp.ctypes.data_as(ctypes.c_void_p), cid.ctypes.data_as(ctypes.c_void_p), len(single))
+        whole = (null, null, null, 0)
+        if self.ignore_merges:
+            raw, ids = [], []
+            for t, i in v.items():
+                if self.byte_level:
+                    try:
+                        raw.append(bytes(self._u2b[ch] for ch in t))
+                    except KeyError:
+                        continue
+                else:
+                    raw.append(t.encode("utf-8"))
+                ids.append(i)
+            blob = np.frombuffer(b"".join(raw) or b"\0", np.uint8)
+            woff = np.zeros(len(raw) + 1, np.int64)
+            np.cumsum([len(x) for x in raw], out=woff[1:])
+            wid = np.array(ids, np.int32)
+            whole = (blob.ctypes.data_as(ctypes.c_void_p), woff.ctypes.data_as(ctypes.c_void_p), wid.ctypes.data_as(ctypes.c_void_p), len(raw))
+        h = rt.ft_bpe_create(left.ctypes.data_as(ctypes.c_void_p), right.ctypes.data_as(ctypes.c_void_p), merged.ctypes.data_as(ctypes.c_void_p),
+                             ctypes.c_int64(len(pairs)), byte_sym.ctypes.data_as(ctypes.c_void_p) if byte_sym is not None else null,
+                             chars[0], chars[1], ctypes.c_int64(chars[2]), whole[0], whole[1], whole[2], ctypes.c_int64(whole[3]))
+        if h:
+            self._native, self._rt = ctypes.c_void_p(h), rt
+            if self._kind is not None:
+                rt.ft_bpe_encode_texts.restype = ctypes.c_int64
+                _install_classes(rt)
+
+    def __del__(self):
+        h, self._native = getattr(self, "_native", None), None
+        if h is not None:
+            try:
+                self._rt.ft_bpe_destroy(h)
+            except Exception:
+                pass
+
+    def _native_pieces(self, pieces: Sequence[str], threads: int = 1):
+        """ids (int32 array) and the running id count after each piece for ``pieces``; None when a piece needs the Python path."""
+        raw = [p.encode("utf-8") for p in pieces]
+        off = np.zeros(len(raw) + 1, np.int64)
+        if raw:
+            np.cumsum([len(x) for x in raw], out=off[1:])
+        blob = b"".join(raw)
+        out = np.empty(max(int(off[-1]), 1), np.int32)
+        out_off = np.empty(len(raw) + 1, np.int64)
+        n = self._rt.ft_bpe_encode(self._native, ctypes.c_char_p(blob), off.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(len(raw)),
+                                   out.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(out.size), out_off.ctypes.data_as(ctypes.c_void_p),
+                                   ctypes.c_int(threads))
+        if n < 0:
+            return None
+        return out[:n], out_off
+
+    def _native_texts(self, texts: Sequence[str], threads: int = 1):
+        """Splits and encodes ``texts`` in the runtime library: ids and the running id count after each text; None when the split
+        pattern is not one of the two restated ones or a text needs the Python path."""
+        if self._native is None or self._kind is None:
+            return None
+        try:
+            raw = [t.encode("utf-8") for t in texts]
+        except UnicodeEncodeError:                     # lone surrogates
+            return None
+        off = np.zeros(len(raw) + 1, np.int64)
+        if raw:
+            np.cumsum([len(x) for x in raw], out=off[1:])
+        out = np.empty(max(int(off[-1]), 1), np.int32)
+        out_off = np.empty(len(raw) + 1, np.int64)
+        n = self._rt.ft_bpe_encode_texts(self._native, ctypes.c_int(self._kind), ctypes.c_char_p(b"".join(raw)), off.ctypes.data_as(ctypes.c_void_p),
+                                         ctypes.c_int64(len(raw)), out.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(out.size),
+                                         out_off.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(threads))
+        if n < 0:
+            return None
+        return out[:n], out_off
 
     def vocab_size(self) -> int:
         return len(self.vocab)
@@ -63,6 +220,9 @@ class Tokenizer:
     def _bpe(self, word: str) -> List[str]:
         if word in self._cache:
             return self._cache[word]
+        if self.ignore_merges and word in self.model_vocab:
+            self._cache[word] = [word]
+            return [word]
         parts = list(word)
         while len(parts) > 1:
             best, bi = None, -1
@@ -77,6 +237,16 @@ class Tokenizer:
         return parts
 
     def _encode_plain(self, text: str) -> List[int]:
+        got = self._native_texts([text])
+        if got is not None:
+            return got[0].tolist()
+        if self._native is not None:
+            got = self._native_pieces(self.split.findall(text))
+            if got is not None:
+                return got[0].tolist()
+        return self._encode_plain_py(text)
+
+    def _encode_plain_py(self, text: str) -> List[int]:
         ids: List[int] = []
         for piece in self.split.findall(text):
             w = "".join(self._b2u[b] for b in piece.encode("utf-8")) if self.byte_level else piece
@@ -106,8 +276,83 @@ class Tokenizer:
                 ids += self._encode_plain(text[pos:])
         return ids
 
+    def _segments(self, text: str):
+        """(plain text | None, special id | None) runs of ``text`` in order."""
+        if self._special_re is None:
+            if text:
+                yield text, None
+            return
+        pos = 0
+        for m in self._special_re.finditer(text):
+            if m.start() > pos:
+                yield text[pos: m.start()], None
+            yield None, self.added[m.group(0)]
+            pos = m.end()
+        if pos < len(text):
+            yield text[pos:], None
+
     def encode_batch(self, texts: Iterable[str], add_special_tokens: bool = False) -> List[List[int]]:
-        return [self.encode(t, add_special_tokens) for t in texts]
+        """All texts in one call of the native engine (their pieces spread over the host's cores); a batch that holds a piece the engine
+        cannot take goes text by text."""
+        texts = list(texts)
+        if self._native is None or not texts:
+            return [self.encode(t, add_special_tokens) for t in texts]
+        threads = min(os.cpu_count() or 1, 16)
+        bos = [self.vocab[self.bos_token]] if add_special_tokens and self.bos_token else []
+        if self._kind is not None:                     # splitting and merging both in the library: one run of plain text = one unit of work
+            runs: List[str] = []
+            plan = []
+            for t in texts:
+                items = []
+                for plain, special in self._segments(t):
+                    if plain is None:
+                        items.append(special)
+                    else:
+                        items.append((len(runs),))
+                        runs.append(plain)
+                plan.append(items)
+            got = self._native_texts(runs, threads)
+            if got is not None:
+                ids, off = got
+                out = []
+                for items in plan:
+                    if len(items) == 1 and isinstance(items[0], tuple) and not bos:
+                        out.append(ids[off[items[0][0]]: off[items[0][0] + 1]].tolist())
+                        continue
+                    row = list(bos)
+                    for it in items:
+                        if isinstance(it, tuple):
+                            row += ids[off[it[0]]: off[it[0] + 1]].tolist()
+                        else:
+                            row.append(it)
+                    out.append(row)
+                return out
+        pieces: List[str] = []
+        plan = []                                      # per text: list of (first piece, end piece) ranges or special ids
+        for t in texts:
+            items = []
+            for plain, special in self._segments(t):
+                if plain is None:
+                    items.append(special)
+                else:
+                    ps = self.split.findall(plain)
+                    items.append((len(pieces), len(pieces) + len(ps)))
+                    pieces += ps
+            plan.append(items)
+        got = self._native_pieces(pieces, threads=threads)
+        if got is None:
+            return [self.encode(t, add_special_tokens) for t in texts]
+        ids, off = got
+        out = []
+        for items in plan:
+            row = list(bos)
+            for it in items:
+                if isinstance(it, tuple):
+                    row += ids[off[it[0]]: off[it[1]]].tolist()
+                else:
+                    row.append(it)
+            out.append(row)
+        return out
 
     def decode(self, ids: Iterable[int], skip_special_tokens: bool = True) -> str:
         out, buf = [], bytearray()
@@ -159,7 +404,8 @@ def load_tokenizer(path) -> Tokenizer:
         def tok(v):
             return v.get("content") if isinstance(v, dict) else v
         bos, eos = tok(c.get("bos_token")), tok(c.get("eos_token"))
-    return Tokenizer(model.get("vocab", {}), merges, added, byte_level, pattern, bos, eos, model.get("unk_token"))
+    return Tokenizer(model.get("vocab", {}), merges, added, byte_level, pattern, bos, eos, model.get("unk_token"),
+                     ignore_merges=bool(model.get("ignore_merges", False)))
 
 
 def encode(tok: Tokenizer, text: str, add_special_tokens: bool = False) -> List[int]:
