@@ -46,6 +46,11 @@ void* ft_bpe_create(const int32_t* left, const int32_t* right, const int32_t* me
                     const int32_t* char_id, int64_t n_chars, const uint8_t* whole_bytes, const int64_t* whole_off, const int32_t* whole_id, int64_t n_whole);
 void ft_bpe_destroy(void* h);
 int64_t ft_bpe_encode(void* h, const uint8_t* bytes, const int64_t* off, int64_t n_pieces, int32_t* out, int64_t out_cap, int64_t* out_off, int nthreads);
+void* ft_json_grammar_create(const int32_t* kind, const int32_t* edge_first, int64_t n_nodes, const uint8_t* lits, const int64_t* lit_off,
+                             const int32_t* edge_child, const uint8_t* edge_required, const uint8_t* vocab, const int64_t* voff, int64_t n_vocab);
+void ft_json_grammar_destroy(void* h);
+int ft_json_grammar_check(void* h, const uint8_t* text, int64_t n, int* is_complete);
+int64_t ft_json_grammar_mask(void* h, const uint8_t* text, int64_t n, int64_t eos_id, uint8_t* allowed, int nthreads);
 int64_t ft_bpe_encode_texts(void* h, int kind, const uint8_t* bytes, const int64_t* off, int64_t n_texts, int32_t* out, int64_t out_cap, int64_t* out_off,
                             int nthreads);
 }
@@ -233,9 +238,36 @@ static void test_tokenizer() {
   ft_bpe_destroy(h);
 }
 
+// Schema {"a": integer (required)} over a vocabulary large enough for the threaded walk; the masks of one and of several threads must agree.
+static void test_grammar() {
+  const int32_t kind[2] = {0, 4}, edge_first[3] = {0, 1, 1}, child[1] = {1};
+  const uint8_t req[1] = {1};
+  const std::string lits = "\"a\"";
+  const int64_t lit_off[2] = {0, 3};
+  std::vector<std::string> vocab = {"{", "}", "\"a\"", ":", "1", "12}", "x", "", "<eos>"};
+  for (int i = 0; i < 9000; i++) vocab.push_back((i % 3 == 0 ? "1" : "q") + std::to_string(i));
+  std::string blob;
+  std::vector<int64_t> voff{0};
+  for (auto& v : vocab) { blob += v; voff.push_back((int64_t)blob.size()); }
+  void* h = ft_json_grammar_create(kind, edge_first, 2, (const uint8_t*)lits.data(), lit_off, child, req, (const uint8_t*)blob.data(), voff.data(), (int64_t)vocab.size());
+  CHECK(h != nullptr);
+  int done = -1;
+  CHECK(ft_json_grammar_check(h, (const uint8_t*)"{\"a\":1", 6, &done) == 1 && done == 0);
+  CHECK(ft_json_grammar_check(h, (const uint8_t*)"{\"a\":1}", 7, &done) == 1 && done == 1);
+  CHECK(ft_json_grammar_check(h, (const uint8_t*)"{\"b", 3, &done) == 0);
+  std::vector<uint8_t> m1(vocab.size()), m4(vocab.size());
+  const int64_t c1 = ft_json_grammar_mask(h, (const uint8_t*)"{\"a\":", 5, 8, m1.data(), 1);
+  const int64_t c4 = ft_json_grammar_mask(h, (const uint8_t*)"{\"a\":", 5, 8, m4.data(), 4);
+  CHECK(c1 == c4 && m1 == m4 && c1 == 2 + 3000);          // "1", "12}" and every "1<digits>" entry
+  CHECK(m1[4] == 1 && m1[5] == 1 && m1[6] == 0 && m1[7] == 0 && m1[8] == 0);
+  CHECK(ft_json_grammar_mask(h, (const uint8_t*)"{\"a\":1}", 7, 8, m1.data(), 4) == 1 && m1[8] == 1);
+  ft_json_grammar_destroy(h);
+}
+
 int main() {
   test_loader_and_planner();
   test_tokenizer();
+  test_grammar();
   test_simulated();
   test_tcp(0);
   test_tcp(1);

@@ -7,14 +7,20 @@ JsonSchemaProcessor), gpu_dispatch.rs:778 (compute_mask_gpu)}; the mask kernel r
 """
 from __future__ import annotations
 
+import ctypes
 import enum
 import json
+import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..errors import FerrotorchError, InvalidArgument
+
+
+_DIGITS = "0123456789"                          # JSON numbers take ASCII digits only (``str.isdigit`` also accepts other scripts)
 
 
 @dataclass
@@ -63,6 +69,8 @@ class JsonGrammar:
         r = self._value(s, t, i)
         if r is None:
             return None
+        if isinstance(r, tuple):                       # a number that ends with the text: complete, and a valid prefix of a longer one
+            return r[1] if r[1] == len(t) else None
         if r == -1:
             return len(t) if partial else None
         if r != len(t):
@@ -105,12 +113,12 @@ class JsonGrammar:
             j += 1
             if j >= len(t):
                 return -1
-        if not t[j].isdigit():
+        if not t[j] in _DIGITS:
             return None
         if t[j] == "0":
             j += 1
         else:
-            while j < len(t) and t[j].isdigit():
+            while j < len(t) and t[j] in _DIGITS:
                 j += 1
         if j >= len(t):
             return ("open", j)
@@ -118,9 +126,9 @@ class JsonGrammar:
             j += 1
             if j >= len(t):
                 return -1
-            if not t[j].isdigit():
+            if not t[j] in _DIGITS:
                 return None
-            while j < len(t) and t[j].isdigit():
+            while j < len(t) and t[j] in _DIGITS:
                 j += 1
             if j >= len(t):
                 return ("open", j)
@@ -130,9 +138,9 @@ class JsonGrammar:
                 j += 1
             if j >= len(t):
                 return -1
-            if not t[j].isdigit():
+            if not t[j] in _DIGITS:
                 return None
-            while j < len(t) and t[j].isdigit():
+            while j < len(t) and t[j] in _DIGITS:
                 j += 1
             if j >= len(t):
                 return ("open", j)
@@ -334,14 +342,94 @@ class TokenMask:
         return int(self.allowed.sum())
 
 
+_KIND_CODE = {"object": 0, "array": 1, "string": 2, "number": 3, "integer": 4, "boolean": 5, "null": 6, "enum": 7, "any": 8}
+
+
+def _flatten_schema(root: Schema):
+    """Schema tree -> the arrays ``ft_json_grammar_create`` takes (node kinds, edge ranges, edge literals / children / required flags)."""
+    nodes: List[Schema] = []
+    index: Dict[int, int] = {}
+
+    def visit(s: Schema) -> int:
+        if s.kind not in _KIND_CODE:
+            raise InvalidArgument(f"unsupported schema kind {s.kind}")
+        index[id(s)] = len(nodes)
+        nodes.append(s)
+        for sub in list(s.properties.values()) + ([s.items] if s.items is not None else []):
+            visit(sub)
+        return index[id(s)]
+    visit(root)
+    kinds, first, lits, child, req = [], [0], [], [], []
+    for s in nodes:
+        kinds.append(_KIND_CODE[s.kind])
+        if s.kind == "object":
+            for name, sub in s.properties.items():
+                lits.append(json.dumps(name).encode("utf-8"))
+                child.append(index[id(sub)])
+                req.append(1 if name in s.required else 0)
+        elif s.kind == "array" and s.items is not None:
+            lits.append(b"")
+            child.append(index[id(s.items)])
+            req.append(0)
+        elif s.kind == "enum":
+            for v in s.enum or []:
+                lits.append(json.dumps(v).encode("utf-8"))
+                child.append(-1)
+                req.append(0)
+        first.append(len(lits))
+    return kinds, first, lits, child, req
+
+
+def _blob(items: Sequence[bytes]):
+    off = np.zeros(len(items) + 1, np.int64)
+    if items:
+        np.cumsum([len(x) for x in items], out=off[1:])
+    return np.frombuffer(b"".join(items) + b"\0", np.uint8), off
+
+
 class JsonSchemaProcessor:
-    """Logits processor: keeps only tokens whose text leaves the generated string a valid prefix of a schema-conforming document."""
+    """Logits processor: keeps only tokens whose text leaves the generated string a valid prefix of a schema-conforming document.
+
+    The per-step walk over the vocabulary runs in the host runtime library (``csrc/runtime/grammar.cpp``: the same prefix matcher as
+    ``JsonGrammar``, the vocabulary spread over threads); ``FT_GRAMMAR_NATIVE=0`` or a missing library keeps it on the Python matcher."""
 
     def __init__(self, schema, vocab_texts: Sequence[str], eos_id: Optional[int] = None):
         self.grammar = JsonGrammar(schema if isinstance(schema, Schema) else Schema.from_json(schema))
         self.vocab = list(vocab_texts)
         self.eos_id = eos_id
         self.text = ""
+        self._native = None
+        if os.environ.get("FT_GRAMMAR_NATIVE", "1") != "0":
+            self._build_native()
+
+    def _build_native(self) -> None:
+        try:
+            from .. import _lib
+            rt = _lib.runtime()
+            rt.ft_json_grammar_create.restype = ctypes.c_void_p
+            rt.ft_json_grammar_mask.restype = ctypes.c_int64
+            rt.ft_json_grammar_destroy.restype = None
+            kinds, first, lits, child, req = _flatten_schema(self.grammar.schema)
+            vocab = [t.encode("utf-8") for t in self.vocab]
+        except Exception:
+            return
+        p = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+        lit_blob, lit_off = _blob(lits)
+        vocab_blob, voff = _blob(vocab)
+        kind_a, first_a = np.array(kinds, np.int32), np.array(first, np.int32)
+        child_a, req_a = np.array(child + [0], np.int32), np.array(req + [0], np.uint8)
+        h = rt.ft_json_grammar_create(p(kind_a), p(first_a), ctypes.c_int64(len(kinds)), p(lit_blob), p(lit_off), p(child_a), p(req_a), p(vocab_blob), p(voff),
+                                      ctypes.c_int64(len(vocab)))
+        if h:
+            self._native, self._rt = ctypes.c_void_p(h), rt
+
+    def __del__(self):
+        h, self._native = getattr(self, "_native", None), None
+        if h is not None:
+            try:
+                self._rt.ft_json_grammar_destroy(h)
+            except Exception:
+                pass
 
     def reset(self) -> None:
         self.text = ""
@@ -367,6 +455,15 @@ class JsonSchemaProcessor:
         return r is not None and r != -1 and r == len(self.text)
 
     def mask(self) -> TokenMask:
+        if self._native is not None:
+            allowed = np.empty(max(len(self.vocab), 1), np.uint8)
+            raw = self.text.encode("utf-8")
+            self._rt.ft_json_grammar_mask(self._native, ctypes.c_char_p(raw), ctypes.c_int64(len(raw)), ctypes.c_int64(-1 if self.eos_id is None else self.eos_id),
+                                          allowed.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(min(os.cpu_count() or 1, 16)))
+            return TokenMask(torch.from_numpy(allowed[: len(self.vocab)]).to(torch.bool))
+        return self._mask_py()
+
+    def _mask_py(self) -> TokenMask:
         ok = torch.zeros(len(self.vocab), dtype=torch.bool)
         done = self._complete()
         for i, tok in enumerate(self.vocab):
