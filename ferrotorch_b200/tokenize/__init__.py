@@ -22,6 +22,7 @@ import regex as _re
 from dataclasses import dataclass
 
 from ..errors import Internal, InvalidArgument
+from . import pipeline as _pl
 
 _GPT2_SPLIT = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
 _LLAMA3_SPLIT = r"""(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+|\s+(?!\S)|\s+"""
@@ -87,7 +88,17 @@ def _bytes_to_unicode() -> Dict[int, str]:
 class Tokenizer:
     def __init__(self, vocab: Dict[str, int], merges: Sequence[Tuple[str, str]], added_tokens: Optional[Dict[str, int]] = None,
                  byte_level: bool = True, split_pattern: Optional[str] = None, bos_token: Optional[str] = None, eos_token: Optional[str] = None,
-                 unk_token: Optional[str] = None, ignore_merges: bool = False):
+                 unk_token: Optional[str] = None, ignore_merges: bool = False, model_type: str = "BPE", normalizer=None, pre_tokenizer=None,
+                 post_processor=None, decoder=None, continuing_subword_prefix: str = "", end_of_word_suffix: str = "", byte_fallback: bool = False,
+                 max_input_chars_per_word: int = 100, special_tokens: Optional[Iterable[str]] = None):
+        """``vocab`` / ``merges`` / ``added_tokens`` with the GPT-2 split (or ``split_pattern``) is the short form; ``load_tokenizer`` passes
+        the stages of a ``tokenizer.json`` (``normalizer``: str -> str; ``pre_tokenizer``: ``pipeline.PreTokenizer``; ``post_processor``: ids ->
+        ids with the special tokens of one sequence; ``decoder``: token strings -> strings) and the model's type and affixes."""
+        if model_type not in ("BPE", "WordPiece"):
+            raise InvalidArgument(f"unsupported tokenizer model {model_type}")
+        self.model_type = model_type
+        self.normalizer, self.pre_tokenizer, self.post_processor, self.decoder_chain = normalizer, pre_tokenizer, post_processor, decoder
+        self.prefix, self.suffix, self.byte_fallback, self.max_chars = continuing_subword_prefix or "", end_of_word_suffix or "", byte_fallback, max_input_chars_per_word
         self.vocab = dict(vocab)
         self.model_vocab = dict(vocab)                 # without the added tokens: what ``ignore_merges`` looks whole pieces up in
         self.ignore_merges = bool(ignore_merges)
@@ -95,7 +106,10 @@ class Tokenizer:
         self.vocab.update(self.added)
         self.inv = {i: t for t, i in self.vocab.items()}
         self.ranks = {tuple(m): i for i, m in enumerate(merges)}
-        self.byte_level = byte_level
+        self.byte_level = pre_tokenizer.byte_level if pre_tokenizer is not None else byte_level
+        self.special = set(self.added) if special_tokens is None else set(special_tokens)        # what ``skip_special_tokens`` drops
+        if pre_tokenizer is not None and pre_tokenizer.regex_source is not None:
+            split_pattern = pre_tokenizer.regex_source
         self.split = _re.compile(split_pattern or _GPT2_SPLIT)
         self.bos_token, self.eos_token, self.unk_token = bos_token, eos_token, unk_token
         self._b2u = _bytes_to_unicode()
@@ -105,7 +119,9 @@ class Tokenizer:
         self._native = None
         pat = split_pattern or _GPT2_SPLIT
         self._kind = 0 if pat == _GPT2_SPLIT else 1 if pat == _LLAMA3_SPLIT else None      # patterns the native splitter restates
-        if os.environ.get("FT_TOKENIZE_NATIVE", "1") != "0":
+        if normalizer is not None or (pre_tokenizer is not None and pre_tokenizer.regex_source is None):
+            self._kind = None                          # other stages run in Python; the merges may still be native
+        if os.environ.get("FT_TOKENIZE_NATIVE", "1") != "0" and model_type == "BPE" and not self.prefix and not self.suffix and not byte_fallback:
             self._build_native()
 
     # ------------------------------------------------------------------ native merge engine
@@ -224,6 +240,10 @@ class Tokenizer:
             self._cache[word] = [word]
             return [word]
         parts = list(word)
+        if self.prefix:
+            parts = parts[:1] + [self.prefix + c for c in parts[1:]]
+        if self.suffix and parts:
+            parts[-1] += self.suffix
         while len(parts) > 1:
             best, bi = None, -1
             for i in range(len(parts) - 1):
@@ -237,29 +257,69 @@ class Tokenizer:
         return parts
 
     def _encode_plain(self, text: str) -> List[int]:
+        if self.normalizer is not None:
+            text = self.normalizer(text)
         got = self._native_texts([text])
         if got is not None:
             return got[0].tolist()
         if self._native is not None:
-            got = self._native_pieces(self.split.findall(text))
+            raw = self.pre_tokenizer.pieces(text, mapped=False) if self.pre_tokenizer is not None else self.split.findall(text)
+            got = self._native_pieces(raw)
             if got is not None:
                 return got[0].tolist()
         return self._encode_plain_py(text)
 
+    def _lookup(self, tok: str, ids: List[int]) -> None:
+        i = self.vocab.get(tok)
+        if i is None and self.byte_fallback:
+            fb = [self.vocab.get(f"<0x{b:02X}>") for b in tok.encode("utf-8")]
+            if all(x is not None for x in fb):
+                ids += fb
+                return
+        if i is None:
+            if self.unk_token is None:
+                raise InvalidArgument(f"token {tok!r} not in vocabulary and no unk token configured")
+            i = self.vocab[self.unk_token]
+        ids.append(i)
+
+    def _wordpiece(self, word: str) -> List[str]:
+        """Greedy longest match from the left; pieces after the first carry the continuing prefix; a word with a part that matches nothing
+        is the unknown token as a whole."""
+        unk = [self.unk_token or "[UNK]"]
+        if len(word) > self.max_chars:
+            return unk
+        out, start = [], 0
+        while start < len(word):
+            end, cur = len(word), None
+            while start < end:
+                sub = word[start:end] if start == 0 else self.prefix + word[start:end]
+                if sub in self.model_vocab:
+                    cur = sub
+                    break
+                end -= 1
+            if cur is None:
+                return unk
+            out.append(cur)
+            start = end
+        return out
+
     def _encode_plain_py(self, text: str) -> List[int]:
+        """``text`` is already normalised."""
         ids: List[int] = []
-        for piece in self.split.findall(text):
-            w = "".join(self._b2u[b] for b in piece.encode("utf-8")) if self.byte_level else piece
-            for tok in self._bpe(w):
-                i = self.vocab.get(tok)
-                if i is None:
-                    if self.unk_token is None:
-                        raise InvalidArgument(f"token {tok!r} not in vocabulary and no unk token configured")
-                    i = self.vocab[self.unk_token]
-                ids.append(i)
+        if self.pre_tokenizer is not None:
+            pieces = self.pre_tokenizer.pieces(text)
+        else:
+            pieces = ["".join(self._b2u[b] for b in p.encode("utf-8")) if self.byte_level else p for p in self.split.findall(text)]
+        for w in pieces:
+            for tok in (self._wordpiece(w) if self.model_type == "WordPiece" else self._bpe(w)):
+                self._lookup(tok, ids)
         return ids
 
     def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
+        """Ids of ``text``. ``add_special_tokens``: wrap them the way the file's post-processor does for one sequence (without one: the
+        beginning-of-sequence token in front, if the tokenizer names one)."""
+        if add_special_tokens and self.post_processor is not None:
+            return self.post_processor(self.encode(text, False))
         ids: List[int] = []
         if add_special_tokens and self.bos_token:
             ids.append(self.vocab[self.bos_token])
@@ -295,7 +355,8 @@ class Tokenizer:
         """All texts in one call of the native engine (their pieces spread over the host's cores); a batch that holds a piece the engine
         cannot take goes text by text."""
         texts = list(texts)
-        if self._native is None or not texts:
+        if self._native is None or not texts or self.normalizer is not None or self.post_processor is not None \
+                or (self.pre_tokenizer is not None and self._kind is None):
             return [self.encode(t, add_special_tokens) for t in texts]
         threads = min(os.cpu_count() or 1, 16)
         bos = [self.vocab[self.bos_token]] if add_special_tokens and self.bos_token else []
@@ -355,6 +416,11 @@ class Tokenizer:
         return out
 
     def decode(self, ids: Iterable[int], skip_special_tokens: bool = True) -> str:
+        if self.decoder_chain is not None:
+            toks = [self.inv[int(i)] for i in ids if int(i) in self.inv]
+            if skip_special_tokens:
+                toks = [t for t in toks if t not in self.special]
+            return "".join(self.decoder_chain(toks))
         out, buf = [], bytearray()
 
         def flush():
@@ -386,17 +452,17 @@ def load_tokenizer(path) -> Tokenizer:
         p = p / "tokenizer.json"
     j = json.loads(p.read_text())
     model = j.get("model", {})
-    if model.get("type", "BPE") != "BPE":
-        raise InvalidArgument(f"unsupported tokenizer model {model.get('type')}")
+    mtype = model.get("type") or ("WordPiece" if "merges" not in model else "BPE")
+    if mtype not in ("BPE", "WordPiece"):
+        raise InvalidArgument(f"unsupported tokenizer model {mtype}")
     merges = [tuple(m.split(" ", 1)) if isinstance(m, str) else tuple(m) for m in model.get("merges", [])]
     added = {a["content"]: a["id"] for a in j.get("added_tokens", [])}
-    pre = j.get("pre_tokenizer") or {}
-    kinds = [pre.get("type")] + [x.get("type") for x in pre.get("pretokenizers", [])]
-    byte_level = "ByteLevel" in kinds or (j.get("decoder") or {}).get("type") == "ByteLevel"
-    pattern = None
-    for x in [pre] + pre.get("pretokenizers", []):
-        if x.get("type") == "Split" and isinstance(x.get("pattern"), dict):
-            pattern = x["pattern"].get("Regex")
+    special = [a["content"] for a in j.get("added_tokens", []) if a.get("special", False)]
+    b2u = _bytes_to_unicode()
+    pre = _pl.PreTokenizer(j.get("pre_tokenizer"), b2u) if j.get("pre_tokenizer") else None
+    vocab = model.get("vocab", {})
+    full = dict(vocab)
+    full.update(added)
     bos = eos = None
     cfg = p.parent / "tokenizer_config.json"
     if cfg.exists():
@@ -404,8 +470,17 @@ def load_tokenizer(path) -> Tokenizer:
         def tok(v):
             return v.get("content") if isinstance(v, dict) else v
         bos, eos = tok(c.get("bos_token")), tok(c.get("eos_token"))
-    return Tokenizer(model.get("vocab", {}), merges, added, byte_level, pattern, bos, eos, model.get("unk_token"),
-                     ignore_merges=bool(model.get("ignore_merges", False)))
+    byte_level = (pre is not None and pre.byte_level) or (j.get("decoder") or {}).get("type") == "ByteLevel"
+    if pre is None and mtype == "BPE" and byte_level:                       # a byte-level decoder without a pre-tokenizer entry: the GPT-2 form
+        pre = _pl.PreTokenizer({"type": "ByteLevel", "add_prefix_space": False, "use_regex": True}, b2u)
+    if pre is None:
+        pre = _pl.PreTokenizer({"type": "Sequence", "pretokenizers": []}, b2u)     # the model sees the whole normalised text
+    return Tokenizer(vocab, merges, added, byte_level, None, bos, eos, model.get("unk_token"), ignore_merges=bool(model.get("ignore_merges", False)),
+                     model_type=mtype, normalizer=_pl.build_normalizer(j.get("normalizer")), pre_tokenizer=pre,
+                     post_processor=_pl.build_post_processor(j.get("post_processor"), full), decoder=_pl.build_decoder(j.get("decoder"), {v: k for k, v in b2u.items()}),
+                     continuing_subword_prefix=model.get("continuing_subword_prefix") or "", end_of_word_suffix=model.get("end_of_word_suffix") or "",
+                     byte_fallback=bool(model.get("byte_fallback", False)), max_input_chars_per_word=int(model.get("max_input_chars_per_word", 100)),
+                     special_tokens=special)
 
 
 def encode(tok: Tokenizer, text: str, add_special_tokens: bool = False) -> List[int]:
