@@ -286,6 +286,20 @@ class SentenceTransformer(nn.Module):
 
     encode = forward
 
+    @torch.no_grad()
+    def encode_texts(self, tokenizer, texts, max_length: int = 512, pad_id: int = 0) -> torch.Tensor:
+        """Embeddings ``[len(texts), hidden]`` of strings: tokenised with the file's own special tokens (``[CLS] ... [SEP]``), truncated to
+        ``max_length`` keeping the last special token, padded to the longest of the batch with a mask."""
+        rows = []
+        for t in texts:
+            ids = tokenizer.encode(t, add_special_tokens=True)
+            rows.append(ids[: max_length - 1] + ids[-1:] if len(ids) > max_length else ids)
+        n = max(len(r) for r in rows)
+        dev = next(self.parameters()).device
+        ids = torch.tensor([r + [pad_id] * (n - len(r)) for r in rows], dtype=torch.long, device=dev)
+        mask = torch.tensor([[1] * len(r) + [0] * (n - len(r)) for r in rows], dtype=torch.long, device=dev)
+        return self(ids, mask)
+
 
 def load_bert_model(path: str, cfg: Optional[BertConfig] = None, strict: bool = False, device="cpu", dtype=torch.float32):
     """Two forms. ``load_bert_model(directory)`` reads ``config.json`` + ``model.safetensors`` and returns the model (with a pooler when the file

@@ -141,3 +141,32 @@ def test_other_stages_follow_the_hf_library(tmp_path):
         want = sp.encode(t, add_special_tokens=False).ids
         assert ours.encode(t) == want, t
         assert ours.decode(want) == sp.decode(want), t
+
+
+def test_sentence_embeddings_from_strings_match_the_hf_stack(tmp_path):
+    """Strings -> WordPiece ids with [CLS] / [SEP] -> padded batch -> BERT -> masked mean pool -> unit vectors: this package's tokenizer and
+    model against the HF tokenizer feeding transformers' BertModel with the same weights."""
+    import torch
+    import transformers
+    from ferrotorch_b200.models import bert
+    hf = tk.Tokenizer(models.WordPiece(unk_token="[UNK]"))
+    hf.normalizer = normalizers.BertNormalizer()
+    hf.pre_tokenizer = pre_tokenizers.BertPreTokenizer()
+    hf.train(CORPUS, trainers.WordPieceTrainer(vocab_size=800, special_tokens=["[PAD]", "[UNK]", "[CLS]", "[SEP]"], show_progress=False))
+    hf.post_processor = processors.TemplateProcessing(single="[CLS] $A [SEP]", special_tokens=[("[CLS]", hf.token_to_id("[CLS]")), ("[SEP]", hf.token_to_id("[SEP]"))])
+    hf.save(str(tmp_path / "tokenizer.json"))
+    ours_tok = tokenize.load_tokenizer(tmp_path)
+    torch.manual_seed(0)
+    kw = dict(vocab_size=hf.get_vocab_size(), hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64, max_position_embeddings=64)
+    hm, m = transformers.BertModel(transformers.BertConfig(**kw)).eval(), bert.BertModel(bert.BertConfig(**kw)).eval()
+    m.load_state_dict(hm.state_dict(), strict=False)
+    texts = ["return the tensor", "def forward(self, x): pass", "a much longer sentence about kernels, streams and graphs " * 3]
+    emb = bert.SentenceTransformer(m).encode_texts(ours_tok, texts, max_length=48, pad_id=hf.token_to_id("[PAD]"))
+    hf.enable_truncation(48)
+    hf.enable_padding(pad_id=hf.token_to_id("[PAD]"), pad_token="[PAD]")
+    enc = hf.encode_batch(texts)
+    ids, mask = torch.tensor([e.ids for e in enc]), torch.tensor([e.attention_mask for e in enc])
+    with torch.no_grad():
+        h = hm(input_ids=ids, attention_mask=mask).last_hidden_state
+    ref = torch.nn.functional.normalize((h * mask[..., None]).sum(1) / mask.sum(1, keepdim=True), dim=-1)
+    assert emb.shape == (3, 32) and (emb - ref).abs().max() < 1e-5
