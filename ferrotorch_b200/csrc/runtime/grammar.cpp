@@ -19,7 +19,7 @@
 
 namespace {
 
-enum Kind : int32_t { K_OBJECT = 0, K_ARRAY = 1, K_STRING = 2, K_NUMBER = 3, K_INTEGER = 4, K_BOOLEAN = 5, K_NULL = 6, K_ENUM = 7, K_ANY = 8 };
+enum Kind : int32_t { K_OBJECT = 0, K_ARRAY = 1, K_STRING = 2, K_NUMBER = 3, K_INTEGER = 4, K_BOOLEAN = 5, K_NULL = 6, K_ENUM = 7, K_ANY = 8, K_NULLABLE = 9 };
 
 struct Edge { std::string lit; int32_t child; bool required; };
 struct Node { int32_t kind; std::vector<Edge> edges; };      // object: properties in schema order; array: one edge (items); enum: literals
@@ -206,6 +206,11 @@ R value(const Grammar& g, int32_t node, sv t, int64_t i, int depth) {
       return res;
     }
     case K_ANY: return value_any(g, t, i, depth);
+    case K_NULLABLE: {
+      const R r = lit("null", t, i);
+      if (r.tag != INVALID || s.edges.empty()) return r;
+      return value(g, s.edges[0].child, t, i, depth + 1);
+    }
     case K_ARRAY: return array_(g, s.edges.empty() ? -1 : s.edges[0].child, t, i, depth);
     case K_OBJECT: return object_(g, &s, t, i, depth);
   }
@@ -225,8 +230,8 @@ inline bool complete(const Grammar& g, sv t) {
 }  // namespace
 
 // Builds a grammar from a flattened schema and the vocabulary. Node k has kind[k] (0 object, 1 array, 2 string, 3 number, 4 integer,
-// 5 boolean, 6 null, 7 enum, 8 any) and the edges edge_first[k] .. edge_first[k+1]: for an object its properties in schema order (lit = the
-// key as a JSON string literal), for an array at most one (child = items node), for an enum its values as JSON literals (child -1). Edge e
+// 5 boolean, 6 null, 7 enum, 8 any, 9 nullable: null or its one child) and the edges edge_first[k] .. edge_first[k+1]: for an object its properties in schema order (lit = the
+// key as a JSON string literal), for an array or a nullable at most one (child = items / inner node), for an enum its values as JSON literals (child -1). Edge e
 // has the literal lits[lit_off[e] .. lit_off[e+1]). Vocabulary entry v is vocab[voff[v] .. voff[v+1]) in UTF-8. Node 0 is the root.
 FT_API void* ft_json_grammar_create(const int32_t* kind, const int32_t* edge_first, int64_t n_nodes, const uint8_t* lits, const int64_t* lit_off,
                                     const int32_t* edge_child, const uint8_t* edge_required, const uint8_t* vocab, const int64_t* voff, int64_t n_vocab) {

@@ -25,7 +25,7 @@ _DIGITS = "0123456789"                          # JSON numbers take ASCII digits
 
 @dataclass
 class Schema:
-    kind: str                                  # object | array | string | number | integer | boolean | null | enum | any
+    kind: str                                  # object | array | string | number | integer | boolean | null | enum | any | nullable (items = inner)
     properties: Dict[str, "Schema"] = field(default_factory=dict)
     required: List[str] = field(default_factory=list)
     items: Optional["Schema"] = None
@@ -35,9 +35,19 @@ class Schema:
     def from_json(j) -> "Schema":
         if isinstance(j, str):
             j = json.loads(j)
+        if not isinstance(j, dict):
+            raise InvalidArgument("a JSON schema must be an object")
+        for word in ("oneOf", "anyOf", "allOf", "$ref"):        # composition and references are not compiled: refuse rather than ignore them
+            if word in j:
+                raise InvalidArgument(f"unsupported schema keyword {word}")
         if "enum" in j:
             return Schema("enum", enum=list(j["enum"]))
         t = j.get("type", "any")
+        if isinstance(t, list):                        # ["X", "null"]: a nullable X
+            rest = [x for x in t if x != "null"]
+            if len(rest) != 1 or len(rest) + 1 != len(t):
+                raise InvalidArgument(f"unsupported type list {t}: only [X, \"null\"] is compiled")
+            return Schema("nullable", items=Schema.from_json({**j, "type": rest[0]}))
         if t == "object":
             return Schema("object", {k: Schema.from_json(v) for k, v in j.get("properties", {}).items()}, list(j.get("required", [])))
         if t == "array":
@@ -167,6 +177,9 @@ class JsonGrammar:
             return a if a is not None else b
         if k == "null":
             return self._lit("null", t, i)
+        if k == "nullable":
+            r = self._lit("null", t, i)
+            return r if r is not None else self._value(s.items, t, i)
         if k == "enum":
             res = None
             for v in s.enum or []:
@@ -342,7 +355,7 @@ class TokenMask:
         return int(self.allowed.sum())
 
 
-_KIND_CODE = {"object": 0, "array": 1, "string": 2, "number": 3, "integer": 4, "boolean": 5, "null": 6, "enum": 7, "any": 8}
+_KIND_CODE = {"object": 0, "array": 1, "string": 2, "number": 3, "integer": 4, "boolean": 5, "null": 6, "enum": 7, "any": 8, "nullable": 9}
 
 
 def _flatten_schema(root: Schema):
@@ -367,7 +380,7 @@ def _flatten_schema(root: Schema):
                 lits.append(json.dumps(name).encode("utf-8"))
                 child.append(index[id(sub)])
                 req.append(1 if name in s.required else 0)
-        elif s.kind == "array" and s.items is not None:
+        elif s.kind in ("array", "nullable") and s.items is not None:
             lits.append(b"")
             child.append(index[id(s.items)])
             req.append(0)

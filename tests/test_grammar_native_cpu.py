@@ -17,6 +17,10 @@ def _random_schema(rng, depth=0):
         return {"type": "object", "properties": {n: _random_schema(rng, depth + 1) for n in names}, "required": [n for n in names if rng.random() < 0.5]}
     if k == "array":
         return {"type": "array", "items": _random_schema(rng, depth + 1)} if rng.random() < 0.8 else {"type": "array"}
+    if rng.random() < 0.15 and k not in ("enum", "any", "null"):
+        inner = _random_schema(rng, depth + 1)
+        if "type" in inner and isinstance(inner["type"], str) and inner["type"] not in ("any", "null"):
+            return {**inner, "type": [inner["type"], "null"]}
     if k == "enum":
         return {"enum": rng.sample(["red", "green", 1, 2.5, True, None, "a\"b", "é"], rng.randint(1, 4))}
     return {"type": k}
@@ -26,6 +30,8 @@ def _random_doc(rng, s, depth=0):
     if "enum" in s:
         return rng.choice(s["enum"])
     t = s.get("type", "any")
+    if isinstance(t, list):
+        return None if rng.random() < 0.4 else _random_doc(rng, {**s, "type": t[0]}, depth)
     if t == "object":
         out = {}
         for n, sub in s.get("properties", {}).items():
@@ -116,3 +122,20 @@ def test_constrained_generation_reaches_a_complete_document_with_either_route(mo
 def test_numbers_take_ascii_digits_only():
     g = G.JsonGrammar(G.Schema.from_json({"type": "number"}))
     assert g.accepts_prefix("12") and not g.accepts_prefix("٣") and not g.accepts_prefix("1²")
+
+
+def test_nullable_types_and_refused_keywords():
+    s = G.Schema.from_json({"type": "object", "properties": {"a": {"type": ["integer", "null"]}, "b": {"type": ["null", "string"]}}, "required": ["a", "b"]})
+    assert s.properties["a"].kind == "nullable" and s.properties["a"].items.kind == "integer" and s.properties["b"].items.kind == "string"
+    g = G.JsonGrammar(s)
+    for doc in ('{"a":null,"b":"x"}', '{"a":12,"b":null}', '{"a": null, "b": null}'):
+        assert g.is_complete(doc) and all(g.accepts_prefix(doc[:c]) for c in range(1, len(doc)))
+    assert not g.accepts_prefix('{"a":nul1') and not g.accepts_prefix('{"a":"x"')
+    proc = G.JsonSchemaProcessor(s, ["n", "null", "1", "\"", "t", "nu", "x"])
+    proc.text = '{"a":'
+    assert proc.mask().allowed.tolist() == proc._mask_py().allowed.tolist() == [True, True, True, False, False, True, False]
+    for word in ("oneOf", "anyOf", "allOf", "$ref"):
+        with pytest.raises(Exception):
+            G.Schema.from_json({word: [{"type": "string"}]})
+    with pytest.raises(Exception):
+        G.Schema.from_json({"type": ["string", "integer"]})
