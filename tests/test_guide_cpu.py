@@ -48,3 +48,18 @@ def test_guide_snippets(tmp_path):
     enc = nn.TransformerEncoder(nn.TransformerEncoderLayer(64, 4, 128, dropout=0.0, batch_first=True), 2)
     assert enc(torch.randn(2, 10, 64), src_key_padding_mask=torch.zeros(2, 10, dtype=torch.bool)).shape == (2, 10, 64)
     assert nn.attention_backend(torch.randn(1, 2, 8, 64)) == "standard"
+    # 10. tokenizers and constrained decoding
+    from ferrotorch_b200 import grammar, tokenize
+    vocab = {c: i for i, c in enumerate(["<eos>"] + [tokenize._bytes_to_unicode()[b] for b in range(256)])}
+    vocab.update({"he": 257, "ll": 258, "hell": 259, "hello": 260})
+    tok = tokenize.Tokenizer(vocab, [("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o")], {"<eos>": 0})
+    ids = tok.encode("hello {\"n\": 7}")
+    assert ids[0] == 260 and tok.decode(ids) == "hello {\"n\": 7}" and tok.encode_batch(["hello", "hi"])[0] == [260]
+    texts = [tok.decode([i], skip_special_tokens=False) if i else "" for i in range(tok.vocab_size())]
+    proc = grammar.JsonSchemaProcessor({"type": "object", "properties": {"n": {"type": ["integer", "null"]}}, "required": ["n"]}, texts, eos_id=0)
+    for ch in "{\"n\": ":
+        logits = proc.apply(torch.zeros(len(texts)))
+        assert logits[vocab[tokenize._bytes_to_unicode()[ord(ch)]]] == 0
+        proc.advance(vocab[tokenize._bytes_to_unicode()[ord(ch)]])
+    allowed = {texts[i] for i in proc.mask().allowed.nonzero().flatten().tolist()}
+    assert allowed == set("-0123456789n")
