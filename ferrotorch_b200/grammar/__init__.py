@@ -489,6 +489,20 @@ class JsonSchemaProcessor:
     def apply(self, logits: torch.Tensor) -> torch.Tensor:
         return apply_mask(logits, self.mask())
 
+    def as_logits_processor(self, prompt_len: int):
+        """``f(logits, seq)`` for ``models.llama_gen.generate(..., logits_processor=f)`` (batch size 1): every token appended to ``seq`` since
+        the last call is fed to ``advance``, then the mask of the new state is applied. ``prompt_len`` tokens at the front are not output."""
+        seen = [prompt_len]
+
+        def f(logits: torch.Tensor, seq: torch.Tensor) -> torch.Tensor:
+            if seq.shape[0] != 1:
+                raise InvalidArgument("one grammar state constrains one sequence: batch size must be 1")
+            for t in seq[0, seen[0]:].tolist():
+                self.advance(int(t))
+            seen[0] = seq.shape[1]
+            return self.apply(logits)
+        return f
+
 
 def apply_mask(logits: torch.Tensor, mask: TokenMask) -> torch.Tensor:
     """``logits[..., v] = -inf`` where the mask forbids token ``v``."""

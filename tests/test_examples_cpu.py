@@ -40,3 +40,13 @@ def test_llama_entry_point_and_sparsity_report_run_on_cpu():
     assert "FatRelu(0.02)" in out and "mean MLP sparsity" in out
     share = float(out.strip().splitlines()[-1].split(":")[1].split("%")[0])
     assert 40.0 < share < 65.0          # random weights: about half of the gate pre-activations fall below the threshold
+
+
+def test_constrained_generation_example_emits_a_document_of_the_schema():
+    import json
+    out = _run(ROOT / "examples/json_constrained_generate.py", "--new", "160", "--seed", "1")
+    assert "valid prefix: True" in out
+    line = next(l for l in out.splitlines() if l.startswith("generated: "))
+    if "complete document: True" in out:
+        doc = json.loads(line[len("generated: "):])
+        assert isinstance(doc["name"], str) and isinstance(doc["age"], int) and set(doc) <= {"name", "age", "tags", "note"}
