@@ -1,5 +1,5 @@
-"""Tokenizer: a self-contained reader of HF ``tokenizer.json`` (byte-level BPE and plain BPE models, added/special tokens,
-pre-tokenisation by the GPT-2 / Llama-3 split pattern) plus chat templates.
+"""Tokenizer: a self-contained reader of HF ``tokenizer.json`` (BPE, WordPiece, WordLevel and Unigram models with the file's normalizer,
+pre-tokenizer, post-processor and decoder stages, added / special tokens) plus chat templates.
 
 Reference parity: ferrotorch-tokenize/src/lib.rs:59 (load_tokenizer), :85 (encode), :104 (encode_batch), :131 (decode),
 :225 (apply_chat_template) - a wrapper over the HF ``tokenizers`` crate there; here the BPE merge loop is implemented directly: in
@@ -90,15 +90,24 @@ class Tokenizer:
                  byte_level: bool = True, split_pattern: Optional[str] = None, bos_token: Optional[str] = None, eos_token: Optional[str] = None,
                  unk_token: Optional[str] = None, ignore_merges: bool = False, model_type: str = "BPE", normalizer=None, pre_tokenizer=None,
                  post_processor=None, decoder=None, continuing_subword_prefix: str = "", end_of_word_suffix: str = "", byte_fallback: bool = False,
-                 max_input_chars_per_word: int = 100, special_tokens: Optional[Iterable[str]] = None):
+                 max_input_chars_per_word: int = 100, special_tokens: Optional[Iterable[str]] = None, scores: Optional[Sequence[float]] = None,
+                 unk_id: Optional[int] = None):
         """``vocab`` / ``merges`` / ``added_tokens`` with the GPT-2 split (or ``split_pattern``) is the short form; ``load_tokenizer`` passes
         the stages of a ``tokenizer.json`` (``normalizer``: str -> str; ``pre_tokenizer``: ``pipeline.PreTokenizer``; ``post_processor``: ids ->
         ids with the special tokens of one sequence; ``decoder``: token strings -> strings) and the model's type and affixes."""
-        if model_type not in ("BPE", "WordPiece"):
+        if model_type not in ("BPE", "WordPiece", "WordLevel", "Unigram"):
             raise InvalidArgument(f"unsupported tokenizer model {model_type}")
         self.model_type = model_type
         self.normalizer, self.pre_tokenizer, self.post_processor, self.decoder_chain = normalizer, pre_tokenizer, post_processor, decoder
         self.prefix, self.suffix, self.byte_fallback, self.max_chars = continuing_subword_prefix or "", end_of_word_suffix or "", byte_fallback, max_input_chars_per_word
+        self.scores = {t: float(sc) for t, sc in zip(vocab, scores)} if scores is not None else None     # Unigram: log-probability per entry
+        if model_type == "Unigram":
+            if self.scores is None:
+                raise InvalidArgument("a Unigram model needs one score per vocabulary entry")
+            self._max_piece = max((len(t) for t in vocab), default=1)
+            self._unk_score = min(self.scores.values(), default=0.0) - 10.0
+            if unk_id is not None and unk_token is None:
+                unk_token = next((t for t, i in vocab.items() if i == unk_id), None)
         self.vocab = dict(vocab)
         self.model_vocab = dict(vocab)                 # without the added tokens: what ``ignore_merges`` looks whole pieces up in
         self.ignore_merges = bool(ignore_merges)
@@ -303,6 +312,42 @@ class Tokenizer:
             start = end
         return out
 
+    def _unigram(self, word: str) -> List[str]:
+        """Best segmentation of ``word`` under the entry scores (Viterbi over end positions; ties keep the path found first, from the
+        earlier start); a character that starts no entry costs the lowest score minus ten, and runs of such characters come out as one
+        piece (which the lookup maps to the unknown token or to byte tokens)."""
+        n = len(word)
+        best = [float("-inf")] * (n + 1)
+        back = [-1] * (n + 1)
+        best[0] = 0.0
+        scores = self.scores
+        for a in range(n):
+            if best[a] == float("-inf"):
+                continue
+            single = False
+            for e in range(a + 1, min(n, a + self._max_piece) + 1):
+                sc = scores.get(word[a:e])
+                if sc is None:
+                    continue
+                if e == a + 1:
+                    single = True
+                if back[e] < 0 or best[a] + sc > best[e]:
+                    best[e], back[e] = best[a] + sc, a
+            if not single and (back[a + 1] < 0 or best[a] + self._unk_score > best[a + 1]):
+                best[a + 1], back[a + 1] = best[a] + self._unk_score, a
+        out, e = [], n
+        while e > 0:
+            out.append(word[back[e]: e])
+            e = back[e]
+        out.reverse()
+        fused: List[str] = []
+        for t in out:
+            if t not in scores and fused and fused[-1] not in scores:
+                fused[-1] += t
+            else:
+                fused.append(t)
+        return fused
+
     def _encode_plain_py(self, text: str) -> List[int]:
         """``text`` is already normalised."""
         ids: List[int] = []
@@ -311,7 +356,8 @@ class Tokenizer:
         else:
             pieces = ["".join(self._b2u[b] for b in p.encode("utf-8")) if self.byte_level else p for p in self.split.findall(text)]
         for w in pieces:
-            for tok in (self._wordpiece(w) if self.model_type == "WordPiece" else self._bpe(w)):
+            mt = self.model_type
+            for tok in (self._bpe(w) if mt == "BPE" else self._wordpiece(w) if mt == "WordPiece" else self._unigram(w) if mt == "Unigram" else [w]):
                 self._lookup(tok, ids)
         return ids
 
@@ -452,8 +498,9 @@ def load_tokenizer(path) -> Tokenizer:
         p = p / "tokenizer.json"
     j = json.loads(p.read_text())
     model = j.get("model", {})
-    mtype = model.get("type") or ("WordPiece" if "merges" not in model else "BPE")
-    if mtype not in ("BPE", "WordPiece"):
+    mtype = model.get("type") or ("Unigram" if isinstance(model.get("vocab"), list) else "BPE" if "merges" in model else
+                                  "WordPiece" if "continuing_subword_prefix" in model else "WordLevel")
+    if mtype not in ("BPE", "WordPiece", "WordLevel", "Unigram"):
         raise InvalidArgument(f"unsupported tokenizer model {mtype}")
     merges = [tuple(m.split(" ", 1)) if isinstance(m, str) else tuple(m) for m in model.get("merges", [])]
     added = {a["content"]: a["id"] for a in j.get("added_tokens", [])}
@@ -461,6 +508,10 @@ def load_tokenizer(path) -> Tokenizer:
     b2u = _bytes_to_unicode()
     pre = _pl.PreTokenizer(j.get("pre_tokenizer"), b2u) if j.get("pre_tokenizer") else None
     vocab = model.get("vocab", {})
+    scores = None
+    if mtype == "Unigram":                             # a list of [entry, score]; the id is the position
+        scores = [sc for _, sc in vocab]
+        vocab = {t: i for i, (t, _) in enumerate(vocab)}
     full = dict(vocab)
     full.update(added)
     bos = eos = None
@@ -480,7 +531,7 @@ def load_tokenizer(path) -> Tokenizer:
                      post_processor=_pl.build_post_processor(j.get("post_processor"), full), decoder=_pl.build_decoder(j.get("decoder"), {v: k for k, v in b2u.items()}),
                      continuing_subword_prefix=model.get("continuing_subword_prefix") or "", end_of_word_suffix=model.get("end_of_word_suffix") or "",
                      byte_fallback=bool(model.get("byte_fallback", False)), max_input_chars_per_word=int(model.get("max_input_chars_per_word", 100)),
-                     special_tokens=special)
+                     special_tokens=special, scores=scores, unk_id=model.get("unk_id"))
 
 
 def encode(tok: Tokenizer, text: str, add_special_tokens: bool = False) -> List[int]:

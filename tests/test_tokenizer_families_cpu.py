@@ -170,3 +170,40 @@ def test_sentence_embeddings_from_strings_match_the_hf_stack(tmp_path):
         h = hm(input_ids=ids, attention_mask=mask).last_hidden_state
     ref = torch.nn.functional.normalize((h * mask[..., None]).sum(1) / mask.sum(1, keepdim=True), dim=-1)
     assert emb.shape == (3, 32) and (emb - ref).abs().max() < 1e-5
+
+
+def test_unigram_and_word_level_models(tmp_path):
+    """A Unigram model (Viterbi over entry scores, unknown characters fused or spelled as byte tokens) with the metaspace stages of
+    sentencepiece-style files, and a WordLevel model with an unknown token: ids and decoding against the HF library."""
+    for byte_fallback in (False, True):
+        hf = tk.Tokenizer(models.Unigram())
+        hf.normalizer = normalizers.Sequence([normalizers.NFKC(), normalizers.Replace(Regex(" {2,}"), " ")])
+        hf.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="always")
+        hf.decoder = decoders.Metaspace(replacement="▁", prepend_scheme="always")
+        extra = [f"<0x{b:02X}>" for b in range(256)] if byte_fallback else []
+        hf.train(CORPUS[:12], trainers.UnigramTrainer(vocab_size=1400, special_tokens=["<unk>", "<s>", "</s>"] + extra, unk_token="<unk>", show_progress=False))
+        path = tmp_path / "tokenizer.json"
+        hf.save(str(path))
+        if byte_fallback:
+            import json
+            j = json.loads(path.read_text())
+            j["model"]["byte_fallback"] = True
+            path.write_text(json.dumps(j))
+            hf = tk.Tokenizer.from_file(str(path))
+        ours = tokenize.load_tokenizer(path)
+        assert ours.model_type == "Unigram" and ours.unk_token == "<unk>"
+        for t in ["hello world", "def forward(self, x): return self.proj(x)", "the tensor is contiguous", "snowman ☃☃ and 你好 unknown", "  two  spaces ", "x",
+                  Path(CORPUS[2]).read_text()[:1500]]:
+            want = hf.encode(t, add_special_tokens=False).ids
+            assert ours.encode(t) == want, (byte_fallback, t[:40])
+            assert ours.decode(want) == hf.decode(want), (byte_fallback, t[:40])
+    wl = tk.Tokenizer(models.WordLevel(unk_token="[UNK]"))
+    wl.normalizer = normalizers.Lowercase()
+    wl.pre_tokenizer = pre_tokenizers.Whitespace()
+    wl.train(CORPUS[:6], trainers.WordLevelTrainer(vocab_size=500, special_tokens=["[UNK]"], show_progress=False))
+    path = tmp_path / "tokenizer.json"
+    wl.save(str(path))
+    ours = tokenize.load_tokenizer(path)
+    assert ours.model_type == "WordLevel"
+    for t in ["import torch", "Return SELF.value + zzzunknownzzz", "def f(x): pass"]:
+        assert ours.encode(t) == wl.encode(t).ids, t
