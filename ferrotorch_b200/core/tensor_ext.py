@@ -18,6 +18,8 @@ import einops as _einops
 import torch
 
 from ..errors import InvalidArgument, ShapeMismatch
+from . import einsum_impl as _einsum_impl
+from . import special_fns as _sf
 
 L = torch.linalg
 
@@ -70,19 +72,21 @@ class fft:
 
 # -- special --------------------------------------------------------------------------------------------------------------------
 class special:
-    erf, erfc, erfinv = staticmethod(torch.erf), staticmethod(torch.erfc), staticmethod(torch.erfinv)
-    lgamma, digamma = staticmethod(torch.lgamma), staticmethod(torch.digamma)
-    log1p, expm1, sinc, xlogy = staticmethod(torch.log1p), staticmethod(torch.expm1), staticmethod(torch.sinc), staticmethod(torch.xlogy)
+    """Written out in ``core/special_fns.py`` (series, continued fractions, recurrences); ``log1p`` / ``expm1`` are the substrate's primitives."""
+    erf, erfc, erfinv = staticmethod(_sf.erf), staticmethod(_sf.erfc), staticmethod(_sf.erfinv)
+    lgamma, digamma = staticmethod(_sf.lgamma), staticmethod(_sf.digamma)
+    log1p, expm1, sinc, xlogy = staticmethod(torch.log1p), staticmethod(torch.expm1), staticmethod(_sf.sinc), staticmethod(_sf.xlogy)
     for _n in ("chebyshev_polynomial_t", "chebyshev_polynomial_u", "chebyshev_polynomial_v", "chebyshev_polynomial_w", "hermite_polynomial_h",
                "hermite_polynomial_he", "laguerre_polynomial_l", "legendre_polynomial_p", "shifted_chebyshev_polynomial_t",
                "shifted_chebyshev_polynomial_u", "shifted_chebyshev_polynomial_v", "shifted_chebyshev_polynomial_w"):
-        locals()[_n] = staticmethod(getattr(torch.special, _n))
+        locals()[_n] = staticmethod(getattr(_sf, _n))
     del _n
 
 
 # -- einsum / einops ------------------------------------------------------------------------------------------------------------------
 def einsum(equation: str, *operands: torch.Tensor) -> torch.Tensor:
-    return torch.einsum(equation, *operands)
+    """Einstein summation, planned and contracted in ``core/einsum_impl.py`` (diagonals, single-operand sums, pairwise batched products)."""
+    return _einsum_impl.einsum(equation, *operands)
 
 
 einsum_differentiable = einsum

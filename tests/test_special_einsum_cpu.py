@@ -1,0 +1,102 @@
+"""The special functions and the Einstein summation of ``core`` are written out in this package (series / continued fractions / recurrences;
+parse + diagonal + pairwise batched products): values, gradients and edge cases against the substrate's library functions."""
+import pytest
+import torch
+
+from ferrotorch_b200 import core as X
+from ferrotorch_b200.core import einsum_impl, special_fns as S
+
+
+def _rel(got, want, floor=1.0):
+    fin = torch.isfinite(want) & torch.isfinite(got)
+    return ((got - want)[fin].abs() / want[fin].abs().clamp(min=floor)).max().item()
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 2e-12), (torch.float32, 2e-6)])
+def test_error_and_gamma_functions_match_the_library(dtype, tol):
+    x = torch.cat([torch.linspace(-6, 6, 1201), torch.tensor([0.0, 1e-8, -1e-8, 1.9999, 2.0, 2.0001, 10.0, -10.0, 27.0])]).to(dtype)
+    assert (S.erf(x) - torch.erf(x)).abs().max() < tol and (S.erfc(x) - torch.erfc(x)).abs().max() < tol
+    big = torch.tensor([3.0, 5.0, 8.0, 12.0], dtype=dtype)
+    assert _rel(S.erfc(big), torch.erfc(big), floor=torch.finfo(dtype).tiny) < (1e-11 if dtype == torch.float64 else 1e-5)      # the tail keeps its relative accuracy
+    p = torch.cat([torch.linspace(-0.999999, 0.999999, 2001), torch.tensor([0.0, 1 - 1e-7, 1e-30])]).to(dtype)
+    assert _rel(S.erfinv(p), torch.erfinv(p), floor=1e-30) < (1e-10 if dtype == torch.float64 else 1e-5)
+    edge = S.erfinv(torch.tensor([1.0, -1.0, 1.5, -2.0], dtype=dtype))
+    assert edge[0] == float("inf") and edge[1] == float("-inf") and torch.isnan(edge[2:]).all()
+    g = torch.cat([torch.linspace(-9.7, 30, 1501), torch.tensor([1e-6, 0.5, 1.0, 2.0, 100.0, 1e5, -0.5, -2.5])]).to(dtype)
+    assert _rel(S.lgamma(g), torch.lgamma(g)) < tol * 10 and _rel(S.digamma(g), torch.digamma(g)) < tol * 50
+    poles = torch.tensor([0.0, -1.0, -3.0], dtype=dtype)
+    assert torch.isinf(S.lgamma(poles)).all() and S.digamma(poles)[0] == float("-inf") and torch.isnan(S.digamma(poles)[1:]).all()
+    z = torch.linspace(-3, 3, 601).to(dtype)
+    assert (S.sinc(z) - torch.sinc(z)).abs().max() < tol
+    a, b = torch.tensor([0.0, 2.0, 0.0, 3.0], dtype=dtype), torch.tensor([0.0, 3.0, float("nan"), 0.5], dtype=dtype)
+    assert torch.allclose(S.xlogy(a, b), torch.xlogy(a, b), equal_nan=True)
+    assert X.special.erf is not torch.erf and X.special.lgamma is not torch.lgamma                     # the namespace points at the own forms
+
+
+def test_special_functions_are_differentiable():
+    x = torch.tensor([-1.3, -0.2, 0.4, 1.7, 2.6], dtype=torch.float64, requires_grad=True)
+    for ours, theirs in ((S.erf, torch.erf), (S.erfc, torch.erfc), (S.sinc, torch.sinc)):
+        ga, = torch.autograd.grad(ours(x).sum(), x)
+        gb, = torch.autograd.grad(theirs(x).sum(), x)
+        assert torch.allclose(ga, gb, atol=1e-10)
+    p = torch.tensor([0.7, 1.5, 3.2, 8.0, 15.0], dtype=torch.float64, requires_grad=True)
+    for ours, theirs in ((S.lgamma, torch.lgamma), (S.digamma, torch.digamma)):
+        ga, = torch.autograd.grad(ours(p).sum(), p)
+        gb, = torch.autograd.grad(theirs(p).sum(), p)
+        assert torch.allclose(ga, gb, atol=1e-9)
+    q = torch.tensor([-0.8, -0.1, 0.3, 0.9], dtype=torch.float64, requires_grad=True)
+    ga, = torch.autograd.grad(S.erfinv(q).sum(), q)
+    gb, = torch.autograd.grad(torch.erfinv(q).sum(), q)
+    assert torch.allclose(ga, gb, rtol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["chebyshev_polynomial_t", "chebyshev_polynomial_u", "chebyshev_polynomial_v", "chebyshev_polynomial_w", "hermite_polynomial_h",
+                                  "hermite_polynomial_he", "laguerre_polynomial_l", "legendre_polynomial_p", "shifted_chebyshev_polynomial_t",
+                                  "shifted_chebyshev_polynomial_u", "shifted_chebyshev_polynomial_v", "shifted_chebyshev_polynomial_w"])
+def test_orthogonal_polynomials_match_the_library(name):
+    ours, theirs = getattr(X.special, name), getattr(torch.special, name)
+    xs = torch.linspace(-1.2, 1.2, 101, dtype=torch.float64)
+    for n in (0, 1, 2, 3, 7, 12):
+        assert _rel(ours(xs, n), theirs(xs, torch.tensor(n))) < 1e-11, n
+    nt = torch.randint(0, 9, (101,), generator=torch.Generator().manual_seed(0))
+    assert _rel(ours(xs, nt), theirs(xs, nt)) < 1e-11
+    assert _rel(ours(xs.float(), 5), theirs(xs.float(), torch.tensor(5))) < 1e-5 and ours(xs.float(), 5).dtype == torch.float32
+    assert torch.equal(ours(xs, -1), torch.zeros_like(xs))
+    g = xs.clone().requires_grad_()
+    ga, = torch.autograd.grad(ours(g, 4).sum(), g)
+    eps = 1e-6
+    assert torch.allclose(ga, (ours(xs + eps, 4) - ours(xs - eps, 4)) / (2 * eps), atol=1e-5)
+
+
+EINSUM_CASES = [("ij,jk->ik", (3, 4), (4, 5)), ("ij,jk", (3, 4), (4, 5)), ("bij,bjk->bik", (2, 3, 4), (2, 4, 5)), ("ii->i", (4, 4)), ("ii", (4, 4)), ("ij->ji", (3, 4)),
+                ("ij->", (3, 4)), ("i,j->ij", (3,), (4,)), ("...ij,...jk->...ik", (2, 5, 3, 4), (2, 5, 4, 6)), ("bhqd,bhkd->bhqk", (2, 3, 4, 8), (2, 3, 5, 8)),
+                ("ij,ij,ij->i", (3, 4), (3, 4), (3, 4)), ("abc,cd,de->abe", (2, 3, 4), (4, 5), (5, 6)), ("i,i->", (5,), (5,)), ("...,...->...", (3, 4), (3, 4)),
+                ("ij...,j->i...", (3, 4, 2, 2), (4,)), ("iji->j", (3, 4, 3)), ("bn,anm,bm->ba", (2, 3), (5, 3, 4), (2, 4)), ("ab,cd->abcd", (2, 3), (4, 5)),
+                ("a...b,b->a...", (2, 3, 4), (4,)), ("ij,kj->ik", (3, 1), (5, 4)), ("i->", (6,)), ("ijk->kji", (2, 3, 4)), (" i j , j k -> i k ", (2, 3), (3, 2))]
+
+
+@pytest.mark.parametrize("case", EINSUM_CASES, ids=[c[0].strip() for c in EINSUM_CASES])
+def test_einsum_values_and_gradients(case):
+    eq, *shapes = case
+    torch.manual_seed(0)
+    ops = [torch.randn(s, dtype=torch.float64, requires_grad=True) for s in shapes]
+    got, want = X.einsum(eq, *ops), torch.einsum(eq, *ops)
+    assert got.shape == want.shape and torch.allclose(got, want, atol=1e-12)
+    w = torch.randn_like(want)
+    ga, gb = torch.autograd.grad((got * w).sum(), ops), torch.autograd.grad((want * w).sum(), ops)
+    assert all(torch.allclose(a, b, atol=1e-12) for a, b in zip(ga, gb))
+
+
+def test_einsum_dtypes_lists_and_errors():
+    ia, ib = torch.randint(0, 5, (3, 4)), torch.randint(0, 5, (4, 2))
+    assert torch.equal(X.einsum("ij,jk->ik", ia, ib), ia @ ib)
+    a, b = torch.randn(3, 4), torch.randn(4, 5, dtype=torch.float64)
+    assert X.einsum("ij,jk->ik", a, b).dtype == torch.float64
+    assert torch.allclose(X.einsum("ij,jk->ik", [a.double(), b]), a.double() @ b)
+    c = torch.randn(2, 3, dtype=torch.complex64)
+    assert torch.allclose(X.einsum("ij,kj->ik", c, c.conj()), c @ c.conj().t(), atol=1e-5)
+    for eq, shapes in (("ij,jk->ik", [(3, 4), (5, 6)]), ("ij->k", [(2, 3)]), ("ij,jk", [(3, 4)]), ("ii->i", [(3, 4)]), ("ij->ii", [(2, 2)]), ("i.j->ij", [(2, 2)]),
+                       ("ij", [(2, 3, 4)])):
+        with pytest.raises(Exception):
+            einsum_impl.einsum(eq, *[torch.randn(s) for s in shapes])
+    assert X.einsum_differentiable is X.einsum
