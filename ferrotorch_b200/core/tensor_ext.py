@@ -14,10 +14,10 @@ import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
-import einops as _einops
 import torch
 
 from ..errors import InvalidArgument, ShapeMismatch
+from . import einops_impl as _einops_impl
 from . import einsum_impl as _einsum_impl
 from . import special_fns as _sf
 
@@ -93,18 +93,18 @@ einsum_differentiable = einsum
 
 
 def rearrange(t, pattern: str, **axes):
-    return _einops.rearrange(t, pattern, **axes)
+    return _einops_impl.rearrange(t, pattern, **axes)
 
 
 rearrange_with = rearrange
 
 
 def repeat(t, pattern: str, **axes):
-    return _einops.repeat(t, pattern, **axes)
+    return _einops_impl.repeat(t, pattern, **axes)
 
 
 def reduce(t, pattern: str, reduction: str = "mean", **axes):
-    return _einops.reduce(t, pattern, reduction, **axes)
+    return _einops_impl.reduce(t, pattern, reduction, **axes)
 
 
 # -- stride tricks ----------------------------------------------------------------------------------------------------------------

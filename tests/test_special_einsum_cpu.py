@@ -100,3 +100,36 @@ def test_einsum_dtypes_lists_and_errors():
         with pytest.raises(Exception):
             einsum_impl.einsum(eq, *[torch.randn(s) for s in shapes])
     assert X.einsum_differentiable is X.einsum
+
+
+def test_einops_patterns_match_the_einops_package():
+    einops = pytest.importorskip("einops")
+    torch.manual_seed(0)
+    x = torch.randn(2, 6, 8, 10, dtype=torch.float64, requires_grad=True)
+    cases = [("rearrange", "b c h w -> b h w c", {}), ("rearrange", "b c (h p) (w q) -> b (h w) (p q c)", dict(p=2, q=5)), ("rearrange", "b c h w -> (b c) (h w)", {}),
+             ("rearrange", "b (g c) h w -> g b c h w", dict(g=3)), ("rearrange", "... h w -> ... (h w)", {}), ("rearrange", "b ... -> ... b", {}),
+             ("rearrange", "b c h w -> b c h w 1", {}), ("rearrange", "b c h w -> b 1 (c h w)", {}), ("rearrange", "b c h (w w2) -> b c (h w2) w", dict(w2=2)),
+             ("repeat", "b c h w -> b c h w r", dict(r=3)), ("repeat", "b c h w -> b (c r) h w", dict(r=2)), ("repeat", "b c h w -> (r b) c (h s) w", dict(r=2, s=3)),
+             ("repeat", "... -> ... 2", {}), ("reduce", "b c h w -> b c", "mean", {}), ("reduce", "b c h w -> b c", "max", {}),
+             ("reduce", "b c (h p) (w q) -> b c h w", "sum", dict(p=2, q=2)), ("reduce", "b c h w -> b 1 h w", "min", {}), ("reduce", "b c h w -> (b c)", "prod", {}),
+             ("reduce", "... w -> ...", "sum", {}), ("reduce", "b c h w -> b c h w", "mean", {})]
+    for kind, pattern, *rest in cases:
+        if kind == "reduce":
+            got, want = X.reduce(x, pattern, rest[0], **rest[1]), einops.reduce(x, pattern, rest[0], **rest[1])
+        else:
+            got, want = getattr(X, kind)(x, pattern, **rest[0]), getattr(einops, kind)(x, pattern, **rest[0])
+        assert got.shape == want.shape and torch.allclose(got, want), pattern
+        w = torch.randn_like(want)
+        ga, = torch.autograd.grad((got * w).sum(), x)
+        gb, = torch.autograd.grad((want * w).sum(), x)
+        assert torch.allclose(ga, gb), pattern
+    y = torch.randn(3, 1, 5)
+    assert torch.equal(X.rearrange(y, "a 1 c -> a c"), y[:, 0]) and torch.equal(X.rearrange(y, "a () c -> c a"), y[:, 0].t())
+    assert torch.equal(X.rearrange_with(torch.arange(24.0).view(2, 12), "b (h w) -> b h w", h=3), torch.arange(24.0).view(2, 3, 4))
+    for bad in ("b c -> b", "b c h w -> b c h", "b (c d) h w -> b c d h w", "b c h w -> b c h w z", "b (c h w -> b", "b b h w -> b h w", "b c h w"):
+        with pytest.raises(Exception):
+            X.rearrange(x, bad)
+    with pytest.raises(Exception):
+        X.repeat(x, "b c h w -> b c h")
+    with pytest.raises(Exception):
+        X.reduce(x, "b c h w -> b c", "median")
