@@ -121,12 +121,105 @@ def as_strided_scatter(t, src, size, stride, storage_offset: int = 0):
 
 
 # -- signal windows ------------------------------------------------------------------------------------------------------------------
+def _win_n(M: int, sym: bool, dtype, device):
+    """Sample positions 0..M-1 of a window of length M (a periodic window is the symmetric one of length M + 1 without its last sample)."""
+    if M < 0:
+        raise InvalidArgument("window length must be non-negative")
+    dtype = dtype or torch.get_default_dtype()
+    n = torch.arange(M, dtype=torch.float64, device=device)
+    return n, float(M - 1 if sym else M), dtype
+
+
+def _i0(x: torch.Tensor) -> torch.Tensor:
+    """Modified Bessel function of order zero by its power series sum ((x/2)^2k / (k!)^2) (f64; enough terms for |x| up to a few hundred)."""
+    q = (x * 0.5) ** 2
+    term = torch.ones_like(x)
+    total = torch.ones_like(x)
+    for k in range(1, 400):
+        term = term * q / (k * k)
+        total = total + term
+    return total
+
+
 class windows:
-    _w = torch.signal.windows
-    bartlett, blackman, hamming, hann = staticmethod(_w.bartlett), staticmethod(_w.blackman), staticmethod(_w.hamming), staticmethod(_w.hann)
-    hanning = staticmethod(_w.hann)
-    kaiser, cosine, exponential, gaussian = staticmethod(_w.kaiser), staticmethod(_w.cosine), staticmethod(_w.exponential), staticmethod(_w.gaussian)
-    general_cosine, general_hamming, nuttall = staticmethod(_w.general_cosine), staticmethod(_w.general_hamming), staticmethod(_w.nuttall)
+    """Window functions from their formulas (ferrotorch-core/src/signal/windows.rs:35-170); ``sym=False`` gives the periodic form."""
+
+    @staticmethod
+    def general_cosine(M: int, *, a, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        w = torch.zeros_like(n)
+        for k, c in enumerate(a):
+            w = w + ((-1) ** k) * float(c) * torch.cos(2 * math.pi * k * n / L)
+        return w.to(dtype)
+
+    @staticmethod
+    def general_hamming(M: int, *, alpha: float = 0.54, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        return windows.general_cosine(M, a=[alpha, 1.0 - alpha], sym=sym, dtype=dtype, device=device)
+
+    @staticmethod
+    def hamming(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        return windows.general_hamming(M, alpha=0.54, sym=sym, dtype=dtype, device=device)
+
+    @staticmethod
+    def hann(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        return windows.general_hamming(M, alpha=0.5, sym=sym, dtype=dtype, device=device)
+
+    hanning = hann
+
+    @staticmethod
+    def blackman(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        return windows.general_cosine(M, a=[0.42, 0.5, 0.08], sym=sym, dtype=dtype, device=device)
+
+    @staticmethod
+    def nuttall(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        return windows.general_cosine(M, a=[0.3635819, 0.4891775, 0.1365995, 0.0106411], sym=sym, dtype=dtype, device=device)
+
+    @staticmethod
+    def bartlett(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        return (1.0 - (2.0 * n / L - 1.0).abs()).to(dtype)
+
+    @staticmethod
+    def cosine(M: int, *, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        return torch.sin(math.pi * (n + 0.5) / (L + 1.0)).to(dtype)
+
+    @staticmethod
+    def exponential(M: int, *, center: Optional[float] = None, tau: float = 1.0, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        if sym and center is not None:
+            raise InvalidArgument("a symmetric exponential window takes no centre")
+        if tau <= 0:
+            raise InvalidArgument("tau must be positive")
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        c = L / 2.0 if center is None else float(center)
+        return torch.exp(-(n - c).abs() / tau).to(dtype)
+
+    @staticmethod
+    def gaussian(M: int, *, std: float = 1.0, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        if std <= 0:
+            raise InvalidArgument("std must be positive")
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        return torch.exp(-0.5 * ((n - L / 2.0) / std) ** 2).to(dtype)
+
+    @staticmethod
+    def kaiser(M: int, *, beta: float = 12.0, sym: bool = True, dtype=None, device=None) -> torch.Tensor:
+        if beta < 0:
+            raise InvalidArgument("beta must be non-negative")
+        n, L, dtype = _win_n(M, sym, dtype, device)
+        if M == 1:
+            return torch.ones(1, dtype=dtype, device=device)
+        r = (2.0 * n / L - 1.0).clamp(-1.0, 1.0)
+        return (_i0(beta * torch.sqrt(1.0 - r * r)) / _i0(torch.tensor(float(beta), dtype=torch.float64, device=device))).to(dtype)
 
     @staticmethod
     def parzen(n: int) -> torch.Tensor:
@@ -146,7 +239,8 @@ class windows:
         return w.float()
 
     @staticmethod
-    def taylor(n: int, nbar: int = 4, sll: float = 30.0) -> torch.Tensor:
+    def taylor(n: int, nbar: int = 4, sll: float = 30.0, norm: bool = True) -> torch.Tensor:
+        """Taylor window with ``nbar`` nearly constant side lobes ``sll`` dB down; ``norm`` divides by the value at the centre (n - 1) / 2."""
         B = 10 ** (sll / 20)
         A = math.acosh(B) / math.pi
         s2 = nbar ** 2 / (A ** 2 + (nbar - 0.5) ** 2)
@@ -156,9 +250,14 @@ class windows:
             numer = (-1) ** (mi) * torch.prod(1 - m ** 2 / s2 / (A ** 2 + (ma - 0.5) ** 2))
             denom = 2 * torch.prod(torch.tensor([1 - m ** 2 / j ** 2 for j in ma if j != m], dtype=torch.float64))
             Fm[mi] = numer / denom
-        x = (torch.arange(n, dtype=torch.float64) - n / 2 + 0.5) / n
-        w = 1 + 2 * (Fm.view(-1, 1) * torch.cos(2 * math.pi * ma.view(-1, 1) * x.view(1, -1))).sum(0)
-        return (w / w.max()).float()
+
+        def W(pos: torch.Tensor) -> torch.Tensor:
+            x = (pos - n / 2 + 0.5) / n
+            return 1 + 2 * (Fm.view(-1, 1) * torch.cos(2 * math.pi * ma.view(-1, 1) * x.view(1, -1))).sum(0)
+        w = W(torch.arange(n, dtype=torch.float64))
+        if norm:
+            w = w / W(torch.tensor([(n - 1) / 2], dtype=torch.float64))
+        return w.float()
 
 
 # -- pruning -------------------------------------------------------------------------------------------------------------------------

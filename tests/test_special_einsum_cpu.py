@@ -133,3 +133,27 @@ def test_einops_patterns_match_the_einops_package():
         X.repeat(x, "b c h w -> b c h")
     with pytest.raises(Exception):
         X.reduce(x, "b c h w -> b c", "median")
+
+
+def test_window_functions_from_their_formulas():
+    """Every window against ``torch.signal.windows`` (symmetric and periodic, lengths 0, 1, 2 and up) and, where the substrate has none,
+    against scipy."""
+    sw = pytest.importorskip("scipy.signal.windows")
+    W, T = X.windows, torch.signal.windows
+    for M in (0, 1, 2, 7, 16, 65):
+        for sym in (True, False):
+            for name, kw in (("hann", {}), ("hamming", {}), ("blackman", {}), ("nuttall", {}), ("bartlett", {}), ("cosine", {}), ("gaussian", {"std": 2.5}),
+                             ("kaiser", {"beta": 8.6}), ("kaiser", {"beta": 0.0}), ("kaiser", {"beta": 40.0}), ("general_hamming", {"alpha": 0.6}),
+                             ("general_cosine", {"a": [0.5, 0.3, 0.2]}), ("exponential", {"tau": 3.0})):
+                got, want = getattr(W, name)(M, sym=sym, dtype=torch.float64, **kw), getattr(T, name)(M, sym=sym, dtype=torch.float64, **kw)
+                assert got.shape == want.shape and torch.allclose(got, want, atol=1e-12), (name, M, sym)
+    assert torch.allclose(W.exponential(9, center=2.0, tau=2.0, sym=False, dtype=torch.float64), T.exponential(9, center=2.0, tau=2.0, sym=False, dtype=torch.float64))
+    assert W.hann(8).dtype == torch.float32 and W.hanning is W.hann and W.hann is not T.hann
+    for M in (15, 16):
+        assert torch.allclose(W.parzen(M).double(), torch.tensor(sw.parzen(M)), atol=1e-6)
+        assert torch.allclose(W.tukey(M, 0.4).double(), torch.tensor(sw.tukey(M, 0.4)), atol=1e-6)
+        assert torch.allclose(W.taylor(M).double(), torch.tensor(sw.taylor(M)), atol=1e-6)
+        assert torch.allclose(W.taylor(M, 5, 40.0, False).double(), torch.tensor(sw.taylor(M, 5, 40, norm=False)), atol=1e-6)
+    for bad in (lambda: W.gaussian(8, std=0.0), lambda: W.exponential(8, center=1.0), lambda: W.kaiser(8, beta=-1.0), lambda: W.hann(-1)):
+        with pytest.raises(Exception):
+            bad()
