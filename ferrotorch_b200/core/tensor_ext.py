@@ -19,6 +19,7 @@ import torch
 from ..errors import InvalidArgument, ShapeMismatch
 from . import einops_impl as _einops_impl
 from . import einsum_impl as _einsum_impl
+from . import fft_impl as _fft_impl
 from . import special_fns as _sf
 
 L = torch.linalg
@@ -65,8 +66,9 @@ class linalg:  # namespace mirroring ferrotorch_core::linalg
 
 # -- fft ------------------------------------------------------------------------------------------------------------------------
 class fft:
+    """Written out in ``core/fft_impl.py``: radix-2 butterflies for power-of-two lengths, Bluestein's chirp-z form for the others."""
     for _n in ("fft", "ifft", "rfft", "irfft", "fft2", "ifft2", "fftn", "ifftn", "rfftn", "irfftn", "hfft", "ihfft", "fftfreq", "rfftfreq", "fftshift", "ifftshift"):
-        locals()[_n] = staticmethod(getattr(torch.fft, _n))
+        locals()[_n] = staticmethod(getattr(_fft_impl, _n))
     del _n
 
 

@@ -157,3 +157,72 @@ def test_window_functions_from_their_formulas():
     for bad in (lambda: W.gaussian(8, std=0.0), lambda: W.exponential(8, center=1.0), lambda: W.kaiser(8, beta=-1.0), lambda: W.hann(-1)):
         with pytest.raises(Exception):
             bad()
+
+
+def _same(a, b, tol=1e-9):
+    assert a.shape == b.shape and a.dtype == b.dtype, (a.shape, b.shape, a.dtype, b.dtype)
+    assert torch.allclose(a, b, atol=tol, rtol=tol), (a - b).abs().max()
+
+
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 7, 8, 12, 16, 17, 30, 64, 100, 127, 128, 243])
+def test_one_dimensional_transforms_match_the_library(n):
+    """Power-of-two lengths take the radix-2 butterflies, all others Bluestein's form; complex, real, half-spectrum and Hermitian variants,
+    every normalisation, padding and trimming."""
+    F, T = X.fft, torch.fft
+    torch.manual_seed(n)
+    x, r = torch.randn(3, n, dtype=torch.complex128), torch.randn(3, n, dtype=torch.float64)
+    for norm in (None, "ortho", "forward"):
+        _same(F.fft(x, norm=norm), T.fft(x, norm=norm))
+        _same(F.ifft(x, norm=norm), T.ifft(x, norm=norm))
+        _same(F.fft(r, norm=norm), T.fft(r, norm=norm))
+        _same(F.rfft(r, norm=norm), T.rfft(r, norm=norm))
+        _same(F.ihfft(r, norm=norm), T.ihfft(r, norm=norm))
+        h = torch.randn(3, n // 2 + 1, dtype=torch.complex128)
+        for m in (None, n, n + 1, max(1, n - 1)):
+            if m is None and n // 2 + 1 < 2:
+                continue
+            _same(F.irfft(h, m, norm=norm), T.irfft(h, m, norm=norm))
+            _same(F.hfft(h, m, norm=norm), T.hfft(h, m, norm=norm))
+    for m in (max(1, n - 2), n + 3):
+        _same(F.fft(x, m), T.fft(x, m))
+        _same(F.rfft(r, m), T.rfft(r, m))
+    _same(F.fft(x.t(), dim=0), T.fft(x.t(), dim=0))
+    assert F.fft is not T.fft
+
+
+def test_multi_dimensional_transforms_grids_shifts_and_gradients():
+    F, T = X.fft, torch.fft
+    torch.manual_seed(0)
+    y, yr = torch.randn(2, 6, 5, 8, dtype=torch.complex128), torch.randn(2, 6, 5, 8, dtype=torch.float64)
+    for ours, theirs in ((F.fft2, T.fft2), (F.ifft2, T.ifft2), (F.fftn, T.fftn), (F.ifftn, T.ifftn)):
+        _same(ours(y), theirs(y))
+    _same(F.fftn(y, s=(4, 9), dim=(1, 3)), T.fftn(y, s=(4, 9), dim=(1, 3)))
+    _same(F.fftn(y, dim=(0, 2), norm="ortho"), T.fftn(y, dim=(0, 2), norm="ortho"))
+    _same(F.fft2(yr), T.fft2(yr))
+    _same(F.rfftn(yr), T.rfftn(yr))
+    _same(F.rfftn(yr, s=(7, 6)), T.rfftn(yr, s=(7, 6)))
+    _same(F.rfftn(yr, dim=(1, 2)), T.rfftn(yr, dim=(1, 2)))
+    z = T.rfftn(yr)
+    _same(F.irfftn(z), T.irfftn(z))
+    _same(F.irfftn(z, s=(5, 8)), T.irfftn(z, s=(5, 8)))
+    _same(F.irfftn(z, s=(5, 9), dim=(2, 3)), T.irfftn(z, s=(5, 9), dim=(2, 3)))
+    for n in (1, 4, 7, 8):
+        _same(F.fftfreq(n, 0.5), T.fftfreq(n, 0.5), 1e-7)
+        _same(F.rfftfreq(n, 0.25), T.rfftfreq(n, 0.25), 1e-7)
+    _same(F.fftshift(yr), T.fftshift(yr))
+    _same(F.ifftshift(yr, dim=(1, 3)), T.ifftshift(yr, dim=(1, 3)))
+    _same(F.fftshift(yr, dim=2), T.fftshift(yr, dim=2))
+    x32 = torch.randn(4, 100)
+    _same(F.rfft(x32), T.rfft(x32), 1e-4)
+    _same(F.fft(x32.to(torch.complex64)), T.fft(x32.to(torch.complex64)), 1e-4)
+    long = torch.randn(10007, dtype=torch.complex128)                     # a prime length: the chirp phases stay accurate
+    assert (F.fft(long) - T.fft(long)).abs().max() < 1e-10
+    a, w = torch.randn(2, 12, dtype=torch.float64, requires_grad=True), torch.randn(2, 7, dtype=torch.complex128)
+    _same(*[torch.autograd.grad((f(a) * w).abs().sum(), a)[0] for f in (F.rfft, T.rfft)])
+    c = torch.randn(2, 9, dtype=torch.complex128, requires_grad=True)
+    _same(*[torch.autograd.grad(f(c).abs().sum(), c)[0] for f in (F.ifft, T.ifft)])
+    hh = torch.randn(2, 7, dtype=torch.complex128, requires_grad=True)
+    _same(*[torch.autograd.grad((f(hh, 12) ** 2).sum(), hh)[0] for f in (F.irfft, T.irfft)])
+    for bad in (lambda: F.fft(torch.randn(4), norm="unitary"), lambda: F.rfft(y), lambda: F.fft(torch.randn(4), 0), lambda: F.fftn(y, dim=(1, 1)), lambda: F.fftfreq(0)):
+        with pytest.raises(Exception):
+            bad()
