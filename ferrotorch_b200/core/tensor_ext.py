@@ -20,48 +20,23 @@ from ..errors import InvalidArgument, ShapeMismatch
 from . import einops_impl as _einops_impl
 from . import einsum_impl as _einsum_impl
 from . import fft_impl as _fft_impl
+from . import linalg_impl as _la
 from . import special_fns as _sf
 
-L = torch.linalg
 
 
 # -- linalg ---------------------------------------------------------------------------------------------------------------------
-class linalg:  # namespace mirroring ferrotorch_core::linalg
-    svd = staticmethod(lambda a, full_matrices=False: L.svd(a, full_matrices=full_matrices))
-    solve = staticmethod(L.solve)
-    det = staticmethod(L.det)
-    inv = staticmethod(L.inv)
-    qr = staticmethod(L.qr)
-    cholesky = staticmethod(L.cholesky)
-    matrix_norm = staticmethod(L.matrix_norm)
-    pinv = staticmethod(L.pinv)
-    eigh = staticmethod(L.eigh)
-    eigvalsh = staticmethod(L.eigvalsh)
-    eig = staticmethod(L.eig)
-    eigvals = staticmethod(L.eigvals)
-    lu = staticmethod(L.lu)
-    lu_factor = staticmethod(L.lu_factor)
-    svdvals = staticmethod(L.svdvals)
-    lstsq = staticmethod(lambda a, b: L.lstsq(a, b))
-    lstsq_solve = staticmethod(lambda a, b: L.lstsq(a, b).solution)
-    matrix_power = staticmethod(L.matrix_power)
-    tensorsolve = staticmethod(L.tensorsolve)
-    tensorinv = staticmethod(L.tensorinv)
-    vector_norm = staticmethod(L.vector_norm)
-    slogdet = staticmethod(L.slogdet)
-    matrix_rank = staticmethod(L.matrix_rank)
-    cond = staticmethod(L.cond)
-    cross = staticmethod(L.cross)
-    multi_dot = staticmethod(L.multi_dot)
-    diagonal = staticmethod(L.diagonal)
-    solve_triangular = staticmethod(lambda a, b, upper=True, left=True, unitriangular=False: L.solve_triangular(a, b, upper=upper, left=left, unitriangular=unitriangular))
-    ldl_factor = staticmethod(L.ldl_factor)
-    ldl_solve = staticmethod(L.ldl_solve)
-    householder_product = staticmethod(L.householder_product)
-    matrix_exp = staticmethod(L.matrix_exp)
-    cholesky_ex = staticmethod(L.cholesky_ex)
-    inv_ex = staticmethod(L.inv_ex)
-    solve_ex = staticmethod(L.solve_ex)
+class linalg:
+    """``core/linalg_impl.py``: factorisations in the host runtime library with the derivative formulas beside them, the rest composed from
+    them (ferrotorch_core::linalg). CUDA / complex / half inputs and the general eigenproblem go to the substrate's library call."""
+    svd = staticmethod(lambda a, full_matrices=False: _la.svd(a, full_matrices=full_matrices))
+    lstsq = staticmethod(lambda a, b, rcond=None: _la.lstsq(a, b, rcond))
+    for _n in ("solve", "det", "inv", "qr", "cholesky", "matrix_norm", "pinv", "eigh", "eigvalsh", "eig", "eigvals", "lu", "lu_factor", "svdvals", "lstsq_solve",
+               "matrix_power", "tensorsolve", "tensorinv", "vector_norm", "slogdet", "matrix_rank", "cond", "cross", "multi_dot", "diagonal", "solve_triangular",
+               "ldl_factor", "ldl_solve", "householder_product", "matrix_exp", "cholesky_ex", "inv_ex", "solve_ex"):
+        locals()[_n] = staticmethod(getattr(_la, _n))
+    del _n
+    LinAlgError = _la.LinAlgError
 
 
 # -- fft ------------------------------------------------------------------------------------------------------------------------

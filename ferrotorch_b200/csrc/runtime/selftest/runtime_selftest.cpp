@@ -5,6 +5,7 @@
 // The reference has no sanitizer configuration (its ranks-as-threads pattern is ferrotorch-distributed/src/fsdp.rs:946-976 and
 // tests/conformance_distributed.rs:615-680); this driver is that pattern under ThreadSanitizer / AddressSanitizer.
 #include <atomic>
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -51,6 +52,13 @@ void* ft_json_grammar_create(const int32_t* kind, const int32_t* edge_first, int
 void ft_json_grammar_destroy(void* h);
 int ft_json_grammar_check(void* h, const uint8_t* text, int64_t n, int* is_complete);
 int64_t ft_json_grammar_mask(void* h, const uint8_t* text, int64_t n, int64_t eos_id, uint8_t* allowed, int nthreads);
+int ft_la_cholesky(double* a, int64_t batch, int64_t n, int32_t* info);
+int ft_la_lu(double* a, int64_t batch, int64_t m, int64_t n, int32_t* piv, int32_t* info);
+int ft_la_lu_solve(const double* lu, const int32_t* piv, double* bmat, int64_t batch, int64_t n, int64_t k, int trans);
+int ft_la_trsm(const double* t, double* bmat, int64_t batch, int64_t n, int64_t k, int upper, int trans, int unit);
+int ft_la_qr(const double* a, double* q, double* r, int64_t batch, int64_t m, int64_t n, int complete);
+int ft_la_eigh(const double* a, double* w, double* v, int64_t batch, int64_t n, int lower);
+int ft_la_svd(const double* a, double* u, double* s, double* vt, int64_t batch, int64_t m, int64_t n);
 int64_t ft_bpe_encode_texts(void* h, int kind, const uint8_t* bytes, const int64_t* off, int64_t n_texts, int32_t* out, int64_t out_cap, int64_t* out_off,
                             int nthreads);
 }
@@ -264,10 +272,86 @@ static void test_grammar() {
   ft_json_grammar_destroy(h);
 }
 
+// A batch large enough for the threaded path: every factorisation must reproduce its input (A = L L^T, P A = L U and A x = b, A = Q R,
+// A = V diag(w) V^T, A = U diag(s) V^T) on each matrix of the batch.
+static void test_linalg() {
+  const int64_t batch = 64, n = 24, m = 30;
+  uint64_t seed = 7;
+  auto rnd = [&]() { seed = seed * 6364136223846793005ull + 1442695040888963407ull; return (double)((seed >> 33) % 2001) / 1000.0 - 1.0; };
+  std::vector<double> a((size_t)(batch * n * n)), spd(a.size()), rect((size_t)(batch * m * n));
+  for (auto& x : a) x = rnd();
+  for (auto& x : rect) x = rnd();
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t j = 0; j < n; j++) {
+        double s = i == j ? (double)n : 0.0;
+        for (int64_t k = 0; k < n; k++) s += a[(size_t)(b * n * n + i * n + k)] * a[(size_t)(b * n * n + j * n + k)];
+        spd[(size_t)(b * n * n + i * n + j)] = s;
+      }
+  auto maxerr = [](const std::vector<double>& x, const std::vector<double>& y) { double e = 0; for (size_t i = 0; i < x.size(); i++) e = std::max(e, std::fabs(x[i] - y[i])); return e; };
+  std::vector<int32_t> info((size_t)batch), piv((size_t)(batch * n));
+  std::vector<double> l = spd, rec(spd.size());
+  CHECK(ft_la_cholesky(l.data(), batch, n, info.data()) == 0);
+  for (int64_t b = 0; b < batch; b++) {
+    CHECK(info[(size_t)b] == 0);
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t j = 0; j < n; j++) {
+        double s = 0;
+        for (int64_t k = 0; k < n; k++) s += l[(size_t)(b * n * n + i * n + k)] * l[(size_t)(b * n * n + j * n + k)];
+        rec[(size_t)(b * n * n + i * n + j)] = s;
+      }
+  }
+  CHECK(maxerr(rec, spd) < 1e-9);
+  std::vector<double> lu = a, rhs((size_t)(batch * n * 2)), x;
+  for (auto& v : rhs) v = rnd();
+  x = rhs;
+  CHECK(ft_la_lu(lu.data(), batch, n, n, piv.data(), info.data()) == 0);
+  CHECK(ft_la_lu_solve(lu.data(), piv.data(), x.data(), batch, n, 2, 0) == 0);
+  std::vector<double> ax(rhs.size(), 0.0);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t c = 0; c < 2; c++)
+        for (int64_t k = 0; k < n; k++) ax[(size_t)(b * n * 2 + i * 2 + c)] += a[(size_t)(b * n * n + i * n + k)] * x[(size_t)(b * n * 2 + k * 2 + c)];
+  CHECK(maxerr(ax, rhs) < 1e-8);
+  std::vector<double> t = l, y = rhs;                       // L z = rhs, then check L z
+  CHECK(ft_la_trsm(t.data(), y.data(), batch, n, 2, 0, 0, 0) == 0);
+  std::fill(ax.begin(), ax.end(), 0.0);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t c = 0; c < 2; c++)
+        for (int64_t k = 0; k <= i; k++) ax[(size_t)(b * n * 2 + i * 2 + c)] += l[(size_t)(b * n * n + i * n + k)] * y[(size_t)(b * n * 2 + k * 2 + c)];
+  CHECK(maxerr(ax, rhs) < 1e-9);
+  std::vector<double> q((size_t)(batch * m * n)), r((size_t)(batch * n * n)), qr(rect.size(), 0.0);
+  CHECK(ft_la_qr(rect.data(), q.data(), r.data(), batch, m, n, 0) == 0);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < m; i++)
+      for (int64_t j = 0; j < n; j++)
+        for (int64_t k = 0; k < n; k++) qr[(size_t)(b * m * n + i * n + j)] += q[(size_t)(b * m * n + i * n + k)] * r[(size_t)(b * n * n + k * n + j)];
+  CHECK(maxerr(qr, rect) < 1e-10);
+  std::vector<double> w((size_t)(batch * n)), v((size_t)(batch * n * n));
+  CHECK(ft_la_eigh(spd.data(), w.data(), v.data(), batch, n, 1) > 0);
+  std::fill(rec.begin(), rec.end(), 0.0);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < n; i++)
+      for (int64_t j = 0; j < n; j++)
+        for (int64_t k = 0; k < n; k++) rec[(size_t)(b * n * n + i * n + j)] += v[(size_t)(b * n * n + i * n + k)] * w[(size_t)(b * n + k)] * v[(size_t)(b * n * n + j * n + k)];
+  CHECK(maxerr(rec, spd) < 1e-8);
+  std::vector<double> u((size_t)(batch * m * n)), sv((size_t)(batch * n)), vt((size_t)(batch * n * n)), usv(rect.size(), 0.0);
+  CHECK(ft_la_svd(rect.data(), u.data(), sv.data(), vt.data(), batch, m, n) > 0);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t i = 0; i < m; i++)
+      for (int64_t j = 0; j < n; j++)
+        for (int64_t k = 0; k < n; k++) usv[(size_t)(b * m * n + i * n + j)] += u[(size_t)(b * m * n + i * n + k)] * sv[(size_t)(b * n + k)] * vt[(size_t)(b * n * n + k * n + j)];
+  CHECK(maxerr(usv, rect) < 1e-10);
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t k = 0; k + 1 < n; k++) CHECK(sv[(size_t)(b * n + k)] >= sv[(size_t)(b * n + k + 1)]);
+}
+
 int main() {
   test_loader_and_planner();
   test_tokenizer();
   test_grammar();
+  test_linalg();
   test_simulated();
   test_tcp(0);
   test_tcp(1);
