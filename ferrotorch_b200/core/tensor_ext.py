@@ -390,71 +390,7 @@ class HistogramObserver:
 
 
 # -- sparse --------------------------------------------------------------------------------------------------------------------------
-class CooTensor:
-    def __init__(self, indices: torch.Tensor, values: torch.Tensor, shape):
-        self.t = torch.sparse_coo_tensor(indices, values, tuple(shape)).coalesce()
-
-    @staticmethod
-    def from_dense(d: torch.Tensor) -> "CooTensor":
-        s = d.to_sparse()
-        return CooTensor(s.indices(), s.values(), d.shape)
-
-    def to_dense(self):
-        return self.t.to_dense()
-
-    def nnz(self) -> int:
-        return self.t._nnz()
-
-    def matmul(self, dense: torch.Tensor) -> torch.Tensor:
-        return torch.sparse.mm(self.t, dense)
-
-    def to_csr(self) -> "CsrTensor":
-        return CsrTensor(self.t.to_sparse_csr())
-
-
-class CsrTensor:
-    def __init__(self, t: torch.Tensor):
-        self.t = t
-
-    @staticmethod
-    def from_dense(d):
-        return CsrTensor(d.to_sparse_csr())
-
-    def to_dense(self):
-        return self.t.to_dense()
-
-    def crow_indices(self):
-        return self.t.crow_indices()
-
-    def col_indices(self):
-        return self.t.col_indices()
-
-    def values(self):
-        return self.t.values()
-
-    def matmul(self, dense):
-        return self.t @ dense
-
-    def to_csc(self) -> "CscTensor":
-        return CscTensor(self.t.to_sparse_csc())
-
-
-class CscTensor:
-    def __init__(self, t):
-        self.t = t
-
-    @staticmethod
-    def from_dense(d):
-        return CscTensor(d.to_sparse_csc())
-
-    def to_dense(self):
-        return self.t.to_dense()
-
-    def matmul(self, dense):
-        return self.t.to_dense() @ dense
-
-
-SparseTensor = CooTensor
+from .sparse_impl import CooTensor, CscTensor, CsrTensor, SparseTensor  # noqa: E402  (own storage and algorithms: core/sparse_impl.py)
 
 
 class SemiStructuredSparseTensor:
