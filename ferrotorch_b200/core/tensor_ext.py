@@ -463,10 +463,10 @@ class PackedNestedTensor:
 
 def nested_scaled_dot_product_attention(q: NestedTensor, k: NestedTensor, v: NestedTensor, causal: bool = False) -> NestedTensor:
     """Per-sequence attention on ``[len, heads, dim]`` entries (no padding waste)."""
+    from ..nn.functional import scaled_dot_product_attention as sdpa      # this package's attention (the tcgen05 kernels for bf16 on a device)
     out = []
     for qi, ki, vi in zip(q.tensors, k.tensors, v.tensors):
-        o = torch.nn.functional.scaled_dot_product_attention(qi.transpose(0, 1).unsqueeze(0), ki.transpose(0, 1).unsqueeze(0),
-                                                             vi.transpose(0, 1).unsqueeze(0), is_causal=causal)
+        o = sdpa(qi.transpose(0, 1).unsqueeze(0), ki.transpose(0, 1).unsqueeze(0), vi.transpose(0, 1).unsqueeze(0), is_causal=causal)
         out.append(o.squeeze(0).transpose(0, 1))
     return NestedTensor(out)
 
