@@ -6,9 +6,10 @@
 //                    are kept per consuming edge and summed in edge order when a node becomes ready, so the serial engine and the parallel one
 //                    (worker threads over the ready queue) give identical bits; tensor hooks (may rewrite a gradient) run before accumulation
 //                    into a leaf, post-accumulate hooks after it (what DDP uses to launch a bucket's all-reduce)
-//   operations       add / sub / mul (row-broadcast of a vector), scale, matmul, transpose, relu, tanh, sigmoid, sum, mean, linear,
-//                    cross-entropy on logits, mse
-//   ft::Sgd          momentum / dampening / nesterov / weight decay, same update rule as the device kernel
+//   operations       add / sub / mul / div (row-broadcast of a vector), scale, matmul, transpose, reshape, relu, tanh, sigmoid and the
+//                    element-wise family (exp, log, sqrt, gelu, silu, leaky relu, power, abs, square, reciprocal), sum / mean over everything or
+//                    along one dimension, softmax / log-softmax, linear, conv2d (patch matrix x GEMM), max_pool2d, cross-entropy on logits
+//   ft::Sgd, ft::Adam momentum / dampening / nesterov / weight decay; Adam and AdamW (decoupled decay): same update rules as the device kernels
 //
 // Everything is exported through a small C ABI (opaque handles) for the Python binding in ferrotorch_b200/native.py.
 //
@@ -473,6 +474,343 @@ struct Sgd {
   }
 };
 
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// more operations: element-wise family, division, reshape, reductions along one dimension, softmax, convolution, pooling
+// ---------------------------------------------------------------------------------------------------------------------------------------
+enum class Un { Exp = 0, Log = 1, Sqrt = 2, Gelu = 3, Silu = 4, LeakyRelu = 5, Pow = 6, Abs = 7, Square = 8, Reciprocal = 9 };
+static inline float un_fwd(Un k, float x, float p) {
+  switch (k) {
+    case Un::Exp: return std::exp(x);
+    case Un::Log: return std::log(x);
+    case Un::Sqrt: return std::sqrt(x);
+    case Un::Gelu: return 0.5f * x * (1.f + std::erf(x * 0.70710678118654752f));
+    case Un::Silu: return x / (1.f + std::exp(-x));
+    case Un::LeakyRelu: return x > 0.f ? x : p * x;
+    case Un::Pow: return std::pow(x, p);
+    case Un::Abs: return std::fabs(x);
+    case Un::Square: return x * x;
+    case Un::Reciprocal: return 1.f / x;
+  }
+  return 0.f;
+}
+static inline float un_bwd(Un k, float x, float y, float p) {      // d out / d in from the input x and the output y
+  switch (k) {
+    case Un::Exp: return y;
+    case Un::Log: return 1.f / x;
+    case Un::Sqrt: return 0.5f / y;
+    case Un::Gelu: return 0.5f * (1.f + std::erf(x * 0.70710678118654752f)) + x * 0.3989422804014327f * std::exp(-0.5f * x * x);
+    case Un::Silu: { const float sg = 1.f / (1.f + std::exp(-x)); return sg * (1.f + x * (1.f - sg)); }
+    case Un::LeakyRelu: return x > 0.f ? 1.f : p;
+    case Un::Pow: return p * std::pow(x, p - 1.f);
+    case Un::Abs: return x > 0.f ? 1.f : (x < 0.f ? -1.f : 0.f);
+    case Un::Square: return 2.f * x;
+    case Un::Reciprocal: return -y * y;
+  }
+  return 0.f;
+}
+struct UnaryNode : Node {
+  Un k; float p; Tensor x, y;
+  UnaryNode(Un kk, float pp, Tensor in, Tensor out) : k(kk), p(pp), x(std::move(in)), y(std::move(out)) { name = "unary"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(gc->shape);
+    for (int64_t i = 0; i < gc->numel(); i++) o->data()[i] = gc->data()[i] * un_bwd(k, x->data()[i], y->data()[i], p);
+    return {o};
+  }
+};
+static Tensor unary(Un k, const Tensor& a0, float p) {
+  Tensor a = contiguous(a0), o = make(a->shape);
+  for (int64_t i = 0; i < a->numel(); i++) o->data()[i] = un_fwd(k, a->data()[i], p);
+  attach<UnaryNode>(o, {a0}, k, p, a, o);
+  return o;
+}
+
+// a / b with the row-broadcast rule of the other binary operations
+struct DivNode : Node {
+  Tensor a, b;
+  DivNode(Tensor x, Tensor y) : a(std::move(x)), b(std::move(y)) { name = "div"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), ga = make(a->shape), gb = make(a->shape);
+    const int64_t n = gc->numel(), nb = b->numel();
+    for (int64_t i = 0; i < n; i++) {
+      const float d = b->data()[i % nb];
+      ga->data()[i] = gc->data()[i] / d;
+      gb->data()[i] = -gc->data()[i] * a->data()[i] / (d * d);
+    }
+    return {ga, reduce_to(gb, b->shape)};
+  }
+};
+static Tensor divide(const Tensor& a0, const Tensor& b0) {
+  Tensor a = contiguous(a0), b = contiguous(b0);
+  const int64_t n = a->numel(), nb = b->numel();
+  if (nb == 0 || n % nb || (nb != n && (b->shape.size() != 1 || a->shape.back() != b->shape[0]))) { g_last_error = "div: shapes do not match or broadcast"; return nullptr; }
+  Tensor o = make(a->shape);
+  for (int64_t i = 0; i < n; i++) o->data()[i] = a->data()[i] / b->data()[i % nb];
+  attach<DivNode>(o, {a0, b0}, a, b);
+  return o;
+}
+
+static Tensor reshape(const Tensor& a0, const std::vector<int64_t>& shape);
+struct ReshapeNode : Node {
+  std::vector<int64_t> from;
+  explicit ReshapeNode(std::vector<int64_t> s) : from(std::move(s)) { name = "reshape"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    const bool prev = g_grad_enabled;
+    g_grad_enabled = false;
+    Tensor o = reshape(g, from);
+    g_grad_enabled = prev;
+    return {o};
+  }
+};
+static Tensor reshape(const Tensor& a0, const std::vector<int64_t>& shape_in) {       // a view of the (contiguous copy of the) storage; one -1 is inferred
+  std::vector<int64_t> shape = shape_in;
+  int64_t known = 1, infer = -1;
+  for (size_t i = 0; i < shape.size(); i++) {
+    if (shape[i] == -1) { if (infer >= 0) { g_last_error = "reshape: only one dimension can be inferred"; return nullptr; } infer = (int64_t)i; }
+    else if (shape[i] < 0) { g_last_error = "reshape: negative dimension"; return nullptr; }
+    else known *= shape[i];
+  }
+  if (infer >= 0) { if (known == 0 || a0->numel() % known) { g_last_error = "reshape: cannot infer the dimension"; return nullptr; } shape[(size_t)infer] = a0->numel() / known; known *= shape[(size_t)infer]; }
+  if (known != a0->numel()) { g_last_error = "reshape: element counts differ"; return nullptr; }
+  Tensor a = contiguous(a0);
+  auto t = std::make_shared<TensorImpl>();
+  t->storage = a->storage;
+  t->offset = a->offset;
+  t->shape = shape;
+  t->strides = row_major(shape);
+  attach<ReshapeNode>(t, {a0}, a0->shape);
+  return t;
+}
+
+// sum (or mean) along one dimension: the tensor is seen as [outer, len, inner]
+struct SumDimNode : Node {
+  std::vector<int64_t> shape; int64_t outer, len, inner; float w;
+  SumDimNode(std::vector<int64_t> s, int64_t o, int64_t l, int64_t i, float ww) : shape(std::move(s)), outer(o), len(l), inner(i), w(ww) { name = "sum_dim"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(shape);
+    for (int64_t a = 0; a < outer; a++)
+      for (int64_t l = 0; l < len; l++)
+        for (int64_t i = 0; i < inner; i++) o->data()[(a * len + l) * inner + i] = gc->data()[a * inner + i] * w;
+    return {o};
+  }
+};
+static Tensor sum_dim(const Tensor& a0, int dim, bool keepdim, bool mean) {
+  const int nd = (int)a0->shape.size();
+  if (dim < 0) dim += nd;
+  if (dim < 0 || dim >= nd) { g_last_error = "sum: dimension out of range"; return nullptr; }
+  Tensor a = contiguous(a0);
+  int64_t outer = 1, inner = 1;
+  const int64_t len = a->shape[(size_t)dim];
+  for (int i = 0; i < dim; i++) outer *= a->shape[(size_t)i];
+  for (int i = dim + 1; i < nd; i++) inner *= a->shape[(size_t)i];
+  std::vector<int64_t> os;
+  for (int i = 0; i < nd; i++) { if (i != dim) os.push_back(a->shape[(size_t)i]); else if (keepdim) os.push_back(1); }
+  Tensor o = make(os);
+  const float w = mean ? 1.f / (float)std::max<int64_t>(len, 1) : 1.f;
+  for (int64_t x = 0; x < outer; x++)
+    for (int64_t i = 0; i < inner; i++) {
+      double s = 0;
+      for (int64_t l = 0; l < len; l++) s += a->data()[(x * len + l) * inner + i];
+      o->data()[x * inner + i] = (float)(s * w);
+    }
+  attach<SumDimNode>(o, {a0}, a->shape, outer, len, inner, w);
+  return o;
+}
+
+// softmax / log-softmax over the last dimension
+struct SoftmaxNode : Node {
+  Tensor y; bool log;
+  SoftmaxNode(Tensor out, bool l) : y(std::move(out)), log(l) { name = "softmax"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(gc->shape);
+    const int64_t C = y->shape.back(), R = y->numel() / std::max<int64_t>(C, 1);
+    for (int64_t r = 0; r < R; r++) {
+      const float* yy = y->data() + r * C;
+      const float* gg = gc->data() + r * C;
+      double dot = 0;
+      for (int64_t c = 0; c < C; c++) dot += log ? gg[c] : gg[c] * yy[c];
+      for (int64_t c = 0; c < C; c++) o->data()[r * C + c] = log ? gg[c] - std::exp(yy[c]) * (float)dot : yy[c] * (gg[c] - (float)dot);
+    }
+    return {o};
+  }
+};
+static Tensor softmax(const Tensor& a0, bool log) {
+  if (a0->shape.empty()) { g_last_error = "softmax needs at least one dimension"; return nullptr; }
+  Tensor a = contiguous(a0), o = make(a->shape);
+  const int64_t C = a->shape.back(), R = a->numel() / std::max<int64_t>(C, 1);
+  for (int64_t r = 0; r < R; r++) {
+    const float* x = a->data() + r * C;
+    float m = x[0];
+    for (int64_t c = 1; c < C; c++) m = std::max(m, x[c]);
+    double z = 0;
+    for (int64_t c = 0; c < C; c++) z += std::exp((double)x[c] - m);
+    const double lz = std::log(z) + m;
+    for (int64_t c = 0; c < C; c++) o->data()[r * C + c] = log ? (float)(x[c] - lz) : (float)std::exp((double)x[c] - lz);
+  }
+  attach<SoftmaxNode>(o, {a0}, o, log);
+  return o;
+}
+
+// 2-d convolution (NCHW, weight [O, C, kh, kw]) as patch matrix x GEMM, image by image
+struct ConvGeom { int64_t N, C, H, W, O, kh, kw, sh, sw, ph, pw, Ho, Wo; };
+static void im2col(const float* x, const ConvGeom& g, float* col) {          // col [C*kh*kw, Ho*Wo]
+  for (int64_t c = 0; c < g.C; c++)
+    for (int64_t i = 0; i < g.kh; i++)
+      for (int64_t j = 0; j < g.kw; j++) {
+        float* row = col + ((c * g.kh + i) * g.kw + j) * g.Ho * g.Wo;
+        for (int64_t oy = 0; oy < g.Ho; oy++) {
+          const int64_t iy = oy * g.sh - g.ph + i;
+          for (int64_t ox = 0; ox < g.Wo; ox++) {
+            const int64_t ix = ox * g.sw - g.pw + j;
+            row[oy * g.Wo + ox] = (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) ? x[(c * g.H + iy) * g.W + ix] : 0.f;
+          }
+        }
+      }
+}
+static void col2im_add(const float* col, const ConvGeom& g, float* x) {
+  for (int64_t c = 0; c < g.C; c++)
+    for (int64_t i = 0; i < g.kh; i++)
+      for (int64_t j = 0; j < g.kw; j++) {
+        const float* row = col + ((c * g.kh + i) * g.kw + j) * g.Ho * g.Wo;
+        for (int64_t oy = 0; oy < g.Ho; oy++) {
+          const int64_t iy = oy * g.sh - g.ph + i;
+          if (iy < 0 || iy >= g.H) continue;
+          for (int64_t ox = 0; ox < g.Wo; ox++) {
+            const int64_t ix = ox * g.sw - g.pw + j;
+            if (ix >= 0 && ix < g.W) x[(c * g.H + iy) * g.W + ix] += row[oy * g.Wo + ox];
+          }
+        }
+      }
+}
+struct Conv2dNode : Node {
+  Tensor x, w; ConvGeom g; bool has_bias;
+  Conv2dNode(Tensor xx, Tensor ww, ConvGeom gg, bool hb) : x(std::move(xx)), w(std::move(ww)), g(gg), has_bias(hb) { name = "conv2d"; }
+  std::vector<Tensor> backward(const Tensor& gout) override {
+    Tensor gy = contiguous(gout);
+    const int64_t K = g.C * g.kh * g.kw, P = g.Ho * g.Wo;
+    Tensor gx = inputs[0] ? make(x->shape) : nullptr, gw = inputs[1] ? make(w->shape) : nullptr, gb = (has_bias && inputs[2]) ? make({g.O}) : nullptr;
+    std::vector<float> col((size_t)(K * P)), tmp((size_t)std::max(K * P, g.O * K)), wt((size_t)(K * g.O));
+    for (int64_t o = 0; o < g.O; o++)
+      for (int64_t k = 0; k < K; k++) wt[(size_t)(k * g.O + o)] = w->data()[o * K + k];
+    for (int64_t n = 0; n < g.N; n++) {
+      const float* gyn = gy->data() + n * g.O * P;
+      if (gw) {                                          // dW += dY [O, P] x col^T [P, K]
+        im2col(x->data() + n * g.C * g.H * g.W, g, col.data());
+        for (int64_t o = 0; o < g.O; o++)
+          for (int64_t k = 0; k < K; k++) {
+            const float* a = gyn + o * P;
+            const float* b = col.data() + k * P;
+            float sacc = 0.f;
+            for (int64_t q = 0; q < P; q++) sacc += a[q] * b[q];
+            gw->data()[o * K + k] += sacc;
+          }
+      }
+      if (gx) {                                          // dcol [K, P] = W^T [K, O] x dY [O, P], scattered back
+        gemm_raw(wt.data(), gyn, tmp.data(), K, P, g.O);
+        col2im_add(tmp.data(), g, gx->data() + n * g.C * g.H * g.W);
+      }
+      if (gb)
+        for (int64_t o = 0; o < g.O; o++) {
+          float sacc = 0.f;
+          for (int64_t q = 0; q < P; q++) sacc += gyn[o * P + q];
+          gb->data()[o] += sacc;
+        }
+    }
+    std::vector<Tensor> out{gx, gw};
+    if (has_bias) out.push_back(gb);
+    return out;
+  }
+};
+static Tensor conv2d(const Tensor& x0, const Tensor& w0, const Tensor& b0, int sh, int sw, int ph, int pw) {
+  if (x0->shape.size() != 4 || w0->shape.size() != 4 || x0->shape[1] != w0->shape[1] || sh < 1 || sw < 1 || ph < 0 || pw < 0 ||
+      (b0 && (b0->shape.size() != 1 || b0->shape[0] != w0->shape[0]))) { g_last_error = "conv2d: x [N, C, H, W], weight [O, C, kh, kw], bias [O], stride >= 1, padding >= 0"; return nullptr; }
+  Tensor x = contiguous(x0), w = contiguous(w0), b = b0 ? contiguous(b0) : nullptr;
+  ConvGeom g{x->shape[0], x->shape[1], x->shape[2], x->shape[3], w->shape[0], w->shape[2], w->shape[3], sh, sw, ph, pw, 0, 0};
+  g.Ho = (g.H + 2 * g.ph - g.kh) / g.sh + 1;
+  g.Wo = (g.W + 2 * g.pw - g.kw) / g.sw + 1;
+  if (g.H + 2 * g.ph < g.kh || g.W + 2 * g.pw < g.kw) { g_last_error = "conv2d: kernel larger than the padded input"; return nullptr; }
+  const int64_t K = g.C * g.kh * g.kw, P = g.Ho * g.Wo;
+  Tensor o = make({g.N, g.O, g.Ho, g.Wo});
+  std::vector<float> col((size_t)(K * P));
+  for (int64_t n = 0; n < g.N; n++) {
+    im2col(x->data() + n * g.C * g.H * g.W, g, col.data());
+    float* on = o->data() + n * g.O * P;
+    gemm_raw(w->data(), col.data(), on, g.O, P, K);
+    if (b)
+      for (int64_t oc = 0; oc < g.O; oc++)
+        for (int64_t q = 0; q < P; q++) on[oc * P + q] += b->data()[oc];
+  }
+  if (b0) attach<Conv2dNode>(o, {x0, w0, b0}, x, w, g, true);
+  else attach<Conv2dNode>(o, {x0, w0}, x, w, g, false);
+  return o;
+}
+
+// max pooling over k x k windows with the given stride (no padding); the position of each maximum is kept for the backward pass
+struct MaxPoolNode : Node {
+  std::vector<int64_t> shape; std::vector<int64_t> arg;
+  MaxPoolNode(std::vector<int64_t> s, std::vector<int64_t> a) : shape(std::move(s)), arg(std::move(a)) { name = "max_pool2d"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(shape);
+    for (int64_t i = 0; i < gc->numel(); i++) o->data()[arg[(size_t)i]] += gc->data()[i];
+    return {o};
+  }
+};
+static Tensor max_pool2d(const Tensor& x0, int k, int stride) {
+  if (x0->shape.size() != 4 || k < 1 || stride < 1 || x0->shape[2] < k || x0->shape[3] < k) { g_last_error = "max_pool2d: x [N, C, H, W] with H, W >= kernel"; return nullptr; }
+  Tensor x = contiguous(x0);
+  const int64_t N = x->shape[0], C = x->shape[1], Hh = x->shape[2], Ww = x->shape[3], Ho = (Hh - k) / stride + 1, Wo = (Ww - k) / stride + 1;
+  Tensor o = make({N, C, Ho, Wo});
+  std::vector<int64_t> arg((size_t)o->numel());
+  for (int64_t nc = 0; nc < N * C; nc++)
+    for (int64_t oy = 0; oy < Ho; oy++)
+      for (int64_t ox = 0; ox < Wo; ox++) {
+        int64_t best = (nc * Hh + oy * stride) * Ww + ox * stride;
+        for (int64_t i = 0; i < k; i++)
+          for (int64_t j = 0; j < k; j++) {
+            const int64_t at = (nc * Hh + oy * stride + i) * Ww + ox * stride + j;
+            if (x->data()[at] > x->data()[best]) best = at;
+          }
+        const int64_t oi = (nc * Ho + oy) * Wo + ox;
+        o->data()[oi] = x->data()[best];
+        arg[(size_t)oi] = best;
+      }
+  attach<MaxPoolNode>(o, {x0}, x->shape, std::move(arg));
+  return o;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------------
+// Adam / AdamW (decoupled decay when `decoupled`, else the decay is added to the gradient), bias-corrected, same rule as the device kernel
+// ---------------------------------------------------------------------------------------------------------------------------------------
+struct Adam {
+  std::vector<Tensor> params;
+  std::vector<std::vector<float>> m, v;
+  float lr, beta1, beta2, eps, weight_decay;
+  bool decoupled;
+  int64_t t = 0;
+  void step() {
+    if (m.size() != params.size()) { m.resize(params.size()); v.resize(params.size()); }
+    t++;
+    const double c1 = 1.0 - std::pow((double)beta1, (double)t), c2 = 1.0 - std::pow((double)beta2, (double)t);
+    for (size_t k = 0; k < params.size(); k++) {
+      Tensor& p = params[k];
+      if (!p->grad || !p->is_contiguous()) continue;
+      Tensor gc = contiguous(p->grad);
+      const int64_t n = p->numel();
+      if (m[k].empty()) { m[k].assign((size_t)n, 0.f); v[k].assign((size_t)n, 0.f); }
+      float* w = p->data();
+      for (int64_t i = 0; i < n; i++) {
+        float g = gc->data()[i];
+        if (decoupled) w[i] *= 1.f - lr * weight_decay;
+        else g += weight_decay * w[i];
+        m[k][(size_t)i] = beta1 * m[k][(size_t)i] + (1.f - beta1) * g;
+        v[k][(size_t)i] = beta2 * v[k][(size_t)i] + (1.f - beta2) * g * g;
+        const double mh = m[k][(size_t)i] / c1, vh = v[k][(size_t)i] / c2;
+        w[i] -= (float)(lr * mh / (std::sqrt(vh) + eps));
+      }
+      p->version++;
+    }
+  }
+};
+
 }  // namespace ft
 
 // ---------------------------------------------------------------------------------------------------------------------------------------
@@ -572,3 +910,32 @@ FT_API void ftc_sgd_step(void* s) { static_cast<ft::Sgd*>(s)->step(); }
 FT_API void ftc_sgd_set_lr(void* s, float lr) { static_cast<ft::Sgd*>(s)->lr = lr; }
 FT_API void ftc_sgd_zero_grad(void* s) { for (auto& p : static_cast<ft::Sgd*>(s)->params) p->grad = nullptr; }
 FT_API void ftc_sgd_free(void* s) { delete static_cast<ft::Sgd*>(s); }
+
+// Element-wise operation `kind` (0 exp, 1 log, 2 sqrt, 3 gelu (erf form), 4 silu, 5 leaky relu with slope p, 6 power p, 7 abs, 8 square, 9 reciprocal).
+FT_API void* ftc_unary(const void* a, int kind, float p) {
+  if (kind < 0 || kind > 9) { ft::g_last_error = "unary: unknown kind"; return nullptr; }
+  return H(ft::unary((ft::Un)kind, T(a), p));
+}
+FT_API void* ftc_div(const void* a, const void* b) { return H(ft::divide(T(a), T(b))); }
+// A view with another shape (one entry may be -1); a non-contiguous input is copied first.
+FT_API void* ftc_reshape(const void* a, const int64_t* shape, int ndim) { return H(ft::reshape(T(a), std::vector<int64_t>(shape, shape + ndim))); }
+// Sum (mean = 0) or mean (mean = 1) along dimension dim (negative counts from the end).
+FT_API void* ftc_sum_dim(const void* a, int dim, int keepdim, int mean) { return H(ft::sum_dim(T(a), dim, keepdim != 0, mean != 0)); }
+// Softmax (log = 0) or log-softmax (log = 1) over the last dimension.
+FT_API void* ftc_softmax(const void* a, int log) { return H(ft::softmax(T(a), log != 0)); }
+// x [N, C, H, W], weight [O, C, kh, kw], bias [O] or null.
+FT_API void* ftc_conv2d(const void* x, const void* w, const void* b, int sh, int sw, int ph, int pw) {
+  return H(ft::conv2d(T(x), T(w), b ? T(b) : nullptr, sh, sw, ph, pw));
+}
+FT_API void* ftc_max_pool2d(const void* x, int k, int stride) { return H(ft::max_pool2d(T(x), k, stride)); }
+
+FT_API void* ftc_adam_new(void* const* params, int n, float lr, float beta1, float beta2, float eps, float weight_decay, int decoupled) {
+  auto* a = new ft::Adam();
+  for (int i = 0; i < n; i++) a->params.push_back(T(params[i]));
+  a->lr = lr; a->beta1 = beta1; a->beta2 = beta2; a->eps = eps; a->weight_decay = weight_decay; a->decoupled = decoupled != 0;
+  return a;
+}
+FT_API void ftc_adam_step(void* s) { static_cast<ft::Adam*>(s)->step(); }
+FT_API void ftc_adam_set_lr(void* s, float lr) { static_cast<ft::Adam*>(s)->lr = lr; }
+FT_API void ftc_adam_zero_grad(void* s) { for (auto& p : static_cast<ft::Adam*>(s)->params) p->grad = nullptr; }
+FT_API void ftc_adam_free(void* s) { delete static_cast<ft::Adam*>(s); }

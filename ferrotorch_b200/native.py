@@ -2,8 +2,9 @@
 
 ``Tensor`` wraps a handle of the C++ ``ft::Tensor`` (f32, strided, reference counted); the operations record ``ft::Node`` objects and
 ``Tensor.backward()`` runs the C++ engine (graph collection, Kahn ordering, reverse sweep, hooks; ``threads > 1`` selects the parallel sweep,
-which produces the same bits). ``Linear`` / ``Sequential`` / ``Sgd`` are the smallest framework layer over it: enough to train the MLP of the
-CPU data-parallel benchmark without ``torch.nn`` / ``torch.autograd`` / ``torch.optim`` on the path. NumPy arrays are the interchange format
+which produces the same bits). ``Linear`` / ``Conv2d`` / ``MaxPool2d`` / ``Flatten`` / activations / ``Sequential`` with ``Sgd`` / ``Adam`` /
+``AdamW`` are the smallest framework layer over it: enough to train the MLP of the CPU data-parallel benchmark, or a small convolutional
+network, without ``torch.nn`` / ``torch.autograd`` / ``torch.optim`` on the path. NumPy arrays are the interchange format
 (``Tensor.numpy()`` of a contiguous tensor is a zero-copy view of the native storage).
 
 Reference parity: ferrotorch-core/src/tensor.rs:46-103, autograd/graph.rs:20-458, ferrotorch-nn/src/{module,linear,loss}.rs,
@@ -35,7 +36,12 @@ _SIGS = {
     "ftc_register_post_accumulate_hook": (None, [_vp, _POST_HOOK, _vp]),
     "ftc_sgd_new": (_vp, [_vp, _i, _f, _f, _f, _f, _i]), "ftc_sgd_step": (None, [_vp]), "ftc_sgd_set_lr": (None, [_vp, _f]),
     "ftc_sgd_zero_grad": (None, [_vp]), "ftc_sgd_free": (None, [_vp]),
+    "ftc_unary": (_vp, [_vp, _i, _f]), "ftc_div": (_vp, [_vp, _vp]), "ftc_reshape": (_vp, [_vp, _vp, _i]), "ftc_sum_dim": (_vp, [_vp, _i, _i, _i]),
+    "ftc_softmax": (_vp, [_vp, _i]), "ftc_conv2d": (_vp, [_vp, _vp, _vp, _i, _i, _i, _i]), "ftc_max_pool2d": (_vp, [_vp, _i, _i]),
+    "ftc_adam_new": (_vp, [_vp, _i, _f, _f, _f, _f, _f, _i]), "ftc_adam_step": (None, [_vp]), "ftc_adam_set_lr": (None, [_vp, _f]),
+    "ftc_adam_zero_grad": (None, [_vp]), "ftc_adam_free": (None, [_vp]),
 }
+_UNARY = {"exp": 0, "log": 1, "sqrt": 2, "gelu": 3, "silu": 4, "leaky_relu": 5, "pow": 6, "abs": 7, "square": 8, "reciprocal": 9}
 _bound = {}
 
 
@@ -154,8 +160,50 @@ class Tensor:
     def relu(self): return Tensor(_handle=_check(_fn("ftc_relu")(self._h)))
     def tanh(self): return Tensor(_handle=_check(_fn("ftc_tanh")(self._h)))
     def sigmoid(self): return Tensor(_handle=_check(_fn("ftc_sigmoid")(self._h)))
-    def sum(self): return Tensor(_handle=_check(_fn("ftc_sum")(self._h)))
-    def mean(self): return Tensor(_handle=_check(_fn("ftc_mean")(self._h)))
+    def __truediv__(self, o):
+        if not isinstance(o, Tensor) and np.isscalar(o):
+            return Tensor(_handle=_check(_fn("ftc_scale")(self._h, 1.0 / float(o))))
+        return self._bin("ftc_div", o)
+
+    def _un(self, kind: str, p: float = 0.0): return Tensor(_handle=_check(_fn("ftc_unary")(self._h, _UNARY[kind], float(p))))
+    def exp(self): return self._un("exp")
+    def log(self): return self._un("log")
+    def sqrt(self): return self._un("sqrt")
+    def gelu(self): return self._un("gelu")
+    def silu(self): return self._un("silu")
+    def leaky_relu(self, negative_slope: float = 0.01): return self._un("leaky_relu", negative_slope)
+    def pow(self, p: float): return self._un("pow", p)
+    __pow__ = pow
+    def abs(self): return self._un("abs")
+    def square(self): return self._un("square")
+    def reciprocal(self): return self._un("reciprocal")
+
+    def reshape(self, *shape):
+        """A view with another shape (one entry may be -1); a non-contiguous tensor is copied first."""
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+            shape = tuple(shape[0])
+        arr = (ctypes.c_int64 * max(len(shape), 1))(*[int(v) for v in shape])
+        return Tensor(_handle=_check(_fn("ftc_reshape")(self._h, arr, len(shape))))
+
+    view = reshape
+
+    def flatten(self, start_dim: int = 0):
+        sh = self.shape
+        start_dim %= max(len(sh), 1)
+        return self.reshape(*sh[:start_dim], -1)
+
+    def sum(self, dim: Optional[int] = None, keepdim: bool = False):
+        if dim is None:
+            return Tensor(_handle=_check(_fn("ftc_sum")(self._h)))
+        return Tensor(_handle=_check(_fn("ftc_sum_dim")(self._h, int(dim), int(keepdim), 0)))
+
+    def mean(self, dim: Optional[int] = None, keepdim: bool = False):
+        if dim is None:
+            return Tensor(_handle=_check(_fn("ftc_mean")(self._h)))
+        return Tensor(_handle=_check(_fn("ftc_sum_dim")(self._h, int(dim), int(keepdim), 1)))
+
+    def softmax(self): return Tensor(_handle=_check(_fn("ftc_softmax")(self._h, 0)))
+    def log_softmax(self): return Tensor(_handle=_check(_fn("ftc_softmax")(self._h, 1)))
 
     def backward(self, grad: Optional["Tensor"] = None, threads: int = 1) -> None:
         """Reverse sweep from this tensor. ``threads > 1`` runs independent nodes on worker threads (``backward_parallel``); gradients are
@@ -205,6 +253,24 @@ def cross_entropy(logits: Tensor, targets) -> Tensor:
     return Tensor(_handle=_check(_fn("ftc_cross_entropy")(logits._h, t.ctypes.data, t.size)))
 
 
+def _pair(v):
+    return (int(v), int(v)) if np.isscalar(v) else (int(v[0]), int(v[1]))
+
+
+def conv2d(x: Tensor, w: Tensor, b: Optional[Tensor] = None, stride=1, padding=0) -> Tensor:
+    """``x`` [N, C, H, W], ``w`` [O, C, kh, kw], ``b`` [O]: patch matrix times GEMM in the native core, with its backward rule."""
+    (sh, sw), (ph, pw) = _pair(stride), _pair(padding)
+    return Tensor(_handle=_check(_fn("ftc_conv2d")(x._h, w._h, b._h if b is not None else None, sh, sw, ph, pw)))
+
+
+def max_pool2d(x: Tensor, kernel_size: int, stride: Optional[int] = None) -> Tensor:
+    return Tensor(_handle=_check(_fn("ftc_max_pool2d")(x._h, int(kernel_size), int(stride or kernel_size))))
+
+
+def mse_loss(a: Tensor, b: Tensor) -> Tensor:
+    return (a - b).square().mean()
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # the smallest module layer
 # ----------------------------------------------------------------------------------------------------------------------
@@ -249,6 +315,54 @@ class ReLU(Module):
         return x.relu()
 
 
+class Conv2d(Module):
+    """Kaiming-uniform weights (bound ``sqrt(6 / (C kh kw))``) and zero bias, like ``Linear``."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, bias: bool = True, rng: Optional[np.random.Generator] = None):
+        rng = rng or np.random.default_rng(0)
+        kh, kw = _pair(kernel_size)
+        bound = math.sqrt(6.0 / (in_channels * kh * kw))
+        self.weight = Tensor(rng.uniform(-bound, bound, size=(out_channels, in_channels, kh, kw)).astype(np.float32), requires_grad=True)
+        self.bias = Tensor(np.zeros(out_channels, np.float32), requires_grad=True) if bias else None
+        self.stride, self.padding = stride, padding
+
+    def forward(self, x: Tensor) -> Tensor:
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding)
+
+
+class MaxPool2d(Module):
+    def __init__(self, kernel_size: int, stride: Optional[int] = None):
+        self.kernel_size, self.stride = kernel_size, stride
+
+    def forward(self, x: Tensor) -> Tensor:
+        return max_pool2d(x, self.kernel_size, self.stride)
+
+
+class Flatten(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.flatten(1)
+
+
+class GELU(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.gelu()
+
+
+class SiLU(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.silu()
+
+
+class Tanh(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.tanh()
+
+
+class Sigmoid(Module):
+    def forward(self, x: Tensor) -> Tensor:
+        return x.sigmoid()
+
+
 class Sequential(Module):
     def __init__(self, *mods: Module):
         self.mods = list(mods)
@@ -284,3 +398,35 @@ class Sgd:
                 _fn("ftc_sgd_free")(h)
             except Exception:
                 pass
+
+
+class Adam:
+    """Native Adam; ``decoupled=True`` is AdamW (the weights shrink by ``1 - lr * weight_decay`` before the step), else the decay joins the
+    gradient (ferrotorch-optim/src/adam.rs, adamw.rs:315)."""
+
+    def __init__(self, params: Iterable[Tensor], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, decoupled: bool = False):
+        self.params = list(params)
+        arr = (ctypes.c_void_p * len(self.params))(*[p._h for p in self.params])
+        self._h = _fn("ftc_adam_new")(arr, len(self.params), lr, betas[0], betas[1], eps, weight_decay, int(decoupled))
+
+    def step(self) -> None:
+        _fn("ftc_adam_step")(self._h)
+
+    def zero_grad(self) -> None:
+        _fn("ftc_adam_zero_grad")(self._h)
+
+    def set_lr(self, lr: float) -> None:
+        _fn("ftc_adam_set_lr")(self._h, lr)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _fn("ftc_adam_free")(h)
+            except Exception:
+                pass
+
+
+class AdamW(Adam):
+    def __init__(self, params: Iterable[Tensor], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 1e-2):
+        super().__init__(params, lr, betas, eps, weight_decay, decoupled=True)

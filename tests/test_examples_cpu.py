@@ -50,3 +50,10 @@ def test_constrained_generation_example_emits_a_document_of_the_schema():
     if "complete document: True" in out:
         doc = json.loads(line[len("generated: "):])
         assert isinstance(doc["name"], str) and isinstance(doc["age"], int) and set(doc) <= {"name", "age", "tags", "note"}
+
+
+def test_native_core_cnn_example_learns():
+    out = _run(ROOT / "examples/native_cnn.py", "--steps", "60")
+    acc = float(out.split("accuracy on 512 fresh samples:")[1].split()[0])
+    first, last = (float(l.split("loss")[1]) for l in (out.splitlines()[0], [l for l in out.splitlines() if l.startswith("step")][-1]))
+    assert acc > 0.8 and last < 0.5 * first

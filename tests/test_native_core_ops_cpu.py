@@ -1,0 +1,124 @@
+"""The wider operation set of the native C++ tensor / autograd core (element-wise family, division, reshape, reductions along a dimension,
+softmax, conv2d, max-pool) and its Adam / AdamW: values and gradients against PyTorch, then a small convolutional network trained by the
+native core step for step beside the same network in PyTorch."""
+import numpy as np
+import pytest
+import torch
+
+from ferrotorch_b200 import native as N
+
+
+def _t(a, grad=True):
+    return N.Tensor(np.asarray(a, np.float32), requires_grad=grad)
+
+
+def _check(native_fn, torch_fn, *arrays, tol=2e-5):
+    nts = [_t(a) for a in arrays]
+    tts = [torch.tensor(np.asarray(a, np.float32), requires_grad=True) for a in arrays]
+    yn, yt = native_fn(*nts), torch_fn(*tts)
+    assert tuple(yn.shape) == tuple(yt.shape), (yn.shape, yt.shape)
+    assert np.allclose(yn.numpy(), yt.detach().numpy(), atol=tol, rtol=tol)
+    w = np.random.default_rng(1).standard_normal(yt.shape).astype(np.float32)
+    (yn * _t(w, False)).sum().backward()
+    (yt * torch.tensor(w)).sum().backward()
+    for a, b in zip(nts, tts):
+        assert np.allclose(a.grad.numpy(), b.grad.numpy(), atol=tol * 5, rtol=tol * 5)
+
+
+def test_elementwise_family_matches_pytorch():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((5, 7)).astype(np.float32)
+    pos = np.abs(x) + 0.5
+    for name, tf, arg in (("exp", torch.exp, x), ("log", torch.log, pos), ("sqrt", torch.sqrt, pos), ("gelu", torch.nn.functional.gelu, x),
+                          ("silu", torch.nn.functional.silu, x), ("abs", torch.abs, x), ("square", torch.square, x), ("reciprocal", torch.reciprocal, pos)):
+        _check(lambda t, n=name: getattr(t, n)(), tf, arg)
+    _check(lambda t: t.leaky_relu(0.2), lambda t: torch.nn.functional.leaky_relu(t, 0.2), x)
+    _check(lambda t: t.pow(2.5), lambda t: t.pow(2.5), pos)
+    _check(lambda t: t ** 3.0, lambda t: t ** 3.0, x)
+    y = rng.standard_normal((5, 7)).astype(np.float32) + 3.0
+    _check(lambda a, b: a / b, lambda a, b: a / b, x, y)
+    _check(lambda a, b: a / b, lambda a, b: a / b, x, y[0])                        # a row vector broadcasts over the rows
+    _check(lambda a: a / 4.0, lambda a: a / 4.0, x)
+    with pytest.raises(Exception):
+        _t(x) / _t(np.ones((3,), np.float32))
+
+
+def test_reshape_reductions_and_softmax_match_pytorch():
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 3, 4)).astype(np.float32)
+    _check(lambda t: t.reshape(6, 4).t().reshape(2, -1), lambda t: t.reshape(6, 4).t().reshape(2, -1), x)        # a view of a transposed view
+    _check(lambda t: t.flatten(1), lambda t: t.flatten(1), x)
+    for dim in (0, 1, 2, -1):
+        for keep in (False, True):
+            _check(lambda t, d=dim, k=keep: t.sum(d, k), lambda t, d=dim, k=keep: t.sum(d, k), x)
+            _check(lambda t, d=dim, k=keep: t.mean(d, k), lambda t, d=dim, k=keep: t.mean(d, k), x)
+    _check(lambda t: t.softmax(), lambda t: torch.softmax(t, -1), x)
+    _check(lambda t: t.log_softmax(), lambda t: torch.log_softmax(t, -1), x)
+    _check(lambda a, b: N.mse_loss(a, b), torch.nn.functional.mse_loss, x, x[::-1].copy())
+    for bad in (lambda: _t(x).reshape(5, 5), lambda: _t(x).reshape(-1, -1), lambda: _t(x).sum(3)):
+        with pytest.raises(Exception):
+            bad()
+
+
+@pytest.mark.parametrize("stride,padding,bias", [(1, 0, True), (1, 1, True), (2, 1, False), ((2, 1), (0, 2), True)])
+def test_conv2d_and_max_pool_match_pytorch(stride, padding, bias):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 3, 9, 8)).astype(np.float32)
+    w = rng.standard_normal((4, 3, 3, 3)).astype(np.float32) * 0.3
+    b = rng.standard_normal((4,)).astype(np.float32)
+    if bias:
+        _check(lambda a, c, d: N.conv2d(a, c, d, stride, padding), lambda a, c, d: torch.nn.functional.conv2d(a, c, d, stride, padding), x, w, b, tol=1e-4)
+    else:
+        _check(lambda a, c: N.conv2d(a, c, None, stride, padding), lambda a, c: torch.nn.functional.conv2d(a, c, None, stride, padding), x, w, tol=1e-4)
+    _check(lambda a: N.max_pool2d(a, 2), lambda a: torch.nn.functional.max_pool2d(a, 2), x)
+    _check(lambda a: N.max_pool2d(a, 3, 2), lambda a: torch.nn.functional.max_pool2d(a, 3, 2), x)
+    with pytest.raises(Exception):
+        N.conv2d(_t(x), _t(rng.standard_normal((4, 2, 3, 3))))
+
+
+@pytest.mark.parametrize("decoupled", [False, True])
+def test_adam_and_adamw_follow_pytorch(decoupled):
+    rng = np.random.default_rng(4)
+    w0, x, y = rng.standard_normal((6, 5)).astype(np.float32), rng.standard_normal((8, 5)).astype(np.float32), rng.standard_normal((8, 6)).astype(np.float32)
+    wn, wt = _t(w0), torch.tensor(w0, requires_grad=True)
+    on = (N.AdamW([wn], lr=0.05, weight_decay=0.1) if decoupled else N.Adam([wn], lr=0.05, weight_decay=0.1))
+    ot = (torch.optim.AdamW([wt], lr=0.05, weight_decay=0.1) if decoupled else torch.optim.Adam([wt], lr=0.05, weight_decay=0.1))
+    for _ in range(6):
+        on.zero_grad()
+        N.mse_loss(N.linear(_t(x, False), wn), _t(y, False)).backward()
+        on.step()
+        ot.zero_grad()
+        torch.nn.functional.mse_loss(torch.tensor(x) @ wt.t(), torch.tensor(y)).backward()
+        ot.step()
+    assert np.allclose(wn.numpy(), wt.detach().numpy(), atol=2e-5)
+
+
+def test_small_convolutional_network_trains_like_pytorch():
+    """Conv - ReLU - MaxPool - Conv - GELU - Flatten - Linear with cross-entropy, Adam, 8 steps: losses and final weights track PyTorch."""
+    rng = np.random.default_rng(5)
+    net = N.Sequential(N.Conv2d(1, 4, 3, padding=1, rng=rng), N.ReLU(), N.MaxPool2d(2), N.Conv2d(4, 6, 3, stride=2, rng=rng), N.GELU(), N.Flatten(),
+                       N.Linear(6 * 3 * 3, 5, rng=rng))
+    ref = torch.nn.Sequential(torch.nn.Conv2d(1, 4, 3, padding=1), torch.nn.ReLU(), torch.nn.MaxPool2d(2), torch.nn.Conv2d(4, 6, 3, stride=2), torch.nn.GELU(),
+                              torch.nn.Flatten(), torch.nn.Linear(54, 5))
+    with torch.no_grad():
+        for mine, theirs in zip([net.mods[0], net.mods[3], net.mods[6]], [ref[0], ref[3], ref[6]]):
+            theirs.weight.copy_(torch.tensor(mine.weight.numpy()))
+            theirs.bias.copy_(torch.tensor(mine.bias.numpy()))
+    assert len(net.parameters()) == 6
+    x = rng.standard_normal((16, 1, 14, 14)).astype(np.float32)
+    y = rng.integers(0, 5, 16)
+    on, ot = N.Adam(net.parameters(), lr=0.01), torch.optim.Adam(ref.parameters(), lr=0.01)
+    losses = []
+    for _ in range(8):
+        on.zero_grad()
+        ln = N.cross_entropy(net(_t(x, False)), y)
+        ln.backward(threads=2)
+        on.step()
+        ot.zero_grad()
+        lt = torch.nn.functional.cross_entropy(ref(torch.tensor(x)), torch.tensor(y))
+        lt.backward()
+        ot.step()
+        losses.append((ln.item(), lt.item()))
+    assert all(abs(a - b) < 2e-3 for a, b in losses) and losses[-1][0] < losses[0][0]
+    assert np.allclose(net.mods[0].weight.numpy(), ref[0].weight.detach().numpy(), atol=2e-3)
+    assert np.allclose(net.mods[6].weight.numpy(), ref[6].weight.detach().numpy(), atol=2e-3)
