@@ -6,9 +6,10 @@
 //                    are kept per consuming edge and summed in edge order when a node becomes ready, so the serial engine and the parallel one
 //                    (worker threads over the ready queue) give identical bits; tensor hooks (may rewrite a gradient) run before accumulation
 //                    into a leaf, post-accumulate hooks after it (what DDP uses to launch a bucket's all-reduce)
-//   operations       add / sub / mul / div (row-broadcast of a vector), scale, matmul, transpose, reshape, relu, tanh, sigmoid and the
+//   operations       add / sub / mul / div (the second operand may have the shape of the trailing dimensions), scale, matmul, transpose, reshape, relu, tanh, sigmoid and the
 //                    element-wise family (exp, log, sqrt, gelu, silu, leaky relu, power, abs, square, reciprocal), sum / mean over everything or
-//                    along one dimension, softmax / log-softmax, linear, conv2d (patch matrix x GEMM), max_pool2d, cross-entropy on logits
+//                    along one dimension, softmax / log-softmax, linear, batched matmul, permute, narrow, layer norm, embedding, conv2d (patch matrix x GEMM),
+//                    max_pool2d, cross-entropy on logits
 //   ft::Sgd, ft::Adam momentum / dampening / nesterov / weight decay; Adam and AdamW (decoupled decay): same update rules as the device kernels
 //
 // Everything is exported through a small C ABI (opaque handles) for the Python binding in ferrotorch_b200/native.py.
@@ -260,6 +261,19 @@ static void backward(const Tensor& root, const Tensor& grad_root, int threads) {
 // ---------------------------------------------------------------------------------------------------------------------------------------
 // operations (inputs are made contiguous; row-broadcast means b has the shape of a's last dimension)
 // ---------------------------------------------------------------------------------------------------------------------------------------
+// b may have the shape of a, or of a's trailing dimensions (a bias vector, a [S, S] mask under [B, H, S, S]): element i of a pairs with i % numel(b)
+static bool suffix_broadcast_ok(const std::vector<int64_t>& a, const std::vector<int64_t>& b) {
+  int64_t na = 1, nb0 = 1;
+  for (auto v : a) na *= v;
+  for (auto v : b) nb0 *= v;
+  if (na == nb0 && na > 0) return true;                      // same number of elements: paired in order (a scalar with a one-element vector)
+  if (b.size() > a.size() || b.empty()) return false;
+  for (size_t i = 0; i < b.size(); i++)
+    if (b[b.size() - 1 - i] != a[a.size() - 1 - i]) return false;
+  int64_t nb = 1;
+  for (auto v : b) nb *= v;
+  return nb > 0;
+}
 static Tensor reduce_to(const Tensor& g, const std::vector<int64_t>& shape) {       // sum a [rows, n] gradient down to [n]
   if (g->shape == shape) return g;
   Tensor o = make(shape);
@@ -289,7 +303,7 @@ struct BinNode : Node {
 static Tensor binary(Bin op, const Tensor& a0, const Tensor& b0) {
   Tensor a = contiguous(a0), b = contiguous(b0);
   const int64_t n = a->numel(), nb = b->numel();
-  if (nb == 0 || n % nb || (nb != n && (b->shape.size() != 1 || a->shape.back() != b->shape[0]))) { g_last_error = "binary: shapes do not match or broadcast"; return nullptr; }
+  if (!suffix_broadcast_ok(a->shape, b->shape)) { g_last_error = "binary: shapes do not match or broadcast (the second operand must have the shape of the first or of its trailing dimensions)"; return nullptr; }
   Tensor o = make(a->shape);
   for (int64_t i = 0; i < n; i++) {
     const float x = a->data()[i], y = b->data()[i % nb];
@@ -542,7 +556,7 @@ struct DivNode : Node {
 static Tensor divide(const Tensor& a0, const Tensor& b0) {
   Tensor a = contiguous(a0), b = contiguous(b0);
   const int64_t n = a->numel(), nb = b->numel();
-  if (nb == 0 || n % nb || (nb != n && (b->shape.size() != 1 || a->shape.back() != b->shape[0]))) { g_last_error = "div: shapes do not match or broadcast"; return nullptr; }
+  if (!suffix_broadcast_ok(a->shape, b->shape)) { g_last_error = "div: shapes do not match or broadcast"; return nullptr; }
   Tensor o = make(a->shape);
   for (int64_t i = 0; i < n; i++) o->data()[i] = a->data()[i] / b->data()[i % nb];
   attach<DivNode>(o, {a0, b0}, a, b);
@@ -777,6 +791,204 @@ static Tensor max_pool2d(const Tensor& x0, int k, int stride) {
   return o;
 }
 
+
+
+// a view of `len` consecutive entries of dimension `dim` starting at `start`
+struct NarrowNode : Node {
+  std::vector<int64_t> shape; int dim; int64_t start;
+  NarrowNode(std::vector<int64_t> s, int d, int64_t st) : shape(std::move(s)), dim(d), start(st) { name = "narrow"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(shape);
+    int64_t outer = 1, inner = 1;
+    for (int i = 0; i < dim; i++) outer *= shape[(size_t)i];
+    for (size_t i = (size_t)dim + 1; i < shape.size(); i++) inner *= shape[i];
+    const int64_t full = shape[(size_t)dim], len = gc->shape[(size_t)dim];
+    for (int64_t a = 0; a < outer; a++)
+      std::memcpy(o->data() + (a * full + start) * inner, gc->data() + a * len * inner, sizeof(float) * (size_t)(len * inner));
+    return {o};
+  }
+};
+static Tensor narrow(const Tensor& a, int dim, int64_t start, int64_t len) {
+  const int nd = (int)a->shape.size();
+  if (dim < 0) dim += nd;
+  if (dim < 0 || dim >= nd || start < 0 || len < 0 || start + len > a->shape[(size_t)dim]) { g_last_error = "narrow: range outside the dimension"; return nullptr; }
+  auto t = std::make_shared<TensorImpl>();
+  t->storage = a->storage;
+  t->offset = a->offset + start * a->strides[(size_t)dim];
+  t->shape = a->shape;
+  t->shape[(size_t)dim] = len;
+  t->strides = a->strides;
+  attach<NarrowNode>(t, {a}, a->shape, dim, start);
+  return t;
+}
+
+// a view with permuted dimensions
+static Tensor permute(const Tensor& a, const std::vector<int64_t>& dims);
+struct PermuteNode : Node {
+  std::vector<int64_t> inverse;
+  explicit PermuteNode(std::vector<int64_t> inv) : inverse(std::move(inv)) { name = "permute"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    const bool prev = g_grad_enabled;
+    g_grad_enabled = false;
+    Tensor o = permute(g, inverse);
+    g_grad_enabled = prev;
+    return {o};
+  }
+};
+static Tensor permute(const Tensor& a, const std::vector<int64_t>& dims) {
+  const size_t nd = a->shape.size();
+  std::vector<int64_t> inv(nd, -1);
+  if (dims.size() != nd) { g_last_error = "permute: one entry per dimension"; return nullptr; }
+  for (size_t i = 0; i < nd; i++) {
+    const int64_t d = dims[i] < 0 ? dims[i] + (int64_t)nd : dims[i];
+    if (d < 0 || d >= (int64_t)nd || inv[(size_t)d] >= 0) { g_last_error = "permute: not a permutation"; return nullptr; }
+    inv[(size_t)d] = (int64_t)i;
+  }
+  auto t = std::make_shared<TensorImpl>();
+  t->storage = a->storage;
+  t->offset = a->offset;
+  for (size_t i = 0; i < nd; i++) {
+    const int64_t d = dims[i] < 0 ? dims[i] + (int64_t)nd : dims[i];
+    t->shape.push_back(a->shape[(size_t)d]);
+    t->strides.push_back(a->strides[(size_t)d]);
+  }
+  attach<PermuteNode>(t, {a}, inv);
+  return t;
+}
+
+// batched matrix product: [..., M, K] x [..., K, N] with equal leading dimensions
+struct BmmNode : Node {
+  Tensor a, b;
+  BmmNode(Tensor x, Tensor y) : a(std::move(x)), b(std::move(y)) { name = "bmm"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g);
+    const size_t nd = a->shape.size();
+    const int64_t M = a->shape[nd - 2], K = a->shape[nd - 1], N = b->shape[nd - 1], B = a->numel() / std::max<int64_t>(M * K, 1);
+    Tensor ga = inputs[0] ? make(a->shape) : nullptr, gb = inputs[1] ? make(b->shape) : nullptr;
+    std::vector<float> bt((size_t)(N * K)), at((size_t)(K * M));
+    for (int64_t i = 0; i < B; i++) {
+      const float* A = a->data() + i * M * K;
+      const float* Bm = b->data() + i * K * N;
+      const float* G = gc->data() + i * M * N;
+      if (ga) {                                          // dA = G [M, N] x B^T [N, K]
+        for (int64_t k = 0; k < K; k++)
+          for (int64_t n = 0; n < N; n++) bt[(size_t)(n * K + k)] = Bm[k * N + n];
+        gemm_raw(G, bt.data(), ga->data() + i * M * K, M, K, N);
+      }
+      if (gb) {                                          // dB = A^T [K, M] x G [M, N]
+        for (int64_t m = 0; m < M; m++)
+          for (int64_t k = 0; k < K; k++) at[(size_t)(k * M + m)] = A[m * K + k];
+        gemm_raw(at.data(), G, gb->data() + i * K * N, K, N, M);
+      }
+    }
+    return {ga, gb};
+  }
+};
+static Tensor bmm(const Tensor& a0, const Tensor& b0) {
+  const size_t nd = a0->shape.size();
+  if (nd < 2 || b0->shape.size() != nd || a0->shape[nd - 1] != b0->shape[nd - 2]) { g_last_error = "bmm: [..., M, K] x [..., K, N] with equal leading dimensions"; return nullptr; }
+  for (size_t i = 0; i + 2 < nd; i++)
+    if (a0->shape[i] != b0->shape[i]) { g_last_error = "bmm: leading dimensions differ"; return nullptr; }
+  Tensor a = contiguous(a0), b = contiguous(b0);
+  const int64_t M = a->shape[nd - 2], K = a->shape[nd - 1], N = b->shape[nd - 1], B = a->numel() / std::max<int64_t>(M * K, 1);
+  std::vector<int64_t> os(a->shape.begin(), a->shape.end() - 1);
+  os.push_back(N);
+  Tensor o = make(os);
+  for (int64_t i = 0; i < B; i++) gemm_raw(a->data() + i * M * K, b->data() + i * K * N, o->data() + i * M * N, M, N, K);
+  attach<BmmNode>(o, {a0, b0}, a, b);
+  return o;
+}
+
+// layer normalisation over the last dimension with an optional scale and shift
+struct LayerNormNode : Node {
+  Tensor xhat, w; std::vector<float> rstd; bool has_w, has_b;
+  LayerNormNode(Tensor xh, Tensor ww, std::vector<float> r, bool hw, bool hb) : xhat(std::move(xh)), w(std::move(ww)), rstd(std::move(r)), has_w(hw), has_b(hb) { name = "layer_norm"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g);
+    const int64_t C = xhat->shape.back(), R = xhat->numel() / std::max<int64_t>(C, 1);
+    Tensor gx = inputs[0] ? make(xhat->shape) : nullptr;
+    Tensor gw = (has_w && inputs[1]) ? make({C}) : nullptr;
+    Tensor gb = (has_b && inputs[has_w ? 2 : 1]) ? make({C}) : nullptr;
+    for (int64_t r = 0; r < R; r++) {
+      const float* gg = gc->data() + r * C;
+      const float* xh = xhat->data() + r * C;
+      double s1 = 0, s2 = 0;
+      for (int64_t c = 0; c < C; c++) {
+        const float gy = has_w ? gg[c] * w->data()[c] : gg[c];
+        s1 += gy;
+        s2 += gy * xh[c];
+        if (gw) gw->data()[c] += gg[c] * xh[c];
+        if (gb) gb->data()[c] += gg[c];
+      }
+      if (gx)
+        for (int64_t c = 0; c < C; c++) {
+          const float gy = has_w ? gg[c] * w->data()[c] : gg[c];
+          gx->data()[r * C + c] = rstd[(size_t)r] * (gy - (float)(s1 / C) - xh[c] * (float)(s2 / C));
+        }
+    }
+    std::vector<Tensor> out{gx};
+    if (has_w) out.push_back(gw);
+    if (has_b) out.push_back(gb);
+    return out;
+  }
+};
+static Tensor layer_norm(const Tensor& x0, const Tensor& w0, const Tensor& b0, float eps) {
+  if (x0->shape.empty()) { g_last_error = "layer_norm needs at least one dimension"; return nullptr; }
+  const int64_t C = x0->shape.back();
+  if ((w0 && (w0->shape.size() != 1 || w0->shape[0] != C)) || (b0 && (b0->shape.size() != 1 || b0->shape[0] != C))) { g_last_error = "layer_norm: scale and shift have the length of the last dimension"; return nullptr; }
+  Tensor x = contiguous(x0), w = w0 ? contiguous(w0) : nullptr, b = b0 ? contiguous(b0) : nullptr, o = make(x->shape), xh = make(x->shape);
+  const int64_t R = x->numel() / std::max<int64_t>(C, 1);
+  std::vector<float> rstd((size_t)R);
+  for (int64_t r = 0; r < R; r++) {
+    const float* xx = x->data() + r * C;
+    double m = 0, v = 0;
+    for (int64_t c = 0; c < C; c++) m += xx[c];
+    m /= (double)C;
+    for (int64_t c = 0; c < C; c++) v += (xx[c] - m) * (xx[c] - m);
+    const float rs = (float)(1.0 / std::sqrt(v / (double)C + eps));
+    rstd[(size_t)r] = rs;
+    for (int64_t c = 0; c < C; c++) {
+      const float h = (float)(xx[c] - m) * rs;
+      xh->data()[r * C + c] = h;
+      o->data()[r * C + c] = (w ? h * w->data()[c] : h) + (b ? b->data()[c] : 0.f);
+    }
+  }
+  if (w0 && b0) attach<LayerNormNode>(o, {x0, w0, b0}, xh, w, rstd, true, true);
+  else if (w0) attach<LayerNormNode>(o, {x0, w0}, xh, w, rstd, true, false);
+  else if (b0) attach<LayerNormNode>(o, {x0, b0}, xh, w, rstd, false, true);
+  else attach<LayerNormNode>(o, {x0}, xh, w, rstd, false, false);
+  return o;
+}
+
+// rows of a table selected by integer ids: out [..., D] for ids [...]
+struct EmbeddingNode : Node {
+  std::vector<int64_t> ids, table_shape;
+  EmbeddingNode(std::vector<int64_t> i, std::vector<int64_t> ts) : ids(std::move(i)), table_shape(std::move(ts)) { name = "embedding"; }
+  std::vector<Tensor> backward(const Tensor& g) override {
+    Tensor gc = contiguous(g), o = make(table_shape);
+    const int64_t D = table_shape[1];
+    for (size_t r = 0; r < ids.size(); r++)
+      for (int64_t d = 0; d < D; d++) o->data()[ids[r] * D + d] += gc->data()[(int64_t)r * D + d];
+    return {o};
+  }
+};
+static Tensor embedding(const Tensor& table0, const int64_t* ids, const int64_t* ids_shape, int ids_ndim) {
+  if (table0->shape.size() != 2) { g_last_error = "embedding: the table is [rows, dim]"; return nullptr; }
+  Tensor table = contiguous(table0);
+  const int64_t V = table->shape[0], D = table->shape[1];
+  std::vector<int64_t> os(ids_shape, ids_shape + ids_ndim);
+  int64_t n = 1;
+  for (auto v : os) n *= v;
+  os.push_back(D);
+  Tensor o = make(os);
+  for (int64_t r = 0; r < n; r++) {
+    if (ids[r] < 0 || ids[r] >= V) { g_last_error = "embedding: id out of range"; return nullptr; }
+    std::memcpy(o->data() + r * D, table->data() + ids[r] * D, sizeof(float) * (size_t)D);
+  }
+  attach<EmbeddingNode>(o, {table0}, std::vector<int64_t>(ids, ids + n), table->shape);
+  return o;
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------------------
 // Adam / AdamW (decoupled decay when `decoupled`, else the decay is added to the gradient), bias-corrected, same rule as the device kernel
 // ---------------------------------------------------------------------------------------------------------------------------------------
@@ -939,3 +1151,14 @@ FT_API void ftc_adam_step(void* s) { static_cast<ft::Adam*>(s)->step(); }
 FT_API void ftc_adam_set_lr(void* s, float lr) { static_cast<ft::Adam*>(s)->lr = lr; }
 FT_API void ftc_adam_zero_grad(void* s) { for (auto& p : static_cast<ft::Adam*>(s)->params) p->grad = nullptr; }
 FT_API void ftc_adam_free(void* s) { delete static_cast<ft::Adam*>(s); }
+
+// A view with the dimensions in the order dims (negative entries count from the end).
+FT_API void* ftc_permute(const void* a, const int64_t* dims, int ndim) { return H(ft::permute(T(a), std::vector<int64_t>(dims, dims + ndim))); }
+// [..., M, K] x [..., K, N] with equal leading dimensions.
+FT_API void* ftc_bmm(const void* a, const void* b) { return H(ft::bmm(T(a), T(b))); }
+// Normalisation over the last dimension; w and b ([last dim]) may be null.
+FT_API void* ftc_layer_norm(const void* x, const void* w, const void* b, float eps) { return H(ft::layer_norm(T(x), w ? T(w) : nullptr, b ? T(b) : nullptr, eps)); }
+// Rows ids (host int64, shape ids_shape) of table [rows, dim].
+FT_API void* ftc_embedding(const void* table, const int64_t* ids, const int64_t* ids_shape, int ids_ndim) { return H(ft::embedding(T(table), ids, ids_shape, ids_ndim)); }
+// A view of len consecutive entries of dimension dim starting at start.
+FT_API void* ftc_narrow(const void* a, int dim, int64_t start, int64_t len) { return H(ft::narrow(T(a), dim, start, len)); }

@@ -40,6 +40,8 @@ _SIGS = {
     "ftc_softmax": (_vp, [_vp, _i]), "ftc_conv2d": (_vp, [_vp, _vp, _vp, _i, _i, _i, _i]), "ftc_max_pool2d": (_vp, [_vp, _i, _i]),
     "ftc_adam_new": (_vp, [_vp, _i, _f, _f, _f, _f, _f, _i]), "ftc_adam_step": (None, [_vp]), "ftc_adam_set_lr": (None, [_vp, _f]),
     "ftc_adam_zero_grad": (None, [_vp]), "ftc_adam_free": (None, [_vp]),
+    "ftc_permute": (_vp, [_vp, _vp, _i]), "ftc_bmm": (_vp, [_vp, _vp]), "ftc_layer_norm": (_vp, [_vp, _vp, _vp, _f]), "ftc_embedding": (_vp, [_vp, _vp, _vp, _i]),
+    "ftc_narrow": (_vp, [_vp, _i, _i64, _i64]),
 }
 _UNARY = {"exp": 0, "log": 1, "sqrt": 2, "gelu": 3, "silu": 4, "leaky_relu": 5, "pow": 6, "abs": 7, "square": 8, "reciprocal": 9}
 _bound = {}
@@ -155,7 +157,35 @@ class Tensor:
     def __mul__(self, o): return self._bin("ftc_mul", o)
     __rmul__ = __mul__
     def __neg__(self): return Tensor(_handle=_check(_fn("ftc_scale")(self._h, -1.0)))
-    def __matmul__(self, o): return Tensor(_handle=_check(_fn("ftc_matmul")(self._h, o._h)))
+    def __matmul__(self, o):
+        """Matrix product; tensors with leading (batch) dimensions multiply batch by batch."""
+        return Tensor(_handle=_check(_fn("ftc_matmul" if len(self.shape) == 2 else "ftc_bmm")(self._h, o._h)))
+
+    def permute(self, *dims):
+        if len(dims) == 1 and isinstance(dims[0], (tuple, list)):
+            dims = tuple(dims[0])
+        arr = (ctypes.c_int64 * max(len(dims), 1))(*[int(d) for d in dims])
+        return Tensor(_handle=_check(_fn("ftc_permute")(self._h, arr, len(dims))))
+
+    def narrow(self, dim: int, start: int, length: int):
+        """A view of ``length`` consecutive entries of dimension ``dim``."""
+        return Tensor(_handle=_check(_fn("ftc_narrow")(self._h, int(dim), int(start), int(length))))
+
+    def __getitem__(self, i):
+        """``t[i]`` (an integer) or ``t[a:b]`` on the first dimension."""
+        n = self.shape[0]
+        if isinstance(i, slice):
+            a, b, step = i.indices(n)
+            if step != 1:
+                raise InvalidArgument("native Tensor: slices have step 1")
+            return self.narrow(0, a, max(b - a, 0))
+        i = int(i) + (n if int(i) < 0 else 0)
+        return self.narrow(0, i, 1).reshape(*self.shape[1:])
+
+    def transpose(self, d0: int, d1: int):
+        order = list(range(len(self.shape)))
+        order[d0], order[d1] = order[d1], order[d0]
+        return self.permute(*order)
     def t(self): return Tensor(_handle=_check(_fn("ftc_transpose")(self._h)))
     def relu(self): return Tensor(_handle=_check(_fn("ftc_relu")(self._h)))
     def tanh(self): return Tensor(_handle=_check(_fn("ftc_tanh")(self._h)))
@@ -251,6 +281,18 @@ def relu(x: Tensor) -> Tensor:
 def cross_entropy(logits: Tensor, targets) -> Tensor:
     t = np.ascontiguousarray(np.asarray(targets, dtype=np.int64))
     return Tensor(_handle=_check(_fn("ftc_cross_entropy")(logits._h, t.ctypes.data, t.size)))
+
+
+def layer_norm(x: Tensor, weight: Optional[Tensor] = None, bias: Optional[Tensor] = None, eps: float = 1e-5) -> Tensor:
+    """Normalisation over the last dimension."""
+    return Tensor(_handle=_check(_fn("ftc_layer_norm")(x._h, weight._h if weight is not None else None, bias._h if bias is not None else None, eps)))
+
+
+def embedding(ids, table: Tensor) -> Tensor:
+    """Rows ``ids`` (any integer array) of ``table`` [rows, dim]: the result has the shape of ``ids`` plus the row length."""
+    a = np.ascontiguousarray(np.asarray(ids, dtype=np.int64))
+    shape = (ctypes.c_int64 * max(a.ndim, 1))(*a.shape)
+    return Tensor(_handle=_check(_fn("ftc_embedding")(table._h, a.ctypes.data, shape, a.ndim)))
 
 
 def _pair(v):
@@ -361,6 +403,23 @@ class Tanh(Module):
 class Sigmoid(Module):
     def forward(self, x: Tensor) -> Tensor:
         return x.sigmoid()
+
+
+class LayerNorm(Module):
+    def __init__(self, dim: int, eps: float = 1e-5):
+        self.weight, self.bias, self.eps = Tensor(np.ones(dim, np.float32), requires_grad=True), Tensor(np.zeros(dim, np.float32), requires_grad=True), eps
+
+    def forward(self, x: Tensor) -> Tensor:
+        return layer_norm(x, self.weight, self.bias, self.eps)
+
+
+class Embedding(Module):
+    def __init__(self, rows: int, dim: int, rng: Optional[np.random.Generator] = None):
+        rng = rng or np.random.default_rng(0)
+        self.weight = Tensor(rng.standard_normal((rows, dim)).astype(np.float32), requires_grad=True)
+
+    def forward(self, ids) -> Tensor:
+        return embedding(ids, self.weight)
 
 
 class Sequential(Module):

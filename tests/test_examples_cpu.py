@@ -57,3 +57,10 @@ def test_native_core_cnn_example_learns():
     acc = float(out.split("accuracy on 512 fresh samples:")[1].split()[0])
     first, last = (float(l.split("loss")[1]) for l in (out.splitlines()[0], [l for l in out.splitlines() if l.startswith("step")][-1]))
     assert acc > 0.8 and last < 0.5 * first
+
+
+def test_native_core_transformer_example_learns_its_corpus():
+    out = _run(ROOT / "examples/native_gpt.py", "--steps", "90")
+    losses = [float(l.split("loss")[1]) for l in out.splitlines() if l.startswith("step")]
+    assert losses[-1] < 0.2 < losses[0]
+    assert "sample: the quick brown fox jumps over the lazy dog." in out

@@ -122,3 +122,79 @@ def test_small_convolutional_network_trains_like_pytorch():
     assert all(abs(a - b) < 2e-3 for a, b in losses) and losses[-1][0] < losses[0][0]
     assert np.allclose(net.mods[0].weight.numpy(), ref[0].weight.detach().numpy(), atol=2e-3)
     assert np.allclose(net.mods[6].weight.numpy(), ref[6].weight.detach().numpy(), atol=2e-3)
+
+
+def test_permute_batched_matmul_layer_norm_embedding_and_suffix_broadcast_match_pytorch():
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    _check(lambda t: t.permute(0, 2, 1, 3).reshape(2, 4, 15), lambda t: t.permute(0, 2, 1, 3).reshape(2, 4, 15), x)
+    _check(lambda t: t.transpose(1, 3), lambda t: t.transpose(1, 3).contiguous(), x)
+    a, b = rng.standard_normal((2, 3, 4, 5)).astype(np.float32), rng.standard_normal((2, 3, 5, 6)).astype(np.float32)
+    _check(lambda p, q: p @ q, lambda p, q: p @ q, a, b, tol=1e-4)
+    _check(lambda p, q: p @ q.transpose(2, 3), lambda p, q: p @ q.transpose(2, 3), a, rng.standard_normal((2, 3, 7, 5)).astype(np.float32), tol=1e-4)
+    w, bias = rng.standard_normal(5).astype(np.float32), rng.standard_normal(5).astype(np.float32)
+    _check(lambda t, u, v: N.layer_norm(t, u, v), lambda t, u, v: torch.nn.functional.layer_norm(t, (5,), u, v), x, w, bias, tol=1e-4)
+    _check(lambda t: N.layer_norm(t), lambda t: torch.nn.functional.layer_norm(t, (5,)), x, tol=1e-4)
+    _check(lambda t, u: N.layer_norm(t, u), lambda t, u: torch.nn.functional.layer_norm(t, (5,), u), x, w, tol=1e-4)
+    _check(lambda t: t.narrow(2, 1, 2).reshape(2, 3, 10) * 2.0, lambda t: t.narrow(2, 1, 2).reshape(2, 3, 10) * 2.0, x)
+    _check(lambda t: t[1] + t[0] + t[-1], lambda t: t[1] + t[0] + t[-1], x)
+    _check(lambda t: t.permute(1, 0, 2, 3)[1:3], lambda t: t.permute(1, 0, 2, 3)[1:3], x)
+    mask = np.triu(np.full((4, 4), -1e4, np.float32), 1)
+    s = rng.standard_normal((2, 3, 4, 4)).astype(np.float32)
+    _check(lambda t, m: (t + m).softmax(), lambda t, m: torch.softmax(t + m, -1), s, mask)                          # a [S, S] mask under [B, H, S, S]
+    _check(lambda t, m: t * m, lambda t, m: t * m, x, rng.standard_normal((4, 5)).astype(np.float32))
+    ids = rng.integers(0, 9, (3, 6))
+    table = rng.standard_normal((9, 4)).astype(np.float32)
+    tn, tt = _t(table), torch.tensor(table, requires_grad=True)
+    en, et = N.embedding(ids, tn), torch.nn.functional.embedding(torch.tensor(ids), tt)
+    assert en.shape == (3, 6, 4) and np.allclose(en.numpy(), et.detach().numpy())
+    en.square().sum().backward()
+    et.square().sum().backward()
+    assert np.allclose(tn.grad.numpy(), tt.grad.numpy(), atol=1e-5)
+    for bad in (lambda: _t(x).narrow(1, 2, 5), lambda: _t(x)[::2], lambda: _t(x).permute(0, 1, 1, 2), lambda: _t(a) @ _t(a), lambda: N.embedding([[9]], tn), lambda: N.layer_norm(_t(x), _t(np.ones(4))),
+                lambda: _t(x) + _t(np.ones((3, 5), np.float32))):
+        with pytest.raises(Exception):
+            bad()
+
+
+def test_transformer_block_forward_and_backward_match_pytorch():
+    """Pre-norm block with causal multi-head attention and a GELU MLP written on the native core against the same arithmetic in PyTorch."""
+    rng = np.random.default_rng(7)
+    B, S, D, H = 2, 6, 16, 4
+    names = ["wq", "wk", "wv", "wo", "w1", "w2"]
+    shapes = {"wq": (D, D), "wk": (D, D), "wv": (D, D), "wo": (D, D), "w1": (4 * D, D), "w2": (D, 4 * D)}
+    P = {n: (rng.standard_normal(shapes[n]) / np.sqrt(shapes[n][1])).astype(np.float32) for n in names}
+    x = rng.standard_normal((B, S, D)).astype(np.float32)
+    mask = np.triu(np.full((S, S), -1e4, np.float32), 1)
+
+    def block_native(xt, p):
+        def heads(t):
+            return t.reshape(B, S, H, D // H).permute(0, 2, 1, 3)
+        h = N.layer_norm(xt)
+        q, k, v = (heads(N.linear(h.reshape(B * S, D), p[n]).reshape(B, S, D)) for n in ("wq", "wk", "wv"))
+        att = ((q @ k.transpose(2, 3)) * (1.0 / np.sqrt(D // H)) + N.Tensor(mask)).softmax()
+        o = (att @ v).permute(0, 2, 1, 3).reshape(B * S, D)
+        xt = xt + N.linear(o, p["wo"]).reshape(B, S, D)
+        m = N.linear(N.linear(N.layer_norm(xt).reshape(B * S, D), p["w1"]).gelu(), p["w2"]).reshape(B, S, D)
+        return xt + m
+
+    def block_torch(xt, p):
+        F = torch.nn.functional
+        def heads(t):
+            return t.reshape(B, S, H, D // H).permute(0, 2, 1, 3)
+        h = F.layer_norm(xt, (D,))
+        q, k, v = (heads(h @ p[n].t()) for n in ("wq", "wk", "wv"))
+        att = torch.softmax((q @ k.transpose(2, 3)) / np.sqrt(D // H) + torch.tensor(mask), -1)
+        o = (att @ v).permute(0, 2, 1, 3).reshape(B, S, D)
+        xt = xt + o @ p["wo"].t()
+        return xt + F.gelu(F.layer_norm(xt, (D,)) @ p["w1"].t()) @ p["w2"].t()
+    pn = {n: _t(P[n]) for n in names}
+    pt = {n: torch.tensor(P[n], requires_grad=True) for n in names}
+    xn, xt = _t(x), torch.tensor(x, requires_grad=True)
+    yn, yt = block_native(xn, pn), block_torch(xt, pt)
+    assert np.allclose(yn.numpy(), yt.detach().numpy(), atol=2e-4)
+    yn.square().mean().backward(threads=2)
+    yt.square().mean().backward()
+    assert np.allclose(xn.grad.numpy(), xt.grad.numpy(), atol=2e-4)
+    for n in names:
+        assert np.allclose(pn[n].grad.numpy(), pt[n].grad.numpy(), atol=2e-4), n
