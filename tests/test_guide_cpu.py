@@ -63,3 +63,22 @@ def test_guide_snippets(tmp_path):
         proc.advance(vocab[tokenize._bytes_to_unicode()[ord(ch)]])
     allowed = {texts[i] for i in proc.mask().allowed.nonzero().flatten().tolist()}
     assert allowed == set("-0123456789n")
+    # 11. native core
+    import numpy as np
+    from ferrotorch_b200 import native as N
+    rng = np.random.default_rng(0)
+    images, labels = rng.standard_normal((8, 1, 14, 14)).astype(np.float32), rng.integers(0, 10, 8)
+    net = N.Sequential(N.Conv2d(1, 8, 3, padding=1), N.ReLU(), N.MaxPool2d(2), N.Flatten(), N.Linear(8 * 7 * 7, 10))
+    opt = N.AdamW(net.parameters(), lr=3e-3)
+    first = None
+    for _ in range(5):
+        opt.zero_grad()
+        loss = N.cross_entropy(net(N.Tensor(images)), labels)
+        loss.backward(threads=4)
+        opt.step()
+        first = first if first is not None else loss.item()
+    assert loss.item() < first
+    ids, table = rng.integers(0, 5, (2, 3)), N.Tensor(rng.standard_normal((5, 4)).astype(np.float32))
+    hq = N.layer_norm(N.embedding(ids, table)).reshape(1, 2, 3, 4)
+    att = (hq @ hq.transpose(2, 3) + N.Tensor(np.zeros((3, 3), np.float32))).softmax() @ hq
+    assert att.shape == (1, 2, 3, 4)
