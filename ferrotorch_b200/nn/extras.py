@@ -340,17 +340,7 @@ class GELU(Module):
         return f"approximate={self.approximate!r}"
 
 
-def interpolate(x, size=None, scale_factor=None, mode="nearest", align_corners=None, **kw):
-    """``F.interpolate`` that also takes an :class:`InterpolateMode`."""
-    return F.interpolate(x, size=size, scale_factor=scale_factor, mode=_enum_value(mode), align_corners=align_corners, **kw)
-
-
-def grid_sample(x, grid, mode="bilinear", padding_mode="zeros", align_corners=False):
-    """``F.grid_sample`` that also takes :class:`GridSampleMode` / :class:`GridSamplePaddingMode`."""
-    return F.grid_sample(x, grid, mode=_enum_value(mode), padding_mode=_enum_value(padding_mode), align_corners=align_corners)
-
-
-affine_grid = F.affine_grid
+from .resample import affine_grid, grid_sample, interpolate  # noqa: E402,F401  (written out on gather arithmetic: nn/resample.py)
 
 # functional pooling / reshaping forms the reference exports at the crate root (ferrotorch-nn/src/pooling.rs, upsample.rs)
 from .pooling import (max_pool1d, max_pool2d, max_pool3d, avg_pool1d, avg_pool2d, avg_pool3d, adaptive_avg_pool1d, adaptive_avg_pool2d,  # noqa: E402,F401
