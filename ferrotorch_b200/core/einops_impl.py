@@ -6,7 +6,7 @@ groups, ``1`` axes, an ellipsis, axis lengths by keyword, reductions sum / mean 
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import Dict, List
 
 import torch
 

@@ -12,9 +12,8 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import List, NamedTuple, Optional, Sequence, Tuple
+from typing import NamedTuple, Optional, Sequence
 
-import numpy as np
 import torch
 from torch.autograd.function import once_differentiable
 

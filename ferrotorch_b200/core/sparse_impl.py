@@ -8,7 +8,7 @@ conversions, ``spmm``, ``add``, ``coalesce``, ``t``).
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import torch
 

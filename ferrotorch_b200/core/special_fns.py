@@ -7,7 +7,6 @@ orthogonal-polynomial families). ``log1p`` / ``expm1`` stay the substrate's prim
 from __future__ import annotations
 
 import math
-from typing import Union
 
 import torch
 

@@ -9,7 +9,7 @@ Reference parity: ferrotorch-nn/src/upsample.rs:140 (interpolate), :672 (Upsampl
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 

@@ -8,7 +8,7 @@ and the common ones beside them, are implemented here.
 from __future__ import annotations
 
 import unicodedata
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import regex as _re
 
