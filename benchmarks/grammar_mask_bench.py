@@ -22,6 +22,7 @@ from pathlib import Path
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--threads", type=int, default=1, help="worker threads of the native walk")
     ap.add_argument("--python-vocab", type=int, default=8192, help="entries the Python matcher is timed on (scaled to --vocab in the output)")
     a = ap.parse_args()
     sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
@@ -43,6 +44,7 @@ def main():
              '{"name": "Ada", "age": 36, "scores": [1.5, 2.25, 3], "address": {"city": "London", "zip": "N1 9GU"}}']
     proc = G.JsonSchemaProcessor(schema, vocab, eos_id=len(vocab) - 1)
     assert proc._native is not None
+    proc.threads = a.threads
     os.environ["FT_GRAMMAR_NATIVE"] = "0"
     small = G.JsonSchemaProcessor(schema, vocab[: a.python_vocab] + ["<eos>"], eos_id=a.python_vocab)
     nat, py, allowed = [], [], []
@@ -59,7 +61,7 @@ def main():
         mp = small._mask_py()
         py.append((time.perf_counter() - t0) * 1e3 * a.vocab / (a.python_vocab + 1))
         assert bool((mp.allowed[: a.python_vocab] == m.allowed[: a.python_vocab]).all())
-    print(json.dumps({"bench": "json_schema_token_mask", "vocab": len(vocab), "cpus": os.cpu_count(), "positions": len(texts), "allowed": allowed,
+    print(json.dumps({"bench": "json_schema_token_mask", "vocab": len(vocab), "cpus": os.cpu_count(), "threads": a.threads, "positions": len(texts), "allowed": allowed,
                       "native_ms_per_mask": [round(x, 2) for x in nat], "python_ms_per_mask_scaled": [round(x, 1) for x in py],
                       "speedup_median": round(statistics.median(p / n for p, n in zip(py, nat)), 1)}))
 

@@ -28,7 +28,13 @@ struct Grammar {
   std::vector<Node> nodes;                                    // node 0 is the root
   std::string vocab;                                          // all entries back to back
   std::vector<int64_t> voff;
+  std::vector<uint8_t> plain;                                 // per entry: no quote, no backslash, no control byte (stays inside a string body)
 };
+
+// Where the innermost matcher ran out of text on the last PARTIAL outcome of this thread: inside the body of a string (not right after a
+// backslash) or anywhere else. A text that ends inside a string body stays valid under any continuation made of plain characters, which lets
+// the mask skip the re-parse for most of the vocabulary while a string is being generated.
+thread_local bool g_ended_in_string_body = false;
 
 // Outcome of matching a value that starts at a position of the text.
 enum Tag : int { INVALID = 0, PARTIAL = 1, OPEN = 2, POS = 3 };   // PARTIAL: text ended inside a still-valid value; OPEN: a number that is complete
@@ -40,6 +46,7 @@ constexpr int MAX_DEPTH = 256;
 inline bool digit(char c) { return c >= '0' && c <= '9'; }
 
 R lit(sv l, sv t, int64_t i) {
+  g_ended_in_string_body = false;
   const int64_t n = (int64_t)t.size() - i, m = (int64_t)l.size();
   if (n >= m) return t.compare((size_t)i, (size_t)m, l) == 0 ? R{POS, i + m} : R{INVALID, 0};
   return l.compare(0, (size_t)n, t.substr((size_t)i)) == 0 ? R{PARTIAL, 0} : R{INVALID, 0};
@@ -47,6 +54,7 @@ R lit(sv l, sv t, int64_t i) {
 
 R string_(sv t, int64_t i) {
   const int64_t n = (int64_t)t.size();
+  g_ended_in_string_body = false;
   if (i >= n) return {PARTIAL, 0};
   if (t[i] != '"') return {INVALID, 0};
   i++;
@@ -62,10 +70,12 @@ R string_(sv t, int64_t i) {
     if (c < 0x20) return {INVALID, 0};
     i++;
   }
+  g_ended_in_string_body = true;
   return {PARTIAL, 0};
 }
 
 R number_(sv t, int64_t i, bool integer) {
+  g_ended_in_string_body = false;
   const int64_t n = (int64_t)t.size();
   int64_t j = i;
   if (j >= n) return {PARTIAL, 0};
@@ -106,11 +116,12 @@ R array_(const Grammar& g, int32_t items, sv t, int64_t i, int depth) {      // 
   const int64_t n = (int64_t)t.size();
   if (t[i] != '[') return {INVALID, 0};
   i++;
-  if (i >= n) return {PARTIAL, 0};
+  if (i >= n) { g_ended_in_string_body = false; return {PARTIAL, 0}; }
   if (t[i] == ']') return {POS, i + 1};
   for (;;) {
     const R r = items >= 0 ? value(g, items, t, i, depth + 1) : value_any(g, t, i, depth + 1);
     if (r.tag == INVALID || r.tag == PARTIAL) return r;
+    g_ended_in_string_body = false;                       // the element is complete: whatever follows is structure
     if (r.tag == OPEN) return {PARTIAL, 0};
     i = r.pos;
     if (i >= n) return {PARTIAL, 0};
@@ -123,6 +134,7 @@ R array_(const Grammar& g, int32_t items, sv t, int64_t i, int depth) {      // 
 
 R object_(const Grammar& g, const Node* s, sv t, int64_t i, int depth) {      // s null: no properties
   const int64_t n = (int64_t)t.size();
+  g_ended_in_string_body = false;
   if (t[i] != '{') return {INVALID, 0};
   i++;
   if (!s || s->edges.empty()) {
@@ -157,6 +169,7 @@ R object_(const Grammar& g, const Node* s, sv t, int64_t i, int depth) {      //
     i = sep(t, i + 1);
     r = value(g, props[idx].child, t, i, depth + 1);
     if (r.tag == INVALID || r.tag == PARTIAL) return r;
+    g_ended_in_string_body = false;                       // the property value is complete
     if (r.tag == OPEN) return {PARTIAL, 0};
     i = r.pos;
     first = false;
@@ -172,7 +185,7 @@ R boolean_(sv t, int64_t i) {
 
 R value_any(const Grammar& g, sv t, int64_t i, int depth) {
   if (depth > MAX_DEPTH) return {INVALID, 0};
-  if (i >= (int64_t)t.size()) return {PARTIAL, 0};
+  if (i >= (int64_t)t.size()) { g_ended_in_string_body = false; return {PARTIAL, 0}; }
   R r = string_(t, i);
   if (r.tag != INVALID) return r;
   r = number_(t, i, false);
@@ -188,7 +201,7 @@ R value_any(const Grammar& g, sv t, int64_t i, int depth) {
 
 R value(const Grammar& g, int32_t node, sv t, int64_t i, int depth) {
   if (depth > MAX_DEPTH) return {INVALID, 0};
-  if (i >= (int64_t)t.size()) return {PARTIAL, 0};
+  if (i >= (int64_t)t.size()) { g_ended_in_string_body = false; return {PARTIAL, 0}; }
   const Node& s = g.nodes[(size_t)node];
   switch (s.kind) {
     case K_STRING: return string_(t, i);
@@ -245,6 +258,15 @@ FT_API void* ft_json_grammar_create(const int32_t* kind, const int32_t* edge_fir
   }
   g->vocab.assign((const char*)vocab, (size_t)voff[n_vocab]);
   g->voff.assign(voff, voff + n_vocab + 1);
+  g->plain.resize((size_t)n_vocab);
+  for (int64_t v = 0; v < n_vocab; v++) {
+    bool ok = voff[v + 1] > voff[v];
+    for (int64_t k = voff[v]; k < voff[v + 1] && ok; k++) {
+      const unsigned char c = vocab[k];
+      ok = c != '"' && c != '\\' && c >= 0x20;
+    }
+    g->plain[(size_t)v] = ok ? 1 : 0;
+  }
   return g;
 }
 
@@ -267,17 +289,33 @@ FT_API int64_t ft_json_grammar_mask(void* h, const uint8_t* text, int64_t n, int
   const int64_t V = (int64_t)g.voff.size() - 1;
   const bool done = complete(g, t);
   const bool closed = done && g.nodes[0].kind != K_NUMBER && g.nodes[0].kind != K_INTEGER;
+  g_ended_in_string_body = false;
+  const R whole = value(g, 0, t, 0, 0);
+  const bool in_string = whole.tag == PARTIAL && g_ended_in_string_body;       // text ends inside a string body: plain entries need no re-parse
   nthreads = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(nthreads, 64), V / 2048));
+  if (closed) nthreads = 1;                               // nothing to parse: starting threads would cost more than the loop
   std::vector<int64_t> counts((size_t)nthreads, 0);
   auto work = [&](int k) {
     const int64_t lo = V * k / nthreads, hi = V * (k + 1) / nthreads;
     std::string buf(t);
     int64_t c = 0;
+    int8_t first_ok[256];                                 // does text + this byte still parse? (-1: not asked yet) An entry whose first byte
+    std::memset(first_ok, -1, sizeof(first_ok));          // already fails cannot be valid: the matcher never recovers from an invalid prefix
     for (int64_t v = lo; v < hi; v++) {
       bool ok;
       const int64_t len = g.voff[(size_t)v + 1] - g.voff[(size_t)v];
       if (v == eos_id) ok = done;
       else if (len == 0 || closed) ok = false;
+      else if (in_string && g.plain[(size_t)v]) ok = true;
+      else if (len > 1 && [&] {
+                 const unsigned char b0 = (unsigned char)g.vocab[(size_t)g.voff[(size_t)v]];
+                 if (first_ok[b0] < 0) {
+                   buf.resize((size_t)n);
+                   buf.push_back((char)b0);
+                   first_ok[b0] = valid(g, buf) ? 1 : 0;
+                 }
+                 return first_ok[b0] == 0;
+               }()) ok = false;
       else {
         buf.resize((size_t)n);
         buf.append(g.vocab.data() + g.voff[(size_t)v], (size_t)len);

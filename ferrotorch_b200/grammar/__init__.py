@@ -412,6 +412,9 @@ class JsonSchemaProcessor:
         self.eos_id = eos_id
         self.text = ""
         self._native = None
+        # Worker threads of the native vocabulary walk. One by default: a walk costs 0.3 - 3 ms on one core, and threads started next to a
+        # process whose math library keeps its own workers spinning are scheduled late more often than they help.
+        self.threads = 1
         if os.environ.get("FT_GRAMMAR_NATIVE", "1") != "0":
             self._build_native()
 
@@ -435,6 +438,7 @@ class JsonSchemaProcessor:
                                       ctypes.c_int64(len(vocab)))
         if h:
             self._native, self._rt = ctypes.c_void_p(h), rt
+            self._mask_buf = np.zeros(max(len(vocab), 1), np.uint8)
 
     def __del__(self):
         h, self._native = getattr(self, "_native", None), None
@@ -469,10 +473,10 @@ class JsonSchemaProcessor:
 
     def mask(self) -> TokenMask:
         if self._native is not None:
-            allowed = np.empty(max(len(self.vocab), 1), np.uint8)
+            allowed = self._mask_buf                  # one buffer for the life of the processor: a fresh 128 KB array per step costs page faults
             raw = self.text.encode("utf-8")
             self._rt.ft_json_grammar_mask(self._native, ctypes.c_char_p(raw), ctypes.c_int64(len(raw)), ctypes.c_int64(-1 if self.eos_id is None else self.eos_id),
-                                          allowed.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(min(os.cpu_count() or 1, 16)))
+                                          allowed.ctypes.data_as(ctypes.c_void_p), ctypes.c_int(self.threads))
             return TokenMask(torch.from_numpy(allowed[: len(self.vocab)]).to(torch.bool))
         return self._mask_py()
 
