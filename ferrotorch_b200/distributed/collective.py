@@ -168,17 +168,47 @@ def sendrecv(tensor: torch.Tensor, dst: int, src: int, backend: Backend, timeout
 
 
 # -- async handles (ferrotorch-distributed/src/async_collective.rs:16-133) ----------------------------------------------
-class PendingCollective:
-    """A collective running on a background thread; ``wait()`` returns its result or re-raises its error."""
+_turns_lock = threading.Lock()
 
-    def __init__(self, fn, *args):
+
+def _turn_state(backend):
+    """[tickets issued, tickets served, condition] of a backend, kept on the backend object."""
+    with _turns_lock:
+        st = getattr(backend, "_async_turns", None)
+        if st is None:
+            st = [0, 0, threading.Condition()]
+            backend._async_turns = st
+        return st
+
+
+class PendingCollective:
+    """A collective running on a background thread; ``wait()`` returns its result or re-raises its error.
+
+    The channels of a backend are untagged, so two collectives must not interleave on one rank. Each handle takes a ticket from its backend
+    when it is created (in the caller's thread, that is in program order) and its thread runs the collective when the ticket comes up:
+    several handles may be outstanding at once, and they execute in the order they were issued, the same on every rank."""
+
+    def __init__(self, fn, *args, _backend=None, **kwargs):
         self._result, self._error = None, None
+        st = _turn_state(_backend) if _backend is not None else None
+        if st is not None:
+            with st[2]:
+                ticket = st[0]
+                st[0] += 1
 
         def run():
+            if st is not None:
+                with st[2]:
+                    st[2].wait_for(lambda: st[1] == ticket)
             try:
-                self._result = fn(*args)
+                self._result = fn(*args, **kwargs)
             except BaseException as e:  # converted to an error for the waiter, as thread panics are in the reference
                 self._error = e
+            finally:
+                if st is not None:
+                    with st[2]:
+                        st[1] += 1
+                        st[2].notify_all()
         self._t = threading.Thread(target=run, daemon=True)
         self._t.start()
 
@@ -197,12 +227,12 @@ class PendingCollective:
 
 
 def async_all_gather(tensor, backend, timeout=DEFAULT_COLLECTIVE_TIMEOUT) -> PendingCollective:
-    return PendingCollective(all_gather, tensor, backend, timeout)
+    return PendingCollective(all_gather, tensor, backend, timeout, _backend=backend)
 
 
 def async_reduce_scatter(tensor, backend, op=ReduceOp.Sum, timeout=DEFAULT_COLLECTIVE_TIMEOUT) -> PendingCollective:
-    return PendingCollective(reduce_scatter, tensor, backend, op, timeout)
+    return PendingCollective(reduce_scatter, tensor, backend, op, timeout, _backend=backend)
 
 
 def async_allreduce(tensor, backend, op=ReduceOp.Sum, timeout=DEFAULT_COLLECTIVE_TIMEOUT) -> PendingCollective:
-    return PendingCollective(allreduce, tensor, backend, op, timeout)
+    return PendingCollective(allreduce, tensor, backend, op, timeout, _backend=backend)

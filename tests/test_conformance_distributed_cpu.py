@@ -111,3 +111,22 @@ def test_error_types_and_backend_contracts():
             return 2
     with pytest.raises(errors.InvalidArgument):
         fd.HybridBackend(a, FakeNccl())
+
+
+def test_several_outstanding_async_collectives_run_in_issue_order():
+    """Five handles outstanding at once on each rank, repeated: the ticket of each handle keeps the untagged channels from interleaving."""
+    def fn(b, r):
+        outs = []
+        for rep in range(6):
+            hs = [fd.async_allreduce(torch.full((3 + k,), float(r + 1 + k + rep)), b) for k in range(3)]
+            hs.append(fd.async_all_gather(torch.tensor([float(r), float(rep)]), b))
+            hs.append(fd.async_reduce_scatter(torch.arange(4.0) + rep, b))
+            outs.append([h.wait() for h in reversed(hs)][::-1])             # waited in reverse: execution order is the issue order all the same
+        return outs
+    res = _ranks(2, fn)
+    for r in range(2):
+        for rep, (a0, a1, a2, ag, rs) in enumerate(res[r]):
+            for k, a in enumerate((a0, a1, a2)):
+                assert a.shape == (3 + k,) and torch.equal(a, torch.full((3 + k,), float(1 + k + rep) + float(2 + k + rep)))
+            assert torch.equal(ag.flatten(), torch.tensor([0.0, float(rep), 1.0, float(rep)]))
+            assert torch.equal(rs, 2 * (torch.arange(4.0) + rep)[2 * r: 2 * r + 2])
