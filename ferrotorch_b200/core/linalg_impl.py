@@ -3,8 +3,8 @@ triangular solves, Householder QR, Jacobi eigen- and singular value decompositio
 formulas written here; everything else (determinants, inverses, least squares, pseudo-inverse, norms, rank, condition numbers, powers, the
 matrix exponential, chain products, ...) is composed from them, so it is differentiable by composition.
 
-Real f32 / f64 tensors on the host take this route. CUDA tensors, complex and half types go to the substrate's library call of the same name
-(cuSOLVER / LAPACK), as do ``eig`` / ``eigvals`` of general matrices.
+Real f32 / f64 tensors on the host take this route (``eig`` / ``eigvals`` of general matrices too, through a complex Schur form, when no
+derivative is asked of them). CUDA tensors, complex and half types go to the substrate's library call of the same name (cuSOLVER / LAPACK).
 
 Reference parity: ferrotorch-core/src/linalg.rs:121-2170 (35 functions) and grad_fns/linalg.rs:777-1780 (their derivatives).
 """
@@ -795,9 +795,25 @@ def ldl_solve(ld: torch.Tensor, pivots: torch.Tensor, b: torch.Tensor, hermitian
 
 
 def eig(a: torch.Tensor):
-    """General (non-symmetric) eigenproblem: the substrate's library call (complex results)."""
-    return L.eig(a)
+    """General (non-symmetric) eigenproblem: complex eigenvalues ``w`` [.., n] and unit eigenvectors in the columns of ``V`` [.., n, n] with
+    ``A V = V diag(w)``, from the complex Schur form computed in the runtime library (the order of the eigenvalues is that form's, not
+    LAPACK's). An input that takes part in differentiation goes to the substrate's library call, which carries the derivative."""
+    if not _own(a) or a.requires_grad:
+        return L.eig(a)
+    _square(a, "eig")
+    n = a.shape[-1]
+    a64 = a.detach().to(torch.float64).contiguous()
+    w = torch.zeros(*a.shape[:-2], n, 2, dtype=torch.float64)
+    v = torch.zeros(*a.shape[:-2], n, n, 2, dtype=torch.float64)
+    if n and _batch(a):
+        _rt().ft_la_eig.restype = ctypes.c_int
+        if _rt().ft_la_eig(_p(a64), _p(w), _p(v), _i64(_batch(a)), _i64(n)) < 0:
+            raise LinAlgError("linalg.eig: the QR iterations did not converge")
+    ct = torch.complex64 if a.dtype == torch.float32 else torch.complex128
+    return torch.view_as_complex(w).to(ct), torch.view_as_complex(v).to(ct)
 
 
 def eigvals(a: torch.Tensor):
-    return L.eigvals(a)
+    if not _own(a) or a.requires_grad:
+        return L.eigvals(a)
+    return eig(a)[0]

@@ -1,6 +1,7 @@
 // Dense factorisations on the host for `ferrotorch_b200.core.linalg`: Cholesky, LU with partial pivoting (and the solves built on it),
 // triangular solves, Householder QR, the symmetric eigenproblem by Householder tridiagonalisation + implicit QL iterations (cyclic Jacobi
-// rotations as the fallback) and the singular value decomposition by one-sided (Hestenes) Jacobi rotations. Row-major f64 at the interface
+// rotations as the fallback), the singular value decomposition by one-sided (Hestenes) Jacobi rotations and the general eigenproblem through
+// the complex Schur form (Hessenberg reduction + shifted QR). Row-major f64 at the interface
 // (the QR, QL and Jacobi loops work on transposed copies so that they run over contiguous memory), batched over a leading dimension with
 // the matrices of a batch spread over threads.
 // The Python side supplies f64 copies of f32 inputs and the derivative formulas.
@@ -10,6 +11,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <complex>
 #include <cstdint>
 #include <cstring>
 #include <thread>
@@ -534,4 +536,126 @@ FT_API int ft_la_svd(const double* a, double* u, double* s, double* vt, int64_t 
     while ((mine < 0 ? cur >= 0 : (cur >= 0 && mine > cur)) && !worst.compare_exchange_weak(cur, mine)) {}
   });
   return worst.load();
+}
+
+// General (non-symmetric) eigenproblem in complex arithmetic: Householder reduction to Hessenberg form, shifted QR iterations with Givens
+// rotations (Wilkinson shift, an exceptional shift every tenth iteration) down to the complex Schur form T = Q^H A Q, eigenvalues from the
+// diagonal of T, eigenvectors by back-substitution on T and multiplication by Q, each scaled to unit length with its largest component
+// real and positive. a [batch, n, n] real; w [batch, n, 2] (real, imaginary); v [batch, n, n, 2] with the eigenvectors in the columns.
+// Returns 1, or -1 if the iterations of some matrix did not converge.
+FT_API int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64_t n) {
+  using cd = std::complex<double>;
+  std::atomic<int> status{1};
+  for_batch(batch, n * n * n * 30 + 1, [&](int64_t b) {
+    std::vector<cd> H((size_t)(n * n)), Z((size_t)(n * n), cd(0.0)), u((size_t)n);
+    double norm = 0.0;
+    for (int64_t i = 0; i < n * n; i++) { H[(size_t)i] = a[b * n * n + i]; norm = std::max(norm, std::fabs(a[b * n * n + i])); }
+    for (int64_t i = 0; i < n; i++) Z[(size_t)(i * n + i)] = 1.0;
+    if (norm == 0.0) norm = 1.0;
+    for (int64_t k = 0; k + 2 < n; k++) {                               // Hessenberg: zero column k below the sub-diagonal
+      double xn = 0.0;
+      for (int64_t i = k + 1; i < n; i++) xn += std::norm(H[(size_t)(i * n + k)]);
+      xn = std::sqrt(xn);
+      if (xn == 0.0) continue;
+      const cd x0 = H[(size_t)((k + 1) * n + k)];
+      const cd alpha = (std::abs(x0) == 0.0 ? cd(1.0) : x0 / std::abs(x0)) * (-xn);
+      double un = 0.0;
+      for (int64_t i = k + 1; i < n; i++) { u[(size_t)i] = H[(size_t)(i * n + k)] - (i == k + 1 ? alpha : cd(0.0)); un += std::norm(u[(size_t)i]); }
+      if (un == 0.0) continue;
+      for (int64_t j = 0; j < n; j++) {                                 // H <- (I - 2 u u^H / u^H u) H
+        cd s = 0.0;
+        for (int64_t i = k + 1; i < n; i++) s += std::conj(u[(size_t)i]) * H[(size_t)(i * n + j)];
+        s *= 2.0 / un;
+        for (int64_t i = k + 1; i < n; i++) H[(size_t)(i * n + j)] -= s * u[(size_t)i];
+      }
+      for (int64_t i = 0; i < n; i++) {                                 // H <- H (I - 2 u u^H / u^H u), and the same on Z
+        cd s = 0.0, sz = 0.0;
+        for (int64_t j = k + 1; j < n; j++) { s += H[(size_t)(i * n + j)] * u[(size_t)j]; sz += Z[(size_t)(i * n + j)] * u[(size_t)j]; }
+        s *= 2.0 / un;
+        sz *= 2.0 / un;
+        for (int64_t j = k + 1; j < n; j++) { H[(size_t)(i * n + j)] -= s * std::conj(u[(size_t)j]); Z[(size_t)(i * n + j)] -= sz * std::conj(u[(size_t)j]); }
+      }
+    }
+    std::vector<cd> gc((size_t)n), gs((size_t)n);
+    int64_t hi = n - 1;
+    int iter = 0;
+    bool ok = true;
+    while (hi > 0) {
+      int64_t l = hi;
+      while (l > 0) {
+        double s = std::abs(H[(size_t)((l - 1) * n + l - 1)]) + std::abs(H[(size_t)(l * n + l)]);
+        if (s == 0.0) s = norm;
+        if (std::abs(H[(size_t)(l * n + l - 1)]) < 2.3e-16 * s) { H[(size_t)(l * n + l - 1)] = 0.0; break; }
+        l--;
+      }
+      if (l == hi) { hi--; iter = 0; continue; }
+      if (++iter > 300) { ok = false; break; }
+      const cd pa = H[(size_t)((hi - 1) * n + hi - 1)], pb = H[(size_t)((hi - 1) * n + hi)], pc = H[(size_t)(hi * n + hi - 1)], pd = H[(size_t)(hi * n + hi)];
+      const cd tr = pa + pd, disc = std::sqrt(tr * tr * 0.25 - (pa * pd - pb * pc));
+      const cd m1 = tr * 0.5 + disc, m2 = tr * 0.5 - disc;
+      cd mu = std::abs(m1 - pd) < std::abs(m2 - pd) ? m1 : m2;
+      if (iter % 10 == 0) mu = pd + cd(std::abs(pc) + (hi >= 2 ? std::abs(H[(size_t)((hi - 1) * n + hi - 2)]) : 0.0), 0.0);
+      for (int64_t k = l; k <= hi; k++) H[(size_t)(k * n + k)] -= mu;
+      for (int64_t k = l; k < hi; k++) {                                // rotations from the left make the active block upper triangular
+        const cd x = H[(size_t)(k * n + k)], y = H[(size_t)((k + 1) * n + k)];
+        const double r = std::sqrt(std::norm(x) + std::norm(y));
+        cd c = 1.0, s = 0.0;
+        if (r != 0.0) { c = x / r; s = y / r; }
+        gc[(size_t)k] = c;
+        gs[(size_t)k] = s;
+        for (int64_t j = k; j < n; j++) {
+          const cd t0 = H[(size_t)(k * n + j)], t1 = H[(size_t)((k + 1) * n + j)];
+          H[(size_t)(k * n + j)] = std::conj(c) * t0 + std::conj(s) * t1;
+          H[(size_t)((k + 1) * n + j)] = -s * t0 + c * t1;
+        }
+      }
+      for (int64_t k = l; k < hi; k++) {                                // the same rotations from the right restore the Hessenberg form
+        const cd c = gc[(size_t)k], s = gs[(size_t)k];
+        const int64_t top = std::min<int64_t>(k + 2, hi);
+        for (int64_t i = 0; i <= top; i++) {
+          const cd t0 = H[(size_t)(i * n + k)], t1 = H[(size_t)(i * n + k + 1)];
+          H[(size_t)(i * n + k)] = t0 * c + t1 * s;
+          H[(size_t)(i * n + k + 1)] = -t0 * std::conj(s) + t1 * std::conj(c);
+        }
+        for (int64_t i = 0; i < n; i++) {
+          const cd t0 = Z[(size_t)(i * n + k)], t1 = Z[(size_t)(i * n + k + 1)];
+          Z[(size_t)(i * n + k)] = t0 * c + t1 * s;
+          Z[(size_t)(i * n + k + 1)] = -t0 * std::conj(s) + t1 * std::conj(c);
+        }
+      }
+      for (int64_t k = l; k <= hi; k++) H[(size_t)(k * n + k)] += mu;
+    }
+    if (!ok) { status.store(-1); return; }
+    std::vector<cd> y((size_t)n);
+    for (int64_t k = 0; k < n; k++) {
+      const cd lam = H[(size_t)(k * n + k)];
+      w[(b * n + k) * 2] = lam.real();
+      w[(b * n + k) * 2 + 1] = lam.imag();
+      y[(size_t)k] = 1.0;
+      for (int64_t i = k - 1; i >= 0; i--) {                            // (T - lambda I) y = 0 on the leading block
+        cd s = 0.0;
+        for (int64_t j = i + 1; j <= k; j++) s += H[(size_t)(i * n + j)] * y[(size_t)j];
+        cd d = H[(size_t)(i * n + i)] - lam;
+        if (std::abs(d) < 2.3e-16 * norm) d = 2.3e-16 * norm;
+        y[(size_t)i] = -s / d;
+      }
+      double vn = 0.0, biggest = -1.0;
+      cd phase = 1.0;
+      for (int64_t i = 0; i < n; i++) {
+        cd s = 0.0;
+        for (int64_t j = 0; j <= k; j++) s += Z[(size_t)(i * n + j)] * y[(size_t)j];
+        u[(size_t)i] = s;
+        vn += std::norm(s);
+        if (std::abs(s) > biggest) { biggest = std::abs(s); phase = s; }
+      }
+      vn = std::sqrt(vn);
+      const cd scale = (vn == 0.0 || biggest <= 0.0) ? cd(1.0) : std::conj(phase) / (std::abs(phase) * vn);
+      for (int64_t i = 0; i < n; i++) {
+        const cd e = u[(size_t)i] * scale;
+        v[((b * n + i) * n + k) * 2] = e.real();
+        v[((b * n + i) * n + k) * 2 + 1] = e.imag();
+      }
+    }
+  });
+  return status.load();
 }

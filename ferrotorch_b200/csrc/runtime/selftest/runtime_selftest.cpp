@@ -59,6 +59,7 @@ int ft_la_trsm(const double* t, double* bmat, int64_t batch, int64_t n, int64_t 
 int ft_la_qr(const double* a, double* q, double* r, int64_t batch, int64_t m, int64_t n, int complete);
 int ft_la_eigh(const double* a, double* w, double* v, int64_t batch, int64_t n, int lower);
 int ft_la_svd(const double* a, double* u, double* s, double* vt, int64_t batch, int64_t m, int64_t n);
+int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64_t n);
 int64_t ft_bpe_encode_texts(void* h, int kind, const uint8_t* bytes, const int64_t* off, int64_t n_texts, int32_t* out, int64_t out_cap, int64_t* out_off,
                             int nthreads);
 }
@@ -345,6 +346,23 @@ static void test_linalg() {
   CHECK(maxerr(usv, rect) < 1e-10);
   for (int64_t b = 0; b < batch; b++)
     for (int64_t k = 0; k + 1 < n; k++) CHECK(sv[(size_t)(b * n + k)] >= sv[(size_t)(b * n + k + 1)]);
+  std::vector<double> ew((size_t)(batch * n * 2)), ev((size_t)(batch * n * n * 2));
+  CHECK(ft_la_eig(a.data(), ew.data(), ev.data(), batch, n) == 1);
+  double worst = 0.0;                                      // A v - lambda v, real and imaginary parts, for every pair of every matrix
+  for (int64_t b = 0; b < batch; b++)
+    for (int64_t k = 0; k < n; k++) {
+      const double lr = ew[(size_t)((b * n + k) * 2)], li = ew[(size_t)((b * n + k) * 2 + 1)];
+      for (int64_t i = 0; i < n; i++) {
+        double sr = 0, si = 0;
+        for (int64_t j = 0; j < n; j++) {
+          sr += a[(size_t)(b * n * n + i * n + j)] * ev[(size_t)(((b * n + j) * n + k) * 2)];
+          si += a[(size_t)(b * n * n + i * n + j)] * ev[(size_t)(((b * n + j) * n + k) * 2 + 1)];
+        }
+        const double vr = ev[(size_t)(((b * n + i) * n + k) * 2)], vi = ev[(size_t)(((b * n + i) * n + k) * 2 + 1)];
+        worst = std::max(worst, std::max(std::fabs(sr - (lr * vr - li * vi)), std::fabs(si - (lr * vi + li * vr))));
+      }
+    }
+  CHECK(worst < 1e-10);
 }
 
 int main() {

@@ -223,3 +223,48 @@ def test_householder_product_gradient_and_dtype_of_gradients():
     x = torch.randn(4, 4, requires_grad=True)
     M.inv(x).sum().backward()
     assert x.grad.dtype == torch.float32
+
+
+def _sorted_eigs(w):
+    flat = w.reshape(-1, w.shape[-1])
+    rows = []
+    for r in flat:
+        order = sorted(range(len(r)), key=lambda i: (round(r[i].real.item(), 5), round(r[i].imag.item(), 5)))
+        rows.append(r[order])
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("dt,tol", [(torch.float64, 1e-9), (torch.float32, 2e-4)])
+@pytest.mark.parametrize("shape", [(1, 1), (2, 2), (3, 3), (6, 6), (4, 5, 5), (30, 30), (64, 64)])
+def test_general_eigenproblem_through_the_complex_schur_form(dt, tol, shape):
+    """Eigenvalues equal the library's as a set; every returned pair satisfies A v = lambda v with a unit vector whose largest component
+    is real and positive."""
+    torch.manual_seed(sum(shape))
+    a = torch.randn(shape, dtype=dt)
+    (w, v), (w2, v2) = M.eig(a), L.eig(a)
+    assert w.dtype == w2.dtype and v.shape == v2.shape and v.dtype == v2.dtype
+    assert (a.to(v.dtype) @ v - v * w.unsqueeze(-2)).abs().max() < tol * 50 * max(1.0, a.abs().max().item() * shape[-1])
+    assert ((v.abs() ** 2).sum(-2).sqrt() - 1).abs().max() < tol * 10
+    assert (_sorted_eigs(w) - _sorted_eigs(w2)).abs().max() < tol * 1000
+    assert (_sorted_eigs(M.eigvals(a)) - _sorted_eigs(w2)).abs().max() < tol * 1000
+    big = v.abs().argmax(-2, keepdim=True)
+    lead = v.gather(-2, big)
+    assert lead.imag.abs().max() < tol * 10 and (lead.real > 0).all()
+
+
+def test_general_eigenproblem_special_matrices_and_routes():
+    rot = torch.tensor([[0.0, 1.0], [-1.0, 0.0]], dtype=D)
+    w = M.eigvals(rot)
+    assert torch.allclose(_sorted_eigs(w)[0], torch.tensor([-1j, 1j], dtype=torch.complex128))
+    for a in (torch.zeros(3, 3, dtype=D), torch.eye(4, dtype=D), torch.tensor([[2.0, 1.0], [0.0, 2.0]], dtype=D), torch.triu(torch.randn(5, 5, dtype=D))):
+        w, v = M.eig(a)
+        assert (a.to(v.dtype) @ v - v * w.unsqueeze(-2)).abs().max() < 1e-12
+        assert torch.allclose(_sorted_eigs(w)[0].real, torch.sort(torch.diagonal(a)).values)
+    sym = torch.randn(6, 6, dtype=D)
+    sym = sym + sym.T
+    assert torch.allclose(torch.sort(M.eigvals(sym).real).values, M.eigvalsh(sym), atol=1e-10) and M.eigvals(sym).imag.abs().max() < 1e-10
+    g = torch.randn(4, 4, dtype=D, requires_grad=True)                  # a derivative is asked: the library call carries it
+    M.eig(g)[0].abs().sum().backward()
+    assert g.grad is not None and g.grad.shape == (4, 4)
+    with pytest.raises(Exception):
+        M.eig(torch.randn(2, 3))
