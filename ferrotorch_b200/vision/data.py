@@ -22,6 +22,7 @@ import torch.nn.functional as F
 
 from ..data import Dataset
 from ..errors import InvalidArgument
+from ..nn import resample as _resample
 
 
 # -- image IO (PNG/JPEG via Pillow, PPM natively) ---------------------------------------------------------------------------------------
@@ -352,7 +353,7 @@ class Resize:
         self.size, self.mode = (size, size) if isinstance(size, int) else tuple(size), mode
 
     def __call__(self, x):
-        return F.interpolate(x.unsqueeze(0).float(), self.size, mode=self.mode, align_corners=False if self.mode != "nearest" else None).squeeze(0)
+        return _resample.interpolate(x.unsqueeze(0).float(), self.size, mode=self.mode, align_corners=False if self.mode != "nearest" else None).squeeze(0)
 
 
 class CenterCrop:
@@ -417,8 +418,8 @@ class RandomRotation:
     def __call__(self, x):
         a = math.radians(_vision_rng.uniform(-self.degrees, self.degrees))
         theta = torch.tensor([[math.cos(a), -math.sin(a), 0.0], [math.sin(a), math.cos(a), 0.0]]).unsqueeze(0)
-        grid = F.affine_grid(theta, [1, *x.shape], align_corners=False)
-        return F.grid_sample(x.unsqueeze(0).float(), grid, align_corners=False).squeeze(0)
+        grid = _resample.affine_grid(theta, [1, *x.shape], align_corners=False)
+        return _resample.grid_sample(x.unsqueeze(0).float(), grid, align_corners=False).squeeze(0)
 
 
 class ColorJitter:
@@ -496,7 +497,7 @@ class ElasticTransform:
         d = F.conv2d(F.pad(d, [0, 0, k // 2, k // 2], mode="reflect"), g.view(1, 1, -1, 1).repeat(2, 1, 1, 1), groups=2) * self.alpha
         ys, xs = torch.meshgrid(torch.linspace(-1, 1, h), torch.linspace(-1, 1, w), indexing="ij")
         grid = torch.stack([xs + d[0, 0] * 2 / w, ys + d[0, 1] * 2 / h], -1).unsqueeze(0)
-        return F.grid_sample(x.unsqueeze(0).float(), grid, align_corners=True, padding_mode="reflection").squeeze(0)
+        return _resample.grid_sample(x.unsqueeze(0).float(), grid, align_corners=True, padding_mode="reflection").squeeze(0)
 
 
 class TrivialAugmentWide:
