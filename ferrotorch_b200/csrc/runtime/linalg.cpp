@@ -550,8 +550,8 @@ FT_API int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64
     std::vector<cd> H((size_t)(n * n)), Z((size_t)(n * n), cd(0.0)), u((size_t)n);
     double norm = 0.0;
     for (int64_t i = 0; i < n * n; i++) { H[(size_t)i] = a[b * n * n + i]; norm = std::max(norm, std::fabs(a[b * n * n + i])); }
-    for (int64_t i = 0; i < n; i++) Z[(size_t)(i * n + i)] = 1.0;
-    if (norm == 0.0) norm = 1.0;
+    for (int64_t i = 0; i < n; i++) Z[(size_t)(i * n + i)] = 1.0;      // Z is kept transposed (row j = column j of the accumulated
+    if (norm == 0.0) norm = 1.0;                                        // transformation), so a rotation of two columns touches two contiguous rows
     for (int64_t k = 0; k + 2 < n; k++) {                               // Hessenberg: zero column k below the sub-diagonal
       double xn = 0.0;
       for (int64_t i = k + 1; i < n; i++) xn += std::norm(H[(size_t)(i * n + k)]);
@@ -570,10 +570,10 @@ FT_API int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64
       }
       for (int64_t i = 0; i < n; i++) {                                 // H <- H (I - 2 u u^H / u^H u), and the same on Z
         cd s = 0.0, sz = 0.0;
-        for (int64_t j = k + 1; j < n; j++) { s += H[(size_t)(i * n + j)] * u[(size_t)j]; sz += Z[(size_t)(i * n + j)] * u[(size_t)j]; }
+        for (int64_t j = k + 1; j < n; j++) { s += H[(size_t)(i * n + j)] * u[(size_t)j]; sz += Z[(size_t)(j * n + i)] * u[(size_t)j]; }
         s *= 2.0 / un;
         sz *= 2.0 / un;
-        for (int64_t j = k + 1; j < n; j++) { H[(size_t)(i * n + j)] -= s * std::conj(u[(size_t)j]); Z[(size_t)(i * n + j)] -= sz * std::conj(u[(size_t)j]); }
+        for (int64_t j = k + 1; j < n; j++) { H[(size_t)(i * n + j)] -= s * std::conj(u[(size_t)j]); Z[(size_t)(j * n + i)] -= sz * std::conj(u[(size_t)j]); }
       }
     }
     std::vector<cd> gc((size_t)n), gs((size_t)n);
@@ -617,10 +617,12 @@ FT_API int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64
           H[(size_t)(i * n + k)] = t0 * c + t1 * s;
           H[(size_t)(i * n + k + 1)] = -t0 * std::conj(s) + t1 * std::conj(c);
         }
+        cd* z0 = &Z[(size_t)(k * n)];
+        cd* z1 = &Z[(size_t)((k + 1) * n)];
         for (int64_t i = 0; i < n; i++) {
-          const cd t0 = Z[(size_t)(i * n + k)], t1 = Z[(size_t)(i * n + k + 1)];
-          Z[(size_t)(i * n + k)] = t0 * c + t1 * s;
-          Z[(size_t)(i * n + k + 1)] = -t0 * std::conj(s) + t1 * std::conj(c);
+          const cd t0 = z0[i], t1 = z1[i];
+          z0[i] = t0 * c + t1 * s;
+          z1[i] = -t0 * std::conj(s) + t1 * std::conj(c);
         }
       }
       for (int64_t k = l; k <= hi; k++) H[(size_t)(k * n + k)] += mu;
@@ -643,7 +645,7 @@ FT_API int ft_la_eig(const double* a, double* w, double* v, int64_t batch, int64
       cd phase = 1.0;
       for (int64_t i = 0; i < n; i++) {
         cd s = 0.0;
-        for (int64_t j = 0; j <= k; j++) s += Z[(size_t)(i * n + j)] * y[(size_t)j];
+        for (int64_t j = 0; j <= k; j++) s += Z[(size_t)(j * n + i)] * y[(size_t)j];
         u[(size_t)i] = s;
         vn += std::norm(s);
         if (std::abs(s) > biggest) { biggest = std::abs(s); phase = s; }
