@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Callable, Iterable, List, Optional, Sequence
+from typing import Callable, Iterable, List, Optional
 
 import numpy as np
 
