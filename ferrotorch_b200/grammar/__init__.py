@@ -508,6 +508,55 @@ class JsonSchemaProcessor:
         return f
 
 
+class BatchJsonSchemaProcessor:
+    """One schema constraining a batch of sequences (a serving batch): the compiled grammar and the packed vocabulary are shared, each
+    sequence keeps its own generated text. ``apply(logits [B, V])`` masks row by row, ``advance(tokens [B])`` feeds one token per sequence;
+    a sequence that has emitted its end token stays finished and its row is left untouched."""
+
+    def __init__(self, schema, vocab_texts: Sequence[str], batch: int, eos_id: Optional[int] = None):
+        self._proc = JsonSchemaProcessor(schema, vocab_texts, eos_id)
+        self.eos_id = eos_id
+        self.texts: List[str] = [""] * batch
+        self.finished: List[bool] = [False] * batch
+
+    def reset(self) -> None:
+        self.texts = [""] * len(self.texts)
+        self.finished = [False] * len(self.texts)
+
+    def masks(self) -> torch.Tensor:
+        """bool [B, V]; the row of a finished sequence is all True."""
+        rows = []
+        for text, done in zip(self.texts, self.finished):
+            if done:
+                rows.append(torch.ones(len(self._proc.vocab), dtype=torch.bool))
+            else:
+                self._proc.text = text
+                rows.append(self._proc.mask().allowed.clone())
+        return torch.stack(rows)
+
+    def apply(self, logits: torch.Tensor) -> torch.Tensor:
+        if logits.dim() != 2 or logits.shape[0] != len(self.texts):
+            raise InvalidArgument(f"logits must be [batch = {len(self.texts)}, vocab], got {tuple(logits.shape)}")
+        return logits.masked_fill(~self.masks().to(logits.device), float("-inf"))
+
+    def advance(self, tokens) -> None:
+        toks = tokens.tolist() if isinstance(tokens, torch.Tensor) else list(tokens)
+        if len(toks) != len(self.texts):
+            raise InvalidArgument("one token per sequence")
+        for b, t in enumerate(toks):
+            if self.finished[b]:
+                continue
+            if not 0 <= int(t) < len(self._proc.vocab):
+                raise GrammarError.invalid_token_id(int(t))
+            if int(t) == self.eos_id:
+                self.finished[b] = True
+            else:
+                self.texts[b] += self._proc.vocab[int(t)]
+
+    def is_complete(self, b: int) -> bool:
+        return self._proc.grammar.is_complete(self.texts[b])
+
+
 def apply_mask(logits: torch.Tensor, mask: TokenMask) -> torch.Tensor:
     """``logits[..., v] = -inf`` where the mask forbids token ``v``."""
     allowed = mask.allowed.to(logits.device)

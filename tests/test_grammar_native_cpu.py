@@ -139,3 +139,36 @@ def test_nullable_types_and_refused_keywords():
             G.Schema.from_json({word: [{"type": "string"}]})
     with pytest.raises(Exception):
         G.Schema.from_json({"type": ["string", "integer"]})
+
+
+def test_batch_processor_constrains_every_sequence_of_a_serving_batch():
+    schema = {"type": "object", "properties": {"n": {"type": "integer"}, "ok": {"type": "boolean"}}, "required": ["n", "ok"]}
+    B = 4
+    bp = G.BatchJsonSchemaProcessor(schema, VOCAB_ALL, B, eos_id=EOS)
+    g = torch.Generator().manual_seed(11)
+    for step in range(120):
+        logits = torch.randn(B, len(VOCAB_ALL), generator=g)
+        logits[:, EOS] += 6.0
+        logits[:, VOCAB_ALL.index("}")] += 2.0
+        masked = bp.apply(logits)
+        single = G.JsonSchemaProcessor(schema, VOCAB_ALL, eos_id=EOS)
+        for b in range(B):
+            if not bp.finished[b]:
+                single.text = bp.texts[b]
+                assert torch.equal(torch.isfinite(masked[b]), single.mask().allowed)
+            else:
+                assert torch.equal(masked[b], logits[b])
+        bp.advance(masked.argmax(-1))
+        if all(bp.finished):
+            break
+    assert all(bp.finished)
+    for b in range(B):
+        doc = json.loads(bp.texts[b])
+        assert isinstance(doc["n"], int) and isinstance(doc["ok"], bool) and bp.is_complete(b)
+    assert len(set(bp.texts)) > 1                                    # the sequences went their own ways
+    bp.reset()
+    assert bp.texts == [""] * B and not any(bp.finished)
+    with pytest.raises(Exception):
+        bp.apply(torch.zeros(B + 1, len(VOCAB_ALL)))
+    with pytest.raises(Exception):
+        bp.advance([0])
