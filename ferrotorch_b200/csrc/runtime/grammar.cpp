@@ -8,6 +8,7 @@
 //
 // Capability parity: ferrotorch-grammar/src/json_schema.rs:53-125 (Schema, JsonGrammar), lib.rs:58-85 (TokenMask, JsonSchemaProcessor).
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 #include <cstring>
 #include <string>
@@ -336,4 +337,27 @@ FT_API int64_t ft_json_grammar_mask(void* h, const uint8_t* text, int64_t n, int
   int64_t total = 0;
   for (auto c : counts) total += c;
   return total;
+}
+
+// The masks of several texts over the same grammar and vocabulary: text k is texts[off[k] .. off[k+1]), its mask goes to allowed[k * V ..].
+// The texts are spread over up to nthreads threads (each mask itself runs on one). counts [n_texts] (may be null) receives the number of
+// allowed entries per text.
+FT_API void ft_json_grammar_mask_batch(void* h, const uint8_t* texts, const int64_t* off, int64_t n_texts, int64_t eos_id, uint8_t* allowed, int64_t* counts,
+                                       int nthreads) {
+  const Grammar& g = *static_cast<const Grammar*>(h);
+  const int64_t V = (int64_t)g.voff.size() - 1;
+  nthreads = (int)std::max<int64_t>(1, std::min<int64_t>(std::min(nthreads, 64), n_texts));
+  std::atomic<int64_t> next{0};
+  auto work = [&] {
+    for (;;) {
+      const int64_t k = next.fetch_add(1);
+      if (k >= n_texts) return;
+      const int64_t c = ft_json_grammar_mask(h, texts + off[k], off[k + 1] - off[k], eos_id, allowed + k * V, 1);
+      if (counts) counts[k] = c;
+    }
+  };
+  if (nthreads == 1) { work(); return; }
+  std::vector<std::thread> ts;
+  for (int t = 0; t < nthreads; t++) ts.emplace_back(work);
+  for (auto& th : ts) th.join();
 }

@@ -523,16 +523,30 @@ class BatchJsonSchemaProcessor:
         self.texts = [""] * len(self.texts)
         self.finished = [False] * len(self.texts)
 
-    def masks(self) -> torch.Tensor:
-        """bool [B, V]; the row of a finished sequence is all True."""
-        rows = []
-        for text, done in zip(self.texts, self.finished):
-            if done:
-                rows.append(torch.ones(len(self._proc.vocab), dtype=torch.bool))
-            else:
-                self._proc.text = text
-                rows.append(self._proc.mask().allowed.clone())
-        return torch.stack(rows)
+    def masks(self, threads: Optional[int] = None) -> torch.Tensor:
+        """bool [B, V]; the row of a finished sequence is all True. With the native walk all live sequences go to the library in one call,
+        one sequence per thread."""
+        V = len(self._proc.vocab)
+        live = [b for b, done in enumerate(self.finished) if not done]
+        out = torch.ones(len(self.texts), V, dtype=torch.bool)
+        if not live:
+            return out
+        if self._proc._native is not None:
+            raw = [self.texts[b].encode("utf-8") for b in live]
+            off = np.zeros(len(raw) + 1, np.int64)
+            np.cumsum([len(x) for x in raw], out=off[1:])
+            buf = np.zeros((len(live), max(V, 1)), np.uint8)
+            rt = self._proc._rt
+            rt.ft_json_grammar_mask_batch.restype = None
+            rt.ft_json_grammar_mask_batch(self._proc._native, ctypes.c_char_p(b"".join(raw) + b"\0"), off.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(len(live)),
+                                          ctypes.c_int64(-1 if self.eos_id is None else self.eos_id), buf.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(None),
+                                          ctypes.c_int(threads or min(os.cpu_count() or 1, len(live))))
+            out[live] = torch.from_numpy(buf[:, :V]).to(torch.bool)
+            return out
+        for b in live:
+            self._proc.text = self.texts[b]
+            out[b] = self._proc.mask().allowed
+        return out
 
     def apply(self, logits: torch.Tensor) -> torch.Tensor:
         if logits.dim() != 2 or logits.shape[0] != len(self.texts):
