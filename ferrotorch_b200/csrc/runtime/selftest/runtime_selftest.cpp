@@ -52,6 +52,7 @@ void* ft_json_grammar_create(const int32_t* kind, const int32_t* edge_first, int
 void ft_json_grammar_destroy(void* h);
 int ft_json_grammar_check(void* h, const uint8_t* text, int64_t n, int* is_complete);
 int64_t ft_json_grammar_mask(void* h, const uint8_t* text, int64_t n, int64_t eos_id, uint8_t* allowed, int nthreads);
+void ft_json_grammar_mask_batch(void* h, const uint8_t* texts, const int64_t* off, int64_t n_texts, int64_t eos_id, uint8_t* allowed, int64_t* counts, int nthreads);
 int ft_la_cholesky(double* a, int64_t batch, int64_t n, int32_t* info);
 int ft_la_lu(double* a, int64_t batch, int64_t m, int64_t n, int32_t* piv, int32_t* info);
 int ft_la_lu_solve(const double* lu, const int32_t* piv, double* bmat, int64_t batch, int64_t n, int64_t k, int trans);
@@ -270,6 +271,17 @@ static void test_grammar() {
   CHECK(c1 == c4 && m1 == m4 && c1 == 2 + 3000);          // "1", "12}" and every "1<digits>" entry
   CHECK(m1[4] == 1 && m1[5] == 1 && m1[6] == 0 && m1[7] == 0 && m1[8] == 0);
   CHECK(ft_json_grammar_mask(h, (const uint8_t*)"{\"a\":1}", 7, 8, m1.data(), 4) == 1 && m1[8] == 1);
+  const std::vector<std::string> texts = {"", "{", "{\"a\"", "{\"a\":", "{\"a\":1", "{\"a\":12}"};
+  std::string tb;
+  std::vector<int64_t> toff{0};
+  for (auto& t : texts) { tb += t; toff.push_back((int64_t)tb.size()); }
+  std::vector<uint8_t> mb(texts.size() * vocab.size());
+  std::vector<int64_t> cnt(texts.size());
+  ft_json_grammar_mask_batch(h, (const uint8_t*)tb.data(), toff.data(), (int64_t)texts.size(), 8, mb.data(), cnt.data(), 4);
+  for (size_t k = 0; k < texts.size(); k++) {              // every row equals the mask of that text computed on its own
+    const int64_t c = ft_json_grammar_mask(h, (const uint8_t*)texts[k].data(), (int64_t)texts[k].size(), 8, m1.data(), 1);
+    CHECK(c == cnt[k] && std::equal(m1.begin(), m1.end(), mb.begin() + (int64_t)(k * vocab.size())));
+  }
   ft_json_grammar_destroy(h);
 }
 
