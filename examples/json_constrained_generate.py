@@ -34,18 +34,23 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--prompt", default="Describe a person as JSON: ")
     a = ap.parse_args()
+    def byte_tokenizer():
+        b2u = tokenize._bytes_to_unicode()
+        return tokenize.Tokenizer({b2u[b]: b for b in range(256)}, [], {"<eos>": 256}, eos_token="<eos>"), 256
     if a.model_dir:
         from ferrotorch_b200.serialize import load_safetensors
         d = Path(a.model_dir)
         cfg = LlamaConfig.from_hf(json.load(open(d / "config.json")))
-        tok = tokenize.load_tokenizer(d)
+        if (d / "tokenizer.json").exists():
+            tok = tokenize.load_tokenizer(d)
+            eos = tok.vocab.get(tok.eos_token) if tok.eos_token else None
+        elif cfg.vocab_size >= 257:                        # a checkpoint without a tokenizer file: bytes plus an end token
+            tok, eos = byte_tokenizer()
+        else:
+            raise SystemExit("the model directory has no tokenizer.json and its vocabulary is too small for the byte tokenizer")
         W = {k: v.float() for k, v in load_safetensors(d / "model.safetensors").items()}
-        eos = tok.vocab.get(tok.eos_token) if tok.eos_token else None
     else:
-        b2u = tokenize._bytes_to_unicode()
-        vocab = {b2u[b]: b for b in range(256)}
-        tok = tokenize.Tokenizer(vocab, [], {"<eos>": 256}, eos_token="<eos>")
-        eos = 256
+        tok, eos = byte_tokenizer()
         cfg = LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                           max_position_embeddings=1024)
         W = {k: v.float() for k, v in random_hf_weights(cfg, "cpu", a.seed, 0.08).items()}

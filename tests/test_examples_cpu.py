@@ -64,3 +64,26 @@ def test_native_core_transformer_example_learns_its_corpus():
     losses = [float(l.split("loss")[1]) for l in out.splitlines() if l.startswith("step")]
     assert losses[-1] < 0.2 < losses[0]
     assert "sample: the quick brown fox jumps over the lazy dog." in out
+
+
+def test_constrained_generation_with_a_checkpoint_directory_and_its_tokenizer_file(tmp_path):
+    """A random checkpoint in the Hugging Face layout plus a byte-level BPE ``tokenizer.json`` trained with the HF library: the example loads
+    both and its output stays a valid prefix of the schema."""
+    tk = pytest.importorskip("tokenizers")
+    import glob
+    import json
+    from tokenizers import decoders, models, pre_tokenizers, trainers
+    ckpt = tmp_path / "ckpt"
+    _run(ROOT / "examples/llm_inference_dump.py", "--write-random", ckpt)
+    vocab = json.loads((ckpt / "config.json").read_text())["vocab_size"]
+    out = _run(ROOT / "examples/json_constrained_generate.py", "--model-dir", ckpt, "--new", "40")          # no tokenizer file yet: the byte tokenizer
+    assert "valid prefix: True" in out
+    hf = tk.Tokenizer(models.BPE())
+    hf.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    hf.decoder = decoders.ByteLevel()
+    files = sorted(glob.glob(str(ROOT / "ferrotorch_b200" / "*.py")))[:6]
+    hf.train(files, trainers.BpeTrainer(vocab_size=min(vocab, 400), special_tokens=["<|end|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False))
+    hf.save(str(ckpt / "tokenizer.json"))
+    (ckpt / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|end|>"}))
+    out = _run(ROOT / "examples/json_constrained_generate.py", "--model-dir", ckpt, "--new", "40")
+    assert "valid prefix: True" in out and out.splitlines()[0].startswith("generated: {")
