@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Train a small CNN on (synthetic) MNIST with the Learner: data loader, AdamW, cosine schedule, accuracy metric, checkpoints, TensorBoard.
 
-    python examples/train_mnist.py [--epochs 3] [--device cuda]
+    python examples/train_mnist.py [--epochs 3] [--device cuda] [--out DIR]
 
 Counterpart of the reference's ferrotorch/examples/train_mnist.rs.
 """
@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--epochs", type=int, default=3)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--samples", type=int, default=2048)
+    ap.add_argument("--out", default=None, help="directory for checkpoints and TensorBoard events (default: a new temporary directory)")
     a = ap.parse_args()
     torch.manual_seed(0)
     ds = Mnist.synthetic(a.samples)
@@ -30,7 +31,8 @@ def main():
     model = nn.Sequential(nn.Conv2d(1, 16, 3, padding=1), nn.BatchNorm2d(16), nn.ReLU(), nn.MaxPool2d(2), nn.Conv2d(16, 32, 3, padding=1), nn.ReLU(),
                           nn.AdaptiveAvgPool2d(1), nn.Flatten(), nn.Linear(32, 10)).to(a.device)
     opt = optim.AdamW(model.parameters(), lr=3e-3)
-    out = Path(tempfile.mkdtemp(prefix="ft_mnist_"))
+    out = Path(a.out) if a.out else Path(tempfile.mkdtemp(prefix="ft_mnist_"))
+    out.mkdir(parents=True, exist_ok=True)
     learner = train.Learner(model, opt, nn.CrossEntropyLoss(), device=a.device, metrics=[train.AccuracyMetric()],
                             callbacks=[train.ProgressLogger(), train.TensorBoardCallback(str(out / "tb"))]).with_checkpointing(str(out / "ckpt"))
     hist = learner.fit(loader, epochs=a.epochs)

@@ -270,7 +270,8 @@ def default_collate(samples: List[Any]):
     if isinstance(e, (int, float, bool)):
         return torch.tensor(samples)
     if isinstance(e, (tuple, list)):
-        return type(e)(default_collate([s[i] for s in samples]) for i in range(len(e)))
+        parts = [default_collate([s[i] for s in samples]) for i in range(len(e))]
+        return type(e)(*parts) if hasattr(e, "_fields") else type(e)(parts)          # a named tuple takes its fields one by one
     if isinstance(e, dict):
         return {k: default_collate([s[k] for s in samples]) for k in e}
     return samples

@@ -123,3 +123,20 @@ def test_safetensors_metadata_mapped_loading_and_shard_progress(tmp_path):
     assert torch.equal(sd["a"], a) and len(seen) == 2 and all(isinstance(e, S.ShardProgress) for e in seen)
     assert [e.shard_index for e in seen] == [0, 1] and seen[0].shard_count == 2 and seen[-1].total_tensors == 2
     assert seen[1].tensors_loaded_so_far == 1
+
+
+def test_default_collate_keeps_named_tuples_lists_and_dicts():
+    from typing import NamedTuple
+    import ferrotorch_b200.data as D
+
+    class Sample(NamedTuple):
+        image: torch.Tensor
+        label: int
+    batch = D.default_collate([Sample(torch.full((2, 2), float(i)), i) for i in range(3)])
+    assert isinstance(batch, Sample) and batch.image.shape == (3, 2, 2) and batch.label.tolist() == [0, 1, 2]
+    pair = D.default_collate([(torch.zeros(2), 1.5), (torch.ones(2), 2.5)])
+    assert isinstance(pair, tuple) and pair[0].shape == (2, 2) and pair[1].tolist() == [1.5, 2.5]
+    lst = D.default_collate([[1, 2], [3, 4]])
+    assert isinstance(lst, list) and lst[0].tolist() == [1, 3]
+    dct = D.default_collate([{"a": torch.zeros(1)}, {"a": torch.ones(1)}])
+    assert dct["a"].shape == (2, 1)

@@ -87,3 +87,10 @@ def test_constrained_generation_with_a_checkpoint_directory_and_its_tokenizer_fi
     (ckpt / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|end|>"}))
     out = _run(ROOT / "examples/json_constrained_generate.py", "--model-dir", ckpt, "--new", "40")
     assert "valid prefix: True" in out and out.splitlines()[0].startswith("generated: {")
+
+
+def test_learner_example_trains_on_synthetic_digits(tmp_path):
+    out = _run(ROOT / "examples/train_mnist.py", "--epochs", "3", "--device", "cpu", "--samples", "512", "--out", tmp_path / "run")
+    losses = [float(l.split("train_loss")[1].split()[0]) for l in out.splitlines() if l.startswith("epoch")]
+    assert len(losses) == 3 and losses[-1] < losses[0]
+    assert any((tmp_path / "run").rglob("*")), "checkpoints / event files were written"
