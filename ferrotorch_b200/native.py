@@ -150,12 +150,24 @@ class Tensor:
             if np.isscalar(other) and name == "ftc_mul":
                 return Tensor(_handle=_check(_fn("ftc_scale")(self._h, float(other))))
             other = Tensor(np.broadcast_to(np.asarray(other, np.float32), self.shape))
+        a, b = self.shape, other.shape
+        if len(a) < len(b) and tuple(b[len(b) - len(a):]) == tuple(a):
+            # The kernels broadcast the SECOND operand over the first one's leading dimensions; with the smaller tensor first, rewrite.
+            if name in ("ftc_add", "ftc_mul"):
+                return other._bin(name, self)
+            if name == "ftc_sub":
+                return -(other._bin("ftc_sub", self))
+            if name == "ftc_div":
+                return other.reciprocal()._bin("ftc_mul", self)
         return Tensor(_handle=_check(_fn(name)(self._h, other._h)))
 
     def __add__(self, o): return self._bin("ftc_add", o)
     def __sub__(self, o): return self._bin("ftc_sub", o)
     def __mul__(self, o): return self._bin("ftc_mul", o)
     __rmul__ = __mul__
+    __radd__ = __add__
+    def __rsub__(self, o): return -(self._bin("ftc_sub", o))
+    def __rtruediv__(self, o): return self.reciprocal() * o
     def __neg__(self): return Tensor(_handle=_check(_fn("ftc_scale")(self._h, -1.0)))
     def __matmul__(self, o):
         """Matrix product; tensors with leading (batch) dimensions multiply batch by batch."""
@@ -232,8 +244,16 @@ class Tensor:
             return Tensor(_handle=_check(_fn("ftc_mean")(self._h)))
         return Tensor(_handle=_check(_fn("ftc_sum_dim")(self._h, int(dim), int(keepdim), 1)))
 
-    def softmax(self): return Tensor(_handle=_check(_fn("ftc_softmax")(self._h, 0)))
-    def log_softmax(self): return Tensor(_handle=_check(_fn("ftc_softmax")(self._h, 1)))
+    def _softmax(self, dim: int, log: int):
+        nd = len(self.shape)
+        dim = int(dim) % max(nd, 1)
+        if dim == nd - 1 or nd == 0:
+            return Tensor(_handle=_check(_fn("ftc_softmax")(self._h, log)))
+        moved = self.transpose(dim, nd - 1)           # the kernel normalises the last dimension
+        return Tensor(_handle=_check(_fn("ftc_softmax")(moved._h, log))).transpose(dim, nd - 1)
+
+    def softmax(self, dim: int = -1): return self._softmax(dim, 0)
+    def log_softmax(self, dim: int = -1): return self._softmax(dim, 1)
 
     def backward(self, grad: Optional["Tensor"] = None, threads: int = 1) -> None:
         """Reverse sweep from this tensor. ``threads > 1`` runs independent nodes on worker threads (``backward_parallel``); gradients are

@@ -198,3 +198,32 @@ def test_transformer_block_forward_and_backward_match_pytorch():
     assert np.allclose(xn.grad.numpy(), xt.grad.numpy(), atol=2e-4)
     for n in names:
         assert np.allclose(pn[n].grad.numpy(), pt[n].grad.numpy(), atol=2e-4), n
+
+
+def test_smaller_first_operand_and_reflected_operators_match_torch():
+    a = torch.rand(4, 3) + 0.5
+    b = torch.rand(3) + 0.5
+    for op in (lambda x, y: y + x, lambda x, y: y - x, lambda x, y: y * x, lambda x, y: y / x,
+               lambda x, y: 2.0 - x, lambda x, y: 2.0 / x, lambda x, y: 1.5 + x):
+        ta, tb = a.clone().requires_grad_(True), b.clone().requires_grad_(True)
+        na, nb = N.Tensor(a.numpy().copy(), requires_grad=True), N.Tensor(b.numpy().copy(), requires_grad=True)
+        to, no = op(ta, tb), op(na, nb)
+        assert tuple(no.shape) == tuple(to.shape)
+        np.testing.assert_allclose(no.numpy(), to.detach().numpy(), rtol=1e-5, atol=1e-6)
+        to.sum().backward(); no.sum().backward()
+        np.testing.assert_allclose(na.grad.numpy(), ta.grad.numpy(), rtol=1e-4, atol=1e-5)
+        if tb.grad is not None:
+            np.testing.assert_allclose(nb.grad.numpy(), tb.grad.numpy(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dim", [0, 1, -1, -3])
+def test_softmax_over_any_dimension(dim):
+    x = torch.randn(3, 4, 5)
+    for name in ("softmax", "log_softmax"):
+        tx = x.clone().requires_grad_(True)
+        nx = N.Tensor(x.numpy().copy(), requires_grad=True)
+        to, no = getattr(tx, name)(dim), getattr(nx, name)(dim)
+        np.testing.assert_allclose(no.numpy(), to.detach().numpy(), rtol=1e-5, atol=1e-6)
+        w = torch.randn(3, 4, 5)
+        (to * w).sum().backward(); (no * N.Tensor(w.numpy().copy())).sum().backward()
+        np.testing.assert_allclose(nx.grad.numpy(), tx.grad.numpy(), rtol=1e-4, atol=1e-5)
