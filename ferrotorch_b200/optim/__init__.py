@@ -7,3 +7,7 @@ from .optimizers import (Optimizer, ParamGroup, SgdConfig, AdamConfig, AdamWConf
 from .extras import (GradScaler, GradScalerConfig, GradScalerState, GradientAccumulator, ExponentialMovingAverage, AveragedModel, AveragingStrategy, Swalr)
 from . import scheduler
 from .scheduler import *  # noqa: F401,F403
+
+# PyTorch's spellings of the same classes, so that code written against torch.optim runs unchanged.
+SGD, RMSprop, ASGD, LBFGS, SWALR = Sgd, Rmsprop, Asgd, Lbfgs, Swalr
+SequentialLR = SequentialLr  # noqa: F405

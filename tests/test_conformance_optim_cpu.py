@@ -97,3 +97,9 @@ def test_distribution_base_and_kl_registration():
 
     got = kl_divergence(Point(torch.tensor(0.5)), Normal(torch.tensor(0.0), torch.tensor(1.0)))
     assert abs(got.item() - (0.5 * 0.25 + 0.5 * math.log(2 * math.pi))) < 1e-6
+
+
+def test_pytorch_spellings_name_the_same_classes():
+    from ferrotorch_b200 import optim as O
+    assert O.SGD is O.Sgd and O.RMSprop is O.Rmsprop and O.ASGD is O.Asgd and O.LBFGS is O.Lbfgs
+    assert O.SWALR is O.Swalr and O.SequentialLR is O.SequentialLr
