@@ -96,6 +96,9 @@ class LogNormal(Distribution):
     def cdf(self, value):
         return self.base.cdf(value.log())
 
+    def icdf(self, p):
+        return self.base.icdf(p).exp()
+
     def entropy(self):
         return self.base.entropy() + self.loc
 
@@ -293,6 +296,10 @@ class Laplace(Distribution):
         z = (value - self.loc) / self.scale
         return 0.5 - 0.5 * z.sign() * torch.expm1(-z.abs())
 
+    def icdf(self, p):
+        t = p - 0.5
+        return self.loc - self.scale * t.sign() * torch.log1p(-2 * t.abs())
+
     def entropy(self):
         return 1 + torch.log(2 * self.scale)
 
@@ -320,6 +327,9 @@ class Gumbel(Distribution):
 
     def cdf(self, value):
         return torch.exp(-torch.exp(-(value - self.loc) / self.scale))
+
+    def icdf(self, p):
+        return self.loc - self.scale * torch.log(-torch.log(p))
 
     def entropy(self):
         return self.scale.log() + (1 + _EULER)
@@ -380,6 +390,9 @@ class HalfNormal(Distribution):
 
     def cdf(self, value):
         return torch.erf(value / (self.scale * math.sqrt(2)))
+
+    def icdf(self, p):
+        return self.scale * math.sqrt(2) * torch.erfinv(p)
 
     def entropy(self):
         return 0.5 * math.log(math.pi / 2) + 0.5 + self.scale.log()
@@ -556,6 +569,9 @@ class Weibull(Distribution):
     def cdf(self, value):
         return 1 - torch.exp(-(value / self.scale).pow(self.concentration))
 
+    def icdf(self, p):
+        return self.scale * (-torch.log1p(-p)).pow(1 / self.concentration)
+
     def entropy(self):
         k = self.concentration
         return _EULER * (1 - 1 / k) + (self.scale / k).log() + 1
@@ -594,6 +610,9 @@ class Pareto(Distribution):
     def cdf(self, value):
         return 1 - (self.scale / value).pow(self.alpha)
 
+    def icdf(self, p):
+        return self.scale * (1 - p).pow(-1 / self.alpha)
+
     def entropy(self):
         return (self.scale / self.alpha).log() + 1 + self.alpha.reciprocal()
 
@@ -625,6 +644,9 @@ class Kumaraswamy(Distribution):
 
     def cdf(self, value):
         return 1 - (1 - value.pow(self.concentration1)).pow(self.concentration0)
+
+    def icdf(self, p):
+        return (1 - (1 - p).pow(1 / self.concentration0)).pow(1 / self.concentration1)
 
     def entropy(self):
         a, b = self.concentration1, self.concentration0
@@ -812,6 +834,75 @@ def _kl_gumbel(p, q):
     ct2 = q.loc / q.scale
     ct3 = p.loc / q.scale
     return -ct1.log() - ct2 + ct3 + ct1 * _EULER + torch.exp(ct2 + (1 + ct1).lgamma() - ct3) - (1 + _EULER)
+
+
+@register_kl(Normal, Uniform)
+def _kl_normal_uniform(p, q):
+    """A normal puts mass outside every bounded interval, so the divergence is infinite (kl.rs:334)."""
+    return torch.full_like(p.loc + q.low, math.inf)
+
+
+@register_kl(Uniform, Normal)
+def _kl_uniform_normal(p, q):
+    """E_p[log p - log q] with the second moment of a uniform about q's mean (kl.rs:367)."""
+    width = p.high - p.low
+    second = width.pow(2) / 12 + ((p.high + p.low) / 2 - q.loc).pow(2)
+    return -width.log() + 0.5 * math.log(2 * math.pi) + q.scale.log() + second / (2 * q.scale.pow(2))
+
+
+@register_kl(Gamma, Exponential)
+def _kl_gamma_exponential(p, q):
+    """Exponential(rate) is Gamma(1, rate) (kl.rs:533)."""
+    return _kl_gamma(p, Gamma(torch.ones_like(q.rate), q.rate))
+
+
+@register_kl(Exponential, Gamma)
+def _kl_exponential_gamma(p, q):
+    return _kl_gamma(Gamma(torch.ones_like(p.rate), p.rate), q)
+
+
+@register_kl(HalfNormal, HalfNormal)
+def _kl_half_normal(p, q):
+    """Folding both normals at zero leaves the log-ratio of the densities unchanged on the support."""
+    vr = (p.scale / q.scale).pow(2)
+    return 0.5 * (vr - 1 - vr.log())
+
+
+@register_kl(LogNormal, LogNormal)
+def _kl_lognormal(p, q):
+    """The divergence is invariant under the shared bijection exp, so it equals that of the underlying normals."""
+    return _kl_normal(p.base, q.base)
+
+
+@register_kl(Cauchy, Cauchy)
+def _kl_cauchy(p, q):
+    """Closed form of Chyzak and Nielsen (2019)."""
+    return torch.log(((p.scale + q.scale).pow(2) + (p.loc - q.loc).pow(2)) / (4 * p.scale * q.scale))
+
+
+@register_kl(Pareto, Pareto)
+def _kl_pareto(p, q):
+    """Infinite when p reaches below q's lower bound."""
+    ratio = p.scale / q.scale
+    ar = q.alpha / p.alpha
+    out = q.alpha * ratio.log() - ar.log() + ar - 1
+    return torch.where(p.scale < q.scale, torch.full_like(out, math.inf), out)
+
+
+@register_kl(Normal, Laplace)
+def _kl_normal_laplace(p, q):
+    """-H(p) + log(2 b) + E_p|x - m| / b, with the mean absolute deviation of a normal about m in closed form."""
+    d = p.loc - q.loc
+    z = d / p.scale
+    mad = p.scale * math.sqrt(2 / math.pi) * torch.exp(-0.5 * z.pow(2)) + d * torch.erf(z / math.sqrt(2))
+    return -p.entropy() + torch.log(2 * q.scale) + mad / q.scale
+
+
+@register_kl(Beta, Normal)
+def _kl_beta_normal(p, q):
+    """-H(p) minus the expected normal log-density, which needs only p's mean and variance."""
+    second = p.variance + (p.mean - q.loc).pow(2)
+    return -p.entropy() + 0.5 * math.log(2 * math.pi) + q.scale.log() + second / (2 * q.scale.pow(2))
 
 
 @register_kl(MultivariateNormal, MultivariateNormal)

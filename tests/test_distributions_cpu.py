@@ -230,3 +230,47 @@ def test_low_rank_multivariate_normal_matches_torch():
     assert (emp - ours.covariance_matrix).abs().max() < 0.15
     with pytest.raises(ValueError):
         FD.LowRankMultivariateNormal(loc, torch.randn(2, 5, 2), d)
+
+
+def _params(name):
+    g = torch.Generator().manual_seed(11)
+    pos = lambda: torch.rand(4, dtype=torch.float64, generator=g) * 2 + 0.3
+    real = lambda: torch.randn(4, dtype=torch.float64, generator=g)
+    return {"LogNormal": (real(), pos()), "Laplace": (real(), pos()), "Gumbel": (real(), pos()), "HalfNormal": (pos(),), "Weibull": (pos(), pos()),
+            "Pareto": (pos(), pos()), "Kumaraswamy": (pos(), pos()), "Normal": (real(), pos()), "Uniform": (real() - 3, real().abs() + 1),
+            "Gamma": (pos(), pos()), "Exponential": (pos(),), "Cauchy": (real(), pos()), "Beta": (pos(), pos())}[name]
+
+
+@pytest.mark.parametrize("name", ["LogNormal", "Laplace", "Gumbel", "HalfNormal", "Weibull", "Pareto", "Kumaraswamy"])
+def test_quantile_functions_invert_the_cdf_and_match_torch(name):
+    import ferrotorch_b200.distributions as D
+    args = _params(name)
+    mine, ref = getattr(D, name)(*args), getattr(torch.distributions, name)(*args)
+    p = torch.rand(6, 4, dtype=torch.float64, generator=torch.Generator().manual_seed(2)) * 0.96 + 0.02
+    x = mine.icdf(p)
+    torch.testing.assert_close(mine.cdf(x), p, rtol=1e-9, atol=1e-9)
+    try:
+        want = ref.icdf(p)
+    except NotImplementedError:
+        return
+    torch.testing.assert_close(x, want, rtol=1e-9, atol=1e-9)
+
+
+@pytest.mark.parametrize("pn,qn", [("Uniform", "Normal"), ("Gamma", "Exponential"), ("Exponential", "Gamma"), ("HalfNormal", "HalfNormal"),
+                                   ("LogNormal", "LogNormal"), ("Cauchy", "Cauchy"), ("Pareto", "Pareto"), ("Normal", "Laplace"), ("Beta", "Normal")])
+def test_more_closed_form_kl_pairs_match_torch(pn, qn):
+    import ferrotorch_b200.distributions as D
+    a, b = _params(pn), tuple(t * 1.1 + 0.05 for t in _params(qn))
+    if pn == qn == "Pareto":
+        b = (a[0] * 0.6, b[1])                                  # q's support must contain p's for a finite value
+    got = D.kl_divergence(getattr(D, pn)(*a), getattr(D, qn)(*b))
+    want = torch.distributions.kl_divergence(getattr(torch.distributions, pn)(*a), getattr(torch.distributions, qn)(*b))
+    assert torch.isfinite(want).all()
+    torch.testing.assert_close(got, want, rtol=1e-8, atol=1e-9)
+
+
+def test_kl_is_infinite_where_the_support_is_not_covered():
+    import ferrotorch_b200.distributions as D
+    one = torch.ones(2, dtype=torch.float64)
+    assert torch.isinf(D.kl_divergence(D.Normal(0 * one, one), D.Uniform(-one, one))).all()
+    assert torch.isinf(D.kl_divergence(D.Pareto(one, one), D.Pareto(2 * one, one))).all()
