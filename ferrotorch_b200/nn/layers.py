@@ -399,16 +399,18 @@ class CrossEntropyLoss(Module):
     """Mean/sum/none cross-entropy on ``[N, C]`` logits. Targets may be integer class indices or, as in the reference
     (ferrotorch-nn/src/loss.rs:187-215), a float tensor holding class indices."""
 
-    def __init__(self, reduction: str = "mean", ignore_index: int = -100, label_smoothing: float = 0.0):
+    def __init__(self, reduction: str = "mean", ignore_index: int = -100, label_smoothing: float = 0.0, weight: Optional[torch.Tensor] = None):
         super().__init__()
         self.reduction, self.ignore_index, self.label_smoothing = reduction, ignore_index, label_smoothing
+        self.weight = weight          # per-class weights; the weighted form runs outside the fused kernel
 
     def forward(self, logits, target):
         if target.is_floating_point() and target.dim() == logits.dim() - 1:
             target = target.long()
-        if self.reduction == "mean" and target.dtype == torch.long and logits.is_cuda and logits.dim() == 2:
+        if self.weight is None and self.reduction == "mean" and target.dtype == torch.long and logits.is_cuda and logits.dim() == 2:
             return ops.cross_entropy(logits, target, self.ignore_index, self.label_smoothing)
-        return F.cross_entropy(logits, target, reduction=self.reduction, ignore_index=self.ignore_index, label_smoothing=self.label_smoothing)
+        w = None if self.weight is None else self.weight.to(device=logits.device, dtype=logits.dtype)
+        return F.cross_entropy(logits, target, weight=w, reduction=self.reduction, ignore_index=self.ignore_index, label_smoothing=self.label_smoothing)
 
 
 from .transformer import (TransformerEncoderLayer, TransformerDecoderLayer, TransformerEncoder, TransformerDecoder, Transformer)  # noqa: F401,E402

@@ -549,3 +549,18 @@ def test_functional_forms_are_this_packages():
     FF.embedding(ids, w, padding_idx=2).sum().backward()
     assert float(w.grad[2].abs().sum()) == 0 and float(w.grad[1].sum()) == 4.0
     _close(FF.layer_norm(x, (5,)), TF.layer_norm(x, (5,)))
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_cross_entropy_loss_takes_class_weights(reduction):
+    import ferrotorch_b200.nn as ftnn
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(9, 5, generator=g)
+    target = torch.randint(0, 5, (9,), generator=g)
+    w = torch.rand(5, generator=g) + 0.5
+    a, b = logits.clone().requires_grad_(True), logits.clone().requires_grad_(True)
+    got = ftnn.CrossEntropyLoss(reduction=reduction, label_smoothing=0.1, weight=w)(a, target)
+    want = torch.nn.CrossEntropyLoss(weight=w, reduction=reduction, label_smoothing=0.1)(b, target)
+    torch.testing.assert_close(got, want)
+    got.sum().backward(); want.sum().backward()
+    torch.testing.assert_close(a.grad, b.grad)
