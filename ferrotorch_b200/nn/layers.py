@@ -371,6 +371,20 @@ class MultiheadAttention(Module):
         self.k_proj = Linear(embed_dim, kv, bias, device, dtype)
         self.v_proj = Linear(embed_dim, kv, bias, device, dtype)
         self.out_proj = Linear(embed_dim, embed_dim, bias, device, dtype)
+        self._register_load_state_dict_pre_hook(self._split_packed_projection)
+
+    def _split_packed_projection(self, state_dict, prefix, *_):
+        """A checkpoint written by ``torch.nn.MultiheadAttention`` stores the three input projections as one ``in_proj_weight`` /
+        ``in_proj_bias``; cut them into this layer's q, k and v entries (rows in that order) before the keys are matched."""
+        kv = self.num_kv_heads * self.head_dim
+        for packed, leaf in (("in_proj_weight", "weight"), ("in_proj_bias", "bias")):
+            t = state_dict.pop(prefix + packed, None)
+            if t is None:
+                continue
+            if t.shape[0] != self.embed_dim + 2 * kv:
+                raise ShapeMismatch(f"{prefix}{packed}: {t.shape[0]} rows, expected {self.embed_dim + 2 * kv}")
+            q, k, v = t.split([self.embed_dim, kv, kv], 0)
+            state_dict[f"{prefix}q_proj.{leaf}"], state_dict[f"{prefix}k_proj.{leaf}"], state_dict[f"{prefix}v_proj.{leaf}"] = q, k, v
 
     @classmethod
     def with_gqa(cls, embed_dim: int, num_heads: int, num_kv_heads: int, **kw) -> "MultiheadAttention":

@@ -564,3 +564,17 @@ def test_cross_entropy_loss_takes_class_weights(reduction):
     torch.testing.assert_close(got, want)
     got.sum().backward(); want.sum().backward()
     torch.testing.assert_close(a.grad, b.grad)
+
+
+def test_torch_transformer_checkpoints_with_packed_projections_load_and_match():
+    torch.manual_seed(0)
+    x, y = torch.randn(2, 5, 8), torch.randn(2, 3, 8)
+    ref = torch.nn.Transformer(8, 2, 2, 2, 16, dropout=0.0, batch_first=True).eval()
+    mine = nn.Transformer(8, 2, 2, 2, 16, dropout=0.0, batch_first=True).eval()
+    assert any(k.endswith("in_proj_weight") for k in ref.state_dict())
+    result = mine.load_state_dict(ref.state_dict())
+    assert not result.missing_keys and not result.unexpected_keys
+    torch.testing.assert_close(mine(x, y), ref(x, y), rtol=1e-4, atol=1e-5)
+    bad = {k: (v[:-1] if k.endswith("in_proj_weight") else v) for k, v in ref.state_dict().items()}
+    with pytest.raises(ShapeMismatch):
+        mine.load_state_dict(bad)
