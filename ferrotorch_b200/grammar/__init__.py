@@ -57,6 +57,23 @@ class Schema:
         raise InvalidArgument(f"unsupported schema type {t}")
 
 
+def _key_literal(name: str) -> str:
+    """A property name as it is written in the document: characters outside ASCII stay as they are (models emit them raw)."""
+    return json.dumps(name, ensure_ascii=False)
+
+
+def _enum_literals(s: "Schema") -> List[str]:
+    """The accepted spellings of an enum's values: each value with characters outside ASCII written raw and, where that differs,
+    also as ``\\uXXXX`` escapes."""
+    out: List[str] = []
+    for v in s.enum or []:
+        raw, escaped = json.dumps(v, ensure_ascii=False), json.dumps(v)
+        out.append(raw)
+        if escaped != raw:
+            out.append(escaped)
+    return out
+
+
 class JsonGrammar:
     """Incremental validator: ``accepts_prefix(text)`` is true iff ``text`` can be extended to a document matching the schema.
     Objects emit their properties in schema order (required ones mandatory), compact separators, no insignificant whitespace
@@ -182,8 +199,8 @@ class JsonGrammar:
             return r if r is not None else self._value(s.items, t, i)
         if k == "enum":
             res = None
-            for v in s.enum or []:
-                r = self._lit(json.dumps(v), t, i)
+            for lit in _enum_literals(s):
+                r = self._lit(lit, t, i)
                 if r is not None and r != -1:
                     return r
                 if r == -1:
@@ -241,7 +258,7 @@ class JsonGrammar:
                     i = self._sep(t, i + 1)
                     if i >= len(t):
                         return -1
-                key = json.dumps(name)
+                key = _key_literal(name)
                 r = self._lit(key, t, i)
                 if r is None:
                     if name in s.required:
@@ -249,7 +266,7 @@ class JsonGrammar:
                     continue_ok = False
                     # an optional property may be skipped: try the following ones at this position
                     for n2, _ in props[idx + 1:]:
-                        r2 = self._lit(json.dumps(n2), t, i)
+                        r2 = self._lit(_key_literal(n2), t, i)
                         if r2 is not None:
                             continue_ok = True
                             break
@@ -377,7 +394,7 @@ def _flatten_schema(root: Schema):
         kinds.append(_KIND_CODE[s.kind])
         if s.kind == "object":
             for name, sub in s.properties.items():
-                lits.append(json.dumps(name).encode("utf-8"))
+                lits.append(_key_literal(name).encode("utf-8"))
                 child.append(index[id(sub)])
                 req.append(1 if name in s.required else 0)
         elif s.kind in ("array", "nullable") and s.items is not None:
@@ -385,8 +402,8 @@ def _flatten_schema(root: Schema):
             child.append(index[id(s.items)])
             req.append(0)
         elif s.kind == "enum":
-            for v in s.enum or []:
-                lits.append(json.dumps(v).encode("utf-8"))
+            for lit in _enum_literals(s):
+                lits.append(lit.encode("utf-8"))
                 child.append(-1)
                 req.append(0)
         first.append(len(lits))

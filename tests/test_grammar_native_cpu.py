@@ -172,3 +172,22 @@ def test_batch_processor_constrains_every_sequence_of_a_serving_batch():
         bp.apply(torch.zeros(B + 1, len(VOCAB_ALL)))
     with pytest.raises(Exception):
         bp.advance([0])
+
+
+def test_enum_values_and_property_names_outside_ascii_are_accepted_raw_and_escaped():
+    import json
+    from ferrotorch_b200.grammar import JsonGrammar, JsonSchemaProcessor, Schema
+    schema = {"type": "object", "properties": {"né": {"enum": ["é✓", "plain", 3]}}, "required": ["né"]}
+    g = JsonGrammar(Schema.from_json(schema))
+    raw = json.dumps({"né": "é✓"}, ensure_ascii=False, separators=(",", ":"))
+    assert g.is_complete(raw) and all(g.accepts_prefix(raw[:i]) for i in range(len(raw) + 1))
+    assert g.is_complete('{"né":"\\u00e9\\u2713"}')
+    assert not g.accepts_prefix('{"né":"è')
+    vocab = ['{"', "né", '":', '"', "é", "✓", "è", "\\u00e9", "\\u2713", "}", "plain", "3"]
+    proc = JsonSchemaProcessor(schema, vocab)
+    for text in ("", '{"né":', '{"né":"', '{"né":"é', '{"né":"\\u00e9'):
+        proc.text = text
+        assert torch.equal(proc.mask().allowed, proc._mask_py().allowed), text
+    proc.text = '{"né":"'
+    allowed = {vocab[i] for i, ok in enumerate(proc.mask().allowed.tolist()) if ok}
+    assert {"é", "\\u00e9", "plain"} <= allowed and "è" not in allowed and "✓" not in allowed
