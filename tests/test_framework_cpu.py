@@ -455,3 +455,26 @@ def test_adafactor_matches_the_transformers_implementation(kw):
         a.step()
         b.step()
     assert max(float((p - q).abs().max()) for p, q in zip(pa, pb)) < 2e-6
+
+
+def test_tensorboard_event_files_are_read_by_the_tensorboard_package(tmp_path):
+    """Scalars, grouped scalars, a histogram and a text record, written by ``TensorBoardWriter`` and read back by TensorBoard's own event
+    loader (which checks the record framing and both checksums)."""
+    pytest.importorskip("tensorboard")
+    from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+    from ferrotorch_b200.train import TensorBoardWriter
+    w = TensorBoardWriter(str(tmp_path))
+    for i in range(5):
+        w.add_scalar("loss", 1.0 / (i + 1), i)
+    w.add_scalars("m", {"a": 1.0, "b": 2.0}, 3)
+    w.add_histogram("h", torch.linspace(-2, 3, 1000), 1)
+    w.add_text("note", "hello ✓", 0)
+    w.close() if hasattr(w, "close") else w.flush()
+    ea = EventAccumulator(str(tmp_path), size_guidance={"histograms": 0, "tensors": 0, "scalars": 0})
+    ea.Reload()
+    tags = ea.Tags()
+    assert set(tags["scalars"]) == {"loss", "m/a", "m/b"} and tags["histograms"] == ["h"] and tags["tensors"] == ["note"]
+    assert [(e.step, round(e.value, 6)) for e in ea.Scalars("loss")] == [(i, round(1.0 / (i + 1), 6)) for i in range(5)]
+    h = ea.Histograms("h")[0].histogram_value
+    assert h.num == 1000 and abs(h.min + 2) < 1e-6 and abs(h.max - 3) < 1e-6 and abs(sum(h.bucket) - 1000) < 1e-6
+    assert ea.Tensors("note")[0].tensor_proto.string_val == ["hello ✓".encode()]
