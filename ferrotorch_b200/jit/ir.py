@@ -90,7 +90,9 @@ class IrGraph:
 
     def add_constant(self, t: torch.Tensor) -> IrValue:
         v = self.new_value(t.shape, t.dtype)
-        self.constants[v.id] = t.detach()
+        # A trainable leaf (a module's parameter) is kept as it is, so that a compiled module can be trained: gradients reach it through the
+        # eagerly evaluated nodes and through the recompute backward of the generated kernels. Anything else is cut from its history.
+        self.constants[v.id] = t if (t.requires_grad and t.is_leaf) else t.detach()
         return v
 
     def add_node(self, op: str, inputs: Sequence[int], out_specs: Sequence[Tuple[Sequence[int], Any]], **attrs) -> IrNode:

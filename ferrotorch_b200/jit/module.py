@@ -121,6 +121,37 @@ def split_at_breaks(g: IrGraph) -> List[GraphSegment]:
     return segs
 
 
+class _FusedWithGrad(torch.autograd.Function):
+    """A generated kernel inside a differentiated computation: the forward pass runs the kernel and keeps only its inputs; the backward pass
+    evaluates the region's body again with the interpreter under autograd (the region's intermediates are recomputed, not stored) and
+    differentiates that."""
+
+    @staticmethod
+    def forward(ctx, kernel, node, graph, *ins):
+        ctx.node, ctx.graph = node, graph
+        ctx.save_for_backward(*ins)
+        out = kernel([t.detach() for t in ins])
+        if isinstance(out, (tuple, list)):
+            outs = tuple(out)
+            ctx.mark_non_differentiable(*[o for o in outs if not (o.is_floating_point() or o.is_complex())])
+            return outs
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, *grad_outputs):
+        needs = ctx.needs_input_grad[3:]
+        with torch.enable_grad():
+            leaves = [t.detach().requires_grad_(bool(need) and (t.is_floating_point() or t.is_complex())) for t, need in zip(ctx.saved_tensors, needs)]
+            out = eval_node(ctx.node, leaves, ctx.graph)
+            outs = list(out) if isinstance(out, (tuple, list)) else [out]
+            pairs = [(o, go) for o, go in zip(outs, grad_outputs) if go is not None and isinstance(o, torch.Tensor) and o.requires_grad]
+            wanted = [leaf for leaf in leaves if leaf.requires_grad]
+            grads = torch.autograd.grad([o for o, _ in pairs], wanted, [go for _, go in pairs], allow_unused=True) if pairs and wanted else ()
+        it = iter(grads)
+        return (None, None, None, *[next(it, None) if leaf.requires_grad else None for leaf in leaves])
+
+
 class _Executable:
     """One optimised graph plus its compiled fused kernels."""
 
@@ -158,7 +189,10 @@ class _Executable:
             ins = [env[v] for v in n.inputs]
             k = self.kernels.get(n.id)
             if k is not None and (self.backend == "host" or any(t.is_cuda for t in ins)):
-                out = k(ins)
+                if torch.is_grad_enabled() and any(t.requires_grad for t in ins):
+                    out = _FusedWithGrad.apply(k, n, g, *ins)
+                else:
+                    out = k([t.detach() for t in ins])
                 self.stats.kernel_launches += 1
             else:
                 out = eval_node(n, ins, g)

@@ -39,6 +39,8 @@ def constant_folding(g: IrGraph) -> int:
     for n in g.topo_order():
         if n.op in ("opaque", "dropout", "fused") or not n.inputs:
             continue
+        if any(i in g.constants and g.constants[i].requires_grad for i in n.inputs):
+            continue                                   # a trainable parameter changes between calls: nothing computed from it is a constant
         if all(i in g.constants for i in n.inputs) and all(g.values[o].numel() <= _FOLD_LIMIT for o in n.outputs):
             out = eval_node(n, [g.constants[i] for i in n.inputs], g)
             outs = out if isinstance(out, (tuple, list)) else [out]

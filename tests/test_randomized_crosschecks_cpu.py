@@ -154,3 +154,35 @@ def test_random_schemas_accept_their_documents_and_both_mask_engines_agree():
         for cut in sorted({0, len(doc) // 3, len(doc) // 2, max(0, len(doc) - 1), len(doc)}):
             proc.text = doc[:cut]
             assert torch.equal(proc.mask().allowed, proc._mask_py().allowed), (schema, doc[:cut])
+
+
+def test_gradients_flow_through_generated_kernels_and_into_module_parameters():
+    """A compiled function differentiates like the eager one although its fused region runs as a generated kernel, and a compiled module
+    trains: its parameters receive gradients and the optimiser's in-place updates are seen by the next call."""
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(0)
+    f = lambda x, w1, b1, w2: (F.gelu(x @ w1 + b1) * torch.sigmoid(x @ w1) @ w2).pow(2).mean()      # noqa: E731
+    xs = [torch.randn(8, 16, generator=g), torch.randn(16, 32, generator=g), torch.randn(32, generator=g), torch.randn(32, 4, generator=g)]
+    a = [t.clone().requires_grad_(True) for t in xs]
+    b = [t.clone().requires_grad_(True) for t in xs]
+    compiled = jit.compile(f, example_inputs=a)
+    out, ref = compiled(*a), f(*b)
+    assert compiled.stats.fused_kernels >= 1 and compiled.stats.kernel_launches >= 1
+    out.backward(); ref.backward()
+    for p, q in zip(a, b):
+        torch.testing.assert_close(p.grad, q.grad, rtol=1e-4, atol=1e-5)
+
+    torch.manual_seed(0)
+    mine = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.GELU(), torch.nn.Linear(8, 1))
+    eager = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.GELU(), torch.nn.Linear(8, 1))
+    eager.load_state_dict(mine.state_dict())
+    cm = jit.compile(mine, example_inputs=[torch.randn(5, 4)])
+    o1, o2 = torch.optim.SGD(mine.parameters(), lr=0.1), torch.optim.SGD(eager.parameters(), lr=0.1)
+    x, y = torch.randn(32, 4, generator=g), torch.randn(32, 1, generator=g)
+    for _ in range(10):
+        o1.zero_grad(); l1 = ((cm(x) - y) ** 2).mean(); l1.backward(); o1.step()
+        o2.zero_grad(); l2 = ((eager(x) - y) ** 2).mean(); l2.backward(); o2.step()
+    assert all(p.grad is not None for p in mine.parameters())
+    torch.testing.assert_close(l1, l2, rtol=1e-5, atol=1e-6)
+    with torch.no_grad():
+        torch.testing.assert_close(cm(x), eager(x), rtol=1e-5, atol=1e-6)
