@@ -67,6 +67,7 @@ class IrNode:
 
 class IrGraph:
     def __init__(self):
+        self.mutations: List[str] = []          # in-place operations seen while tracing (names); a non-empty list sends the caller to eager execution
         self.values: Dict[int, IrValue] = {}
         self.nodes: Dict[int, IrNode] = {}
         self.inputs: List[int] = []

@@ -152,6 +152,18 @@ class _FusedWithGrad(torch.autograd.Function):
         return (None, None, None, *[next(it, None) if leaf.requires_grad else None for leaf in leaves])
 
 
+class _EagerExecutable:
+    """A function that writes into tensors in place (into an input, through a view, or between two reads of one tensor) is run as written:
+    the value graph has no faithful form for such writes. The traced graph is kept for inspection."""
+
+    def __init__(self, fn: Callable, g: IrGraph):
+        self.fn, self.g = fn, g
+
+    def run(self, inputs: Sequence[torch.Tensor]):
+        out = self.fn(*inputs)
+        return [out] if isinstance(out, torch.Tensor) else list(out)
+
+
 class _Executable:
     """One optimised graph plus its compiled fused kernels."""
 
@@ -239,8 +251,13 @@ class CompiledFunction:
         elif self.shape_env is not None:
             for spec, t in zip(self.dynamic_dims, inputs):
                 self.shape_env.bind(spec, t.shape)
-        g = trace(self.fn, inputs)
+        g = trace(self.fn, [t.clone() if isinstance(t, torch.Tensor) else t for t in inputs])    # copies: tracing runs the function once
         self.stats.traces += 1
+        if g.mutations:
+            ex = _EagerExecutable(self.fn, g)
+            self.stats.graph_breaks += 1
+            self.cache[sig] = ex
+            return ex
         passes.optimize(g, fuse=self.fuse)
         ex = _Executable(g, self._backend_for(inputs), self.stats)
         self.cache[sig] = ex

@@ -73,6 +73,11 @@ class _Recorder(TorchDispatchMode):
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         kwargs = kwargs or {}
         out = func(*args, **kwargs)
+        schema = getattr(func, "_schema", None)
+        if schema is not None and schema.is_mutable and not any(k in str(func) for k in ("bernoulli_", "uniform_", "normal_", "random_", "exponential_")):
+            # An operation that writes into one of its arguments. The graph is a dataflow of values: a write through a view, into an input,
+            # or between two reads of the same tensor has no faithful form in it, so the caller runs such a function eagerly.
+            self.g.mutations.append(str(func))
         try:
             self.record(func, args, kwargs, out)
         except _Unsupported:

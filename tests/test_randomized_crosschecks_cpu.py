@@ -186,3 +186,32 @@ def test_gradients_flow_through_generated_kernels_and_into_module_parameters():
     torch.testing.assert_close(l1, l2, rtol=1e-5, atol=1e-6)
     with torch.no_grad():
         torch.testing.assert_close(cm(x), eager(x), rtol=1e-5, atol=1e-6)
+
+
+def test_functions_that_write_in_place_run_as_written():
+    """Writes into a copy, through a view, into an intermediate and into an input: the compiled callable returns what the function returns
+    and leaves (or changes) the caller's tensors exactly as the function does, once per call."""
+    def into_copy(x):
+        y = x.clone(); y.add_(1.0); y.mul_(2.0)
+        return y
+
+    def through_view(x):
+        y = x.clone(); y[:, 0] = 0.0
+        return y
+
+    def into_intermediate(x):
+        y = x + 0.5
+        return y.relu_()
+
+    def into_input(x):
+        x.add_(1.0)
+        return x * 2
+
+    for fn in (into_copy, through_view, into_intermediate, into_input):
+        compiled = jit.compile(fn, example_inputs=[torch.randn(3, 4)])
+        x = torch.randn(3, 4, generator=torch.Generator().manual_seed(1))
+        mine, theirs = x.clone(), x.clone()
+        for _ in range(2):
+            torch.testing.assert_close(compiled(mine), fn(theirs))
+            torch.testing.assert_close(mine, theirs)
+        assert compiled.stats.graph_breaks >= 1 and compiled.graph_for(x).mutations
