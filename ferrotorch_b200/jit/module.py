@@ -228,6 +228,9 @@ class CompiledFunction:
         self.shape_env = ShapeEnv() if dynamic_dims is not None else None
 
     def _sig(self, inputs) -> Tuple:
+        for t in inputs:
+            if not isinstance(t, torch.Tensor):
+                raise InvalidArgument(f"compiled callables take tensors; got {type(t).__name__} (close over Python numbers, or pass them as 0-d tensors)")
         return tuple((tuple(t.shape), t.dtype, t.device.type) for t in inputs)
 
     def _backend_for(self, inputs) -> str:
@@ -251,7 +254,14 @@ class CompiledFunction:
         elif self.shape_env is not None:
             for spec, t in zip(self.dynamic_dims, inputs):
                 self.shape_env.bind(spec, t.shape)
-        g = trace(self.fn, [t.clone() if isinstance(t, torch.Tensor) else t for t in inputs])    # copies: tracing runs the function once
+        owner = self.fn if isinstance(self.fn, torch.nn.Module) else getattr(self.fn, "__self__", None)
+        kept = [(b, b.detach().clone()) for b in owner.buffers()] if isinstance(owner, torch.nn.Module) else []
+        try:
+            g = trace(self.fn, [t.clone() if isinstance(t, torch.Tensor) else t for t in inputs])    # copies: tracing runs the function once
+        finally:
+            with torch.no_grad():
+                for b, before in kept:             # running statistics and other buffers as they were before the tracing run
+                    b.copy_(before)
         self.stats.traces += 1
         if g.mutations:
             ex = _EagerExecutable(self.fn, g)

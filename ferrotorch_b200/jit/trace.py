@@ -41,6 +41,7 @@ class _Recorder(TorchDispatchMode):
         super().__init__()
         self.g, self.env = graph, env          # env: id(tensor) -> value id
         self.keep: List[torch.Tensor] = []     # keeps traced tensors alive so ids stay unique
+        self.saved: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}      # id(tensor written in place) -> (tensor, its content before the first write)
 
     # -- helpers
     def vid(self, t: torch.Tensor) -> int:
@@ -72,12 +73,20 @@ class _Recorder(TorchDispatchMode):
     # -- dispatch
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         kwargs = kwargs or {}
-        out = func(*args, **kwargs)
         schema = getattr(func, "_schema", None)
-        if schema is not None and schema.is_mutable and not any(k in str(func) for k in ("bernoulli_", "uniform_", "normal_", "random_", "exponential_")):
+        if schema is not None and (schema.is_mutable or any(a.alias_info is not None and a.alias_info.is_write for a in schema.arguments)) and not any(k in str(func) for k in ("bernoulli_", "uniform_", "normal_", "random_", "exponential_")):
             # An operation that writes into one of its arguments. The graph is a dataflow of values: a write through a view, into an input,
             # or between two reads of the same tensor has no faithful form in it, so the caller runs such a function eagerly.
             self.g.mutations.append(str(func))
+            # Tracing must leave no trace: what is about to be overwritten (a module's running statistics, a captured buffer, an input) is
+            # kept and put back when the trace ends.
+            named = list(zip(args, schema.arguments)) + [(kwargs[spec.name], spec) for spec in schema.arguments if spec.name in kwargs]
+            for a, spec in named:
+                if isinstance(a, torch.Tensor) and spec.alias_info is not None and spec.alias_info.is_write:
+                    base = a._base if a._base is not None else a
+                    if id(base) not in self.saved:
+                        self.saved[id(base)] = (base, base.clone())
+        out = func(*args, **kwargs)
         try:
             self.record(func, args, kwargs, out)
         except _Unsupported:
@@ -232,8 +241,16 @@ def trace(fn: Callable, example_inputs: Sequence[torch.Tensor]) -> IrGraph:
             raise InvalidArgument("trace inputs must be tensors")
         env[id(t)] = g.add_input(t.shape, t.dtype).id
     rec = _Recorder(g, env)
-    with torch.no_grad(), rec:
-        out = fn(*example_inputs)
+    # Some primitives update an argument without saying so in their signature (batch normalisation and its running statistics), so a
+    # module's buffers are kept as a whole.
+    buffers = [(b, b.clone()) for b in fn.buffers()] if isinstance(fn, torch.nn.Module) else []
+    try:
+        with torch.no_grad(), rec:
+            out = fn(*example_inputs)
+    finally:
+        with torch.no_grad():
+            for base, before in list(rec.saved.values()) + buffers:
+                base.copy_(before)
     outs = [out] if isinstance(out, torch.Tensor) else list(out)
     ids = []
     for o in outs:

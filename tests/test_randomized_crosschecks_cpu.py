@@ -215,3 +215,18 @@ def test_functions_that_write_in_place_run_as_written():
             torch.testing.assert_close(compiled(mine), fn(theirs))
             torch.testing.assert_close(mine, theirs)
         assert compiled.stats.graph_breaks >= 1 and compiled.graph_for(x).mutations
+
+
+def test_tracing_leaves_module_state_untouched_and_batch_norm_trains_like_eager():
+    torch.manual_seed(0)
+    mine, eager = torch.nn.BatchNorm1d(4), torch.nn.BatchNorm1d(4)
+    compiled = jit.compile(mine, example_inputs=[torch.randn(8, 4)])
+    assert int(mine.num_batches_tracked) == 0 and float(mine.running_mean.abs().sum()) == 0.0
+    for _ in range(3):
+        x = torch.randn(8, 4)
+        torch.testing.assert_close(compiled(x), eager(x))
+    assert int(mine.num_batches_tracked) == int(eager.num_batches_tracked) == 3
+    torch.testing.assert_close(mine.running_mean, eager.running_mean)
+    torch.testing.assert_close(mine.running_var, eager.running_var)
+    with pytest.raises(Exception, match="take tensors"):
+        jit.compile(lambda x, s: x * s, example_inputs=[torch.ones(3), 2.5])
